@@ -1,0 +1,213 @@
+/*
+ * qmk_b200.h -- C ABI of the B200 (sm_100a) decode megakernel library, libqmk_b200.so.
+ *
+ * This is the drop-in boundary for the `--route mk` decode path of QiMeng-MegaKernel.
+ * The reference binds one pybind11 function per model,
+ *     mk(instructions, hidden_states, q_post_rope, k_cache, v_cache, attn_out,
+ *        attn_lse_intermediates, attn_out_intermediates, silu_out, logits,
+ *        attn_norm_weights, qkv_weights, rope_cos, rope_sin, o_proj_weights,
+ *        mlp_norm_weights, up_proj_weights, gate_proj_weights, down_proj_weights,
+ *        head_norm_weights, head_weights, barriers, pos_id, attn_scale, rms_norm_eps)
+ * (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/pybind.cpp:11-39,
+ *  mk.h:8-31, host launcher mk.cu:97-198).  Here the same tensors are passed once as raw
+ * device pointers (weights at create time, per-request state at bind time) and each decode
+ * step is one call that launches one persistent kernel.  No torch / pybind types cross
+ * this boundary; every entry point returns 0 or a negative qmk_error code.
+ *
+ * The library owns its scheduler: there is no `instructions` tensor and no `barriers`
+ * tensor to zero between steps (the reference's STATIC_MEGAKERNEL contract,
+ * qimeng_megakernel/models/LLM/decode.py:609-642, 688-689, 1383-1384).
+ *
+ * Threading: a handle is not thread-safe.  One handle per (device, request stream).
+ */
+#ifndef QMK_B200_H
+#define QMK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMK_ABI_VERSION 1
+
+/* Error codes (negative).  qmk_strerror() gives the text. */
+enum qmk_error {
+  QMK_OK = 0,
+  QMK_ERR_INVALID_ARG = -1,      /* null pointer, bad size, misaligned pointer            */
+  QMK_ERR_UNSUPPORTED_MODEL = -2, /* descriptor does not match a compiled specialisation   */
+  QMK_ERR_CUDA = -3,             /* a CUDA runtime call failed (see qmk_last_cuda_error)  */
+  QMK_ERR_DEVICE = -4,           /* not an sm_100 device, or too few SMs / shared memory  */
+  QMK_ERR_NOT_BOUND = -5,        /* decode called before qmk_bind_state                   */
+  QMK_ERR_POSITION = -6,         /* pos_id outside the bound KV cache or RoPE table       */
+  QMK_ERR_DEVICE_TIMEOUT = -7,   /* a bounded device-side wait expired (see qmk_status)   */
+  QMK_ERR_OOM = -8               /* scratch allocation failed                             */
+};
+
+/* Architecture families (selects epilogue variants). */
+enum qmk_arch {
+  QMK_ARCH_LLAMA = 0            /* RMSNorm -> QKV -> interleaved RoPE -> GQA -> SwiGLU    */
+};
+
+/*
+ * Model descriptor.  Mirrors LlamaConfig of the reference
+ * (.../A100/single_batch/decode_schedule/model_config.py:4-17).  hidden_size,
+ * intermediate_size, head counts and head_dim must match a compiled specialisation;
+ * num_layers and vocab_size are free runtime values.
+ */
+typedef struct qmk_model_desc {
+  int32_t abi_version;       /* QMK_ABI_VERSION */
+  int32_t arch;              /* enum qmk_arch */
+  int32_t num_layers;
+  int32_t hidden_size;
+  int32_t intermediate_size;
+  int32_t num_attention_heads;
+  int32_t num_key_value_heads;
+  int32_t head_dim;
+  int32_t vocab_size;
+  int32_t rope_rows;         /* rows of rope_cos / rope_sin (max positions)                */
+  float rms_norm_eps;
+  float attn_scale;          /* 1/sqrt(head_dim), as the reference passes it (mk_kernel.py:61) */
+} qmk_model_desc;
+
+/*
+ * Weights: device pointers, bf16 row-major unless noted, layouts exactly as the reference's
+ * Globals (decode_schedule/globs.py:13-24):
+ *   attn_norm [L,H]  qkv [L,(NH+2*NKV)*HD,H] (Q and K rows interleaved per head,
+ *   qimeng_megakernel/models/LLM/llama/preprocess.py:57-83)  o_proj [L,H,NH*HD]
+ *   mlp_norm [L,H]  up/gate [L,I,H]  down [L,H,I]  lm_head_norm [H]  lm_head [V,H]
+ *   rope_cos/rope_sin [rope_rows,HD] fp32, interleaved (preprocess.py:31-44)
+ *   embed_tokens [V,H] (may alias lm_head; only read in token-input mode).
+ * All matrix pointers must be 16-byte aligned.  The library never frees them.
+ */
+typedef struct qmk_weight_ptrs {
+  const void* attn_norm;
+  const void* qkv;
+  const void* o_proj;
+  const void* mlp_norm;
+  const void* up_proj;
+  const void* gate_proj;
+  const void* down_proj;
+  const void* lm_head_norm;
+  const void* lm_head;
+  const void* embed_tokens;
+  const float* rope_cos;
+  const float* rope_sin;
+} qmk_weight_ptrs;
+
+/*
+ * Per-request state: device pointers borrowed until the next qmk_bind_state / qmk_destroy
+ * (the reference re-allocates the KV cache between requests, decode.py:587-591, so binding
+ * is separate from creation).  bf16 unless noted:
+ *   hidden_states [H]  q_post_rope [NH*HD]  attn_out [NH*HD]  silu_out [I]  logits [V]
+ *   k_cache / v_cache [L, batch, kv_seq_len, NKV, HD] (K stored in the interleaved layout)
+ *   next_token: optional int64[1]; receives argmax(logits) (lowest index on ties).
+ *   token_in:   optional int64[1]; when non-null the step reads embed_tokens[*token_in]
+ *               instead of hidden_states as the layer-0 input (may alias next_token for a
+ *               device-resident greedy loop).
+ *   out_tokens: optional int64[]; when non-null the step also stores the argmax at
+ *               out_tokens[pos_id + 1] (the reference's output_tokens row, decode.py:1391-1395).
+ */
+typedef struct qmk_state_ptrs {
+  void* hidden_states;
+  void* q_post_rope;
+  void* k_cache;
+  void* v_cache;
+  void* attn_out;
+  void* silu_out;
+  void* logits;
+  int64_t* next_token;
+  const int64_t* token_in;
+  int64_t* out_tokens;
+  int64_t out_tokens_len;
+  int32_t batch;             /* 1 */
+  int32_t kv_seq_len;        /* S: allocated positions per sequence */
+} qmk_state_ptrs;
+
+/* Device-side status record, filled when a bounded wait expires. */
+typedef struct qmk_status {
+  int32_t code;      /* 0 = healthy; 1 = dependency-counter wait expired; 2 = weight-copy wait expired;
+                        3 = activation-staging wait expired */
+  int32_t sm;        /* CTA (one per SM) that reported */
+  int32_t warp;
+  int32_t phase;     /* global phase index: layer*5 + {0 qkv,1 attn,2 oproj,3 upgate,4 down}; 5*L = lm head */
+  uint32_t seen;
+  uint32_t expected;
+  int32_t detail;
+  int32_t reserved;
+} qmk_status;
+
+typedef struct qmk_handle qmk_handle;
+
+/* Phase kinds inside one layer; phase index = layer * QMK_PHASES_PER_LAYER + kind, LM head last. */
+#define QMK_PHASES_PER_LAYER 5
+#define QMK_PHASE_QKV 0
+#define QMK_PHASE_ATTN 1
+#define QMK_PHASE_OPROJ 2
+#define QMK_PHASE_UPGATE 3
+#define QMK_PHASE_DOWN 4
+
+/* Replaces get_mk()/module load (decode_schedule/mk_kernel.py:40-53): validates the descriptor
+ * and the device, allocates library-owned scratch (dependency counters, split-KV partials,
+ * status words) on `device`. */
+int qmk_create(const qmk_model_desc* desc, const qmk_weight_ptrs* weights, int device, qmk_handle** out);
+
+/* Replaces the per-call tensor marshalling of call_mk (mk_kernel.py:56-94). */
+int qmk_bind_state(qmk_handle* h, const qmk_state_ptrs* state);
+
+/* Replaces one mk(...) launch (mk.cu:97-198): one persistent kernel on `cuda_stream`
+ * (a cudaStream_t; 0 = legacy default stream like the A100 reference, mk.cu:191).
+ * Asynchronous; pos_id is the position of the token being fed (KV length becomes pos_id+1). */
+int qmk_decode_step(qmk_handle* h, int32_t pos_id, void* cuda_stream);
+
+/* Per-op isolation, the counterpart of the reference's run_instructions() with a filtered
+ * instruction list (mk_kernel.py:97-111; verifier barrier pre-fill, verifier/common/barrier_fill.py:67-147):
+ * runs phases [phase_begin, phase_end).  mode 0: one launch per phase, ordered by the stream,
+ * no device-side dependency waits.  mode 1: one persistent launch with dependency counters. */
+int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin, int32_t phase_end, int32_t mode,
+                   void* cuda_stream);
+
+/* Greedy decode with HOST token buffers (the end-to-end form of FusedGenerator.generate_greedy_fast,
+ * decode.py:1340-1435): for i in [0,n_steps): copies host_tokens[first_pos+i] to the device, runs one
+ * step at position first_pos+i, copies the argmax back into host_tokens[first_pos+i+1] before the
+ * next step.  If teacher_forced != 0 the device never reads a generated token: inputs always come
+ * from host_tokens as given and the argmax is written to host_argmax[i] instead.
+ * Synchronous on `cuda_stream`. */
+int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t host_tokens_len, int32_t first_pos,
+                      int32_t n_steps, int32_t teacher_forced, int64_t* host_argmax, void* cuda_stream);
+
+/* Reads the device status record (synchronises the stream it was last launched on). */
+int qmk_poll_status(qmk_handle* h, qmk_status* out);
+
+/* Device-side wait budget in SM clock cycles (default 2e9, about one second). */
+int qmk_set_timeout_cycles(qmk_handle* h, int64_t cycles);
+
+/* Debug knob used by the failure-detection test: when set, qmk_run_phases(mode 1) also waits for the
+ * dependency of its first phase, which nothing publishes, so the bounded wait must expire. */
+int qmk_set_wait_first_dependency(qmk_handle* h, int32_t on);
+
+/* Optional device timeline (the counterpart of the reference's ENABLE_PROFILING clock64 buffer,
+ * qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/multi_batch/decode_kernel/profiling.cuh:7-35, selected
+ * at run time instead of compile time).  device_buffer: uint64 [CTAs, phases, 8] globaltimer nanoseconds,
+ * slots 0 dependency satisfied, 1 activations staged, 2 first worker enters, 5 first worker leaves,
+ * 6 last worker leaves.  NULL switches tracing off. */
+int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes);
+
+/* Algorithmic HBM bytes of one decode step at KV length pos_id+1 (weights + KV read + KV write). */
+int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id);
+
+/* Number of kernels the library has launched through this handle. */
+int64_t qmk_launch_count(const qmk_handle* h);
+
+/* Launch geometry actually used: CTAs (= SMs), threads per CTA, dynamic shared memory bytes. */
+int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes);
+
+void qmk_destroy(qmk_handle* h);
+const char* qmk_strerror(int code);
+const char* qmk_last_cuda_error(const qmk_handle* h);
+int qmk_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QMK_B200_H */

@@ -1,0 +1,396 @@
+// Host side of libqmk_b200.so: the C ABI declared in include/qmk_b200.h.
+// Plain CUDA runtime, no torch / pybind types.  The reference's host launcher is
+// qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/mk.cu:97-198
+// (fills a globals POD from tensors, sets the dynamic shared-memory limit, launches, prints errors);
+// here errors are returned, the stream is explicit and scratch is owned by the handle.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/qmk_b200.h"
+#include "qmk_megakernel.cuh"
+
+using namespace qmk;
+using Shape = ShapeLlama1B;
+
+struct qmk_handle {
+  qmk_model_desc desc;
+  qmk_weight_ptrs w;
+  qmk_state_ptrs st;
+  bool bound;
+  int device;
+  int n_sm;
+  unsigned epoch;
+  long long timeout_cycles;
+  int wait_first;
+  long long launches;
+  cudaStream_t last_stream;
+  char cuda_err[256];
+  // scratch (one allocation)
+  unsigned char* scratch;
+  size_t scratch_bytes;
+  float* part_o;
+  float* part_ml;
+  unsigned* counters;
+  size_t counters_bytes;
+  unsigned* tickets;
+  unsigned long long* argmax_key;
+  unsigned* status;
+  long long* d_tok;   // [2]: token fed, token produced (host-buffer generate path)
+  unsigned long long* trace;
+};
+
+static int cuda_fail(qmk_handle* h, cudaError_t e, const char* what) {
+  if (h) snprintf(h->cuda_err, sizeof(h->cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return QMK_ERR_CUDA;
+}
+#define QMK_CUDA(h, call)                                   \
+  do {                                                      \
+    cudaError_t e__ = (call);                               \
+    if (e__ != cudaSuccess) return cuda_fail(h, e__, #call); \
+  } while (0)
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+extern "C" int qmk_abi_version(void) { return QMK_ABI_VERSION; }
+
+extern "C" const char* qmk_strerror(int code) {
+  switch (code) {
+    case QMK_OK: return "ok";
+    case QMK_ERR_INVALID_ARG: return "invalid argument (null or misaligned pointer, bad size)";
+    case QMK_ERR_UNSUPPORTED_MODEL: return "model descriptor matches no compiled specialisation";
+    case QMK_ERR_CUDA: return "CUDA runtime call failed";
+    case QMK_ERR_DEVICE: return "device is not sm_100 or lacks SMs / shared memory";
+    case QMK_ERR_NOT_BOUND: return "no request state bound (call qmk_bind_state)";
+    case QMK_ERR_POSITION: return "position outside the bound KV cache or RoPE table";
+    case QMK_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+    case QMK_ERR_OOM: return "scratch allocation failed";
+    default: return "unknown error";
+  }
+}
+
+extern "C" const char* qmk_last_cuda_error(const qmk_handle* h) { return h ? h->cuda_err : ""; }
+
+static int reset_scratch(qmk_handle* h, cudaStream_t s) {
+  QMK_CUDA(h, cudaMemsetAsync(h->scratch, 0, h->scratch_bytes, s));
+  h->epoch = 0;
+  return QMK_OK;
+}
+
+extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int device, qmk_handle** out) {
+  if (!d || !w || !out) return QMK_ERR_INVALID_ARG;
+  *out = nullptr;
+  if (d->abi_version != QMK_ABI_VERSION) return QMK_ERR_INVALID_ARG;
+  if (d->arch != QMK_ARCH_LLAMA || d->hidden_size != Shape::H || d->intermediate_size != Shape::I ||
+      d->num_attention_heads != Shape::NH || d->num_key_value_heads != Shape::NKV || d->head_dim != Shape::HD)
+    return QMK_ERR_UNSUPPORTED_MODEL;
+  if (d->num_layers < 0 || d->num_layers > 1024 || d->vocab_size < 1 || d->rope_rows < 1) return QMK_ERR_INVALID_ARG;
+  if (!(d->rms_norm_eps > 0.f) || !(d->attn_scale > 0.f)) return QMK_ERR_INVALID_ARG;
+  const void* ptrs[] = {w->attn_norm, w->qkv, w->o_proj, w->mlp_norm, w->up_proj, w->gate_proj,
+                        w->down_proj, w->lm_head_norm, w->lm_head, w->rope_cos, w->rope_sin};
+  for (const void* p : ptrs)
+    if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
+  if (w->embed_tokens && !aligned16(w->embed_tokens)) return QMK_ERR_INVALID_ARG;
+
+  qmk_handle* h = new (std::nothrow) qmk_handle();
+  if (!h) return QMK_ERR_OOM;
+  memset(h, 0, sizeof(*h));
+  h->desc = *d;
+  h->w = *w;
+  h->device = device;
+  h->timeout_cycles = 2000000000ll;
+  int rc = QMK_OK;
+  do {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaSetDevice"); break; }
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaGetDeviceProperties"); break; }
+    if (prop.major != 10 || (int)prop.sharedMemPerBlockOptin < SmemLayout<Shape>::kTotal ||
+        prop.multiProcessorCount < 1 || !prop.cooperativeLaunch) {
+      rc = QMK_ERR_DEVICE;
+      break;
+    }
+    h->n_sm = prop.multiProcessorCount;
+    e = cudaFuncSetAttribute(qmk_decode_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout<Shape>::kTotal);
+    if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaFuncSetAttribute"); break; }
+    const size_t nph = (size_t)num_phases(d->num_layers);
+    const size_t b_part_o = align_up((size_t)Shape::NH * kMaxSplits * Shape::HD * 4, 256);
+    const size_t b_part_ml = align_up((size_t)Shape::NH * kMaxSplits * 2 * 4, 256);
+    const size_t b_counters = align_up(nph * kCounterShards * kCounterStrideWords * 4, 256);
+    const size_t b_tickets = 512, b_argmax = 256, b_status = 256, b_tok = 256;
+    h->scratch_bytes = b_part_o + b_part_ml + b_counters + b_tickets + b_argmax + b_status + b_tok;
+    e = cudaMalloc((void**)&h->scratch, h->scratch_bytes);
+    if (e != cudaSuccess) { rc = QMK_ERR_OOM; cuda_fail(h, e, "cudaMalloc"); break; }
+    unsigned char* q = h->scratch;
+    h->part_o = (float*)q; q += b_part_o;
+    h->part_ml = (float*)q; q += b_part_ml;
+    h->counters = (unsigned*)q; q += b_counters;
+    h->counters_bytes = b_counters;
+    h->tickets = (unsigned*)q; q += b_tickets;
+    h->argmax_key = (unsigned long long*)q; q += b_argmax;
+    h->status = (unsigned*)q; q += b_status;
+    h->d_tok = (long long*)q;
+    e = cudaMemset(h->scratch, 0, h->scratch_bytes);
+    if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaMemset"); break; }
+  } while (0);
+  if (rc != QMK_OK) {
+    if (h->scratch) cudaFree(h->scratch);
+    delete h;
+    return rc;
+  }
+  *out = h;
+  return QMK_OK;
+}
+
+extern "C" void qmk_destroy(qmk_handle* h) {
+  if (!h) return;
+  cudaSetDevice(h->device);
+  if (h->scratch) cudaFree(h->scratch);
+  delete h;
+}
+
+extern "C" int qmk_bind_state(qmk_handle* h, const qmk_state_ptrs* s) {
+  if (!h || !s) return QMK_ERR_INVALID_ARG;
+  if (s->batch != 1 || s->kv_seq_len < 1) return QMK_ERR_INVALID_ARG;
+  void* ptrs[] = {s->hidden_states, s->q_post_rope, s->k_cache, s->v_cache, s->attn_out, s->silu_out, s->logits};
+  for (void* p : ptrs)
+    if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
+  if (s->token_in && !h->w.embed_tokens) return QMK_ERR_INVALID_ARG;
+  if (s->out_tokens && s->out_tokens_len < 1) return QMK_ERR_INVALID_ARG;
+  h->st = *s;
+  h->bound = true;
+  return QMK_OK;
+}
+
+static void fill_params(const qmk_handle* h, Params& p, int pos) {
+  memset(&p, 0, sizeof(p));
+  const qmk_weight_ptrs& w = h->w;
+  const qmk_state_ptrs& s = h->st;
+  p.attn_norm = (const uint16_t*)w.attn_norm;
+  p.qkv = (const uint16_t*)w.qkv;
+  p.o_proj = (const uint16_t*)w.o_proj;
+  p.mlp_norm = (const uint16_t*)w.mlp_norm;
+  p.up = (const uint16_t*)w.up_proj;
+  p.gate = (const uint16_t*)w.gate_proj;
+  p.down = (const uint16_t*)w.down_proj;
+  p.lm_norm = (const uint16_t*)w.lm_head_norm;
+  p.lm_head = (const uint16_t*)w.lm_head;
+  p.embed = (const uint16_t*)w.embed_tokens;
+  p.rope_cos = w.rope_cos;
+  p.rope_sin = w.rope_sin;
+  p.hidden = (uint16_t*)s.hidden_states;
+  p.q_post_rope = (uint16_t*)s.q_post_rope;
+  p.k_cache = (uint16_t*)s.k_cache;
+  p.v_cache = (uint16_t*)s.v_cache;
+  p.attn_out = (uint16_t*)s.attn_out;
+  p.silu_out = (uint16_t*)s.silu_out;
+  p.logits = (uint16_t*)s.logits;
+  p.next_token = (long long*)s.next_token;
+  p.token_in = (const long long*)s.token_in;
+  p.out_tokens = (long long*)s.out_tokens;
+  p.out_tokens_len = s.out_tokens_len;
+  p.kv_seq_stride = (long long)Shape::NKV * Shape::HD;
+  p.kv_layer_stride = (long long)s.batch * s.kv_seq_len * p.kv_seq_stride;
+  p.part_o = h->part_o;
+  p.part_ml = h->part_ml;
+  p.counters = h->counters;
+  p.tickets = h->tickets;
+  p.argmax_key = h->argmax_key;
+  p.status = h->status;
+  p.trace = h->trace;
+  p.num_layers = h->desc.num_layers;
+  p.vocab = h->desc.vocab_size;
+  p.pos = pos;
+  p.eps = h->desc.rms_norm_eps;
+  p.scale_log2e = h->desc.attn_scale * 1.4426950408889634f;
+  p.timeout_cycles = h->timeout_cycles;
+  p.wait_first = 0;
+}
+
+static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)h->n_sm);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = SmemLayout<Shape>::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another
+  attr[0].val.cooperative = p.sync ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p));
+  h->launches++;
+  h->last_stream = stream;
+  return QMK_OK;
+}
+
+static int check_step_args(const qmk_handle* h, int pos) {
+  if (!h) return QMK_ERR_INVALID_ARG;
+  if (!h->bound) return QMK_ERR_NOT_BOUND;
+  if (pos < 0 || pos >= h->st.kv_seq_len || pos >= h->desc.rope_rows) return QMK_ERR_POSITION;
+  return QMK_OK;
+}
+
+static int step_with(qmk_handle* h, Params& p, cudaStream_t stream) {
+  if (h->epoch >= (1u << 24)) {
+    int rc = reset_scratch(h, stream);
+    if (rc) return rc;
+  }
+  p.phase_begin = 0;
+  p.phase_end = num_phases(p.num_layers);
+  p.sync = 1;
+  p.epoch = h->epoch;
+  int rc = launch(h, p, stream);
+  if (rc == QMK_OK) h->epoch++;
+  return rc;
+}
+
+extern "C" int qmk_decode_step(qmk_handle* h, int32_t pos_id, void* cuda_stream) {
+  int rc = check_step_args(h, pos_id);
+  if (rc) return rc;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  Params p;
+  fill_params(h, p, pos_id);
+  return step_with(h, p, (cudaStream_t)cuda_stream);
+}
+
+extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin, int32_t phase_end, int32_t mode,
+                              void* cuda_stream) {
+  int rc = check_step_args(h, pos_id);
+  if (rc) return rc;
+  const int nph = num_phases(h->desc.num_layers);
+  if (phase_begin < 0 || phase_end > nph || phase_begin > phase_end || (mode != 0 && mode != 1))
+    return QMK_ERR_INVALID_ARG;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  Params p;
+  fill_params(h, p, pos_id);
+  if (mode == 0) {
+    for (int ph = phase_begin; ph < phase_end; ++ph) {
+      p.phase_begin = ph;
+      p.phase_end = ph + 1;
+      p.sync = 0;
+      rc = launch(h, p, stream);
+      if (rc) return rc;
+    }
+    return QMK_OK;
+  }
+  if (phase_begin == phase_end) return QMK_OK;
+  // A synchronised sub-range leaves the counters of other phases behind: run it on zeroed
+  // counters at epoch 0 and zero them again afterwards.
+  rc = reset_scratch(h, stream);
+  if (rc) return rc;
+  p.phase_begin = phase_begin;
+  p.phase_end = phase_end;
+  p.sync = 1;
+  p.epoch = 0;
+  p.wait_first = h->wait_first;
+  rc = launch(h, p, stream);
+  if (rc) return rc;
+  QMK_CUDA(h, cudaMemsetAsync(h->counters, 0, h->counters_bytes, stream));
+  h->epoch = 0;
+  return QMK_OK;
+}
+
+extern "C" int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t host_tokens_len, int32_t first_pos,
+                                 int32_t n_steps, int32_t teacher_forced, int64_t* host_argmax,
+                                 void* cuda_stream) {
+  if (!h || !host_tokens || n_steps < 0 || first_pos < 0) return QMK_ERR_INVALID_ARG;
+  if (!h->w.embed_tokens) return QMK_ERR_INVALID_ARG;
+  if (teacher_forced && !host_argmax) return QMK_ERR_INVALID_ARG;
+  const long long need = (long long)first_pos + n_steps + (teacher_forced ? 0 : 1);
+  if (need > host_tokens_len) return QMK_ERR_INVALID_ARG;
+  if (n_steps == 0) return QMK_OK;
+  int rc = check_step_args(h, first_pos + n_steps - 1);
+  if (rc) return rc;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  for (int i = 0; i < n_steps; ++i) {
+    const int pos = first_pos + i;
+    QMK_CUDA(h, cudaMemcpyAsync(h->d_tok, host_tokens + pos, sizeof(int64_t), cudaMemcpyHostToDevice, stream));
+    Params p;
+    fill_params(h, p, pos);
+    p.token_in = h->d_tok;
+    p.next_token = h->d_tok + 1;
+    p.out_tokens = nullptr;
+    rc = step_with(h, p, stream);
+    if (rc) return rc;
+    int64_t* dst = teacher_forced ? host_argmax + i : host_tokens + pos + 1;
+    QMK_CUDA(h, cudaMemcpyAsync(dst, h->d_tok + 1, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    QMK_CUDA(h, cudaStreamSynchronize(stream));
+  }
+  return QMK_OK;
+}
+
+extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
+  if (!h || !out) return QMK_ERR_INVALID_ARG;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
+  unsigned words[8];
+  QMK_CUDA(h, cudaMemcpy(words, h->status, sizeof(words), cudaMemcpyDeviceToHost));
+  out->code = (int32_t)words[kStCode];
+  out->sm = (int32_t)words[kStSm];
+  out->warp = (int32_t)words[kStWarp];
+  out->phase = (int32_t)words[kStPhase];
+  out->seen = words[kStSeen];
+  out->expected = words[kStExpected];
+  out->detail = (int32_t)words[kStDetail];
+  out->reserved = 0;
+  if (out->code != 0) {
+    // The aborted launch left counters and tickets mid-step: start over from a clean slate.
+    int rc = reset_scratch(h, h->last_stream);
+    if (rc) return rc;
+    QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
+    return QMK_ERR_DEVICE_TIMEOUT;
+  }
+  return QMK_OK;
+}
+
+extern "C" int qmk_set_timeout_cycles(qmk_handle* h, int64_t cycles) {
+  if (!h || cycles < 1000) return QMK_ERR_INVALID_ARG;
+  h->timeout_cycles = cycles;
+  return QMK_OK;
+}
+
+extern "C" int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes) {
+  if (!h) return QMK_ERR_INVALID_ARG;
+  if (device_buffer == nullptr) { h->trace = nullptr; return QMK_OK; }
+  const int64_t need = (int64_t)h->n_sm * num_phases(h->desc.num_layers) * 8 * 8;
+  if (bytes < need || (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) return QMK_ERR_INVALID_ARG;
+  h->trace = (unsigned long long*)device_buffer;
+  return QMK_OK;
+}
+
+extern "C" int qmk_set_wait_first_dependency(qmk_handle* h, int32_t on) {
+  if (!h) return QMK_ERR_INVALID_ARG;
+  h->wait_first = on ? 1 : 0;
+  return QMK_OK;
+}
+
+extern "C" int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id) {
+  if (!h) return 0;
+  const qmk_model_desc& d = h->desc;
+  const long long H = d.hidden_size, I = d.intermediate_size, QKV = Shape::QKV_ROWS, QD = Shape::QDIM;
+  const long long per_layer = 2 * (QKV * H + H * QD + 2 * I * H + H * I);
+  const long long lm = 2ll * d.vocab_size * H;
+  const long long kv_row = 2ll * Shape::NKV * Shape::HD * 2;   // K and V, bf16
+  const long long T = (long long)pos_id + 1;
+  return d.num_layers * per_layer + lm + d.num_layers * kv_row * T + d.num_layers * kv_row;
+}
+
+extern "C" int64_t qmk_launch_count(const qmk_handle* h) { return h ? h->launches : 0; }
+
+extern "C" int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes) {
+  if (!h) return QMK_ERR_INVALID_ARG;
+  if (ctas) *ctas = h->n_sm;
+  if (threads) *threads = kThreads;
+  if (smem_bytes) *smem_bytes = SmemLayout<Shape>::kTotal;
+  return QMK_OK;
+}

@@ -1,0 +1,63 @@
+// Kernel parameter block of the decode megakernel (plain data, passed by value as a
+// __grid_constant__).  Plays the role of the reference's LlamaGlobals POD
+// (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/globals.cuh:1-277)
+// without the CuTe views: raw pointers, strides in elements.
+#pragma once
+#include <stdint.h>
+
+namespace qmk {
+
+// Words of the device status record (mirrors qmk_status in the C ABI).
+enum StatusWord : int { kStCode = 0, kStSm = 1, kStWarp = 2, kStPhase = 3, kStSeen = 4, kStExpected = 5, kStDetail = 6 };
+enum StatusCode : int { kOkCode = 0, kErrCounterWait = 1, kErrCopyWait = 2, kErrStageWait = 3 };
+
+struct Params {
+  // ---- weights (bf16 as raw 16-bit words) ----
+  const uint16_t* attn_norm;     // [L, H]
+  const uint16_t* qkv;           // [L, QKV_ROWS, H]
+  const uint16_t* o_proj;        // [L, H, QDIM]
+  const uint16_t* mlp_norm;      // [L, H]
+  const uint16_t* up;            // [L, I, H]
+  const uint16_t* gate;          // [L, I, H]
+  const uint16_t* down;          // [L, H, I]
+  const uint16_t* lm_norm;       // [H]
+  const uint16_t* lm_head;       // [V, H]
+  const uint16_t* embed;         // [V, H]
+  const float* rope_cos;         // [rope_rows, HD]
+  const float* rope_sin;
+  // ---- request state ----
+  uint16_t* hidden;              // [H]
+  uint16_t* q_post_rope;         // [QDIM]
+  uint16_t* k_cache;             // [L, B, S, NKV, HD]
+  uint16_t* v_cache;
+  uint16_t* attn_out;            // [QDIM]
+  uint16_t* silu_out;            // [I]
+  uint16_t* logits;              // [V]
+  long long* next_token;         // optional
+  const long long* token_in;     // optional
+  long long* out_tokens;         // optional, written at [pos+1]
+  long long out_tokens_len;
+  long long kv_layer_stride;     // elements between layers (= B*S*NKV*HD)
+  long long kv_seq_stride;       // elements between positions (= NKV*HD)
+  // ---- library-owned scratch ----
+  float* part_o;                 // [NH, kMaxSplits, HD] un-normalised split-KV partial outputs
+  float* part_ml;                // [NH, kMaxSplits, 2]  (running max in log2 domain, sum)
+  unsigned* counters;            // [num_phases, 32 shards, 32 words]
+  unsigned* tickets;             // [NKV] split-KV arrival tickets + [32] lm-head ticket at tickets[64]
+  unsigned long long* argmax_key;  // packed (ordered logit bits << 32) | ~index
+  unsigned* status;              // [8] status words
+  unsigned long long* trace;     // optional [CTAs, num_phases, 8] globaltimer stamps (ns); null = off
+  // ---- scalars ----
+  int num_layers;
+  int vocab;
+  int pos;                       // position of the token being fed
+  int phase_begin, phase_end;    // phases executed by this launch
+  int sync;                      // 1: device-side dependency counters; 0: single phase, stream-ordered
+  int wait_first;                // 1: also wait for the dependency of phase_begin (debug / failure test)
+  unsigned epoch;                // completed synchronised steps since the counters were last zeroed
+  float eps;
+  float scale_log2e;             // attn_scale * log2(e)
+  long long timeout_cycles;      // bounded-wait budget
+};
+
+}  // namespace qmk

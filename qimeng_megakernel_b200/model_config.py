@@ -1,0 +1,71 @@
+"""Llama-family model config for the B200 decode schedule.
+
+Same class-attribute interface as the reference's LlamaConfig
+(qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_schedule/model_config.py:4-78),
+so host code that reads `ModelConfig.head_dim` etc. works unchanged.  The CUDA side takes these
+as a runtime descriptor checked against its compiled shapes instead of mirrored constexprs.
+"""
+from __future__ import annotations
+
+
+class LlamaConfig:
+    num_hidden_layers = 16
+    hidden_size = 2048
+    intermediate_size = 8192
+    head_dim = 64
+    num_attention_heads = 32
+    num_key_value_heads = 8
+    num_heads = num_attention_heads + num_key_value_heads * 2
+    qkv_out_dim = num_heads * head_dim
+    vocab_size = 128256
+    rms_norm_eps = 1e-5
+    rope_theta = 500000.0
+    # llama3 rope scaling (factor, low_freq_factor, high_freq_factor, original context); None = plain theta
+    rope_scaling = (32.0, 1.0, 4.0, 8192)
+    max_position_embeddings = 8192
+
+    _KEYS = ("num_hidden_layers", "hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
+             "num_key_value_heads", "vocab_size", "rms_norm_eps", "rope_theta", "rope_scaling",
+             "max_position_embeddings")
+
+    @classmethod
+    def update_from_dict(cls, config: dict) -> None:
+        cls.num_hidden_layers = config["num_hidden_layers"]
+        cls.hidden_size = config["hidden_size"]
+        cls.intermediate_size = config["intermediate_size"]
+        cls.num_attention_heads = config["num_attention_heads"]
+        cls.head_dim = config.get("head_dim") or (config["hidden_size"] // config["num_attention_heads"])
+        cls.num_key_value_heads = config.get("num_key_value_heads", cls.num_attention_heads)
+        cls.num_heads = cls.num_attention_heads + cls.num_key_value_heads * 2
+        cls.qkv_out_dim = cls.num_heads * cls.head_dim
+        cls.vocab_size = config["vocab_size"]
+        cls.rms_norm_eps = config.get("rms_norm_eps", 1e-5)
+        cls.rope_theta = float(config.get("rope_theta", 10000.0))
+        rs = config.get("rope_scaling")
+        if isinstance(rs, dict):
+            rs = (float(rs["factor"]), float(rs["low_freq_factor"]), float(rs["high_freq_factor"]),
+                  int(rs["original_max_position_embeddings"]))
+        cls.rope_scaling = tuple(rs) if rs else None
+        cls.max_position_embeddings = int(config.get("max_position_embeddings", 8192))
+
+    @classmethod
+    def update_from_hf(cls, config) -> None:
+        d = {k: getattr(config, k) for k in ("num_hidden_layers", "hidden_size", "intermediate_size",
+                                             "num_attention_heads", "vocab_size")}
+        for k in ("head_dim", "num_key_value_heads", "rms_norm_eps", "rope_theta", "rope_scaling",
+                  "max_position_embeddings"):
+            if getattr(config, k, None) is not None:
+                d[k] = getattr(config, k)
+        cls.update_from_dict(d)
+
+    @classmethod
+    def as_dict(cls) -> dict:
+        d = {k: getattr(cls, k) for k in cls._KEYS}
+        d["num_heads"] = cls.num_heads
+        d["qkv_out_dim"] = cls.qkv_out_dim
+        return d
+
+
+LLAMA_3_2_1B = dict(num_hidden_layers=16, hidden_size=2048, intermediate_size=8192, head_dim=64,
+                    num_attention_heads=32, num_key_value_heads=8, vocab_size=128256, rms_norm_eps=1e-5,
+                    rope_theta=500000.0, rope_scaling=(32.0, 1.0, 4.0, 8192), max_position_embeddings=8192)

@@ -1,0 +1,94 @@
+"""Seeded synthetic model and prompt: the stand-in for the checkpoints the reference loads.
+
+Every matrix ~ N(0, 0.02) in bf16, RMSNorm gains 1, embeddings tied to the LM head, prompt ids
+uniform over the vocabulary.  Q/K rows are generated directly in the interleaved layout (the
+distribution is invariant under the row permutation the reference applies at load,
+qimeng_megakernel/models/LLM/llama/load_weights.py:175-178).
+"""
+from __future__ import annotations
+
+import torch
+
+from .globs import Globals
+from .model_config import LlamaConfig
+from .rope import rope_tables_interleaved
+
+WEIGHT_NAMES = ("attn_norm_weights", "qkv_weights", "o_proj_weights", "mlp_norm_weights", "up_proj_weights",
+                "gate_proj_weights", "down_proj_weights", "lm_head_norm_weights", "lm_head_weights",
+                "embed_tokens", "rope_cos", "rope_sin")
+
+
+def make_weights(config: dict, seed: int = 0, device: str | torch.device = "cpu", std: float = 0.02,
+                 max_positions: int | None = None) -> dict:
+    """Seeded weights as a dict of tensors on `device` (generator lives on that device)."""
+    L, H, I = config["num_hidden_layers"], config["hidden_size"], config["intermediate_size"]
+    NH, NKV, HD, V = (config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"],
+                      config["vocab_size"])
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+
+    def mat(*shape):
+        out = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        # generate per leading slice in fp32 to bound the temporary
+        flat = out.view(shape[0], -1)
+        for i in range(shape[0]):
+            flat[i].copy_(torch.randn(flat.shape[1], generator=gen, device=dev, dtype=torch.float32) * std)
+        return out
+
+    w = {
+        "qkv_weights": mat(L, (NH + 2 * NKV) * HD, H),
+        "o_proj_weights": mat(L, H, NH * HD),
+        "up_proj_weights": mat(L, I, H),
+        "gate_proj_weights": mat(L, I, H),
+        "down_proj_weights": mat(L, H, I),
+        "attn_norm_weights": torch.ones(L, H, dtype=torch.bfloat16, device=dev),
+        "mlp_norm_weights": torch.ones(L, H, dtype=torch.bfloat16, device=dev),
+        "lm_head_norm_weights": torch.ones(H, dtype=torch.bfloat16, device=dev),
+    }
+    lm = torch.empty(V, H, dtype=torch.bfloat16, device=dev)
+    rows = 8192
+    for r0 in range(0, V, rows):
+        r1 = min(V, r0 + rows)
+        lm[r0:r1].copy_(torch.randn(r1 - r0, H, generator=gen, device=dev, dtype=torch.float32) * std)
+    w["lm_head_weights"] = lm
+    w["embed_tokens"] = lm                      # tied
+    cos, sin = rope_tables_interleaved(HD, max_positions or config.get("max_position_embeddings", 8192),
+                                       config.get("rope_theta", 10000.0), config.get("rope_scaling"))
+    w["rope_cos"], w["rope_sin"] = cos.to(dev), sin.to(dev)
+    return w
+
+
+def make_prompt(vocab_size: int, length: int = 16, seed: int = 1) -> torch.Tensor:
+    gen = torch.Generator()
+    gen.manual_seed(seed)
+    return torch.randint(0, vocab_size, (length,), generator=gen, dtype=torch.int64)
+
+
+def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | torch.device = "cuda") -> Globals:
+    """Allocate the B = 1 buffers the reference's fused prefill allocates
+    (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/fused_prefill.py:61-160) around `weights`."""
+    LlamaConfig.update_from_dict(config)
+    dev = torch.device(device)
+    L, H, I = config["num_hidden_layers"], config["hidden_size"], config["intermediate_size"]
+    NH, NKV, HD, V = (config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"],
+                      config["vocab_size"])
+    bf = torch.bfloat16
+    moved = {}
+    for name in WEIGHT_NAMES:
+        t = weights[name]
+        key = t.data_ptr()
+        if key not in moved:
+            moved[key] = t.to(dev).contiguous()
+        weights_dev = moved[key]
+        moved[name] = weights_dev
+    g = Globals(position_id=0, **{n: moved[n] for n in WEIGHT_NAMES})
+    g.k_cache = torch.zeros(L, 1, kv_seq_len, NKV, HD, dtype=bf, device=dev)
+    g.v_cache = torch.zeros(L, 1, kv_seq_len, NKV, HD, dtype=bf, device=dev)
+    g.hidden_states = torch.zeros(H, dtype=bf, device=dev)
+    g.q_post_rope = torch.zeros(NH * HD, dtype=bf, device=dev)
+    g.attn_out = torch.zeros(NH * HD, dtype=bf, device=dev)
+    g.silu_out = torch.zeros(I, dtype=bf, device=dev)
+    g.logits = torch.zeros(V, dtype=bf, device=dev)
+    g.next_token = torch.zeros(1, dtype=torch.int64, device=dev)
+    return g
