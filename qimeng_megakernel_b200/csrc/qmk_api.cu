@@ -116,6 +116,12 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
       break;
     }
     h->n_sm = prop.multiProcessorCount;
+    {
+      // the device splits work with 32-bit arithmetic: (worker + 1) * units must fit
+      const unsigned long long nwt = (unsigned long long)h->n_sm * kWorkers;
+      const unsigned long long units = d->vocab_size > Shape::I ? d->vocab_size : Shape::I;
+      if ((nwt + 1) * units >= (1ull << 32)) { rc = QMK_ERR_INVALID_ARG; break; }
+    }
     e = cudaFuncSetAttribute(qmk_decode_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SmemLayout<Shape>::kTotal);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaFuncSetAttribute"); break; }

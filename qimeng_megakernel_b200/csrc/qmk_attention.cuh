@@ -45,21 +45,6 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
 #pragma unroll
       for (int i = 0; i < KV4; ++i) kreg[i] = ldcg_u4(kp + i);
     }
-    // V rows of the block, lane = output dims; clamped rows carry probability 0.
-    uint32_t vreg[kAttnBlockKeys][DPL / 2];
-#pragma unroll
-    for (int j = 0; j < kAttnBlockKeys; ++j) {
-      int kj = kb + j;
-      if (kj > k1 - 1) kj = k1 - 1;
-      const uint16_t* vp = vbase + (size_t)kj * p.kv_seq_stride;
-      if (DPL == 2) {
-        vreg[j][0] = ldcg_u32(vp);
-      } else {
-        const uint2 t = __ldcg(reinterpret_cast<const uint2*>(vp));
-        vreg[j][0] = t.x;
-        vreg[j][DPL / 2 - 1] = t.y;
-      }
-    }
     float pr[GQA];
 #pragma unroll
     for (int h = 0; h < GQA; ++h) {
@@ -87,15 +72,34 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
       for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
       m[h] = m_new;
     }
+    // P.V: lane = output dims.  Rows past the end are clamped and carry probability 0.
+#pragma unroll 1
+    for (int j0 = 0; j0 < kAttnBlockKeys; j0 += 8) {
+      if (kb + j0 >= k1) break;
+      uint32_t vreg[8][DPL / 2];
 #pragma unroll
-    for (int j = 0; j < kAttnBlockKeys; ++j) {
+      for (int j = 0; j < 8; ++j) {
+        int kj = kb + j0 + j;
+        if (kj > k1 - 1) kj = k1 - 1;
+        const uint16_t* vp = vbase + (size_t)kj * p.kv_seq_stride;
+        if (DPL == 2) {
+          vreg[j][0] = ldcg_u32(vp);
+        } else {
+          const uint2 t = __ldcg(reinterpret_cast<const uint2*>(vp));
+          vreg[j][0] = t.x;
+          vreg[j][DPL / 2 - 1] = t.y;
+        }
+      }
 #pragma unroll
-      for (int h = 0; h < GQA; ++h) {
-        const float pj = __shfl_sync(kFullMask, pr[h], j);
+      for (int j = 0; j < 8; ++j) {
 #pragma unroll
-        for (int d2 = 0; d2 < DPL / 2; ++d2) {
-          acc[h][2 * d2] = fmaf(pj, bf_lo(vreg[j][d2]), acc[h][2 * d2]);
-          acc[h][2 * d2 + 1] = fmaf(pj, bf_hi(vreg[j][d2]), acc[h][2 * d2 + 1]);
+        for (int h = 0; h < GQA; ++h) {
+          const float pj = __shfl_sync(kFullMask, pr[h], j0 + j);
+#pragma unroll
+          for (int d2 = 0; d2 < DPL / 2; ++d2) {
+            acc[h][2 * d2] = fmaf(pj, bf_lo(vreg[j][d2]), acc[h][2 * d2]);
+            acc[h][2 * d2 + 1] = fmaf(pj, bf_hi(vreg[j][d2]), acc[h][2 * d2 + 1]);
+          }
         }
       }
     }
@@ -129,51 +133,71 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
       *reinterpret_cast<float2*>(ml) = make_float2(m[h], l[h]);
     }
   }
-  __threadfence();
+  // Release the partial (all lanes' stores are ordered before lane 0's atomic by the __syncwarp),
+  // take a ticket; only the last arrival goes on, and its atomic acquires the other partials.
   __syncwarp();
   unsigned ticket = 0;
-  if (s.lane == 0) ticket = atomicAdd(p.tickets + kvh, 1u);
+  if (s.lane == 0) ticket = atom_add_acq_rel_gpu(p.tickets + kvh, 1u);
   ticket = __shfl_sync(kFullMask, ticket, 0);
   if (ticket != (unsigned)(P - 1)) return;
-  __threadfence();
 
-#pragma unroll 1
-  for (int h = 0; h < GQA; ++h) {
-    const int head = kvh * GQA + h;
-    const float* mlb = p.part_ml + (size_t)head * kMaxSplits * 2;
-    // lanes hold partials lane and lane+32
-    float m_lo = -INFINITY, l_lo = 0.f, m_hi = -INFINITY, l_hi = 0.f;
-    if (s.lane < P) {
-      const float2 t = ldcg_f2(mlb + 2 * s.lane);
-      m_lo = t.x;
-      l_lo = t.y;
-    }
-    if (s.lane + 32 < P) {
-      const float2 t = ldcg_f2(mlb + 2 * (s.lane + 32));
-      m_hi = t.x;
-      l_hi = t.y;
-    }
-    const float M = warp_max(fmaxf(m_lo, m_hi));
-    const float w_lo = exp2f(m_lo - M), w_hi = exp2f(m_hi - M);
-    const float den = warp_sum(w_lo * l_lo + w_hi * l_hi);
-    float num[DPL];
+  // Merge all GQA heads at once so that the loads of the whole merge overlap: first every (max, sum)
+  // pair (lane = partial, two rounds cover kMaxSplits = 64), then the partial outputs four at a time.
+  float w_lo[GQA], w_hi[GQA], inv[GQA];
+  {
+    float2 t_lo[GQA], t_hi[GQA];
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) num[d] = 0.f;
-    const float* pob = p.part_o + (size_t)head * kMaxSplits * HD + s.lane * DPL;
-    for (int q = 0; q < P; ++q) {
-      const float wq = __shfl_sync(kFullMask, q < 32 ? w_lo : w_hi, q & 31);
+    for (int h = 0; h < GQA; ++h) {
+      const float* mlb = p.part_ml + (size_t)(kvh * GQA + h) * kMaxSplits * 2;
+      t_lo[h] = s.lane < P ? ldcg_f2(mlb + 2 * s.lane) : make_float2(-INFINITY, 0.f);
+      t_hi[h] = s.lane + 32 < P ? ldcg_f2(mlb + 2 * (s.lane + 32)) : make_float2(-INFINITY, 0.f);
+    }
 #pragma unroll
-      for (int d2 = 0; d2 < DPL / 2; ++d2) {
-        const float2 t = ldcg_f2(pob + (size_t)q * HD + 2 * d2);
-        num[2 * d2] = fmaf(wq, t.x, num[2 * d2]);
-        num[2 * d2 + 1] = fmaf(wq, t.y, num[2 * d2 + 1]);
+    for (int h = 0; h < GQA; ++h) {
+      const float M = warp_max(fmaxf(t_lo[h].x, t_hi[h].x));
+      w_lo[h] = exp2f(t_lo[h].x - M);
+      w_hi[h] = exp2f(t_hi[h].x - M);
+      inv[h] = 1.0f / warp_sum(w_lo[h] * t_lo[h].y + w_hi[h] * t_hi[h].y);
+    }
+  }
+  float num[GQA][DPL];
+#pragma unroll
+  for (int h = 0; h < GQA; ++h)
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) num[h][d] = 0.f;
+  const float* pob = p.part_o + (size_t)kvh * GQA * kMaxSplits * HD + s.lane * DPL;
+  for (int q0 = 0; q0 < P; q0 += 4) {
+    float2 t[4][GQA][DPL / 2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int q = (q0 + j) < P ? (q0 + j) : (P - 1);
+#pragma unroll
+      for (int h = 0; h < GQA; ++h)
+#pragma unroll
+        for (int d2 = 0; d2 < DPL / 2; ++d2)
+          t[j][h][d2] = ldcg_f2(pob + ((size_t)h * kMaxSplits + q) * HD + 2 * d2);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int q = q0 + j;
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) {
+        float wq = __shfl_sync(kFullMask, q < 32 ? w_lo[h] : w_hi[h], q & 31);
+        if (q >= P) wq = 0.f;
+#pragma unroll
+        for (int d2 = 0; d2 < DPL / 2; ++d2) {
+          num[h][2 * d2] = fmaf(wq, t[j][h][d2].x, num[h][2 * d2]);
+          num[h][2 * d2 + 1] = fmaf(wq, t[j][h][d2].y, num[h][2 * d2 + 1]);
+        }
       }
     }
-    const float inv = 1.0f / den;
-    uint16_t* dst = p.attn_out + (size_t)head * HD + s.lane * DPL;
+  }
+#pragma unroll
+  for (int h = 0; h < GQA; ++h) {
+    uint16_t* dst = p.attn_out + (size_t)(kvh * GQA + h) * HD + s.lane * DPL;
 #pragma unroll
     for (int d2 = 0; d2 < DPL / 2; ++d2)
-      reinterpret_cast<uint32_t*>(dst)[d2] = pack_bf16x2(num[2 * d2] * inv, num[2 * d2 + 1] * inv);
+      reinterpret_cast<uint32_t*>(dst)[d2] = pack_bf16x2(num[h][2 * d2] * inv[h], num[h][2 * d2 + 1] * inv[h]);
   }
   if (s.lane == 0) p.tickets[kvh] = 0u;   // self-reset: every partial of this step has arrived
   publish(s, p, ph, kvh % kCounterShards);

@@ -24,8 +24,14 @@
 
 namespace qmk {
 
-constexpr int kWorkers = 8;            // worker warps per CTA
-constexpr int kSlots = 6;              // ring slots per worker warp
+#ifndef QMK_WORKERS
+#define QMK_WORKERS 8
+#endif
+#ifndef QMK_SLOTS
+#define QMK_SLOTS 6
+#endif
+constexpr int kWorkers = QMK_WORKERS;  // worker warps per CTA
+constexpr int kSlots = QMK_SLOTS;      // ring slots per worker warp
 constexpr int kThreads = (kWorkers + 1) * 32;
 constexpr unsigned kAbortFlag = 0xffffffffu;
 
@@ -42,11 +48,12 @@ struct SmemLayout {
   static constexpr int kOffActD = kOffActB + kActSmall;
   static constexpr int kOffBars = kOffActD + kActBig;                // kWorkers*kSlots u64
   static constexpr int kOffCtl = kOffBars + kWorkers * kSlots * 8;   // control words
-  static constexpr int kTotal = kOffCtl + 64;
+  static constexpr int kOffRope = kOffCtl + 64;                      // cos[HD], sin[HD] of this step's position
+  static constexpr int kTotal = kOffRope + S::HD * 8;
 };
 // control words (u32 index from kOffCtl): 0 staged, 1 lm_arrive, 2..3 cta argmax key (u64)
 
-__device__ __forceinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
+__device__ __noinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
                                              unsigned expected, int detail) {
   if (atomicCAS(&p.status[kStCode], 0u, (unsigned)code) == 0u) {
     p.status[kStSm] = blockIdx.x;
@@ -59,6 +66,14 @@ __device__ __forceinline__ void report_error(const Params& p, int code, int warp
   }
 }
 
+// Optional timeline: slot of (CTA, phase) <- globaltimer.  Slots: 0 dependency satisfied, 1 activations
+// staged (controller); worker 0: 2 enters the phase, 3 sees the staged flag, 4 has its first chunk,
+// 7 starts publishing, 5 leaves; 6 last worker leaves.
+__device__ __forceinline__ void trace_stamp(const Params& p, int ph, int slot, int lane) {
+  if (p.trace != nullptr && lane == 0)
+    p.trace[((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8 + slot] = globaltimer_ns();
+}
+
 // ------------------------------------------------------------------------------------------
 // Worker state: ring + issue cursor.  All fields are warp-uniform.
 // ------------------------------------------------------------------------------------------
@@ -68,80 +83,142 @@ struct Worker {
   uint32_t ring;       // shared address of this warp's first slot
   uint32_t bars;       // shared address of this warp's first mbarrier
   uint32_t ctl;        // shared address of the control words
-  unsigned n_issued, n_consumed;
-  int i_ph, i_c, i_cend;   // issue cursor: phase, next chunk, end chunk
+  unsigned n_issued, n_acquired;
+  unsigned i_slot;         // slot the next issue goes into
+  unsigned c_slot, c_par;  // slot and mbarrier parity of the next chunk to consume
+  int i_ph, i_kind, i_layer, i_c, i_cend;   // issue cursor: phase, its kind / layer, next chunk, end chunk
+  // This worker's chunk range per streaming kind: identical for every layer, so the 32-bit
+  // divisions of the even split are done once per launch.
+  int q0, q1, o0, o1, u0, u1, d0, d1, l0, l1;
   int staged_seen;         // highest staged value observed
   bool aborted;
+  bool trace_first;        // next acquired chunk is the first of its phase (timeline only)
+  long long cyc_wait, cyc_issue, cyc_stage;   // timeline only: cycles of worker 0 in chunk waits / copy issue / staged wait
   uint64_t policy;
   WeightBases wb;
 };
 
+__device__ __forceinline__ void split_range_u32(unsigned units, unsigned parts, unsigned g, int& lo, int& hi) {
+  lo = (int)((g * units) / parts);            // g * units < 2^32 is checked on the host
+  hi = (int)(((g + 1u) * units) / parts);
+}
+
+template <class S>
+__device__ __forceinline__ void init_ranges(Worker<S>& s, const Params& p) {
+  int a, b;
+  split_range_u32(S::QKV_ROWS / 2, s.nwt, s.g, a, b); s.q0 = 2 * a; s.q1 = 2 * b;
+  split_range_u32(S::H, s.nwt, s.g, a, b); s.o0 = a * (S::QDIM / kChunkElems); s.o1 = b * (S::QDIM / kChunkElems);
+  split_range_u32(S::I, s.nwt, s.g, a, b); s.u0 = 2 * a; s.u1 = 2 * b;
+  split_range_u32(S::H, s.nwt, s.g, a, b); s.d0 = a * (S::I / kChunkElems); s.d1 = b * (S::I / kChunkElems);
+  split_range_u32((unsigned)p.vocab, s.nwt, s.g, a, b); s.l0 = a; s.l1 = b;
+}
+
+template <class S>
+__device__ __forceinline__ void kind_range(const Worker<S>& s, int kind, int& c0, int& c1) {
+  switch (kind) {
+    case kQkv: c0 = s.q0; c1 = s.q1; break;
+    case kOproj: c0 = s.o0; c1 = s.o1; break;
+    case kUpGate: c0 = s.u0; c1 = s.u1; break;
+    case kDown: c0 = s.d0; c1 = s.d1; break;
+    case kLmHead: c0 = s.l0; c1 = s.l1; break;
+    default: c0 = c1 = 0; break;
+  }
+}
+
+// Down-projection rows are consumed two at a time, k-slice by k-slice, so that both chunks of a pair
+// meet the same activations: order (row a, slice 0), (row b, slice 0), (row a, slice 1), ...; an odd
+// last row goes alone.  Maps the t-th chunk of this worker's down-proj stream to row * slices + slice.
+template <class S>
+__device__ __forceinline__ int down_canonical(int t, int d0, int d1) {
+  constexpr int kSlices = S::I / kChunkElems;
+  const int r0 = d0 / kSlices, nrows = (d1 - d0) / kSlices;
+  const int pair = t / (2 * kSlices), tt = t % (2 * kSlices);
+  int row = 2 * pair, slice;
+  if (row + 1 < nrows) {
+    slice = tt >> 1;
+    row += tt & 1;
+  } else {
+    slice = tt;
+  }
+  return (r0 + row) * kSlices + slice;
+}
+
+// Position the issue cursor on the first phase >= i_ph in which this worker streams weights.
 template <class S>
 __device__ __forceinline__ void cursor_seek(Worker<S>& s, const Params& p) {
   while (s.i_ph < p.phase_end) {
-    const int kind = phase_kind(s.i_ph, p.num_layers);
-    int c0, c1;
-    phase_chunk_range<S>(kind, p.vocab, s.g, s.nwt, c0, c1);
-    if (c0 < c1) {
-      s.i_c = c0;
-      s.i_cend = c1;
-      return;
-    }
+    const int layer = s.i_ph / kPhasesPerLayer;
+    s.i_kind = layer >= p.num_layers ? (int)kLmHead : s.i_ph - layer * kPhasesPerLayer;
+    s.i_layer = layer;
+    kind_range(s, s.i_kind, s.i_c, s.i_cend);
+    if (s.i_c < s.i_cend) return;
     ++s.i_ph;
   }
 }
 
-// Issue the next chunk of the stream into slot (n_issued % kSlots), if any is left.
+// Issue the next chunk of the stream into the oldest free slot, if any chunk is left.
 template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
   if (s.aborted || s.i_ph >= p.phase_end) return;
-  const int kind = phase_kind(s.i_ph, p.num_layers);
-  const uint16_t* src = chunk_ptr<S>(s.wb, kind, phase_layer(s.i_ph), s.i_c);
-  const unsigned slot = s.n_issued % kSlots;
   if (s.lane == 0) {
-    const uint32_t bar = s.bars + slot * 8;
+    const long long t0 = clock64();
+    const int c = s.i_kind == kDown ? down_canonical<S>(s.i_c - s.d0, s.d0, s.d1) : s.i_c;
+    const uint16_t* src = chunk_ptr<S>(s.wb, s.i_kind, s.i_layer, c);
+    const uint32_t bar = s.bars + s.i_slot * 8;
     mbar_expect_tx(bar, kChunkBytes);
-    bulk_g2s(s.ring + slot * kChunkBytes, src, kChunkBytes, bar, s.policy);
+    bulk_g2s(s.ring + s.i_slot * kChunkBytes, src, kChunkBytes, bar, s.policy);
+    s.cyc_issue += clock64() - t0;
   }
   ++s.n_issued;
+  s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
   if (++s.i_c == s.i_cend) {
     ++s.i_ph;
     cursor_seek(s, p);
   }
 }
 
-// Bounded wait for chunk n of this warp's stream.  Returns false (and flags the error) on expiry.
-template <class S>
-__device__ __forceinline__ bool wait_chunk(Worker<S>& s, const Params& p, unsigned n, int phase) {
-  const uint32_t bar = s.bars + (n % kSlots) * 8;
-  const uint32_t parity = (n / kSlots) & 1u;
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait on one ring slot.  Returns false (and flags the error) on expiry.  The spin with its
+// deadline is a separate, non-inlined function: it runs only when the data is not there yet.
+__device__ __noinline__ bool wait_slot_slow(const Params& p, uint32_t bar, uint32_t parity, int warp, int phase,
+                                            unsigned acquired, unsigned issued, int slot, int lane) {
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0u && clock64() - t0 > p.timeout_cycles) {
-      if (s.lane == 0) report_error(p, kErrCopyWait, s.w, phase, n, s.n_issued, (int)(n % kSlots));
+      if (lane == 0) report_error(p, kErrCopyWait, warp, phase, acquired, issued, slot);
       return false;
     }
   }
 }
-
-// Next chunk in consumption order: returns the slot's generic shared pointer (as uint4*).
 template <class S>
-__device__ __forceinline__ const uint4* acquire_chunk(Worker<S>& s, const Params& p, unsigned char* smem,
-                                                      int phase) {
-  if (!s.aborted && !wait_chunk(s, p, s.n_consumed, phase)) s.aborted = true;
-  const unsigned slot = s.n_consumed % kSlots;
-  return reinterpret_cast<const uint4*>(smem + SmemLayout<S>::kOffRing +
-                                        (s.w * kSlots + slot) * kChunkBytes);
+__device__ __forceinline__ bool wait_slot(Worker<S>& s, const Params& p, unsigned slot, unsigned parity, int phase) {
+  const uint32_t bar = s.bars + slot * 8;
+  if (mbar_try_wait(bar, parity)) return true;
+  return wait_slot_slow(p, bar, parity, s.w, phase, s.n_acquired, s.n_issued, (int)slot, s.lane);
 }
-// All lanes are done reading the slot: hand it back to the copy engine with the next chunk.
+
+// Next chunk in consumption order: waits for it, returns the slot (generic shared pointer) and
+// advances the consume cursor; returns the slot's shared address.  The slot stays owned by the warp until release_chunks().
 template <class S>
-__device__ __forceinline__ void release_chunk(Worker<S>& s, const Params& p) {
+__device__ __forceinline__ uint32_t acquire_chunk(Worker<S>& s, const Params& p, int phase) {
+  const unsigned slot = s.c_slot;
+  if (!s.aborted) {
+    const long long t0 = clock64();
+    if (!wait_slot(s, p, slot, s.c_par, phase)) s.aborted = true;
+    s.cyc_wait += clock64() - t0;
+    ++s.n_acquired;
+    if (++s.c_slot == kSlots) {
+      s.c_slot = 0;
+      s.c_par ^= 1u;
+    }
+  }
+  return s.ring + slot * kChunkBytes;
+}
+// All lanes are done reading the `n` oldest acquired slots: refill them with the next chunks.
+template <class S>
+__device__ __forceinline__ void release_chunks(Worker<S>& s, const Params& p, int n) {
   __syncwarp();
-  if (s.aborted) return;
-  ++s.n_consumed;
-  issue_one(s, p);
+  for (int i = 0; i < n; ++i) issue_one(s, p);
 }
 
 // Wait until the controller has staged the activations of `phase` (staged >= phase+1).
@@ -149,6 +226,7 @@ template <class S>
 __device__ __forceinline__ bool wait_staged(Worker<S>& s, const Params& p, int phase) {
   if (s.aborted) return false;
   if (s.staged_seen > phase && s.staged_seen != (int)kAbortFlag) return true;
+  const long long ts0 = clock64();
   unsigned v = 0;
   if (s.lane == 0) {
     const long long t0 = clock64();
@@ -163,6 +241,7 @@ __device__ __forceinline__ bool wait_staged(Worker<S>& s, const Params& p, int p
     }
   }
   v = __shfl_sync(kFullMask, v, 0);
+  s.cyc_stage += clock64() - ts0;
   if (v == kAbortFlag) {
     s.aborted = true;
     return false;
@@ -176,7 +255,7 @@ template <class S>
 __device__ __forceinline__ void publish(const Worker<S>& s, const Params& p, int phase, int shard) {
   __syncwarp();
   if (p.sync && !s.aborted && s.lane == 0) {
-    __threadfence();
+    // red.release orders every earlier store of this warp (made visible to lane 0 by the __syncwarp).
     red_release_gpu_add(p.counters + ((size_t)phase * kCounterShards + shard) * kCounterStrideWords, 1u);
   }
 }
@@ -191,36 +270,71 @@ __device__ __forceinline__ int small_buf_index(int phase, int num_layers) {
   return idx & 1;
 }
 
-// Load this lane's 64 activation values of a 2048-element bf16 vector staged in shared memory:
-// element k = j*256 + lane*8 + e  ->  x[j*8 + e]  (the same positions the lane reads in a weight chunk).
-__device__ __forceinline__ void load_x64(float (&x)[64], const unsigned char* act, int lane) {
-  const uint4* v = reinterpret_cast<const uint4*>(act);
+// ------------------------------------------------------------------------------------------
+// GEMV core.  One 4-KiB chunk is 2048 consecutive weights of one output row.  View it as 8
+// "pseudo-rows": pseudo-row r holds the 16-byte pieces r, r+8, r+16, ... of the chunk (256 weights).
+// The dot product of the chunk with its 2048 activations is the sum over r of
+// (pseudo-row r) . (the same pieces of the activation vector), i.e. the diagonal of an 8x8 product.
+// A warp computes that product on the tensor pipe for TWO chunks at once with mma.m16n8k16:
+// A rows 0-7 = pseudo-rows of chunk 0, rows 8-15 = pseudo-rows of chunk 1, B column n = activation
+// pieces of pseudo-row n, 16 k-steps of 16 weights.  Products of bf16 are exact in fp32 and the
+// accumulation is fp32, so the arithmetic is the same as an fp32 FMA chain in a different order.
+// Eight consecutive pseudo-rows of one piece index are 128 contiguous bytes: ldmatrix reads them
+// without bank conflicts, and the B fragments are plain 32-bit words x32[32*i + lane].
+// ------------------------------------------------------------------------------------------
+struct XFrag {
+  uint32_t b[32];   // b[2t], b[2t+1]: B fragment of k-step t
+};
+
+__device__ __forceinline__ void load_xfrag(XFrag& xf, const unsigned char* act_bf16, int lane) {
+  const uint32_t* v = reinterpret_cast<const uint32_t*>(act_bf16);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const uint4 q = v[j * 32 + lane];
-    x[j * 8 + 0] = bf_lo(q.x); x[j * 8 + 1] = bf_hi(q.x);
-    x[j * 8 + 2] = bf_lo(q.y); x[j * 8 + 3] = bf_hi(q.y);
-    x[j * 8 + 4] = bf_lo(q.z); x[j * 8 + 5] = bf_hi(q.z);
-    x[j * 8 + 6] = bf_lo(q.w); x[j * 8 + 7] = bf_hi(q.w);
-  }
+  for (int i = 0; i < 32; ++i) xf.b[i] = v[32 * i + lane];
 }
 
-// Per-lane partial dot product of one 4-KiB weight chunk with the lane's 64 activations.
-__device__ __forceinline__ float dot_chunk(const uint4* slot, const float (&x)[64], int lane) {
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, a4 = 0.f, a5 = 0.f, a6 = 0.f, a7 = 0.f;
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&a)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+               : "r"(saddr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Accumulate the 16x8 product of two chunks (shared addresses slot0 / slot1) into cc.
+__device__ __forceinline__ void mma_chunk_pair(float (&cc)[4], uint32_t slot0, uint32_t slot1, const XFrag& xf,
+                                               int lane) {
+  // ldmatrix row address of this lane: matrices 0/2 come from chunk 0, 1/3 from chunk 1;
+  // matrices 2/3 are the second piece (k 8..15) of the k-step.
+  const uint32_t addr = ((lane & 8) ? slot1 : slot0) + ((((lane >> 4) << 3) + (lane & 7)) << 4);
+  float c[4][4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const uint4 q = slot[j * 32 + lane];
-    a0 = fmaf(bf_lo(q.x), x[j * 8 + 0], a0);
-    a1 = fmaf(bf_hi(q.x), x[j * 8 + 1], a1);
-    a2 = fmaf(bf_lo(q.y), x[j * 8 + 2], a2);
-    a3 = fmaf(bf_hi(q.y), x[j * 8 + 3], a3);
-    a4 = fmaf(bf_lo(q.z), x[j * 8 + 4], a4);
-    a5 = fmaf(bf_hi(q.z), x[j * 8 + 5], a5);
-    a6 = fmaf(bf_lo(q.w), x[j * 8 + 6], a6);
-    a7 = fmaf(bf_hi(q.w), x[j * 8 + 7], a7);
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    uint32_t a[4];
+    ldmatrix_x4(a, addr + t * 256);
+    mma_bf16_16816(c[t & 3], a, xf.b[2 * t], xf.b[2 * t + 1]);
   }
-  return ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
+#pragma unroll
+  for (int j = 0; j < 4; ++j) cc[j] += (c[0][j] + c[1][j]) + (c[2][j] + c[3][j]);
+}
+
+// Diagonal of the accumulated product -> the two dot products, summed over the warp.
+__device__ __forceinline__ void diag_reduce(const float (&cc)[4], int lane, float& s0, float& s1) {
+  const int r = lane >> 2, q2 = (lane & 3) * 2;
+  s0 = r == q2 ? cc[0] : (r == q2 + 1 ? cc[1] : 0.f);
+  s1 = r == q2 ? cc[2] : (r == q2 + 1 ? cc[3] : 0.f);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s0 += __shfl_xor_sync(kFullMask, s0, o);
+    s1 += __shfl_xor_sync(kFullMask, s1, o);
+  }
 }
 
 }  // namespace qmk

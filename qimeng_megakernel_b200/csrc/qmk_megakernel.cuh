@@ -4,13 +4,6 @@
 
 namespace qmk {
 
-// Optional timeline: slot of (CTA, phase) <- globaltimer.  Slots: 0 dependency satisfied, 1 activations
-// staged (controller); 2 worker 0 enters the phase, 5 worker 0 leaves it, 6 last worker leaves it.
-__device__ __forceinline__ void trace_stamp(const Params& p, int ph, int slot, int lane) {
-  if (p.trace != nullptr && lane == 0)
-    p.trace[((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8 + slot] = globaltimer_ns();
-}
-
 // Wait until every publisher of phase `dep` has arrived for this step.  Lane i watches shard i.
 template <class S>
 __device__ __forceinline__ bool poll_dependency(const Params& p, int dep, int ph, int lane, int nwt) {
@@ -37,7 +30,18 @@ __device__ __forceinline__ bool poll_dependency(const Params& p, int dep, int ph
 // RMSNorm of the residual stream into a bf16 shared-memory vector:
 // y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps)))   (_rms_norm, fused/operations.py:126-131).
 template <class S>
-__device__ __forceinline__ void stage_rmsnorm(const uint16_t* src, const uint16_t* weight, float eps,
+struct NormWeights {
+  uint4 w[S::H / 8 / 32];
+};
+// The gains do not depend on the step: fetch them before the dependency wait.
+template <class S>
+__device__ __forceinline__ void load_norm_weights(NormWeights<S>& nw, const uint16_t* weight, int lane) {
+#pragma unroll
+  for (int j = 0; j < S::H / 8 / 32; ++j) nw.w[j] = __ldg(reinterpret_cast<const uint4*>(weight) + j * 32 + lane);
+}
+
+template <class S>
+__device__ __forceinline__ void stage_rmsnorm(const uint16_t* src, const NormWeights<S>& nw, float eps,
                                               unsigned char* dst, int lane) {
   constexpr int N4 = S::H / 8 / 32;   // uint4 per lane
   uint4 v[N4];
@@ -58,7 +62,7 @@ __device__ __forceinline__ void stage_rmsnorm(const uint16_t* src, const uint16_
   uint4* out = reinterpret_cast<uint4*>(dst);
 #pragma unroll
   for (int j = 0; j < N4; ++j) {
-    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight) + j * 32 + lane);
+    const uint4 wv = nw.w[j];
     const uint32_t u[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
     const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
     uint32_t o[4];
@@ -73,17 +77,29 @@ __device__ __forceinline__ void stage_rmsnorm(const uint16_t* src, const uint16_
 
 __device__ __forceinline__ void stage_copy(const uint16_t* src, unsigned char* dst, int n_elems, int lane) {
   uint4* out = reinterpret_cast<uint4*>(dst);
-  const int n4 = n_elems / 8;
-  for (int i = lane; i < n4; i += 32) out[i] = ldcg_u4(reinterpret_cast<const uint4*>(src) + i);
+  const int n4 = n_elems / 8;          // a multiple of 256: eight independent loads per lane per round
+  for (int base = 0; base < n4; base += 256) {
+    uint4 t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = ldcg_u4(reinterpret_cast<const uint4*>(src) + base + j * 32 + lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[base + j * 32 + lane] = t[j];
+  }
 }
 
 __device__ __forceinline__ void stage_bf16_to_f32(const uint16_t* src, unsigned char* dst, int n_elems, int lane) {
   float4* out = reinterpret_cast<float4*>(dst);
   const int n4 = n_elems / 8;
-  for (int i = lane; i < n4; i += 32) {
-    const uint4 q = ldcg_u4(reinterpret_cast<const uint4*>(src) + i);
-    out[2 * i] = make_float4(bf_lo(q.x), bf_hi(q.x), bf_lo(q.y), bf_hi(q.y));
-    out[2 * i + 1] = make_float4(bf_lo(q.z), bf_hi(q.z), bf_lo(q.w), bf_hi(q.w));
+  for (int base = 0; base < n4; base += 256) {
+    uint4 t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = ldcg_u4(reinterpret_cast<const uint4*>(src) + base + j * 32 + lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + j * 32 + lane;
+      out[2 * i] = make_float4(bf_lo(t[j].x), bf_hi(t[j].x), bf_lo(t[j].y), bf_hi(t[j].y));
+      out[2 * i + 1] = make_float4(bf_lo(t[j].z), bf_hi(t[j].z), bf_lo(t[j].w), bf_hi(t[j].w));
+    }
   }
 }
 
@@ -92,9 +108,24 @@ __device__ __forceinline__ void controller(const Params& p, unsigned char* smem,
   using L = SmemLayout<S>;
   const uint32_t ctl = smem_u32(smem + L::kOffCtl);
   const int nwt = (int)gridDim.x * kWorkers;
+  // cos / sin of this step's position: read by the QKV epilogues of every layer.
+  {
+    float* rope = reinterpret_cast<float*>(smem + L::kOffRope);
+    for (int i = lane; i < S::HD; i += 32) {
+      rope[i] = __ldg(p.rope_cos + (size_t)p.pos * S::HD + i);
+      rope[S::HD + i] = __ldg(p.rope_sin + (size_t)p.pos * S::HD + i);
+    }
+  }
   for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
     const int kind = phase_kind(ph, p.num_layers);
     const int layer = phase_layer(ph);
+    NormWeights<S> nw;
+    const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
+    if (normed) {
+      const uint16_t* gains = kind == kQkv ? p.attn_norm + (size_t)layer * S::H
+                                           : (kind == kUpGate ? p.mlp_norm + (size_t)layer * S::H : p.lm_norm);
+      load_norm_weights<S>(nw, gains, lane);
+    }
     if (p.sync && ph > 0 && (ph > p.phase_begin || p.wait_first)) {
       if (!poll_dependency<S>(p, ph - 1, ph, lane, nwt)) {
         __syncwarp();
@@ -104,28 +135,17 @@ __device__ __forceinline__ void controller(const Params& p, unsigned char* smem,
     }
     trace_stamp(p, ph, 0, lane);
     unsigned char* small = smem + (small_buf_index(ph, p.num_layers) ? L::kOffActB : L::kOffActA);
-    switch (kind) {
-      case kQkv:
-        stage_rmsnorm<S>(residual_src<S>(p, layer), p.attn_norm + (size_t)layer * S::H, p.eps, small, lane);
-        break;
-      case kAttn: {
-        int bps, P;
-        attn_plan(p.pos + 1, bps, P);
-        if ((int)blockIdx.x < S::NKV * P) stage_bf16_to_f32(p.q_post_rope, smem + L::kOffActD, S::QDIM, lane);
-        break;
-      }
-      case kOproj:
-        stage_copy(p.attn_out, small, S::QDIM, lane);
-        break;
-      case kUpGate:
-        stage_rmsnorm<S>(p.hidden, p.mlp_norm + (size_t)layer * S::H, p.eps, small, lane);
-        break;
-      case kDown:
-        stage_copy(p.silu_out, smem + L::kOffActD, S::I, lane);
-        break;
-      default:
-        stage_rmsnorm<S>(p.num_layers == 0 ? residual_src<S>(p, 0) : p.hidden, p.lm_norm, p.eps, small, lane);
-        break;
+    if (normed) {
+      const bool from_token = kind == kQkv || (kind == kLmHead && p.num_layers == 0);
+      stage_rmsnorm<S>(from_token ? residual_src<S>(p, layer) : p.hidden, nw, p.eps, small, lane);
+    } else if (kind == kAttn) {
+      int bps, P;
+      attn_plan(p.pos + 1, bps, P);
+      if ((int)blockIdx.x < S::NKV * P) stage_bf16_to_f32(p.q_post_rope, smem + L::kOffActD, S::QDIM, lane);
+    } else if (kind == kOproj) {
+      stage_copy(p.attn_out, small, S::QDIM, lane);
+    } else {
+      stage_copy(p.silu_out, smem + L::kOffActD, S::I, lane);
     }
     __syncwarp();
     if (lane == 0) st_release_cta_shared(ctl, (unsigned)(ph + 1));
@@ -144,11 +164,14 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.ring = smem_u32(smem + L::kOffRing + w * kSlots * kChunkBytes);
   s.bars = smem_u32(smem + L::kOffBars + w * kSlots * 8);
   s.ctl = smem_u32(smem + L::kOffCtl);
-  s.n_issued = s.n_consumed = 0;
+  s.n_issued = s.n_acquired = 0;
+  s.i_slot = s.c_slot = s.c_par = 0;
   s.i_ph = p.phase_begin;
-  s.i_c = s.i_cend = 0;
+  s.i_kind = s.i_layer = s.i_c = s.i_cend = 0;
+  init_ranges(s, p);
   s.staged_seen = 0;
   s.aborted = false;
+  s.trace_first = false;
   s.policy = l2_policy_evict_first();
   s.wb.qkv = p.qkv;
   s.wb.o_proj = p.o_proj;
@@ -163,20 +186,19 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
 #pragma unroll 1
   for (int ph = p.phase_begin; ph < p.phase_end && !s.aborted; ++ph) {
     if (w == 0) trace_stamp(p, ph, 2, lane);
-    switch (phase_kind(ph, p.num_layers)) {
-      case kQkv: phase_qkv(s, p, smem, ph); break;
-      case kAttn: phase_attn(s, p, smem, ph); break;
-      case kOproj: phase_oproj(s, p, smem, ph); break;
-      case kUpGate: phase_upgate(s, p, smem, ph); break;
-      case kDown: phase_down(s, p, smem, ph); break;
-      default: phase_lm_head(s, p, smem, ph); break;
-    }
+    s.cyc_wait = s.cyc_issue = s.cyc_stage = 0;
+    const long long tph = clock64();
+    const int kind = phase_kind(ph, p.num_layers);
+#ifndef QMK_NO_ATTN
+    if (kind == kAttn) phase_attn(s, p, smem, ph);
+    else
+#endif
+    phase_stream(s, p, smem, ph, kind);
     if (w == 0) trace_stamp(p, ph, 5, lane);
-    if (w == kWorkers - 1) trace_stamp(p, ph, 6, lane);
   }
   if (s.aborted) {
     // Leave no bulk copy in flight into this CTA's shared memory: wait (bounded) for each.
-    for (unsigned n = s.n_consumed; n < s.n_issued; ++n) {
+    for (unsigned n = s.n_acquired; n < s.n_issued; ++n) {
       const uint32_t bar = s.bars + (n % kSlots) * 8;
       const long long t0 = clock64();
       while (!mbar_try_wait(bar, (n / kSlots) & 1u)) {

@@ -1,4 +1,8 @@
 // Worker-side phase bodies of the decode megakernel.  Included by qmk_kernel.cuh.
+//
+// All weight-streaming phases (QKV, O-proj, up/gate, down, LM head) share ONE instance of the hot
+// loop (acquire chunks -> tensor-pipe dot products -> release) and differ only in their epilogue;
+// keeping a single copy keeps the persistent kernel's code footprint inside the instruction cache.
 #pragma once
 
 namespace qmk {
@@ -17,172 +21,148 @@ __device__ __forceinline__ const uint16_t* residual_src(const Params& p, int lay
   return p.hidden;
 }
 
-// ---- phase 0: RMSNorm -> QKV GEMV -> interleaved RoPE -> q_post_rope / KV cache append ----
-// fused_rms_qkvproj_gemv_rope (operations.py:151-215).  Unit = two adjacent output rows
-// (one RoPE pair).  The GEMV result is rounded to bf16 before the rotation, like the einsum
-// on bf16 tensors in the reference; the rotation itself is fp32 with separately rounded products.
 template <class S>
-__device__ __forceinline__ void phase_qkv(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
+__device__ __forceinline__ const unsigned char* small_act(const Params& p, const unsigned char* smem, int ph) {
+  return smem + (small_buf_index(ph, p.num_layers) ? SmemLayout<S>::kOffActB : SmemLayout<S>::kOffActA);
+}
+
+__device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, int row) {
+  return ((unsigned long long)float_ordered_bits(bf16_bits_to_f32(bits)) << 32) | (0xffffffffu - (unsigned)row);
+}
+
+// ---- epilogues: lane i of a batch holds the fp32 sums of the batch's i-th item -------------------
+
+// QKV item = one RoPE pair (rows 2u, 2u+1).  fused_rms_qkvproj_gemv_rope (operations.py:151-215):
+// the GEMV result is rounded to bf16 (einsum on bf16 tensors), the rotation is fp32 with separately
+// rounded products, the result is rounded to bf16 and written to q_post_rope / the KV cache row.
+template <class S>
+__device__ __forceinline__ void epilogue_qkv(const Params& p, const unsigned char* smem, int layer, int unit,
+                                             float a, float b) {
+  const float* rope = reinterpret_cast<const float*>(smem + SmemLayout<S>::kOffRope);
+  const int row = 2 * unit;
+  a = bf16_round(a);
+  b = bf16_round(b);
+  constexpr int kStart = S::NH * S::HD;
+  constexpr int vStart = kStart + S::NKV * S::HD;
+  if (row < vStart) {
+    const int d = row % S::HD;
+    const float c0 = rope[d], c1 = rope[d + 1], s0 = rope[S::HD + d], s1 = rope[S::HD + d + 1];
+    const float o0 = __fadd_rn(__fmul_rn(a, c0), __fmul_rn(-b, s0));
+    const float o1 = __fadd_rn(__fmul_rn(b, c1), __fmul_rn(a, s1));
+    const uint32_t packed = pack_bf16x2(o0, o1);
+    if (row < kStart) {
+      *reinterpret_cast<uint32_t*>(p.q_post_rope + row) = packed;
+    } else {
+      uint16_t* dst = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - kStart);
+      *reinterpret_cast<uint32_t*>(dst) = packed;
+    }
+  } else {
+    uint16_t* dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - vStart);
+    *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(a, b);
+  }
+}
+
+// SwiGLU item = (up row u, gate row u).  fused_mlp_upgate (operations.py:265-282): up and gate rounded
+// to bf16, silu(gate) rounded to bf16, product rounded to bf16.
+__device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
+  const float g = bf16_round(gate);
+  const float sl = bf16_round(g / (1.0f + __expf(-g)));
+  return f32_to_bf16_bits(sl * bf16_round(up));
+}
+
+// ---- the streaming phase -----------------------------------------------------------------------
+// kind:  QKV / up-gate: an item is two chunks (one output unit) sharing the activations;
+//        O-proj / LM head: an item is one row = one chunk, two rows are computed per tensor-pipe tile;
+//        down-proj: an item is one row = I/2048 chunks; rows go in pairs, k-slice by k-slice (the
+//        order down_canonical() gives the weight stream), each slice against its own activations.
+// Residual phases (fused_oproj_gemv_residual, operations.py:251-262; fused_mlp_down_residual, 285-295):
+// hidden[r] = bf16(hidden[r] + bf16(W[r,:] . x)); the old values are fetched, one per lane, before the
+// first chunk is awaited.  One warp owns a whole down-proj row, so its K reduction has a fixed order
+// (the reference adds four split-K partials with bf16 CAS in arrival order,
+// decode_kernel/down_proj_gemv_residual.cu:39-52, 225-234).
+// LM head (fused_rms_lmhead_gemv, operations.py:303-321) also keeps the arg-max of the bf16 logits,
+// lowest index on ties, replacing `logits.argmax()` of the host loop (decode.py:1391-1395).
+template <class S>
+__device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kind) {
+  constexpr int kSlices = S::I / kChunkElems;
+  static_assert(S::QDIM == kChunkElems && S::H == kChunkElems, "rows of QKV/O/up/gate/LM must be one chunk");
   const int layer = phase_layer(ph);
-  int u0, u1;
-  split_range(S::QKV_ROWS / 2, s.nwt, s.g, u0, u1);
-  if (u0 < u1 && wait_staged(s, p, ph)) {
-    float x[64];
-    const int buf = small_buf_index(ph, p.num_layers);
-    load_x64(x, smem + (buf ? SmemLayout<S>::kOffActB : SmemLayout<S>::kOffActA), s.lane);
-    for (int u = u0; u < u1 && !s.aborted; ++u) {
-      const uint4* c0 = acquire_chunk(s, p, smem, ph);
-      float a = warp_sum(dot_chunk(c0, x, s.lane));
-      release_chunk(s, p);
-      const uint4* c1 = acquire_chunk(s, p, smem, ph);
-      float b = warp_sum(dot_chunk(c1, x, s.lane));
-      release_chunk(s, p);
-      if (s.lane == 0 && !s.aborted) {
-        const int row = 2 * u;
-        a = bf16_round(a);
-        b = bf16_round(b);
-        constexpr int kStart = S::NH * S::HD;
-        constexpr int vStart = kStart + S::NKV * S::HD;
-        if (row < vStart) {
-          const int d = row % S::HD;
-          const float* cs = p.rope_cos + (size_t)p.pos * S::HD + d;
-          const float* sn = p.rope_sin + (size_t)p.pos * S::HD + d;
-          const float o0 = __fadd_rn(__fmul_rn(a, cs[0]), __fmul_rn(-b, sn[0]));
-          const float o1 = __fadd_rn(__fmul_rn(b, cs[1]), __fmul_rn(a, sn[1]));
-          const uint32_t packed = pack_bf16x2(o0, o1);
-          if (row < kStart) {
-            *reinterpret_cast<uint32_t*>(p.q_post_rope + row) = packed;
-          } else {
-            uint16_t* dst = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride +
-                            (row - kStart);
-            *reinterpret_cast<uint32_t*>(dst) = packed;
+  int c0, c1;
+  kind_range(s, kind, c0, c1);
+  const bool unit_pairs = kind == kQkv || kind == kUpGate;
+  const int nsl = kind == kDown ? kSlices : 1;
+  const int cpi = unit_pairs ? 2 : nsl;          // chunks per item
+  const int i0 = c0 / cpi, i1 = c1 / cpi;
+  unsigned long long best = 0ull;
+  const long long tq0 = clock64();
+  long long tq1 = 0, tq2 = 0, tq3 = 0;
+  if (i0 < i1 && wait_staged(s, p, ph)) {
+    tq1 = clock64() - tq0;
+    const unsigned char* act = kind == kDown ? smem + SmemLayout<S>::kOffActD : small_act<S>(p, smem, ph);
+    const uint16_t* res = kind == kOproj ? residual_src<S>(p, layer) : p.hidden;
+    const bool residual = kind == kOproj || kind == kDown;
+    XFrag xf;
+    if (nsl == 1) load_xfrag(xf, act, s.lane);
+    tq2 = clock64() - tq0;
+#pragma unroll 1
+    for (int ib = i0; ib < i1 && !s.aborted; ib += 32) {
+      const int nb = (i1 - ib) < 32 ? (i1 - ib) : 32;
+      float old = 0.f;
+      if (residual && s.lane < nb) old = bf16_bits_to_f32(ldcg_u16(res + ib + s.lane));
+      float va = 0.f, vb = 0.f;
+      const int step = unit_pairs ? 1 : 2;
+#pragma unroll 1
+      for (int i = 0; i < nb; i += step) {
+        const bool two = unit_pairs || (i + 1 < nb);
+        float cc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int k = 0; k < nsl; ++k) {
+          if (nsl > 1) load_xfrag(xf, act + k * kChunkBytes, s.lane);
+          const uint32_t a0 = acquire_chunk(s, p, ph);
+          const uint32_t a1 = two ? acquire_chunk(s, p, ph) : a0;
+          mma_chunk_pair(cc, a0, a1, xf, s.lane);
+          release_chunks(s, p, two ? 2 : 1);
+        }
+        float sa, sb;
+        diag_reduce(cc, s.lane, sa, sb);
+        if (s.lane == i) {
+          va = sa;
+          vb = sb;
+        }
+        if (!unit_pairs && two && s.lane == i + 1) va = sb;
+      }
+      if (s.lane < nb && !s.aborted) {
+        const int item = ib + s.lane;
+        switch (kind) {
+          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb); break;
+          case kUpGate: p.silu_out[item] = epilogue_silu(va, vb); break;
+          case kLmHead: {
+            const unsigned short bits = f32_to_bf16_bits(va);
+            p.logits[item] = bits;
+            const unsigned long long key = argmax_key(bits, item);
+            best = key > best ? key : best;
+            break;
           }
-        } else {
-          uint16_t* dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride +
-                          (row - vStart);
-          *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(a, b);
+          default: p.hidden[item] = f32_to_bf16_bits(old + bf16_round(va)); break;
         }
       }
     }
   }
-  publish(s, p, ph, s.g % kCounterShards);
-}
-
-// ---- phase 2: O-projection GEMV + residual.  fused_oproj_gemv_residual (operations.py:251-262):
-// hidden[r] = bf16(hidden[r] + bf16(W_o[r,:] . attn_out)).
-template <class S>
-__device__ __forceinline__ void phase_oproj(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
-  static_assert(S::QDIM == kChunkElems, "O-proj row must be one chunk");
-  const int layer = phase_layer(ph);
-  int r0, r1;
-  split_range(S::H, s.nwt, s.g, r0, r1);
-  if (r0 < r1 && wait_staged(s, p, ph)) {
-    float x[64];
-    const int buf = small_buf_index(ph, p.num_layers);
-    load_x64(x, smem + (buf ? SmemLayout<S>::kOffActB : SmemLayout<S>::kOffActA), s.lane);
-    const uint16_t* res = residual_src<S>(p, layer);
-    for (int r = r0; r < r1 && !s.aborted; ++r) {
-      const uint4* c = acquire_chunk(s, p, smem, ph);
-      const float acc = warp_sum(dot_chunk(c, x, s.lane));
-      release_chunk(s, p);
-      if (s.lane == 0 && !s.aborted) {
-        const float old = bf16_bits_to_f32(ldcg_u16(res + r));
-        p.hidden[r] = f32_to_bf16_bits(old + bf16_round(acc));
-      }
+  tq3 = clock64() - tq0;
+  if (kind != kLmHead) {
+    publish(s, p, ph, s.g % kCounterShards);
+    if (s.w == 0 && s.lane == 0 && p.trace != nullptr) {
+      unsigned long long* t = p.trace + ((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8;
+      t[3] = tq1; t[4] = tq2; t[6] = tq3; t[7] = clock64() - tq0;
     }
+    return;
   }
-  publish(s, p, ph, s.g % kCounterShards);
-}
-
-// ---- phase 3: RMSNorm -> up / gate GEMV -> SiLU(gate) * up.  fused_mlp_upgate (operations.py:265-282).
-// Rounding points of the reference: up and gate to bf16, silu(gate) to bf16, product to bf16.
-template <class S>
-__device__ __forceinline__ void phase_upgate(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
-  static_assert(S::H == kChunkElems, "hidden row must be one chunk");
-  int u0, u1;
-  split_range(S::I, s.nwt, s.g, u0, u1);
-  if (u0 < u1 && wait_staged(s, p, ph)) {
-    float x[64];
-    const int buf = small_buf_index(ph, p.num_layers);
-    load_x64(x, smem + (buf ? SmemLayout<S>::kOffActB : SmemLayout<S>::kOffActA), s.lane);
-    for (int u = u0; u < u1 && !s.aborted; ++u) {
-      const uint4* cu = acquire_chunk(s, p, smem, ph);
-      const float up = warp_sum(dot_chunk(cu, x, s.lane));
-      release_chunk(s, p);
-      const uint4* cg = acquire_chunk(s, p, smem, ph);
-      const float gt = warp_sum(dot_chunk(cg, x, s.lane));
-      release_chunk(s, p);
-      if (s.lane == 0 && !s.aborted) {
-        const float g = bf16_round(gt);
-        const float sl = bf16_round(g / (1.0f + __expf(-g)));
-        p.silu_out[u] = f32_to_bf16_bits(sl * bf16_round(up));
-      }
-    }
+  // LM head: warp -> CTA -> grid arg-max.  Every worker arrives, also those without rows.
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(kFullMask, best, o);
+    best = other > best ? other : best;
   }
-  publish(s, p, ph, s.g % kCounterShards);
-}
-
-// ---- phase 4: down-projection GEMV + residual.  fused_mlp_down_residual (operations.py:285-295).
-// A row is I/2048 consecutive chunks; one warp owns the whole row, so the K reduction has a fixed
-// order (the reference's kernel adds four split-K partials with bf16 CAS in arrival order,
-// decode_kernel/down_proj_gemv_residual.cu:39-52, 225-234).
-template <class S>
-__device__ __forceinline__ void phase_down(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
-  constexpr int kSlices = S::I / kChunkElems;
-  int r0, r1;
-  split_range(S::H, s.nwt, s.g, r0, r1);
-  if (r0 < r1 && wait_staged(s, p, ph)) {
-    for (int r = r0; r < r1 && !s.aborted; ++r) {
-      float acc = 0.f;
-#pragma unroll 1
-      for (int k = 0; k < kSlices; ++k) {
-        float x[64];
-        load_x64(x, smem + SmemLayout<S>::kOffActD + k * kChunkBytes, s.lane);
-        const uint4* c = acquire_chunk(s, p, smem, ph);
-        acc += dot_chunk(c, x, s.lane);
-        release_chunk(s, p);
-      }
-      acc = warp_sum(acc);
-      if (s.lane == 0 && !s.aborted) {
-        const float old = bf16_bits_to_f32(ldcg_u16(p.hidden + r));
-        p.hidden[r] = f32_to_bf16_bits(old + bf16_round(acc));
-      }
-    }
-  }
-  publish(s, p, ph, s.g % kCounterShards);
-}
-
-// ---- last phase: RMSNorm -> LM head GEMV -> logits (+ fused argmax).  fused_rms_lmhead_gemv
-// (operations.py:303-321); the argmax replaces `logits.argmax()` of the host loop (decode.py:1391-1395):
-// maximum of the bf16-rounded logits, lowest index on ties.
-template <class S>
-__device__ __forceinline__ void phase_lm_head(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
-  int r0, r1;
-  split_range(p.vocab, s.nwt, s.g, r0, r1);
-  unsigned long long best = 0ull;
-  if (r0 < r1 && wait_staged(s, p, ph)) {
-    float x[64];
-    const int buf = small_buf_index(ph, p.num_layers);
-    load_x64(x, smem + (buf ? SmemLayout<S>::kOffActB : SmemLayout<S>::kOffActA), s.lane);
-    unsigned short mine = 0;
-    for (int r = r0; r < r1 && !s.aborted; ++r) {
-      const uint4* c = acquire_chunk(s, p, smem, ph);
-      const float acc = warp_sum(dot_chunk(c, x, s.lane));
-      release_chunk(s, p);
-      const unsigned short bits = f32_to_bf16_bits(acc);
-      const unsigned long long key =
-          ((unsigned long long)float_ordered_bits(bf16_bits_to_f32(bits)) << 32) | (0xffffffffu - (unsigned)r);
-      best = key > best ? key : best;
-      const int i = r - r0;
-      if ((i & 31) == s.lane) mine = bits;
-      if ((i & 31) == 31 || r == r1 - 1) {
-        const int base = r0 + (i & ~31);
-        if (base + s.lane <= r) p.logits[base + s.lane] = mine;
-      }
-    }
-  }
-  // CTA-level then grid-level argmax; every worker arrives, also those without rows.
-  __syncwarp();
   if (s.lane == 0 && !s.aborted) {
     unsigned long long* cta_key = reinterpret_cast<unsigned long long*>(smem + SmemLayout<S>::kOffCtl + 8);
     unsigned* arrive = reinterpret_cast<unsigned*>(smem + SmemLayout<S>::kOffCtl + 4);
