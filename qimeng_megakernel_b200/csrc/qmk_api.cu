@@ -34,8 +34,11 @@ struct qmk_handle {
   size_t scratch_bytes;
   float* part_o;
   float* part_ml;
-  unsigned* counters;
-  size_t counters_bytes;
+  uint32_t* t_hid_o;
+  uint32_t* t_hid_d;
+  uint32_t* t_q;
+  uint32_t* t_attn;
+  uint32_t* t_silu;
   unsigned* tickets;
   unsigned long long* argmax_key;
   unsigned* status;
@@ -76,7 +79,8 @@ extern "C" const char* qmk_strerror(int code) {
 extern "C" const char* qmk_last_cuda_error(const qmk_handle* h) { return h ? h->cuda_err : ""; }
 
 static int reset_scratch(qmk_handle* h, cudaStream_t s) {
-  QMK_CUDA(h, cudaMemsetAsync(h->scratch, 0, h->scratch_bytes, s));
+  // everything but the status record, which sits last and is cleared only after it has been read
+  QMK_CUDA(h, cudaMemsetAsync(h->scratch, 0, (size_t)((unsigned char*)h->status - h->scratch), s));
   h->epoch = 0;
   return QMK_OK;
 }
@@ -125,23 +129,28 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
     e = cudaFuncSetAttribute(qmk_decode_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SmemLayout<Shape>::kTotal);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaFuncSetAttribute"); break; }
-    const size_t nph = (size_t)num_phases(d->num_layers);
     const size_t b_part_o = align_up((size_t)Shape::NH * kMaxSplits * Shape::HD * 4, 256);
     const size_t b_part_ml = align_up((size_t)Shape::NH * kMaxSplits * 2 * 4, 256);
-    const size_t b_counters = align_up(nph * kCounterShards * kCounterStrideWords * 4, 256);
+    const size_t b_hid = align_up((size_t)Shape::H * 4, 256);
+    const size_t b_q = align_up((size_t)(Shape::QDIM + 2 * Shape::NKV * Shape::HD) * 4, 256);
+    const size_t b_attn = align_up((size_t)Shape::QDIM * 4, 256);
+    const size_t b_silu = align_up((size_t)Shape::I * 4, 256);
     const size_t b_tickets = 512, b_argmax = 256, b_status = 256, b_tok = 256;
-    h->scratch_bytes = b_part_o + b_part_ml + b_counters + b_tickets + b_argmax + b_status + b_tok;
+    h->scratch_bytes = b_part_o + b_part_ml + 2 * b_hid + b_q + b_attn + b_silu + b_tickets + b_argmax + b_tok + b_status;
     e = cudaMalloc((void**)&h->scratch, h->scratch_bytes);
     if (e != cudaSuccess) { rc = QMK_ERR_OOM; cuda_fail(h, e, "cudaMalloc"); break; }
     unsigned char* q = h->scratch;
     h->part_o = (float*)q; q += b_part_o;
     h->part_ml = (float*)q; q += b_part_ml;
-    h->counters = (unsigned*)q; q += b_counters;
-    h->counters_bytes = b_counters;
+    h->t_hid_o = (uint32_t*)q; q += b_hid;
+    h->t_hid_d = (uint32_t*)q; q += b_hid;
+    h->t_q = (uint32_t*)q; q += b_q;
+    h->t_attn = (uint32_t*)q; q += b_attn;
+    h->t_silu = (uint32_t*)q; q += b_silu;
     h->tickets = (unsigned*)q; q += b_tickets;
     h->argmax_key = (unsigned long long*)q; q += b_argmax;
-    h->status = (unsigned*)q; q += b_status;
-    h->d_tok = (long long*)q;
+    h->d_tok = (long long*)q; q += b_tok;
+    h->status = (unsigned*)q;
     e = cudaMemset(h->scratch, 0, h->scratch_bytes);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaMemset"); break; }
   } while (0);
@@ -205,7 +214,11 @@ static void fill_params(const qmk_handle* h, Params& p, int pos) {
   p.kv_layer_stride = (long long)s.batch * s.kv_seq_len * p.kv_seq_stride;
   p.part_o = h->part_o;
   p.part_ml = h->part_ml;
-  p.counters = h->counters;
+  p.t_hid_o = h->t_hid_o;
+  p.t_hid_d = h->t_hid_d;
+  p.t_q = h->t_q;
+  p.t_attn = h->t_attn;
+  p.t_silu = h->t_silu;
   p.tickets = h->tickets;
   p.argmax_key = h->argmax_key;
   p.status = h->status;
@@ -245,7 +258,7 @@ static int check_step_args(const qmk_handle* h, int pos) {
 }
 
 static int step_with(qmk_handle* h, Params& p, cudaStream_t stream) {
-  if (h->epoch >= (1u << 24)) {
+  if (h->epoch >= (1u << 20)) {   // keeps epoch * phases inside 32 bits; tags restart from a zeroed scratch
     int rc = reset_scratch(h, stream);
     if (rc) return rc;
   }
@@ -289,8 +302,8 @@ extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin
     return QMK_OK;
   }
   if (phase_begin == phase_end) return QMK_OK;
-  // A synchronised sub-range leaves the counters of other phases behind: run it on zeroed
-  // counters at epoch 0 and zero them again afterwards.
+  // A synchronised sub-range leaves tags of an incomplete step behind: run it on zeroed scratch at
+  // epoch 0 and zero the scratch again afterwards.
   rc = reset_scratch(h, stream);
   if (rc) return rc;
   p.phase_begin = phase_begin;
@@ -300,9 +313,7 @@ extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin
   p.wait_first = h->wait_first;
   rc = launch(h, p, stream);
   if (rc) return rc;
-  QMK_CUDA(h, cudaMemsetAsync(h->counters, 0, h->counters_bytes, stream));
-  h->epoch = 0;
-  return QMK_OK;
+  return reset_scratch(h, stream);
 }
 
 extern "C" int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t host_tokens_len, int32_t first_pos,
@@ -353,6 +364,7 @@ extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
     // The aborted launch left counters and tickets mid-step: start over from a clean slate.
     int rc = reset_scratch(h, h->last_stream);
     if (rc) return rc;
+    QMK_CUDA(h, cudaMemsetAsync(h->status, 0, 32, h->last_stream));
     QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
     return QMK_ERR_DEVICE_TIMEOUT;
   }

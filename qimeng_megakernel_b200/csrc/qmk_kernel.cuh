@@ -1,22 +1,24 @@
-// The persistent decode megakernel for sm_100a: one CTA per SM, eight independent worker warps
-// plus one controller warp per CTA.
+// Core of the persistent decode megakernel for sm_100a: one CTA per SM, eight identical worker warps.
 //
-//  * Worker warps own a private ring of 4-KiB shared-memory slots.  Lane 0 streams the warp's
-//    weight chunks into the ring with cp.async.bulk (TMA engine, mbarrier byte completion); the
-//    stream is one static sequence that runs across phase and layer boundaries, so the next
-//    phase's weights are already in flight while the warp waits for its activations.
-//  * The controller warp of each CTA waits for the previous phase's dependency counters (32
-//    shards, one per lane, ld.acquire.gpu), stages the phase's activation vector into shared
-//    memory (fusing RMSNorm where the phase starts with one) and releases the workers through a
-//    shared-memory flag.
-//  * Workers publish a phase with one red.release.gpu per warp on a sharded counter.  Counters are
-//    never reset: the target of step n is (n+1) * publishers.
+//  * Weight stream.  Every warp owns a private ring of 4-KiB shared-memory slots.  Lane 0 streams
+//    the warp's weight chunks into it with cp.async.bulk (TMA engine, mbarrier byte completion); the
+//    stream is one static sequence that runs across phase and layer boundaries, so the next phases'
+//    weights are in flight while the warp waits for activations.
+//  * Hand-off between phases without fences or counters.  Every activation word that crosses SMs is
+//    written as ONE 32-bit store {bf16 value, 16-bit tag of (step, phase)}.  A consumer polls the
+//    data itself until every word carries the expected tag (the idea of NCCL's LL protocol).  The
+//    eight warps of a CTA each fetch one eighth of the vector ("cooperative staging"), drop it in
+//    shared memory, raise a per-warp flag and then wait for the other seven.
+//  * The residual stream never goes through memory on the critical path: the warp that owns row r
+//    in the O-projection owns it in the down-projection and in every later layer, so hidden[r]
+//    stays in a register of that warp.
 //
 // What each phase computes follows the reference's fused PyTorch ops, including their bf16
 // rounding points (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/
 // decode_schedule/fused/operations.py:126-321); the CUDA phases they correspond to in the
 // reference are decode_kernel/{rms_qkv_gemv_rope,decode_attention_splitkv,decode_attention_reduction,
-// oproj_gemv_residual,rms_upgate_gemv_silu,down_proj_gemv_residual,rms_lm_head}.cu.
+// oproj_gemv_residual,rms_upgate_gemv_silu,down_proj_gemv_residual,rms_lm_head}.cu, whose
+// cross-SM protocol is counters + acquire spins (decode_kernel/utils.cuh:266-328).
 #pragma once
 #include "qmk_device.cuh"
 #include "qmk_params.h"
@@ -30,31 +32,36 @@ namespace qmk {
 #ifndef QMK_SLOTS
 #define QMK_SLOTS 6
 #endif
-constexpr int kWorkers = QMK_WORKERS;  // worker warps per CTA
-constexpr int kSlots = QMK_SLOTS;      // ring slots per worker warp
-constexpr int kThreads = (kWorkers + 1) * 32;
+constexpr int kWorkers = QMK_WORKERS;  // warps per CTA (all of them stream weights)
+constexpr int kSlots = QMK_SLOTS;      // ring slots per warp
+constexpr int kThreads = kWorkers * 32;
 constexpr unsigned kAbortFlag = 0xffffffffu;
+static_assert(kWorkers <= 8, "the staging flags are polled by lanes 0..7");
 
 template <class S>
 struct SmemLayout {
   static constexpr int kRingBytes = kWorkers * kSlots * kChunkBytes;
-  static constexpr int kActSmall = S::H * 2;                        // bf16 activation vector
-  static constexpr int kActBigA = S::I * 2;                         // silu_out (bf16)
-  static constexpr int kActBigB = S::QDIM * 4;                      // q in fp32 for attention
+  static constexpr int kActSmall = S::H * 2;                                  // bf16 activation vector
+  static constexpr int kActBigA = S::I * 2;                                   // silu_out (bf16)
+  static constexpr int kActBigB = S::QDIM * 4 + 2 * S::NKV * S::HD * 2;       // q fp32 + new K/V rows bf16
   static constexpr int kActBig = kActBigA > kActBigB ? kActBigA : kActBigB;
   static constexpr int kOffRing = 0;
   static constexpr int kOffActA = kOffRing + kRingBytes;
   static constexpr int kOffActB = kOffActA + kActSmall;
   static constexpr int kOffActD = kOffActB + kActSmall;
   static constexpr int kOffBars = kOffActD + kActBig;                // kWorkers*kSlots u64
-  static constexpr int kOffCtl = kOffBars + kWorkers * kSlots * 8;   // control words
-  static constexpr int kOffRope = kOffCtl + 64;                      // cos[HD], sin[HD] of this step's position
+  static constexpr int kOffCtl = kOffBars + kWorkers * kSlots * 8;   // control words (128 B)
+  static constexpr int kOffRope = kOffCtl + 128;                     // cos[HD], sin[HD] of this step's position
   static constexpr int kTotal = kOffRope + S::HD * 8;
 };
-// control words (u32 index from kOffCtl): 0 staged, 1 lm_arrive, 2..3 cta argmax key (u64)
+// control block, 32-bit words from kOffCtl:
+//   [0..7]   part_done[w]: last phase (+1) whose staging part warp w has written; kAbortFlag = abort
+//   [8]      lm_arrive     [10..11] CTA arg-max key (u64)
+//   [16..23] sum-of-squares partials, buffer A     [24..31] buffer B
+constexpr int kCtlLmArrive = 8, kCtlKey = 10, kCtlSumSq = 16;
 
 __device__ __noinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
-                                             unsigned expected, int detail) {
+                                          unsigned expected, int detail) {
   if (atomicCAS(&p.status[kStCode], 0u, (unsigned)code) == 0u) {
     p.status[kStSm] = blockIdx.x;
     p.status[kStWarp] = warp;
@@ -66,16 +73,21 @@ __device__ __noinline__ void report_error(const Params& p, int code, int warp, i
   }
 }
 
-// Optional timeline: slot of (CTA, phase) <- globaltimer.  Slots: 0 dependency satisfied, 1 activations
-// staged (controller); worker 0: 2 enters the phase, 3 sees the staged flag, 4 has its first chunk,
-// 7 starts publishing, 5 leaves; 6 last worker leaves.
-__device__ __forceinline__ void trace_stamp(const Params& p, int ph, int slot, int lane) {
-  if (p.trace != nullptr && lane == 0)
-    p.trace[((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8 + slot] = globaltimer_ns();
+// Optional timeline: slot of (CTA, phase).  Warp 0 writes: 2 enters the phase (globaltimer ns),
+// 5 leaves it (ns); cycles spent 3 polling its staging part, 4 waiting for the other warps' parts,
+// 6 in the streaming loop + epilogue, 7 in the whole phase.
+__device__ __forceinline__ void trace_put(const Params& p, int ph, int slot, unsigned long long v, int lane) {
+  if (p.trace != nullptr && lane == 0) p.trace[((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8 + slot] = v;
+}
+
+// Tag of (step, phase): 1..65535, consecutive phases get consecutive tags, so a stale word (written
+// at most one step earlier) can never carry the tag a reader waits for.  0 = never written.
+__device__ __forceinline__ unsigned phase_tag(const Params& p, int ph) {
+  return (p.epoch * (unsigned)num_phases(p.num_layers) + (unsigned)ph) % 65535u + 1u;
 }
 
 // ------------------------------------------------------------------------------------------
-// Worker state: ring + issue cursor.  All fields are warp-uniform.
+// Worker state: ring + issue cursor.  All fields are warp-uniform except `res`.
 // ------------------------------------------------------------------------------------------
 template <class S>
 struct Worker {
@@ -90,16 +102,15 @@ struct Worker {
   // This worker's chunk range per streaming kind: identical for every layer, so the 32-bit
   // divisions of the even split are done once per launch.
   int q0, q1, o0, o1, u0, u1, d0, d1, l0, l1;
-  int staged_seen;         // highest staged value observed
+  float res;               // residual stream value of row (first row of this warp + lane), bf16-exact
+  bool res_valid;
   bool aborted;
-  bool trace_first;        // next acquired chunk is the first of its phase (timeline only)
-  long long cyc_wait, cyc_issue, cyc_stage;   // timeline only: cycles of worker 0 in chunk waits / copy issue / staged wait
   uint64_t policy;
   WeightBases wb;
 };
 
 __device__ __forceinline__ void split_range_u32(unsigned units, unsigned parts, unsigned g, int& lo, int& hi) {
-  lo = (int)((g * units) / parts);            // g * units < 2^32 is checked on the host
+  lo = (int)((g * units) / parts);            // (g + 1) * units < 2^32 is checked on the host
   hi = (int)(((g + 1u) * units) / parts);
 }
 
@@ -161,13 +172,11 @@ template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
   if (s.aborted || s.i_ph >= p.phase_end) return;
   if (s.lane == 0) {
-    const long long t0 = clock64();
     const int c = s.i_kind == kDown ? down_canonical<S>(s.i_c - s.d0, s.d0, s.d1) : s.i_c;
     const uint16_t* src = chunk_ptr<S>(s.wb, s.i_kind, s.i_layer, c);
     const uint32_t bar = s.bars + s.i_slot * 8;
     mbar_expect_tx(bar, kChunkBytes);
     bulk_g2s(s.ring + s.i_slot * kChunkBytes, src, kChunkBytes, bar, s.policy);
-    s.cyc_issue += clock64() - t0;
   }
   ++s.n_issued;
   s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
@@ -190,22 +199,17 @@ __device__ __noinline__ bool wait_slot_slow(const Params& p, uint32_t bar, uint3
     }
   }
 }
-template <class S>
-__device__ __forceinline__ bool wait_slot(Worker<S>& s, const Params& p, unsigned slot, unsigned parity, int phase) {
-  const uint32_t bar = s.bars + slot * 8;
-  if (mbar_try_wait(bar, parity)) return true;
-  return wait_slot_slow(p, bar, parity, s.w, phase, s.n_acquired, s.n_issued, (int)slot, s.lane);
-}
 
-// Next chunk in consumption order: waits for it, returns the slot (generic shared pointer) and
-// advances the consume cursor; returns the slot's shared address.  The slot stays owned by the warp until release_chunks().
+// Next chunk in consumption order: waits for it, advances the consume cursor and returns the slot's
+// shared address.  The slot stays owned by the warp until release_chunks().
 template <class S>
 __device__ __forceinline__ uint32_t acquire_chunk(Worker<S>& s, const Params& p, int phase) {
   const unsigned slot = s.c_slot;
   if (!s.aborted) {
-    const long long t0 = clock64();
-    if (!wait_slot(s, p, slot, s.c_par, phase)) s.aborted = true;
-    s.cyc_wait += clock64() - t0;
+    const uint32_t bar = s.bars + slot * 8;
+    if (!mbar_try_wait(bar, s.c_par) &&
+        !wait_slot_slow(p, bar, s.c_par, s.w, phase, s.n_acquired, s.n_issued, (int)slot, s.lane))
+      s.aborted = true;
     ++s.n_acquired;
     if (++s.c_slot == kSlots) {
       s.c_slot = 0;
@@ -219,45 +223,6 @@ template <class S>
 __device__ __forceinline__ void release_chunks(Worker<S>& s, const Params& p, int n) {
   __syncwarp();
   for (int i = 0; i < n; ++i) issue_one(s, p);
-}
-
-// Wait until the controller has staged the activations of `phase` (staged >= phase+1).
-template <class S>
-__device__ __forceinline__ bool wait_staged(Worker<S>& s, const Params& p, int phase) {
-  if (s.aborted) return false;
-  if (s.staged_seen > phase && s.staged_seen != (int)kAbortFlag) return true;
-  const long long ts0 = clock64();
-  unsigned v = 0;
-  if (s.lane == 0) {
-    const long long t0 = clock64();
-    for (unsigned it = 0;; ++it) {
-      v = ld_acquire_cta_shared(s.ctl);
-      if (v == kAbortFlag || v >= (unsigned)(phase + 1)) break;
-      if ((it & 1023u) == 1023u && clock64() - t0 > 4 * p.timeout_cycles) {   // outlasts the controller's own wait
-        report_error(p, kErrStageWait, s.w, phase, v, (unsigned)(phase + 1), 0);
-        v = kAbortFlag;
-        break;
-      }
-    }
-  }
-  v = __shfl_sync(kFullMask, v, 0);
-  s.cyc_stage += clock64() - ts0;
-  if (v == kAbortFlag) {
-    s.aborted = true;
-    return false;
-  }
-  s.staged_seen = (int)v;
-  return true;
-}
-
-// Publish this warp's share of `phase` (all of its global stores precede the release).
-template <class S>
-__device__ __forceinline__ void publish(const Worker<S>& s, const Params& p, int phase, int shard) {
-  __syncwarp();
-  if (p.sync && !s.aborted && s.lane == 0) {
-    // red.release orders every earlier store of this warp (made visible to lane 0 by the __syncwarp).
-    red_release_gpu_add(p.counters + ((size_t)phase * kCounterShards + shard) * kCounterStrideWords, 1u);
-  }
 }
 
 // Which small activation buffer (A or B) a phase uses: they alternate along the phase sequence.
@@ -281,6 +246,7 @@ __device__ __forceinline__ int small_buf_index(int phase, int num_layers) {
 // accumulation is fp32, so the arithmetic is the same as an fp32 FMA chain in a different order.
 // Eight consecutive pseudo-rows of one piece index are 128 contiguous bytes: ldmatrix reads them
 // without bank conflicts, and the B fragments are plain 32-bit words x32[32*i + lane].
+// (tcgen05 tiles pay off only when the batch makes the projection a real matrix product.)
 // ------------------------------------------------------------------------------------------
 struct XFrag {
   uint32_t b[32];   // b[2t], b[2t+1]: B fragment of k-step t
@@ -290,6 +256,17 @@ __device__ __forceinline__ void load_xfrag(XFrag& xf, const unsigned char* act_b
   const uint32_t* v = reinterpret_cast<const uint32_t*>(act_bf16);
 #pragma unroll
   for (int i = 0; i < 32; ++i) xf.b[i] = v[32 * i + lane];
+}
+
+// The same, applying RMSNorm on the way: y = bf16(g * bf16(x * rstd))  (_rms_norm, operations.py:126-131).
+__device__ __forceinline__ void load_xfrag_normed(XFrag& xf, const unsigned char* act_bf16, const uint32_t (&gains)[32],
+                                                  float rstd, int lane) {
+  const uint32_t* v = reinterpret_cast<const uint32_t*>(act_bf16);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const uint32_t x = v[32 * i + lane], g = gains[i];
+    xf.b[i] = pack_bf16x2(bf_lo(g) * bf16_round(bf_lo(x) * rstd), bf_hi(g) * bf16_round(bf_hi(x) * rstd));
+  }
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&a)[4], uint32_t saddr) {
@@ -339,4 +316,5 @@ __device__ __forceinline__ void diag_reduce(const float (&cc)[4], int lane, floa
 
 }  // namespace qmk
 
+#include "qmk_staging.cuh"
 #include "qmk_phases.cuh"

@@ -9,6 +9,7 @@ namespace qmk {
 
 // Words of the device status record (mirrors qmk_status in the C ABI).
 enum StatusWord : int { kStCode = 0, kStSm = 1, kStWarp = 2, kStPhase = 3, kStSeen = 4, kStExpected = 5, kStDetail = 6 };
+// 1: a producer's tagged words never arrived; 2: a weight copy never completed; 3: another warp of the CTA never staged its part
 enum StatusCode : int { kOkCode = 0, kErrCounterWait = 1, kErrCopyWait = 2, kErrStageWait = 3 };
 
 struct Params {
@@ -42,8 +43,13 @@ struct Params {
   // ---- library-owned scratch ----
   float* part_o;                 // [NH, kMaxSplits, HD] un-normalised split-KV partial outputs
   float* part_ml;                // [NH, kMaxSplits, 2]  (running max in log2 domain, sum)
-  unsigned* counters;            // [num_phases, 32 shards, 32 words]
-  unsigned* tickets;             // [NKV] split-KV arrival tickets + [32] lm-head ticket at tickets[64]
+  // tagged activation words {low 16: bf16 value, high 16: tag of (step, phase)}: the cross-SM hand-off
+  uint32_t* t_hid_o;             // [H]   residual stream after the O-projection
+  uint32_t* t_hid_d;             // [H]   residual stream after the down-projection
+  uint32_t* t_q;                 // [QDIM + 2*NKV*HD]  q_post_rope, then this step's K row and V row
+  uint32_t* t_attn;              // [QDIM] attention output
+  uint32_t* t_silu;              // [I]   SwiGLU output
+  unsigned* tickets;             // [2][32] split-KV arrival tickets by layer parity; lm-head ticket at [64]
   unsigned long long* argmax_key;  // packed (ordered logit bits << 32) | ~index
   unsigned* status;              // [8] status words
   unsigned long long* trace;     // optional [CTAs, num_phases, 8] globaltimer stamps (ns); null = off
@@ -52,7 +58,7 @@ struct Params {
   int vocab;
   int pos;                       // position of the token being fed
   int phase_begin, phase_end;    // phases executed by this launch
-  int sync;                      // 1: device-side dependency counters; 0: single phase, stream-ordered
+  int sync;                      // 1: phases hand off through tagged words; 0: single phase, stream-ordered
   int wait_first;                // 1: also wait for the dependency of phase_begin (debug / failure test)
   unsigned epoch;                // completed synchronised steps since the counters were last zeroed
   float eps;

@@ -2,7 +2,7 @@
 //
 // All weight-streaming phases (QKV, O-proj, up/gate, down, LM head) share ONE instance of the hot
 // loop (acquire chunks -> tensor-pipe dot products -> release) and differ only in their epilogue;
-// keeping a single copy keeps the persistent kernel's code footprint inside the instruction cache.
+// keeping a single copy keeps the persistent kernel's code footprint small.
 #pragma once
 
 namespace qmk {
@@ -21,11 +21,6 @@ __device__ __forceinline__ const uint16_t* residual_src(const Params& p, int lay
   return p.hidden;
 }
 
-template <class S>
-__device__ __forceinline__ const unsigned char* small_act(const Params& p, const unsigned char* smem, int ph) {
-  return smem + (small_buf_index(ph, p.num_layers) ? SmemLayout<S>::kOffActB : SmemLayout<S>::kOffActA);
-}
-
 __device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, int row) {
   return ((unsigned long long)float_ordered_bits(bf16_bits_to_f32(bits)) << 32) | (0xffffffffu - (unsigned)row);
 }
@@ -34,32 +29,40 @@ __device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, in
 
 // QKV item = one RoPE pair (rows 2u, 2u+1).  fused_rms_qkvproj_gemv_rope (operations.py:151-215):
 // the GEMV result is rounded to bf16 (einsum on bf16 tensors), the rotation is fp32 with separately
-// rounded products, the result is rounded to bf16 and written to q_post_rope / the KV cache row.
+// rounded products, the result is rounded to bf16 and written to q_post_rope / the KV cache row and,
+// tagged, to the scratch the attention phase of this step reads.
 template <class S>
 __device__ __forceinline__ void epilogue_qkv(const Params& p, const unsigned char* smem, int layer, int unit,
-                                             float a, float b) {
+                                             float a, float b, unsigned tagw) {
   const float* rope = reinterpret_cast<const float*>(smem + SmemLayout<S>::kOffRope);
   const int row = 2 * unit;
   a = bf16_round(a);
   b = bf16_round(b);
   constexpr int kStart = S::NH * S::HD;
   constexpr int vStart = kStart + S::NKV * S::HD;
+  uint32_t packed;
+  uint16_t* dst;
+  uint32_t* tdst;
   if (row < vStart) {
     const int d = row % S::HD;
     const float c0 = rope[d], c1 = rope[d + 1], s0 = rope[S::HD + d], s1 = rope[S::HD + d + 1];
     const float o0 = __fadd_rn(__fmul_rn(a, c0), __fmul_rn(-b, s0));
     const float o1 = __fadd_rn(__fmul_rn(b, c1), __fmul_rn(a, s1));
-    const uint32_t packed = pack_bf16x2(o0, o1);
+    packed = pack_bf16x2(o0, o1);
     if (row < kStart) {
-      *reinterpret_cast<uint32_t*>(p.q_post_rope + row) = packed;
+      dst = p.q_post_rope + row;
+      tdst = p.t_q + row;
     } else {
-      uint16_t* dst = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - kStart);
-      *reinterpret_cast<uint32_t*>(dst) = packed;
+      dst = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - kStart);
+      tdst = p.t_q + S::QDIM + (row - kStart);
     }
   } else {
-    uint16_t* dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - vStart);
-    *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(a, b);
+    packed = pack_bf16x2(a, b);
+    dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - vStart);
+    tdst = p.t_q + S::QDIM + S::NKV * S::HD + (row - vStart);
   }
+  *reinterpret_cast<uint32_t*>(dst) = packed;
+  if (p.sync) *reinterpret_cast<uint2*>(tdst) = make_uint2((packed & 0xffffu) | tagw, (packed >> 16) | tagw);
 }
 
 // SwiGLU item = (up row u, gate row u).  fused_mlp_upgate (operations.py:265-282): up and gate rounded
@@ -76,17 +79,54 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
 //        down-proj: an item is one row = I/2048 chunks; rows go in pairs, k-slice by k-slice (the
 //        order down_canonical() gives the weight stream), each slice against its own activations.
 // Residual phases (fused_oproj_gemv_residual, operations.py:251-262; fused_mlp_down_residual, 285-295):
-// hidden[r] = bf16(hidden[r] + bf16(W[r,:] . x)); the old values are fetched, one per lane, before the
-// first chunk is awaited.  One warp owns a whole down-proj row, so its K reduction has a fixed order
-// (the reference adds four split-K partials with bf16 CAS in arrival order,
-// decode_kernel/down_proj_gemv_residual.cu:39-52, 225-234).
+// hidden[r] = bf16(hidden[r] + bf16(W[r,:] . x)).  One warp owns a whole down-proj row, so its K
+// reduction has a fixed order (the reference adds four split-K partials with bf16 CAS in arrival
+// order, decode_kernel/down_proj_gemv_residual.cu:39-52, 225-234).
 // LM head (fused_rms_lmhead_gemv, operations.py:303-321) also keeps the arg-max of the bf16 logits,
 // lowest index on ties, replacing `logits.argmax()` of the host loop (decode.py:1391-1395).
 template <class S>
 __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kind) {
+  using L = SmemLayout<S>;
   constexpr int kSlices = S::I / kChunkElems;
   static_assert(S::QDIM == kChunkElems && S::H == kChunkElems, "rows of QKV/O/up/gate/LM must be one chunk");
   const int layer = phase_layer(ph);
+  const bool tagged = p.sync && (ph > p.phase_begin || p.wait_first);
+  const unsigned tag_in = phase_tag(p, ph - 1);
+  const unsigned tagw = phase_tag(p, ph) << 16;
+  const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
+  const int sbuf = small_buf_index(ph, p.num_layers);
+  unsigned char* act = smem + (kind == kDown ? L::kOffActD : (sbuf ? L::kOffActB : L::kOffActA));
+  float* sumsq = reinterpret_cast<float*>(smem + L::kOffCtl) + kCtlSumSq + sbuf * 8;
+  const long long tq0 = clock64();
+
+  // RMSNorm gains do not depend on the step: fetch them before polling for the activations.
+  uint32_t gains[32];
+  if (normed) {
+    const uint16_t* gsrc = kind == kQkv ? p.attn_norm + (size_t)layer * S::H
+                                        : (kind == kUpGate ? p.mlp_norm + (size_t)layer * S::H : p.lm_norm);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) gains[i] = __ldg(reinterpret_cast<const uint32_t*>(gsrc) + 32 * i + s.lane);
+  }
+
+  // ---- stage this warp's eighth of the phase input
+  {
+    bool ok;
+    float ss = 0.f;
+    if (kind == kDown) {
+      ok = stage_part_bf16<S::I>(p, p.t_silu, p.silu_out, tagged, tag_in, act, s.w, s.lane, ph, ss);
+    } else {
+      const uint32_t* tsrc = kind == kOproj ? p.t_attn : (kind == kUpGate ? p.t_hid_o : p.t_hid_d);
+      const uint16_t* psrc = kind == kOproj ? p.attn_out
+                                            : (kind == kQkv || (kind == kLmHead && p.num_layers == 0)
+                                                   ? residual_src<S>(p, layer) : p.hidden);
+      ok = stage_part_bf16<S::H>(p, tsrc, psrc, tagged, tag_in, act, s.w, s.lane, ph, ss);
+    }
+    if (!ok) s.aborted = true;
+    if (normed && s.lane == 0) sumsq[s.w] = ss;
+    raise_part_flag(s.ctl, s.w, s.lane, s.aborted ? kAbortFlag : (unsigned)(ph + 1));
+  }
+  const long long tq1 = clock64();
+
   int c0, c1;
   kind_range(s, kind, c0, c1);
   const bool unit_pairs = kind == kQkv || kind == kUpGate;
@@ -94,21 +134,34 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   const int cpi = unit_pairs ? 2 : nsl;          // chunks per item
   const int i0 = c0 / cpi, i1 = c1 / cpi;
   unsigned long long best = 0ull;
-  const long long tq0 = clock64();
-  long long tq1 = 0, tq2 = 0, tq3 = 0;
-  if (i0 < i1 && wait_staged(s, p, ph)) {
-    tq1 = clock64() - tq0;
-    const unsigned char* act = kind == kDown ? smem + SmemLayout<S>::kOffActD : small_act<S>(p, smem, ph);
-    const uint16_t* res = kind == kOproj ? residual_src<S>(p, layer) : p.hidden;
-    const bool residual = kind == kOproj || kind == kDown;
+  long long tq2 = tq1;
+  long long cyc_acq = 0, cyc_mma = 0, cyc_rel = 0, cyc_red = 0, cyc_xf = 0;
+  if (i0 < i1 && !s.aborted) {
+    if (!wait_parts(p, s.ctl, s.w, s.lane, ph)) s.aborted = true;
+    tq2 = clock64();
     XFrag xf;
-    if (nsl == 1) load_xfrag(xf, act, s.lane);
-    tq2 = clock64() - tq0;
+    if (normed) {
+      float tot = 0.f;
+#pragma unroll
+      for (int j = 0; j < kWorkers; ++j) tot += sumsq[j];
+      load_xfrag_normed(xf, act, gains, rsqrtf(tot * (1.0f / S::H) + p.eps), s.lane);
+    } else if (nsl == 1) {
+      load_xfrag(xf, act, s.lane);
+    }
+    cyc_xf = clock64() - tq2;
+    const bool residual = kind == kOproj || kind == kDown;
+    const uint16_t* res = kind == kOproj ? residual_src<S>(p, layer) : p.hidden;
+    uint32_t* tres = kind == kOproj ? p.t_hid_o : p.t_hid_d;
 #pragma unroll 1
     for (int ib = i0; ib < i1 && !s.aborted; ib += 32) {
       const int nb = (i1 - ib) < 32 ? (i1 - ib) : 32;
+      // residual value of this lane's row: kept in a register from phase to phase for the first
+      // 32 rows of the warp, re-read (this thread wrote it) for any further rows.
       float old = 0.f;
-      if (residual && s.lane < nb) old = bf16_bits_to_f32(ldcg_u16(res + ib + s.lane));
+      if (residual && s.lane < nb) {
+        if (ib == i0 && s.res_valid) old = s.res;
+        else old = bf16_bits_to_f32(ldcg_u16(res + ib + s.lane));
+      }
       float va = 0.f, vb = 0.f;
       const int step = unit_pairs ? 1 : 2;
 #pragma unroll 1
@@ -118,13 +171,20 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
 #pragma unroll 1
         for (int k = 0; k < nsl; ++k) {
           if (nsl > 1) load_xfrag(xf, act + k * kChunkBytes, s.lane);
+          const long long ta = clock64();
           const uint32_t a0 = acquire_chunk(s, p, ph);
           const uint32_t a1 = two ? acquire_chunk(s, p, ph) : a0;
+          const long long tb = clock64();
           mma_chunk_pair(cc, a0, a1, xf, s.lane);
+          const long long tc = clock64();
           release_chunks(s, p, two ? 2 : 1);
+          const long long td = clock64();
+          cyc_acq += tb - ta; cyc_mma += tc - tb; cyc_rel += td - tc;
         }
         float sa, sb;
+        const long long te = clock64();
         diag_reduce(cc, s.lane, sa, sb);
+        cyc_red += clock64() - te;
         if (s.lane == i) {
           va = sa;
           vb = sb;
@@ -134,8 +194,13 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
       if (s.lane < nb && !s.aborted) {
         const int item = ib + s.lane;
         switch (kind) {
-          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb); break;
-          case kUpGate: p.silu_out[item] = epilogue_silu(va, vb); break;
+          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb, tagw); break;
+          case kUpGate: {
+            const unsigned short bits = epilogue_silu(va, vb);
+            p.silu_out[item] = bits;
+            if (p.sync) p.t_silu[item] = bits | tagw;
+            break;
+          }
           case kLmHead: {
             const unsigned short bits = f32_to_bf16_bits(va);
             p.logits[item] = bits;
@@ -143,32 +208,42 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
             best = key > best ? key : best;
             break;
           }
-          default: p.hidden[item] = f32_to_bf16_bits(old + bf16_round(va)); break;
+          default: {
+            const unsigned short bits = f32_to_bf16_bits(old + bf16_round(va));
+            p.hidden[item] = bits;
+            if (p.sync) tres[item] = bits | tagw;
+            if (ib == i0) s.res = bf16_bits_to_f32(bits);
+            break;
+          }
         }
       }
+      if (residual && ib == i0) s.res_valid = true;
     }
   }
-  tq3 = clock64() - tq0;
-  if (kind != kLmHead) {
-    publish(s, p, ph, s.g % kCounterShards);
-    if (s.w == 0 && s.lane == 0 && p.trace != nullptr) {
-      unsigned long long* t = p.trace + ((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8;
-      t[3] = tq1; t[4] = tq2; t[6] = tq3; t[7] = clock64() - tq0;
-    }
-    return;
+  if (s.w == 0) {
+    const long long tq3 = clock64();
+    trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
+    trace_put(p, ph, 4, (unsigned long long)(tq2 - tq1), s.lane);
+    trace_put(p, ph, 6, (unsigned long long)(tq3 - tq2), s.lane);
+    // diagnostic packing: acquire | mma | release | reduce | xfrag cycles (16 bits each would overflow: use slots 0,1 too)
+    trace_put(p, ph, 0, ((unsigned long long)cyc_acq << 32) | (unsigned long long)(cyc_mma & 0xffffffffll), s.lane);
+    trace_put(p, ph, 1, ((unsigned long long)cyc_rel << 32) | (unsigned long long)(cyc_red & 0xffffffffll), s.lane);
+    trace_put(p, ph, 7, (unsigned long long)cyc_xf, s.lane);
   }
-  // LM head: warp -> CTA -> grid arg-max.  Every worker arrives, also those without rows.
+  if (kind != kLmHead) return;
+
+  // LM head: warp -> CTA -> grid arg-max.  Every warp arrives, also those without rows.
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const unsigned long long other = __shfl_xor_sync(kFullMask, best, o);
     best = other > best ? other : best;
   }
   if (s.lane == 0 && !s.aborted) {
-    unsigned long long* cta_key = reinterpret_cast<unsigned long long*>(smem + SmemLayout<S>::kOffCtl + 8);
-    unsigned* arrive = reinterpret_cast<unsigned*>(smem + SmemLayout<S>::kOffCtl + 4);
+    unsigned* ctl = reinterpret_cast<unsigned*>(smem + L::kOffCtl);
+    unsigned long long* cta_key = reinterpret_cast<unsigned long long*>(ctl + kCtlKey);
     atomicMax(cta_key, best);
     __threadfence();
-    if (atomicAdd(arrive, 1u) == (unsigned)(kWorkers - 1)) {
+    if (atomicAdd(ctl + kCtlLmArrive, 1u) == (unsigned)(kWorkers - 1)) {
       const unsigned long long k = atomicMax(cta_key, 0ull);
       atomicMax(p.argmax_key, k);
       __threadfence();

@@ -5,7 +5,10 @@ each phase), in the manner of the reference's pyvm_to_megakernel op tests
 (qimeng_megakernel/verifier/LLM/llama/llama3_2__1b/A100/single_batch/pyvm_to_megakernel/test_op_qkv_rope.py:22-62).
 Tolerances (stated once here): a per-op output may differ from the bf16 oracle by bf16 rounding of a
 differently-ordered fp32 sum: |d| <= 1e-2*|ref| + 2e-3*max|ref|.  Whole-step hidden states are held to
-rtol 2e-2 against the fp32 oracle in the L2 sense and elementwise with an absolute floor of 2e-2*rms.
+rtol 2e-2 against the fp32 oracle: relative L2 error <= 2e-2 and elementwise |d| <= 2e-2*|ref| + 5e-2*rms(ref)
+(the reference's own bf16 route sits at relative L2 ~1e-2 and elementwise ~3.3e-2*(|ref|+rms) from fp32 on
+these weights, so a tighter elementwise bound would reject the reference itself); and to relative L2 <= 1e-2
+against the bf16 oracle.
 """
 import pytest
 import torch
@@ -133,8 +136,10 @@ def test_full_step_teacher_forced(env):
                 ref = st32.layer_hidden[l]
                 got = g.hidden_states.float().cpu()
                 assert U.rel_l2(got, ref) <= 2e-2, f"layer {l} pos {pos}: rel L2 {U.rel_l2(got, ref):.4g}"
-                tol = 2e-2 * ref.abs() + 2e-2 * float(ref.pow(2).mean().sqrt())
-                assert bool(((got - ref).abs() <= tol).all()), f"layer {l} pos {pos}: elementwise rtol 2e-2"
+                tol = 2e-2 * ref.abs() + 5e-2 * float(ref.pow(2).mean().sqrt())
+                assert bool(((got - ref).abs() <= tol).all()), f"layer {l} pos {pos}: elementwise rtol 2e-2 + floor"
+                ref16 = st.layer_hidden[l]
+                assert U.rel_l2(got, ref16) <= 1e-2, f"layer {l} pos {pos}: vs bf16 oracle {U.rel_l2(got, ref16):.4g}"
             g.k_cache.copy_(kc); g.v_cache.copy_(vc)
         g.hidden_states.copy_(g.embed_tokens[tok]); g.position_id = pos
         mk(g)
