@@ -23,7 +23,7 @@ struct qmk_handle {
   bool bound;
   int device;
   int n_sm;
-  unsigned epoch;
+  unsigned launch_seq;
   long long timeout_cycles;
   int wait_first;
   long long launches;
@@ -32,8 +32,7 @@ struct qmk_handle {
   // scratch (one allocation)
   unsigned char* scratch;
   size_t scratch_bytes;
-  float* part_o;
-  float* part_ml;
+  unsigned long long* part_rec;
   uint32_t* t_hid_o;
   uint32_t* t_hid_d;
   uint32_t* t_q;
@@ -81,7 +80,6 @@ extern "C" const char* qmk_last_cuda_error(const qmk_handle* h) { return h ? h->
 static int reset_scratch(qmk_handle* h, cudaStream_t s) {
   // everything but the status record, which sits last and is cleared only after it has been read
   QMK_CUDA(h, cudaMemsetAsync(h->scratch, 0, (size_t)((unsigned char*)h->status - h->scratch), s));
-  h->epoch = 0;
   return QMK_OK;
 }
 
@@ -129,19 +127,17 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
     e = cudaFuncSetAttribute(qmk_decode_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SmemLayout<Shape>::kTotal);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaFuncSetAttribute"); break; }
-    const size_t b_part_o = align_up((size_t)Shape::NH * kMaxSplits * Shape::HD * 4, 256);
-    const size_t b_part_ml = align_up((size_t)Shape::NH * kMaxSplits * 2 * 4, 256);
+    const size_t b_part = align_up((size_t)Shape::NH * kMaxSplits * (Shape::HD + 2) * 8, 256);
     const size_t b_hid = align_up((size_t)Shape::H * 4, 256);
     const size_t b_q = align_up((size_t)(Shape::QDIM + 2 * Shape::NKV * Shape::HD) * 4, 256);
     const size_t b_attn = align_up((size_t)Shape::QDIM * 4, 256);
     const size_t b_silu = align_up((size_t)Shape::I * 4, 256);
     const size_t b_tickets = 512, b_argmax = 256, b_status = 256, b_tok = 256;
-    h->scratch_bytes = b_part_o + b_part_ml + 2 * b_hid + b_q + b_attn + b_silu + b_tickets + b_argmax + b_tok + b_status;
+    h->scratch_bytes = b_part + 2 * b_hid + b_q + b_attn + b_silu + b_tickets + b_argmax + b_tok + b_status;
     e = cudaMalloc((void**)&h->scratch, h->scratch_bytes);
     if (e != cudaSuccess) { rc = QMK_ERR_OOM; cuda_fail(h, e, "cudaMalloc"); break; }
     unsigned char* q = h->scratch;
-    h->part_o = (float*)q; q += b_part_o;
-    h->part_ml = (float*)q; q += b_part_ml;
+    h->part_rec = (unsigned long long*)q; q += b_part;
     h->t_hid_o = (uint32_t*)q; q += b_hid;
     h->t_hid_d = (uint32_t*)q; q += b_hid;
     h->t_q = (uint32_t*)q; q += b_q;
@@ -212,8 +208,7 @@ static void fill_params(const qmk_handle* h, Params& p, int pos) {
   p.out_tokens_len = s.out_tokens_len;
   p.kv_seq_stride = (long long)Shape::NKV * Shape::HD;
   p.kv_layer_stride = (long long)s.batch * s.kv_seq_len * p.kv_seq_stride;
-  p.part_o = h->part_o;
-  p.part_ml = h->part_ml;
+  p.part_rec = h->part_rec;
   p.t_hid_o = h->t_hid_o;
   p.t_hid_d = h->t_hid_d;
   p.t_q = h->t_q;
@@ -241,7 +236,8 @@ static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another
-  attr[0].val.cooperative = p.sync ? 1 : 0;
+  attr[0].val.cooperative = 1;
+  p.launch_seq = ++h->launch_seq;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p));
@@ -258,17 +254,15 @@ static int check_step_args(const qmk_handle* h, int pos) {
 }
 
 static int step_with(qmk_handle* h, Params& p, cudaStream_t stream) {
-  if (h->epoch >= (1u << 20)) {   // keeps epoch * phases inside 32 bits; tags restart from a zeroed scratch
+  if (h->launch_seq >= (1u << 23)) {   // record tags are launch_seq * 256 + phase: restart from a zeroed scratch
     int rc = reset_scratch(h, stream);
     if (rc) return rc;
+    h->launch_seq = 0;
   }
   p.phase_begin = 0;
   p.phase_end = num_phases(p.num_layers);
   p.sync = 1;
-  p.epoch = h->epoch;
-  int rc = launch(h, p, stream);
-  if (rc == QMK_OK) h->epoch++;
-  return rc;
+  return launch(h, p, stream);
 }
 
 extern "C" int qmk_decode_step(qmk_handle* h, int32_t pos_id, void* cuda_stream) {
@@ -302,18 +296,17 @@ extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin
     return QMK_OK;
   }
   if (phase_begin == phase_end) return QMK_OK;
-  // A synchronised sub-range leaves tags of an incomplete step behind: run it on zeroed scratch at
-  // epoch 0 and zero the scratch again afterwards.
-  rc = reset_scratch(h, stream);
-  if (rc) return rc;
+  // Tags are unique per launch, so a sub-range needs no clean-up.  The failure-detection knob waits
+  // for words nothing writes: zero the scratch first so that no stale tag can match by accident.
+  if (h->wait_first) {
+    rc = reset_scratch(h, stream);
+    if (rc) return rc;
+  }
   p.phase_begin = phase_begin;
   p.phase_end = phase_end;
   p.sync = 1;
-  p.epoch = 0;
   p.wait_first = h->wait_first;
-  rc = launch(h, p, stream);
-  if (rc) return rc;
-  return reset_scratch(h, stream);
+  return launch(h, p, stream);
 }
 
 extern "C" int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t host_tokens_len, int32_t first_pos,
@@ -361,7 +354,7 @@ extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
   out->detail = (int32_t)words[kStDetail];
   out->reserved = 0;
   if (out->code != 0) {
-    // The aborted launch left counters and tickets mid-step: start over from a clean slate.
+    // The aborted launch left half-written tagged words: start over from a clean slate.
     int rc = reset_scratch(h, h->last_stream);
     if (rc) return rc;
     QMK_CUDA(h, cudaMemsetAsync(h->status, 0, 32, h->last_stream));

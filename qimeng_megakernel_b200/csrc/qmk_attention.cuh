@@ -4,10 +4,17 @@
 // in fp32 over keys 0..pos, output rounded to bf16.  Partials keep a running maximum in the log2
 // domain and are merged with exp2, as the reference's split / reduction kernels do
 // (decode_kernel/decode_attention_splitkv.cu:265-281, 355-381; decode_attention_reduction.cu:212-251).
-// Unlike the reference there is no separate reduction instruction: the last partial of a kv head
-// to arrive (atomic ticket) performs the merge, which saves one cross-SM hand-off per layer.
-// The heads of a GQA group are processed by a rolled loop whose per-head state rotates through
-// fixed registers, so the code is emitted once instead of once per head.
+//
+// Differences from the reference's two instructions (split, then reduction behind a counter):
+//  * a unit fetches the K / V rows of its first block BEFORE it waits for this step's q: old keys do
+//    not depend on the step, so their HBM latency hides behind the QKV phase's tail;
+//  * this step's own K / V row never goes through the cache on the critical path: it is staged from
+//    the tagged scratch next to q;
+//  * partials are written as self-validating records (every 64-bit word = {fp32 value, 32-bit tag}),
+//    and the units (kv head, part < GQA) merge one head each by polling those records: no fence,
+//    no atomic, no separate reduction phase;
+//  * the heads of a GQA group are processed by a rolled loop whose per-head state rotates through
+//    fixed registers, so the code is emitted once instead of once per head.
 #pragma once
 
 namespace qmk {
@@ -51,14 +58,7 @@ __device__ __forceinline__ bool stage_attn_part(const Params& p, unsigned char* 
         ok = ok && tags_ok(vk[j], tagw);
       }
       if (__all_sync(kFullMask, ok)) break;
-      if ((it & 15u) == 15u) {
-        const bool expired = clock64() - t0 > p.timeout_cycles;
-        const unsigned st = ld_relaxed_gpu(p.status + kStCode);
-        if (__any_sync(kFullMask, expired || st != 0u)) {
-          if (!ok && st == 0u) report_error(p, kErrCounterWait, warp, ph, vq[0].x >> 16, tag, lane);
-          return false;
-        }
-      }
+      if ((it & 15u) == 15u && poll_give_up(p, t0, ok, vq[0].x >> 16, tag, warp, ph, lane)) return false;
     }
 #pragma unroll
     for (int j = 0; j < NQ; ++j) {
@@ -79,23 +79,86 @@ __device__ __forceinline__ bool stage_attn_part(const Params& p, unsigned char* 
   return true;
 }
 
+// One block of 32 keys of one kv head: lane = key for K (a whole row per lane), lane = output dims for V.
 template <class S>
-__device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const unsigned char* smem, int ph,
-                                          int kvh, int part, int bps, int P, bool staged_kv, unsigned tagw) {
+struct KvBlock {
+  static constexpr int KV4 = S::HD / 8;     // uint4 per K row
+  static constexpr int DPL = S::HD / 32;    // V dims per lane
+  uint4 k[KV4];
+  uint32_t v[kAttnBlockKeys][DPL / 2];
+};
+
+// Rows come from the cache in global memory; rows past the end of the range are clamped to its last
+// row (they get probability 0).  With `skip_pos` the row of this step's own position is not fetched
+// (its slot keeps whatever it held): patch_new_row() fills it from shared memory after the staging.
+template <class S>
+__device__ __forceinline__ void load_kv_block(KvBlock<S>& b, const Params& p, int layer, int kvh, int kb, int k1,
+                                              int lane) {
+  constexpr int HD = S::HD, DPL = KvBlock<S>::DPL;
+  const uint16_t* kbase = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)kvh * HD;
+  const uint16_t* vbase = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)kvh * HD + lane * DPL;
+  int kc = kb + lane;
+  if (kc > k1 - 1) kc = k1 - 1;
+  const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)kc * p.kv_seq_stride);
+#pragma unroll
+  for (int i = 0; i < KvBlock<S>::KV4; ++i) b.k[i] = ldcg_u4(kp + i);
+#pragma unroll
+  for (int j = 0; j < kAttnBlockKeys; ++j) {
+    int kj = kb + j;
+    if (kj > k1 - 1) kj = k1 - 1;
+    const uint16_t* vp = vbase + (size_t)kj * p.kv_seq_stride;
+    if (DPL == 2) {
+      b.v[j][0] = ldcg_u32(vp);
+    } else {
+      const uint2 t = __ldcg(reinterpret_cast<const uint2*>(vp));
+      b.v[j][0] = t.x;
+      b.v[j][DPL / 2 - 1] = t.y;
+    }
+  }
+}
+
+// Overwrite the row of position `pos` (if it falls in this block, clamped copies included) with the
+// K / V row staged in shared memory.
+template <class S>
+__device__ __forceinline__ void patch_new_row(KvBlock<S>& b, const unsigned char* smem, int kvh, int kb, int k1, int pos,
+                                              int lane) {
   using L = SmemLayout<S>;
-  constexpr int HD = S::HD, GQA = S::GQA;
-  constexpr int DPL = HD / 32;          // output dims per lane
-  constexpr int KV4 = HD / 8;           // uint4 per K row
+  constexpr int HD = S::HD, DPL = KvBlock<S>::DPL;
+  if (pos < kb || pos >= kb + kAttnBlockKeys || pos != k1 - 1) return;   // the new row is always the last key
+  const unsigned char* knew = smem + L::kOffActD + S::QDIM * 4 + (size_t)kvh * HD * 2;
+  const unsigned char* vnew = knew + (size_t)S::NKV * HD * 2 + lane * DPL * 2;
+  if (kb + lane >= pos) {
+#pragma unroll
+    for (int i = 0; i < KvBlock<S>::KV4; ++i) b.k[i] = reinterpret_cast<const uint4*>(knew)[i];
+  }
+#pragma unroll
+  for (int j = 0; j < kAttnBlockKeys; ++j) {
+    if (kb + j >= pos) {
+#pragma unroll
+      for (int d2 = 0; d2 < DPL / 2; ++d2) b.v[j][d2] = reinterpret_cast<const uint32_t*>(vnew)[d2];
+    }
+  }
+}
+
+// Partial record of (head, part): HD words of un-normalised output, then running max (log2 domain)
+// and sum; every 64-bit word is {fp32 bits, tag}.
+template <class S>
+__device__ __forceinline__ unsigned long long* part_record(const Params& p, int head, int part) {
+  return p.part_rec + ((size_t)head * kMaxSplits + part) * (S::HD + 2);
+}
+
+template <class S>
+__device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kvh,
+                                          int part, int bps, int P, bool staged_kv, unsigned tagw, KvBlock<S>& blk,
+                                          bool blk_loaded) {
+  using L = SmemLayout<S>;
+  constexpr int HD = S::HD, GQA = S::GQA, DPL = KvBlock<S>::DPL, KV4 = KvBlock<S>::KV4;
   static_assert(DPL == 2 || DPL == 4, "head_dim must be 64 or 128");
   const int layer = phase_layer(ph);
   const int T = p.pos + 1;
   const int k0 = part * bps * kAttnBlockKeys;
   int k1 = k0 + bps * kAttnBlockKeys;
   if (k1 > T) k1 = T;
-  const uint16_t* kbase = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)kvh * HD;
-  const uint16_t* vbase = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)kvh * HD + s.lane * DPL;
-  const unsigned char* knew = smem + L::kOffActD + S::QDIM * 4 + (size_t)kvh * HD * 2;
-  const unsigned char* vnew = knew + (size_t)S::NKV * HD * 2 + s.lane * DPL * 2;
   const float4* q4 = reinterpret_cast<const float4*>(smem + L::kOffActD) + (size_t)kvh * GQA * (HD / 4);
 
   float m[GQA], l[GQA], acc0[GQA], acc1[GQA], acc2[GQA], acc3[GQA];
@@ -107,38 +170,9 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
 
 #pragma unroll 1
   for (int kb = k0; kb < k1; kb += kAttnBlockKeys) {
-    const int key = kb + s.lane;
-    const bool valid = key < k1;
-    const int kc = valid ? key : (k1 - 1);
-    uint4 kreg[KV4];
-    if (staged_kv && kc == p.pos) {
-#pragma unroll
-      for (int i = 0; i < KV4; ++i) kreg[i] = reinterpret_cast<const uint4*>(knew)[i];
-    } else {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)kc * p.kv_seq_stride);
-#pragma unroll
-      for (int i = 0; i < KV4; ++i) kreg[i] = ldcg_u4(kp + i);
-    }
-    // V rows of the block, lane = output dims; rows past the end are clamped and carry probability 0.
-    uint32_t vreg[kAttnBlockKeys][DPL / 2];
-#pragma unroll
-    for (int j = 0; j < kAttnBlockKeys; ++j) {
-      int kj = kb + j;
-      if (kj > k1 - 1) kj = k1 - 1;
-      if (staged_kv && kj == p.pos) {
-#pragma unroll
-        for (int d2 = 0; d2 < DPL / 2; ++d2) vreg[j][d2] = reinterpret_cast<const uint32_t*>(vnew)[d2];
-      } else {
-        const uint16_t* vp = vbase + (size_t)kj * p.kv_seq_stride;
-        if (DPL == 2) {
-          vreg[j][0] = ldcg_u32(vp);
-        } else {
-          const uint2 t = __ldcg(reinterpret_cast<const uint2*>(vp));
-          vreg[j][0] = t.x;
-          vreg[j][DPL / 2 - 1] = t.y;
-        }
-      }
-    }
+    if (!(blk_loaded && kb == k0)) load_kv_block(blk, p, layer, kvh, kb, k1, s.lane);
+    if (staged_kv) patch_new_row(blk, smem, kvh, kb, k1, p.pos, s.lane);
+    const bool valid = kb + s.lane < k1;
 #pragma unroll 1
     for (int h = 0; h < GQA; ++h) {
       const float4* qh = q4 + h * (HD / 4);
@@ -146,7 +180,7 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
 #pragma unroll
       for (int i = 0; i < KV4; ++i) {
         const float4 qa = qh[2 * i], qb = qh[2 * i + 1];
-        const uint4 kk = kreg[i];
+        const uint4 kk = blk.k[i];
         s0 = fmaf(bf_lo(kk.x), qa.x, s0);
         s1 = fmaf(bf_hi(kk.x), qa.y, s1);
         s0 = fmaf(bf_lo(kk.y), qa.z, s0);
@@ -166,11 +200,11 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
 #pragma unroll
       for (int j = 0; j < kAttnBlockKeys; ++j) {
         const float pj = __shfl_sync(kFullMask, pr, j);
-        a0 = fmaf(pj, bf_lo(vreg[j][0]), a0);
-        a1 = fmaf(pj, bf_hi(vreg[j][0]), a1);
+        a0 = fmaf(pj, bf_lo(blk.v[j][0]), a0);
+        a1 = fmaf(pj, bf_hi(blk.v[j][0]), a1);
         if (DPL == 4) {
-          a2 = fmaf(pj, bf_lo(vreg[j][DPL / 2 - 1]), a2);
-          a3 = fmaf(pj, bf_hi(vreg[j][DPL / 2 - 1]), a3);
+          a2 = fmaf(pj, bf_lo(blk.v[j][DPL / 2 - 1]), a2);
+          a3 = fmaf(pj, bf_hi(blk.v[j][DPL / 2 - 1]), a3);
         }
       }
       acc0[0] = a0; acc1[0] = a1; acc2[0] = a2; acc3[0] = a3;
@@ -197,72 +231,75 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, const u
     return;
   }
 
-  // Store the un-normalised partial, then take a ticket; the last arrival merges.
+  // ---- publish the partial as a self-validating record
+  const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
 #pragma unroll
   for (int h = 0; h < GQA; ++h) {
-    const int head = kvh * GQA + h;
-    float* po = p.part_o + ((size_t)head * kMaxSplits + part) * HD + s.lane * DPL;
-    *reinterpret_cast<float2*>(po) = make_float2(acc0[h], acc1[h]);
-    if (DPL == 4) *reinterpret_cast<float2*>(po + 2) = make_float2(acc2[h], acc3[h]);
-    if (s.lane == 0) *reinterpret_cast<float2*>(p.part_ml + ((size_t)head * kMaxSplits + part) * 2) = make_float2(m[h], l[h]);
+    unsigned long long* rec = part_record<S>(p, kvh * GQA + h, part);
+    uint4* dst = reinterpret_cast<uint4*>(rec + s.lane * DPL);
+    dst[0] = make_uint4(__float_as_uint(acc0[h]), rtag, __float_as_uint(acc1[h]), rtag);
+    if (DPL == 4) dst[1] = make_uint4(__float_as_uint(acc2[h]), rtag, __float_as_uint(acc3[h]), rtag);
+    if (s.lane == 0)
+      *reinterpret_cast<uint4*>(rec + HD) = make_uint4(__float_as_uint(m[h]), rtag, __float_as_uint(l[h]), rtag);
   }
-  // Release the partial (all lanes' stores are ordered before lane 0's atomic by the __syncwarp),
-  // take a ticket; only the last arrival goes on, and its atomic acquires the other partials.
-  __syncwarp();
-  unsigned* ticket_word = p.tickets + (layer & 1) * 32 + kvh;
-  unsigned ticket = 0;
-  if (s.lane == 0) ticket = atom_add_acq_rel_gpu(ticket_word, 1u);
-  ticket = __shfl_sync(kFullMask, ticket, 0);
-  if (ticket != (unsigned)(P - 1)) return;
-  if (s.lane == 0) atomicExch(ticket_word, 0u);   // every partial of this step has arrived
 
-  // Merge: the warp's lanes are divided among the heads of the group, each lane owns DPM output dims
-  // of one head and walks the partials with a running maximum (one pass, loads four partials ahead).
-  constexpr int LPH = 32 / GQA;                // lanes per head
-  constexpr int DPM = HD / LPH;                // dims per lane (multiple of 4)
-  static_assert(DPM % 4 == 0, "merge lanes read float4");
-  const int head = kvh * GQA + s.lane / LPH;
-  const int d0 = (s.lane % LPH) * DPM;
-  const float* mlb = p.part_ml + (size_t)head * kMaxSplits * 2;
-  const float* pob = p.part_o + (size_t)head * kMaxSplits * HD + d0;
-  float M = -INFINITY, den = 0.f, num[DPM];
-#pragma unroll
-  for (int d = 0; d < DPM; ++d) num[d] = 0.f;
+  // ---- merge: unit `part` merges the heads h = part, part + nm, ... of its group (nm = min(P, GQA))
+  const int nm = P < GQA ? P : GQA;
+  if (part >= nm) return;
 #pragma unroll 1
-  for (int q0 = 0; q0 < P; q0 += 4) {
-    float2 ml[4];
-    float4 t[4][DPM / 4];
+  for (int h = part; h < GQA; h += nm) {
+    const int head = kvh * GQA + h;
+    float M = -INFINITY, den = 0.f, num[DPL];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int q = (q0 + j) < P ? (q0 + j) : (P - 1);
-      ml[j] = ldcg_f2(mlb + 2 * q);
+    for (int d = 0; d < DPL; ++d) num[d] = 0.f;
+#pragma unroll 1
+    for (int q0 = 0; q0 < P; q0 += 4) {
+      uint4 ta[4][DPL / 2], tm[4];
+      const long long t0 = clock64();
+      for (unsigned it = 0;; ++it) {
+        bool ok = true;
 #pragma unroll
-      for (int d4 = 0; d4 < DPM / 4; ++d4) t[j][d4] = __ldcg(reinterpret_cast<const float4*>(pob + (size_t)q * HD) + d4);
-    }
+        for (int j = 0; j < 4; ++j) {
+          const int q = (q0 + j) < P ? (q0 + j) : (P - 1);
+          const unsigned long long* rec = part_record<S>(p, head, q);
+          tm[j] = ldcg_u4(rec + HD);
+          ok = ok && tm[j].y == rtag && tm[j].w == rtag;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (q0 + j < P) {
-        const float M_new = fmaxf(M, ml[j].x);
-        const float corr = exp2f(M - M_new), wq = exp2f(ml[j].x - M_new);
-        den = den * corr + wq * ml[j].y;
-#pragma unroll
-        for (int d4 = 0; d4 < DPM / 4; ++d4) {
-          num[4 * d4 + 0] = fmaf(wq, t[j][d4].x, num[4 * d4 + 0] * corr);
-          num[4 * d4 + 1] = fmaf(wq, t[j][d4].y, num[4 * d4 + 1] * corr);
-          num[4 * d4 + 2] = fmaf(wq, t[j][d4].z, num[4 * d4 + 2] * corr);
-          num[4 * d4 + 3] = fmaf(wq, t[j][d4].w, num[4 * d4 + 3] * corr);
+          for (int d2 = 0; d2 < DPL / 2; ++d2) {
+            ta[j][d2] = ldcg_u4(rec + s.lane * DPL + 2 * d2);
+            ok = ok && ta[j][d2].y == rtag && ta[j][d2].w == rtag;
+          }
         }
-        M = M_new;
+        if (__all_sync(kFullMask, ok)) break;
+        if ((it & 15u) == 15u && poll_give_up(p, t0, ok, tm[0].y, rtag, s.w, ph, s.lane)) {
+          s.aborted = true;
+          return;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (q0 + j < P) {
+          const float mq = __uint_as_float(tm[j].x), lq = __uint_as_float(tm[j].z);
+          const float M_new = fmaxf(M, mq);
+          const float corr = exp2f(M - M_new), wq = exp2f(mq - M_new);
+          den = den * corr + wq * lq;
+#pragma unroll
+          for (int d2 = 0; d2 < DPL / 2; ++d2) {
+            num[2 * d2] = fmaf(wq, __uint_as_float(ta[j][d2].x), num[2 * d2] * corr);
+            num[2 * d2 + 1] = fmaf(wq, __uint_as_float(ta[j][d2].z), num[2 * d2 + 1] * corr);
+          }
+          M = M_new;
+        }
       }
     }
-  }
-  const float inv = 1.0f / den;
-  const int e = head * HD + d0;
+    const float inv = 1.0f / den;
+    const int e = head * HD + s.lane * DPL;
 #pragma unroll
-  for (int d = 0; d < DPM; d += 2) {
-    const uint32_t w = pack_bf16x2(num[d] * inv, num[d + 1] * inv);
-    *reinterpret_cast<uint32_t*>(p.attn_out + e + d) = w;
-    if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e + d) = make_uint2((w & 0xffffu) | tagw, (w >> 16) | tagw);
+    for (int d = 0; d < DPL; d += 2) {
+      const uint32_t w = pack_bf16x2(num[d] * inv, num[d + 1] * inv);
+      *reinterpret_cast<uint32_t*>(p.attn_out + e + d) = w;
+      if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e + d) = make_uint2((w & 0xffffu) | tagw, (w >> 16) | tagw);
+    }
   }
 }
 
@@ -275,20 +312,28 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   if ((int)blockIdx.x >= n_units) return;          // no unit lands on this CTA: nothing to stage
   const bool tagged = p.sync && (ph > p.phase_begin || p.wait_first);
   const long long tq0 = clock64();
-  if (!stage_attn_part<S>(p, smem, tagged, phase_tag(p, ph - 1), s.w, s.lane, ph)) s.aborted = true;
-  raise_part_flag(s.ctl, s.w, s.lane, s.aborted ? kAbortFlag : (unsigned)(ph + 1));
-  const long long tq1 = clock64();
   const int first = s.w * (int)gridDim.x + (int)blockIdx.x;
-  if (first < n_units && !s.aborted) {
-    if (!wait_parts(p, s.ctl, s.w, s.lane, ph)) s.aborted = true;
-    const long long tq2 = clock64();
+  const bool has_unit = first < n_units && !s.aborted;
+  KvBlock<S> blk;
+  if (has_unit) {   // old keys do not depend on this step: fetch the first block before waiting for q
+    const int part = first % P, k0 = part * bps * kAttnBlockKeys;
+    int k1 = k0 + bps * kAttnBlockKeys;
+    if (k1 > p.pos + 1) k1 = p.pos + 1;
+    load_kv_block(blk, p, phase_layer(ph), first / P, k0, k1, s.lane);
+  }
+  if (!s.aborted && !stage_attn_part<S>(p, smem, tagged, phase_tag(p, ph - 1), s.w, s.lane, ph)) flag_abort(s, smem);
+  cta_sync(s, smem);
+  if (s.cta_abort) return;
+  const long long tq1 = clock64();
+  if (has_unit) {
     const unsigned tagw = phase_tag(p, ph) << 16;
-    for (int u = first; u < n_units && !s.aborted; u += s.nwt) attn_unit(s, p, smem, ph, u / P, u % P, bps, P, tagged, tagw);
-    if (s.w == 0) {
-      trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
-      trace_put(p, ph, 4, (unsigned long long)(tq2 - tq1), s.lane);
-      trace_put(p, ph, 6, (unsigned long long)(clock64() - tq2), s.lane);
-    }
+    for (int u = first; u < n_units && !s.aborted; u += s.nwt)
+      attn_unit(s, p, smem, ph, u / P, u % P, bps, P, tagged, tagw, blk, u == first);
+    if (s.aborted) flag_abort(s, smem);
+  }
+  if (s.w == 0) {
+    trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
+    trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
   }
 }
 

@@ -30,17 +30,17 @@ namespace qmk {
 #define QMK_WORKERS 8
 #endif
 #ifndef QMK_SLOTS
-#define QMK_SLOTS 6
+#define QMK_SLOTS 3
 #endif
 constexpr int kWorkers = QMK_WORKERS;  // warps per CTA (all of them stream weights)
-constexpr int kSlots = QMK_SLOTS;      // ring slots per warp
+constexpr int kSlots = QMK_SLOTS;      // ring slots (8 KiB tiles) per warp
 constexpr int kThreads = kWorkers * 32;
 constexpr unsigned kAbortFlag = 0xffffffffu;
-static_assert(kWorkers <= 8, "the staging flags are polled by lanes 0..7");
+
 
 template <class S>
 struct SmemLayout {
-  static constexpr int kRingBytes = kWorkers * kSlots * kChunkBytes;
+  static constexpr int kRingBytes = kWorkers * kSlots * 2 * kChunkBytes;
   static constexpr int kActSmall = S::H * 2;                                  // bf16 activation vector
   static constexpr int kActBigA = S::I * 2;                                   // silu_out (bf16)
   static constexpr int kActBigB = S::QDIM * 4 + 2 * S::NKV * S::HD * 2;       // q fp32 + new K/V rows bf16
@@ -55,10 +55,9 @@ struct SmemLayout {
   static constexpr int kTotal = kOffRope + S::HD * 8;
 };
 // control block, 32-bit words from kOffCtl:
-//   [0..7]   part_done[w]: last phase (+1) whose staging part warp w has written; kAbortFlag = abort
-//   [8]      lm_arrive     [10..11] CTA arg-max key (u64)
+//   [0] abort word (non-zero: a warp of this CTA gave up)   [8] lm_arrive   [10..11] CTA arg-max key (u64)
 //   [16..23] sum-of-squares partials, buffer A     [24..31] buffer B
-constexpr int kCtlLmArrive = 8, kCtlKey = 10, kCtlSumSq = 16;
+constexpr int kCtlAbort = 0, kCtlLmArrive = 8, kCtlKey = 10, kCtlSumSq = 16;
 
 __device__ __noinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
                                           unsigned expected, int detail) {
@@ -80,14 +79,25 @@ __device__ __forceinline__ void trace_put(const Params& p, int ph, int slot, uns
   if (p.trace != nullptr && lane == 0) p.trace[((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8 + slot] = v;
 }
 
-// Tag of (step, phase): 1..65535, consecutive phases get consecutive tags, so a stale word (written
-// at most one step earlier) can never carry the tag a reader waits for.  0 = never written.
+// Tag of (launch, phase): 1..65535, consecutive phases and launches get consecutive tags, so a stale
+// word (every tagged word is rewritten by every full step) cannot carry the tag a reader waits for.
+// 0 = never written.
 __device__ __forceinline__ unsigned phase_tag(const Params& p, int ph) {
-  return (p.epoch * (unsigned)num_phases(p.num_layers) + (unsigned)ph) % 65535u + 1u;
+  return (p.launch_seq * (unsigned)num_phases(p.num_layers) + (unsigned)ph) % 65535u + 1u;
 }
 
 // ------------------------------------------------------------------------------------------
-// Worker state: ring + issue cursor.  All fields are warp-uniform except `res`.
+// Worker state: tile ring + issue cursor.  All fields are warp-uniform except `res`.
+//
+// The weight stream of a warp is a sequence of TILES.  A tile is what one tensor-pipe product
+// consumes: two 4-KiB chunks (or one, for an odd last row) that meet the same activations.  It
+// occupies one 8-KiB ring slot with one mbarrier and is fetched by one 8-KiB bulk copy when its two
+// chunks are adjacent in memory, else by two 4-KiB copies completing on the same mbarrier:
+//   QKV      rows (2u, 2u+1) of one RoPE pair                      one copy
+//   O-proj   rows (r, r+1)                                          one copy
+//   LM head  rows (r, r+1)                                          one copy
+//   up/gate  (up row u, gate row u)                                 two copies
+//   down     (row a, k-slice j), (row a+1, k-slice j), j = 0..I/2048-1 per row pair   two copies
 // ------------------------------------------------------------------------------------------
 template <class S>
 struct Worker {
@@ -97,16 +107,25 @@ struct Worker {
   uint32_t ctl;        // shared address of the control words
   unsigned n_issued, n_acquired;
   unsigned i_slot;         // slot the next issue goes into
-  unsigned c_slot, c_par;  // slot and mbarrier parity of the next chunk to consume
-  int i_ph, i_kind, i_layer, i_c, i_cend;   // issue cursor: phase, its kind / layer, next chunk, end chunk
-  // This worker's chunk range per streaming kind: identical for every layer, so the 32-bit
+  unsigned c_slot, c_par;  // slot and mbarrier parity of the next tile to consume
+  // issue cursor
+  int i_ph, i_kind;        // phase being issued and its kind
+  int i_left;              // tiles left in that phase
+  int i_sub;               // down-proj: k-slice of the next tile
+  int i_rows_left;         // rows (O-proj / LM / down) still to be covered, to spot the odd last row
+  const unsigned char* i_p0;   // next source (first chunk)
+  const unsigned char* i_p1;   // up/gate: gate row
+  // this worker's item ranges per streaming kind: identical for every layer, so the 32-bit
   // divisions of the even split are done once per launch.
-  int q0, q1, o0, o1, u0, u1, d0, d1, l0, l1;
-  float res;               // residual stream value of row (first row of this warp + lane), bf16-exact
+  int q0, q1;              // QKV units (RoPE pairs)
+  int r0, r1;              // rows of the residual phases (O-proj and down-proj share the split)
+  int u0, u1;              // SwiGLU units
+  int l0, l1;              // LM head rows
+  float res;               // residual stream value of row (r0 + lane), bf16-exact
   bool res_valid;
-  bool aborted;
+  bool aborted;            // this warp gave up (bounded wait expired)
+  bool cta_abort;          // the whole CTA leaves the phase loop
   uint64_t policy;
-  WeightBases wb;
 };
 
 __device__ __forceinline__ void split_range_u32(unsigned units, unsigned parts, unsigned g, int& lo, int& hi) {
@@ -116,71 +135,110 @@ __device__ __forceinline__ void split_range_u32(unsigned units, unsigned parts, 
 
 template <class S>
 __device__ __forceinline__ void init_ranges(Worker<S>& s, const Params& p) {
-  int a, b;
-  split_range_u32(S::QKV_ROWS / 2, s.nwt, s.g, a, b); s.q0 = 2 * a; s.q1 = 2 * b;
-  split_range_u32(S::H, s.nwt, s.g, a, b); s.o0 = a * (S::QDIM / kChunkElems); s.o1 = b * (S::QDIM / kChunkElems);
-  split_range_u32(S::I, s.nwt, s.g, a, b); s.u0 = 2 * a; s.u1 = 2 * b;
-  split_range_u32(S::H, s.nwt, s.g, a, b); s.d0 = a * (S::I / kChunkElems); s.d1 = b * (S::I / kChunkElems);
-  split_range_u32((unsigned)p.vocab, s.nwt, s.g, a, b); s.l0 = a; s.l1 = b;
+  split_range_u32(S::QKV_ROWS / 2, s.nwt, s.g, s.q0, s.q1);
+  split_range_u32(S::H, s.nwt, s.g, s.r0, s.r1);
+  split_range_u32(S::I, s.nwt, s.g, s.u0, s.u1);
+  split_range_u32((unsigned)p.vocab, s.nwt, s.g, s.l0, s.l1);
 }
 
+// Number of tiles of this worker in a phase of `kind`.
 template <class S>
-__device__ __forceinline__ void kind_range(const Worker<S>& s, int kind, int& c0, int& c1) {
-  switch (kind) {
-    case kQkv: c0 = s.q0; c1 = s.q1; break;
-    case kOproj: c0 = s.o0; c1 = s.o1; break;
-    case kUpGate: c0 = s.u0; c1 = s.u1; break;
-    case kDown: c0 = s.d0; c1 = s.d1; break;
-    case kLmHead: c0 = s.l0; c1 = s.l1; break;
-    default: c0 = c1 = 0; break;
-  }
-}
-
-// Down-projection rows are consumed two at a time, k-slice by k-slice, so that both chunks of a pair
-// meet the same activations: order (row a, slice 0), (row b, slice 0), (row a, slice 1), ...; an odd
-// last row goes alone.  Maps the t-th chunk of this worker's down-proj stream to row * slices + slice.
-template <class S>
-__device__ __forceinline__ int down_canonical(int t, int d0, int d1) {
+__device__ __forceinline__ int kind_tiles(const Worker<S>& s, int kind) {
   constexpr int kSlices = S::I / kChunkElems;
-  const int r0 = d0 / kSlices, nrows = (d1 - d0) / kSlices;
-  const int pair = t / (2 * kSlices), tt = t % (2 * kSlices);
-  int row = 2 * pair, slice;
-  if (row + 1 < nrows) {
-    slice = tt >> 1;
-    row += tt & 1;
-  } else {
-    slice = tt;
+  switch (kind) {
+    case kQkv: return s.q1 - s.q0;
+    case kOproj: return (s.r1 - s.r0 + 1) >> 1;
+    case kUpGate: return s.u1 - s.u0;
+    case kDown: return ((s.r1 - s.r0 + 1) >> 1) * kSlices;
+    case kLmHead: return (s.l1 - s.l0 + 1) >> 1;
+    default: return 0;
   }
-  return (r0 + row) * kSlices + slice;
 }
 
-// Position the issue cursor on the first phase >= i_ph in which this worker streams weights.
+// Position the issue cursor on the first phase >= i_ph in which this worker streams weights and
+// set the source pointers of its first tile.
 template <class S>
 __device__ __forceinline__ void cursor_seek(Worker<S>& s, const Params& p) {
   while (s.i_ph < p.phase_end) {
     const int layer = s.i_ph / kPhasesPerLayer;
-    s.i_kind = layer >= p.num_layers ? (int)kLmHead : s.i_ph - layer * kPhasesPerLayer;
-    s.i_layer = layer;
-    kind_range(s, s.i_kind, s.i_c, s.i_cend);
-    if (s.i_c < s.i_cend) return;
+    const int kind = layer >= p.num_layers ? (int)kLmHead : s.i_ph - layer * kPhasesPerLayer;
+    const int n = kind_tiles(s, kind);
+    if (n > 0) {
+      s.i_kind = kind;
+      s.i_left = n;
+      s.i_sub = 0;
+      const size_t row_b = (size_t)kChunkBytes;
+      switch (kind) {
+        case kQkv:
+          s.i_p0 = reinterpret_cast<const unsigned char*>(p.qkv) + ((size_t)layer * S::QKV_ROWS + 2 * s.q0) * row_b;
+          break;
+        case kOproj:
+          s.i_p0 = reinterpret_cast<const unsigned char*>(p.o_proj) + ((size_t)layer * S::H + s.r0) * row_b;
+          s.i_rows_left = s.r1 - s.r0;
+          break;
+        case kUpGate:
+          s.i_p0 = reinterpret_cast<const unsigned char*>(p.up) + ((size_t)layer * S::I + s.u0) * row_b;
+          s.i_p1 = reinterpret_cast<const unsigned char*>(p.gate) + ((size_t)layer * S::I + s.u0) * row_b;
+          break;
+        case kDown:
+          s.i_p0 = reinterpret_cast<const unsigned char*>(p.down) + ((size_t)layer * S::H + s.r0) * (size_t)S::I * 2;
+          s.i_rows_left = s.r1 - s.r0;
+          break;
+        default:
+          s.i_p0 = reinterpret_cast<const unsigned char*>(p.lm_head) + (size_t)s.l0 * row_b;
+          s.i_rows_left = s.l1 - s.l0;
+          break;
+      }
+      return;
+    }
     ++s.i_ph;
   }
 }
 
-// Issue the next chunk of the stream into the oldest free slot, if any chunk is left.
+// Issue the next tile of the stream into the oldest free slot, if any tile is left.
 template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
   if (s.aborted || s.i_ph >= p.phase_end) return;
+  constexpr int kSlices = S::I / kChunkElems;
+  const unsigned char* a = s.i_p0;
+  const unsigned char* b = nullptr;
+  uint32_t bytes_a = 2 * kChunkBytes;
+  switch (s.i_kind) {
+    case kQkv:
+      s.i_p0 += 2 * kChunkBytes;
+      break;
+    case kUpGate:
+      bytes_a = kChunkBytes;
+      b = s.i_p1;
+      s.i_p0 += kChunkBytes;
+      s.i_p1 += kChunkBytes;
+      break;
+    case kDown:
+      bytes_a = kChunkBytes;
+      a += s.i_sub * kChunkBytes;
+      if (s.i_rows_left > 1) b = a + (size_t)S::I * 2;
+      if (++s.i_sub == kSlices) {
+        s.i_sub = 0;
+        s.i_p0 += 2 * (size_t)S::I * 2;
+        s.i_rows_left -= 2;
+      }
+      break;
+    default:   // O-proj, LM head
+      if (s.i_rows_left < 2) bytes_a = kChunkBytes;
+      s.i_rows_left -= 2;
+      s.i_p0 += 2 * kChunkBytes;
+      break;
+  }
   if (s.lane == 0) {
-    const int c = s.i_kind == kDown ? down_canonical<S>(s.i_c - s.d0, s.d0, s.d1) : s.i_c;
-    const uint16_t* src = chunk_ptr<S>(s.wb, s.i_kind, s.i_layer, c);
     const uint32_t bar = s.bars + s.i_slot * 8;
-    mbar_expect_tx(bar, kChunkBytes);
-    bulk_g2s(s.ring + s.i_slot * kChunkBytes, src, kChunkBytes, bar, s.policy);
+    const uint32_t dst = s.ring + s.i_slot * (2 * kChunkBytes);
+    mbar_expect_tx(bar, bytes_a + (b != nullptr ? (uint32_t)kChunkBytes : 0u));
+    bulk_g2s(dst, a, bytes_a, bar, s.policy);
+    if (b != nullptr) bulk_g2s(dst + kChunkBytes, b, kChunkBytes, bar, s.policy);
   }
   ++s.n_issued;
   s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
-  if (++s.i_c == s.i_cend) {
+  if (--s.i_left == 0) {
     ++s.i_ph;
     cursor_seek(s, p);
   }
@@ -200,10 +258,10 @@ __device__ __noinline__ bool wait_slot_slow(const Params& p, uint32_t bar, uint3
   }
 }
 
-// Next chunk in consumption order: waits for it, advances the consume cursor and returns the slot's
-// shared address.  The slot stays owned by the warp until release_chunks().
+// Next tile in consumption order: waits for it, advances the consume cursor and returns the slot's
+// shared address.  The slot stays owned by the warp until release_tile().
 template <class S>
-__device__ __forceinline__ uint32_t acquire_chunk(Worker<S>& s, const Params& p, int phase) {
+__device__ __forceinline__ uint32_t acquire_tile(Worker<S>& s, const Params& p, int phase) {
   const unsigned slot = s.c_slot;
   if (!s.aborted) {
     const uint32_t bar = s.bars + slot * 8;
@@ -216,13 +274,13 @@ __device__ __forceinline__ uint32_t acquire_chunk(Worker<S>& s, const Params& p,
       s.c_par ^= 1u;
     }
   }
-  return s.ring + slot * kChunkBytes;
+  return s.ring + slot * (2 * kChunkBytes);
 }
-// All lanes are done reading the `n` oldest acquired slots: refill them with the next chunks.
+// All lanes are done reading the oldest acquired slot: refill it with the next tile.
 template <class S>
-__device__ __forceinline__ void release_chunks(Worker<S>& s, const Params& p, int n) {
+__device__ __forceinline__ void release_tile(Worker<S>& s, const Params& p) {
   __syncwarp();
-  for (int i = 0; i < n; ++i) issue_one(s, p);
+  issue_one(s, p);
 }
 
 // Which small activation buffer (A or B) a phase uses: they alternate along the phase sequence.
@@ -256,17 +314,6 @@ __device__ __forceinline__ void load_xfrag(XFrag& xf, const unsigned char* act_b
   const uint32_t* v = reinterpret_cast<const uint32_t*>(act_bf16);
 #pragma unroll
   for (int i = 0; i < 32; ++i) xf.b[i] = v[32 * i + lane];
-}
-
-// The same, applying RMSNorm on the way: y = bf16(g * bf16(x * rstd))  (_rms_norm, operations.py:126-131).
-__device__ __forceinline__ void load_xfrag_normed(XFrag& xf, const unsigned char* act_bf16, const uint32_t (&gains)[32],
-                                                  float rstd, int lane) {
-  const uint32_t* v = reinterpret_cast<const uint32_t*>(act_bf16);
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const uint32_t x = v[32 * i + lane], g = gains[i];
-    xf.b[i] = pack_bf16x2(bf_lo(g) * bf16_round(bf_lo(x) * rstd), bf_hi(g) * bf16_round(bf_hi(x) * rstd));
-  }
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&a)[4], uint32_t saddr) {

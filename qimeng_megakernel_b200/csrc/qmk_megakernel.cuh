@@ -12,31 +12,26 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.w = w;
   s.nwt = (int)gridDim.x * kWorkers;
   s.g = (int)blockIdx.x * kWorkers + w;
-  s.ring = smem_u32(smem + L::kOffRing + w * kSlots * kChunkBytes);
+  s.ring = smem_u32(smem + L::kOffRing + w * kSlots * 2 * kChunkBytes);
   s.bars = smem_u32(smem + L::kOffBars + w * kSlots * 8);
   s.ctl = smem_u32(smem + L::kOffCtl);
   s.n_issued = s.n_acquired = 0;
   s.i_slot = s.c_slot = s.c_par = 0;
   s.i_ph = p.phase_begin;
-  s.i_kind = s.i_layer = s.i_c = s.i_cend = 0;
+  s.i_kind = s.i_left = s.i_sub = s.i_rows_left = 0;
+  s.i_p0 = s.i_p1 = nullptr;
+  s.cta_abort = false;
   s.res = 0.f;
   s.res_valid = false;
   s.aborted = false;
   s.policy = l2_policy_evict_first();
-  s.wb.qkv = p.qkv;
-  s.wb.o_proj = p.o_proj;
-  s.wb.up = p.up;
-  s.wb.gate = p.gate;
-  s.wb.down = p.down;
-  s.wb.lm_head = p.lm_head;
   init_ranges(s, p);
   cursor_seek(s, p);
 #pragma unroll 1
   for (int i = 0; i < kSlots; ++i) issue_one(s, p);
 
 #pragma unroll 1
-  for (int ph = p.phase_begin; ph < p.phase_end && !s.aborted; ++ph) {
-    const long long tph = clock64();
+  for (int ph = p.phase_begin; ph < p.phase_end && !s.cta_abort; ++ph) {
     if (w == 0) trace_put(p, ph, 2, globaltimer_ns(), lane);
     const int kind = phase_kind(ph, p.num_layers);
     if (kind == kAttn) phase_attn(s, p, smem, ph);
@@ -45,10 +40,8 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
       trace_put(p, ph, 5, globaltimer_ns(), lane);
     }
   }
-  if (s.aborted) {
-    // Tell the other warps of the CTA, then leave no bulk copy in flight into this CTA's shared
-    // memory: wait (bounded) for each outstanding one.
-    raise_part_flag(s.ctl, w, lane, kAbortFlag);
+  if (s.n_acquired != s.n_issued) {
+    // (only after an abort)  Leave no bulk copy in flight into this CTA's shared memory: wait (bounded) for each one.
     for (unsigned n = s.n_acquired; n < s.n_issued; ++n) {
       const uint32_t bar = s.bars + (n % kSlots) * 8;
       const long long t0 = clock64();

@@ -41,15 +41,14 @@ struct Params {
   long long kv_layer_stride;     // elements between layers (= B*S*NKV*HD)
   long long kv_seq_stride;       // elements between positions (= NKV*HD)
   // ---- library-owned scratch ----
-  float* part_o;                 // [NH, kMaxSplits, HD] un-normalised split-KV partial outputs
-  float* part_ml;                // [NH, kMaxSplits, 2]  (running max in log2 domain, sum)
+  unsigned long long* part_rec;  // [NH, kMaxSplits, HD + 2] split-KV partial records, words {fp32 bits, tag}
   // tagged activation words {low 16: bf16 value, high 16: tag of (step, phase)}: the cross-SM hand-off
   uint32_t* t_hid_o;             // [H]   residual stream after the O-projection
   uint32_t* t_hid_d;             // [H]   residual stream after the down-projection
   uint32_t* t_q;                 // [QDIM + 2*NKV*HD]  q_post_rope, then this step's K row and V row
   uint32_t* t_attn;              // [QDIM] attention output
   uint32_t* t_silu;              // [I]   SwiGLU output
-  unsigned* tickets;             // [2][32] split-KV arrival tickets by layer parity; lm-head ticket at [64]
+  unsigned* tickets;             // lm-head arrival ticket at [64]
   unsigned long long* argmax_key;  // packed (ordered logit bits << 32) | ~index
   unsigned* status;              // [8] status words
   unsigned long long* trace;     // optional [CTAs, num_phases, 8] globaltimer stamps (ns); null = off
@@ -60,7 +59,7 @@ struct Params {
   int phase_begin, phase_end;    // phases executed by this launch
   int sync;                      // 1: phases hand off through tagged words; 0: single phase, stream-ordered
   int wait_first;                // 1: also wait for the dependency of phase_begin (debug / failure test)
-  unsigned epoch;                // completed synchronised steps since the counters were last zeroed
+  unsigned launch_seq;           // number of this launch (per handle): makes every launch's tags distinct
   float eps;
   float scale_log2e;             // attn_scale * log2(e)
   long long timeout_cycles;      // bounded-wait budget

@@ -1,7 +1,7 @@
 // Worker-side phase bodies of the decode megakernel.  Included by qmk_kernel.cuh.
 //
 // All weight-streaming phases (QKV, O-proj, up/gate, down, LM head) share ONE instance of the hot
-// loop (acquire chunks -> tensor-pipe dot products -> release) and differ only in their epilogue;
+// loop (acquire tile -> tensor-pipe product -> release) and differ only in their epilogue;
 // keeping a single copy keeps the persistent kernel's code footprint small.
 #pragma once
 
@@ -74,10 +74,9 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
 }
 
 // ---- the streaming phase -----------------------------------------------------------------------
-// kind:  QKV / up-gate: an item is two chunks (one output unit) sharing the activations;
-//        O-proj / LM head: an item is one row = one chunk, two rows are computed per tensor-pipe tile;
-//        down-proj: an item is one row = I/2048 chunks; rows go in pairs, k-slice by k-slice (the
-//        order down_canonical() gives the weight stream), each slice against its own activations.
+// An item is what one lane of the epilogue owns: a QKV RoPE pair or SwiGLU unit (one tile each), or a
+// row of O-proj / LM head (two rows per tile) or of down-proj (two rows per I/2048 tiles, one tile
+// per k-slice, each slice against its own 2048 activations).
 // Residual phases (fused_oproj_gemv_residual, operations.py:251-262; fused_mlp_down_residual, 285-295):
 // hidden[r] = bf16(hidden[r] + bf16(W[r,:] . x)).  One warp owns a whole down-proj row, so its K
 // reduction has a fixed order (the reference adds four split-K partials with bf16 CAS in arrival
@@ -99,56 +98,58 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   float* sumsq = reinterpret_cast<float*>(smem + L::kOffCtl) + kCtlSumSq + sbuf * 8;
   const long long tq0 = clock64();
 
-  // RMSNorm gains do not depend on the step: fetch them before polling for the activations.
-  uint32_t gains[32];
-  if (normed) {
-    const uint16_t* gsrc = kind == kQkv ? p.attn_norm + (size_t)layer * S::H
-                                        : (kind == kUpGate ? p.mlp_norm + (size_t)layer * S::H : p.lm_norm);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) gains[i] = __ldg(reinterpret_cast<const uint32_t*>(gsrc) + 32 * i + s.lane);
-  }
-
-  // ---- stage this warp's eighth of the phase input
-  {
-    bool ok;
-    float ss = 0.f;
-    if (kind == kDown) {
-      ok = stage_part_bf16<S::I>(p, p.t_silu, p.silu_out, tagged, tag_in, act, s.w, s.lane, ph, ss);
-    } else {
-      const uint32_t* tsrc = kind == kOproj ? p.t_attn : (kind == kUpGate ? p.t_hid_o : p.t_hid_d);
-      const uint16_t* psrc = kind == kOproj ? p.attn_out
-                                            : (kind == kQkv || (kind == kLmHead && p.num_layers == 0)
-                                                   ? residual_src<S>(p, layer) : p.hidden);
-      ok = stage_part_bf16<S::H>(p, tsrc, psrc, tagged, tag_in, act, s.w, s.lane, ph, ss);
+  // ---- stage this warp's eighth of the phase input (see qmk_staging.cuh)
+  if (kind == kDown) {
+    Part<S::I> part;
+    if (!s.aborted) {
+      if (fetch_part<S::I>(p, p.t_silu, p.silu_out, tagged, tag_in, s.w, s.lane, ph, part)) store_part(part, act, s.w, s.lane);
+      else flag_abort(s, smem);
     }
-    if (!ok) s.aborted = true;
-    if (normed && s.lane == 0) sumsq[s.w] = ss;
-    raise_part_flag(s.ctl, s.w, s.lane, s.aborted ? kAbortFlag : (unsigned)(ph + 1));
-  }
-  const long long tq1 = clock64();
-
-  int c0, c1;
-  kind_range(s, kind, c0, c1);
-  const bool unit_pairs = kind == kQkv || kind == kUpGate;
-  const int nsl = kind == kDown ? kSlices : 1;
-  const int cpi = unit_pairs ? 2 : nsl;          // chunks per item
-  const int i0 = c0 / cpi, i1 = c1 / cpi;
-  unsigned long long best = 0ull;
-  long long tq2 = tq1;
-  long long cyc_acq = 0, cyc_mma = 0, cyc_rel = 0, cyc_red = 0, cyc_xf = 0;
-  if (i0 < i1 && !s.aborted) {
-    if (!wait_parts(p, s.ctl, s.w, s.lane, ph)) s.aborted = true;
-    tq2 = clock64();
-    XFrag xf;
+    cta_sync(s, smem);
+  } else {
+    Part<S::H> part;
+    uint2 gains[Part<S::H>::NPL];
+    if (normed) {   // the gains do not depend on the step: fetch them before polling for the activations
+      const uint16_t* gsrc = kind == kQkv ? p.attn_norm + (size_t)layer * S::H
+                                          : (kind == kUpGate ? p.mlp_norm + (size_t)layer * S::H : p.lm_norm);
+      const uint2* g2 = reinterpret_cast<const uint2*>(gsrc + s.w * Part<S::H>::kElems);
+#pragma unroll
+      for (int j = 0; j < Part<S::H>::NPL; ++j) gains[j] = __ldg(g2 + j * 32 + s.lane);
+    }
+    const uint32_t* tsrc = kind == kOproj ? p.t_attn : (kind == kUpGate ? p.t_hid_o : p.t_hid_d);
+    const uint16_t* psrc = kind == kOproj ? p.attn_out
+                                          : (kind == kQkv || (kind == kLmHead && p.num_layers == 0)
+                                                 ? residual_src<S>(p, layer) : p.hidden);
+    if (!s.aborted && !fetch_part<S::H>(p, tsrc, psrc, tagged, tag_in, s.w, s.lane, ph, part)) flag_abort(s, smem);
     if (normed) {
+      const float ss = s.aborted ? 0.f : part_sumsq(part);
+      if (s.lane == 0) sumsq[s.w] = ss;
+      cta_sync(s, smem);
+      if (s.cta_abort) return;
       float tot = 0.f;
 #pragma unroll
       for (int j = 0; j < kWorkers; ++j) tot += sumsq[j];
-      load_xfrag_normed(xf, act, gains, rsqrtf(tot * (1.0f / S::H) + p.eps), s.lane);
-    } else if (nsl == 1) {
-      load_xfrag(xf, act, s.lane);
+      normalise_part(part, gains, rsqrtf(tot * (1.0f / S::H) + p.eps));
     }
-    cyc_xf = clock64() - tq2;
+    if (!s.aborted) store_part(part, act, s.w, s.lane);
+    cta_sync(s, smem);
+  }
+  if (s.cta_abort) return;
+  const long long tq1 = clock64();
+
+  int i0, i1;
+  switch (kind) {
+    case kQkv: i0 = s.q0; i1 = s.q1; break;
+    case kUpGate: i0 = s.u0; i1 = s.u1; break;
+    case kLmHead: i0 = s.l0; i1 = s.l1; break;
+    default: i0 = s.r0; i1 = s.r1; break;
+  }
+  const bool unit_tiles = kind == kQkv || kind == kUpGate;   // one item per tile (else two rows per tile)
+  const int nsl = kind == kDown ? kSlices : 1;
+  unsigned long long best = 0ull;
+  if (i0 < i1 && !s.aborted) {
+    XFrag xf;
+    if (nsl == 1) load_xfrag(xf, act, s.lane);
     const bool residual = kind == kOproj || kind == kDown;
     const uint16_t* res = kind == kOproj ? residual_src<S>(p, layer) : p.hidden;
     uint32_t* tres = kind == kOproj ? p.t_hid_o : p.t_hid_d;
@@ -163,34 +164,27 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
         else old = bf16_bits_to_f32(ldcg_u16(res + ib + s.lane));
       }
       float va = 0.f, vb = 0.f;
-      const int step = unit_pairs ? 1 : 2;
+      const int step = unit_tiles ? 1 : 2;
 #pragma unroll 1
       for (int i = 0; i < nb; i += step) {
-        const bool two = unit_pairs || (i + 1 < nb);
         float cc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
         for (int k = 0; k < nsl; ++k) {
           if (nsl > 1) load_xfrag(xf, act + k * kChunkBytes, s.lane);
-          const long long ta = clock64();
-          const uint32_t a0 = acquire_chunk(s, p, ph);
-          const uint32_t a1 = two ? acquire_chunk(s, p, ph) : a0;
-          const long long tb = clock64();
-          mma_chunk_pair(cc, a0, a1, xf, s.lane);
-          const long long tc = clock64();
-          release_chunks(s, p, two ? 2 : 1);
-          const long long td = clock64();
-          cyc_acq += tb - ta; cyc_mma += tc - tb; cyc_rel += td - tc;
+          const uint32_t t0 = acquire_tile(s, p, ph);
+          const bool two = unit_tiles || (i + 1 < nb);
+          mma_chunk_pair(cc, t0, two ? t0 + kChunkBytes : t0, xf, s.lane);
+          release_tile(s, p);
         }
         float sa, sb;
-        const long long te = clock64();
         diag_reduce(cc, s.lane, sa, sb);
-        cyc_red += clock64() - te;
         if (s.lane == i) {
           va = sa;
           vb = sb;
         }
-        if (!unit_pairs && two && s.lane == i + 1) va = sb;
+        if (!unit_tiles && s.lane == i + 1) va = sb;
       }
+      if (s.aborted) flag_abort(s, smem);
       if (s.lane < nb && !s.aborted) {
         const int item = ib + s.lane;
         switch (kind) {
@@ -221,14 +215,15 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     }
   }
   if (s.w == 0) {
-    const long long tq3 = clock64();
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
-    trace_put(p, ph, 4, (unsigned long long)(tq2 - tq1), s.lane);
-    trace_put(p, ph, 6, (unsigned long long)(tq3 - tq2), s.lane);
-    // diagnostic packing: acquire | mma | release | reduce | xfrag cycles (16 bits each would overflow: use slots 0,1 too)
-    trace_put(p, ph, 0, ((unsigned long long)cyc_acq << 32) | (unsigned long long)(cyc_mma & 0xffffffffll), s.lane);
-    trace_put(p, ph, 1, ((unsigned long long)cyc_rel << 32) | (unsigned long long)(cyc_red & 0xffffffffll), s.lane);
-    trace_put(p, ph, 7, (unsigned long long)cyc_xf, s.lane);
+    trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
+  }
+  if (p.trace != nullptr && s.lane == 0) {   // per CTA: earliest and latest end of the streaming loop over its warps
+    unsigned long long* t = p.trace + ((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8;
+    const unsigned long long now = globaltimer_ns();
+    atomicMax(t + 1, now);
+    atomicMax(t + 0, ~now);
+    atomicMax(t + 4, (unsigned long long)(clock64() - tq1));
   }
   if (kind != kLmHead) return;
 

@@ -2,15 +2,29 @@
 //
 // The producers of a vector (other SMs, earlier phase of the same step) store every element as one
 // 32-bit word {low: bf16 value, high: tag of (step, phase)}.  Each of the CTA's warps polls one
-// eighth of the words until all carry the expected tag, writes the bf16 values to shared memory,
-// raises part_done[warp] and later waits for the other warps' flags.  When the launch runs a single
-// phase on stream order (or for the first phase of a launch) the plain bf16 buffers are read instead.
+// eighth of the words until all carry the expected tag; after a CTA barrier the warp normalises its
+// eighth (when the phase starts with RMSNorm) and writes bf16 to shared memory; after a second
+// barrier every warp reads the whole vector.  When the launch runs a single phase on stream order
+// (or for the first phase of a launch) the plain bf16 buffers are read instead of the tagged words.
 #pragma once
 
 namespace qmk {
 
 __device__ __forceinline__ bool tags_ok(const uint4& v, unsigned tagw) {
   return (((v.x ^ tagw) | (v.y ^ tagw) | (v.z ^ tagw) | (v.w ^ tagw)) & 0xffff0000u) == 0u;
+}
+
+// Non-inlined tail of a tagged poll: checks the deadline and the global status word.
+// Returns true when the poll must give up.
+__device__ __noinline__ bool poll_give_up(const Params& p, long long t0, bool ok, unsigned seen_tag, unsigned tag,
+                                          int warp, int ph, int lane) {
+  const bool expired = clock64() - t0 > p.timeout_cycles;
+  const unsigned st = ld_relaxed_gpu(p.status + kStCode);
+  if (__any_sync(kFullMask, expired || st != 0u)) {
+    if (!ok && st == 0u) report_error(p, kErrCounterWait, warp, ph, seen_tag, tag, lane);
+    return true;
+  }
+  return false;
 }
 
 // Poll NPL uint4 per lane (4 tagged words each) starting at word `word0` until every word carries `tag`.
@@ -28,14 +42,7 @@ __device__ __forceinline__ bool poll_tagged(const Params& p, const uint32_t* tsr
       ok = ok && tags_ok(v[j], tagw);
     }
     if (__all_sync(kFullMask, ok)) return true;
-    if ((it & 15u) == 15u) {
-      const bool expired = clock64() - t0 > p.timeout_cycles;
-      const unsigned st = ld_relaxed_gpu(p.status + kStCode);
-      if (__any_sync(kFullMask, expired || st != 0u)) {
-        if (!ok && st == 0u) report_error(p, kErrCounterWait, warp, ph, v[0].x >> 16, tag, lane);
-        return false;
-      }
-    }
+    if ((it & 15u) == 15u && poll_give_up(p, t0, ok, v[0].x >> 16, tag, warp, ph, lane)) return false;
   }
 }
 
@@ -48,60 +55,72 @@ __device__ __forceinline__ float sumsq4(const uint2& b) {
   return fmaf(a0, a0, fmaf(a1, a1, fmaf(a2, a2, a3 * a3)));
 }
 
-// This warp's part of an N-element vector -> bf16 in shared memory at dst.  Returns the part's sum of
-// squares (warp-reduced) through `ss`.  tsrc: tagged words (used when `tagged`), psrc: plain bf16.
+// Fetch this warp's part of an N-element vector into registers: v[j] holds elements
+// e0 + (j*32 + lane)*4 .. +3 as packed bf16.  tsrc: tagged words (polled when `tagged`), psrc: plain bf16.
 template <int N>
-__device__ __forceinline__ bool stage_part_bf16(const Params& p, const uint32_t* tsrc, const uint16_t* psrc, bool tagged,
-                                                unsigned tag, unsigned char* dst, int warp, int lane, int ph,
-                                                float& ss) {
-  constexpr int kPart = N / kWorkers;              // elements per warp
-  static_assert(kPart % 128 == 0, "a warp's part must be whole uint4 rounds of tagged words");
-  constexpr int NPL = kPart / 128;                 // uint4 of tagged words per lane
-  const int e0 = warp * kPart;
-  float acc = 0.f;
+struct Part {
+  static constexpr int kElems = N / kWorkers;      // elements per warp
+  static constexpr int NPL = kElems / 128;         // 4-element groups per lane
+  static_assert(kElems % 128 == 0, "a warp's part must be whole rounds of 32 lanes x 4 elements");
+  uint2 v[NPL];
+};
+
+template <int N>
+__device__ __forceinline__ bool fetch_part(const Params& p, const uint32_t* tsrc, const uint16_t* psrc, bool tagged,
+                                           unsigned tag, int warp, int lane, int ph, Part<N>& part) {
+  const int e0 = warp * Part<N>::kElems;
   if (tagged) {
-    uint4 v[NPL];
-    if (!poll_tagged<NPL>(p, tsrc, e0, tag, lane, warp, ph, v)) return false;
+    uint4 t[Part<N>::NPL];
+    if (!poll_tagged<Part<N>::NPL>(p, tsrc, e0, tag, lane, warp, ph, t)) return false;
 #pragma unroll
-    for (int j = 0; j < NPL; ++j) {
-      const uint2 b = untag4(v[j]);
-      acc += sumsq4(b);
-      *reinterpret_cast<uint2*>(dst + (size_t)(e0 + (j * 32 + lane) * 4) * 2) = b;
-    }
+    for (int j = 0; j < Part<N>::NPL; ++j) part.v[j] = untag4(t[j]);
   } else {
     const uint2* src = reinterpret_cast<const uint2*>(psrc + e0);
 #pragma unroll
-    for (int j = 0; j < NPL; ++j) {
-      const uint2 b = __ldcg(src + j * 32 + lane);
-      acc += sumsq4(b);
-      *reinterpret_cast<uint2*>(dst + (size_t)(e0 + (j * 32 + lane) * 4) * 2) = b;
-    }
+    for (int j = 0; j < Part<N>::NPL; ++j) part.v[j] = __ldcg(src + j * 32 + lane);
   }
-  ss = warp_sum(acc);
   return true;
 }
 
-// Raise this warp's staging flag for `ph` (its shared-memory writes are ordered before it).
-__device__ __forceinline__ void raise_part_flag(uint32_t ctl, int warp, int lane, unsigned value) {
-  __syncwarp();
-  if (lane == 0) st_release_cta_shared(ctl + warp * 4, value);
+template <int N>
+__device__ __forceinline__ void store_part(const Part<N>& part, unsigned char* dst, int warp, int lane) {
+  const int e0 = warp * Part<N>::kElems;
+#pragma unroll
+  for (int j = 0; j < Part<N>::NPL; ++j)
+    *reinterpret_cast<uint2*>(dst + (size_t)(e0 + (j * 32 + lane) * 4) * 2) = part.v[j];
 }
 
-// Wait until every warp of the CTA has staged its part of `ph`.
-__device__ __noinline__ bool wait_parts(const Params& p, uint32_t ctl, int warp, int lane, int ph) {
-  const unsigned want = (unsigned)(ph + 1);
-  const long long t0 = clock64();
-  for (unsigned it = 0;; ++it) {
-    unsigned v = want;
-    if (lane < kWorkers) v = ld_acquire_cta_shared(ctl + lane * 4);
-    const bool aborted = __any_sync(kFullMask, v == kAbortFlag);
-    if (aborted) return false;
-    if (__all_sync(kFullMask, v >= want)) return true;
-    if ((it & 255u) == 255u && clock64() - t0 > 4 * p.timeout_cycles) {   // outlasts the pollers' own deadline
-      if (lane == 0) report_error(p, kErrStageWait, warp, ph, v, want, 0);
-      return false;
-    }
+template <int N>
+__device__ __forceinline__ float part_sumsq(const Part<N>& part) {
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < Part<N>::NPL; ++j) acc += sumsq4(part.v[j]);
+  return warp_sum(acc);
+}
+
+// RMSNorm of the part in registers: y = bf16(g * bf16(x * rstd))  (_rms_norm, fused/operations.py:126-131).
+template <int N>
+__device__ __forceinline__ void normalise_part(Part<N>& part, const uint2 (&gains)[Part<N>::NPL], float rstd) {
+#pragma unroll
+  for (int j = 0; j < Part<N>::NPL; ++j) {
+    const uint2 x = part.v[j], g = gains[j];
+    part.v[j].x = pack_bf16x2(bf_lo(g.x) * bf16_round(bf_lo(x.x) * rstd), bf_hi(g.x) * bf16_round(bf_hi(x.x) * rstd));
+    part.v[j].y = pack_bf16x2(bf_lo(g.y) * bf16_round(bf_lo(x.y) * rstd), bf_hi(g.y) * bf16_round(bf_hi(x.y) * rstd));
   }
+}
+
+// CTA barrier followed by a look at the CTA's abort word.  Every warp of the CTA executes the same
+// sequence of these (also warps that have given up), so a bounded wait that expires in one warp
+// never leaves the others stuck at a barrier.
+template <class S>
+__device__ __forceinline__ void cta_sync(Worker<S>& s, const unsigned char* smem) {
+  __syncthreads();
+  if (reinterpret_cast<const volatile unsigned*>(smem + SmemLayout<S>::kOffCtl)[kCtlAbort] != 0u) s.cta_abort = true;
+}
+template <class S>
+__device__ __forceinline__ void flag_abort(Worker<S>& s, unsigned char* smem) {
+  s.aborted = true;
+  if (s.lane == 0) reinterpret_cast<volatile unsigned*>(smem + SmemLayout<S>::kOffCtl)[kCtlAbort] = 1u;
 }
 
 }  // namespace qmk

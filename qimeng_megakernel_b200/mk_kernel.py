@@ -49,6 +49,13 @@ def _ptr(t) -> int | None:
     return t.data_ptr()
 
 
+def _sig(t):
+    """Identity of a bound tensor: address, shape and dtype (a view with another shape must re-validate)."""
+    if t is None:
+        return None
+    return (t.data_ptr(), tuple(t.shape), t.dtype)
+
+
 class MegaKernel:
     """Callable returned by get_mk(): owns one native handle per set of weights."""
 
@@ -100,7 +107,7 @@ class MegaKernel:
     def _ensure(self, g: Globals) -> None:
         wkey = tuple(_ptr(getattr(g, f, None)) for _, f in _WEIGHT_FIELDS) + tuple(
             LlamaConfig.as_dict().items())
-        skey = tuple(_ptr(getattr(g, f, None)) for f in _STATE_FIELDS) + (tuple(g.k_cache.shape),)
+        skey = tuple(_sig(getattr(g, f, None)) for f in _STATE_FIELDS)
         if wkey == self._weights_key and skey == self._state_key:
             return
         rows, S = self._validate(g)
