@@ -182,6 +182,11 @@ int qmk_poll_status(qmk_handle* h, qmk_status* out);
 /* Device-side wait budget in SM clock cycles (default 2e9, about one second). */
 int qmk_set_timeout_cycles(qmk_handle* h, int64_t cycles);
 
+/* Launch mode.  on (default): cooperative launch, the driver guarantees that all CTAs are co-resident
+ * (they wait on one another) or fails the launch.  off: plain launch, for a GPU the caller knows to be
+ * otherwise idle; the bounded waits still turn a missing CTA into QMK_ERR_DEVICE_TIMEOUT. */
+int qmk_set_cooperative_launch(qmk_handle* h, int32_t on);
+
 /* Debug knob used by the failure-detection test: when set, qmk_run_phases(mode 1) also waits for the
  * dependency of its first phase, which nothing publishes, so the bounded wait must expire. */
 int qmk_set_wait_first_dependency(qmk_handle* h, int32_t on);

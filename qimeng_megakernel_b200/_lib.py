@@ -55,6 +55,7 @@ SYMBOLS = [
     ("qmk_poll_status", C.c_int, [C.c_void_p, C.POINTER(Status)]),
     ("qmk_set_timeout_cycles", C.c_int, [C.c_void_p, C.c_int64]),
     ("qmk_set_trace", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
+    ("qmk_set_cooperative_launch", C.c_int, [C.c_void_p, C.c_int32]),
     ("qmk_set_wait_first_dependency", C.c_int, [C.c_void_p, C.c_int32]),
     ("qmk_step_bytes", C.c_int64, [C.c_void_p, C.c_int32]),
     ("qmk_launch_count", C.c_int64, [C.c_void_p]),

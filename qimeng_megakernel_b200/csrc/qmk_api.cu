@@ -24,6 +24,7 @@ struct qmk_handle {
   int device;
   int n_sm;
   unsigned launch_seq;
+  int cooperative;
   long long timeout_cycles;
   int wait_first;
   long long launches;
@@ -105,6 +106,7 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
   h->w = *w;
   h->device = device;
   h->timeout_cycles = 2000000000ll;
+  h->cooperative = 1;
   int rc = QMK_OK;
   do {
     cudaError_t e = cudaSetDevice(device);
@@ -236,7 +238,7 @@ static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another
-  attr[0].val.cooperative = 1;
+  attr[0].val.cooperative = h->cooperative;
   p.launch_seq = ++h->launch_seq;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -376,6 +378,12 @@ extern "C" int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes) 
   const int64_t need = (int64_t)h->n_sm * num_phases(h->desc.num_layers) * 8 * 8;
   if (bytes < need || (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) return QMK_ERR_INVALID_ARG;
   h->trace = (unsigned long long*)device_buffer;
+  return QMK_OK;
+}
+
+extern "C" int qmk_set_cooperative_launch(qmk_handle* h, int32_t on) {
+  if (!h) return QMK_ERR_INVALID_ARG;
+  h->cooperative = on ? 1 : 0;
   return QMK_OK;
 }
 

@@ -59,6 +59,7 @@ __device__ __forceinline__ bool stage_attn_part(const Params& p, unsigned char* 
       }
       if (__all_sync(kFullMask, ok)) break;
       if ((it & 15u) == 15u && poll_give_up(p, t0, ok, vq[0].x >> 16, tag, warp, ph, lane)) return false;
+      poll_backoff(it);
     }
 #pragma unroll
     for (int j = 0; j < NQ; ++j) {
@@ -228,6 +229,7 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigne
         if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e + 2) = make_uint2((w1 & 0xffffu) | tagw, (w1 >> 16) | tagw);
       }
     }
+    __threadfence();   // push the tagged stores out (see phase_stream)
     return;
   }
 
@@ -242,6 +244,8 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigne
     if (s.lane == 0)
       *reinterpret_cast<uint4*>(rec + HD) = make_uint4(__float_as_uint(m[h]), rtag, __float_as_uint(l[h]), rtag);
   }
+
+  __threadfence();     // push the record out (see phase_stream)
 
   // ---- merge: unit `part` merges the heads h = part, part + nm, ... of its group (nm = min(P, GQA))
   const int nm = P < GQA ? P : GQA;
@@ -275,6 +279,7 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigne
           s.aborted = true;
           return;
         }
+        poll_backoff(it);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -301,6 +306,7 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigne
       if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e + d) = make_uint2((w & 0xffffu) | tagw, (w >> 16) | tagw);
     }
   }
+  __threadfence();
 }
 
 // ---- phase 1: attention.  Units (kv head, partial) are dealt round-robin over SMs first.

@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmk_decode_kernel(const __grid_co
   extern __shared__ __align__(128) unsigned char smem[];
   using L = SmemLayout<S>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned long long t_entry = globaltimer_ns();
   if (lane == 0)
     for (int i = 0; i < kSlots; ++i) mbar_init(smem_u32(smem + L::kOffBars + (warp * kSlots + i) * 8), 1);
   if (warp == 0) {
@@ -72,6 +73,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmk_decode_kernel(const __grid_co
   if (lane == 0) fence_barrier_init();
   __syncthreads();
   worker_main<S>(p, smem, warp, lane);
+  if (p.trace != nullptr && lane == 0) {   // kernel entry / exit of this CTA, kept in the slots of the first phase
+    unsigned long long* t = p.trace + ((size_t)blockIdx.x * num_phases(p.num_layers) + p.phase_begin) * 8;
+    atomicMax(t + 3, ~t_entry);
+    atomicMax(t + 7, globaltimer_ns());
+  }
 }
 
 }  // namespace qmk

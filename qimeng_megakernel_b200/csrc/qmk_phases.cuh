@@ -214,6 +214,10 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
       if (residual && ib == i0) s.res_valid = true;
     }
   }
+  // Push this warp's tagged stores out now.  Nothing waits for the fence itself (the warp would only
+  // start polling for the next phase), but without it the stores linger behind the polling loads and
+  // every consumer sees them about a microsecond later (measured: 16 % of the whole step).
+  __threadfence();
   if (s.w == 0) {
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
     trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);

@@ -27,6 +27,15 @@ __device__ __noinline__ bool poll_give_up(const Params& p, long long t0, bool ok
   return false;
 }
 
+// Optional pause between two polls of words that are not there yet (measured on B200: any pause only
+// adds latency, the polling traffic itself does not disturb the weight stream; default off).
+#ifndef QMK_POLL_SLEEP_NS
+#define QMK_POLL_SLEEP_NS 0
+#endif
+__device__ __forceinline__ void poll_backoff(unsigned it) {
+  if (QMK_POLL_SLEEP_NS > 0) __nanosleep(it < 2 ? QMK_POLL_SLEEP_NS / 2 : QMK_POLL_SLEEP_NS);
+}
+
 // Poll NPL uint4 per lane (4 tagged words each) starting at word `word0` until every word carries `tag`.
 template <int NPL>
 __device__ __forceinline__ bool poll_tagged(const Params& p, const uint32_t* tsrc, int word0, unsigned tag, int lane,
@@ -43,6 +52,7 @@ __device__ __forceinline__ bool poll_tagged(const Params& p, const uint32_t* tsr
     }
     if (__all_sync(kFullMask, ok)) return true;
     if ((it & 15u) == 15u && poll_give_up(p, t0, ok, v[0].x >> 16, tag, warp, ph, lane)) return false;
+    poll_backoff(it);
   }
 }
 

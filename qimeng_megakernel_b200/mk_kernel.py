@@ -188,6 +188,9 @@ class MegaKernel:
     def set_timeout_cycles(self, cycles: int) -> None:
         _lib.check(self._lib.qmk_set_timeout_cycles(self._handle, int(cycles)))
 
+    def set_cooperative_launch(self, on: bool) -> None:
+        _lib.check(self._lib.qmk_set_cooperative_launch(self._handle, 1 if on else 0))
+
     def set_wait_first_dependency(self, on: bool) -> None:
         _lib.check(self._lib.qmk_set_wait_first_dependency(self._handle, 1 if on else 0))
 
