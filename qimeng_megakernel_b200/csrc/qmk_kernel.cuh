@@ -1,14 +1,15 @@
 // Core of the persistent decode megakernel for sm_100a: one CTA per SM, eight identical worker warps.
 //
-//  * Weight stream.  Every warp owns a private ring of 4-KiB shared-memory slots.  Lane 0 streams
-//    the warp's weight chunks into it with cp.async.bulk (TMA engine, mbarrier byte completion); the
+//  * Weight stream.  Every warp owns a private ring of 8-KiB shared-memory slots.  Lane 0 streams
+//    the warp's weight tiles into it with cp.async.bulk (TMA engine, mbarrier byte completion); the
 //    stream is one static sequence that runs across phase and layer boundaries, so the next phases'
 //    weights are in flight while the warp waits for activations.
 //  * Hand-off between phases without fences or counters.  Every activation word that crosses SMs is
 //    written as ONE 32-bit store {bf16 value, 16-bit tag of (step, phase)}.  A consumer polls the
 //    data itself until every word carries the expected tag (the idea of NCCL's LL protocol).  The
 //    eight warps of a CTA each fetch one eighth of the vector ("cooperative staging"), drop it in
-//    shared memory, raise a per-warp flag and then wait for the other seven.
+//    shared memory and meet at a CTA barrier.  A warp pushes its tagged stores out with a fence that
+//    nothing waits for.
 //  * The residual stream never goes through memory on the critical path: the warp that owns row r
 //    in the O-projection owns it in the down-projection and in every later layer, so hidden[r]
 //    stays in a register of that warp.
@@ -87,17 +88,7 @@ __device__ __forceinline__ unsigned phase_tag(const Params& p, int ph) {
 }
 
 // ------------------------------------------------------------------------------------------
-// Worker state: tile ring + issue cursor.  All fields are warp-uniform except `res`.
-//
-// The weight stream of a warp is a sequence of TILES.  A tile is what one tensor-pipe product
-// consumes: two 4-KiB chunks (or one, for an odd last row) that meet the same activations.  It
-// occupies one 8-KiB ring slot with one mbarrier and is fetched by one 8-KiB bulk copy when its two
-// chunks are adjacent in memory, else by two 4-KiB copies completing on the same mbarrier:
-//   QKV      rows (2u, 2u+1) of one RoPE pair                      one copy
-//   O-proj   rows (r, r+1)                                          one copy
-//   LM head  rows (r, r+1)                                          one copy
-//   up/gate  (up row u, gate row u)                                 two copies
-//   down     (row a, k-slice j), (row a+1, k-slice j), j = 0..I/2048-1 per row pair   two copies
+// Worker state: tile ring + issue cursor (qmk_schedule.h).  All fields are warp-uniform except `res`.
 // ------------------------------------------------------------------------------------------
 template <class S>
 struct Worker {
@@ -108,140 +99,30 @@ struct Worker {
   unsigned n_issued, n_acquired;
   unsigned i_slot;         // slot the next issue goes into
   unsigned c_slot, c_par;  // slot and mbarrier parity of the next tile to consume
-  // issue cursor
-  int i_ph, i_kind;        // phase being issued and its kind
-  int i_left;              // tiles left in that phase
-  int i_sub;               // down-proj: k-slice of the next tile
-  int i_rows_left;         // rows (O-proj / LM / down) still to be covered, to spot the odd last row
-  const unsigned char* i_p0;   // next source (first chunk)
-  const unsigned char* i_p1;   // up/gate: gate row
-  // this worker's item ranges per streaming kind: identical for every layer, so the 32-bit
-  // divisions of the even split are done once per launch.
-  int q0, q1;              // QKV units (RoPE pairs)
-  int r0, r1;              // rows of the residual phases (O-proj and down-proj share the split)
-  int u0, u1;              // SwiGLU units
-  int l0, l1;              // LM head rows
-  float res;               // residual stream value of row (r0 + lane), bf16-exact
+  TileCursor<S> cur;       // where the weight stream is; also holds this worker's item ranges
+  StreamBases wb;
+  float res;               // residual stream value of row (cur.r0 + lane), bf16-exact
   bool res_valid;
   bool aborted;            // this warp gave up (bounded wait expired)
   bool cta_abort;          // the whole CTA leaves the phase loop
   uint64_t policy;
 };
 
-__device__ __forceinline__ void split_range_u32(unsigned units, unsigned parts, unsigned g, int& lo, int& hi) {
-  lo = (int)((g * units) / parts);            // (g + 1) * units < 2^32 is checked on the host
-  hi = (int)(((g + 1u) * units) / parts);
-}
-
-template <class S>
-__device__ __forceinline__ void init_ranges(Worker<S>& s, const Params& p) {
-  split_range_u32(S::QKV_ROWS / 2, s.nwt, s.g, s.q0, s.q1);
-  split_range_u32(S::H, s.nwt, s.g, s.r0, s.r1);
-  split_range_u32(S::I, s.nwt, s.g, s.u0, s.u1);
-  split_range_u32((unsigned)p.vocab, s.nwt, s.g, s.l0, s.l1);
-}
-
-// Number of tiles of this worker in a phase of `kind`.
-template <class S>
-__device__ __forceinline__ int kind_tiles(const Worker<S>& s, int kind) {
-  constexpr int kSlices = S::I / kChunkElems;
-  switch (kind) {
-    case kQkv: return s.q1 - s.q0;
-    case kOproj: return (s.r1 - s.r0 + 1) >> 1;
-    case kUpGate: return s.u1 - s.u0;
-    case kDown: return ((s.r1 - s.r0 + 1) >> 1) * kSlices;
-    case kLmHead: return (s.l1 - s.l0 + 1) >> 1;
-    default: return 0;
-  }
-}
-
-// Position the issue cursor on the first phase >= i_ph in which this worker streams weights and
-// set the source pointers of its first tile.
-template <class S>
-__device__ __forceinline__ void cursor_seek(Worker<S>& s, const Params& p) {
-  while (s.i_ph < p.phase_end) {
-    const int layer = s.i_ph / kPhasesPerLayer;
-    const int kind = layer >= p.num_layers ? (int)kLmHead : s.i_ph - layer * kPhasesPerLayer;
-    const int n = kind_tiles(s, kind);
-    if (n > 0) {
-      s.i_kind = kind;
-      s.i_left = n;
-      s.i_sub = 0;
-      const size_t row_b = (size_t)kChunkBytes;
-      switch (kind) {
-        case kQkv:
-          s.i_p0 = reinterpret_cast<const unsigned char*>(p.qkv) + ((size_t)layer * S::QKV_ROWS + 2 * s.q0) * row_b;
-          break;
-        case kOproj:
-          s.i_p0 = reinterpret_cast<const unsigned char*>(p.o_proj) + ((size_t)layer * S::H + s.r0) * row_b;
-          s.i_rows_left = s.r1 - s.r0;
-          break;
-        case kUpGate:
-          s.i_p0 = reinterpret_cast<const unsigned char*>(p.up) + ((size_t)layer * S::I + s.u0) * row_b;
-          s.i_p1 = reinterpret_cast<const unsigned char*>(p.gate) + ((size_t)layer * S::I + s.u0) * row_b;
-          break;
-        case kDown:
-          s.i_p0 = reinterpret_cast<const unsigned char*>(p.down) + ((size_t)layer * S::H + s.r0) * (size_t)S::I * 2;
-          s.i_rows_left = s.r1 - s.r0;
-          break;
-        default:
-          s.i_p0 = reinterpret_cast<const unsigned char*>(p.lm_head) + (size_t)s.l0 * row_b;
-          s.i_rows_left = s.l1 - s.l0;
-          break;
-      }
-      return;
-    }
-    ++s.i_ph;
-  }
-}
-
-// Issue the next tile of the stream into the oldest free slot, if any tile is left.
+// Issue the next tile of the stream into the oldest free slot, if any tile is left: one 8-KiB bulk
+// copy, or two 4-KiB copies completing on the same mbarrier.
 template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
-  if (s.aborted || s.i_ph >= p.phase_end) return;
-  constexpr int kSlices = S::I / kChunkElems;
-  const unsigned char* a = s.i_p0;
-  const unsigned char* b = nullptr;
-  uint32_t bytes_a = 2 * kChunkBytes;
-  switch (s.i_kind) {
-    case kQkv:
-      s.i_p0 += 2 * kChunkBytes;
-      break;
-    case kUpGate:
-      bytes_a = kChunkBytes;
-      b = s.i_p1;
-      s.i_p0 += kChunkBytes;
-      s.i_p1 += kChunkBytes;
-      break;
-    case kDown:
-      bytes_a = kChunkBytes;
-      a += s.i_sub * kChunkBytes;
-      if (s.i_rows_left > 1) b = a + (size_t)S::I * 2;
-      if (++s.i_sub == kSlices) {
-        s.i_sub = 0;
-        s.i_p0 += 2 * (size_t)S::I * 2;
-        s.i_rows_left -= 2;
-      }
-      break;
-    default:   // O-proj, LM head
-      if (s.i_rows_left < 2) bytes_a = kChunkBytes;
-      s.i_rows_left -= 2;
-      s.i_p0 += 2 * kChunkBytes;
-      break;
-  }
+  if (s.aborted || s.cur.done(p.phase_end)) return;
+  const Tile t = s.cur.next(s.wb, p.num_layers, p.phase_end);
   if (s.lane == 0) {
     const uint32_t bar = s.bars + s.i_slot * 8;
     const uint32_t dst = s.ring + s.i_slot * (2 * kChunkBytes);
-    mbar_expect_tx(bar, bytes_a + (b != nullptr ? (uint32_t)kChunkBytes : 0u));
-    bulk_g2s(dst, a, bytes_a, bar, s.policy);
-    if (b != nullptr) bulk_g2s(dst + kChunkBytes, b, kChunkBytes, bar, s.policy);
+    mbar_expect_tx(bar, t.bytes_a + (t.b != nullptr ? (uint32_t)kChunkBytes : 0u));
+    bulk_g2s(dst, t.a, t.bytes_a, bar, s.policy);
+    if (t.b != nullptr) bulk_g2s(dst + kChunkBytes, t.b, kChunkBytes, bar, s.policy);
   }
   ++s.n_issued;
   s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
-  if (--s.i_left == 0) {
-    ++s.i_ph;
-    cursor_seek(s, p);
-  }
 }
 
 // Bounded wait on one ring slot.  Returns false (and flags the error) on expiry.  The spin with its

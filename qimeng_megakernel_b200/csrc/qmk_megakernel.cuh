@@ -17,16 +17,19 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.ctl = smem_u32(smem + L::kOffCtl);
   s.n_issued = s.n_acquired = 0;
   s.i_slot = s.c_slot = s.c_par = 0;
-  s.i_ph = p.phase_begin;
-  s.i_kind = s.i_left = s.i_sub = s.i_rows_left = 0;
-  s.i_p0 = s.i_p1 = nullptr;
-  s.cta_abort = false;
   s.res = 0.f;
   s.res_valid = false;
   s.aborted = false;
+  s.cta_abort = false;
   s.policy = l2_policy_evict_first();
-  init_ranges(s, p);
-  cursor_seek(s, p);
+  s.wb.qkv = reinterpret_cast<const unsigned char*>(p.qkv);
+  s.wb.o_proj = reinterpret_cast<const unsigned char*>(p.o_proj);
+  s.wb.up = reinterpret_cast<const unsigned char*>(p.up);
+  s.wb.gate = reinterpret_cast<const unsigned char*>(p.gate);
+  s.wb.down = reinterpret_cast<const unsigned char*>(p.down);
+  s.wb.lm_head = reinterpret_cast<const unsigned char*>(p.lm_head);
+  s.cur.init(s.g, s.nwt, p.vocab, p.phase_begin);
+  s.cur.seek(s.wb, p.num_layers, p.phase_end);
 #pragma unroll 1
   for (int i = 0; i < kSlots; ++i) issue_one(s, p);
 

@@ -139,10 +139,10 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
 
   int i0, i1;
   switch (kind) {
-    case kQkv: i0 = s.q0; i1 = s.q1; break;
-    case kUpGate: i0 = s.u0; i1 = s.u1; break;
-    case kLmHead: i0 = s.l0; i1 = s.l1; break;
-    default: i0 = s.r0; i1 = s.r1; break;
+    case kQkv: i0 = s.cur.q0; i1 = s.cur.q1; break;
+    case kUpGate: i0 = s.cur.u0; i1 = s.cur.u1; break;
+    case kLmHead: i0 = s.cur.l0; i1 = s.cur.l1; break;
+    default: i0 = s.cur.r0; i1 = s.cur.r1; break;
   }
   const bool unit_tiles = kind == kQkv || kind == kUpGate;   // one item per tile (else two rows per tile)
   const int nsl = kind == kDown ? kSlices : 1;

@@ -1,12 +1,14 @@
 // Static on-device schedule of the decode megakernel: phases, per-worker work ranges and the
-// weight-chunk stream.  Everything here is pure integer arithmetic shared by host and device
-// (the host uses it for validation and for the CPU simulation of the schedule in the tests).
+// weight-tile stream.  Everything here is pure integer / pointer arithmetic shared by host and device:
+// the device uses it to drive its bulk copies, the host tests replay it on the CPU and check that the
+// streams of all workers cover every weight byte exactly once, in the order the phases consume them.
 //
 // The reference builds per-SM instruction queues on the host for every request
 // (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_schedule/instructions/scheduler.py:164-361)
 // and ships them as an int32 tensor.  Here every worker warp derives its own work from
 // (phase, worker id) with the closed-form splits below, so nothing is built or uploaded.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #if defined(__CUDACC__)
@@ -17,14 +19,12 @@
 
 namespace qmk {
 
-// One weight chunk = 2048 contiguous bf16 = 4 KiB: the unit of every bulk copy and ring slot.
+// One weight chunk = 2048 contiguous bf16 = 4 KiB = one row (or one k-slice of a row).
 constexpr int kChunkElems = 2048;
 constexpr int kChunkBytes = kChunkElems * 2;
 
 enum PhaseKind : int { kQkv = 0, kAttn = 1, kOproj = 2, kUpGate = 3, kDown = 4, kLmHead = 5 };
 constexpr int kPhasesPerLayer = 5;
-constexpr int kCounterShards = 32;        // dependency counter shards per phase (one per controller lane)
-constexpr int kCounterStrideWords = 32;   // each shard in its own 128-byte line
 constexpr int kAttnBlockKeys = 32;        // keys per attention block (one per lane)
 constexpr int kMaxSplits = 64;            // upper bound on split-KV partials per head
 
@@ -46,69 +46,11 @@ QMK_HD int phase_kind(int ph, int num_layers) {
 QMK_HD int phase_layer(int ph) { return ph / kPhasesPerLayer; }
 QMK_HD int num_phases(int num_layers) { return num_layers * kPhasesPerLayer + 1; }
 
-// Even contiguous split of `units` over `parts`: part g owns [lo, hi).
-QMK_HD void split_range(int units, int parts, int g, int& lo, int& hi) {
-  lo = (int)(((long long)g * units) / parts);
-  hi = (int)(((long long)(g + 1) * units) / parts);
-}
-
-// Work units of a streaming phase for worker g of nwt: units are row pairs (QKV: RoPE pairs),
-// rows (O-proj, down-proj, LM head) or up/gate row pairs (SwiGLU).
-template <class S>
-QMK_HD int phase_units(int kind, int vocab) {
-  switch (kind) {
-    case kQkv: return S::QKV_ROWS / 2;
-    case kOproj: return S::H;
-    case kUpGate: return S::I;
-    case kDown: return S::H;
-    case kLmHead: return vocab;
-    default: return 0;
-  }
-}
-template <class S>
-QMK_HD int chunks_per_unit(int kind) {
-  switch (kind) {
-    case kQkv: return 2;
-    case kOproj: return S::QDIM / kChunkElems;
-    case kUpGate: return 2;
-    case kDown: return S::I / kChunkElems;
-    case kLmHead: return 1;
-    default: return 0;
-  }
-}
-
-// Chunk range [c0, c1) of worker g in a phase of this kind (empty for attention).
-template <class S>
-QMK_HD void phase_chunk_range(int kind, int vocab, int g, int nwt, int& c0, int& c1) {
-  if (kind == kAttn) { c0 = c1 = 0; return; }
-  int u0, u1;
-  split_range(phase_units<S>(kind, vocab), nwt, g, u0, u1);
-  const int cpu = chunks_per_unit<S>(kind);
-  c0 = u0 * cpu;
-  c1 = u1 * cpu;
-}
-
-struct WeightBases {
-  const uint16_t* qkv;
-  const uint16_t* o_proj;
-  const uint16_t* up;
-  const uint16_t* gate;
-  const uint16_t* down;
-  const uint16_t* lm_head;
-};
-
-// Address of chunk c of (kind, layer).  Chunk numbering follows consumption order inside a unit:
-// QKV: chunk = row (rows 2u, 2u+1); SwiGLU: chunk 2u = up row u, 2u+1 = gate row u;
-// down-proj: chunk = row * (I/2048) + k-slice; O-proj / LM head: chunk = row.
-template <class S>
-QMK_HD const uint16_t* chunk_ptr(const WeightBases& w, int kind, int layer, int c) {
-  switch (kind) {
-    case kQkv: return w.qkv + ((size_t)layer * S::QKV_ROWS + c) * S::H;
-    case kOproj: return w.o_proj + (size_t)layer * S::H * S::QDIM + (size_t)c * kChunkElems;
-    case kUpGate: return ((c & 1) ? w.gate : w.up) + ((size_t)layer * S::I + (c >> 1)) * S::H;
-    case kDown: return w.down + (size_t)layer * S::H * S::I + (size_t)c * kChunkElems;
-    default: return w.lm_head + (size_t)c * S::H;
-  }
+// Even contiguous split of `units` over `parts`: part g owns [lo, hi).  32-bit arithmetic:
+// (g + 1) * units must stay below 2^32 (checked by the host when a handle is created).
+QMK_HD void split_range_u32(unsigned units, unsigned parts, unsigned g, int& lo, int& hi) {
+  lo = (int)((g * units) / parts);
+  hi = (int)(((g + 1u) * units) / parts);
 }
 
 // Split-KV plan for KV length T (= pos+1): blocks of 32 keys, `bps` blocks per partial, P partials.
@@ -123,11 +65,147 @@ QMK_HD void attn_plan(int T, int& bps, int& P) {
   if (P < 1) P = 1;
 }
 
-// How many publishers of a phase land on counter shard `shard`.
-// Streaming phases: every worker publishes once (shard = g % 32).
-// Attention: one publish per (kv head) merge (shard = kv_head % 32).
-QMK_HD unsigned shard_contrib(int n_publishers, int shard) {
-  return n_publishers > shard ? (unsigned)((n_publishers - shard + kCounterShards - 1) / kCounterShards) : 0u;
-}
+// ------------------------------------------------------------------------------------------
+// The weight stream of a worker is a sequence of TILES.  A tile is what one tensor-pipe product
+// consumes: two 4-KiB chunks (or one, for an odd last row) that meet the same activations.  It
+// occupies one 8-KiB ring slot and is fetched by one 8-KiB bulk copy when its two chunks are
+// adjacent in memory, else by two 4-KiB copies:
+//   QKV      rows (2u, 2u+1) of one RoPE pair                                          one copy
+//   O-proj   rows (r, r+1)                                                              one copy
+//   LM head  rows (r, r+1)                                                              one copy
+//   up/gate  (up row u, gate row u)                                                     two copies
+//   down     (row a, k-slice j), (row a+1, k-slice j), j = 0..I/2048-1 per row pair     two copies
+// ------------------------------------------------------------------------------------------
+struct StreamBases {
+  const unsigned char* qkv;
+  const unsigned char* o_proj;
+  const unsigned char* up;
+  const unsigned char* gate;
+  const unsigned char* down;
+  const unsigned char* lm_head;
+};
+
+struct Tile {
+  const unsigned char* a;   // first chunk (or both, when bytes_a == 8192)
+  const unsigned char* b;   // second chunk when it is not adjacent, else null
+  uint32_t bytes_a;
+};
+
+template <class S>
+struct TileCursor {
+  // this worker's item ranges per streaming kind: identical for every layer, so the divisions of the
+  // even split are done once per launch.
+  int q0, q1;              // QKV units (RoPE pairs)
+  int r0, r1;              // rows of the residual phases (O-proj and down-proj share the split)
+  int u0, u1;              // SwiGLU units
+  int l0, l1;              // LM head rows
+  // position in the stream
+  int ph, kind;            // phase being issued and its kind
+  int left;                // tiles left in that phase
+  int sub;                 // down-proj: k-slice of the next tile
+  int rows_left;           // rows (O-proj / LM / down) still to be covered, to spot the odd last row
+  const unsigned char* p0; // next source (first chunk)
+  const unsigned char* p1; // up/gate: gate row
+
+  QMK_HD void init(int g, int nwt, int vocab, int phase_begin) {
+    split_range_u32(S::QKV_ROWS / 2, nwt, g, q0, q1);
+    split_range_u32(S::H, nwt, g, r0, r1);
+    split_range_u32(S::I, nwt, g, u0, u1);
+    split_range_u32((unsigned)vocab, nwt, g, l0, l1);
+    ph = phase_begin;
+    kind = left = sub = rows_left = 0;
+    p0 = p1 = nullptr;
+  }
+
+  // Number of tiles of this worker in a phase of kind k.
+  QMK_HD int tiles(int k) const {
+    switch (k) {
+      case kQkv: return q1 - q0;
+      case kOproj: return (r1 - r0 + 1) >> 1;
+      case kUpGate: return u1 - u0;
+      case kDown: return ((r1 - r0 + 1) >> 1) * (S::I / kChunkElems);
+      case kLmHead: return (l1 - l0 + 1) >> 1;
+      default: return 0;
+    }
+  }
+
+  // Position on the first phase >= ph in which this worker streams weights; set its first sources.
+  QMK_HD void seek(const StreamBases& w, int num_layers, int phase_end) {
+    while (ph < phase_end) {
+      const int layer = ph / kPhasesPerLayer;
+      const int k = layer >= num_layers ? (int)kLmHead : ph - layer * kPhasesPerLayer;
+      const int n = tiles(k);
+      if (n > 0) {
+        kind = k;
+        left = n;
+        sub = 0;
+        const size_t row_b = (size_t)kChunkBytes;
+        switch (k) {
+          case kQkv: p0 = w.qkv + ((size_t)layer * S::QKV_ROWS + 2 * (size_t)q0) * row_b; break;
+          case kOproj:
+            p0 = w.o_proj + ((size_t)layer * S::H + r0) * row_b;
+            rows_left = r1 - r0;
+            break;
+          case kUpGate:
+            p0 = w.up + ((size_t)layer * S::I + u0) * row_b;
+            p1 = w.gate + ((size_t)layer * S::I + u0) * row_b;
+            break;
+          case kDown:
+            p0 = w.down + ((size_t)layer * S::H + r0) * (size_t)S::I * 2;
+            rows_left = r1 - r0;
+            break;
+          default:
+            p0 = w.lm_head + (size_t)l0 * row_b;
+            rows_left = l1 - l0;
+            break;
+        }
+        return;
+      }
+      ++ph;
+    }
+  }
+
+  QMK_HD bool done(int phase_end) const { return ph >= phase_end; }
+
+  // The next tile of the stream; advances the cursor (and seeks the next phase when this one ends).
+  QMK_HD Tile next(const StreamBases& w, int num_layers, int phase_end) {
+    constexpr int kSlices = S::I / kChunkElems;
+    Tile t;
+    t.a = p0;
+    t.b = nullptr;
+    t.bytes_a = 2 * kChunkBytes;
+    switch (kind) {
+      case kQkv:
+        p0 += 2 * kChunkBytes;
+        break;
+      case kUpGate:
+        t.bytes_a = kChunkBytes;
+        t.b = p1;
+        p0 += kChunkBytes;
+        p1 += kChunkBytes;
+        break;
+      case kDown:
+        t.bytes_a = kChunkBytes;
+        t.a += (size_t)sub * kChunkBytes;
+        if (rows_left > 1) t.b = t.a + (size_t)S::I * 2;
+        if (++sub == kSlices) {
+          sub = 0;
+          p0 += 2 * (size_t)S::I * 2;
+          rows_left -= 2;
+        }
+        break;
+      default:   // O-proj, LM head
+        if (rows_left < 2) t.bytes_a = kChunkBytes;
+        rows_left -= 2;
+        p0 += 2 * kChunkBytes;
+        break;
+    }
+    if (--left == 0) {
+      ++ph;
+      seek(w, num_layers, phase_end);
+    }
+    return t;
+  }
+};
 
 }  // namespace qmk
