@@ -308,3 +308,47 @@ def test_full_size_against_reference_fixture():
     mk.close()
     assert agree / n_steps >= 0.99 or untied_agree == untied, f"top-1 agreement {agree}/{n_steps}"
     assert untied_agree == untied, f"arg-max differs on {untied - untied_agree} untied steps"
+
+
+def test_decode_api_host_and_device_loops(small_config, small_weights):
+    """`decode(route='mk', hardware='B200')`: the reference's host loop (embed / call_mk / arg-max in PyTorch)
+    and the device-resident loop generate the same tokens as the CPU oracle's greedy loop, and the timing
+    dictionary carries the reference's keys."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.decode import decode
+    from qimeng_megakernel_b200.prefill import run_prefill_synthetic
+    prompt = synthetic.make_prompt(small_config["vocab_size"], 16, seed=21)
+    n_new = 24
+    st = U.oracle_state(small_config, small_weights, 16 + n_new, torch.bfloat16)
+    seq = prompt.tolist()
+    for pos in range(16 + n_new - 1):
+        nxt = fo.feed_token(st, seq[pos], pos)
+        if pos + 1 >= len(seq):
+            seq.append(nxt)
+    outs = []
+    for host_loop in (True, False):
+        pre = run_prefill_synthetic(small_config, small_weights, prompt, n_new, device="cuda:0")
+        out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, decode_route="mk", hardware="B200",
+                     decode_time=True, ignore_eos=True, host_loop=host_loop)
+        assert out["generated_ids"].shape == (1, 16 + n_new)
+        assert out["per_row_new_tokens"].tolist() == [n_new]
+        t = out["timing"]
+        for key in ("decode_wall_s", "decode_gpu_s", "mk_kernel_gpu_s", "effective_new_tokens",
+                    "decode_window_new_tokens", "effective_tok_s_wall", "effective_tok_s_gpu", "kernel_tok_s", "kernel_steps"):
+            assert key in t
+        assert t["decode_window_new_tokens"] == n_new - 1 and t["kernel_steps"] == n_new - 1 and t["kernel_tok_s"] > 0
+        outs.append(out["generated_ids"][0].tolist())
+        pre.mk.close()
+    assert outs[0] == outs[1]
+    agree = sum(int(a == b) for a, b in zip(outs[0], seq)) / len(seq)
+    assert agree >= 0.99 or outs[0][:17] == seq[:17], f"greedy tokens agree with the oracle on {agree:.0%}"
+    # EOS handling: stop at the first EOS, pad after it
+    pre = run_prefill_synthetic(small_config, small_weights, prompt, n_new, device="cuda:0")
+    eos = outs[0][16 + 5]
+    out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, eos_token_ids=[eos], pad_token_id=0)
+    first = outs[0][16:].index(eos)
+    assert out["per_row_new_tokens"].tolist() == [first + 1]
+    assert out["new_tokens"].shape[1] == first + 1
+    pre.mk.close()

@@ -1,0 +1,152 @@
+"""Host-side logic that needs no GPU: registry, config, RoPE tables, synthetic model, Globals contract,
+argument validation of the kernel wrapper, and the rank-sharding arithmetic of the multi-GPU bench
+(gloo, world size 2)."""
+import dataclasses
+import math
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_package_contract():
+    import qimeng_megakernel_b200 as pkg
+    assert pkg.STATIC_MEGAKERNEL is True and pkg.HARDWARE == "B200"
+    assert pkg.ModelConfig is pkg.LlamaConfig
+    from qimeng_megakernel_b200 import mk_kernel
+    assert callable(mk_kernel.get_mk) and callable(mk_kernel.call_mk)
+    # field-for-field superset of the reference's Globals (decode_schedule/globs.py:8-41)
+    names = {f.name for f in dataclasses.fields(pkg.Globals)}
+    for ref_field in ("instructions", "barriers", "position_id", "attn_norm_weights", "qkv_weights", "rope_cos",
+                      "rope_sin", "o_proj_weights", "mlp_norm_weights", "up_proj_weights", "gate_proj_weights",
+                      "down_proj_weights", "lm_head_norm_weights", "lm_head_weights", "k_cache", "v_cache",
+                      "hidden_states", "q_post_rope", "attn_out", "attn_out_intermediates", "attn_lse_intermediates",
+                      "silu_out", "logits"):
+        assert ref_field in names
+
+
+def test_registry():
+    from qimeng_megakernel_b200 import registry as R
+    assert R.decode_schedule_package_name("meta-llama/Llama-3.2-1B", "B200") == "qimeng_megakernel_b200"
+    sched = R.import_decode_schedule("llama-3.2-1b", "B200", 1)
+    assert sched.get_mk is not None and sched.call_mk is not None and sched.scheduler is None
+    assert sched.config.hidden_size == 2048
+    with pytest.raises(NotImplementedError):
+        R.decode_schedule_package_name("llama-3.2-1b", "B200", batch_size=2)
+    with pytest.raises(NotImplementedError):
+        R.decode_schedule_package_name("qwen3-0.6b", "B200")
+    with pytest.raises(ValueError):
+        R.resolve_hardware("H100")
+    assert R.resolve_hardware("auto", device_name="NVIDIA B200") == "B200"
+    with pytest.raises(RuntimeError):
+        R.resolve_hardware("auto", device_name="NVIDIA A100-SXM4-80GB")
+
+
+def test_model_config_roundtrip():
+    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, LlamaConfig
+    LlamaConfig.update_from_dict(dict(LLAMA_3_2_1B, num_hidden_layers=3))
+    d = LlamaConfig.as_dict()
+    assert d["num_hidden_layers"] == 3 and d["qkv_out_dim"] == 3072 and d["num_heads"] == 48
+    LlamaConfig.update_from_dict({"num_hidden_layers": 1, "hidden_size": 2048, "intermediate_size": 8192,
+                                  "num_attention_heads": 32, "vocab_size": 10,
+                                  "rope_scaling": {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                                   "original_max_position_embeddings": 8192}})
+    assert LlamaConfig.head_dim == 64 and LlamaConfig.num_key_value_heads == 32
+    assert LlamaConfig.rope_scaling == (8.0, 1.0, 4.0, 8192)
+    LlamaConfig.update_from_dict(LLAMA_3_2_1B)
+
+
+def test_rope_tables_layout_and_llama3_scaling():
+    from qimeng_megakernel_b200.rope import inv_frequencies, rope_tables_interleaved
+    cos, sin = rope_tables_interleaved(64, 32, 500000.0, (32.0, 1.0, 4.0, 8192))
+    assert cos.shape == (32, 64) and cos.dtype == torch.float32
+    assert torch.equal(cos[:, 0::2], cos[:, 1::2]) and torch.equal(sin[:, 0::2], sin[:, 1::2])   # pairs share a frequency
+    assert torch.allclose(cos[0], torch.ones(64)) and torch.allclose(sin[0], torch.zeros(64))
+    plain = inv_frequencies(64, 500000.0)
+    scaled = inv_frequencies(64, 500000.0, (32.0, 1.0, 4.0, 8192))
+    wavelen = 2 * math.pi / plain
+    assert torch.allclose(scaled[wavelen < 8192 / 4], plain[wavelen < 8192 / 4])            # high frequencies untouched
+    assert torch.allclose(scaled[wavelen > 8192], plain[wavelen > 8192] / 32.0)             # low frequencies / factor
+    mid = (wavelen >= 8192 / 4) & (wavelen <= 8192)
+    assert bool(((scaled[mid] <= plain[mid]) & (scaled[mid] >= plain[mid] / 32.0)).all())
+    # against the transformers implementation, when it is importable
+    try:
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        from transformers import LlamaConfig as HFLlamaConfig
+        hf = HFLlamaConfig(hidden_size=2048, num_attention_heads=32, rope_theta=500000.0, max_position_embeddings=131072,
+                           rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})
+        inv, _ = ROPE_INIT_FUNCTIONS["llama3"](hf, "cpu")
+        assert torch.allclose(inv.float(), scaled, rtol=1e-5, atol=1e-9)
+    except Exception as e:                                   # API differences between transformers versions
+        pytest.skip(f"transformers llama3 rope not comparable here: {e}")
+
+
+def test_synthetic_model_is_seeded_and_tied(small_config):
+    from qimeng_megakernel_b200 import synthetic
+    a = synthetic.make_weights(small_config, seed=5)
+    b = synthetic.make_weights(small_config, seed=5)
+    c = synthetic.make_weights(small_config, seed=6)
+    assert torch.equal(a["qkv_weights"], b["qkv_weights"]) and not torch.equal(a["qkv_weights"], c["qkv_weights"])
+    assert a["embed_tokens"].data_ptr() == a["lm_head_weights"].data_ptr()
+    assert abs(float(a["up_proj_weights"].float().std()) - 0.02) < 1e-3
+    assert bool((a["attn_norm_weights"] == 1).all())
+    p = synthetic.make_prompt(small_config["vocab_size"], 16, seed=1)
+    assert p.shape == (16,) and int(p.max()) < small_config["vocab_size"] and torch.equal(p, synthetic.make_prompt(small_config["vocab_size"], 16, 1))
+
+
+def test_kernel_wrapper_rejects_cpu_tensors(small_config, small_weights):
+    """There is no CPU fallback: CPU tensors are refused before anything is launched."""
+    from qimeng_megakernel_b200 import mk_kernel, synthetic
+    g = synthetic.make_globals(small_config, small_weights, kv_seq_len=8, device="cpu")
+    mk = mk_kernel.get_mk()
+    with pytest.raises(ValueError, match="no CPU path"):
+        mk(g)
+
+
+def test_decode_rejects_other_routes():
+    from qimeng_megakernel_b200.decode import decode
+    from qimeng_megakernel_b200.prefill import PrefillOutput
+    pre = PrefillOutput(input_ids=torch.zeros(1, 4, dtype=torch.int64), first_gen_token=torch.zeros(1, 1, dtype=torch.int64),
+                        logits=torch.zeros(1, 8))
+    with pytest.raises(NotImplementedError):
+        decode("llama-3.2-1b", prefill=pre, max_new_tokens=4, decode_route="fused")
+    with pytest.raises(NotImplementedError):
+        decode("llama-3.2-1b", prefill=pre, max_new_tokens=4, temperature=0.7)
+    out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=0)
+    assert out["new_tokens"].shape == (1, 0)
+
+
+def test_two_rank_sharding_and_max_over_ranks(tmp_path):
+    """The multi-GPU bench shards sequences over ranks without a data-path collective and reports the
+    maximum time over ranks: exercised with two gloo ranks on the CPU."""
+    script = tmp_path / "rank.py"
+    script.write_text(textwrap.dedent(f"""
+        import os, sys, torch, torch.distributed as dist
+        sys.path.insert(0, {ROOT!r})
+        from qimeng_megakernel_b200 import synthetic
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        prompt = synthetic.make_prompt(128256, 16, seed=1 + rank)          # bench.py: independent prompt per rank
+        gathered = [torch.zeros(16, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(gathered, prompt)
+        assert not torch.equal(gathered[0], gathered[1])
+        t = torch.tensor([1.0 + rank], dtype=torch.float64)               # rank 1 is slower
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        K = 100
+        value = world * K / float(t)
+        if rank == 0:
+            print("VALUE", value)
+        dist.barrier(); dist.destroy_process_group()
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29613")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29613", str(script)],
+                         capture_output=True, text=True, env=env, timeout=240)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "VALUE 100.0" in out.stdout
