@@ -10,11 +10,11 @@
 //    not depend on the step, so their HBM latency hides behind the QKV phase's tail;
 //  * this step's own K / V row never goes through the cache on the critical path: it is staged from
 //    the tagged scratch next to q;
+//  * a compute unit is one kv head x one block of keys; the heads of its GQA group are processed by a
+//    rolled loop whose per-head state rotates through fixed registers (code emitted once, not per head);
 //  * partials are written as self-validating records (every 64-bit word = {fp32 value, 32-bit tag}),
-//    and the units (kv head, part < GQA) merge one head each by polling those records: no fence,
-//    no atomic, no separate reduction phase;
-//  * the heads of a GQA group are processed by a rolled loop whose per-head state rotates through
-//    fixed registers, so the code is emitted once instead of once per head.
+//    and one merge unit per head, on an otherwise idle warp, polls those records from the start of the
+//    phase: no atomic, no separate reduction phase, and no fence in front of the merge.
 #pragma once
 
 namespace qmk {
@@ -148,6 +148,7 @@ __device__ __forceinline__ unsigned long long* part_record(const Params& p, int 
   return p.part_rec + ((size_t)head * kMaxSplits + part) * (S::HD + 2);
 }
 
+// ---- compute unit: one kv head (all query heads of its group) x one range of keys --------------
 template <class S>
 __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kvh,
                                           int part, int bps, int P, bool staged_kv, unsigned tagw, KvBlock<S>& blk,
@@ -222,14 +223,14 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigne
       const int e = (kvh * GQA + h) * HD + s.lane * DPL;
       const uint32_t w0 = pack_bf16x2(acc0[h] * inv, acc1[h] * inv);
       *reinterpret_cast<uint32_t*>(p.attn_out + e) = w0;
-      if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e) = make_uint2((w0 & 0xffffu) | tagw, (w0 >> 16) | tagw);
+      if (p.sync) st_handoff(p.t_attn + e, make_uint2((w0 & 0xffffu) | tagw, (w0 >> 16) | tagw));
       if (DPL == 4) {
         const uint32_t w1 = pack_bf16x2(acc2[h] * inv, acc3[h] * inv);
         *reinterpret_cast<uint32_t*>(p.attn_out + e + 2) = w1;
-        if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e + 2) = make_uint2((w1 & 0xffffu) | tagw, (w1 >> 16) | tagw);
+        if (p.sync) st_handoff(p.t_attn + e + 2, make_uint2((w1 & 0xffffu) | tagw, (w1 >> 16) | tagw));
       }
     }
-    __threadfence();   // push the tagged stores out (see phase_stream)
+    flush_handoff();
     return;
   }
 
@@ -239,89 +240,96 @@ __device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigne
   for (int h = 0; h < GQA; ++h) {
     unsigned long long* rec = part_record<S>(p, kvh * GQA + h, part);
     uint4* dst = reinterpret_cast<uint4*>(rec + s.lane * DPL);
-    dst[0] = make_uint4(__float_as_uint(acc0[h]), rtag, __float_as_uint(acc1[h]), rtag);
-    if (DPL == 4) dst[1] = make_uint4(__float_as_uint(acc2[h]), rtag, __float_as_uint(acc3[h]), rtag);
+    st_handoff(dst, make_uint4(__float_as_uint(acc0[h]), rtag, __float_as_uint(acc1[h]), rtag));
+    if (DPL == 4) st_handoff(dst + 1, make_uint4(__float_as_uint(acc2[h]), rtag, __float_as_uint(acc3[h]), rtag));
     if (s.lane == 0)
-      *reinterpret_cast<uint4*>(rec + HD) = make_uint4(__float_as_uint(m[h]), rtag, __float_as_uint(l[h]), rtag);
+      st_handoff(rec + HD, make_uint4(__float_as_uint(m[h]), rtag, __float_as_uint(l[h]), rtag));
   }
 
-  __threadfence();     // push the record out (see phase_stream)
-
-  // ---- merge: unit `part` merges the heads h = part, part + nm, ... of its group (nm = min(P, GQA))
-  const int nm = P < GQA ? P : GQA;
-  if (part >= nm) return;
-#pragma unroll 1
-  for (int h = part; h < GQA; h += nm) {
-    const int head = kvh * GQA + h;
-    float M = -INFINITY, den = 0.f, num[DPL];
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) num[d] = 0.f;
-#pragma unroll 1
-    for (int q0 = 0; q0 < P; q0 += 4) {
-      uint4 ta[4][DPL / 2], tm[4];
-      const long long t0 = clock64();
-      for (unsigned it = 0;; ++it) {
-        bool ok = true;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int q = (q0 + j) < P ? (q0 + j) : (P - 1);
-          const unsigned long long* rec = part_record<S>(p, head, q);
-          tm[j] = ldcg_u4(rec + HD);
-          ok = ok && tm[j].y == rtag && tm[j].w == rtag;
-#pragma unroll
-          for (int d2 = 0; d2 < DPL / 2; ++d2) {
-            ta[j][d2] = ldcg_u4(rec + s.lane * DPL + 2 * d2);
-            ok = ok && ta[j][d2].y == rtag && ta[j][d2].w == rtag;
-          }
-        }
-        if (__all_sync(kFullMask, ok)) break;
-        if ((it & 15u) == 15u && poll_give_up(p, t0, ok, tm[0].y, rtag, s.w, ph, s.lane)) {
-          s.aborted = true;
-          return;
-        }
-        poll_backoff(it);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (q0 + j < P) {
-          const float mq = __uint_as_float(tm[j].x), lq = __uint_as_float(tm[j].z);
-          const float M_new = fmaxf(M, mq);
-          const float corr = exp2f(M - M_new), wq = exp2f(mq - M_new);
-          den = den * corr + wq * lq;
-#pragma unroll
-          for (int d2 = 0; d2 < DPL / 2; ++d2) {
-            num[2 * d2] = fmaf(wq, __uint_as_float(ta[j][d2].x), num[2 * d2] * corr);
-            num[2 * d2 + 1] = fmaf(wq, __uint_as_float(ta[j][d2].z), num[2 * d2 + 1] * corr);
-          }
-          M = M_new;
-        }
-      }
-    }
-    const float inv = 1.0f / den;
-    const int e = head * HD + s.lane * DPL;
-#pragma unroll
-    for (int d = 0; d < DPL; d += 2) {
-      const uint32_t w = pack_bf16x2(num[d] * inv, num[d + 1] * inv);
-      *reinterpret_cast<uint32_t*>(p.attn_out + e + d) = w;
-      if (p.sync) *reinterpret_cast<uint2*>(p.t_attn + e + d) = make_uint2((w & 0xffffu) | tagw, (w >> 16) | tagw);
-    }
-  }
-  __threadfence();
+  flush_handoff();     // push the records out
 }
 
-// ---- phase 1: attention.  Units (kv head, partial) are dealt round-robin over SMs first.
+
+
+// ---- merge unit: one query head; polls the P partial records of that head (eight at a time, all
+// loads in flight together), merges them with a running maximum and writes attn_out.
+template <class S>
+__device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph, int head, int P, unsigned tagw) {
+  constexpr int HD = S::HD, DPL = KvBlock<S>::DPL;
+  constexpr int kBatch = 8;
+  const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
+  float M = -INFINITY, den = 0.f, num[DPL];
+#pragma unroll
+  for (int d = 0; d < DPL; ++d) num[d] = 0.f;
+#pragma unroll 1
+  for (int q0 = 0; q0 < P; q0 += kBatch) {
+    uint4 ta[kBatch][DPL / 2], tm[kBatch];
+    const long long t0 = clock64();
+    for (unsigned it = 0;; ++it) {
+      bool ok = true;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int q = (q0 + j) < P ? (q0 + j) : (P - 1);
+        const unsigned long long* rec = part_record<S>(p, head, q);
+        tm[j] = ldcg_u4(rec + HD);
+        ok = ok && tm[j].y == rtag && tm[j].w == rtag;
+#pragma unroll
+        for (int d2 = 0; d2 < DPL / 2; ++d2) {
+          ta[j][d2] = ldcg_u4(rec + s.lane * DPL + 2 * d2);
+          ok = ok && ta[j][d2].y == rtag && ta[j][d2].w == rtag;
+        }
+      }
+      if (__all_sync(kFullMask, ok)) break;
+      if ((it & 15u) == 15u && poll_give_up(p, t0, ok, tm[0].y, rtag, s.w, ph, s.lane)) {
+        s.aborted = true;
+        return;
+      }
+      poll_backoff(it);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (q0 + j < P) {
+        const float mq = __uint_as_float(tm[j].x), lq = __uint_as_float(tm[j].z);
+        const float M_new = fmaxf(M, mq);
+        const float corr = exp2f(M - M_new), wq = exp2f(mq - M_new);
+        den = den * corr + wq * lq;
+#pragma unroll
+        for (int d2 = 0; d2 < DPL / 2; ++d2) {
+          num[2 * d2] = fmaf(wq, __uint_as_float(ta[j][d2].x), num[2 * d2] * corr);
+          num[2 * d2 + 1] = fmaf(wq, __uint_as_float(ta[j][d2].z), num[2 * d2 + 1] * corr);
+        }
+        M = M_new;
+      }
+    }
+  }
+  const float inv = 1.0f / den;
+  const int e = head * HD + s.lane * DPL;
+#pragma unroll
+  for (int d = 0; d < DPL; d += 2) {
+    const uint32_t w = pack_bf16x2(num[d] * inv, num[d + 1] * inv);
+    *reinterpret_cast<uint32_t*>(p.attn_out + e + d) = w;
+    if (p.sync) st_handoff(p.t_attn + e + d, make_uint2((w & 0xffffu) | tagw, (w >> 16) | tagw));
+  }
+  flush_handoff();
+}
+
+// ---- phase 1: attention.  Compute units (kv head, part) come first, then (when P > 1) one merge unit per
+// head; units are dealt round-robin over SMs first, so a merge unit usually lands on a warp that has
+// nothing else to do and polls from the start of the phase.  In any warp's own sequence the merge unit
+// is the last one, so it never waits for work queued behind it.
 template <class S>
 __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
   int bps, P;
   attn_plan(p.pos + 1, bps, P);
-  const int n_units = S::NKV * P;
+  const int n_compute = S::NKV * P;
+  const int n_units = n_compute + (P > 1 ? S::NH : 0);
   if ((int)blockIdx.x >= n_units) return;          // no unit lands on this CTA: nothing to stage
   const bool tagged = p.sync && (ph > p.phase_begin || p.wait_first);
   const long long tq0 = clock64();
   const int first = s.w * (int)gridDim.x + (int)blockIdx.x;
   const bool has_unit = first < n_units && !s.aborted;
   KvBlock<S> blk;
-  if (has_unit) {   // old keys do not depend on this step: fetch the first block before waiting for q
+  if (has_unit && first < n_compute) {   // old keys do not depend on this step: fetch them before waiting for q
     const int part = first % P, k0 = part * bps * kAttnBlockKeys;
     int k1 = k0 + bps * kAttnBlockKeys;
     if (k1 > p.pos + 1) k1 = p.pos + 1;
@@ -331,15 +339,19 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   cta_sync(s, smem);
   if (s.cta_abort) return;
   const long long tq1 = clock64();
+  if (s.w == 0) trace_put(p, ph, 0, globaltimer_ns(), s.lane);
   if (has_unit) {
     const unsigned tagw = phase_tag(p, ph) << 16;
-    for (int u = first; u < n_units && !s.aborted; u += s.nwt)
-      attn_unit(s, p, smem, ph, u / P, u % P, bps, P, tagged, tagw, blk, u == first);
+    for (int u = first; u < n_units && !s.aborted; u += s.nwt) {
+      if (u < n_compute) attn_unit(s, p, smem, ph, u / P, u % P, bps, P, tagged, tagw, blk, u == first);
+      else attn_merge(s, p, ph, u - n_compute, P, tagw);
+    }
     if (s.aborted) flag_abort(s, smem);
   }
   if (s.w == 0) {
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
     trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
+    trace_put(p, ph, 7, globaltimer_ns(), s.lane);
   }
 }
 

@@ -86,6 +86,57 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+// ---- stores of hand-off words (tagged activations, split-KV records): straight to L2 ----
+#ifndef QMK_ST_MODE
+#define QMK_ST_MODE 0
+#endif
+__device__ __forceinline__ void st_handoff(uint32_t* p, uint32_t v) {
+#if QMK_ST_MODE == 1
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+#elif QMK_ST_MODE == 2
+  asm volatile("st.global.cg.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+#else
+  *p = v;
+#endif
+}
+__device__ __forceinline__ void st_handoff(uint32_t* p, uint2 v) {
+#if QMK_ST_MODE == 1
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+#elif QMK_ST_MODE == 2
+  asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+#else
+  *reinterpret_cast<uint2*>(p) = v;
+#endif
+}
+__device__ __forceinline__ void st_handoff(void* p, uint4 v) {
+#if QMK_ST_MODE == 1
+  asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#elif QMK_ST_MODE == 2
+  asm volatile("st.global.cg.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#else
+  *reinterpret_cast<uint4*>(p) = v;
+#endif
+}
+#ifndef QMK_FENCE
+#define QMK_FENCE 1
+#endif
+// Push this warp's hand-off stores out (nothing waits for it).
+__device__ __forceinline__ void flush_handoff() {
+#if QMK_FENCE == 1
+  __threadfence();
+#elif QMK_FENCE == 2
+  __threadfence_block();
+#elif QMK_FENCE == 3
+  __threadfence();
+  __nanosleep(500);
+#elif QMK_FENCE == 4
+  __threadfence();
+  __threadfence();
+#elif QMK_FENCE == 5
+  __threadfence_system();
+#endif
+}
+
 // ---- L2-coherent loads (activations written by other SMs inside the same launch) ----
 __device__ __forceinline__ uint4 ldcg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ unsigned ldcg_u32(const void* p) { return __ldcg(reinterpret_cast<const unsigned*>(p)); }

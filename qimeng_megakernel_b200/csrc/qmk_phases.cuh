@@ -62,7 +62,7 @@ __device__ __forceinline__ void epilogue_qkv(const Params& p, const unsigned cha
     tdst = p.t_q + S::QDIM + S::NKV * S::HD + (row - vStart);
   }
   *reinterpret_cast<uint32_t*>(dst) = packed;
-  if (p.sync) *reinterpret_cast<uint2*>(tdst) = make_uint2((packed & 0xffffu) | tagw, (packed >> 16) | tagw);
+  if (p.sync) st_handoff(tdst, make_uint2((packed & 0xffffu) | tagw, (packed >> 16) | tagw));
 }
 
 // SwiGLU item = (up row u, gate row u).  fused_mlp_upgate (operations.py:265-282): up and gate rounded
@@ -192,7 +192,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
           case kUpGate: {
             const unsigned short bits = epilogue_silu(va, vb);
             p.silu_out[item] = bits;
-            if (p.sync) p.t_silu[item] = bits | tagw;
+            if (p.sync) st_handoff(p.t_silu + item, (uint32_t)bits | tagw);
             break;
           }
           case kLmHead: {
@@ -205,7 +205,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
           default: {
             const unsigned short bits = f32_to_bf16_bits(old + bf16_round(va));
             p.hidden[item] = bits;
-            if (p.sync) tres[item] = bits | tagw;
+            if (p.sync) st_handoff(tres + item, (uint32_t)bits | tagw);
             if (ib == i0) s.res = bf16_bits_to_f32(bits);
             break;
           }
@@ -217,7 +217,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   // Push this warp's tagged stores out now.  Nothing waits for the fence itself (the warp would only
   // start polling for the next phase), but without it the stores linger behind the polling loads and
   // every consumer sees them about a microsecond later (measured: 16 % of the whole step).
-  __threadfence();
+  flush_handoff();
   if (s.w == 0) {
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
     trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
