@@ -41,7 +41,8 @@ enum qmk_error {
   QMK_ERR_NOT_BOUND = -5,        /* decode called before qmk_bind_state                   */
   QMK_ERR_POSITION = -6,         /* pos_id outside the bound KV cache or RoPE table       */
   QMK_ERR_DEVICE_TIMEOUT = -7,   /* a bounded device-side wait expired (see qmk_status)   */
-  QMK_ERR_OOM = -8               /* scratch allocation failed                             */
+  QMK_ERR_OOM = -8,              /* scratch allocation failed                             */
+  QMK_ERR_SCRATCH_TOO_LARGE = -9 /* qmk_decode_step_static: the model needs more than the fixed scratch array */
 };
 
 /* Architecture families (selects epilogue variants). */
@@ -206,6 +207,21 @@ int64_t qmk_launch_count(const qmk_handle* h);
 
 /* Launch geometry actually used: CTAs (= SMs), threads per CTA, dynamic shared memory bytes. */
 int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes);
+
+/* No counterpart in the reference.  One decode step for callers that must not allocate device memory
+ * (a serving loop whose memory belongs to a framework's pool allocator, an embedder with a fixed memory
+ * budget, code running where an allocation would synchronise the device): same kernel as qmk_decode_step,
+ * but the library's scratch (hand-off words, split-KV records, status) lives in a file-scope __device__
+ * array of QMK_STATIC_SCRATCH_MAX_BYTES inside the library image instead of a cudaMalloc'ed block, and
+ * there is no handle: descriptor, weights and state are passed on every call.  Calls no cudaMalloc /
+ * cudaFree / allocating routine.  Every GPU that loads the library holds the array until exit.  All calls
+ * on a device share it: run them on one stream, one after the other (overlapping calls race); what must
+ * start at zero is cleared by each call.  The first call on a device does the set-up (symbol address,
+ * kernel attribute): make it outside any stream capture.  A model whose scratch would not fit returns
+ * QMK_ERR_SCRATCH_TOO_LARGE.  Asynchronous on `cuda_stream`; not thread-safe. */
+#define QMK_STATIC_SCRATCH_MAX_BYTES (2u << 20)
+int qmk_decode_step_static(const qmk_model_desc* desc, const qmk_weight_ptrs* weights, const qmk_state_ptrs* state,
+                           int32_t pos_id, int device, void* cuda_stream);
 
 void qmk_destroy(qmk_handle* h);
 const char* qmk_strerror(int code);

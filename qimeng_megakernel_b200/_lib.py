@@ -17,6 +17,8 @@ PHASES_PER_LAYER = 5
 PHASE_QKV, PHASE_ATTN, PHASE_OPROJ, PHASE_UPGATE, PHASE_DOWN = range(5)
 
 ERR_DEVICE_TIMEOUT = -7
+ERR_SCRATCH_TOO_LARGE = -9
+STATIC_SCRATCH_MAX_BYTES = 2 << 20
 
 
 class ModelDesc(C.Structure):
@@ -61,6 +63,8 @@ SYMBOLS = [
     ("qmk_launch_count", C.c_int64, [C.c_void_p]),
     ("qmk_launch_geometry", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                       C.POINTER(C.c_int32)]),
+    ("qmk_decode_step_static", C.c_int, [C.POINTER(ModelDesc), C.POINTER(WeightPtrs), C.POINTER(StatePtrs), C.c_int32,
+                                         C.c_int, C.c_void_p]),
     ("qmk_destroy", None, [C.c_void_p]),
     ("qmk_strerror", C.c_char_p, [C.c_int]),
     ("qmk_last_cuda_error", C.c_char_p, [C.c_void_p]),

@@ -72,6 +72,7 @@ extern "C" const char* qmk_strerror(int code) {
     case QMK_ERR_POSITION: return "position outside the bound KV cache or RoPE table";
     case QMK_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
     case QMK_ERR_OOM: return "scratch allocation failed";
+    case QMK_ERR_SCRATCH_TOO_LARGE: return "model needs more scratch than the fixed array of qmk_decode_step_static";
     default: return "unknown error";
   }
 }

@@ -60,7 +60,7 @@ struct SmemLayout {
 //   [16..23] sum-of-squares partials, buffer A     [24..31] buffer B
 constexpr int kCtlAbort = 0, kCtlLmArrive = 8, kCtlKey = 10, kCtlSumSq = 16;
 
-__device__ __noinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
+static __device__ __noinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
                                           unsigned expected, int detail) {
   if (atomicCAS(&p.status[kStCode], 0u, (unsigned)code) == 0u) {
     p.status[kStSm] = blockIdx.x;
@@ -127,7 +127,7 @@ __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
 
 // Bounded wait on one ring slot.  Returns false (and flags the error) on expiry.  The spin with its
 // deadline is a separate, non-inlined function: it runs only when the data is not there yet.
-__device__ __noinline__ bool wait_slot_slow(const Params& p, uint32_t bar, uint32_t parity, int warp, int phase,
+static __device__ __noinline__ bool wait_slot_slow(const Params& p, uint32_t bar, uint32_t parity, int warp, int phase,
                                             unsigned acquired, unsigned issued, int slot, int lane) {
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {

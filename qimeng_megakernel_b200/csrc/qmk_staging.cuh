@@ -16,7 +16,7 @@ __device__ __forceinline__ bool tags_ok(const uint4& v, unsigned tagw) {
 
 // Non-inlined tail of a tagged poll: checks the deadline and the global status word.
 // Returns true when the poll must give up.
-__device__ __noinline__ bool poll_give_up(const Params& p, long long t0, bool ok, unsigned seen_tag, unsigned tag,
+static __device__ __noinline__ bool poll_give_up(const Params& p, long long t0, bool ok, unsigned seen_tag, unsigned tag,
                                           int warp, int ph, int lane) {
   const bool expired = clock64() - t0 > p.timeout_cycles;
   const unsigned st = ld_relaxed_gpu(p.status + kStCode);
