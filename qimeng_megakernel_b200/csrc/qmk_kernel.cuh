@@ -100,6 +100,7 @@ struct Worker {
   unsigned i_slot;         // slot the next issue goes into
   unsigned c_slot, c_par;  // slot and mbarrier parity of the next tile to consume
   TileCursor<S> cur;       // where the weight stream is; also holds this worker's item ranges
+  TileCursor<S> pf;        // the same stream, kL2Ahead tiles further: what is being pulled into L2
   StreamBases wb;
   float res;               // residual stream value of row (cur.r0 + lane), bf16-exact
   bool res_valid;
@@ -107,6 +108,26 @@ struct Worker {
   bool cta_abort;          // the whole CTA leaves the phase loop
   uint64_t policy;
 };
+
+// Optional far look-ahead (off by default).  The shared-memory ring holds 24 KiB per warp; while a warp
+// waits for activations at a phase boundary the ring is full and HBM idles.  With QMK_L2_AHEAD = n the
+// stream is also run n tiles further ahead with cp.async.bulk.prefetch.L2.  Measured on B200: n = 3 changes
+// nothing (592 us per step either way, the up/gate phase does not get shorter), n >= 6 (57 MB ahead) is
+// slower, so the prefetched lines evidently do not survive in L2 until the ring asks for them.
+#ifndef QMK_L2_AHEAD
+#define QMK_L2_AHEAD 0
+#endif
+constexpr int kL2Ahead = QMK_L2_AHEAD;
+
+template <class S>
+__device__ __forceinline__ void prefetch_one(Worker<S>& s, const Params& p) {
+  if (kL2Ahead <= 0 || s.pf.done(p.phase_end)) return;
+  const Tile t = s.pf.next(s.wb, p.num_layers, p.phase_end);
+  if (s.lane == 0) {
+    bulk_prefetch_l2(t.a, t.bytes_a);
+    if (t.b != nullptr) bulk_prefetch_l2(t.b, kChunkBytes);
+  }
+}
 
 // Issue the next tile of the stream into the oldest free slot, if any tile is left: one 8-KiB bulk
 // copy, or two 4-KiB copies completing on the same mbarrier.
@@ -123,6 +144,7 @@ __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
   }
   ++s.n_issued;
   s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
+  prefetch_one(s, p);
 }
 
 // Bounded wait on one ring slot.  Returns false (and flags the error) on expiry.  The spin with its

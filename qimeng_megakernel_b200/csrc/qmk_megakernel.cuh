@@ -30,6 +30,11 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.wb.lm_head = reinterpret_cast<const unsigned char*>(p.lm_head);
   s.cur.init(s.g, s.nwt, p.vocab, p.phase_begin);
   s.cur.seek(s.wb, p.num_layers, p.phase_end);
+  s.pf = s.cur;
+  if (kL2Ahead > 0) {   // run the look-ahead cursor kSlots + kL2Ahead tiles in front
+#pragma unroll 1
+    for (int i = 0; i < kSlots + kL2Ahead; ++i) prefetch_one(s, p);
+  }
 #pragma unroll 1
   for (int i = 0; i < kSlots; ++i) issue_one(s, p);
 
