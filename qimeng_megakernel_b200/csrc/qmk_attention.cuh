@@ -29,8 +29,9 @@ __device__ __forceinline__ void rotate(float (&a)[N]) {
 
 // Stage this warp's part of q (fp32) and of the new K / V rows (bf16) into the big activation buffer.
 template <class S>
-__device__ __forceinline__ bool stage_attn_part(const Params& p, unsigned char* smem, bool tagged, unsigned tag,
-                                                int warp, int lane, int ph) {
+__device__ __forceinline__ bool stage_attn_part(Worker<S>& s, const Params& p, unsigned char* smem, bool tagged,
+                                                unsigned tag, int ph) {
+  const int warp = s.w, lane = s.lane;
   using L = SmemLayout<S>;
   constexpr int kQPart = S::QDIM / kWorkers;                 // q elements per warp
   constexpr int kKvPart = 2 * S::NKV * S::HD / kWorkers;     // new K+V elements per warp
@@ -59,7 +60,7 @@ __device__ __forceinline__ bool stage_attn_part(const Params& p, unsigned char* 
       }
       if (__all_sync(kFullMask, ok)) break;
       if ((it & 15u) == 15u && poll_give_up(p, t0, ok, vq[0].x >> 16, tag, warp, ph, lane)) return false;
-      poll_backoff(it);
+      poll_backoff(s, p, it);
     }
 #pragma unroll
     for (int j = 0; j < NQ; ++j) {
@@ -284,7 +285,7 @@ __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph
         s.aborted = true;
         return;
       }
-      poll_backoff(it);
+      poll_pause(it);
     }
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
@@ -335,7 +336,7 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
     if (k1 > p.pos + 1) k1 = p.pos + 1;
     load_kv_block(blk, p, phase_layer(ph), first / P, k0, k1, s.lane);
   }
-  if (!s.aborted && !stage_attn_part<S>(p, smem, tagged, phase_tag(p, ph - 1), s.w, s.lane, ph)) flag_abort(s, smem);
+  if (!s.aborted && !stage_attn_part<S>(s, p, smem, tagged, phase_tag(p, ph - 1), ph)) flag_abort(s, smem);
   cta_sync(s, smem);
   if (s.cta_abort) return;
   const long long tq1 = clock64();

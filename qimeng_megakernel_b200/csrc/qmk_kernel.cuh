@@ -58,7 +58,7 @@ struct SmemLayout {
 // control block, 32-bit words from kOffCtl:
 //   [0] abort word (non-zero: a warp of this CTA gave up)   [8] lm_arrive   [10..11] CTA arg-max key (u64)
 //   [16..23] sum-of-squares partials, buffer A     [24..31] buffer B
-constexpr int kCtlAbort = 0, kCtlLmArrive = 8, kCtlKey = 10, kCtlSumSq = 16;
+constexpr int kCtlAbort = 0, kCtlTmem = 4, kCtlLmArrive = 8, kCtlKey = 10, kCtlSumSq = 16;
 
 static __device__ __noinline__ void report_error(const Params& p, int code, int warp, int phase, unsigned seen,
                                           unsigned expected, int detail) {
@@ -101,6 +101,8 @@ struct Worker {
   unsigned c_slot, c_par;  // slot and mbarrier parity of the next tile to consume
   TileCursor<S> cur;       // where the weight stream is; also holds this worker's item ranges
   TileCursor<S> pf;        // the same stream, kL2Ahead tiles further: what is being pulled into L2
+  uint32_t tmem;           // tensor-memory address of this warp's parking space (its lane quarter, its column half)
+  unsigned t_head, t_count;   // oldest parked tile and number of parked tiles (FIFO, all older than the ring's tiles)
   StreamBases wb;
   float res;               // residual stream value of row (cur.r0 + lane), bf16-exact
   bool res_valid;
@@ -134,13 +136,22 @@ __device__ __forceinline__ void prefetch_one(Worker<S>& s, const Params& p) {
 template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
   if (s.aborted || s.cur.done(p.phase_end)) return;
-  const Tile t = s.cur.next(s.wb, p.num_layers, p.phase_end);
+  Tile t = s.cur.next(s.wb, p.num_layers, p.phase_end);
+#ifdef QMK_PROBE_L2_WINDOW   // measurement only (wrong results): every tile comes from one L2-resident window
+  t.a = s.wb.lm_head + ((size_t)(t.a - (const unsigned char*)nullptr) & (size_t)(QMK_PROBE_L2_WINDOW - 1));
+  if (t.b != nullptr) t.b = s.wb.lm_head + ((size_t)(t.b - (const unsigned char*)nullptr) & (size_t)(QMK_PROBE_L2_WINDOW - 1));
+#endif
   if (s.lane == 0) {
     const uint32_t bar = s.bars + s.i_slot * 8;
     const uint32_t dst = s.ring + s.i_slot * (2 * kChunkBytes);
+#ifdef QMK_PROBE_NO_COPY   // measurement only (wrong results): no weight traffic at all, the slot is "there" at once
+    mbar_expect_tx(bar, 0u);
+    (void)dst;
+#else
     mbar_expect_tx(bar, t.bytes_a + (t.b != nullptr ? (uint32_t)kChunkBytes : 0u));
     bulk_g2s(dst, t.a, t.bytes_a, bar, s.policy);
     if (t.b != nullptr) bulk_g2s(dst + kChunkBytes, t.b, kChunkBytes, bar, s.policy);
+#endif
   }
   ++s.n_issued;
   s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
@@ -234,9 +245,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 // Accumulate the 16x8 product of two chunks (shared addresses slot0 / slot1) into cc.
 __device__ __forceinline__ void mma_chunk_pair(float (&cc)[4], uint32_t slot0, uint32_t slot1, const XFrag& xf,
                                                int lane) {
-  // ldmatrix row address of this lane: matrices 0/2 come from chunk 0, 1/3 from chunk 1;
-  // matrices 2/3 are the second piece (k 8..15) of the k-step.
-  const uint32_t addr = ((lane & 8) ? slot1 : slot0) + ((((lane >> 4) << 3) + (lane & 7)) << 4);
+  const uint32_t addr = ((lane & 8) ? slot1 : slot0) + ((((lane >> 4) << 3) + (lane & 7)) << 4);   // = ldmatrix_lane_addr
   float c[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -261,6 +270,164 @@ __device__ __forceinline__ void diag_reduce(const float (&cc)[4], int lane, floa
   for (int o = 16; o > 0; o >>= 1) {
     s0 += __shfl_xor_sync(kFullMask, s0, o);
     s1 += __shfl_xor_sync(kFullMask, s1, o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor-memory parking.  The ring holds 24 KiB per warp, i.e. all rings together hold about 4 us of
+// HBM streaming; whenever the workers wait for activations longer than that (the attention chain
+// between QKV and the O-projection takes about 10 us) the rings are full and HBM idles.  The
+// tensor memory of the SM (256 KiB, unused by mma.sync) more than doubles the depth: a warp that
+// is polling moves landed tiles from its ring into its TMEM share (32 lanes x 256 columns = 4 tiles)
+// and refills the freed slots, so the weight stream keeps running through the wait.  A tile is parked
+// as the very registers ldmatrix produces for the product (tcgen05.st) and comes back with
+// tcgen05.ld, so the product is bit-identical whichever way a tile took.  Parked tiles are older
+// than every tile in the ring: consume them first.
+// ------------------------------------------------------------------------------------------
+#ifndef QMK_TMEM_SLOTS
+#define QMK_TMEM_SLOTS 4
+#endif
+constexpr int kTSlots = QMK_TMEM_SLOTS;
+constexpr int kTileCols = 2 * kChunkBytes / (32 * 4);   // 32-bit columns one tile takes in a 32-lane quarter
+static_assert(kTSlots * kTileCols * (kWorkers / 4) <= 512, "parking space exceeds the tensor memory");
+
+// A tile moves to and from tensor memory in pieces of kPieceSteps k-steps (4 registers per k-step).
+#ifndef QMK_TMEM_PIECE_STEPS
+#define QMK_TMEM_PIECE_STEPS 2
+#endif
+constexpr int kPieceSteps = QMK_TMEM_PIECE_STEPS;
+__device__ __forceinline__ void tmem_st_piece(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
+__device__ __forceinline__ void tmem_st_piece(uint32_t taddr, const uint32_t (&r)[8]) { tmem_st8(taddr, r); }
+__device__ __forceinline__ void tmem_ld_piece(uint32_t (&r)[16], uint32_t taddr) { tmem_ld16(r, taddr); }
+__device__ __forceinline__ void tmem_ld_piece(uint32_t (&r)[8], uint32_t taddr) { tmem_ld8(r, taddr); }
+
+__device__ __forceinline__ uint32_t ldmatrix_lane_addr(uint32_t slot0, uint32_t slot1, int lane) {
+  // matrices 0/2 come from chunk 0, 1/3 from chunk 1; matrices 2/3 are the second piece (k 8..15) of the k-step.
+  return ((lane & 8) ? slot1 : slot0) + ((((lane >> 4) << 3) + (lane & 7)) << 4);
+}
+
+// Move the oldest landed tile of the ring into tensor memory, if there is one and room for it.
+template <class S>
+__device__ __forceinline__ void park_one(Worker<S>& s, const Params& p) {
+  if (kTSlots == 0 || s.aborted || s.t_count == (unsigned)kTSlots || s.n_acquired == s.n_issued) return;
+  const unsigned slot = s.c_slot;
+  if (!mbar_try_wait(s.bars + slot * 8, s.c_par)) return;
+  const uint32_t src = s.ring + slot * (2 * kChunkBytes);
+  const uint32_t addr = ldmatrix_lane_addr(src, src + kChunkBytes, s.lane);
+  unsigned tail = s.t_head + s.t_count;
+  if (tail >= (unsigned)kTSlots) tail -= kTSlots;
+  const uint32_t dst = s.tmem + tail * kTileCols;
+#pragma unroll
+  for (int q = 0; q < 16 / kPieceSteps; ++q) {
+    uint32_t r[4 * kPieceSteps];
+#pragma unroll
+    for (int t = 0; t < kPieceSteps; ++t) {
+      uint32_t a[4];
+      ldmatrix_x4(a, addr + (kPieceSteps * q + t) * 256);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[4 * t + j] = a[j];
+    }
+    tmem_st_piece(dst + q * 4 * kPieceSteps, r);
+  }
+  tmem_wait_st();
+  ++s.t_count;
+  ++s.n_acquired;
+  if (++s.c_slot == kSlots) {
+    s.c_slot = 0;
+    s.c_par ^= 1u;
+  }
+  release_tile(s, p);
+}
+
+// The next tile of the stream times the activations in xf, accumulated into cc: from tensor memory
+// when tiles are parked there, else from the ring (waits for the copy, refills the slot).
+// two = false: the tile holds a single row (its second half is not read from the ring).
+template <class S>
+__device__ __forceinline__ void consume_tile(Worker<S>& s, const Params& p, int ph, float (&cc)[4], const XFrag& xf,
+                                             bool two) {
+  if (kTSlots > 0 && s.t_count > 0) {
+    const uint32_t src = s.tmem + s.t_head * kTileCols;
+    float c[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
+#pragma unroll
+    for (int q = 0; q < 16 / kPieceSteps; ++q) {
+      uint32_t r[4 * kPieceSteps];
+      tmem_ld_piece(r, src + q * 4 * kPieceSteps);
+      tmem_wait_ld();
+#pragma unroll
+      for (int t = 0; t < kPieceSteps; ++t) {
+        const int ks = kPieceSteps * q + t;   // k-step: same accumulator and order as mma_chunk_pair
+        const uint32_t a[4] = {r[4 * t], r[4 * t + 1], r[4 * t + 2], r[4 * t + 3]};
+        mma_bf16_16816(c[ks & 3], a, xf.b[2 * ks], xf.b[2 * ks + 1]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) cc[j] += (c[0][j] + c[1][j]) + (c[2][j] + c[3][j]);
+    --s.t_count;
+    if (++s.t_head == (unsigned)kTSlots) s.t_head = 0;
+    return;
+  }
+  const uint32_t t0 = acquire_tile(s, p, ph);
+  mma_chunk_pair(cc, t0, two ? t0 + kChunkBytes : t0, xf, s.lane);
+  release_tile(s, p);
+}
+
+// Two tiles at once against the same activations: their ldmatrix / mma chains interleave, which hides
+// most of the latency a single warp would otherwise sit through tile after tile (two warps per
+// scheduler cannot hide it).  ca / cb must be zero on entry; the sums equal those of consume_tile.
+template <class S>
+__device__ __forceinline__ void consume_two(Worker<S>& s, const Params& p, int ph, float (&ca)[4], float (&cb)[4],
+                                            const XFrag& xf, bool two_a, bool two_b) {
+  if (kTSlots > 0 && s.t_count > 0) {   // parked tiles first, one by one
+    consume_tile(s, p, ph, ca, xf, two_a);
+    consume_tile(s, p, ph, cb, xf, two_b);
+    return;
+  }
+  const uint32_t ta = acquire_tile(s, p, ph);
+  const uint32_t tb = acquire_tile(s, p, ph);
+  const uint32_t addr_a = ldmatrix_lane_addr(ta, two_a ? ta + kChunkBytes : ta, s.lane);
+  const uint32_t addr_b = ldmatrix_lane_addr(tb, two_b ? tb + kChunkBytes : tb, s.lane);
+  float c[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    uint32_t fa[4], fb[4];
+    ldmatrix_x4(fa, addr_a + t * 256);
+    ldmatrix_x4(fb, addr_b + t * 256);
+    mma_bf16_16816(c[t & 3], fa, xf.b[2 * t], xf.b[2 * t + 1]);
+    mma_bf16_16816(c[4 + (t & 3)], fb, xf.b[2 * t], xf.b[2 * t + 1]);
+  }
+  __syncwarp();
+  issue_one(s, p);
+  issue_one(s, p);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    ca[j] += (c[0][j] + c[1][j]) + (c[2][j] + c[3][j]);
+    cb[j] += (c[4][j] + c[5][j]) + (c[6][j] + c[7][j]);
+  }
+}
+// diag_reduce of two products, the shuffles of both in flight together.
+__device__ __forceinline__ void diag_reduce2(const float (&ca)[4], const float (&cb)[4], int lane, float& a0, float& a1,
+                                             float& b0, float& b1) {
+  const int r = lane >> 2, q2 = (lane & 3) * 2;
+  a0 = r == q2 ? ca[0] : (r == q2 + 1 ? ca[1] : 0.f);
+  a1 = r == q2 ? ca[2] : (r == q2 + 1 ? ca[3] : 0.f);
+  b0 = r == q2 ? cb[0] : (r == q2 + 1 ? cb[1] : 0.f);
+  b1 = r == q2 ? cb[2] : (r == q2 + 1 ? cb[3] : 0.f);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float x0 = __shfl_xor_sync(kFullMask, a0, o), x1 = __shfl_xor_sync(kFullMask, a1, o);
+    const float x2 = __shfl_xor_sync(kFullMask, b0, o), x3 = __shfl_xor_sync(kFullMask, b1, o);
+    a0 += x0;
+    a1 += x1;
+    b0 += x2;
+    b1 += x3;
   }
 }
 

@@ -16,6 +16,10 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.bars = smem_u32(smem + L::kOffBars + w * kSlots * 8);
   s.ctl = smem_u32(smem + L::kOffCtl);
   s.n_issued = s.n_acquired = 0;
+  s.t_head = s.t_count = 0;
+  // this warp's parking space: lanes of its quarter (warp rank mod 4), first or second half of the columns
+  s.tmem = reinterpret_cast<const volatile uint32_t*>(smem + L::kOffCtl)[kCtlTmem] + ((uint32_t)(32 * (w & 3)) << 16) +
+           (uint32_t)((w >> 2) * kTSlots * kTileCols);
   s.i_slot = s.c_slot = s.c_par = 0;
   s.res = 0.f;
   s.res_valid = false;
@@ -79,8 +83,22 @@ __global__ void __launch_bounds__(kThreads, 1) qmk_decode_kernel(const __grid_co
     }
   }
   if (lane == 0) fence_barrier_init();
+  __syncthreads();   // (the control words are zeroed before the allocation writes its address among them)
+  if (kTSlots > 0 && warp == 0) {
+    tmem_alloc_512(smem_u32(smem + L::kOffCtl + kCtlTmem * 4));
+    tmem_fence_before_sync();
+  }
   __syncthreads();
+  tmem_fence_after_sync();
   worker_main<S>(p, smem, warp, lane);
+  if (kTSlots > 0) {   // every warp is done with its tensor-memory share: the allocating warp frees it
+    tmem_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+      tmem_fence_after_sync();
+      tmem_dealloc_512(reinterpret_cast<const volatile uint32_t*>(smem + L::kOffCtl)[kCtlTmem]);
+    }
+  }
   if (p.trace != nullptr && lane == 0) {   // kernel entry / exit of this CTA, kept in the slots of the first phase
     unsigned long long* t = p.trace + ((size_t)blockIdx.x * num_phases(p.num_layers) + p.phase_begin) * 8;
     atomicMax(t + 3, ~t_entry);

@@ -83,6 +83,11 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
 // order, decode_kernel/down_proj_gemv_residual.cu:39-52, 225-234).
 // LM head (fused_rms_lmhead_gemv, operations.py:303-321) also keeps the arg-max of the bf16 logits,
 // lowest index on ties, replacing `logits.argmax()` of the host loop (decode.py:1391-1395).
+#ifndef QMK_PAIR_TILES
+#define QMK_PAIR_TILES 0
+#endif
+constexpr bool kPairTiles = QMK_PAIR_TILES != 0;
+
 template <class S>
 __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kind) {
   using L = SmemLayout<S>;
@@ -102,7 +107,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   if (kind == kDown) {
     Part<S::I> part;
     if (!s.aborted) {
-      if (fetch_part<S::I>(p, p.t_silu, p.silu_out, tagged, tag_in, s.w, s.lane, ph, part)) store_part(part, act, s.w, s.lane);
+      if (fetch_part<S::I>(s, p, p.t_silu, p.silu_out, tagged, tag_in, ph, part)) store_part(part, act, s.w, s.lane);
       else flag_abort(s, smem);
     }
     cta_sync(s, smem);
@@ -120,7 +125,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     const uint16_t* psrc = kind == kOproj ? p.attn_out
                                           : (kind == kQkv || (kind == kLmHead && p.num_layers == 0)
                                                  ? residual_src<S>(p, layer) : p.hidden);
-    if (!s.aborted && !fetch_part<S::H>(p, tsrc, psrc, tagged, tag_in, s.w, s.lane, ph, part)) flag_abort(s, smem);
+    if (!s.aborted && !fetch_part<S::H>(s, p, tsrc, psrc, tagged, tag_in, ph, part)) flag_abort(s, smem);
     if (normed) {
       const float ss = s.aborted ? 0.f : part_sumsq(part);
       if (s.lane == 0) sumsq[s.w] = ss;
@@ -168,13 +173,28 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
 #pragma unroll 1
       for (int i = 0; i < nb; i += step) {
         float cc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (kPairTiles && nsl == 1 && i + step < nb) {   // two tiles of the same activations at once
+          float cb[4] = {0.f, 0.f, 0.f, 0.f};
+          consume_two(s, p, ph, cc, cb, xf, unit_tiles || (i + 1 < nb), unit_tiles || (i + step + 1 < nb));
+          float a0, a1, b0, b1;
+          diag_reduce2(cc, cb, s.lane, a0, a1, b0, b1);
+          if (s.lane == i) {
+            va = a0;
+            vb = a1;
+          }
+          if (!unit_tiles && s.lane == i + 1) va = a1;
+          i += step;
+          if (s.lane == i) {
+            va = b0;
+            vb = b1;
+          }
+          if (!unit_tiles && s.lane == i + 1) va = b1;
+          continue;
+        }
 #pragma unroll 1
         for (int k = 0; k < nsl; ++k) {
           if (nsl > 1) load_xfrag(xf, act + k * kChunkBytes, s.lane);
-          const uint32_t t0 = acquire_tile(s, p, ph);
-          const bool two = unit_tiles || (i + 1 < nb);
-          mma_chunk_pair(cc, t0, two ? t0 + kChunkBytes : t0, xf, s.lane);
-          release_tile(s, p);
+          consume_tile(s, p, ph, cc, xf, unit_tiles || (i + 1 < nb));
         }
         float sa, sb;
         diag_reduce(cc, s.lane, sa, sb);

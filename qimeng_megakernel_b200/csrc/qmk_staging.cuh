@@ -32,27 +32,32 @@ static __device__ __noinline__ bool poll_give_up(const Params& p, long long t0, 
 #ifndef QMK_POLL_SLEEP_NS
 #define QMK_POLL_SLEEP_NS 0
 #endif
-__device__ __forceinline__ void poll_backoff(unsigned it) {
+__device__ __forceinline__ void poll_pause(unsigned it) {
+  if (QMK_POLL_SLEEP_NS > 0) __nanosleep(it < 2 ? QMK_POLL_SLEEP_NS / 2 : QMK_POLL_SLEEP_NS);
+}
+template <class S>
+__device__ __forceinline__ void poll_backoff(Worker<S>& s, const Params& p, unsigned it) {
+  park_one(s, p);   // use the wait: keep the weight stream moving (tensor-memory parking, qmk_kernel.cuh)
   if (QMK_POLL_SLEEP_NS > 0) __nanosleep(it < 2 ? QMK_POLL_SLEEP_NS / 2 : QMK_POLL_SLEEP_NS);
 }
 
 // Poll NPL uint4 per lane (4 tagged words each) starting at word `word0` until every word carries `tag`.
-template <int NPL>
-__device__ __forceinline__ bool poll_tagged(const Params& p, const uint32_t* tsrc, int word0, unsigned tag, int lane,
-                                            int warp, int ph, uint4 (&v)[NPL]) {
+template <int NPL, class S>
+__device__ __forceinline__ bool poll_tagged(Worker<S>& s, const Params& p, const uint32_t* tsrc, int word0, unsigned tag,
+                                            int ph, uint4 (&v)[NPL]) {
+  const int lane = s.lane, warp = s.w;
   const unsigned tagw = tag << 16;
   const uint4* src = reinterpret_cast<const uint4*>(tsrc + word0) + lane;
   const long long t0 = clock64();
   for (unsigned it = 0;; ++it) {
     bool ok = true;
 #pragma unroll
-    for (int j = 0; j < NPL; ++j) {
-      v[j] = ldcg_u4(src + j * 32);
-      ok = ok && tags_ok(v[j], tagw);
-    }
+    for (int j = 0; j < NPL; ++j) v[j] = ldcg_u4(src + j * 32);
+    if (it > 0) poll_backoff(s, p, it);   // while the loads are in flight
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) ok = ok && tags_ok(v[j], tagw);
     if (__all_sync(kFullMask, ok)) return true;
     if ((it & 15u) == 15u && poll_give_up(p, t0, ok, v[0].x >> 16, tag, warp, ph, lane)) return false;
-    poll_backoff(it);
   }
 }
 
@@ -75,13 +80,14 @@ struct Part {
   uint2 v[NPL];
 };
 
-template <int N>
-__device__ __forceinline__ bool fetch_part(const Params& p, const uint32_t* tsrc, const uint16_t* psrc, bool tagged,
-                                           unsigned tag, int warp, int lane, int ph, Part<N>& part) {
-  const int e0 = warp * Part<N>::kElems;
+template <int N, class S>
+__device__ __forceinline__ bool fetch_part(Worker<S>& s, const Params& p, const uint32_t* tsrc, const uint16_t* psrc,
+                                           bool tagged, unsigned tag, int ph, Part<N>& part) {
+  const int lane = s.lane;
+  const int e0 = s.w * Part<N>::kElems;
   if (tagged) {
     uint4 t[Part<N>::NPL];
-    if (!poll_tagged<Part<N>::NPL>(p, tsrc, e0, tag, lane, warp, ph, t)) return false;
+    if (!poll_tagged<Part<N>::NPL>(s, p, tsrc, e0, tag, ph, t)) return false;
 #pragma unroll
     for (int j = 0; j < Part<N>::NPL; ++j) part.v[j] = untag4(t[j]);
   } else {
