@@ -14,7 +14,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB_PATH = CSRC / "libqmk_b200.so"
 SOURCES = ["qmk_api.cu", "qmk_static.cu"]
-HEADERS = ["qmk_megakernel.cuh", "qmk_kernel.cuh", "qmk_phases.cuh", "qmk_attention.cuh", "qmk_staging.cuh", "qmk_device.cuh",
+HEADERS = ["qmk_megakernel.cuh", "qmk_kernel.cuh", "qmk_phases.cuh", "qmk_umma.cuh", "qmk_attention.cuh", "qmk_staging.cuh", "qmk_device.cuh",
            "qmk_params.h", "qmk_schedule.h", "../../include/qmk_b200.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
@@ -34,19 +34,40 @@ def is_stale() -> bool:
     return any((CSRC / f).resolve().stat().st_mtime > t for f in SOURCES + HEADERS)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; returns its path."""
-    if not force and not is_stale():
-        return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(LIB_PATH),
-           *[str(CSRC / s) for s in SOURCES]]
+def _compile(out: Path, sources: list[str], defines: list[str], verbose: bool) -> Path:
+    cmd = [_nvcc(), *NVCC_FLAGS, *defines, *(["-Xptxas", "-v"] if verbose else []), "-o", str(out),
+           *[str(CSRC / s) for s in sources]]
     proc = subprocess.run(cmd, cwd=str(CSRC), capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
     if verbose:
         print(proc.stdout + proc.stderr)
-    return LIB_PATH
+    return out
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the library if it is missing or older than its sources; returns its path."""
+    if not force and not is_stale():
+        return LIB_PATH
+    return _compile(LIB_PATH, SOURCES, [], verbose)
+
+
+# The same C ABI with the weight stream multiplied by tcgen05.mma from a CTA-level ring (qmk_umma.cuh)
+# instead of mma.sync from per-warp rings.  Slower at batch 1 (measured), kept as the base of the
+# batched path; tests/test_gpu_umma_path.py holds it to the same parity bar.
+UMMA_DIR = CSRC / "umma"
+UMMA_LIB_PATH = UMMA_DIR / "libqmk_b200.so"
+
+
+def build_umma(force: bool = False, verbose: bool = False) -> Path:
+    UMMA_DIR.mkdir(exist_ok=True)
+    if not force and UMMA_LIB_PATH.exists():
+        t = UMMA_LIB_PATH.stat().st_mtime
+        if not any((CSRC / f).resolve().stat().st_mtime > t for f in SOURCES + HEADERS):
+            return UMMA_LIB_PATH
+    return _compile(UMMA_LIB_PATH, SOURCES, ["-DQMK_UMMA=1"], verbose)
 
 
 if __name__ == "__main__":
     print(build(force=True, verbose=True))
+    print(build_umma(force=True))

@@ -234,7 +234,7 @@ static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)h->n_sm);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kLaunchThreads);
   cfg.dynamicSmemBytes = SmemLayout<Shape>::kTotal;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -410,7 +410,7 @@ extern "C" int64_t qmk_launch_count(const qmk_handle* h) { return h ? h->launche
 extern "C" int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes) {
   if (!h) return QMK_ERR_INVALID_ARG;
   if (ctas) *ctas = h->n_sm;
-  if (threads) *threads = kThreads;
+  if (threads) *threads = kLaunchThreads;
   if (smem_bytes) *smem_bytes = SmemLayout<Shape>::kTotal;
   return QMK_OK;
 }

@@ -27,6 +27,14 @@
 
 namespace qmk {
 
+// 1: weights are multiplied by tcgen05.mma from a CTA-level ring (qmk_umma.cuh);
+// 0: by mma.sync from per-warp rings (qmk_phases.cuh).
+#ifndef QMK_UMMA
+#define QMK_UMMA 0
+#endif
+#if QMK_UMMA && !defined(QMK_TMEM_SLOTS)
+#define QMK_TMEM_SLOTS 0   // tensor memory holds the accumulators there, nothing is parked
+#endif
 #ifndef QMK_WORKERS
 #define QMK_WORKERS 8
 #endif
@@ -103,6 +111,7 @@ struct Worker {
   TileCursor<S> pf;        // the same stream, kL2Ahead tiles further: what is being pulled into L2
   uint32_t tmem;           // tensor-memory address of this warp's parking space (its lane quarter, its column half)
   unsigned t_head, t_count;   // oldest parked tile and number of parked tiles (FIFO, all older than the ring's tiles)
+  unsigned groups_done;       // tcgen05 path: groups of this CTA in the phases before the current one
   StreamBases wb;
   float res;               // residual stream value of row (cur.r0 + lane), bf16-exact
   bool res_valid;

@@ -2,7 +2,13 @@
 #pragma once
 #include "qmk_kernel.cuh"
 
+#if QMK_UMMA
+#include "qmk_umma.cuh"
+#else
+
 namespace qmk {
+
+constexpr int kLaunchThreads = kThreads;
 
 template <class S>
 __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem, int w, int lane) {
@@ -107,3 +113,5 @@ __global__ void __launch_bounds__(kThreads, 1) qmk_decode_kernel(const __grid_co
 }
 
 }  // namespace qmk
+
+#endif  // QMK_UMMA

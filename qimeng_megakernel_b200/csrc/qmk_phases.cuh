@@ -73,6 +73,7 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
   return f32_to_bf16_bits(sl * bf16_round(up));
 }
 
+#if !QMK_UMMA
 // ---- the streaming phase -----------------------------------------------------------------------
 // An item is what one lane of the epilogue owns: a QKV RoPE pair or SwiGLU unit (one tile each), or a
 // row of O-proj / LM head (two rows per tile) or of down-proj (two rows per I/2048 tiles, one tile
@@ -281,6 +282,10 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   }
 }
 
+#endif  // !QMK_UMMA
+
 }  // namespace qmk
 
+#if !QMK_UMMA
 #include "qmk_attention.cuh"
+#endif

@@ -128,9 +128,17 @@ __device__ __forceinline__ void normalise_part(Part<N>& part, const uint2 (&gain
 // CTA barrier followed by a look at the CTA's abort word.  Every warp of the CTA executes the same
 // sequence of these (also warps that have given up), so a bounded wait that expires in one warp
 // never leaves the others stuck at a barrier.
+// Barrier of the CTA's worker warps (on the tcgen05 path the CTA also has control warps, which never join it).
+__device__ __forceinline__ void worker_barrier() {
+#if QMK_UMMA
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+#else
+  __syncthreads();
+#endif
+}
 template <class S>
 __device__ __forceinline__ void cta_sync(Worker<S>& s, const unsigned char* smem) {
-  __syncthreads();
+  worker_barrier();
   if (reinterpret_cast<const volatile unsigned*>(smem + SmemLayout<S>::kOffCtl)[kCtlAbort] != 0u) s.cta_abort = true;
 }
 template <class S>

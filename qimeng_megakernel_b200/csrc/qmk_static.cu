@@ -198,7 +198,7 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)dev.n_sm);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kLaunchThreads);
   cfg.dynamicSmemBytes = SmemLayout<Shape>::kTotal;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -4,7 +4,9 @@ Per-op tests give both sides identical inputs (the oracle's state is copied to t
 each phase), in the manner of the reference's pyvm_to_megakernel op tests
 (qimeng_megakernel/verifier/LLM/llama/llama3_2__1b/A100/single_batch/pyvm_to_megakernel/test_op_qkv_rope.py:22-62).
 Tolerances (stated once here): a per-op output may differ from the bf16 oracle by bf16 rounding of a
-differently-ordered fp32 sum: |d| <= 1e-2*|ref| + 2e-3*max|ref|.  Whole-step hidden states are held to
+differently-ordered fp32 sum: |d| <= 1e-2*|ref| + 2e-3*max|ref|.  The residual phases round the projection
+to bf16 BEFORE adding it to the stream (operations.py:251-262, 285-295), so there the rounding unit is that of
+the projection term, which can be much larger than the sum: the bound gains 1e-2*|ref - residual input|.  Whole-step hidden states are held to
 rtol 2e-2 against the fp32 oracle: relative L2 error <= 2e-2 and elementwise |d| <= 2e-2*|ref| + 5e-2*rms(ref)
 (the reference's own bf16 route sits at relative L2 ~1e-2 and elementwise ~3.3e-2*(|ref|+rms) from fp32 on
 these weights, so a tighter elementwise bound would reject the reference itself); and to relative L2 <= 1e-2
@@ -21,9 +23,11 @@ pytestmark = pytest.mark.gpu
 OP_RTOL, OP_ATOL_FRAC = 1e-2, 2e-3
 
 
-def assert_op_close(actual, expected, what):
+def assert_op_close(actual, expected, what, residual_in=None):
     a, e = actual.float().cpu(), expected.float().cpu()
     tol = OP_RTOL * e.abs() + OP_ATOL_FRAC * float(e.abs().max())
+    if residual_in is not None:   # bf16 rounding of the projection term that was added to residual_in
+        tol = tol + OP_RTOL * (e - residual_in.float().cpu()).abs()
     bad = (a - e).abs() > tol
     assert not bool(bad.any()), (
         f"{what}: {int(bad.sum())} of {bad.numel()} elements out of tolerance; "
@@ -77,15 +81,15 @@ def test_per_op_parity(env, mode):
             U.push_state(st, g); fo.decode_attention(st, layer)
             mk.run_phases(g, _phase(layer, 1), _phase(layer, 1) + 1, mode)
             assert_op_close(g.attn_out, st.attn_out, f"attn_out pos {pos} layer {layer}")
-            U.push_state(st, g); fo.oproj_residual(st, layer)
+            U.push_state(st, g); h_in = st.hidden_states.clone(); fo.oproj_residual(st, layer)
             mk.run_phases(g, _phase(layer, 2), _phase(layer, 2) + 1, mode)
-            assert_op_close(g.hidden_states, st.hidden_states, f"o-proj hidden pos {pos} layer {layer}")
+            assert_op_close(g.hidden_states, st.hidden_states, f"o-proj hidden pos {pos} layer {layer}", h_in)
             U.push_state(st, g); fo.mlp_upgate(st, layer)
             mk.run_phases(g, _phase(layer, 3), _phase(layer, 3) + 1, mode)
             assert_op_close(g.silu_out, st.silu_out, f"silu_out pos {pos} layer {layer}")
-            U.push_state(st, g); fo.mlp_down_residual(st, layer)
+            U.push_state(st, g); h_in = st.hidden_states.clone(); fo.mlp_down_residual(st, layer)
             mk.run_phases(g, _phase(layer, 4), _phase(layer, 4) + 1, mode)
-            assert_op_close(g.hidden_states, st.hidden_states, f"down hidden pos {pos} layer {layer}")
+            assert_op_close(g.hidden_states, st.hidden_states, f"down hidden pos {pos} layer {layer}", h_in)
         U.push_state(st, g); fo.lm_head(st)
         mk.run_phases(g, 5 * L, 5 * L + 1, mode)
         assert_op_close(g.logits, st.logits, f"logits pos {pos}")
@@ -115,8 +119,9 @@ def test_long_context_attention(env):
 
 def test_full_step_teacher_forced(env):
     """Whole persistent step, 48 teacher-forced tokens: hidden states per layer vs the fp32 oracle
-    (rtol 2e-2), logits vs the bf16 oracle, top-1 agreement >= 99 %, exact argmax where the oracle's
-    top-2 logits are not tied."""
+    (rtol 2e-2), logits vs the bf16 oracle, exact argmax where the oracle's top-2 logits are not tied, and where
+    they are tied (within 2 bf16 ulps) the kernel's token must be one of the tied ones: on random weights near-ties
+    are common, so a plain agreement rate would measure the weights, not the kernel."""
     _reset(env)
     g, mk, st, st32, cfg = env["g"], env["mk"], env["st"], env["st32"], env["cfg"]
     L, V = cfg["num_hidden_layers"], cfg["vocab_size"]
@@ -149,13 +154,16 @@ def test_full_step_teacher_forced(env):
         assert U.rel_l2(lg, st.logits) <= 2e-2, f"logits pos {pos}: rel L2 {U.rel_l2(lg, st.logits):.4g}"
         top2 = st.logits.float().topk(2).values
         agree += int(got_tok == nxt)
+        if got_tok != nxt:   # only acceptable between logits the oracle itself cannot tell apart at bf16 resolution
+            gap = float(top2[0] - st.logits.float()[got_tok])
+            assert gap <= 2 * 2 ** -8 * float(top2[0].abs()), f"pos {pos}: token {got_tok} is {gap:.4g} below the oracle's best logit"
         if float(top2[0] - top2[1]) > 2 * 2 ** -8 * float(top2[0].abs()):
             untied += 1
             untied_agree += int(got_tok == nxt)
         if pos + 1 >= len(tokens):
             tokens.append(nxt)          # teacher forcing: the oracle's token is replayed
     mk.check_status()
-    assert agree / n_steps >= 0.99, f"top-1 agreement {agree}/{n_steps}"
+    assert agree / n_steps >= 0.9, f"top-1 agreement {agree}/{n_steps}"
     assert untied_agree == untied, f"argmax differs on {untied - untied_agree} untied steps"
 
 
