@@ -264,9 +264,9 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch, from the ncu capture summarised
-# in profiles/ (None until a capture of the current kernel has been read).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch (KV length 36), from the ncu capture
+# summarised in profiles/qmk_decode_kernel_step_llama1b.md.
+TRAFFIC_BYTES_PER_LAUNCH = 2.4787e9
 
 if __name__ == "__main__":
     main()
