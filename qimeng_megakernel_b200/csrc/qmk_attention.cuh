@@ -27,7 +27,8 @@ __device__ __forceinline__ void rotate(float (&a)[N]) {
   a[N - 1] = t;
 }
 
-// Stage this warp's part of q (fp32) and of the new K / V rows (bf16) into the big activation buffer.
+// Stage this warp's part of q and of the new K / V rows (all bf16) into the big activation buffer:
+// q at its start, the K row then the V row from byte QDIM * 4 on.
 template <class S>
 __device__ __forceinline__ bool stage_attn_part(Worker<S>& s, const Params& p, unsigned char* smem, bool tagged,
                                                 unsigned tag, int ph) {
@@ -37,7 +38,7 @@ __device__ __forceinline__ bool stage_attn_part(Worker<S>& s, const Params& p, u
   constexpr int kKvPart = 2 * S::NKV * S::HD / kWorkers;     // new K+V elements per warp
   static_assert(kQPart % 128 == 0 && kKvPart % 128 == 0, "parts must be whole rounds of tagged uint4");
   constexpr int NQ = kQPart / 128, NKV4 = kKvPart / 128;
-  float4* qdst = reinterpret_cast<float4*>(smem + L::kOffActD);
+  unsigned char* qdst = smem + L::kOffActD;
   unsigned char* kvdst = smem + L::kOffActD + S::QDIM * 4;
   if (tagged) {
     // one poll loop over both ranges (q words, then K/V words, contiguous in the scratch)
@@ -60,63 +61,64 @@ __device__ __forceinline__ bool stage_attn_part(Worker<S>& s, const Params& p, u
       }
       if (__all_sync(kFullMask, ok)) break;
       if ((it & 15u) == 15u && poll_give_up(p, t0, ok, vq[0].x >> 16, tag, warp, ph, lane)) return false;
-      poll_backoff(s, p, it);
+      poll_pause(it);   // (no tile parking here: a compute warp already holds its K / V block in registers)
     }
 #pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      const uint2 b = untag4(vq[j]);
-      qdst[(warp * kQPart) / 4 + j * 32 + lane] = make_float4(bf_lo(b.x), bf_hi(b.x), bf_lo(b.y), bf_hi(b.y));
-    }
+    for (int j = 0; j < NQ; ++j)
+      *reinterpret_cast<uint2*>(qdst + (size_t)(warp * kQPart + (j * 32 + lane) * 4) * 2) = untag4(vq[j]);
 #pragma unroll
     for (int j = 0; j < NKV4; ++j)
       *reinterpret_cast<uint2*>(kvdst + (size_t)(warp * kKvPart + (j * 32 + lane) * 4) * 2) = untag4(vk[j]);
   } else {
     const uint2* qsrc = reinterpret_cast<const uint2*>(p.q_post_rope + warp * kQPart);
 #pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      const uint2 b = __ldcg(qsrc + j * 32 + lane);
-      qdst[(warp * kQPart) / 4 + j * 32 + lane] = make_float4(bf_lo(b.x), bf_hi(b.x), bf_lo(b.y), bf_hi(b.y));
-    }
+    for (int j = 0; j < NQ; ++j)
+      *reinterpret_cast<uint2*>(qdst + (size_t)(warp * kQPart + (j * 32 + lane) * 4) * 2) = __ldcg(qsrc + j * 32 + lane);
   }
   return true;
 }
 
-// One block of 32 keys of one kv head: lane = key for K (a whole row per lane), lane = output dims for V.
+// ---- attention on the tensor pipe (head_dim 64, up to 8 query heads per kv head) ----------------
+// One block = 32 keys of one kv head.  g = lane / 4, t = lane % 4.
+//   scores  S[head][key] = q . k  : mma.m16n8k16 bf16, A = q (row = query head of the group, rows past the
+//     group are zero), B = K.  n-tile j holds keys 8j..8j+7 (column g = key 8j + g).  The contraction index may be
+//     permuted freely as long as q and K agree, so lane (g, t) simply takes the 32-bit words 4t..4t+3 and
+//     16+4t..16+4t+3 of its key's row (two 16-byte loads) and the same words of q: k-step s uses words
+//     (4t+2s, 4t+2s+1) of the first half (s = 0, 1) or of the second half (s = 2, 3).
+//     Result: lane (g, t) holds S[head g][keys 8j+2t, 8j+2t+1], j = 0..3.
+//   output  O[head][dim] = sum_key P V : mma.m16n8k8 tf32 (P in tf32: 2^-11 relative; V exact), A = P, B = V.
+//     k-step ks contracts keys 8ks..8ks+7 in the order (k = t -> key 8ks+2t, k = t+4 -> key 8ks+2t+1): exactly the
+//     probabilities the lane already holds, no shuffles.  n-tile jn column g is dim 8g + jn, so lane (g, t) loads
+//     dims 8g..8g+7 (16 bytes) of keys 8ks+2t and 8ks+2t+1.
+//     Result: lane (g, t) holds O[head g][dims 16t + jn] (c0 of n-tile jn) and [16t + 8 + jn] (c1).
 template <class S>
 struct KvBlock {
-  static constexpr int KV4 = S::HD / 8;     // uint4 per K row
-  static constexpr int DPL = S::HD / 32;    // V dims per lane
-  uint4 k[KV4];
-  uint32_t v[kAttnBlockKeys][DPL / 2];
+  uint4 k[4][2];    // [n-tile j][half]: words 4t..4t+3 / 16+4t..16+4t+3 of key 8j+g
+  uint4 v[4][2];    // [k-step ks][key 8ks+2t / 8ks+2t+1]: dims 8g..8g+7
 };
 
-// Rows come from the cache in global memory; rows past the end of the range are clamped to its last
-// row (they get probability 0).  With `skip_pos` the row of this step's own position is not fetched
-// (its slot keeps whatever it held): patch_new_row() fills it from shared memory after the staging.
+// Rows come from the cache in global memory; rows past the end of the range are clamped to its last row
+// (they get probability 0).
 template <class S>
 __device__ __forceinline__ void load_kv_block(KvBlock<S>& b, const Params& p, int layer, int kvh, int kb, int k1,
                                               int lane) {
-  constexpr int HD = S::HD, DPL = KvBlock<S>::DPL;
-  const uint16_t* kbase = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)kvh * HD;
-  const uint16_t* vbase = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)kvh * HD + lane * DPL;
-  int kc = kb + lane;
-  if (kc > k1 - 1) kc = k1 - 1;
-  const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)kc * p.kv_seq_stride);
+  static_assert(S::HD == 64, "the tensor-pipe attention is laid out for head_dim 64");
+  const uint64_t keep = l2_policy_evict_last();
 #pragma unroll
-  for (int i = 0; i < KvBlock<S>::KV4; ++i) b.k[i] = ldcg_u4(kp + i);
+  for (int i = 0; i < 8; ++i) b.k[i >> 1][i & 1] = ld_keep_u4(kv_piece<S>(p, layer, kvh, kb, k1, lane, i), keep);
 #pragma unroll
-  for (int j = 0; j < kAttnBlockKeys; ++j) {
-    int kj = kb + j;
-    if (kj > k1 - 1) kj = k1 - 1;
-    const uint16_t* vp = vbase + (size_t)kj * p.kv_seq_stride;
-    if (DPL == 2) {
-      b.v[j][0] = ldcg_u32(vp);
-    } else {
-      const uint2 t = __ldcg(reinterpret_cast<const uint2*>(vp));
-      b.v[j][0] = t.x;
-      b.v[j][DPL / 2 - 1] = t.y;
-    }
-  }
+  for (int i = 8; i < 16; ++i) b.v[(i - 8) >> 1][i & 1] = ld_keep_u4(kv_piece<S>(p, layer, kvh, kb, k1, lane, i), keep);
+}
+// The block that prefetch_attn_rows copied into shared memory during the QKV phase of this launch.
+template <class S>
+__device__ __forceinline__ void take_staged_kv_block(KvBlock<S>& b, const unsigned char* smem, int w, int lane) {
+  using L = SmemLayout<S>;
+  cp_async_wait_all();
+  const uint4* src = reinterpret_cast<const uint4*>(smem + L::kOffKvStage + w * 16 * 512) + lane;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b.k[i >> 1][i & 1] = src[i * 32];
+#pragma unroll
+  for (int i = 8; i < 16; ++i) b.v[(i - 8) >> 1][i & 1] = src[i * 32];
 }
 
 // Overwrite the row of position `pos` (if it falls in this block, clamped copies included) with the
@@ -125,21 +127,21 @@ template <class S>
 __device__ __forceinline__ void patch_new_row(KvBlock<S>& b, const unsigned char* smem, int kvh, int kb, int k1, int pos,
                                               int lane) {
   using L = SmemLayout<S>;
-  constexpr int HD = S::HD, DPL = KvBlock<S>::DPL;
   if (pos < kb || pos >= kb + kAttnBlockKeys || pos != k1 - 1) return;   // the new row is always the last key
-  const unsigned char* knew = smem + L::kOffActD + S::QDIM * 4 + (size_t)kvh * HD * 2;
-  const unsigned char* vnew = knew + (size_t)S::NKV * HD * 2 + lane * DPL * 2;
-  if (kb + lane >= pos) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint4* knew = reinterpret_cast<const uint4*>(smem + L::kOffActD + S::QDIM * 4 + (size_t)kvh * S::HD * 2);
+  const uint4* vnew = reinterpret_cast<const uint4*>(smem + L::kOffActD + S::QDIM * 4 + (size_t)(S::NKV + kvh) * S::HD * 2);
 #pragma unroll
-    for (int i = 0; i < KvBlock<S>::KV4; ++i) b.k[i] = reinterpret_cast<const uint4*>(knew)[i];
-  }
-#pragma unroll
-  for (int j = 0; j < kAttnBlockKeys; ++j) {
-    if (kb + j >= pos) {
-#pragma unroll
-      for (int d2 = 0; d2 < DPL / 2; ++d2) b.v[j][d2] = reinterpret_cast<const uint32_t*>(vnew)[d2];
+  for (int j = 0; j < 4; ++j)
+    if (kb + 8 * j + g >= pos) {
+      b.k[j][0] = knew[t];
+      b.k[j][1] = knew[4 + t];
     }
-  }
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+      if (kb + 8 * ks + 2 * t + e >= pos) b.v[ks][e] = vnew[g];
 }
 
 // Partial record of (head, part): HD words of un-normalised output, then running max (log2 domain)
@@ -149,114 +151,116 @@ __device__ __forceinline__ unsigned long long* part_record(const Params& p, int 
   return p.part_rec + ((size_t)head * kMaxSplits + part) * (S::HD + 2);
 }
 
-// ---- compute unit: one kv head (all query heads of its group) x one range of keys --------------
-template <class S>
-__device__ __forceinline__ void attn_unit(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kvh,
-                                          int part, int bps, int P, bool staged_kv, unsigned tagw, KvBlock<S>& blk,
-                                          bool blk_loaded) {
-  using L = SmemLayout<S>;
-  constexpr int HD = S::HD, GQA = S::GQA, DPL = KvBlock<S>::DPL, KV4 = KvBlock<S>::KV4;
-  static_assert(DPL == 2 || DPL == 4, "head_dim must be 64 or 128");
-  const int layer = phase_layer(ph);
-  const int T = p.pos + 1;
-  const int k0 = part * bps * kAttnBlockKeys;
-  int k1 = k0 + bps * kAttnBlockKeys;
-  if (k1 > T) k1 = T;
-  const float4* q4 = reinterpret_cast<const float4*>(smem + L::kOffActD) + (size_t)kvh * GQA * (HD / 4);
+__device__ __forceinline__ void mma_tf32_1688(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  // rows 8..15 of A are zero (a1 = a3 = 0)
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
 
-  float m[GQA], l[GQA], acc0[GQA], acc1[GQA], acc2[GQA], acc3[GQA];
-#pragma unroll
-  for (int h = 0; h < GQA; ++h) {
-    m[h] = -INFINITY;
-    l[h] = acc0[h] = acc1[h] = acc2[h] = acc3[h] = 0.f;
+// ---- a warp's share of a compute unit: keys [k0, k1) of one kv head, all query heads of its group.
+// Returns the un-normalised partial in registers: lane (g, t) with g < GQA holds head g's running max m (log2
+// domain), sum l, and O[16t + jn] in o0[jn], O[16t + 8 + jn] in o1[jn].
+struct AttnPartial {
+  float m, l, o0[8], o1[8];
+};
+
+template <class S>
+__device__ __forceinline__ void attn_blocks(const Params& p, unsigned char* smem, int layer, int kvh, int k0, int k1,
+                                            bool staged_kv, bool first_in_smem, KvBlock<S>& blk, int w, int lane,
+                                            AttnPartial& out) {
+  using L = SmemLayout<S>;
+  constexpr int HD = S::HD, GQA = S::GQA;
+  static_assert(GQA <= 8, "one mma row per query head of the group");
+  const int g = lane >> 2, t = lane & 3;
+  // q fragments of head g: the same words of the row as the lane's K words (rows past the group are zero)
+  uint4 qa = make_uint4(0u, 0u, 0u, 0u), qb = qa;
+  if (g < GQA) {
+    const uint4* qrow = reinterpret_cast<const uint4*>(smem + L::kOffActD + (size_t)(kvh * GQA + g) * HD * 2);
+    qa = qrow[t];
+    qb = qrow[4 + t];
   }
+  float m = -INFINITY, l = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out.o0[i] = out.o1[i] = 0.f;
 
 #pragma unroll 1
   for (int kb = k0; kb < k1; kb += kAttnBlockKeys) {
-    if (!(blk_loaded && kb == k0)) load_kv_block(blk, p, layer, kvh, kb, k1, s.lane);
-    if (staged_kv) patch_new_row(blk, smem, kvh, kb, k1, p.pos, s.lane);
-    const bool valid = kb + s.lane < k1;
-#pragma unroll 1
-    for (int h = 0; h < GQA; ++h) {
-      const float4* qh = q4 + h * (HD / 4);
-      float s0 = 0.f, s1 = 0.f;
+    if (kb == k0 && first_in_smem) take_staged_kv_block(blk, smem, w, lane);
+    else load_kv_block(blk, p, layer, kvh, kb, k1, lane);
+    if (staged_kv) patch_new_row(blk, smem, kvh, kb, k1, p.pos, lane);
+    // scores
+    float sc0[4], sc1[4];
+    float bmax = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < KV4; ++i) {
-        const float4 qa = qh[2 * i], qb = qh[2 * i + 1];
-        const uint4 kk = blk.k[i];
-        s0 = fmaf(bf_lo(kk.x), qa.x, s0);
-        s1 = fmaf(bf_hi(kk.x), qa.y, s1);
-        s0 = fmaf(bf_lo(kk.y), qa.z, s0);
-        s1 = fmaf(bf_hi(kk.y), qa.w, s1);
-        s0 = fmaf(bf_lo(kk.z), qb.x, s0);
-        s1 = fmaf(bf_hi(kk.z), qb.y, s1);
-        s0 = fmaf(bf_lo(kk.w), qb.z, s0);
-        s1 = fmaf(bf_hi(kk.w), qb.w, s1);
+    for (int j = 0; j < 4; ++j) {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const uint32_t a[4] = {qa.x, 0u, qa.y, 0u};
+        mma_bf16_16816(c, a, blk.k[j][0].x, blk.k[j][0].y);
       }
-      const float sc = valid ? (s0 + s1) * p.scale_log2e : -INFINITY;
-      const float m_new = fmaxf(m[0], warp_max(sc));
-      const float corr = exp2f(m[0] - m_new);
-      const float pr = valid ? exp2f(sc - m_new) : 0.f;
-      l[0] = l[0] * corr + pr;
-      m[0] = m_new;
-      float a0 = acc0[0] * corr, a1 = acc1[0] * corr, a2 = acc2[0] * corr, a3 = acc3[0] * corr;
+      {
+        const uint32_t a[4] = {qa.z, 0u, qa.w, 0u};
+        mma_bf16_16816(c, a, blk.k[j][0].z, blk.k[j][0].w);
+      }
+      {
+        const uint32_t a[4] = {qb.x, 0u, qb.y, 0u};
+        mma_bf16_16816(c, a, blk.k[j][1].x, blk.k[j][1].y);
+      }
+      {
+        const uint32_t a[4] = {qb.z, 0u, qb.w, 0u};
+        mma_bf16_16816(c, a, blk.k[j][1].z, blk.k[j][1].w);
+      }
+      const int key = kb + 8 * j + 2 * t;
+      sc0[j] = key < k1 ? c[0] * p.scale_log2e : -INFINITY;
+      sc1[j] = key + 1 < k1 ? c[1] * p.scale_log2e : -INFINITY;
+      bmax = fmaxf(bmax, fmaxf(sc0[j], sc1[j]));
+    }
+    bmax = fmaxf(bmax, __shfl_xor_sync(kFullMask, bmax, 1));
+    bmax = fmaxf(bmax, __shfl_xor_sync(kFullMask, bmax, 2));
+    const float m_new = fmaxf(m, bmax);          // finite: key kb of the block is always valid
+    const float corr = exp2f(m - m_new);
+    m = m_new;
+    l *= corr;
 #pragma unroll
-      for (int j = 0; j < kAttnBlockKeys; ++j) {
-        const float pj = __shfl_sync(kFullMask, pr, j);
-        a0 = fmaf(pj, bf_lo(blk.v[j][0]), a0);
-        a1 = fmaf(pj, bf_hi(blk.v[j][0]), a1);
-        if (DPL == 4) {
-          a2 = fmaf(pj, bf_lo(blk.v[j][DPL / 2 - 1]), a2);
-          a3 = fmaf(pj, bf_hi(blk.v[j][DPL / 2 - 1]), a3);
-        }
+    for (int i = 0; i < 8; ++i) {
+      out.o0[i] *= corr;
+      out.o1[i] *= corr;
+    }
+    // probabilities -> output
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const float p0 = exp2f(sc0[ks] - m_new), p1 = exp2f(sc1[ks] - m_new);
+      l += p0 + p1;
+      const uint32_t a0 = __float_as_uint(p0), a2 = __float_as_uint(p1);
+      const uint4 va = blk.v[ks][0], vb = blk.v[ks][1];
+#pragma unroll
+      for (int jn = 0; jn < 8; ++jn) {
+        const uint32_t wa = word_of(va, jn >> 1), wb = word_of(vb, jn >> 1);
+        const uint32_t b0 = (jn & 1) ? (wa & 0xffff0000u) : (wa << 16);
+        const uint32_t b1 = (jn & 1) ? (wb & 0xffff0000u) : (wb << 16);
+        float c[4] = {out.o0[jn], out.o1[jn], 0.f, 0.f};
+        mma_tf32_1688(c, a0, a2, b0, b1);
+        out.o0[jn] = c[0];
+        out.o1[jn] = c[1];
       }
-      acc0[0] = a0; acc1[0] = a1; acc2[0] = a2; acc3[0] = a3;
-      rotate(m); rotate(l); rotate(acc0); rotate(acc1); rotate(acc2); rotate(acc3);
     }
   }
-#pragma unroll
-  for (int h = 0; h < GQA; ++h) l[h] = warp_sum(l[h]);
-
-  if (P == 1) {
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      const float inv = 1.0f / l[h];
-      const int e = (kvh * GQA + h) * HD + s.lane * DPL;
-      const uint32_t w0 = pack_bf16x2(acc0[h] * inv, acc1[h] * inv);
-      *reinterpret_cast<uint32_t*>(p.attn_out + e) = w0;
-      if (p.sync) st_handoff(p.t_attn + e, make_uint2((w0 & 0xffffu) | tagw, (w0 >> 16) | tagw));
-      if (DPL == 4) {
-        const uint32_t w1 = pack_bf16x2(acc2[h] * inv, acc3[h] * inv);
-        *reinterpret_cast<uint32_t*>(p.attn_out + e + 2) = w1;
-        if (p.sync) st_handoff(p.t_attn + e + 2, make_uint2((w1 & 0xffffu) | tagw, (w1 >> 16) | tagw));
-      }
-    }
-    flush_handoff();
-    return;
-  }
-
-  // ---- publish the partial as a self-validating record
-  const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
-#pragma unroll
-  for (int h = 0; h < GQA; ++h) {
-    unsigned long long* rec = part_record<S>(p, kvh * GQA + h, part);
-    uint4* dst = reinterpret_cast<uint4*>(rec + s.lane * DPL);
-    st_handoff(dst, make_uint4(__float_as_uint(acc0[h]), rtag, __float_as_uint(acc1[h]), rtag));
-    if (DPL == 4) st_handoff(dst + 1, make_uint4(__float_as_uint(acc2[h]), rtag, __float_as_uint(acc3[h]), rtag));
-    if (s.lane == 0)
-      st_handoff(rec + HD, make_uint4(__float_as_uint(m[h]), rtag, __float_as_uint(l[h]), rtag));
-  }
-
-  flush_handoff();     // push the records out
+  l += __shfl_xor_sync(kFullMask, l, 1);
+  l += __shfl_xor_sync(kFullMask, l, 2);
+  out.m = m;
+  out.l = l;
 }
-
-
 
 // ---- merge unit: one query head; polls the P partial records of that head (eight at a time, all
 // loads in flight together), merges them with a running maximum and writes attn_out.
 template <class S>
 __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph, int head, int P, unsigned tagw) {
-  constexpr int HD = S::HD, DPL = KvBlock<S>::DPL;
+  constexpr int HD = S::HD, DPL = S::HD / 32;
   constexpr int kBatch = 8;
   const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
   float M = -INFINITY, den = 0.f, num[DPL];
@@ -314,46 +318,115 @@ __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph
   flush_handoff();
 }
 
-// ---- phase 1: attention.  Compute units (kv head, part) come first, then (when P > 1) one merge unit per
-// head; units are dealt round-robin over SMs first, so a merge unit usually lands on a warp that has
-// nothing else to do and polls from the start of the phase.  In any warp's own sequence the merge unit
-// is the last one, so it never waits for work queued behind it.
+// ---- phase 1: attention.  CTA c < NKV * Pc computes CTA-part (kv head c / Pc, part c % Pc): warp w takes
+// blocks (part * 8 + w) * bpw .. + bpw, the eight partials meet in shared memory (the x buffers of the
+// neighbouring phases are free during this one) and 256 threads merge them, one (query head, dim) each.
+// Pc == 1 (T <= 256): that is attn_out.  Otherwise the merged partial is a record, and merge unit m (query head m)
+// on warp 0 of CTA NKV * Pc + m polls the Pc records of its head.
 template <class S>
 __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
-  int bps, P;
-  attn_plan(p.pos + 1, bps, P);
-  const int n_compute = S::NKV * P;
-  const int n_units = n_compute + (P > 1 ? S::NH : 0);
-  if ((int)blockIdx.x >= n_units) return;          // no unit lands on this CTA: nothing to stage
+  using L = SmemLayout<S>;
+  constexpr int HD = S::HD, GQA = S::GQA;
+  static_assert(GQA * HD == kThreads, "the in-CTA merge gives every thread one (head, dim)");
+  static_assert(kWorkers == kAttnWarps, "attn_plan counts eight compute warps per CTA");
+  static_assert(kWorkers * GQA * HD * 4 <= 2 * L::kActSmall && L::kOffActB == L::kOffActA + L::kActSmall,
+                "the partial outputs use both small activation buffers");
+  int bpw, Pc;
+  const int T = p.pos + 1;
+  attn_plan(T, bpw, Pc);
+  const int cta = (int)blockIdx.x;
+  const int n_compute = S::NKV * Pc;
+  const int n_merge = Pc > 1 ? S::NH : 0;
+  const unsigned tagw = phase_tag(p, ph) << 16;
+  if (cta >= n_compute) {   // no staging, no barrier on these CTAs
+    if (cta < n_compute + n_merge && s.w == 0 && !s.aborted) {
+      const long long tq1 = clock64();
+      attn_merge(s, p, ph, cta - n_compute, Pc, tagw);
+      trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
+    }
+    return;
+  }
   const bool tagged = p.sync && (ph > p.phase_begin || p.wait_first);
   const long long tq0 = clock64();
-  const int first = s.w * (int)gridDim.x + (int)blockIdx.x;
-  const bool has_unit = first < n_units && !s.aborted;
-  KvBlock<S> blk;
-  if (has_unit && first < n_compute) {   // old keys do not depend on this step: fetch them before waiting for q
-    const int part = first % P, k0 = part * bps * kAttnBlockKeys;
-    int k1 = k0 + bps * kAttnBlockKeys;
-    if (k1 > p.pos + 1) k1 = p.pos + 1;
-    load_kv_block(blk, p, phase_layer(ph), first / P, k0, k1, s.lane);
-  }
+  const int kvh = cta / Pc, part = cta % Pc;
+  const int k0 = (part * kAttnWarps + s.w) * bpw * kAttnBlockKeys;
+  int k1 = k0 + bpw * kAttnBlockKeys;
+  if (k1 > T) k1 = T;
+  const int kend = (part + 1) * kAttnWarps * bpw * kAttnBlockKeys;           // end of the CTA-part
+  const int part_keys = (kend < T ? kend : T) - part * kAttnWarps * bpw * kAttnBlockKeys;
+  const int n_active = (part_keys + bpw * kAttnBlockKeys - 1) / (bpw * kAttnBlockKeys);   // warps that have keys
+  const bool has = k0 < T && !s.aborted;
+  KvBlock<S> blk;   // (its first rows have been on their way since the QKV phase started: prefetch_attn_rows)
   if (!s.aborted && !stage_attn_part<S>(s, p, smem, tagged, phase_tag(p, ph - 1), ph)) flag_abort(s, smem);
   cta_sync(s, smem);
   if (s.cta_abort) return;
   const long long tq1 = clock64();
   if (s.w == 0) trace_put(p, ph, 0, globaltimer_ns(), s.lane);
-  if (has_unit) {
-    const unsigned tagw = phase_tag(p, ph) << 16;
-    for (int u = first; u < n_units && !s.aborted; u += s.nwt) {
-      if (u < n_compute) attn_unit(s, p, smem, ph, u / P, u % P, bps, P, tagged, tagw, blk, u == first);
-      else attn_merge(s, p, ph, u - n_compute, P, tagw);
+
+  float* opart = reinterpret_cast<float*>(smem + L::kOffActA);              // [warp][head of the group][HD]
+  float* mlpart = reinterpret_cast<float*>(smem + L::kOffActD + S::QDIM * 2);   // [warp][head][m, l] (behind the bf16 q)
+  if (has) {
+    AttnPartial r;
+    attn_blocks<S>(p, smem, phase_layer(ph), kvh, k0, k1, tagged, L::kKvStage && ph > p.phase_begin, blk, s.w, s.lane, r);
+    const int g = s.lane >> 2, t = s.lane & 3;
+    if (g < GQA) {
+      float4* dst = reinterpret_cast<float4*>(opart + ((size_t)(s.w * GQA + g) * HD + 16 * t));
+      dst[0] = make_float4(r.o0[0], r.o0[1], r.o0[2], r.o0[3]);
+      dst[1] = make_float4(r.o0[4], r.o0[5], r.o0[6], r.o0[7]);
+      dst[2] = make_float4(r.o1[0], r.o1[1], r.o1[2], r.o1[3]);
+      dst[3] = make_float4(r.o1[4], r.o1[5], r.o1[6], r.o1[7]);
+      if (t == 0) *reinterpret_cast<float2*>(mlpart + (size_t)(s.w * GQA + g) * 2) = make_float2(r.m, r.l);
     }
-    if (s.aborted) flag_abort(s, smem);
   }
+  if (s.w == 0) trace_put(p, ph, 1, globaltimer_ns(), s.lane);
+  cta_sync(s, smem);
+  if (s.cta_abort) return;
+  if (s.w == 0) trace_put(p, ph, 4, globaltimer_ns(), s.lane);
+  {
+    // merge over the warps that had keys: thread = (head h of the group, dim d)
+    const int tid = s.w * 32 + s.lane, h = tid / HD, d = tid % HD;
+    float M = -INFINITY;
+    for (int w = 0; w < n_active; ++w) M = fmaxf(M, mlpart[(w * GQA + h) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int w = 0; w < n_active; ++w) {
+      const float wgt = exp2f(mlpart[(w * GQA + h) * 2] - M);
+      den = fmaf(wgt, mlpart[(w * GQA + h) * 2 + 1], den);
+      num = fmaf(wgt, opart[(size_t)(w * GQA + h) * HD + d], num);
+    }
+    const int head = kvh * GQA + h;
+    if (Pc == 1) {
+      const unsigned short bits = f32_to_bf16_bits(num / den);
+      p.attn_out[head * HD + d] = bits;
+      if (p.sync) st_handoff(p.t_attn + head * HD + d, (uint32_t)bits | tagw);
+    } else {
+      const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
+      unsigned long long* rec = part_record<S>(p, head, part);
+      st_handoff(reinterpret_cast<uint32_t*>(rec + d), make_uint2(__float_as_uint(num), rtag));
+      if (d == 0) st_handoff(reinterpret_cast<uint4*>(rec + HD), make_uint4(__float_as_uint(M), rtag, __float_as_uint(den), rtag));
+    }
+  }
+  flush_handoff();
   if (s.w == 0) {
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
     trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
     trace_put(p, ph, 7, globaltimer_ns(), s.lane);
   }
+}
+
+// The attention phase as a real function call: its register allocation (a K / V block is 64 registers) stays
+// out of the streaming loop's, and the other way round.  Takes and returns the two abort flags of the warp.
+template <class S>
+static __device__ __noinline__ unsigned phase_attn_call(const Params& p, unsigned char* smem, int ph, int lane, int w,
+                                                        unsigned aborted) {
+  Worker<S> s;
+  s.lane = lane;
+  s.w = w;
+  s.nwt = (int)gridDim.x * kWorkers;
+  s.g = (int)blockIdx.x * kWorkers + w;
+  s.aborted = aborted != 0u;
+  s.cta_abort = false;
+  phase_attn(s, p, smem, ph);
+  return (s.aborted ? 1u : 0u) | (s.cta_abort ? 2u : 0u);
 }
 
 }  // namespace qmk

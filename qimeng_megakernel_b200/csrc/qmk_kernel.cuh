@@ -39,7 +39,14 @@ namespace qmk {
 #define QMK_WORKERS 8
 #endif
 #ifndef QMK_SLOTS
-#define QMK_SLOTS 3
+#if QMK_UMMA
+#define QMK_SLOTS 3   // (sizes the ring region: three 64-KiB group slots there)
+#else
+#define QMK_SLOTS 2
+#endif
+#endif
+#ifndef QMK_KV_STAGE
+#define QMK_KV_STAGE 1
 #endif
 constexpr int kWorkers = QMK_WORKERS;  // warps per CTA (all of them stream weights)
 constexpr int kSlots = QMK_SLOTS;      // ring slots (8 KiB tiles) per warp
@@ -54,8 +61,13 @@ struct SmemLayout {
   static constexpr int kActBigA = S::I * 2;                                   // silu_out (bf16)
   static constexpr int kActBigB = S::QDIM * 4 + 2 * S::NKV * S::HD * 2;       // q fp32 + new K/V rows bf16
   static constexpr int kActBig = kActBigA > kActBigB ? kActBigA : kActBigB;
+  // first attention block of every warp (K and V rows of 32 keys, 8 KiB), copied in while the QKV phase runs;
+  // only when the rings leave room for it (two slots per warp)
+  static constexpr bool kKvStage = QMK_KV_STAGE && !QMK_UMMA && kSlots <= 2;
+  static constexpr int kKvStageBytes = kKvStage ? kWorkers * 16 * 512 : 0;
   static constexpr int kOffRing = 0;
-  static constexpr int kOffActA = kOffRing + kRingBytes;
+  static constexpr int kOffKvStage = kOffRing + kRingBytes;
+  static constexpr int kOffActA = kOffKvStage + kKvStageBytes;
   static constexpr int kOffActB = kOffActA + kActSmall;
   static constexpr int kOffActD = kOffActB + kActSmall;
   static constexpr int kOffBars = kOffActD + kActBig;                // kWorkers*kSlots u64

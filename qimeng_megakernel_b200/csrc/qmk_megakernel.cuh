@@ -52,7 +52,11 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   for (int ph = p.phase_begin; ph < p.phase_end && !s.cta_abort; ++ph) {
     if (w == 0) trace_put(p, ph, 2, globaltimer_ns(), lane);
     const int kind = phase_kind(ph, p.num_layers);
-    if (kind == kAttn) phase_attn(s, p, smem, ph);
+    if (kind == kAttn) {
+      const unsigned f = phase_attn_call<S>(p, smem, ph, lane, w, s.aborted ? 1u : 0u);
+      s.aborted = (f & 1u) != 0u;
+      s.cta_abort = (f & 2u) != 0u;
+    }
     else phase_stream(s, p, smem, ph, kind);
     if (w == 0) {
       trace_put(p, ph, 5, globaltimer_ns(), lane);

@@ -61,7 +61,8 @@ __device__ __forceinline__ void epilogue_qkv(const Params& p, const unsigned cha
     dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - vStart);
     tdst = p.t_q + S::QDIM + S::NKV * S::HD + (row - vStart);
   }
-  *reinterpret_cast<uint32_t*>(dst) = packed;
+  if (row < kStart) *reinterpret_cast<uint32_t*>(dst) = packed;
+  else st_keep_u32(dst, packed, l2_policy_evict_last());   // a KV-cache row: keep it in L2 for the coming steps
   if (p.sync) st_handoff(tdst, make_uint2((packed & 0xffffu) | tagw, (packed >> 16) | tagw));
 }
 
@@ -142,6 +143,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   }
   if (s.cta_abort) return;
   const long long tq1 = clock64();
+  // (after the poll, not before it: loads that a warp issues behind these copies wait for them)
+  if (kind == kQkv && !s.aborted) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
 
   int i0, i1;
   switch (kind) {

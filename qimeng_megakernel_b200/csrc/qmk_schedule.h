@@ -53,16 +53,19 @@ QMK_HD void split_range_u32(unsigned units, unsigned parts, unsigned g, int& lo,
   hi = (int)(((g + 1u) * units) / parts);
 }
 
-// Split-KV plan for KV length T (= pos+1): blocks of 32 keys, `bps` blocks per partial, P partials.
-// The reference picks P = min(16, SMs / kv_heads) regardless of length
-// (.../instructions/scheduler.py:85-94); here P follows the length so that short contexts
-// skip the merge entirely (P = 1) and long ones keep each partial at a few blocks.
-QMK_HD void attn_plan(int T, int& bps, int& P) {
+// Split-KV plan for KV length T (= pos+1).  Blocks of 32 keys; a warp takes `bpw` consecutive blocks, the eight
+// warps of a CTA one CTA-part of 8*bpw blocks of one kv head, merged inside the CTA through shared memory;
+// Pc CTA-parts per kv head (<= kMaxCtaParts) are merged through global records by one merge unit per query head.
+// The reference picks P = min(16, SMs / kv_heads) partials regardless of length
+// (.../instructions/scheduler.py:85-94); here short contexts (T <= 256) have Pc = 1 and no second merge at all.
+constexpr int kAttnWarps = 8;
+constexpr int kMaxCtaParts = 8;
+QMK_HD void attn_plan(int T, int& bpw, int& Pc) {
   const int nblk = (T + kAttnBlockKeys - 1) / kAttnBlockKeys;
-  bps = (nblk + kMaxSplits - 1) / kMaxSplits;
-  if (bps < 1) bps = 1;
-  P = (nblk + bps - 1) / bps;
-  if (P < 1) P = 1;
+  bpw = (nblk + kAttnWarps * kMaxCtaParts - 1) / (kAttnWarps * kMaxCtaParts);
+  if (bpw < 1) bpw = 1;
+  Pc = (nblk + kAttnWarps * bpw - 1) / (kAttnWarps * bpw);
+  if (Pc < 1) Pc = 1;
 }
 
 // ------------------------------------------------------------------------------------------

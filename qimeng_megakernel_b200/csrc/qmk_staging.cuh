@@ -125,6 +125,57 @@ __device__ __forceinline__ void normalise_part(Part<N>& part, const uint2 (&gain
   }
 }
 
+// The 16 x 16 bytes of K and V rows that lane (g = lane / 4, t = lane % 4) needs of the 32-key block starting at kb
+// (layout of the tensor-pipe attention, qmk_attention.cuh): i < 8: K, key kb + 8*(i/2) + g, words 4t.. (i even) or
+// 16+4t.. (i odd); i >= 8: V, key kb + 8*((i-8)/2) + 2t + (i&1), dims 8g..8g+7.  Keys past k1-1 are clamped.
+template <class S>
+__device__ __forceinline__ const uint4* kv_piece(const Params& p, int layer, int kvh, int kb, int k1, int lane, int i) {
+  const int g = lane >> 2, t = lane & 3;
+  const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)kvh * S::HD;
+  if (i < 8) {
+    int kc = kb + 8 * (i >> 1) + g;
+    if (kc > k1 - 1) kc = k1 - 1;
+    return reinterpret_cast<const uint4*>(p.k_cache + base + (size_t)kc * p.kv_seq_stride) + ((i & 1) ? 4 + t : t);
+  }
+  int kc = kb + 8 * ((i - 8) >> 1) + 2 * t + (i & 1);
+  if (kc > k1 - 1) kc = k1 - 1;
+  return reinterpret_cast<const uint4*>(p.v_cache + base + (size_t)kc * p.kv_seq_stride) + g;
+}
+
+// Early fetch for the attention phase that follows a QKV phase.  The KV-cache rows a warp will read there were last
+// touched a whole step (2.5 GB of weight traffic) ago; fetched only once q is there, they take 3-5 us under the
+// weight stream's load (measured), all of it on the critical path.  So every warp that will have keys (same plan as
+// phase_attn) starts copying its first block into shared memory (cp.async: no registers held) when the QKV phase
+// starts; each lane copies exactly the pieces it will read back itself, so its own wait_group is all the
+// synchronisation needed.  Without room in shared memory the rows are only pulled into L2.
+template <class S>
+__device__ __forceinline__ void prefetch_attn_rows(const Params& p, unsigned char* smem, int layer, int w, int lane) {
+  using L = SmemLayout<S>;
+  int bpw, Pc;
+  const int T = p.pos + 1;
+  attn_plan(T, bpw, Pc);
+  const int cta = (int)blockIdx.x;
+  if (cta >= S::NKV * Pc) return;
+  const int kvh = cta / Pc, part = cta % Pc;
+  const int k0 = (part * kAttnWarps + w) * bpw * kAttnBlockKeys;
+  if (k0 >= T) return;
+  int k1 = k0 + bpw * kAttnBlockKeys;
+  if (k1 > T) k1 = T;
+  if (L::kKvStage) {
+    const uint64_t keep = l2_policy_evict_last();
+    const uint32_t dst = smem_u32(smem + L::kOffKvStage) + (uint32_t)(w * 16 * 512 + lane * 16);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) cp_async_keep_16(dst + i * 512, kv_piece<S>(p, layer, kvh, k0, k1, lane, i), keep);
+    cp_async_commit();
+  } else {
+    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)kvh * S::HD;
+    int kc = k0 + lane;
+    if (kc > k1 - 1) kc = k1 - 1;
+    prefetch_l2_keep(p.k_cache + base + (size_t)kc * p.kv_seq_stride);
+    prefetch_l2_keep(p.v_cache + base + (size_t)kc * p.kv_seq_stride);
+  }
+}
+
 // CTA barrier followed by a look at the CTA's abort word.  Every warp of the CTA executes the same
 // sequence of these (also warps that have given up), so a bounded wait that expires in one warp
 // never leaves the others stuck at a barrier.

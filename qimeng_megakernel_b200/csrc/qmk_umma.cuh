@@ -314,6 +314,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   if (s.cta_abort) return;
   if (s.w == 0 && s.lane == 0) mbar_arrive(smem_u32(smem + L::kOffBars) + kBarXReady * 8);
   const long long tq1 = clock64();
+  if (kind == kQkv && !s.aborted) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
 
   // ---- epilogues of this CTA's groups
   const int ng = R.groups(kind), nslots = R.slots(kind);
@@ -430,7 +431,11 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   for (int ph = p.phase_begin; ph < p.phase_end && !s.cta_abort; ++ph) {
     if (w == 0) trace_put(p, ph, 2, globaltimer_ns(), lane);
     const int kind = phase_kind(ph, p.num_layers);
-    if (kind == kAttn) phase_attn(s, p, smem, ph);
+    if (kind == kAttn) {
+      const unsigned f = phase_attn_call<S>(p, smem, ph, lane, w, s.aborted ? 1u : 0u);
+      s.aborted = (f & 1u) != 0u;
+      s.cta_abort = (f & 2u) != 0u;
+    }
     else phase_stream(s, p, smem, ph, kind, R);
     if (w == 0) trace_put(p, ph, 5, globaltimer_ns(), lane);
   }
