@@ -93,9 +93,12 @@ static __device__ __noinline__ void report_error(const Params& p, int code, int 
   }
 }
 
-// Optional timeline: slot of (CTA, phase).  Warp 0 writes: 2 enters the phase (globaltimer ns),
-// 5 leaves it (ns); cycles spent 3 polling its staging part, 4 waiting for the other warps' parts,
-// 6 in the streaming loop + epilogue, 7 in the whole phase.
+// Optional timeline (qmk_set_trace): eight 64-bit slots per (CTA, phase), written by warp 0 unless noted.
+//   2 enters the phase, 5 leaves it (globaltimer ns); 3 cycles until its input was staged; 6 cycles from there to
+//   the end of the phase.  Streaming phases: 1 / 0 latest / (inverted) earliest end of the streaming loop over the
+//   CTA's warps (ns), 4 longest loop of a warp (cycles).  Attention, compute CTAs: 0 staged, 1 own partial done,
+//   4 all partials in shared memory, 7 outputs pushed out (ns).  First phase of the launch: 3 (inverted) entry and
+//   7 exit of the CTA (ns).
 __device__ __forceinline__ void trace_put(const Params& p, int ph, int slot, unsigned long long v, int lane) {
   if (p.trace != nullptr && lane == 0) p.trace[((size_t)blockIdx.x * num_phases(p.num_layers) + ph) * 8 + slot] = v;
 }
