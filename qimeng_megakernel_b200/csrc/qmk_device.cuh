@@ -144,6 +144,8 @@ __device__ __forceinline__ void st_handoff(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 #elif QMK_ST_MODE == 2
   asm volatile("st.global.cg.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+#elif QMK_ST_MODE == 3   // experiment: an exchange performed at L2, result dropped
+  { unsigned old; asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory"); }
 #else
   *p = v;
 #endif
@@ -153,6 +155,8 @@ __device__ __forceinline__ void st_handoff(uint32_t* p, uint2 v) {
   asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 #elif QMK_ST_MODE == 2
   asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+#elif QMK_ST_MODE == 3
+  { unsigned long long old; asm volatile("atom.relaxed.gpu.global.exch.b64 %0, [%1], %2;" : "=l"(old) : "l"(p), "l"((unsigned long long)v.x | ((unsigned long long)v.y << 32)) : "memory"); }
 #else
   *reinterpret_cast<uint2*>(p) = v;
 #endif
