@@ -135,58 +135,56 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
-// ---- stores of hand-off words (tagged activations, split-KV records): straight to L2 ----
+// ---- stores of hand-off words (tagged activations, split-KV records) ----
+// Written as atomic exchanges whose result is dropped: the exchange is performed at L2 at once, while a plain
+// store lingers on the SM behind the warp's polling loads until something flushes it.  Measured on B200 (step at KV
+// 33 / 201 / 1040): plain stores 695 us; plain stores followed by a __threadfence() that nothing waits for
+// 565 / 570 / 580 us; exchanges without any fence 495 / 519 / 543 us.  (st.relaxed.gpu, st.cg, system-scope or
+// doubled fences, pauses: all equal to or worse than the plain store + fence.)  QMK_ST_MODE 0 = plain stores,
+// QMK_FENCE 1 = fence after a phase's stores; the pair (0, 1) is the older scheme.
 #ifndef QMK_ST_MODE
-#define QMK_ST_MODE 0
+#define QMK_ST_MODE 3
 #endif
+__device__ __forceinline__ void exch_drop_u32(void* p, uint32_t v) {
+  unsigned old;
+  asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void exch_drop_u64(void* p, uint32_t lo, uint32_t hi) {
+  unsigned long long old;
+  asm volatile("atom.relaxed.gpu.global.exch.b64 %0, [%1], %2;"
+               : "=l"(old)
+               : "l"(p), "l"((unsigned long long)lo | ((unsigned long long)hi << 32))
+               : "memory");
+}
 __device__ __forceinline__ void st_handoff(uint32_t* p, uint32_t v) {
-#if QMK_ST_MODE == 1
-  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-#elif QMK_ST_MODE == 2
-  asm volatile("st.global.cg.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-#elif QMK_ST_MODE == 3   // experiment: an exchange performed at L2, result dropped
-  { unsigned old; asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory"); }
+#if QMK_ST_MODE == 3
+  exch_drop_u32(p, v);
 #else
   *p = v;
 #endif
 }
 __device__ __forceinline__ void st_handoff(uint32_t* p, uint2 v) {
-#if QMK_ST_MODE == 1
-  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
-#elif QMK_ST_MODE == 2
-  asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
-#elif QMK_ST_MODE == 3
-  { unsigned long long old; asm volatile("atom.relaxed.gpu.global.exch.b64 %0, [%1], %2;" : "=l"(old) : "l"(p), "l"((unsigned long long)v.x | ((unsigned long long)v.y << 32)) : "memory"); }
+#if QMK_ST_MODE == 3
+  exch_drop_u64(p, v.x, v.y);
 #else
   *reinterpret_cast<uint2*>(p) = v;
 #endif
 }
 __device__ __forceinline__ void st_handoff(void* p, uint4 v) {
-#if QMK_ST_MODE == 1
-  asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-#elif QMK_ST_MODE == 2
-  asm volatile("st.global.cg.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#if QMK_ST_MODE == 3
+  exch_drop_u64(p, v.x, v.y);
+  exch_drop_u64(reinterpret_cast<unsigned char*>(p) + 8, v.z, v.w);
 #else
   *reinterpret_cast<uint4*>(p) = v;
 #endif
 }
 #ifndef QMK_FENCE
-#define QMK_FENCE 1
+#define QMK_FENCE 0
 #endif
-// Push this warp's hand-off stores out (nothing waits for it).
+// Push this warp's plain hand-off stores out (nothing waits for it); not needed with exchanges.
 __device__ __forceinline__ void flush_handoff() {
 #if QMK_FENCE == 1
   __threadfence();
-#elif QMK_FENCE == 2
-  __threadfence_block();
-#elif QMK_FENCE == 3
-  __threadfence();
-  __nanosleep(500);
-#elif QMK_FENCE == 4
-  __threadfence();
-  __threadfence();
-#elif QMK_FENCE == 5
-  __threadfence_system();
 #endif
 }
 
