@@ -48,6 +48,9 @@ namespace qmk {
 #ifndef QMK_KV_STAGE
 #define QMK_KV_STAGE 1
 #endif
+#ifndef QMK_KV_EARLY
+#define QMK_KV_EARLY 1   // copy the next layer's first K/V block from the up/gate phase already (else: from its own QKV phase)
+#endif
 constexpr int kWorkers = QMK_WORKERS;  // warps per CTA (all of them stream weights)
 constexpr int kSlots = QMK_SLOTS;      // ring slots (8 KiB tiles) per warp
 constexpr int kThreads = kWorkers * 32;

@@ -144,7 +144,14 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   if (s.cta_abort) return;
   const long long tq1 = clock64();
   // (after the poll, not before it: loads that a warp issues behind these copies wait for them)
-  if (kind == kQkv && !s.aborted) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
+  // First K/V block of the coming attention phase -> shared memory.  Issued from the up/gate phase of the layer before
+  // (the staging area is free from the end of that layer's attention on, and the copy then has ten microseconds to
+  // land); the first layer of a launch does it in its own QKV phase.
+  if (!s.aborted) {
+    if (QMK_KV_EARLY && kind == kUpGate && layer + 1 < p.num_layers && ph + 3 < p.phase_end)
+      prefetch_attn_rows<S>(p, smem, layer + 1, s.w, s.lane);
+    if (kind == kQkv && (!QMK_KV_EARLY || layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
+  }
 
   int i0, i1;
   switch (kind) {
