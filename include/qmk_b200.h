@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define QMK_ABI_VERSION 1
+#define QMK_ABI_VERSION 2
 
 /* Error codes (negative).  qmk_strerror() gives the text. */
 enum qmk_error {
@@ -47,14 +47,20 @@ enum qmk_error {
 
 /* Architecture families (selects epilogue variants). */
 enum qmk_arch {
-  QMK_ARCH_LLAMA = 0            /* RMSNorm -> QKV -> interleaved RoPE -> GQA -> SwiGLU    */
+  QMK_ARCH_LLAMA = 0,           /* RMSNorm -> QKV -> interleaved RoPE -> GQA -> SwiGLU    */
+  QMK_ARCH_QWEN3 = 1            /* the same with a per-head RMSNorm on Q and K before RoPE
+                                   (qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/
+                                   decode_schedule/fused/operations.py:52-120)             */
 };
 
 /*
- * Model descriptor.  Mirrors LlamaConfig of the reference
- * (.../A100/single_batch/decode_schedule/model_config.py:4-17).  hidden_size,
- * intermediate_size, head counts and head_dim must match a compiled specialisation;
- * num_layers and vocab_size are free runtime values.
+ * Model descriptor.  Mirrors LlamaConfig / Qwen3Config of the reference
+ * (.../A100/single_batch/decode_schedule/model_config.py:4-17).  Two kernels serve it:
+ *   - the batch-1 kernel, compiled for the Llama-3.2-1B layer shape (hidden 2048, intermediate 8192,
+ *     32 / 8 heads of 64), any num_layers and vocab_size;
+ *   - the batched kernel, runtime shapes: hidden_size and intermediate_size multiples of 64
+ *     (hidden_size <= 8192), head_dim 64 or 128, query heads per kv head 1, 2 or 4, batch 1..64.
+ * qmk_create picks by descriptor, qmk_bind_state by batch (see qmk_set_kernel_variant).
  */
 typedef struct qmk_model_desc {
   int32_t abi_version;       /* QMK_ABI_VERSION */
@@ -69,6 +75,7 @@ typedef struct qmk_model_desc {
   int32_t rope_rows;         /* rows of rope_cos / rope_sin (max positions)                */
   float rms_norm_eps;
   float attn_scale;          /* 1/sqrt(head_dim), as the reference passes it (mk_kernel.py:61) */
+  float qk_norm_eps;         /* QMK_ARCH_QWEN3: eps of the per-head Q/K norm (0 = rms_norm_eps)     */
 } qmk_model_desc;
 
 /*
@@ -94,20 +101,23 @@ typedef struct qmk_weight_ptrs {
   const void* embed_tokens;
   const float* rope_cos;
   const float* rope_sin;
+  const void* q_norm;        /* QMK_ARCH_QWEN3: [L, HD] bf16, interleaved order; else NULL */
+  const void* k_norm;        /* QMK_ARCH_QWEN3: [L, HD] bf16, interleaved order; else NULL */
 } qmk_weight_ptrs;
 
 /*
  * Per-request state: device pointers borrowed until the next qmk_bind_state / qmk_destroy
  * (the reference re-allocates the KV cache between requests, decode.py:587-591, so binding
  * is separate from creation).  bf16 unless noted:
- *   hidden_states [H]  q_post_rope [NH*HD]  attn_out [NH*HD]  silu_out [I]  logits [V]
+ *   hidden_states [B,H]  q_post_rope [B,NH*HD]  attn_out [B,NH*HD]  silu_out [B,I]  logits [B,V]
+ *   (the leading B is absent / 1 for a single sequence, as in the reference's Globals)
  *   k_cache / v_cache [L, batch, kv_seq_len, NKV, HD] (K stored in the interleaved layout)
- *   next_token: optional int64[1]; receives argmax(logits) (lowest index on ties).
- *   token_in:   optional int64[1]; when non-null the step reads embed_tokens[*token_in]
+ *   next_token: optional int64[B]; receives argmax(logits) per row (lowest index on ties).
+ *   token_in:   optional int64[B]; when non-null the step reads embed_tokens[token_in[b]]
  *               instead of hidden_states as the layer-0 input (may alias next_token for a
  *               device-resident greedy loop).
- *   out_tokens: optional int64[]; when non-null the step also stores the argmax at
- *               out_tokens[pos_id + 1] (the reference's output_tokens row, decode.py:1391-1395).
+ *   out_tokens: optional int64[B, out_tokens_len]; when non-null the step also stores the argmax of
+ *               row b at out_tokens[b, pos_b + 1] (the reference's output_tokens, decode.py:1391-1395).
  */
 typedef struct qmk_state_ptrs {
   void* hidden_states;
@@ -121,8 +131,13 @@ typedef struct qmk_state_ptrs {
   const int64_t* token_in;
   int64_t* out_tokens;
   int64_t out_tokens_len;
-  int32_t batch;             /* 1 */
+  int32_t batch;             /* B: 1..64 sequences decoded per step */
   int32_t kv_seq_len;        /* S: allocated positions per sequence */
+  const int32_t* position_ids;   /* optional int32[B]: position of each row (the reference's multi-batch
+                                    position_ids); NULL = every row at the pos_id of the call */
+  const uint8_t* active_mask;    /* optional uint8[B]: 0 = the row is finished: no KV write, zero attention
+                                    output and projections, logits -1e9 (row_active in the reference's
+                                    fused operations.py:226-317); NULL = all rows active */
 } qmk_state_ptrs;
 
 /* Device-side status record, filled when a bounded wait expires. */
@@ -191,6 +206,12 @@ int qmk_set_cooperative_launch(qmk_handle* h, int32_t on);
 /* Debug knob used by the failure-detection test: when set, qmk_run_phases(mode 1) also waits for the
  * dependency of its first phase, which nothing publishes, so the bounded wait must expire. */
 int qmk_set_wait_first_dependency(qmk_handle* h, int32_t on);
+
+/* Which kernel serves the handle.  0 (default): the batch-1 kernel when the descriptor has its compiled
+ * shape and one sequence is bound, else the batched kernel.  1: always the batched kernel (any batch,
+ * also 1).  The batched kernel implements qmk_decode_step, qmk_run_phases, qmk_generate_host (batch 1),
+ * qmk_poll_status and the wait-first knob; qmk_set_trace applies to the batch-1 kernel only. */
+int qmk_set_kernel_variant(qmk_handle* h, int32_t variant);
 
 /* Optional device timeline (the counterpart of the reference's ENABLE_PROFILING clock64 buffer,
  * qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/multi_batch/decode_kernel/profiling.cuh:7-35, selected

@@ -11,8 +11,10 @@ from pathlib import Path
 
 from ._build import LIB_PATH
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 ARCH_LLAMA = 0
+ARCH_QWEN3 = 1
+MAX_BATCH = 64
 PHASES_PER_LAYER = 5
 PHASE_QKV, PHASE_ATTN, PHASE_OPROJ, PHASE_UPGATE, PHASE_DOWN = range(5)
 
@@ -26,19 +28,20 @@ class ModelDesc(C.Structure):
                 ("hidden_size", C.c_int32), ("intermediate_size", C.c_int32),
                 ("num_attention_heads", C.c_int32), ("num_key_value_heads", C.c_int32),
                 ("head_dim", C.c_int32), ("vocab_size", C.c_int32), ("rope_rows", C.c_int32),
-                ("rms_norm_eps", C.c_float), ("attn_scale", C.c_float)]
+                ("rms_norm_eps", C.c_float), ("attn_scale", C.c_float), ("qk_norm_eps", C.c_float)]
 
 
 class WeightPtrs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "qkv", "o_proj", "mlp_norm", "up_proj", "gate_proj",
                                           "down_proj", "lm_head_norm", "lm_head", "embed_tokens",
-                                          "rope_cos", "rope_sin")]
+                                          "rope_cos", "rope_sin", "q_norm", "k_norm")]
 
 
 class StatePtrs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("hidden_states", "q_post_rope", "k_cache", "v_cache", "attn_out",
                                           "silu_out", "logits", "next_token", "token_in", "out_tokens")] + \
-               [("out_tokens_len", C.c_int64), ("batch", C.c_int32), ("kv_seq_len", C.c_int32)]
+               [("out_tokens_len", C.c_int64), ("batch", C.c_int32), ("kv_seq_len", C.c_int32),
+                ("position_ids", C.c_void_p), ("active_mask", C.c_void_p)]
 
 
 class Status(C.Structure):
@@ -58,6 +61,7 @@ SYMBOLS = [
     ("qmk_set_timeout_cycles", C.c_int, [C.c_void_p, C.c_int64]),
     ("qmk_set_trace", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
     ("qmk_set_cooperative_launch", C.c_int, [C.c_void_p, C.c_int32]),
+    ("qmk_set_kernel_variant", C.c_int, [C.c_void_p, C.c_int32]),
     ("qmk_set_wait_first_dependency", C.c_int, [C.c_void_p, C.c_int32]),
     ("qmk_step_bytes", C.c_int64, [C.c_void_p, C.c_int32]),
     ("qmk_launch_count", C.c_int64, [C.c_void_p]),

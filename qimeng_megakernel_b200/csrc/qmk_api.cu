@@ -11,6 +11,7 @@
 #include <new>
 
 #include "../../include/qmk_b200.h"
+#include "qmk_batch_host.h"
 #include "qmk_megakernel.cuh"
 
 using namespace qmk;
@@ -44,7 +45,19 @@ struct qmk_handle {
   unsigned* status;
   long long* d_tok;   // [2]: token fed, token produced (host-buffer generate path)
   unsigned long long* trace;
+  // which kernels can serve this handle
+  bool tuned_shape;        // the descriptor has the compiled shape of the batch-1 kernel
+  int variant;             // 0: batch-1 kernel when possible; 1: always the batched kernel
+  qmk_batch_ctx* bctx;     // batched kernel: tensor maps + scratch (created on first need)
+  int last_kernel;         // 0 batch-1 kernel, 1 batched kernel: whose status record the next poll reads
 };
+
+static bool use_batched(const qmk_handle* h) { return !h->tuned_shape || h->variant == 1 || (h->bound && h->st.batch != 1); }
+
+static int ensure_bctx(qmk_handle* h) {
+  if (h->bctx) return QMK_OK;
+  return qmkb_create(&h->desc, &h->w, h->n_sm, &h->bctx, h->cuda_err, sizeof(h->cuda_err));
+}
 
 static int cuda_fail(qmk_handle* h, cudaError_t e, const char* what) {
   if (h) snprintf(h->cuda_err, sizeof(h->cuda_err), "%s: %s", what, cudaGetErrorString(e));
@@ -89,9 +102,10 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
   if (!d || !w || !out) return QMK_ERR_INVALID_ARG;
   *out = nullptr;
   if (d->abi_version != QMK_ABI_VERSION) return QMK_ERR_INVALID_ARG;
-  if (d->arch != QMK_ARCH_LLAMA || d->hidden_size != Shape::H || d->intermediate_size != Shape::I ||
-      d->num_attention_heads != Shape::NH || d->num_key_value_heads != Shape::NKV || d->head_dim != Shape::HD)
-    return QMK_ERR_UNSUPPORTED_MODEL;
+  const bool tuned = d->arch == QMK_ARCH_LLAMA && d->hidden_size == Shape::H && d->intermediate_size == Shape::I &&
+                     d->num_attention_heads == Shape::NH && d->num_key_value_heads == Shape::NKV &&
+                     d->head_dim == Shape::HD;
+  if (!tuned && qmkb_supported(d) != QMK_OK) return QMK_ERR_UNSUPPORTED_MODEL;
   if (d->num_layers < 0 || d->num_layers > 1024 || d->vocab_size < 1 || d->rope_rows < 1) return QMK_ERR_INVALID_ARG;
   if (!(d->rms_norm_eps > 0.f) || !(d->attn_scale > 0.f)) return QMK_ERR_INVALID_ARG;
   const void* ptrs[] = {w->attn_norm, w->qkv, w->o_proj, w->mlp_norm, w->up_proj, w->gate_proj,
@@ -99,6 +113,7 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
   for (const void* p : ptrs)
     if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
   if (w->embed_tokens && !aligned16(w->embed_tokens)) return QMK_ERR_INVALID_ARG;
+  if (d->arch == QMK_ARCH_QWEN3 && (!w->q_norm || !w->k_norm)) return QMK_ERR_INVALID_ARG;
 
   qmk_handle* h = new (std::nothrow) qmk_handle();
   if (!h) return QMK_ERR_OOM;
@@ -108,6 +123,7 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
   h->device = device;
   h->timeout_cycles = 2000000000ll;
   h->cooperative = 1;
+  h->tuned_shape = tuned;
   int rc = QMK_OK;
   do {
     cudaError_t e = cudaSetDevice(device);
@@ -115,7 +131,10 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
     cudaDeviceProp prop;
     e = cudaGetDeviceProperties(&prop, device);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaGetDeviceProperties"); break; }
+    int bsmem = 0;
+    qmkb_geometry(nullptr, nullptr, nullptr, &bsmem);
     if (prop.major != 10 || (int)prop.sharedMemPerBlockOptin < SmemLayout<Shape>::kTotal ||
+        (int)prop.sharedMemPerBlockOptin < bsmem ||
         prop.multiProcessorCount < 1 || !prop.cooperativeLaunch) {
       rc = QMK_ERR_DEVICE;
       break;
@@ -152,9 +171,11 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
     h->status = (unsigned*)q;
     e = cudaMemset(h->scratch, 0, h->scratch_bytes);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaMemset"); break; }
+    if (!tuned) rc = ensure_bctx(h);
   } while (0);
   if (rc != QMK_OK) {
     if (h->scratch) cudaFree(h->scratch);
+    qmkb_destroy(h->bctx);
     delete h;
     return rc;
   }
@@ -166,12 +187,13 @@ extern "C" void qmk_destroy(qmk_handle* h) {
   if (!h) return;
   cudaSetDevice(h->device);
   if (h->scratch) cudaFree(h->scratch);
+  qmkb_destroy(h->bctx);
   delete h;
 }
 
 extern "C" int qmk_bind_state(qmk_handle* h, const qmk_state_ptrs* s) {
   if (!h || !s) return QMK_ERR_INVALID_ARG;
-  if (s->batch != 1 || s->kv_seq_len < 1) return QMK_ERR_INVALID_ARG;
+  if (s->batch < 1 || s->batch > 64 || s->kv_seq_len < 1) return QMK_ERR_INVALID_ARG;
   void* ptrs[] = {s->hidden_states, s->q_post_rope, s->k_cache, s->v_cache, s->attn_out, s->silu_out, s->logits};
   for (void* p : ptrs)
     if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
@@ -179,6 +201,28 @@ extern "C" int qmk_bind_state(qmk_handle* h, const qmk_state_ptrs* s) {
   if (s->out_tokens && s->out_tokens_len < 1) return QMK_ERR_INVALID_ARG;
   h->st = *s;
   h->bound = true;
+  if (use_batched(h)) {
+    QMK_CUDA(h, cudaSetDevice(h->device));
+    return ensure_bctx(h);
+  }
+  return QMK_OK;
+}
+
+static int batched_launch(qmk_handle* h, int pos, int phase_begin, int phase_end, int wait_first, cudaStream_t stream) {
+  int rc = ensure_bctx(h);
+  if (rc) return rc;
+  qmkb_launch_args a;
+  a.pos = pos;
+  a.phase_begin = phase_begin;
+  a.phase_end = phase_end;
+  a.wait_first = wait_first;
+  a.cooperative = h->cooperative;
+  a.timeout_cycles = h->timeout_cycles;
+  rc = qmkb_launch(h->bctx, &h->st, &a, stream, h->cuda_err, sizeof(h->cuda_err));
+  if (rc) return rc;
+  h->launches++;
+  h->last_stream = stream;
+  h->last_kernel = 1;
   return QMK_OK;
 }
 
@@ -246,6 +290,7 @@ static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
   QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p));
   h->launches++;
   h->last_stream = stream;
+  h->last_kernel = 0;
   return QMK_OK;
 }
 
@@ -272,6 +317,7 @@ extern "C" int qmk_decode_step(qmk_handle* h, int32_t pos_id, void* cuda_stream)
   int rc = check_step_args(h, pos_id);
   if (rc) return rc;
   QMK_CUDA(h, cudaSetDevice(h->device));
+  if (use_batched(h)) return batched_launch(h, pos_id, 0, num_phases(h->desc.num_layers), 0, (cudaStream_t)cuda_stream);
   Params p;
   fill_params(h, p, pos_id);
   return step_with(h, p, (cudaStream_t)cuda_stream);
@@ -286,6 +332,17 @@ extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin
     return QMK_ERR_INVALID_ARG;
   QMK_CUDA(h, cudaSetDevice(h->device));
   cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (use_batched(h)) {
+    if (mode == 0) {
+      for (int ph = phase_begin; ph < phase_end; ++ph) {
+        rc = batched_launch(h, pos_id, ph, ph + 1, 0, stream);
+        if (rc) return rc;
+      }
+      return QMK_OK;
+    }
+    if (phase_begin == phase_end) return QMK_OK;
+    return batched_launch(h, pos_id, phase_begin, phase_end, h->wait_first, stream);
+  }
   Params p;
   fill_params(h, p, pos_id);
   if (mode == 0) {
@@ -325,15 +382,27 @@ extern "C" int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t ho
   if (rc) return rc;
   QMK_CUDA(h, cudaSetDevice(h->device));
   cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (h->st.batch != 1) return QMK_ERR_INVALID_ARG;
+  const bool batched = use_batched(h);
+  const qmk_state_ptrs saved = h->st;
   for (int i = 0; i < n_steps; ++i) {
     const int pos = first_pos + i;
     QMK_CUDA(h, cudaMemcpyAsync(h->d_tok, host_tokens + pos, sizeof(int64_t), cudaMemcpyHostToDevice, stream));
-    Params p;
-    fill_params(h, p, pos);
-    p.token_in = h->d_tok;
-    p.next_token = h->d_tok + 1;
-    p.out_tokens = nullptr;
-    rc = step_with(h, p, stream);
+    if (batched) {
+      h->st.token_in = (const int64_t*)h->d_tok;
+      h->st.next_token = (int64_t*)(h->d_tok + 1);
+      h->st.out_tokens = nullptr;
+      h->st.position_ids = nullptr;
+      rc = batched_launch(h, pos, 0, num_phases(h->desc.num_layers), 0, stream);
+      h->st = saved;
+    } else {
+      Params p;
+      fill_params(h, p, pos);
+      p.token_in = h->d_tok;
+      p.next_token = h->d_tok + 1;
+      p.out_tokens = nullptr;
+      rc = step_with(h, p, stream);
+    }
     if (rc) return rc;
     int64_t* dst = teacher_forced ? host_argmax + i : host_tokens + pos + 1;
     QMK_CUDA(h, cudaMemcpyAsync(dst, h->d_tok + 1, sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
@@ -347,7 +416,8 @@ extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
   QMK_CUDA(h, cudaSetDevice(h->device));
   QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
   unsigned words[8];
-  QMK_CUDA(h, cudaMemcpy(words, h->status, sizeof(words), cudaMemcpyDeviceToHost));
+  unsigned* status = (h->last_kernel == 1 && h->bctx) ? qmkb_status_ptr(h->bctx) : h->status;
+  QMK_CUDA(h, cudaMemcpy(words, status, sizeof(words), cudaMemcpyDeviceToHost));
   out->code = (int32_t)words[kStCode];
   out->sm = (int32_t)words[kStSm];
   out->warp = (int32_t)words[kStWarp];
@@ -360,6 +430,10 @@ extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
     // The aborted launch left half-written tagged words: start over from a clean slate.
     int rc = reset_scratch(h, h->last_stream);
     if (rc) return rc;
+    if (h->bctx) {
+      rc = qmkb_reset(h->bctx, h->last_stream);
+      if (rc) return rc;
+    }
     QMK_CUDA(h, cudaMemsetAsync(h->status, 0, 32, h->last_stream));
     QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
     return QMK_ERR_DEVICE_TIMEOUT;
@@ -382,6 +456,16 @@ extern "C" int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes) 
   return QMK_OK;
 }
 
+extern "C" int qmk_set_kernel_variant(qmk_handle* h, int32_t variant) {
+  if (!h || (variant != 0 && variant != 1)) return QMK_ERR_INVALID_ARG;
+  h->variant = variant;
+  if (use_batched(h)) {
+    QMK_CUDA(h, cudaSetDevice(h->device));
+    return ensure_bctx(h);
+  }
+  return QMK_OK;
+}
+
 extern "C" int qmk_set_cooperative_launch(qmk_handle* h, int32_t on) {
   if (!h) return QMK_ERR_INVALID_ARG;
   h->cooperative = on ? 1 : 0;
@@ -397,18 +481,25 @@ extern "C" int qmk_set_wait_first_dependency(qmk_handle* h, int32_t on) {
 extern "C" int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id) {
   if (!h) return 0;
   const qmk_model_desc& d = h->desc;
-  const long long H = d.hidden_size, I = d.intermediate_size, QKV = Shape::QKV_ROWS, QD = Shape::QDIM;
+  const long long H = d.hidden_size, I = d.intermediate_size;
+  const long long QKV = (long long)(d.num_attention_heads + 2 * d.num_key_value_heads) * d.head_dim;
+  const long long QD = (long long)d.num_attention_heads * d.head_dim;
   const long long per_layer = 2 * (QKV * H + H * QD + 2 * I * H + H * I);
   const long long lm = 2ll * d.vocab_size * H;
-  const long long kv_row = 2ll * Shape::NKV * Shape::HD * 2;   // K and V, bf16
+  const long long kv_row = 2ll * d.num_key_value_heads * d.head_dim * 2;   // K and V, bf16
   const long long T = (long long)pos_id + 1;
-  return d.num_layers * per_layer + lm + d.num_layers * kv_row * T + d.num_layers * kv_row;
+  const long long B = h->bound ? h->st.batch : 1;   // every row at pos_id: weights once, KV per sequence
+  return d.num_layers * per_layer + lm + B * (d.num_layers * kv_row * T + d.num_layers * kv_row);
 }
 
 extern "C" int64_t qmk_launch_count(const qmk_handle* h) { return h ? h->launches : 0; }
 
 extern "C" int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes) {
   if (!h) return QMK_ERR_INVALID_ARG;
+  if (use_batched(h) && h->bctx) {
+    qmkb_geometry(h->bctx, ctas, threads, smem_bytes);
+    return QMK_OK;
+  }
   if (ctas) *ctas = h->n_sm;
   if (threads) *threads = kLaunchThreads;
   if (smem_bytes) *smem_bytes = SmemLayout<Shape>::kTotal;

@@ -1,0 +1,255 @@
+// Host side of the batched decode kernel: tensor maps of the weight matrices, scratch, launch.
+// The reference's multi-batch launcher fills a globals POD from torch tensors and launches one kernel per
+// step (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/multi_batch/decode_kernel/mk.cu); here the
+// descriptor is plain data, scratch is owned by the context and errors are returned.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "qmk_batch_host.h"
+#include "qmk_batch_kernel.cuh"
+
+using namespace qmkb;
+
+struct qmk_batch_ctx {
+  qmk_model_desc desc;
+  qmk_weight_ptrs w;
+  int n_sm;
+  TensorMaps maps;
+  unsigned char* scratch;
+  size_t scratch_bytes;
+  // regions of the scratch
+  float* ws;
+  float* ss;
+  float* attn_part;
+  unsigned char* zero_begin;   // [phase_done | tile_tickets | attn_tickets | argmax_key]: zeroed before every launch
+  size_t zero_bytes;
+  unsigned* phase_done;
+  unsigned* tile_tickets;
+  unsigned* attn_tickets;
+  unsigned long long* argmax_key;
+  unsigned* status;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static int fail(char* err, size_t n, const char* what, cudaError_t e) {
+  if (err && n) snprintf(err, n, "%s: %s", what, cudaGetErrorString(e));
+  return QMK_ERR_CUDA;
+}
+
+int qmkb_supported(const qmk_model_desc* d) {
+  const int H = d->hidden_size, I = d->intermediate_size, NH = d->num_attention_heads, NKV = d->num_key_value_heads,
+            HD = d->head_dim;
+  if (d->arch != QMK_ARCH_LLAMA && d->arch != QMK_ARCH_QWEN3) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (HD != 64 && HD != 128) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (NH < 1 || NKV < 1 || NH % NKV != 0) return QMK_ERR_UNSUPPORTED_MODEL;
+  const int gq = NH / NKV;
+  if (gq != 1 && gq != 2 && gq != 4) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (H < kBlockK || H % kBlockK != 0 || H > 8192 || I < kBlockK || I % kBlockK != 0) return QMK_ERR_UNSUPPORTED_MODEL;
+  if ((NH * HD) % kBlockK != 0 || NKV > 64) return QMK_ERR_UNSUPPORTED_MODEL;
+  return QMK_OK;
+}
+
+typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// bf16 matrix [layers, rows, k] row-major -> 3-D map {k, rows, layers}, box {64, box_rows, 1}, 128-byte swizzle,
+// rows past the end read as zero.
+static int make_map(encode_fn enc, CUtensorMap* m, const void* base, long long k, long long rows, long long layers,
+                    int box_rows) {
+  const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)(layers > 0 ? layers : 1)};
+  const cuuint64_t strides[2] = {(cuuint64_t)k * 2, (cuuint64_t)k * 2 * (cuuint64_t)rows};
+  const cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows, 1};
+  const cuuint32_t es[3] = {1, 1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk_batch_ctx** out, char* err, size_t errlen) {
+  *out = nullptr;
+  int rc = qmkb_supported(d);
+  if (rc) return rc;
+  if (d->arch == QMK_ARCH_QWEN3 && (!w->q_norm || !w->k_norm)) return QMK_ERR_INVALID_ARG;
+  qmk_batch_ctx* c = new (std::nothrow) qmk_batch_ctx();
+  if (!c) return QMK_ERR_OOM;
+  memset(c, 0, sizeof(*c));
+  c->desc = *d;
+  c->w = *w;
+  c->n_sm = n_sm;
+  const int H = d->hidden_size, I = d->intermediate_size, NH = d->num_attention_heads, NKV = d->num_key_value_heads,
+            HD = d->head_dim, L = d->num_layers, V = d->vocab_size;
+  const int QKV = (NH + 2 * NKV) * HD, QD = NH * HD;
+  do {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess) {
+      rc = fail(err, errlen, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)", e);
+      break;
+    }
+    encode_fn enc = (encode_fn)fn;
+    int bad = 0;
+    if (L > 0) {
+      bad |= make_map(enc, &c->maps.qkv, w->qkv, H, QKV, L, kTileRows);
+      bad |= make_map(enc, &c->maps.o_proj, w->o_proj, QD, H, L, kTileRows);
+      bad |= make_map(enc, &c->maps.up, w->up_proj, H, I, L, kTileRows / 2);
+      bad |= make_map(enc, &c->maps.gate, w->gate_proj, H, I, L, kTileRows / 2);
+      bad |= make_map(enc, &c->maps.down, w->down_proj, I, H, L, kTileRows);
+    }
+    bad |= make_map(enc, &c->maps.lm_head, w->lm_head, H, V, 1, kTileRows);
+    if (bad) {
+      if (err && errlen) snprintf(err, errlen, "cuTensorMapEncodeTiled failed (CUresult %d)", bad);
+      rc = QMK_ERR_CUDA;
+      break;
+    }
+    e = cudaFuncSetAttribute(qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+    if (e != cudaSuccess) { rc = fail(err, errlen, "cudaFuncSetAttribute", e); break; }
+
+    int max_tiles = (V + kTileRows - 1) / kTileRows;
+    const int t_upgate = (I + kTileRows / 2 - 1) / (kTileRows / 2), t_qkv = (QKV + kTileRows - 1) / kTileRows;
+    if (t_upgate > max_tiles) max_tiles = t_upgate;
+    if (t_qkv > max_tiles) max_tiles = t_qkv;
+    if ((H + kTileRows - 1) / kTileRows > max_tiles) max_tiles = (H + kTileRows - 1) / kTileRows;
+    const int gq = NH / NKV;
+    const size_t b_ws = align_up((size_t)n_sm * 2 * kTileRows * kMaxBatch * 4, 256);
+    const size_t b_ss = align_up((size_t)((H + kTileRows - 1) / kTileRows) * kMaxBatch * 4, 256);
+    const size_t b_part = align_up(((size_t)n_sm * 8 + (size_t)kMaxBatch * NKV) * gq * (HD + 2) * 4, 256);
+    const size_t b_done = align_up((size_t)(5 * L + 1 + 2) * 4, 256);
+    const size_t b_tt = align_up((size_t)max_tiles * 4, 256);
+    const size_t b_at = align_up((size_t)kMaxBatch * NKV * 4, 256);
+    const size_t b_am = align_up((size_t)kMaxBatch * 8, 256);
+    const size_t b_status = 256;
+    c->scratch_bytes = b_ws + b_ss + b_part + b_done + b_tt + b_at + b_am + b_status;
+    e = cudaMalloc((void**)&c->scratch, c->scratch_bytes);
+    if (e != cudaSuccess) { rc = QMK_ERR_OOM; fail(err, errlen, "cudaMalloc", e); break; }
+    unsigned char* q = c->scratch;
+    c->ws = (float*)q; q += b_ws;
+    c->ss = (float*)q; q += b_ss;
+    c->attn_part = (float*)q; q += b_part;
+    c->zero_begin = q;
+    c->phase_done = (unsigned*)q; q += b_done;
+    c->tile_tickets = (unsigned*)q; q += b_tt;
+    c->attn_tickets = (unsigned*)q; q += b_at;
+    c->argmax_key = (unsigned long long*)q; q += b_am;
+    c->zero_bytes = (size_t)(q - c->zero_begin);
+    c->status = (unsigned*)q;
+    e = cudaMemset(c->scratch, 0, c->scratch_bytes);
+    if (e != cudaSuccess) { rc = fail(err, errlen, "cudaMemset", e); break; }
+  } while (0);
+  if (rc != QMK_OK) {
+    if (c->scratch) cudaFree(c->scratch);
+    delete c;
+    return rc;
+  }
+  *out = c;
+  return QMK_OK;
+}
+
+void qmkb_destroy(qmk_batch_ctx* c) {
+  if (!c) return;
+  if (c->scratch) cudaFree(c->scratch);
+  delete c;
+}
+
+unsigned* qmkb_status_ptr(qmk_batch_ctx* c) { return c->status; }
+size_t qmkb_scratch_bytes(const qmk_batch_ctx* c) { return c->scratch_bytes; }
+
+int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream) {
+  const cudaError_t e = cudaMemsetAsync(c->scratch, 0, c->scratch_bytes, stream);
+  return e == cudaSuccess ? QMK_OK : QMK_ERR_CUDA;
+}
+
+void qmkb_geometry(const qmk_batch_ctx* c, int* ctas, int* threads, int* smem_bytes) {
+  if (ctas && c) *ctas = c->n_sm;
+  if (threads) *threads = kBatchThreads;
+  if (smem_bytes) *smem_bytes = Smem::kTotal;
+}
+
+int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_args* a, cudaStream_t stream, char* err,
+                size_t errlen) {
+  const qmk_model_desc& d = c->desc;
+  BParams p;
+  memset(&p, 0, sizeof(p));
+  p.attn_norm = (const uint16_t*)c->w.attn_norm;
+  p.mlp_norm = (const uint16_t*)c->w.mlp_norm;
+  p.lm_norm = (const uint16_t*)c->w.lm_head_norm;
+  p.q_norm = d.arch == QMK_ARCH_QWEN3 ? (const uint16_t*)c->w.q_norm : nullptr;
+  p.k_norm = d.arch == QMK_ARCH_QWEN3 ? (const uint16_t*)c->w.k_norm : nullptr;
+  p.embed = (const uint16_t*)c->w.embed_tokens;
+  p.rope_cos = c->w.rope_cos;
+  p.rope_sin = c->w.rope_sin;
+  p.hidden = (uint16_t*)st->hidden_states;
+  p.q_post_rope = (uint16_t*)st->q_post_rope;
+  p.k_cache = (uint16_t*)st->k_cache;
+  p.v_cache = (uint16_t*)st->v_cache;
+  p.attn_out = (uint16_t*)st->attn_out;
+  p.silu_out = (uint16_t*)st->silu_out;
+  p.logits = (uint16_t*)st->logits;
+  p.next_token = (long long*)st->next_token;
+  p.token_in = (const long long*)st->token_in;
+  p.out_tokens = (long long*)st->out_tokens;
+  p.out_tokens_len = st->out_tokens_len;
+  p.position_ids = st->position_ids;
+  p.active_mask = st->active_mask;
+  p.kv_seq_stride = (long long)d.num_key_value_heads * d.head_dim;
+  p.kv_batch_stride = (long long)st->kv_seq_len * p.kv_seq_stride;
+  p.kv_layer_stride = (long long)st->batch * p.kv_batch_stride;
+  p.ws = c->ws;
+  p.tile_tickets = c->tile_tickets;
+  p.ss = c->ss;
+  p.attn_part = c->attn_part;
+  p.attn_tickets = c->attn_tickets;
+  p.argmax_key = c->argmax_key;
+  p.phase_done = c->phase_done;
+  p.status = c->status;
+  p.H = d.hidden_size;
+  p.I = d.intermediate_size;
+  p.NH = d.num_attention_heads;
+  p.NKV = d.num_key_value_heads;
+  p.HD = d.head_dim;
+  p.QKV_ROWS = (p.NH + 2 * p.NKV) * p.HD;
+  p.QDIM = p.NH * p.HD;
+  p.num_layers = d.num_layers;
+  p.vocab = d.vocab_size;
+  p.B = st->batch;
+  p.Bpad = (st->batch + 15) / 16 * 16;
+  p.pos = a->pos;
+  p.phase_begin = a->phase_begin;
+  p.phase_end = a->phase_end;
+  p.wait_first = a->wait_first;
+  p.eps = d.rms_norm_eps;
+  p.qk_eps = d.qk_norm_eps > 0.f ? d.qk_norm_eps : d.rms_norm_eps;
+  p.scale_log2e = d.attn_scale * 1.4426950408889634f;
+  p.timeout_cycles = a->timeout_cycles;
+  // The first phase of the launch, when it starts with an RMSNorm, needs the sums of squares of the residual
+  // stream: computed by a prologue (with the embedding of token_in when the step starts at phase 0).
+  if (a->phase_begin < a->phase_end) {
+    const int k0 = phase_kind(a->phase_begin, p.num_layers);
+    if (k0 == kQkv || k0 == kUpGate || k0 == kLmHead)
+      p.prologue = (a->phase_begin == 0 && st->token_in != nullptr) ? 2 : 1;
+  }
+  if (a->wait_first) p.prologue = 0;
+
+  cudaError_t e = cudaMemsetAsync(c->zero_begin, 0, c->zero_bytes, stream);
+  if (e != cudaSuccess) return fail(err, errlen, "cudaMemsetAsync", e);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)c->n_sm);
+  cfg.blockDim = dim3(kBatchThreads);
+  cfg.dynamicSmemBytes = Smem::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another
+  attr[0].val.cooperative = a->cooperative;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, qmk_batch_kernel, p, c->maps);
+  if (e != cudaSuccess) return fail(err, errlen, "cudaLaunchKernelEx(qmk_batch_kernel)", e);
+  return QMK_OK;
+}

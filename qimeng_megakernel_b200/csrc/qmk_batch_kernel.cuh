@@ -1,0 +1,940 @@
+// Batched decode megakernel for sm_100a: B sequences per step, runtime model shape.
+//
+// One persistent CTA per SM, ten warps with fixed roles:
+//   warp 0      producer   one lane streams the CTA's weight tiles (TMA tensor copies, 128-byte swizzle)
+//   warp 1      issuer     one lane issues tcgen05.mma (M = 128 weight rows, N = padded batch, K = 16)
+//   warps 2-5   epilogue   read accumulators from tensor memory, finish the phase's arithmetic
+//   warps 6-9   stagers    build the activation operand ([batch, 64] bf16, RMSNorm applied) in shared memory
+// In the attention phase warps 2-9 are eight attention workers.
+//
+// Every projection is a stream-K GEMM  out[b, n] = sum_k X[b, k] * W[n, k]:  the (row tile, k-block)
+// units of a phase, 128 x 64 weights = 16 KiB each, are dealt to the CTAs as equal contiguous ranges,
+// so every SM streams the same number of bytes whatever the matrix shape.  A maximal run of units of
+// one row tile is a SEGMENT, accumulated in tensor memory.  A segment that covers the whole K is
+// finished by its CTA; otherwise the partial tile goes to a per-CTA scratch slot and the CTA that
+// arrives last at the tile's ticket adds the partials in CTA order (fixed order: results do not depend
+// on timing) and runs the epilogue.  The reference splits K in the down-projection only and adds the
+// partials with bf16 compare-and-swap in arrival order
+// (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/down_proj_gemv_residual.cu:39-52).
+//
+// Phases are separated by grid-wide arrival counters (one per phase, zeroed by the host before the
+// launch); the weight stream runs ahead across them.  What each phase computes, rounding points
+// included, follows the reference's fused PyTorch ops for [B, H] state
+// (.../A100/single_batch/decode_schedule/fused/operations.py:126-321; per-row positions and the active
+// mask as in decode_pos_id / row_active there; Qwen3's per-head Q/K RMSNorm:
+// qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/decode_schedule/fused/operations.py:52-120).
+//
+// Every wait is bounded.  A wait that expires records a status, raises the CTA's abort word; from then
+// on every wait in the CTA returns at once, work is skipped, the barriers inside the CTA are still
+// executed (trip counts do not depend on data), and all roles meet at the common exit where copies in
+// flight are waited for and the tensor memory is freed.
+#pragma once
+#include <cuda.h>
+
+#include "qmk_batch_params.h"
+#include "qmk_batch_schedule.h"
+#include "qmk_device.cuh"
+#include "qmk_params.h"
+
+namespace qmkb {
+
+using namespace qmk;
+
+constexpr int kStages = 7;
+constexpr int kABytes = kTileRows * kBlockK * 2;        // 16 KiB of weights per unit
+constexpr int kBBytes = kMaxBatch * kBlockK * 2;        // 8 KiB of activations per unit
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kExchStride = kMaxBatch + 1;              // floats per row of the exchange tile
+constexpr int kNumWarps = 10;
+constexpr int kBatchThreads = kNumWarps * 32;
+constexpr int kEpiWarp0 = 2, kStgWarp0 = 6;
+constexpr int kBarEpi = 1, kBarStg = 2, kBarAttn = 3;   // named barriers (0 is __syncthreads)
+
+struct Smem {
+  static constexpr int kOffStages = 0;                                        // 1024-byte aligned
+  static constexpr int kOffExch = kOffStages + kStages * kStageBytes;         // fp32 [128][65]
+  static constexpr int kOffBars = kOffExch + kTileRows * kExchStride * 4;     // mbarriers
+  //   a_full[kStages] b_full[kStages] empty[kStages] acc_full[2] acc_empty[2]
+  static constexpr int kNumBars = 3 * kStages + 4;
+  static constexpr int kOffRs = kOffBars + kNumBars * 8;                      // float [64]  rsqrt factors
+  static constexpr int kOffHs = kOffRs + kMaxBatch * 4;                       // float [2][64] per-head sums
+  static constexpr int kOffPos = kOffHs + 2 * kMaxBatch * 4;                  // int [64]
+  static constexpr int kOffAct = kOffPos + kMaxBatch * 4;                     // int [64]
+  static constexpr int kOffCtl = kOffAct + kMaxBatch * 4;                     // control words
+  static constexpr int kUsed = kOffCtl + 64;
+  static constexpr int kTotal = kUsed + 1024;   // slack to place the stages on a 1024-byte boundary (swizzle atoms)
+};
+// control words: [0] abort  [1] tensor-memory base  [2] Tmax  [3] flag of the epilogue group  [4] flag of the stagers
+// [5] flag of the attention group
+constexpr int kCAbort = 0, kCTmem = 1, kCTmax = 2, kCFlagEpi = 3, kCFlagStg = 4, kCFlagAttn = 5;
+
+struct TensorMaps {
+  CUtensorMap qkv, o_proj, up, gate, down, lm_head;   // 3-D {k, row, layer}; box {64, 128 (up/gate: 64), 1}
+};
+
+// ------------------------------------------------------------------------------------------------
+// small device helpers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void named_bar(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive1(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// Shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// D (f32, tensor memory) = A (bf16, K-major) x B (bf16, K-major), M = 128: the accumulator is overwritten.
+__device__ __forceinline__ void mma_bf16_set(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.u32 p, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(da), "l"(db), "r"(idesc)
+      : "memory");
+}
+// D += A x B.
+__device__ __forceinline__ void mma_bf16_add(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.eq.u32 p, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(da), "l"(db), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+static __device__ __noinline__ void report(const BParams& p, int code, int warp, int phase, unsigned seen, unsigned expected,
+                                           int detail) {
+  if (atomicCAS(&p.status[kStCode], 0u, (unsigned)code) == 0u) {
+    p.status[kStSm] = blockIdx.x;
+    p.status[kStWarp] = warp;
+    p.status[kStPhase] = phase;
+    p.status[kStSeen] = seen;
+    p.status[kStExpected] = expected;
+    p.status[kStDetail] = detail;
+    __threadfence();
+  }
+}
+
+struct Ctx {
+  const BParams* p;
+  unsigned char* smem;
+  volatile unsigned* ctl;
+  uint32_t bars;     // shared address of the mbarriers
+  int warp, lane;
+  __device__ __forceinline__ uint32_t a_full(int s) const { return bars + s * 8; }
+  __device__ __forceinline__ uint32_t b_full(int s) const { return bars + (kStages + s) * 8; }
+  __device__ __forceinline__ uint32_t empty(int s) const { return bars + (2 * kStages + s) * 8; }
+  __device__ __forceinline__ uint32_t acc_full(int b) const { return bars + (3 * kStages + b) * 8; }
+  __device__ __forceinline__ uint32_t acc_empty(int b) const { return bars + (3 * kStages + 2 + b) * 8; }
+  __device__ __forceinline__ bool aborted() const { return ctl[kCAbort] != 0u; }
+};
+
+// Bounded wait on an mbarrier phase.  False when the budget expired or the CTA is aborting.
+static __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity, int phase, int detail) {
+  const long long t0 = clock64();
+  for (unsigned it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (c.ctl[kCAbort] != 0u) return false;
+      // (twice the budget of a dependency wait: these waits sit downstream of one, which should be the one to report)
+      if (clock64() - t0 > 2 * c.p->timeout_cycles) {
+        report(*c.p, kErrCopyWait, c.warp, phase, parity, bar, detail);
+        c.ctl[kCAbort] = 1u;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity, int phase, int detail) {
+  if (c.ctl[kCAbort] != 0u) return false;
+  return mbar_try_wait(bar, parity) || mbar_wait_slow(c, bar, parity, phase, detail);
+}
+
+// Bounded wait until `*counter` reaches `target` (arrivals of all CTAs at the end of a phase).
+static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* counter, unsigned target, int phase) {
+  if (c.ctl[kCAbort] != 0u) return false;
+  const long long t0 = clock64();
+  for (unsigned it = 1;; ++it) {
+    const unsigned v = ld_acquire_gpu(counter);
+    if (v >= target) return true;
+    if ((it & 15u) == 0u) {
+      if (c.ctl[kCAbort] != 0u) return false;
+      if (clock64() - t0 > c.p->timeout_cycles) {
+        report(*c.p, kErrCounterWait, c.warp, phase, v, target, 0);
+        c.ctl[kCAbort] = 1u;
+        return false;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// producer (one thread)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, unsigned& n_issued) {
+  const BParams& p = *c.p;
+  const uint32_t stages = smem_u32(c.smem + Smem::kOffStages);
+  const uint64_t policy = l2_policy_evict_first();
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  unsigned n = 0;
+#pragma unroll 1
+  for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
+    const int kind = phase_kind(ph, p.num_layers);
+    if (kind == kAttn) continue;
+    const int layer = kind == kLmHead ? 0 : ph / 5;
+    const PhaseDims d = phase_dims(p, kind);
+    int lo, hi;
+    unit_range(d.T * d.KB, G, cta, lo, hi);
+    const CUtensorMap* map = kind == kQkv ? &maps.qkv : kind == kOproj ? &maps.o_proj : kind == kUpGate ? &maps.up
+                           : kind == kDown ? &maps.down : &maps.lm_head;
+    int t = lo / d.KB, kb = lo - t * d.KB;
+#pragma unroll 1
+    for (int u = lo; u < hi; ++u, ++n) {
+      const int s = (int)(n % kStages);
+      if (n >= (unsigned)kStages && !mbar_wait(c, c.empty(s), ((n / kStages) - 1u) & 1u, ph, 1)) {
+        n_issued = n;
+        return;
+      }
+      const uint32_t dst = stages + s * kStageBytes;
+      mbar_expect_tx(c.a_full(s), (uint32_t)kABytes);
+      if (kind == kUpGate) {
+        tma_load_3d(dst, map, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
+        tma_load_3d(dst + kABytes / 2, &maps.gate, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
+      } else {
+        tma_load_3d(dst, map, kb * kBlockK, t * kTileRows, layer, c.a_full(s), policy);
+      }
+      if (++kb == d.KB) { kb = 0; ++t; }
+    }
+  }
+  n_issued = n;
+}
+
+// ------------------------------------------------------------------------------------------------
+// issuer (one thread)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
+  const BParams& p = *c.p;
+  const uint32_t stages = smem_u32(c.smem + Smem::kOffStages);
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)p.Bpad >> 3) << 17) | ((128u >> 4) << 24);
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  unsigned n = 0, sg = 0;
+#pragma unroll 1
+  for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
+    const int kind = phase_kind(ph, p.num_layers);
+    if (kind == kAttn) continue;
+    const PhaseDims d = phase_dims(p, kind);
+    int lo, hi;
+    unit_range(d.T * d.KB, G, cta, lo, hi);
+    int kb = lo % d.KB;
+    bool seg_start = true;
+#pragma unroll 1
+    for (int u = lo; u < hi; ++u, ++n) {
+      const unsigned buf = sg & 1u;
+      if (seg_start && sg >= 2u && !mbar_wait(c, c.acc_empty(buf), ((sg >> 1) - 1u) & 1u, ph, 2)) return;
+      const int s = (int)(n % kStages);
+      const unsigned par = (n / kStages) & 1u;
+      if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
+      if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
+      tmem_fence_after_sync();
+      const uint64_t da = desc_sw128(stages + s * kStageBytes), db = desc_sw128(stages + s * kStageBytes + kABytes);
+      const uint32_t dcol = tmem + buf * (uint32_t)p.Bpad;
+      // (k-step k reads 32 bytes further along K: the start-address field grows by 2)
+      if (seg_start) mma_bf16_set(dcol, da, db, idesc);
+      else mma_bf16_add(dcol, da, db, idesc);
+#pragma unroll
+      for (int k = 1; k < kBlockK / 16; ++k) mma_bf16_add(dcol, da + 2u * k, db + 2u * k, idesc);
+      mma_commit(c.empty(s));
+      seg_start = false;
+      if (++kb == d.KB || u + 1 == hi) {
+        mma_commit(c.acc_full(buf));
+        ++sg;
+        kb = kb == d.KB ? 0 : kb;
+        seg_start = true;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// stagers (128 threads): activation operand of every unit
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& needed) {
+  // what must have finished before phase ph reads its input: the phase before it, or the prologue
+  const BParams& p = *c.p;
+  needed = true;
+  if (ph > p.phase_begin) return counter_wait(c, p.phase_done + ph, gridDim.x, ph);          // counter of phase ph - 1
+  if (p.prologue != 0) return counter_wait(c, p.phase_done + 0, gridDim.x, ph);
+  if (p.wait_first) return counter_wait(c, p.phase_done + (ph > 0 ? ph : num_phases(p.num_layers) + 1), gridDim.x, ph);
+  needed = false;
+  return true;
+}
+
+__device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int st, unsigned& n) {
+  // st: thread index inside the stager group, 0..127
+  const BParams& p = *c.p;
+  const int layer = kind == kLmHead ? 0 : ph / 5;
+  const PhaseDims d = phase_dims(p, kind);
+  int lo, hi;
+  unit_range(d.T * d.KB, (int)gridDim.x, (int)blockIdx.x, lo, hi);
+  if (st == 0) {
+    bool needed;
+    const bool ok = phase_dependency(c, ph, needed);
+    (void)ok;
+  }
+  named_bar(kBarStg, 128);
+  const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
+  float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
+  if (normed) {
+    if (st < p.Bpad) {
+      float tot = 0.f;
+      const int nt = (p.H + kTileRows - 1) / kTileRows;
+      for (int t = 0; t < nt; ++t) tot += ldcg_f32(p.ss + t * kMaxBatch + st);
+      rs[st] = rsqrtf(tot / (float)p.H + p.eps);
+    }
+    named_bar(kBarStg, 128);
+  }
+  const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : p.hidden;
+  const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
+                       : kind == kUpGate ? p.mlp_norm + (size_t)layer * p.H : p.lm_norm;
+  const int chunk = st & 7;           // 16-byte piece inside the 128-byte k-block row
+  const int row0 = st >> 3;           // first batch row of this thread (then +16, +32, +48)
+  int kb = lo % d.KB;
+#pragma unroll 1
+  for (int u = lo; u < hi; ++u, ++n) {
+    const int s = (int)(n % kStages);
+    const bool ok = n < (unsigned)kStages || mbar_wait(c, c.empty(s), ((n / kStages) - 1u) & 1u, ph, 5);
+    if (ok) {
+      unsigned char* dst = c.smem + Smem::kOffStages + s * kStageBytes + kABytes;
+      const int k0 = kb * kBlockK + chunk * 8;
+      uint4 g4 = make_uint4(0, 0, 0, 0);
+      if (normed) g4 = __ldg(reinterpret_cast<const uint4*>(gain + k0));
+#pragma unroll 1
+      for (int r = row0; r < p.Bpad; r += 16) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < p.B) {
+          v = ldcg_u4(src + (size_t)r * d.K + k0);
+          if (normed) {
+            const float f = rs[r];
+            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float a = bf16_round(bf_lo(w[j]) * f) * bf_lo(gw[j]);
+              const float b = bf16_round(bf_hi(w[j]) * f) * bf_hi(gw[j]);
+              w[j] = pack_bf16x2(a, b);
+            }
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
+      }
+      fence_async_smem();
+      mbar_arrive1(c.b_full(s));
+    }
+    if (++kb == d.KB) kb = 0;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// epilogues (128 threads, e = thread index in the group) on the fp32 tile exch[128][65]
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned short silu_mul(float up, float gate) {
+  // fused_mlp_upgate (operations.py:265-282): both products rounded to bf16, SiLU rounded, product rounded
+  const float g = bf16_round(gate);
+  const float sl = bf16_round(g / (1.0f + __expf(-g)));
+  return f32_to_bf16_bits(sl * bf16_round(up));
+}
+__device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, int row) {
+  return ((unsigned long long)float_ordered_bits(bf16_bits_to_f32(bits)) << 32) | (0xffffffffu - (unsigned)row);
+}
+
+__device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, int t, int e) {
+  const BParams& p = *c.p;
+  float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
+  const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
+  const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
+  const int layer = kind == kLmHead ? 0 : ph / 5;
+  const int B = p.B;
+  switch (kind) {
+    case kQkv: {
+      const int row = t * kTileRows + e;
+      const int kdim = p.NKV * p.HD;
+      const bool is_v = row >= p.QDIM + kdim;
+      const bool is_k = !is_v && row >= p.QDIM;
+      const int d = row % p.HD;
+      float* hs = reinterpret_cast<float*>(c.smem + Smem::kOffHs);
+      const int heads_in_tile = kTileRows / p.HD;          // 1 or 2
+      if (p.q_norm != nullptr) {
+        // per-head sums of squares of the bf16-rounded projections (_per_head_rms_norm, Qwen3 operations.py:52-63)
+        if (e < p.Bpad) {
+          for (int hh = 0; hh < heads_in_tile; ++hh) {
+            float s = 0.f;
+            for (int r = 0; r < p.HD; ++r) {
+              const float x = bf16_round(exch[(hh * p.HD + r) * kExchStride + e]);
+              s += x * x;
+            }
+            hs[hh * kMaxBatch + e] = s;
+          }
+        }
+        named_bar(kBarEpi, 128);
+      }
+      if (row < p.QKV_ROWS) {
+        const uint16_t* nw = is_v ? nullptr : (is_k ? p.k_norm : p.q_norm);
+        float w_self = 1.f, w_part = 1.f;
+        if (nw != nullptr) {
+          w_self = bf16_bits_to_f32(__ldg(nw + (size_t)layer * p.HD + d));
+          w_part = bf16_bits_to_f32(__ldg(nw + (size_t)layer * p.HD + (d ^ 1)));
+        }
+        const int hh = e / p.HD;
+        for (int b = 0; b < B; ++b) {
+          if (!act_s[b]) continue;
+          float x = bf16_round(exch[e * kExchStride + b]);
+          float y = bf16_round(exch[(e ^ 1) * kExchStride + b]);
+          const int pos = pos_s[b];
+          unsigned short bits;
+          if (is_v) {
+            bits = f32_to_bf16_bits(x);
+          } else {
+            if (nw != nullptr) {
+              const float f = rsqrtf(hs[hh * kMaxBatch + b] / (float)p.HD + p.qk_eps);
+              x = bf16_round(w_self * (x * f));
+              y = bf16_round(w_part * (y * f));
+            }
+            const float cs = __ldg(p.rope_cos + (size_t)pos * p.HD + d);
+            const float sn = __ldg(p.rope_sin + (size_t)pos * p.HD + d);
+            const float rot = (d & 1) ? y : -y;
+            bits = f32_to_bf16_bits(x * cs + rot * sn);
+          }
+          if (!is_k && !is_v) {
+            p.q_post_rope[(size_t)b * p.QDIM + row] = bits;
+          } else {
+            const int col = is_k ? row - p.QDIM : row - p.QDIM - kdim;
+            uint16_t* cache = is_k ? p.k_cache : p.v_cache;
+            cache[(size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)pos * p.kv_seq_stride + col] = bits;
+          }
+        }
+      }
+      break;
+    }
+    case kOproj:
+    case kDown: {
+      // hidden[b, row] = bf16(hidden + bf16(projection)), zero projection for inactive rows
+      // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295)
+      const int row = t * kTileRows + e;
+      for (int b = 0; b < B; ++b) {
+        float sq = 0.f;
+        if (row < p.H) {
+          uint16_t* h = p.hidden + (size_t)b * p.H + row;
+          const float old = bf16_bits_to_f32(ldcg_u16(h));
+          const float add = act_s[b] ? bf16_round(exch[e * kExchStride + b]) : 0.f;
+          const unsigned short bits = f32_to_bf16_bits(old + add);
+          *h = bits;
+          const float nv = bf16_bits_to_f32(bits);
+          sq = nv * nv;
+        }
+        exch[e * kExchStride + b] = sq;
+      }
+      named_bar(kBarEpi, 128);
+      if (e < B) {
+        float s = 0.f;
+        for (int r = 0; r < kTileRows; ++r) s += exch[r * kExchStride + e];
+        p.ss[t * kMaxBatch + e] = s;
+      }
+      break;
+    }
+    case kUpGate: {
+      const int u = e & 63, half = e >> 6;
+      const int unit = t * (kTileRows / 2) + u;
+      if (unit < p.I) {
+        const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
+        for (int b = b0; b < b1 && b < B; ++b) {
+          const unsigned short bits =
+              act_s[b] ? silu_mul(exch[u * kExchStride + b], exch[(64 + u) * kExchStride + b]) : (unsigned short)0;
+          p.silu_out[(size_t)b * p.I + unit] = bits;
+        }
+      }
+      break;
+    }
+    default: {   // LM head: logits and the per-row arg-max (lowest index on ties)
+      const int row = t * kTileRows + e;
+      if (row < p.vocab) {
+        for (int b = 0; b < B; ++b) {
+          const float v = act_s[b] ? exch[e * kExchStride + b] : -1e9f;
+          p.logits[(size_t)b * p.vocab + row] = f32_to_bf16_bits(v);
+        }
+      }
+      if (e < B) {
+        unsigned long long best = 0ull;
+        const int nrow = min(kTileRows, p.vocab - t * kTileRows);
+        for (int r = 0; r < nrow; ++r) {
+          const float v = act_s[e] ? exch[r * kExchStride + e] : -1e9f;
+          const unsigned long long key = argmax_key(f32_to_bf16_bits(v), t * kTileRows + r);
+          best = key > best ? key : best;
+        }
+        atomicMax(p.argmax_key + e, best);
+      }
+      break;
+    }
+  }
+}
+
+__device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, uint32_t tmem, int e, unsigned& sg) {
+  // e: thread index in the epilogue group; the warp's lane quarter of tensor memory is (warp % 4)
+  const BParams& p = *c.p;
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const PhaseDims d = phase_dims(p, kind);
+  const int U = d.T * d.KB;
+  int lo, hi;
+  unit_range(U, G, cta, lo, hi);
+  float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
+  const int quarter = c.warp & 3;
+  const int r = quarter * 32 + c.lane;           // accumulator row (= tile row) of this thread
+  const int nchunk = p.Bpad / 16;
+  int u = lo;
+#pragma unroll 1
+  while (u < hi) {
+    const int t = u / d.KB, kb_lo = u - t * d.KB;
+    const int u_end = min(hi, (t + 1) * d.KB);
+    const bool full = kb_lo == 0 && u_end == (t + 1) * d.KB;
+    const unsigned buf = sg & 1u;
+    const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
+    float* slot = p.ws + ((size_t)cta * 2 + (t == lo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad);
+    if (ok) {
+      tmem_fence_after_sync();
+#pragma unroll 1
+      for (int ch = 0; ch < nchunk; ++ch) {
+        uint32_t v[16];
+        tmem_ld16(v, tmem + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)p.Bpad + ch * 16);
+        tmem_wait_ld();
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) exch[r * kExchStride + ch * 16 + j] = __uint_as_float(v[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(slot + ((size_t)(ch * 4 + j) * kTileRows + r) * 4) =
+                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+      }
+      tmem_fence_before_sync();
+      mbar_arrive1(c.acc_empty(buf));
+    }
+    ++sg;
+    // One thread decides for the group whether this CTA finishes the tile: a full segment always does;
+    // a partial one publishes its tile, takes a ticket, and the last of the tile's segments to arrive
+    // adds the partials in CTA order.
+    const int c_first = unit_owner(U, G, t * d.KB), c_last = unit_owner(U, G, (t + 1) * d.KB - 1);
+    if (!full) __threadfence();
+    named_bar(kBarEpi, 128);
+    if (e == 0) {
+      unsigned fin = 0u;
+      if (ok && !c.aborted()) {
+        if (full) {
+          fin = 1u;
+        } else {
+          const unsigned old = atom_add_acq_rel_gpu(p.tile_tickets + t, 1u);
+          fin = old + 1u == (unsigned)tile_segments(U, G, d.KB, t) ? 1u : 0u;
+          if (fin) p.tile_tickets[t] = 0u;
+        }
+      }
+      c.ctl[kCFlagEpi] = fin;
+    }
+    named_bar(kBarEpi, 128);
+    const bool run = c.ctl[kCFlagEpi] != 0u;
+    if (run && !full) {
+      __threadfence();
+#pragma unroll 1
+      for (int ch4 = 0; ch4 < p.Bpad / 4; ++ch4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int cc = c_first; cc <= c_last; ++cc) {
+          int clo, chi;
+          unit_range(U, G, cc, clo, chi);
+          if (clo == chi) continue;   // a CTA without units (fewer units than CTAs)
+          const float* sl = p.ws + ((size_t)cc * 2 + (t == clo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad);
+          const float4 x = __ldcg(reinterpret_cast<const float4*>(sl + ((size_t)ch4 * kTileRows + r) * 4));
+          acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        float* o = exch + r * kExchStride + ch4 * 4;
+        o[0] = acc.x; o[1] = acc.y; o[2] = acc.z; o[3] = acc.w;
+      }
+    }
+    named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
+    if (run) epilogue_tile(c, ph, kind, t, e);
+    else if ((kind == kQkv && p.q_norm != nullptr) || kind == kOproj || kind == kDown)
+      named_bar(kBarEpi, 128);         // keep the barrier count of epilogue_tile
+    named_bar(kBarEpi, 128);           // the exchange tile is free again
+    u = u_end;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// attention: eight workers per CTA, one (sequence, kv head, key range) item per warp at a time
+// ------------------------------------------------------------------------------------------------
+template <int HD, int GQ>
+__device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw) {
+  const BParams& p = *c.p;
+  constexpr int LPR = HD / 8;          // lanes per K/V row (16 bytes each)
+  constexpr int KPL = 32 / LPR;        // keys per load instruction
+  const int lane = c.lane;
+  const int sub = lane / LPR, dl = lane % LPR;
+  const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
+  const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
+  const int NW = (int)gridDim.x * 8, gw = (int)blockIdx.x * 8 + aw;
+  const int Tmax = (int)c.ctl[kCTmax];
+  const int seqs = p.B * p.NKV;
+  int ck, nch;
+  attn_plan(Tmax, seqs, NW, ck, nch);
+  const int items = seqs * nch;
+  constexpr int REC = GQ * (HD + 2);
+#pragma unroll 1
+  for (int item = gw; item < items; item += NW) {
+    const int ch = item % nch, sq = item / nch;
+    const int kvh = sq % p.NKV, b = sq / p.NKV;
+    const int T = pos_s[b] + 1;
+    const int nsplit = (T + ck - 1) / ck;
+    uint16_t* outp = p.attn_out + (size_t)b * p.QDIM + (size_t)kvh * GQ * HD;
+    if (!act_s[b]) {   // fused_decode_attention zeroes the output of an inactive row (operations.py:226-231)
+      if (ch == 0)
+        for (int i = lane; i < GQ * HD / 8; i += 32) reinterpret_cast<uint4*>(outp)[i] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    if (ch >= nsplit) continue;
+    const int k_lo = ch * ck, k_hi = min(T, k_lo + ck);
+    float q[GQ][8], acc[GQ][8], m[GQ], l[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const uint4 qv = ldcg_u4(p.q_post_rope + (size_t)b * p.QDIM + (size_t)(kvh * GQ + g) * HD + dl * 8);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        q[g][2 * j] = bf_lo(w[j]) * p.scale_log2e;
+        q[g][2 * j + 1] = bf_hi(w[j]) * p.scale_log2e;
+      }
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+    }
+    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
+#pragma unroll 2
+    for (int k0 = k_lo; k0 < k_hi; k0 += KPL) {
+      const int k = k0 + sub;
+      const bool valid = k < k_hi;
+      uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+      if (valid) {
+        kv4 = ldcg_u4(p.k_cache + base + (size_t)k * p.kv_seq_stride);
+        vv4 = ldcg_u4(p.v_cache + base + (size_t)k * p.kv_seq_stride);
+      }
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv4);
+      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vv4);
+      float kf[8], vf[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[2 * j] = bf_lo(kw[j]); kf[2 * j + 1] = bf_hi(kw[j]);
+        vf[2 * j] = bf_lo(vw[j]); vf[2 * j + 1] = bf_hi(vw[j]);
+      }
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += q[g][j] * kf[j];
+#pragma unroll
+        for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(kFullMask, s, o);
+        if (valid) {
+          const float mn = fmaxf(m[g], s);
+          const float corr = exp2f(m[g] - mn);     // 0 when m was -inf
+          const float pe = exp2f(s - mn);
+          l[g] = l[g] * corr + pe;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pe * vf[j];
+          m[g] = mn;
+        }
+      }
+    }
+    // merge the KPL key sub-streams (lanes with equal dl)
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        const float mo = __shfl_xor_sync(kFullMask, m[g], o);
+        const float lo_ = __shfl_xor_sync(kFullMask, l[g], o);
+        const float mn = fmaxf(m[g], mo);
+        const float ca = mn == -INFINITY ? 0.f : exp2f(m[g] - mn);
+        const float cb = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+        l[g] = l[g] * ca + lo_ * cb;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float ao = __shfl_xor_sync(kFullMask, acc[g][j], o);
+          acc[g][j] = acc[g][j] * ca + ao * cb;
+        }
+        m[g] = mn;
+      }
+    }
+    if (nsplit == 1) {
+      if (sub == 0) {
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float inv = 1.0f / l[g];
+          uint4 o4;
+          o4.x = pack_bf16x2(acc[g][0] * inv, acc[g][1] * inv);
+          o4.y = pack_bf16x2(acc[g][2] * inv, acc[g][3] * inv);
+          o4.z = pack_bf16x2(acc[g][4] * inv, acc[g][5] * inv);
+          o4.w = pack_bf16x2(acc[g][6] * inv, acc[g][7] * inv);
+          *reinterpret_cast<uint4*>(outp + g * HD + dl * 8) = o4;
+        }
+      }
+      continue;
+    }
+    float* rec = p.attn_part + (size_t)item * REC;
+    if (sub == 0) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        float4* dst = reinterpret_cast<float4*>(rec + g * (HD + 2) + dl * 8);
+        // (HD + 2) * 4 bytes per head record keeps 8-byte alignment only: write as float2 pairs
+        float2* d2 = reinterpret_cast<float2*>(dst);
+        d2[0] = make_float2(acc[g][0], acc[g][1]);
+        d2[1] = make_float2(acc[g][2], acc[g][3]);
+        d2[2] = make_float2(acc[g][4], acc[g][5]);
+        d2[3] = make_float2(acc[g][6], acc[g][7]);
+        if (dl == 0) *reinterpret_cast<float2*>(rec + g * (HD + 2) + HD) = make_float2(m[g], l[g]);
+      }
+    }
+    __threadfence();
+    __syncwarp();
+    unsigned last = 0u;
+    if (lane == 0) {
+      const unsigned old = atom_add_acq_rel_gpu(p.attn_tickets + sq, 1u);
+      last = old == (unsigned)(nsplit - 1) ? 1u : 0u;
+      if (last) p.attn_tickets[sq] = 0u;
+    }
+    last = __shfl_sync(kFullMask, last, 0);
+    if (!last) continue;
+    __threadfence();
+    // merge the nsplit records of this (sequence, kv head): every lane takes (head, 8 dims) pieces
+    const float* recs = p.attn_part + (size_t)(sq * nch) * REC;
+    for (int piece = lane; piece < GQ * LPR; piece += 32) {
+      const int g = piece / LPR, dd = piece % LPR;
+      float M = -INFINITY;
+      for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ldcg_f32(recs + (size_t)s * REC + g * (HD + 2) + HD));
+      float L = 0.f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < nsplit; ++s) {
+        const float* rr = recs + (size_t)s * REC + g * (HD + 2);
+        const float2 ml = ldcg_f2(rr + HD);
+        const float w = exp2f(ml.x - M);
+        L += ml.y * w;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = ldcg_f2(rr + dd * 8 + 2 * j);
+          o[2 * j] += a.x * w;
+          o[2 * j + 1] += a.y * w;
+        }
+      }
+      const float inv = 1.0f / L;
+      uint4 o4;
+      o4.x = pack_bf16x2(o[0] * inv, o[1] * inv);
+      o4.y = pack_bf16x2(o[2] * inv, o[3] * inv);
+      o4.z = pack_bf16x2(o[4] * inv, o[5] * inv);
+      o4.w = pack_bf16x2(o[6] * inv, o[7] * inv);
+      *reinterpret_cast<uint4*>(outp + g * HD + dd * 8) = o4;
+    }
+  }
+}
+
+__device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
+  const BParams& p = *c.p;
+  if (aw == 0 && c.lane == 0) {
+    bool needed;
+    const bool ok = phase_dependency(c, ph, needed);
+    c.ctl[kCFlagAttn] = ok ? 1u : 0u;
+  }
+  named_bar(kBarAttn, 256);
+  if (c.ctl[kCFlagAttn] != 0u) {
+    const int layer = ph / 5, gq = p.NH / p.NKV;
+    if (p.HD == 64) {
+      if (gq == 4) attention_items<64, 4>(c, layer, aw);
+      else if (gq == 2) attention_items<64, 2>(c, layer, aw);
+      else attention_items<64, 1>(c, layer, aw);
+    } else {
+      if (gq == 4) attention_items<128, 4>(c, layer, aw);
+      else if (gq == 2) attention_items<128, 2>(c, layer, aw);
+      else attention_items<128, 1>(c, layer, aw);
+    }
+  }
+  __threadfence();
+  named_bar(kBarAttn, 256);
+  if (aw == 0 && c.lane == 0 && !c.aborted()) red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+}
+
+// ------------------------------------------------------------------------------------------------
+// prologue / finalize (epilogue group)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void prologue(const Ctx& c, int e) {
+  // rows b = cta, cta + G, ...: optional embedding of token_in[b], then the sum of squares of hidden[b]
+  const BParams& p = *c.p;
+  float* red = reinterpret_cast<float*>(c.smem + Smem::kOffHs);
+  const int nt = (p.H + kTileRows - 1) / kTileRows;
+  for (int b = (int)blockIdx.x; b < p.B; b += (int)gridDim.x) {
+    uint16_t* h = p.hidden + (size_t)b * p.H;
+    const uint16_t* src = h;
+    if (p.prologue == 2) src = p.embed + (size_t)p.token_in[b] * p.H;
+    float s = 0.f;
+    for (int i = e; i < p.H / 8; i += 128) {
+      const uint4 v = ldcg_u4(src + i * 8);
+      if (p.prologue == 2) reinterpret_cast<uint4*>(h)[i] = v;
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s += bf_lo(w[j]) * bf_lo(w[j]) + bf_hi(w[j]) * bf_hi(w[j]);
+    }
+    s = warp_sum(s);
+    if (c.lane == 0) red[e >> 5] = s;
+    named_bar(kBarEpi, 128);
+    if (e < nt) p.ss[e * kMaxBatch + b] = e == 0 ? red[0] + red[1] + red[2] + red[3] : 0.f;
+    named_bar(kBarEpi, 128);
+  }
+  __threadfence();
+  named_bar(kBarEpi, 128);
+  if (e == 0) red_release_gpu_add(p.phase_done + 0, 1u);
+}
+
+__device__ __forceinline__ void finalize(const Ctx& c, int e) {
+  // CTA 0, after every CTA has finished the LM head: tokens out
+  const BParams& p = *c.p;
+  const int lm = 5 * p.num_layers;
+  if (e == 0) c.ctl[kCFlagEpi] = counter_wait(c, p.phase_done + 1 + lm, gridDim.x, lm) ? 1u : 0u;
+  named_bar(kBarEpi, 128);
+  if (c.ctl[kCFlagEpi] != 0u && e < p.B) {
+    const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
+    const unsigned long long win = __ldcg(p.argmax_key + e);
+    const long long tok = (long long)(0xffffffffu - (unsigned)(win & 0xffffffffull));
+    if (p.next_token) p.next_token[e] = tok;
+    if (p.out_tokens && (long long)pos_s[e] + 1 < p.out_tokens_len) p.out_tokens[(size_t)e * p.out_tokens_len + pos_s[e] + 1] = tok;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// kernel
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kBatchThreads, 1)
+qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ TensorMaps maps) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  Ctx c;
+  c.p = &p;
+  c.smem = smem;
+  c.ctl = reinterpret_cast<volatile unsigned*>(smem + Smem::kOffCtl);
+  c.bars = smem_u32(smem + Smem::kOffBars);
+  c.warp = threadIdx.x >> 5;
+  c.lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(c.a_full(s), 1);
+      mbar_init(c.b_full(s), 128);
+      mbar_init(c.empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(c.acc_full(b), 1);
+      mbar_init(c.acc_empty(b), 128);
+    }
+    fence_barrier_init();
+    for (int i = 0; i < 16; ++i) c.ctl[i] = 0u;
+  }
+  if (threadIdx.x < kMaxBatch) {
+    const int b = threadIdx.x;
+    int* pos_s = reinterpret_cast<int*>(smem + Smem::kOffPos);
+    int* act_s = reinterpret_cast<int*>(smem + Smem::kOffAct);
+    pos_s[b] = b < p.B ? (p.position_ids ? p.position_ids[b] : p.pos) : 0;
+    act_s[b] = b < p.B ? (p.active_mask ? (int)p.active_mask[b] : 1) : 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int* pos_s = reinterpret_cast<const int*>(smem + Smem::kOffPos);
+    const int* act_s = reinterpret_cast<const int*>(smem + Smem::kOffAct);
+    int tmax = 1;
+    for (int b = 0; b < p.B; ++b)
+      if (act_s[b]) tmax = max(tmax, pos_s[b] + 1);
+    c.ctl[kCTmax] = (unsigned)tmax;
+  }
+  if (c.warp == 0) {
+    tmem_alloc(smem_u32(smem + Smem::kOffCtl + kCTmem * 4), 128);
+    tmem_fence_before_sync();
+  }
+  __syncthreads();
+  tmem_fence_after_sync();
+  const uint32_t tmem = c.ctl[kCTmem];
+  unsigned n_issued = 0;
+
+  if (c.warp == 0) {
+    if (c.lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.qkv) : "memory");
+      producer(c, maps, n_issued);
+    }
+  } else if (c.warp == 1) {
+    if (c.lane == 0) issuer(c, tmem);
+  } else {
+    const bool epi = c.warp < kStgWarp0;
+    const int gi = (c.warp - (epi ? kEpiWarp0 : kStgWarp0)) * 32 + c.lane;   // index inside the group of 128
+    unsigned n = 0, sg = 0;
+    if (epi && p.prologue != 0) prologue(c, gi);
+#pragma unroll 1
+    for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
+      const int kind = phase_kind(ph, p.num_layers);
+      if (kind == kAttn) {
+        attention_phase(c, ph, c.warp - kEpiWarp0);
+      } else if (epi) {
+        epilogue_phase(c, ph, kind, tmem, gi, sg);
+        __threadfence();
+        named_bar(kBarEpi, 128);
+        if (gi == 0 && !c.aborted()) red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+      } else {
+        stage_phase(c, ph, kind, gi, n);
+      }
+    }
+    if (epi && blockIdx.x == 0 && p.phase_end == num_phases(p.num_layers)) finalize(c, gi);
+  }
+  __syncwarp();
+  tmem_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && c.aborted()) {
+    // leave no tensor copy in flight into this CTA's shared memory: wait (bounded) for the last fills
+    const unsigned first = n_issued > (unsigned)kStages ? n_issued - kStages : 0u;
+    for (unsigned m = first; m < n_issued; ++m) {
+      const long long t0 = clock64();
+      while (!mbar_try_wait(c.a_full((int)(m % kStages)), (m / kStages) & 1u)) {
+        if (clock64() - t0 > p.timeout_cycles) break;
+      }
+    }
+  }
+  __syncthreads();
+  if (c.warp == 0) {
+    tmem_fence_after_sync();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
+}  // namespace qmkb

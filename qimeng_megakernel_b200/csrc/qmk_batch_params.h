@@ -1,0 +1,65 @@
+// Parameter block of the batched decode megakernel (qmk_batch_kernel.cuh): runtime shapes, B sequences
+// per step.  Plays the role of the reference's multi-batch globals POD
+// (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/multi_batch/decode_kernel/mk.h:9-42: the
+// single-batch tensors with a leading [B] dimension plus position_ids / active_mask) and of the Qwen3
+// additions q_norm_weights / k_norm_weights (qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/
+// single_batch/decode_kernel/mk.h:7,18-19), as raw pointers.
+#pragma once
+#include <stdint.h>
+
+namespace qmkb {
+
+constexpr int kMaxBatch = 64;          // sequences per step (N of the tensor-core tile)
+constexpr int kTileRows = 128;         // weight rows per tile (M of the tensor-core tile)
+constexpr int kBlockK = 64;            // bf16 elements per k-block: 128 bytes, one swizzle row
+constexpr int kMaxSplits = 64;         // split-KV partials per (sequence, kv head)
+
+// Phase kinds inside a layer; phase index = layer * 5 + kind, the LM head is phase 5 * L.
+enum Kind : int { kQkv = 0, kAttn = 1, kOproj = 2, kUpGate = 3, kDown = 4, kLmHead = 5 };
+
+struct BParams {
+  // ---- weights that are read with plain loads (the matrices come through tensor maps) ----
+  const uint16_t* attn_norm;     // [L, H]
+  const uint16_t* mlp_norm;      // [L, H]
+  const uint16_t* lm_norm;       // [H]
+  const uint16_t* q_norm;        // [L, HD] or null (per-head RMSNorm on Q before RoPE)
+  const uint16_t* k_norm;        // [L, HD] or null
+  const uint16_t* embed;         // [V, H] or null
+  const float* rope_cos;         // [rope_rows, HD] interleaved
+  const float* rope_sin;
+  // ---- request state, bf16 ----
+  uint16_t* hidden;              // [B, H]
+  uint16_t* q_post_rope;         // [B, QDIM]
+  uint16_t* k_cache;             // [L, Bc, S, NKV, HD]
+  uint16_t* v_cache;
+  uint16_t* attn_out;            // [B, QDIM]
+  uint16_t* silu_out;            // [B, I]
+  uint16_t* logits;              // [B, V]
+  long long* next_token;         // [B] or null
+  const long long* token_in;     // [B] or null
+  long long* out_tokens;         // [B, out_tokens_len] or null; written at [b, pos_b + 1]
+  long long out_tokens_len;
+  const int* position_ids;       // [B] or null (then every row is at `pos`)
+  const unsigned char* active_mask;   // [B] or null (then every row is active)
+  long long kv_layer_stride, kv_batch_stride, kv_seq_stride;   // elements
+  // ---- library-owned scratch ----
+  float* ws;                     // [CTAs, 2, Bpad/4, 128, 4] split-K partial tiles
+  unsigned* tile_tickets;        // [row tiles]   arrivals of a tile's partial segments
+  float* ss;                     // [H/128, kMaxBatch]  sums of squares of the residual stream, per row tile
+  float* attn_part;              // [items, G, HD + 2]  split-KV partials (acc, max, sum)
+  unsigned* attn_tickets;        // [B * NKV]
+  unsigned long long* argmax_key;   // [B]  (ordered logit bits << 32) | ~row
+  unsigned* phase_done;          // [1 + phases]  CTAs that finished the prologue / each phase (zeroed per launch)
+  unsigned* status;              // [8]
+  // ---- shape ----
+  int H, I, NH, NKV, HD, QKV_ROWS, QDIM, num_layers, vocab;
+  int B, Bpad;                   // sequences, padded to a multiple of 16
+  int pos;                       // position of every row when position_ids is null
+  int phase_begin, phase_end;
+  int prologue;                  // 0 none; 1 sums of squares of `hidden`; 2 embed token_in, then sums of squares
+  int wait_first;                // failure test: the first phase waits for a dependency nothing publishes
+  float eps, qk_eps, scale_log2e;
+  long long timeout_cycles;
+};
+
+}  // namespace qmkb

@@ -1,0 +1,69 @@
+// Static schedule of the batched decode kernel: pure integer arithmetic shared by every role of the device
+// code and by the host tests, which replay it on the CPU.
+//
+// The reference deals 16-row output blocks to SMs on the host for every request and ships the result as an
+// instruction tensor (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_schedule/
+// instructions/scheduler.py:138-152, 164-361).  Here a phase is cut into (row tile, k-block) units and every
+// CTA derives its contiguous unit range in closed form.
+#pragma once
+#include "qmk_batch_params.h"
+
+#if defined(__CUDACC__)
+#define QMKB_HD __host__ __device__ __forceinline__
+#else
+#define QMKB_HD inline
+#endif
+
+namespace qmkb {
+
+struct PhaseDims {
+  int N;        // output rows (SwiGLU: units)
+  int K;        // contraction length
+  int T;        // row tiles
+  int KB;       // k-blocks
+  int rows;     // output rows (units) per tile
+};
+QMKB_HD int phase_kind(int ph, int L) { return ph >= 5 * L ? (int)kLmHead : ph % 5; }
+QMKB_HD int num_phases(int L) { return 5 * L + 1; }
+QMKB_HD PhaseDims phase_dims(const BParams& p, int kind) {
+  PhaseDims d;
+  switch (kind) {
+    case kQkv: d.N = p.QKV_ROWS; d.K = p.H; d.rows = kTileRows; break;
+    case kOproj: d.N = p.H; d.K = p.QDIM; d.rows = kTileRows; break;
+    case kUpGate: d.N = p.I; d.K = p.H; d.rows = kTileRows / 2; break;   // 64 up rows + the 64 gate rows of the same units
+    case kDown: d.N = p.H; d.K = p.I; d.rows = kTileRows; break;
+    default: d.N = p.vocab; d.K = p.H; d.rows = kTileRows; break;
+  }
+  d.T = (d.N + d.rows - 1) / d.rows;
+  d.KB = d.K / kBlockK;
+  return d;
+}
+// Units [lo, hi) of CTA c out of G, for U units.
+QMKB_HD void unit_range(int U, int G, int c, int& lo, int& hi) {
+  lo = (int)(((long long)c * U) / G);
+  hi = (int)(((long long)(c + 1) * U) / G);
+}
+// The CTA that owns unit u.
+QMKB_HD int unit_owner(int U, int G, int u) { return (int)((((long long)u + 1) * G - 1) / U); }
+
+// Number of segments (= CTAs with units) of row tile t.  With fewer units than CTAs every CTA owns at most one
+// unit and the owners of consecutive units are not consecutive CTAs: then a tile has KB one-unit segments.
+QMKB_HD int tile_segments(int U, int G, int KB, int t) {
+  if (U < G) return KB;
+  return unit_owner(U, G, (t + 1) * KB - 1) - unit_owner(U, G, t * KB) + 1;
+}
+
+// Split-KV plan: keys per item `ck` (a multiple of 32) and items per (sequence, kv head) `nch`, for the longest
+// context Tmax, `seqs` = sequences x kv heads and NW attention warps: enough items to occupy every warp, at most
+// kMaxSplits per (sequence, kv head); seqs * nch <= NW + seqs.  The reference picks min(16, SMs / kv_heads)
+// partials whatever the length (.../instructions/scheduler.py:85-94).
+QMKB_HD void attn_plan(int Tmax, int seqs, int NW, int& ck, int& nch) {
+  ck = (int)(((long long)Tmax * seqs + NW - 1) / NW);
+  const int floor_ck = (Tmax + kMaxSplits - 1) / kMaxSplits;
+  if (ck < floor_ck) ck = floor_ck;
+  ck = (ck + 31) & ~31;
+  if (ck < 32) ck = 32;
+  nch = (Tmax + ck - 1) / ck;
+}
+
+}  // namespace qmkb

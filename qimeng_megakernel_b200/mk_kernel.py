@@ -23,9 +23,10 @@ _WEIGHT_FIELDS = (("attn_norm", "attn_norm_weights"), ("qkv", "qkv_weights"), ("
                   ("mlp_norm", "mlp_norm_weights"), ("up_proj", "up_proj_weights"),
                   ("gate_proj", "gate_proj_weights"), ("down_proj", "down_proj_weights"),
                   ("lm_head_norm", "lm_head_norm_weights"), ("lm_head", "lm_head_weights"),
-                  ("embed_tokens", "embed_tokens"), ("rope_cos", "rope_cos"), ("rope_sin", "rope_sin"))
+                  ("embed_tokens", "embed_tokens"), ("rope_cos", "rope_cos"), ("rope_sin", "rope_sin"),
+                  ("q_norm", "q_norm_weights"), ("k_norm", "k_norm_weights"))
 _STATE_FIELDS = ("hidden_states", "q_post_rope", "k_cache", "v_cache", "attn_out", "silu_out", "logits",
-                 "next_token", "token_in", "out_tokens")
+                 "next_token", "token_in", "out_tokens", "position_ids", "active_mask")
 
 
 def _check_tensor(name: str, t: torch.Tensor, dtype: torch.dtype, shape: tuple) -> None:
@@ -65,6 +66,7 @@ class MegaKernel:
         self._weights_key = None
         self._state_key = None
         self._device = None
+        self._variant = 0
 
     # -- handle management -------------------------------------------------------------------
     def _validate(self, g: Globals) -> tuple:
@@ -86,23 +88,42 @@ class MegaKernel:
         rows = int(g.rope_cos.shape[0])
         _check_tensor("rope_cos", g.rope_cos, torch.float32, (rows, HD))
         _check_tensor("rope_sin", g.rope_sin, torch.float32, (rows, HD))
+        if cfg.qk_norm:
+            _check_tensor("q_norm_weights", g.q_norm_weights, bf, (L, HD))
+            _check_tensor("k_norm_weights", g.k_norm_weights, bf, (L, HD))
         if g.k_cache.dim() != 5:
             raise ValueError("globs.k_cache must be [L, B, S, NKV, HD]")
-        S = int(g.k_cache.shape[2])
-        _check_tensor("k_cache", g.k_cache, bf, (L, 1, S, NKV, HD))
-        _check_tensor("v_cache", g.v_cache, bf, (L, 1, S, NKV, HD))
-        _check_tensor("hidden_states", g.hidden_states, bf, (H,))
-        _check_tensor("q_post_rope", g.q_post_rope, bf, (NH * HD,))
-        _check_tensor("attn_out", g.attn_out, bf, (NH * HD,))
-        _check_tensor("silu_out", g.silu_out, bf, (I,))
-        _check_tensor("logits", g.logits, bf, (V,))
+        B, S = int(g.k_cache.shape[1]), int(g.k_cache.shape[2])
+        if not 1 <= B <= _lib.MAX_BATCH:
+            raise ValueError(f"batch {B} outside 1..{_lib.MAX_BATCH}")
+        _check_tensor("k_cache", g.k_cache, bf, (L, B, S, NKV, HD))
+        _check_tensor("v_cache", g.v_cache, bf, (L, B, S, NKV, HD))
+
+        def state(name, width):
+            t = getattr(g, name)
+            # one sequence may keep the reference's single-batch shapes ([H]), B sequences are [B, H]
+            shape = (width,) if (B == 1 and isinstance(t, torch.Tensor) and t.dim() == 1) else (B, width)
+            _check_tensor(name, t, bf, shape)
+
+        state("hidden_states", H)
+        state("q_post_rope", NH * HD)
+        state("attn_out", NH * HD)
+        state("silu_out", I)
+        state("logits", V)
         for name in ("next_token", "token_in"):
             t = getattr(g, name, None)
             if t is not None:
-                _check_tensor(name, t, torch.int64, (1,))
+                _check_tensor(name, t, torch.int64, (B,))
         if getattr(g, "out_tokens", None) is not None:
-            _check_tensor("out_tokens", g.out_tokens, torch.int64, (g.out_tokens.numel(),))
-        return rows, S
+            n = g.out_tokens.numel() // B
+            _check_tensor("out_tokens", g.out_tokens, torch.int64, (n,) if (B == 1 and g.out_tokens.dim() == 1) else (B, n))
+        if getattr(g, "position_ids", None) is not None:
+            _check_tensor("position_ids", g.position_ids, torch.int32, (B,))
+        if getattr(g, "active_mask", None) is not None:
+            if g.active_mask.dtype not in (torch.uint8, torch.bool):
+                raise TypeError("globs.active_mask must be uint8 or bool")
+            _check_tensor("active_mask", g.active_mask, g.active_mask.dtype, (B,))
+        return rows, S, B
 
     def _ensure(self, g: Globals) -> None:
         wkey = tuple(_ptr(getattr(g, f, None)) for _, f in _WEIGHT_FIELDS) + tuple(
@@ -110,15 +131,16 @@ class MegaKernel:
         skey = tuple(_sig(getattr(g, f, None)) for f in _STATE_FIELDS)
         if wkey == self._weights_key and skey == self._state_key:
             return
-        rows, S = self._validate(g)
+        rows, S, B = self._validate(g)
         dev = g.hidden_states.device
         if wkey != self._weights_key:
             self.close()
             cfg = LlamaConfig
-            desc = _lib.ModelDesc(_lib.ABI_VERSION, _lib.ARCH_LLAMA, cfg.num_hidden_layers, cfg.hidden_size,
+            desc = _lib.ModelDesc(_lib.ABI_VERSION, _lib.ARCH_QWEN3 if cfg.qk_norm else _lib.ARCH_LLAMA,
+                                  cfg.num_hidden_layers, cfg.hidden_size,
                                   cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads,
                                   cfg.head_dim, cfg.vocab_size, rows, float(cfg.rms_norm_eps),
-                                  1.0 / math.sqrt(cfg.head_dim))
+                                  1.0 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps))
             w = _lib.WeightPtrs(**{c: _ptr(getattr(g, f, None)) for c, f in _WEIGHT_FIELDS})
             h = C.c_void_p()
             _lib.check(self._lib.qmk_create(C.byref(desc), C.byref(w), dev.index or 0, C.byref(h)))
@@ -126,10 +148,12 @@ class MegaKernel:
             self._weights_key = wkey
             self._state_key = None
             self._device = dev
+            if self._variant:
+                _lib.check(self._lib.qmk_set_kernel_variant(self._handle, self._variant), self._handle)
         if skey != self._state_key:
             st = _lib.StatePtrs(**{f: _ptr(getattr(g, f, None)) for f in _STATE_FIELDS})
-            st.out_tokens_len = int(g.out_tokens.numel()) if getattr(g, "out_tokens", None) is not None else 0
-            st.batch = 1
+            st.out_tokens_len = int(g.out_tokens.numel()) // B if getattr(g, "out_tokens", None) is not None else 0
+            st.batch = B
             st.kv_seq_len = S
             _lib.check(self._lib.qmk_bind_state(self._handle, C.byref(st)), self._handle)
             self._state_key = skey
@@ -187,6 +211,12 @@ class MegaKernel:
 
     def set_timeout_cycles(self, cycles: int) -> None:
         _lib.check(self._lib.qmk_set_timeout_cycles(self._handle, int(cycles)))
+
+    def set_kernel_variant(self, variant: int) -> None:
+        """0: the batch-1 kernel when the shape and batch allow it; 1: always the batched kernel."""
+        self._variant = int(variant)
+        if self._handle is not None:
+            _lib.check(self._lib.qmk_set_kernel_variant(self._handle, self._variant), self._handle)
 
     def set_cooperative_launch(self, on: bool) -> None:
         _lib.check(self._lib.qmk_set_cooperative_launch(self._handle, 1 if on else 0))

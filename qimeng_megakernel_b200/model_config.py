@@ -23,10 +23,13 @@ class LlamaConfig:
     # llama3 rope scaling (factor, low_freq_factor, high_freq_factor, original context); None = plain theta
     rope_scaling = (32.0, 1.0, 4.0, 8192)
     max_position_embeddings = 8192
+    # Qwen3: per-head RMSNorm on Q and K before RoPE (the reference's Qwen3Config,
+    # qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/decode_schedule/model_config.py:4-16)
+    qk_norm = False
 
     _KEYS = ("num_hidden_layers", "hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
              "num_key_value_heads", "vocab_size", "rms_norm_eps", "rope_theta", "rope_scaling",
-             "max_position_embeddings")
+             "max_position_embeddings", "qk_norm")
 
     @classmethod
     def update_from_dict(cls, config: dict) -> None:
@@ -47,6 +50,7 @@ class LlamaConfig:
                   int(rs["original_max_position_embeddings"]))
         cls.rope_scaling = tuple(rs) if rs else None
         cls.max_position_embeddings = int(config.get("max_position_embeddings", 8192))
+        cls.qk_norm = bool(config.get("qk_norm", False))
 
     @classmethod
     def update_from_hf(cls, config) -> None:
@@ -69,3 +73,11 @@ class LlamaConfig:
 LLAMA_3_2_1B = dict(num_hidden_layers=16, hidden_size=2048, intermediate_size=8192, head_dim=64,
                     num_attention_heads=32, num_key_value_heads=8, vocab_size=128256, rms_norm_eps=1e-5,
                     rope_theta=500000.0, rope_scaling=(32.0, 1.0, 4.0, 8192), max_position_embeddings=8192)
+
+# Qwen3-0.6B (qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/decode_schedule/model_config.py:4-16)
+QWEN3_0_6B = dict(num_hidden_layers=28, hidden_size=1024, intermediate_size=3072, head_dim=128,
+                  num_attention_heads=16, num_key_value_heads=8, vocab_size=151936, rms_norm_eps=1e-6,
+                  rope_theta=1000000.0, rope_scaling=None, max_position_embeddings=40960, qk_norm=True)
+
+# The reference keeps one config class per model package; here one runtime descriptor serves every shape.
+Qwen3Config = LlamaConfig

@@ -16,11 +16,14 @@ from .rope import rope_tables_interleaved
 WEIGHT_NAMES = ("attn_norm_weights", "qkv_weights", "o_proj_weights", "mlp_norm_weights", "up_proj_weights",
                 "gate_proj_weights", "down_proj_weights", "lm_head_norm_weights", "lm_head_weights",
                 "embed_tokens", "rope_cos", "rope_sin")
+QK_NORM_NAMES = ("q_norm_weights", "k_norm_weights")
 
 
 def make_weights(config: dict, seed: int = 0, device: str | torch.device = "cpu", std: float = 0.02,
-                 max_positions: int | None = None) -> dict:
-    """Seeded weights as a dict of tensors on `device` (generator lives on that device)."""
+                 max_positions: int | None = None, gain_jitter: float = 0.0) -> dict:
+    """Seeded weights as a dict of tensors on `device` (generator lives on that device).
+    gain_jitter > 0 draws the RMSNorm gains from N(1, gain_jitter) instead of 1 (tests only: with gains of
+    exactly 1 a kernel that ignored them would still pass)."""
     L, H, I = config["num_hidden_layers"], config["hidden_size"], config["intermediate_size"]
     NH, NKV, HD, V = (config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"],
                       config["vocab_size"])
@@ -53,6 +56,13 @@ def make_weights(config: dict, seed: int = 0, device: str | torch.device = "cpu"
         lm[r0:r1].copy_(torch.randn(r1 - r0, H, generator=gen, device=dev, dtype=torch.float32) * std)
     w["lm_head_weights"] = lm
     w["embed_tokens"] = lm                      # tied
+    if config.get("qk_norm"):
+        w["q_norm_weights"] = torch.ones(L, HD, dtype=torch.bfloat16, device=dev)
+        w["k_norm_weights"] = torch.ones(L, HD, dtype=torch.bfloat16, device=dev)
+    if gain_jitter > 0.0:
+        for name in ("attn_norm_weights", "mlp_norm_weights", "lm_head_norm_weights", "q_norm_weights", "k_norm_weights"):
+            if name in w:
+                w[name] = (1.0 + gain_jitter * torch.randn(w[name].shape, generator=gen, device=dev)).to(torch.bfloat16)
     cos, sin = rope_tables_interleaved(HD, max_positions or config.get("max_position_embeddings", 8192),
                                        config.get("rope_theta", 10000.0), config.get("rope_scaling"))
     w["rope_cos"], w["rope_sin"] = cos.to(dev), sin.to(dev)
@@ -65,9 +75,16 @@ def make_prompt(vocab_size: int, length: int = 16, seed: int = 1) -> torch.Tenso
     return torch.randint(0, vocab_size, (length,), generator=gen, dtype=torch.int64)
 
 
-def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | torch.device = "cuda") -> Globals:
-    """Allocate the B = 1 buffers the reference's fused prefill allocates
-    (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/fused_prefill.py:61-160) around `weights`."""
+def make_prompts(vocab_size: int, batch: int, length: int = 16, seed: int = 1) -> torch.Tensor:
+    """[batch, length] prompts, row b drawn with seed + b (independent seeded prompts per sequence)."""
+    return torch.stack([make_prompt(vocab_size, length, seed + b) for b in range(batch)])
+
+
+def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | torch.device = "cuda",
+                 batch: int | None = None) -> Globals:
+    """Allocate the buffers the reference's fused prefill allocates
+    (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/fused_prefill.py:61-160) around `weights`:
+    batch=None gives the single-batch shapes ([H], ...), batch=B the multi-batch ones ([B, H], ...)."""
     LlamaConfig.update_from_dict(config)
     dev = torch.device(device)
     L, H, I = config["num_hidden_layers"], config["hidden_size"], config["intermediate_size"]
@@ -75,20 +92,23 @@ def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | tor
                       config["vocab_size"])
     bf = torch.bfloat16
     moved = {}
-    for name in WEIGHT_NAMES:
+    names = WEIGHT_NAMES + tuple(n for n in QK_NORM_NAMES if n in weights)
+    for name in names:
         t = weights[name]
         key = t.data_ptr()
         if key not in moved:
             moved[key] = t.to(dev).contiguous()
         weights_dev = moved[key]
         moved[name] = weights_dev
-    g = Globals(position_id=0, **{n: moved[n] for n in WEIGHT_NAMES})
-    g.k_cache = torch.zeros(L, 1, kv_seq_len, NKV, HD, dtype=bf, device=dev)
-    g.v_cache = torch.zeros(L, 1, kv_seq_len, NKV, HD, dtype=bf, device=dev)
-    g.hidden_states = torch.zeros(H, dtype=bf, device=dev)
-    g.q_post_rope = torch.zeros(NH * HD, dtype=bf, device=dev)
-    g.attn_out = torch.zeros(NH * HD, dtype=bf, device=dev)
-    g.silu_out = torch.zeros(I, dtype=bf, device=dev)
-    g.logits = torch.zeros(V, dtype=bf, device=dev)
-    g.next_token = torch.zeros(1, dtype=torch.int64, device=dev)
+    g = Globals(position_id=0, **{n: moved[n] for n in names})
+    B = batch or 1
+    lead = () if batch is None else (B,)
+    g.k_cache = torch.zeros(L, B, kv_seq_len, NKV, HD, dtype=bf, device=dev)
+    g.v_cache = torch.zeros(L, B, kv_seq_len, NKV, HD, dtype=bf, device=dev)
+    g.hidden_states = torch.zeros(*lead, H, dtype=bf, device=dev)
+    g.q_post_rope = torch.zeros(*lead, NH * HD, dtype=bf, device=dev)
+    g.attn_out = torch.zeros(*lead, NH * HD, dtype=bf, device=dev)
+    g.silu_out = torch.zeros(*lead, I, dtype=bf, device=dev)
+    g.logits = torch.zeros(*lead, V, dtype=bf, device=dev)
+    g.next_token = torch.zeros(B, dtype=torch.int64, device=dev)
     return g

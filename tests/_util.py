@@ -17,13 +17,14 @@ STATE_BUFFERS = ("hidden_states", "q_post_rope", "attn_out", "silu_out", "logits
 
 
 def oracle_config(config: dict) -> fo.OracleConfig:
-    return fo.OracleConfig(**{k: config[k] for k in ("num_hidden_layers", "hidden_size", "intermediate_size",
+    return fo.OracleConfig(qk_norm=bool(config.get("qk_norm", False)),
+                           **{k: config[k] for k in ("num_hidden_layers", "hidden_size", "intermediate_size",
                                                       "head_dim", "num_attention_heads", "num_key_value_heads",
                                                       "vocab_size", "rms_norm_eps")})
 
 
-def oracle_state(config: dict, weights: dict, kv_seq_len: int, dtype=torch.bfloat16) -> fo.OracleState:
-    return fo.make_state(oracle_config(config), weights, kv_seq_len, dtype)
+def oracle_state(config: dict, weights: dict, kv_seq_len: int, dtype=torch.bfloat16, batch=None) -> fo.OracleState:
+    return fo.make_state(oracle_config(config), weights, kv_seq_len, dtype, batch)
 
 
 def push_state(st: fo.OracleState, g) -> None:
@@ -31,6 +32,11 @@ def push_state(st: fo.OracleState, g) -> None:
     for name in STATE_BUFFERS:
         getattr(g, name).copy_(getattr(st, name).to(torch.bfloat16))
     g.position_id = st.position_id
+    if st.position_ids is not None:
+        g.position_ids.copy_(torch.tensor(st.position_ids, dtype=torch.int32))
+        g.position_id = max(st.position_ids)
+    if st.active_mask is not None:
+        g.active_mask.copy_(torch.tensor(st.active_mask, dtype=torch.uint8))
 
 
 def max_rel_with_abs_floor(actual: torch.Tensor, expected: torch.Tensor, floor: float) -> float:

@@ -15,6 +15,13 @@ FusedGenerator.generate_greedy_fast (qimeng_megakernel/models/LLM/decode.py:1373
 Fixtures:
   small_l2_v4096.npz   2 layers, vocabulary 4096, Llama-3.2-1B layer shape; every intermediate buffer of
                        12 teacher-forced steps.  Pins the CPU oracle bit for bit (tests/test_oracle_golden.py).
+  batch3_l2_v4096.npz  the same small Llama shape with THREE sequences in [B, H] state (the reference's multi-batch
+                       Globals, multi_batch/decode_schedule/globs.py, driven through the same fused ops): ragged
+                       positions, a row that starts late and a row that finishes early (active_mask), norm gains
+                       drawn around 1.  Every buffer of 7 steps.
+  qwen3_l2_v4096.npz   the Qwen3-0.6B layer shape (hidden 1024, 16 / 8 heads of 128, intermediate 3072), 2 layers,
+                       vocabulary 4096, through the reference's Qwen3 fused ops (per-head Q/K RMSNorm):
+                       qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/decode_schedule/fused/operations.py
   llama1b_cfg1.npz     (--full) the BASELINE configuration 1: 16 layers, vocabulary 128256, 16 seeded prompt
                        tokens then greedy decode; greedy tokens, top-8 logits per step, per-layer hidden
                        states of selected steps (bf16 and fp32).  Compared with the CUDA kernel on the GPU.
@@ -34,7 +41,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
 from qimeng_megakernel_b200 import synthetic  # noqa: E402
-from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B  # noqa: E402
+from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, QWEN3_0_6B  # noqa: E402
 
 REF_PKG = "qimeng_megakernel.models.LLM.llama.llama3_2__1b.A100.single_batch.decode_schedule"
 
@@ -129,6 +136,144 @@ def make_small(pkg, ops):
     print("wrote small_l2_v4096.npz")
 
 
+BATCH_PLAN = dict(
+    # per step: (position, active) of each of the three rows; row 2 starts two steps late, row 1 stops after step 3
+    positions=[[0, 0, 0], [1, 1, 0], [2, 2, 0], [3, 3, 1], [4, 3, 2], [5, 3, 3], [6, 3, 4]],
+    active=[[1, 1, 0], [1, 1, 0], [1, 1, 1], [1, 1, 1], [1, 0, 1], [1, 0, 1], [1, 0, 1]])
+
+
+def make_batch(ops):
+    """Three sequences through the reference's fused ops on its multi-batch Globals."""
+    import importlib
+    mb = importlib.import_module(
+        "qimeng_megakernel.models.LLM.llama.llama3_2__1b.A100.multi_batch.decode_schedule.globs")
+    pkg = importlib.import_module(REF_PKG)
+    cfg = dict(LLAMA_3_2_1B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    w = synthetic.make_weights(cfg, seed=4321, device="cpu", gain_jitter=0.1)
+    B, S, L = 3, 16, cfg["num_hidden_layers"]
+    prompts = synthetic.make_prompts(cfg["vocab_size"], B, 8, seed=77)
+    out = {"prompts": prompts.numpy(), "weights_seed": np.int64(4321), "prompt_seed": np.int64(77),
+           "positions": np.array(BATCH_PLAN["positions"], dtype=np.int64),
+           "active": np.array(BATCH_PLAN["active"], dtype=np.int64)}
+    for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        base = ref_globals(pkg, cfg, w, S, dtype)
+        NH, NKV, HD, H, I, V = (cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                                cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"])
+        g = mb.Globals(**{f: getattr(base, f) for f in (
+            "attn_norm_weights", "qkv_weights", "o_proj_weights", "mlp_norm_weights", "up_proj_weights",
+            "gate_proj_weights", "down_proj_weights", "lm_head_norm_weights", "lm_head_weights", "rope_cos", "rope_sin")})
+        g.embed_tokens = base.embed_tokens
+        g.k_cache = torch.zeros(L, B, S, NKV, HD, dtype=dtype)
+        g.v_cache = torch.zeros(L, B, S, NKV, HD, dtype=dtype)
+        g.hidden_states = torch.zeros(B, H, dtype=dtype)
+        g.q_post_rope = torch.zeros(B, NH * HD, dtype=dtype)
+        g.attn_out = torch.zeros(B, NH * HD, dtype=dtype)
+        g.silu_out = torch.zeros(B, I, dtype=dtype)
+        g.logits = torch.zeros(B, V, dtype=dtype)
+        recs = []
+        for positions, active in zip(BATCH_PLAN["positions"], BATCH_PLAN["active"]):
+            toks = [int(prompts[b, positions[b]]) for b in range(B)]
+            g.hidden_states.copy_(g.embed_tokens[torch.tensor(toks)].to(dtype))
+            g.position_ids = torch.tensor(positions, dtype=torch.int32)
+            g.active_mask = torch.tensor(active, dtype=torch.bool)
+            g.position_id = None
+            r, hid = {}, []
+            for layer in range(L):
+                ops.fused_rms_qkvproj_gemv_rope(g, layer)
+                if layer == L - 1:
+                    r["q_post_rope"] = g.q_post_rope.clone()
+                    r["k_row"] = torch.stack([g.k_cache[layer, b, positions[b]] for b in range(B)])
+                    r["v_row"] = torch.stack([g.v_cache[layer, b, positions[b]] for b in range(B)])
+                ops.fused_decode_attention(g, layer)
+                if layer == L - 1:
+                    r["attn_out"] = g.attn_out.clone()
+                ops.fused_oproj_gemv_residual(g, layer)
+                if layer == L - 1:
+                    r["hidden_after_oproj"] = g.hidden_states.clone()
+                ops.fused_mlp_upgate(g, layer)
+                if layer == L - 1:
+                    r["silu_out"] = g.silu_out.clone()
+                ops.fused_mlp_down_residual(g, layer)
+                hid.append(g.hidden_states.clone())
+            ops.fused_rms_lmhead_gemv(g)
+            r["layer_hidden"] = torch.stack(hid)
+            r["logits"] = g.logits.clone()
+            r["argmax"] = g.logits.argmax(dim=-1).clone()
+            recs.append(r)
+        keys = ("layer_hidden", "logits") if name == "fp32" else (
+            "q_post_rope", "k_row", "v_row", "attn_out", "hidden_after_oproj", "silu_out", "layer_hidden", "logits")
+        for k in keys:
+            out[f"{name}_{k}"] = np.stack([bits(r[k]) for r in recs])
+        out[f"{name}_argmax"] = np.stack([r["argmax"].numpy() for r in recs]).astype(np.int64)
+    np.savez_compressed(os.path.join(HERE, "batch3_l2_v4096.npz"), **out)
+    print("wrote batch3_l2_v4096.npz")
+
+
+def make_qwen3():
+    """One sequence through the reference's Qwen3 fused ops (per-head Q/K norm before RoPE)."""
+    import importlib
+    qpkg = "qimeng_megakernel.models.LLM.qwen.qwen3__0_6b.A100.single_batch.decode_schedule"
+    pkg = importlib.import_module(qpkg)
+    ops = importlib.import_module(qpkg + ".fused.operations")
+    cfg = dict(QWEN3_0_6B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    pkg.Qwen3Config.update_from_dict({k: cfg[k] for k in (
+        "num_hidden_layers", "hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
+        "num_key_value_heads", "vocab_size", "rms_norm_eps")})
+    w = synthetic.make_weights(cfg, seed=2468, device="cpu", gain_jitter=0.1)
+    n_steps, S, L = 10, 16, cfg["num_hidden_layers"]
+    NH, NKV, HD, H, I, V = (cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                            cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"])
+    tokens = synthetic.make_prompt(V, n_steps, seed=55).tolist()
+    out = {"tokens": np.array(tokens, dtype=np.int64), "weights_seed": np.int64(2468), "prompt_seed": np.int64(55)}
+    for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        cast = lambda t: t.to(dtype)
+        g = pkg.Globals(
+            position_id=0,
+            attn_norm_weights=cast(w["attn_norm_weights"]), qkv_weights=cast(w["qkv_weights"]),
+            q_norm_weights=cast(w["q_norm_weights"]), k_norm_weights=cast(w["k_norm_weights"]),
+            o_proj_weights=cast(w["o_proj_weights"]), mlp_norm_weights=cast(w["mlp_norm_weights"]),
+            up_proj_weights=cast(w["up_proj_weights"]), gate_proj_weights=cast(w["gate_proj_weights"]),
+            down_proj_weights=cast(w["down_proj_weights"]), lm_head_norm_weights=cast(w["lm_head_norm_weights"]),
+            lm_head_weights=cast(w["lm_head_weights"]), rope_cos=w["rope_cos"].float(), rope_sin=w["rope_sin"].float(),
+            k_cache=torch.zeros(L, 1, S, NKV, HD, dtype=dtype), v_cache=torch.zeros(L, 1, S, NKV, HD, dtype=dtype),
+            hidden_states=torch.zeros(H, dtype=dtype), qkv_raw=torch.zeros((NH + 2 * NKV) * HD, dtype=dtype),
+            q_post_rope=torch.zeros(NH * HD, dtype=dtype), attn_out=torch.zeros(NH * HD, dtype=dtype),
+            silu_out=torch.zeros(I, dtype=dtype), logits=torch.zeros(V, dtype=dtype))
+        embed = cast(w["embed_tokens"])
+        recs = []
+        for pos, tok in enumerate(tokens):
+            g.hidden_states.copy_(embed[tok])
+            g.position_id = pos
+            r, hid = {}, []
+            for layer in range(L):
+                ops.fused_rms_qkvproj_gemv_rope(g, layer)
+                if layer == L - 1:
+                    r["q_post_rope"] = g.q_post_rope.clone()
+                    r["k_row"] = g.k_cache[layer, 0, pos].clone()
+                    r["v_row"] = g.v_cache[layer, 0, pos].clone()
+                ops.fused_decode_attention(g, layer)
+                if layer == L - 1:
+                    r["attn_out"] = g.attn_out.clone()
+                ops.fused_oproj_gemv_residual(g, layer)
+                ops.fused_mlp_upgate(g, layer)
+                if layer == L - 1:
+                    r["silu_out"] = g.silu_out.clone()
+                ops.fused_mlp_down_residual(g, layer)
+                hid.append(g.hidden_states.clone())
+            ops.fused_rms_lmhead_gemv(g)
+            r["layer_hidden"] = torch.stack(hid)
+            r["logits"] = g.logits.clone()
+            r["argmax"] = int(g.logits.argmax())
+            recs.append(r)
+        keys = ("layer_hidden", "logits") if name == "fp32" else (
+            "q_post_rope", "k_row", "v_row", "attn_out", "silu_out", "layer_hidden", "logits")
+        for k in keys:
+            out[f"{name}_{k}"] = np.stack([bits(r[k]) for r in recs])
+        out[f"{name}_argmax"] = np.array([r["argmax"] for r in recs], dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "qwen3_l2_v4096.npz"), **out)
+    print("wrote qwen3_l2_v4096.npz")
+
+
 def make_full(pkg, ops, n_new: int):
     cfg = dict(LLAMA_3_2_1B)
     t0 = time.time()
@@ -171,7 +316,13 @@ if __name__ == "__main__":
     ap.add_argument("--new-tokens", type=int, default=16)
     args = ap.parse_args()
     torch.manual_seed(0)
+    ap_only = os.environ.get("QMK_GOLDEN_ONLY", "")
     pkg, ops = ref_modules()
-    make_small(pkg, ops)
+    if ap_only in ("", "small"):
+        make_small(pkg, ops)
+    if ap_only in ("", "batch"):
+        make_batch(ops)
+    if ap_only in ("", "qwen3"):
+        make_qwen3()
     if args.full:
         make_full(pkg, ops, args.new_tokens)

@@ -1,0 +1,387 @@
+"""GPU parity of the batched decode kernel (runtime shapes, B sequences per step, tcgen05 tiles) against the
+CPU oracle, through the C ABI.
+
+Same method and tolerances as tests/test_gpu_parity.py: per-op checks with identical inputs on both sides
+(|d| <= 1e-2*|ref| + 2e-3*max|ref|, plus 1e-2*|projection term| for the two residual phases), whole steps
+against the fp32 oracle (relative L2 <= 2e-2 per layer) and the bf16 oracle, arg-max exact wherever the
+oracle's top two logits are not within two bf16 units of each other.  Covered here: a ragged batch with a
+late row and a finished row, batches that pad to 16 / 32 / 64 tensor-core columns, shapes whose row tiles and
+k-splits do not divide evenly (partial tiles, rows past the end), head_dim 128 with the Qwen3 Q/K norm,
+split-KV with several partials per sequence, the batched kernel at batch 1 on the Llama-3.2-1B layer shape,
+the reference-generated fixtures, and the bounded-wait failure path.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import _util as U
+from oracle import fused_oracle as fo
+
+pytestmark = pytest.mark.gpu
+
+OP_RTOL, OP_ATOL_FRAC = 1e-2, 2e-3
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def assert_op_close(actual, expected, what, residual_in=None):
+    a, e = actual.float().cpu(), expected.float().cpu()
+    tol = OP_RTOL * e.abs() + OP_ATOL_FRAC * float(e.abs().max())
+    if residual_in is not None:
+        tol = tol + OP_RTOL * (e - residual_in.float().cpu()).abs()
+    bad = (a - e).abs() > tol
+    assert not bool(bad.any()), (
+        f"{what}: {int(bad.sum())} of {bad.numel()} elements out of tolerance; "
+        f"max abs diff {float((a - e).abs().max()):.4g}, max |ref| {float(e.abs().max()):.4g}")
+
+
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+
+
+class Env:
+    """Oracle state (bf16 and fp32) and device Globals around the same seeded weights."""
+
+    def __init__(self, cfg, batch, S, seed, variant=1):
+        from qimeng_megakernel_b200 import mk_kernel, synthetic
+        self.cfg, self.B, self.S = cfg, batch, S
+        self.w = synthetic.make_weights(cfg, seed=seed, device="cpu", gain_jitter=0.1, max_positions=S)
+        lead = None if batch is None else batch
+        self.g = synthetic.make_globals(cfg, self.w, kv_seq_len=S, device="cuda", batch=lead)
+        nb = batch or 1
+        self.g.position_ids = torch.zeros(nb, dtype=torch.int32, device="cuda")
+        self.g.active_mask = torch.ones(nb, dtype=torch.uint8, device="cuda")
+        self.st = U.oracle_state(cfg, self.w, S, torch.bfloat16, batch=lead)
+        self.st32 = U.oracle_state(cfg, self.w, S, torch.float32, batch=lead)
+        self.mk = mk_kernel.get_mk()
+        self.mk.set_kernel_variant(variant)
+
+    def close(self):
+        self.mk.close()
+
+    def rows(self, positions):
+        nb = self.B or 1
+        return [(b, positions[b]) for b in range(nb)]
+
+
+def per_op_walk(env, positions, active, modes=(0, 1), layers=None):
+    """One step of the oracle, phase by phase; before every phase its state is copied to the device and the same
+    phase is run there alone (mode 0: its own launch; mode 1: a one-phase persistent launch)."""
+    from qimeng_megakernel_b200.model_config import LlamaConfig
+    st, g, mk, cfg = env.st, env.g, env.mk, env.cfg
+    LlamaConfig.update_from_dict(cfg)   # (a process-wide singleton, like the reference's config classes)
+    L = cfg["num_hidden_layers"]
+    st.position_ids, st.active_mask = list(positions), [bool(a) for a in active]
+    nb = env.B or 1
+    act = [b for b in range(nb) if active[b]]
+    bh = fo._bh
+    for layer in (range(L) if layers is None else layers):
+        for mode in modes:
+            saved = {n: getattr(st, n).clone() for n in U.STATE_BUFFERS}
+            U.push_state(st, g); fo.qkv_rope(st, layer)
+            mk.run_phases(g, layer * 5 + 0, layer * 5 + 1, mode)
+            what = f"layer {layer} mode {mode} pos {positions}"
+            for b in act:
+                assert_op_close(bh(g.q_post_rope)[b], bh(st.q_post_rope)[b], f"q_post_rope row {b} {what}")
+                assert_op_close(g.k_cache[layer, b, positions[b]], st.k_cache[layer, b, positions[b]], f"k row {b} {what}")
+                assert_op_close(g.v_cache[layer, b, positions[b]], st.v_cache[layer, b, positions[b]], f"v row {b} {what}")
+            U.push_state(st, g); fo.decode_attention(st, layer)
+            mk.run_phases(g, layer * 5 + 1, layer * 5 + 2, mode)
+            assert_op_close(g.attn_out, st.attn_out, f"attn_out {what}")
+            U.push_state(st, g); h_in = st.hidden_states.clone(); fo.oproj_residual(st, layer)
+            mk.run_phases(g, layer * 5 + 2, layer * 5 + 3, mode)
+            assert_op_close(g.hidden_states, st.hidden_states, f"o-proj hidden {what}", h_in)
+            U.push_state(st, g); fo.mlp_upgate(st, layer)
+            mk.run_phases(g, layer * 5 + 3, layer * 5 + 4, mode)
+            assert_op_close(g.silu_out, st.silu_out, f"silu_out {what}")
+            U.push_state(st, g); h_in = st.hidden_states.clone(); fo.mlp_down_residual(st, layer)
+            mk.run_phases(g, layer * 5 + 4, layer * 5 + 5, mode)
+            assert_op_close(g.hidden_states, st.hidden_states, f"down hidden {what}", h_in)
+            if mode != modes[-1]:   # replay the layer from the same inputs in the next mode
+                for n, t in saved.items():
+                    getattr(st, n).copy_(t)
+    if layers is None:
+        for mode in modes:
+            U.push_state(st, g); fo.lm_head(st)
+            g.next_token.fill_(-1)
+            mk.run_phases(g, 5 * L, 5 * L + 1, mode)
+            assert_op_close(g.logits, st.logits, f"logits mode {mode} pos {positions}")
+            # fused arg-max = arg-max of the kernel's own bf16 logits, lowest index on ties
+            own = bh(g.logits).float().argmax(dim=-1)
+            assert g.next_token.tolist() == own.tolist()
+    mk.check_status()
+
+
+def random_tokens(cfg, n, seed):
+    return torch.randint(0, cfg["vocab_size"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def embed_rows(st, tokens):
+    st.hidden_states.copy_(fo._bh(st.embed_tokens[torch.tensor(tokens)]).reshape(st.hidden_states.shape))
+
+
+ODD = dict(num_hidden_layers=2, hidden_size=320, intermediate_size=704, head_dim=64, num_attention_heads=4,
+           num_key_value_heads=2, vocab_size=1000, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+           max_position_embeddings=512)
+MHA128 = dict(num_hidden_layers=1, hidden_size=256, intermediate_size=512, head_dim=128, num_attention_heads=2,
+              num_key_value_heads=2, vocab_size=777, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+              max_position_embeddings=512)
+
+
+@pytest.mark.parametrize("cfg,batch", [(ODD, 3), (ODD, 17), (ODD, 64), (MHA128, 5), (ODD, None)])
+def test_small_shapes_per_op(cfg, batch):
+    """Shapes whose row tiles, k-blocks and batch do not divide evenly: 148 CTAs share a handful of tiles, so almost
+    every tile is finished from split-K partials; rows past the end of every matrix; 3 / 17 / 64 rows pad to
+    16 / 32 / 64 columns."""
+    _need_gpu()
+    env = Env(cfg, batch, 512, seed=31)
+    try:
+        nb = batch or 1
+        gen = torch.Generator().manual_seed(3)
+        for step in range(3):
+            positions = [int(p) for p in torch.randint(0, 40, (nb,), generator=gen)] if step else [0] * nb
+            active = [1] * nb
+            if nb > 2 and step == 2:
+                active[1] = 0
+            if step:   # something to attend to
+                env.st.k_cache.copy_(torch.randn(env.st.k_cache.shape, generator=gen) * 0.5)
+                env.st.v_cache.copy_(torch.randn(env.st.v_cache.shape, generator=gen) * 0.5)
+            embed_rows(env.st, random_tokens(cfg, nb, 100 + step))
+            per_op_walk(env, positions, active)
+    finally:
+        env.close()
+
+
+@pytest.fixture(scope="module")
+def llama_small(small_config):
+    _need_gpu()
+    env = Env(small_config, 8, 1024, seed=1234)
+    yield env
+    env.close()
+
+
+def test_llama_shape_batch8_per_op(llama_small):
+    """Llama-3.2-1B layer shape, 2 layers, eight sequences at ragged positions, one finished."""
+    env = llama_small
+    gen = torch.Generator().manual_seed(8)
+    env.st.k_cache.copy_(torch.randn(env.st.k_cache.shape, generator=gen) * 0.5)
+    env.st.v_cache.copy_(torch.randn(env.st.v_cache.shape, generator=gen) * 0.5)
+    embed_rows(env.st, random_tokens(env.cfg, 8, 5))
+    per_op_walk(env, [0, 31, 32, 33, 100, 511, 1023, 7], [1, 1, 1, 0, 1, 1, 1, 1])
+
+
+def test_llama_shape_batch8_steps(llama_small):
+    """Twelve teacher-forced steps of eight sequences: per-layer hidden states against the fp32 oracle (rtol 2e-2)
+    and the bf16 oracle, arg-max exact on untied rows, device-resident token loop (token_in = next_token)."""
+    from qimeng_megakernel_b200.model_config import LlamaConfig
+    env = llama_small
+    st, st32, g, mk, cfg = env.st, env.st32, env.g, env.mk, env.cfg
+    LlamaConfig.update_from_dict(cfg)
+    for s in (st, st32):
+        s.k_cache.zero_(); s.v_cache.zero_()
+    g.k_cache.zero_(); g.v_cache.zero_()
+    B, L, n_steps = 8, cfg["num_hidden_layers"], 12
+    from qimeng_megakernel_b200 import synthetic
+    prompts = synthetic.make_prompts(cfg["vocab_size"], B, n_steps, seed=21)
+    g.token_in = torch.zeros(B, dtype=torch.int64, device="cuda")
+    g.out_tokens = torch.full((B, n_steps + 1), -1, dtype=torch.int64, device="cuda")
+    g.active_mask.fill_(1)
+    agree = total = 0
+    for step in range(n_steps):
+        toks = prompts[:, step].tolist()
+        positions = [step] * B
+        ref = fo.feed_tokens(st, toks, positions, record_layers=True)
+        fo.feed_tokens(st32, toks, positions, record_layers=True)
+        g.token_in.copy_(prompts[:, step])
+        g.position_ids.fill_(step)
+        g.position_id = step
+        mk(g)
+        torch.cuda.synchronize()
+        hid = g.hidden_states.float().cpu()
+        h32, h16 = st32.layer_hidden[-1].float(), st.layer_hidden[-1].float()
+        ref_gap = U.rel_l2(h16, h32)
+        assert U.rel_l2(hid, h32) <= max(2e-2, 1.25 * ref_gap), f"step {step}: hidden vs fp32 oracle"
+        assert U.rel_l2(hid, h16) <= max(2e-2, 1.5 * ref_gap), f"step {step}: hidden vs bf16 oracle"
+        got = g.next_token.tolist()
+        assert got == g.out_tokens[:, step + 1].tolist()
+        top2 = st.logits.float().topk(2, dim=-1).values
+        for b in range(B):
+            total += 1
+            untied = float(top2[b, 0] - top2[b, 1]) > 2 * 2.0 ** -8 * abs(float(top2[b, 0]))
+            if got[b] == ref[b]:
+                agree += 1
+            else:
+                assert not untied, f"step {step} row {b}: arg-max {got[b]} != oracle {ref[b]} on an untied row"
+    assert agree >= 0.99 * total
+    mk.check_status()
+    g.token_in = None
+    g.out_tokens = None
+
+
+def test_batched_kernel_at_batch_one_llama_shape(small_config, small_weights):
+    """The batched kernel serving one sequence with the reference's single-batch shapes ([H] state)."""
+    _need_gpu()
+    env = Env(small_config, None, 256, seed=1234)
+    try:
+        gen = torch.Generator().manual_seed(2)
+        env.st.k_cache.copy_(torch.randn(env.st.k_cache.shape, generator=gen) * 0.5)
+        env.st.v_cache.copy_(torch.randn(env.st.v_cache.shape, generator=gen) * 0.5)
+        embed_rows(env.st, random_tokens(env.cfg, 1, 9))
+        per_op_walk(env, [77], [1])
+    finally:
+        env.close()
+
+
+def test_split_kv_long_context():
+    """Few sequences, long contexts: many key ranges per (sequence, kv head), merged by the last arriver."""
+    _need_gpu()
+    cfg = dict(ODD, max_position_embeddings=8192)
+    env = Env(cfg, 2, 8192, seed=5)
+    try:
+        st, g, mk = env.st, env.g, env.mk
+        gen = torch.Generator().manual_seed(11)
+        st.k_cache.copy_(torch.randn(st.k_cache.shape, generator=gen) * 0.5)
+        st.v_cache.copy_(torch.randn(st.v_cache.shape, generator=gen) * 0.5)
+        for positions in ([8191, 4000], [63, 64], [2047, 0], [777, 5000]):
+            st.position_ids, st.active_mask = positions, [True, True]
+            st.q_post_rope.copy_(torch.randn(st.q_post_rope.shape, generator=gen))
+            for layer in range(cfg["num_hidden_layers"]):
+                U.push_state(st, g); fo.decode_attention(st, layer)
+                for mode in (0, 1):
+                    g.attn_out.zero_()
+                    mk.run_phases(g, layer * 5 + 1, layer * 5 + 2, mode)
+                    assert_op_close(g.attn_out, st.attn_out, f"attn_out pos {positions} layer {layer} mode {mode}")
+        mk.check_status()
+    finally:
+        env.close()
+
+
+def _as_bf16(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+def test_ragged_batch_against_reference_fixture():
+    """The reference's own outputs for three ragged sequences (tests/golden/batch3_l2_v4096.npz)."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import mk_kernel, synthetic
+    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B
+    z = np.load(os.path.join(GOLD, "batch3_l2_v4096.npz"))
+    cfg = dict(LLAMA_3_2_1B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    w = synthetic.make_weights(cfg, seed=int(z["weights_seed"]), device="cpu", gain_jitter=0.1)
+    prompts = torch.from_numpy(z["prompts"])
+    B = prompts.shape[0]
+    g = synthetic.make_globals(cfg, w, kv_seq_len=16, device="cuda", batch=B)
+    g.position_ids = torch.zeros(B, dtype=torch.int32, device="cuda")
+    g.active_mask = torch.ones(B, dtype=torch.uint8, device="cuda")
+    g.token_in = torch.zeros(B, dtype=torch.int64, device="cuda")
+    mk = mk_kernel.get_mk()
+    try:
+        for step, (positions, active) in enumerate(zip(z["positions"].tolist(), z["active"].tolist())):
+            g.token_in.copy_(torch.tensor([int(prompts[b, positions[b]]) for b in range(B)]))
+            g.position_ids.copy_(torch.tensor(positions, dtype=torch.int32))
+            g.active_mask.copy_(torch.tensor(active, dtype=torch.uint8))
+            g.position_id = max(positions)
+            mk(g)
+            torch.cuda.synchronize()
+            ref_h = _as_bf16(z["bf16_layer_hidden"][step])[-1].float()
+            ref32 = torch.from_numpy(z["fp32_layer_hidden"][step])[-1]
+            for b in range(B):
+                gap = U.rel_l2(ref_h[b], ref32[b])
+                assert U.rel_l2(g.hidden_states[b], ref32[b]) <= max(2e-2, 1.25 * gap), f"step {step} row {b} vs fp32"
+                assert U.rel_l2(g.hidden_states[b], ref_h[b]) <= max(2e-2, 1.5 * gap), f"step {step} row {b} vs bf16"
+            ref_logits = _as_bf16(z["bf16_logits"][step]).float()
+            for b in range(B):
+                if not active[b]:
+                    assert bool((g.logits[b].float() <= -9e8).all()), f"step {step}: finished row {b} must get -1e9 logits"
+                    continue
+                top2 = ref_logits[b].topk(2).values
+                if float(top2[0] - top2[1]) > 2 * 2.0 ** -8 * abs(float(top2[0])):
+                    assert int(g.next_token[b]) == int(z["bf16_argmax"][step][b]), f"step {step} row {b} arg-max"
+            assert_op_close(g.q_post_rope[0], _as_bf16(z["bf16_q_post_rope"][step])[0], f"q_post_rope step {step}")
+        st = mk.poll_status()
+        assert st["rc"] == 0, st
+    finally:
+        mk.close()
+
+
+@pytest.mark.parametrize("batch", [None, 5])
+def test_qwen3_shape(batch):
+    """Qwen3-0.6B layer shape (hidden 1024, 16 / 8 heads of 128, intermediate 3072) with the per-head Q/K RMSNorm:
+    per-op parity at ragged positions, then the reference-generated fixture for one sequence."""
+    _need_gpu()
+    from qimeng_megakernel_b200.model_config import QWEN3_0_6B
+    cfg = dict(QWEN3_0_6B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    env = Env(cfg, batch, 256, seed=2468)
+    try:
+        nb = batch or 1
+        gen = torch.Generator().manual_seed(4)
+        env.st.k_cache.copy_(torch.randn(env.st.k_cache.shape, generator=gen) * 0.5)
+        env.st.v_cache.copy_(torch.randn(env.st.v_cache.shape, generator=gen) * 0.5)
+        embed_rows(env.st, random_tokens(cfg, nb, 6))
+        per_op_walk(env, [0, 200, 31, 32, 255][:nb], [1, 1, 0, 1, 1][:nb] if nb > 1 else [1])
+        if batch is not None:
+            return
+        z = np.load(os.path.join(GOLD, "qwen3_l2_v4096.npz"))
+        g, mk = env.g, env.mk
+        g.k_cache.zero_(); g.v_cache.zero_()
+        g.token_in = torch.zeros(1, dtype=torch.int64, device="cuda")
+        g.position_ids = None
+        g.active_mask = None
+        for pos, tok in enumerate(z["tokens"].tolist()):
+            g.token_in.fill_(tok)
+            g.position_id = pos
+            mk(g)
+            torch.cuda.synchronize()
+            ref_h = _as_bf16(z["bf16_layer_hidden"][pos])[-1].float()
+            ref32 = torch.from_numpy(z["fp32_layer_hidden"][pos])[-1]
+            gap = U.rel_l2(ref_h, ref32)
+            assert U.rel_l2(g.hidden_states, ref32) <= max(2e-2, 1.25 * gap), f"step {pos} vs fp32"
+            assert U.rel_l2(g.hidden_states, ref_h) <= max(2e-2, 1.5 * gap), f"step {pos} vs bf16"
+            assert_op_close(g.q_post_rope, _as_bf16(z["bf16_q_post_rope"][pos]), f"q_post_rope step {pos}")
+            top2 = _as_bf16(z["bf16_logits"][pos]).float().topk(2).values
+            if float(top2[0] - top2[1]) > 2 * 2.0 ** -8 * abs(float(top2[0])):
+                assert int(g.next_token[0]) == int(z["bf16_argmax"][pos]), f"step {pos} arg-max"
+        mk.check_status()
+    finally:
+        env.close()
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A phase made to wait for a dependency nothing publishes: the wait expires after its (shortened) budget, the
+    launch returns, the status record names the counter wait, and the handle keeps working afterwards."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import _lib
+    env = Env(ODD, 3, 64, seed=1)
+    try:
+        g, mk = env.g, env.mk
+        embed_rows(env.st, [1, 2, 3]); U.push_state(env.st, g)
+        mk.run_phases(g, 0, 1, 1)          # creates the handle
+        mk.set_timeout_cycles(20_000_000)  # ~10 ms
+        mk.set_wait_first_dependency(True)
+        mk.run_phases(g, 2, 3, 1)
+        st = mk.poll_status()
+        assert st["rc"] == _lib.ERR_DEVICE_TIMEOUT and st["code"] == 1 and st["phase"] == 2, st
+        mk.set_wait_first_dependency(False)
+        mk.set_timeout_cycles(2_000_000_000)
+        env.st.position_ids, env.st.active_mask = [0, 0, 0], [True] * 3
+        per_op_walk(env, [0, 0, 0], [1, 1, 1], modes=(1,))
+    finally:
+        env.close()
+
+
+def test_argument_validation():
+    _need_gpu()
+    from qimeng_megakernel_b200 import synthetic, mk_kernel
+    bad = dict(ODD, head_dim=32, num_attention_heads=8)
+    w = synthetic.make_weights(bad, seed=1, device="cpu", max_positions=64)
+    g = synthetic.make_globals(bad, w, kv_seq_len=64, device="cuda", batch=2)
+    mk = mk_kernel.get_mk()
+    with pytest.raises(RuntimeError):
+        mk(g)
+    mk.close()
+    w = synthetic.make_weights(ODD, seed=1, device="cpu", max_positions=64)
+    with pytest.raises(ValueError):
+        g = synthetic.make_globals(ODD, w, kv_seq_len=64, device="cuda", batch=65)
+        mk_kernel.get_mk()(g)

@@ -66,6 +66,82 @@ def test_small_model_every_buffer(small_config, small_weights):
         assert nxt32 == int(z["fp32_argmax"][pos])
 
 
+def _walk_layers(st, L, z, step, rows_of, names):
+    """Run one step of the oracle layer by layer; compare the last layer's buffers with the fixture."""
+    hid = []
+    for layer in range(L):
+        fo.qkv_rope(st, layer)
+        if layer == L - 1:
+            _assert_bits(st.q_post_rope, z["bf16_q_post_rope"][step], f"q_post_rope step {step}")
+            k_row, v_row = rows_of(st, layer)
+            _assert_bits(k_row, z["bf16_k_row"][step], f"k row step {step}")
+            _assert_bits(v_row, z["bf16_v_row"][step], f"v row step {step}")
+        fo.decode_attention(st, layer)
+        if layer == L - 1:
+            _assert_bits(st.attn_out, z["bf16_attn_out"][step], f"attn_out step {step}")
+        fo.oproj_residual(st, layer)
+        if layer == L - 1 and "hidden_after_oproj" in names:
+            _assert_bits(st.hidden_states, z["bf16_hidden_after_oproj"][step], f"hidden after o-proj step {step}")
+        fo.mlp_upgate(st, layer)
+        if layer == L - 1:
+            _assert_bits(st.silu_out, z["bf16_silu_out"][step], f"silu_out step {step}")
+        fo.mlp_down_residual(st, layer)
+        hid.append(st.hidden_states.clone())
+    fo.lm_head(st)
+    _assert_bits(torch.stack(hid), z["bf16_layer_hidden"][step], f"layer hidden step {step}")
+    _assert_bits(st.logits, z["bf16_logits"][step], f"logits step {step}")
+
+
+def test_ragged_batch_every_buffer():
+    """Three sequences in [B, H] state with per-row positions, a late start and an early finish: the fixture is the
+    reference's fused ops on its multi-batch Globals."""
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B
+    z = np.load(os.path.join(GOLD, "batch3_l2_v4096.npz"))
+    cfg = dict(LLAMA_3_2_1B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    w = synthetic.make_weights(cfg, seed=int(z["weights_seed"]), device="cpu", gain_jitter=0.1)
+    prompts = torch.from_numpy(z["prompts"])
+    B, L = prompts.shape[0], cfg["num_hidden_layers"]
+    st = U.oracle_state(cfg, w, 16, torch.bfloat16, batch=B)
+    st32 = U.oracle_state(cfg, w, 16, torch.float32, batch=B)
+    for step, (positions, active) in enumerate(zip(z["positions"].tolist(), z["active"].tolist())):
+        toks = [int(prompts[b, positions[b]]) for b in range(B)]
+        st.hidden_states.copy_(st.embed_tokens[torch.tensor(toks)])
+        st.position_ids, st.active_mask = positions, [bool(a) for a in active]
+        rows = lambda s, layer: (torch.stack([s.k_cache[layer, b, positions[b]] for b in range(B)]),
+                                 torch.stack([s.v_cache[layer, b, positions[b]] for b in range(B)]))
+        _walk_layers(st, L, z, step, rows, {"hidden_after_oproj"})
+        assert st.logits.argmax(dim=-1).tolist() == z["bf16_argmax"][step].tolist()
+        for b in range(B):
+            if not active[b]:   # a finished row: logits pinned to -1e9, nothing else moves
+                assert bool((st.logits[b].float() <= -9e8).all())
+        got = fo.feed_tokens(st32, toks, positions, active, record_layers=True)
+        exp = torch.from_numpy(z["fp32_layer_hidden"][step])
+        assert torch.allclose(torch.stack(st32.layer_hidden), exp, rtol=1e-5, atol=1e-5), f"fp32 hidden step {step}"
+        assert got == z["fp32_argmax"][step].tolist()
+
+
+def test_qwen3_every_buffer():
+    """Qwen3 layer shape (head_dim 128, per-head Q/K RMSNorm before RoPE) against the reference's Qwen3 fused ops."""
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.model_config import QWEN3_0_6B
+    z = np.load(os.path.join(GOLD, "qwen3_l2_v4096.npz"))
+    cfg = dict(QWEN3_0_6B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    w = synthetic.make_weights(cfg, seed=int(z["weights_seed"]), device="cpu", gain_jitter=0.1)
+    L = cfg["num_hidden_layers"]
+    st = U.oracle_state(cfg, w, 16, torch.bfloat16)
+    st32 = U.oracle_state(cfg, w, 16, torch.float32)
+    for pos, tok in enumerate(z["tokens"].tolist()):
+        st.hidden_states.copy_(st.embed_tokens[tok]); st.position_id = pos
+        rows = lambda s, layer: (s.k_cache[layer, 0, pos], s.v_cache[layer, 0, pos])
+        _walk_layers(st, L, z, pos, rows, set())
+        assert int(st.logits.argmax()) == int(z["bf16_argmax"][pos])
+        nxt32 = fo.feed_token(st32, tok, pos, record_layers=True)
+        exp = torch.from_numpy(z["fp32_layer_hidden"][pos])
+        assert torch.allclose(torch.stack(st32.layer_hidden), exp, rtol=1e-5, atol=1e-5), f"fp32 hidden step {pos}"
+        assert nxt32 == int(z["fp32_argmax"][pos])
+
+
 def test_full_fixture_is_self_consistent():
     """Shape and content checks of the full-size Llama-3.2-1B fixture the GPU tests compare against (the
     oracle itself needs ~3 s per full-size step, so its full-size run is left to the GPU suite)."""
