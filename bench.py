@@ -125,8 +125,15 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (rank 0, N = 1 only)")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per GPU (> 1, or any --model but llama: the batched kernel)")
+    ap.add_argument("--model", default="llama-3.2-1b", choices=["llama-3.2-1b", "qwen3-0.6b"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "batched"], help="batched: the batched kernel also at batch 1")
     args = ap.parse_args()
     K, W = args.steps, max(3, args.warmup)
+    if args.batch != 1 or args.model != "llama-3.2-1b" or args.kernel == "batched":
+        if args.impl == "reference":
+            raise SystemExit("--impl reference times the headline workload (batch 1, Llama-3.2-1B shape) only")
+        return main_batched(args, K, W)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -259,6 +266,121 @@ def main() -> None:
             line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
         else:
             line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main_batched(args, K: int, W: int) -> None:
+    """BASELINE configurations 3 and 4: B independent seeded sequences per GPU (batch-sharded over the ranks, no
+    collective), every step one launch of the batched kernel; the device feeds each row's arg-max back as its next
+    token.  Same timing rules as the headline run; not the line the driver records."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    from qimeng_megakernel_b200 import mk_kernel, synthetic
+    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, QWEN3_0_6B
+    config = dict(LLAMA_3_2_1B if args.model == "llama-3.2-1b" else QWEN3_0_6B)
+    B = args.batch
+    kv_len = PROMPT_LEN + W + K + 1
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    weights = synthetic.make_weights(config, seed=0, device=dev, max_positions=max(2048, kv_len))
+    g = synthetic.make_globals(config, weights, kv_seq_len=kv_len, device=dev, batch=B)
+    mk = mk_kernel.get_mk()
+    mk.set_kernel_variant(1)
+    prompts = synthetic.make_prompts(config["vocab_size"], B, PROMPT_LEN, seed=1 + rank * B).to(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    g.token_in = torch.zeros(B, dtype=torch.int64, device=dev)
+    g.next_token = torch.zeros(B, dtype=torch.int64, device=dev)
+    for pos in range(PROMPT_LEN):           # the prompts, one position per launch (fills the KV cache)
+        g.token_in.copy_(prompts[:, pos]); g.position_id = pos
+        mk(g)
+    g.next_token = g.token_in               # from here on the kernel feeds its arg-max back
+    g.position_id = PROMPT_LEN
+    g.token_in.copy_(prompts[:, 0])
+    mk(g)
+    pos = PROMPT_LEN + 1
+    for _ in range(W):
+        mk._lib.qmk_decode_step(mk._handle, pos, stream); pos += 1
+    torch.cuda.synchronize(dev)
+    mk.check_status()
+    first_timed_pos = pos
+    launches0 = mk.launch_count
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    for i in range(K):
+        events[i][0].record()
+        rc = mk._lib.qmk_decode_step(mk._handle, pos, stream)
+        events[i][1].record()
+        if rc != 0:
+            raise SystemExit(f"qmk_decode_step failed: {rc}")
+        pos += 1
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    mk.check_status()
+    kernel_s = sum(a.elapsed_time(b) for a, b in events) / 1e3
+    launches = mk.launch_count - launches0
+    step_bytes = sum(mk.step_bytes(first_timed_pos + i) for i in range(K)) / K
+
+    # end to end with host token buffers: per step B tokens host -> device, the launch, B arg-max values device -> host
+    host_in = prompts[:, :1].cpu().repeat(1, K + 1).t().contiguous().pin_memory()      # [K + 1, B]
+    host_out = torch.zeros(K, B, dtype=torch.int64).pin_memory()
+    tok_dev = torch.zeros(B, dtype=torch.int64, device=dev)
+    out_dev = torch.zeros(B, dtype=torch.int64, device=dev)
+    g.token_in, g.next_token = tok_dev, out_dev
+    g.position_id = first_timed_pos
+    mk(g)                                   # re-binds the state (untimed)
+    pos = first_timed_pos
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        tok_dev.copy_(host_in[i], non_blocking=True)
+        rc = mk._lib.qmk_decode_step(mk._handle, pos, stream)
+        host_out[i].copy_(out_dev, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        host_in[i + 1].copy_(host_out[i])
+        pos += 1
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    mk.check_status()
+    times = torch.tensor([kernel_s, e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    kernel_s, e2e_s = (float(x) for x in times.tolist())
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        achieved = step_bytes / (kernel_s / K) / 1e9
+        ctas, threads, smem = mk.geometry()
+        line = {
+            "metric": f"decode kernel_tok_s at batch {B} per GPU ({args.model} shape)", "value": world * B * K / kernel_s,
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": kernel_s / K * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.model} shape, bf16, {B} independent seeded 16-token prompts per GPU, greedy decode "
+                                   "forced past EOS", "decode_steps": K,
+                       "kv_lengths": [first_timed_pos + 1, first_timed_pos + K], "sequences_per_gpu": B,
+                       "sharding": "sequences sharded over the GPUs, full weight copy each, no collective",
+                       "l2": "inputs larger than L2: every step streams the weights through a 126 MB L2",
+                       "launch": {"ctas": ctas, "threads": threads, "smem_bytes": smem}},
+            "e2e": {"value": world * B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
+            "gpu_launches": launches + K,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": step_bytes,
+                         "kernel": "qmk_batch_kernel (one persistent launch per decode step)"},
+            "clocks": clocks, "cpu_baseline": None,
+        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -210,7 +210,8 @@ int qmk_set_wait_first_dependency(qmk_handle* h, int32_t on);
 /* Which kernel serves the handle.  0 (default): the batch-1 kernel when the descriptor has its compiled
  * shape and one sequence is bound, else the batched kernel.  1: always the batched kernel (any batch,
  * also 1).  The batched kernel implements qmk_decode_step, qmk_run_phases, qmk_generate_host (batch 1),
- * qmk_poll_status and the wait-first knob; qmk_set_trace applies to the batch-1 kernel only. */
+ * qmk_poll_status, the wait-first knob and qmk_set_trace (slots 0 dependency satisfied, 1 first accumulator of the
+ * phase complete, 2 epilogue warps enter, 5 the CTA arrives at the phase's counter). */
 int qmk_set_kernel_variant(qmk_handle* h, int32_t variant);
 
 /* Optional device timeline (the counterpart of the reference's ENABLE_PROFILING clock64 buffer,

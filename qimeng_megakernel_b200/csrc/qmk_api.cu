@@ -218,6 +218,7 @@ static int batched_launch(qmk_handle* h, int pos, int phase_begin, int phase_end
   a.wait_first = wait_first;
   a.cooperative = h->cooperative;
   a.timeout_cycles = h->timeout_cycles;
+  a.trace = h->trace;
   rc = qmkb_launch(h->bctx, &h->st, &a, stream, h->cuda_err, sizeof(h->cuda_err));
   if (rc) return rc;
   h->launches++;

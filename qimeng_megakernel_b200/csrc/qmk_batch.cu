@@ -208,6 +208,7 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.argmax_key = c->argmax_key;
   p.phase_done = c->phase_done;
   p.status = c->status;
+  p.trace = a->trace;
   p.H = d.hidden_size;
   p.I = d.intermediate_size;
   p.NH = d.num_attention_heads;

@@ -21,6 +21,7 @@ struct qmkb_launch_args {
   int wait_first;
   int cooperative;
   long long timeout_cycles;
+  unsigned long long* trace;   // optional timeline buffer (qmk_set_trace), or null
 };
 // One launch of phases [phase_begin, phase_end) (plus the memset of the arrival counters before it).
 int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_args* a, cudaStream_t stream, char* err,

@@ -142,6 +142,13 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
   }
 }
 
+// Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
+// satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
+// the phase, 5 the CTA arrives at the phase's counter.
+__device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
+  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (5 * p.num_layers + 1) + ph) * 8 + slot] = globaltimer_ns();
+}
+
 struct Ctx {
   const BParams* p;
   unsigned char* smem;
@@ -307,6 +314,7 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
     bool needed;
     const bool ok = phase_dependency(c, ph, needed);
     (void)ok;
+    trace_put(p, ph, 0);
   }
   named_bar(kBarStg, 128);
   const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
@@ -323,27 +331,40 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : p.hidden;
   const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
                        : kind == kUpGate ? p.mlp_norm + (size_t)layer * p.H : p.lm_norm;
-  const int chunk = st & 7;           // 16-byte piece inside the 128-byte k-block row
-  const int row0 = st >> 3;           // first batch row of this thread (then +16, +32, +48)
-  int kb = lo % d.KB;
+  // One warp stages one unit; the four warps take units round-robin, so four units' loads are in flight per CTA
+  // and all of a lane's loads of a unit are issued before the first is used (an L2 round trip per unit otherwise).
+  const int sw = st >> 5, lane = st & 31;
+  const int chunk = lane & 7;         // 16-byte piece inside the 128-byte k-block row
+  const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
+  const int npl = p.Bpad / 4;         // rows (pieces) per lane: 4, 8, 12 or 16
+  constexpr int kMaxPieces = kMaxBatch / 4;
 #pragma unroll 1
-  for (int u = lo; u < hi; ++u, ++n) {
-    const int s = (int)(n % kStages);
-    const bool ok = n < (unsigned)kStages || mbar_wait(c, c.empty(s), ((n / kStages) - 1u) & 1u, ph, 5);
+  for (int u = lo + sw; u < hi; u += 4) {
+    const unsigned nu = n + (unsigned)(u - lo);
+    const int s = (int)(nu % kStages);
+    const int kb = u % d.KB;
+    const int k0 = kb * kBlockK + chunk * 8;
+    uint4 v[kMaxPieces];
+    // (the loads do not depend on the stage being free: issue them before waiting for it)
+#pragma unroll
+    for (int i = 0; i < kMaxPieces; ++i) {
+      const int r = row0 + 4 * i;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (i < npl && r < p.B) v[i] = ldcg_u4(src + (size_t)r * d.K + k0);
+    }
+    uint4 g4 = make_uint4(0, 0, 0, 0);
+    if (normed) g4 = __ldg(reinterpret_cast<const uint4*>(gain + k0));
+    const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / kStages) - 1u) & 1u, ph, 5);
     if (ok) {
       unsigned char* dst = c.smem + Smem::kOffStages + s * kStageBytes + kABytes;
-      const int k0 = kb * kBlockK + chunk * 8;
-      uint4 g4 = make_uint4(0, 0, 0, 0);
-      if (normed) g4 = __ldg(reinterpret_cast<const uint4*>(gain + k0));
-#pragma unroll 1
-      for (int r = row0; r < p.Bpad; r += 16) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < p.B) {
-          v = ldcg_u4(src + (size_t)r * d.K + k0);
-          if (normed) {
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
+#pragma unroll
+      for (int i = 0; i < kMaxPieces; ++i) {
+        const int r = row0 + 4 * i;
+        if (i < npl) {
+          if (normed && r < p.B) {
             const float f = rs[r];
-            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
-            const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
+            uint32_t* w = reinterpret_cast<uint32_t*>(&v[i]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float a = bf16_round(bf_lo(w[j]) * f) * bf_lo(gw[j]);
@@ -351,14 +372,14 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
               w[j] = pack_bf16x2(a, b);
             }
           }
+          *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[i];
         }
-        *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
       }
       fence_async_smem();
       mbar_arrive1(c.b_full(s));
     }
-    if (++kb == d.KB) kb = 0;
   }
+  n += (unsigned)(hi - lo);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -447,18 +468,26 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       // hidden[b, row] = bf16(hidden + bf16(projection)), zero projection for inactive rows
       // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295)
       const int row = t * kTileRows + e;
-      for (int b = 0; b < B; ++b) {
-        float sq = 0.f;
-        if (row < p.H) {
-          uint16_t* h = p.hidden + (size_t)b * p.H + row;
-          const float old = bf16_bits_to_f32(ldcg_u16(h));
-          const float add = act_s[b] ? bf16_round(exch[e * kExchStride + b]) : 0.f;
-          const unsigned short bits = f32_to_bf16_bits(old + add);
-          *h = bits;
-          const float nv = bf16_bits_to_f32(bits);
-          sq = nv * nv;
+#pragma unroll 1
+      for (int b0 = 0; b0 < B; b0 += 8) {
+        unsigned short oldv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)   // eight independent loads in flight
+          oldv[j] = (row < p.H && b0 + j < B) ? ldcg_u16(p.hidden + (size_t)(b0 + j) * p.H + row) : (unsigned short)0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int b = b0 + j;
+          if (b >= B) break;
+          float sq = 0.f;
+          if (row < p.H) {
+            const float add = act_s[b] ? bf16_round(exch[e * kExchStride + b]) : 0.f;
+            const unsigned short bits = f32_to_bf16_bits(bf16_bits_to_f32(oldv[j]) + add);
+            p.hidden[(size_t)b * p.H + row] = bits;
+            const float nv = bf16_bits_to_f32(bits);
+            sq = nv * nv;
+          }
+          exch[e * kExchStride + b] = sq;
         }
-        exch[e * kExchStride + b] = sq;
       }
       named_bar(kBarEpi, 128);
       if (e < B) {
@@ -524,6 +553,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const bool full = kb_lo == 0 && u_end == (t + 1) * d.KB;
     const unsigned buf = sg & 1u;
     const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
+    if (e == 0 && u == lo) trace_put(p, ph, 1);
     float* slot = p.ws + ((size_t)cta * 2 + (t == lo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad);
     if (ok) {
       tmem_fence_after_sync();
@@ -569,19 +599,24 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const bool run = c.ctl[kCFlagEpi] != 0u;
     if (run && !full) {
       __threadfence();
+      bool first = true;
 #pragma unroll 1
-      for (int ch4 = 0; ch4 < p.Bpad / 4; ++ch4) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int cc = c_first; cc <= c_last; ++cc) {
-          int clo, chi;
-          unit_range(U, G, cc, clo, chi);
-          if (clo == chi) continue;   // a CTA without units (fewer units than CTAs)
-          const float* sl = p.ws + ((size_t)cc * 2 + (t == clo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad);
-          const float4 x = __ldcg(reinterpret_cast<const float4*>(sl + ((size_t)ch4 * kTileRows + r) * 4));
-          acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      for (int cc = c_first; cc <= c_last; ++cc) {
+        int clo, chi;
+        unit_range(U, G, cc, clo, chi);
+        if (clo == chi) continue;   // a CTA without units (fewer units than CTAs)
+        const float* sl = p.ws + ((size_t)cc * 2 + (t == clo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad) + r * 4;
+        float* o = exch + r * kExchStride;
+#pragma unroll 4
+        for (int ch4 = 0; ch4 < p.Bpad / 4; ++ch4) {
+          const float4 x = __ldcg(reinterpret_cast<const float4*>(sl + (size_t)ch4 * kTileRows * 4));
+          if (first) {
+            o[ch4 * 4 + 0] = x.x; o[ch4 * 4 + 1] = x.y; o[ch4 * 4 + 2] = x.z; o[ch4 * 4 + 3] = x.w;
+          } else {
+            o[ch4 * 4 + 0] += x.x; o[ch4 * 4 + 1] += x.y; o[ch4 * 4 + 2] += x.z; o[ch4 * 4 + 3] += x.w;
+          }
         }
-        float* o = exch + r * kExchStride + ch4 * 4;
-        o[0] = acc.x; o[1] = acc.y; o[2] = acc.z; o[3] = acc.w;
+        first = false;
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
@@ -772,6 +807,7 @@ __device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
     bool needed;
     const bool ok = phase_dependency(c, ph, needed);
     c.ctl[kCFlagAttn] = ok ? 1u : 0u;
+    trace_put(p, ph, 0);
   }
   named_bar(kBarAttn, 256);
   if (c.ctl[kCFlagAttn] != 0u) {
@@ -788,7 +824,10 @@ __device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
   }
   __threadfence();
   named_bar(kBarAttn, 256);
-  if (aw == 0 && c.lane == 0 && !c.aborted()) red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+  if (aw == 0 && c.lane == 0 && !c.aborted()) {
+    red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+    trace_put(p, ph, 5);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -854,7 +893,7 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(c.a_full(s), 1);
-      mbar_init(c.b_full(s), 128);
+      mbar_init(c.b_full(s), 32);
       mbar_init(c.empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -907,10 +946,14 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
       if (kind == kAttn) {
         attention_phase(c, ph, c.warp - kEpiWarp0);
       } else if (epi) {
+        if (gi == 0) trace_put(p, ph, 2);
         epilogue_phase(c, ph, kind, tmem, gi, sg);
         __threadfence();
         named_bar(kBarEpi, 128);
-        if (gi == 0 && !c.aborted()) red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+        if (gi == 0 && !c.aborted()) {
+          red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+          trace_put(p, ph, 5);
+        }
       } else {
         stage_phase(c, ph, kind, gi, n);
       }

@@ -51,6 +51,7 @@ struct BParams {
   unsigned long long* argmax_key;   // [B]  (ordered logit bits << 32) | ~row
   unsigned* phase_done;          // [1 + phases]  CTAs that finished the prologue / each phase (zeroed per launch)
   unsigned* status;              // [8]
+  unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off
   // ---- shape ----
   int H, I, NH, NKV, HD, QKV_ROWS, QDIM, num_layers, vocab;
   int B, Bpad;                   // sequences, padded to a multiple of 16
