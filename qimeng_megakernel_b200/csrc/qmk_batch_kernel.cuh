@@ -11,10 +11,10 @@
 // units of a phase, 128 x 64 weights = 16 KiB each, are dealt to the CTAs as equal contiguous ranges,
 // so every SM streams the same number of bytes whatever the matrix shape.  A maximal run of units of
 // one row tile is a SEGMENT, accumulated in tensor memory.  A segment that covers the whole K is
-// finished by its CTA; otherwise the partial tile goes to a per-CTA scratch slot and the CTA that
-// arrives last at the tile's ticket adds the partials in CTA order (fixed order: results do not depend
-// on timing) and runs the epilogue.  The reference splits K in the down-projection only and adds the
-// partials with bf16 compare-and-swap in arrival order
+// finished by its CTA; otherwise the partial tile is added to the tile's fp32 accumulator at L2 (vector
+// reductions, nothing returned) and the CTA that arrives last at the tile's ticket reads the sum and runs
+// the epilogue (the order of the fp32 additions follows arrival).  The reference splits K in the
+// down-projection only and adds the partials with bf16 compare-and-swap in arrival order
 // (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/down_proj_gemv_residual.cu:39-52).
 //
 // Phases are separated by grid-wide arrival counters (one per phase, zeroed by the host before the
@@ -124,6 +124,11 @@ __device__ __forceinline__ void mma_bf16_add(uint32_t d_tmem, uint64_t da, uint6
       "}\n" ::"r"(d_tmem),
       "l"(da), "l"(db), "r"(idesc)
       : "memory");
+}
+// Four fp32 adds performed at L2, nothing returned.
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -303,6 +308,67 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
   return true;
 }
 
+// Stages the activation operand of units [lo, hi).  A warp takes D consecutive units at a time (the four warps
+// round-robin over groups of D) and a lane has NPL 16-byte pieces per unit: all D * NPL <= 16 loads of a group are
+// issued before the first is used, so that a warp pays one L2 round trip per group, not per unit or per piece.
+// 5 * D - 1 must stay below 2 * kStages: a warp that got two laps of the ring ahead of the tensor core would take an
+// old completion of a stage's mbarrier (same parity) for the one it waits for.
+template <int NPL, int D>
+__device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
+                                            const uint16_t* src, const uint16_t* gain, const float* rs) {
+  static_assert(4 * D + D - 1 < 2 * kStages, "a stager warp could run two ring laps ahead");
+  const BParams& p = *c.p;
+  const int sw = st >> 5, lane = st & 31;
+  const int chunk = lane & 7;         // 16-byte piece inside the 128-byte k-block row
+  const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
+#pragma unroll 1
+  for (int base = lo + sw * D; base < hi; base += 4 * D) {
+    uint4 v[D][NPL];
+    uint4 g4[D];
+#pragma unroll
+    for (int j = 0; j < D; ++j) {
+      const int u = base + j;
+      const int k0 = (u % d.KB) * kBlockK + chunk * 8;
+      g4[j] = make_uint4(0, 0, 0, 0);
+      if (gain != nullptr && u < hi) g4[j] = __ldg(reinterpret_cast<const uint4*>(gain + k0));
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int r = row0 + 4 * i;
+        v[j][i] = make_uint4(0, 0, 0, 0);
+        if (u < hi && r < p.B) v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < D; ++j) {
+      const int u = base + j;
+      if (u >= hi) break;
+      const unsigned nu = n + (unsigned)(u - lo);
+      const int s = (int)(nu % kStages);
+      const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / kStages) - 1u) & 1u, ph, 5);
+      if (!ok) continue;
+      unsigned char* dst = c.smem + Smem::kOffStages + s * kStageBytes + kABytes;
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4[j]);
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int r = row0 + 4 * i;
+        if (gain != nullptr && r < p.B) {
+          const float f = rs[r];
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v[j][i]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float a = bf16_round(bf_lo(w[q]) * f) * bf_lo(gw[q]);
+            const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
+            w[q] = pack_bf16x2(a, b);
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[j][i];
+      }
+      fence_async_smem();
+      mbar_arrive1(c.b_full(s));
+    }
+  }
+}
+
 __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int st, unsigned& n) {
   // st: thread index inside the stager group, 0..127
   const BParams& p = *c.p;
@@ -331,53 +397,11 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : p.hidden;
   const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
                        : kind == kUpGate ? p.mlp_norm + (size_t)layer * p.H : p.lm_norm;
-  // One warp stages one unit; the four warps take units round-robin, so four units' loads are in flight per CTA
-  // and all of a lane's loads of a unit are issued before the first is used (an L2 round trip per unit otherwise).
-  const int sw = st >> 5, lane = st & 31;
-  const int chunk = lane & 7;         // 16-byte piece inside the 128-byte k-block row
-  const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
-  const int npl = p.Bpad / 4;         // rows (pieces) per lane: 4, 8, 12 or 16
-  constexpr int kMaxPieces = kMaxBatch / 4;
-#pragma unroll 1
-  for (int u = lo + sw; u < hi; u += 4) {
-    const unsigned nu = n + (unsigned)(u - lo);
-    const int s = (int)(nu % kStages);
-    const int kb = u % d.KB;
-    const int k0 = kb * kBlockK + chunk * 8;
-    uint4 v[kMaxPieces];
-    // (the loads do not depend on the stage being free: issue them before waiting for it)
-#pragma unroll
-    for (int i = 0; i < kMaxPieces; ++i) {
-      const int r = row0 + 4 * i;
-      v[i] = make_uint4(0, 0, 0, 0);
-      if (i < npl && r < p.B) v[i] = ldcg_u4(src + (size_t)r * d.K + k0);
-    }
-    uint4 g4 = make_uint4(0, 0, 0, 0);
-    if (normed) g4 = __ldg(reinterpret_cast<const uint4*>(gain + k0));
-    const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / kStages) - 1u) & 1u, ph, 5);
-    if (ok) {
-      unsigned char* dst = c.smem + Smem::kOffStages + s * kStageBytes + kABytes;
-      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
-#pragma unroll
-      for (int i = 0; i < kMaxPieces; ++i) {
-        const int r = row0 + 4 * i;
-        if (i < npl) {
-          if (normed && r < p.B) {
-            const float f = rs[r];
-            uint32_t* w = reinterpret_cast<uint32_t*>(&v[i]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float a = bf16_round(bf_lo(w[j]) * f) * bf_lo(gw[j]);
-              const float b = bf16_round(bf_hi(w[j]) * f) * bf_hi(gw[j]);
-              w[j] = pack_bf16x2(a, b);
-            }
-          }
-          *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[i];
-        }
-      }
-      fence_async_smem();
-      mbar_arrive1(c.b_full(s));
-    }
+  switch (p.Bpad) {
+    case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
+    case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
+    case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
+    default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
   }
   n += (unsigned)(hi - lo);
 }
@@ -554,7 +578,10 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const unsigned buf = sg & 1u;
     const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
     if (e == 0 && u == lo) trace_put(p, ph, 1);
-    float* slot = p.ws + ((size_t)cta * 2 + (t == lo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad);
+    // accumulator of a tile that is split over several CTAs: the slot of the CTA that owns the tile's first unit
+    // (a CTA owns the first unit of at most one split tile, so the slot is the tile's alone)
+    const int c_first = unit_owner(U, G, t * d.KB);
+    float* slot = p.ws + (size_t)c_first * (size_t)(kTileRows * p.Bpad);
     if (ok) {
       tmem_fence_after_sync();
 #pragma unroll 1
@@ -568,18 +595,17 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
         } else {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(slot + ((size_t)(ch * 4 + j) * kTileRows + r) * 4) =
-                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            red_add_f32x4(slot + ((size_t)(ch * 4 + j) * kTileRows + r) * 4, __uint_as_float(v[4 * j]),
+                          __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
         }
       }
       tmem_fence_before_sync();
       mbar_arrive1(c.acc_empty(buf));
     }
     ++sg;
-    // One thread decides for the group whether this CTA finishes the tile: a full segment always does;
-    // a partial one publishes its tile, takes a ticket, and the last of the tile's segments to arrive
-    // adds the partials in CTA order.
-    const int c_first = unit_owner(U, G, t * d.KB), c_last = unit_owner(U, G, (t + 1) * d.KB - 1);
+    // One thread decides for the group whether this CTA finishes the tile: a full segment always does; a partial one
+    // has added its tile to the tile's accumulator at L2, takes a ticket, and the last of the tile's segments to
+    // arrive reads the sum (and leaves the accumulator zeroed for its next user, a phase later).
     if (!full) __threadfence();
     named_bar(kBarEpi, 128);
     if (e == 0) {
@@ -599,24 +625,14 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const bool run = c.ctl[kCFlagEpi] != 0u;
     if (run && !full) {
       __threadfence();
-      bool first = true;
-#pragma unroll 1
-      for (int cc = c_first; cc <= c_last; ++cc) {
-        int clo, chi;
-        unit_range(U, G, cc, clo, chi);
-        if (clo == chi) continue;   // a CTA without units (fewer units than CTAs)
-        const float* sl = p.ws + ((size_t)cc * 2 + (t == clo / d.KB ? 0 : 1)) * (size_t)(kTileRows * p.Bpad) + r * 4;
-        float* o = exch + r * kExchStride;
+      float* o = exch + r * kExchStride;
+      float* sl = slot + r * 4;
 #pragma unroll 4
-        for (int ch4 = 0; ch4 < p.Bpad / 4; ++ch4) {
-          const float4 x = __ldcg(reinterpret_cast<const float4*>(sl + (size_t)ch4 * kTileRows * 4));
-          if (first) {
-            o[ch4 * 4 + 0] = x.x; o[ch4 * 4 + 1] = x.y; o[ch4 * 4 + 2] = x.z; o[ch4 * 4 + 3] = x.w;
-          } else {
-            o[ch4 * 4 + 0] += x.x; o[ch4 * 4 + 1] += x.y; o[ch4 * 4 + 2] += x.z; o[ch4 * 4 + 3] += x.w;
-          }
-        }
-        first = false;
+      for (int ch4 = 0; ch4 < p.Bpad / 4; ++ch4) {
+        float4* src = reinterpret_cast<float4*>(sl + (size_t)ch4 * kTileRows * 4);
+        const float4 x = __ldcg(src);
+        *src = make_float4(0.f, 0.f, 0.f, 0.f);
+        o[ch4 * 4 + 0] = x.x; o[ch4 * 4 + 1] = x.y; o[ch4 * 4 + 2] = x.z; o[ch4 * 4 + 3] = x.w;
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
@@ -677,38 +693,48 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
       for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
     }
     const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
-#pragma unroll 2
-    for (int k0 = k_lo; k0 < k_hi; k0 += KPL) {
-      const int k = k0 + sub;
-      const bool valid = k < k_hi;
-      uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
-      if (valid) {
-        kv4 = ldcg_u4(p.k_cache + base + (size_t)k * p.kv_seq_stride);
-        vv4 = ldcg_u4(p.v_cache + base + (size_t)k * p.kv_seq_stride);
-      }
-      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv4);
-      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vv4);
-      float kf[8], vf[8];
+    constexpr int NLD = 8;               // K-row pieces (and V-row pieces) a lane keeps in flight
+    constexpr int KBK = NLD * KPL;       // keys per block: 32 (head_dim 64) or 16 (head_dim 128)
+#pragma unroll 1
+    for (int k0 = k_lo; k0 < k_hi; k0 += KBK) {
+      uint4 kk[NLD], vv[NLD];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[2 * j] = bf_lo(kw[j]); kf[2 * j + 1] = bf_hi(kw[j]);
-        vf[2 * j] = bf_lo(vw[j]); vf[2 * j + 1] = bf_hi(vw[j]);
+      for (int i = 0; i < NLD; ++i) {
+        const int k = k0 + i * KPL + sub;
+        kk[i] = k < k_hi ? ldcg_u4(p.k_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        float s = 0.f;
+      for (int i = 0; i < NLD; ++i) {
+        const int k = k0 + i * KPL + sub;
+        vv[i] = k < k_hi ? ldcg_u4(p.v_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s += q[g][j] * kf[j];
+      for (int i = 0; i < NLD; ++i) {
+        const bool valid = k0 + i * KPL + sub < k_hi;
+        const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kk[i]);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vv[i]);
+        float kf[8], vf[8];
 #pragma unroll
-        for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(kFullMask, s, o);
-        if (valid) {
-          const float mn = fmaxf(m[g], s);
-          const float corr = exp2f(m[g] - mn);     // 0 when m was -inf
-          const float pe = exp2f(s - mn);
-          l[g] = l[g] * corr + pe;
+        for (int j = 0; j < 4; ++j) {
+          kf[2 * j] = bf_lo(kw[j]); kf[2 * j + 1] = bf_hi(kw[j]);
+          vf[2 * j] = bf_lo(vw[j]); vf[2 * j + 1] = bf_hi(vw[j]);
+        }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pe * vf[j];
-          m[g] = mn;
+        for (int g = 0; g < GQ; ++g) {
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s += q[g][j] * kf[j];
+#pragma unroll
+          for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(kFullMask, s, o);
+          if (valid) {
+            const float mn = fmaxf(m[g], s);
+            const float corr = exp2f(m[g] - mn);     // 0 when m was -inf
+            const float pe = exp2f(s - mn);
+            l[g] = l[g] * corr + pe;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pe * vf[j];
+            m[g] = mn;
+          }
         }
       }
     }
@@ -771,24 +797,28 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
     last = __shfl_sync(kFullMask, last, 0);
     if (!last) continue;
     __threadfence();
-    // merge the nsplit records of this (sequence, kv head): every lane takes (head, 8 dims) pieces
+    // merge the nsplit records of this (sequence, kv head): every lane takes (head, 8 dims) pieces and folds the
+    // records in split order (loads of four records in flight)
     const float* recs = p.attn_part + (size_t)(sq * nch) * REC;
     for (int piece = lane; piece < GQ * LPR; piece += 32) {
       const int g = piece / LPR, dd = piece % LPR;
-      float M = -INFINITY;
-      for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ldcg_f32(recs + (size_t)s * REC + g * (HD + 2) + HD));
-      float L = 0.f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float M = -INFINITY, L = 0.f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
       for (int s = 0; s < nsplit; ++s) {
         const float* rr = recs + (size_t)s * REC + g * (HD + 2);
         const float2 ml = ldcg_f2(rr + HD);
-        const float w = exp2f(ml.x - M);
-        L += ml.y * w;
+        float2 a[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = ldcg_f2(rr + dd * 8 + 2 * j);
+        const float mn = fmaxf(M, ml.x);
+        const float c0 = exp2f(M - mn), c1 = exp2f(ml.x - mn);
+        L = L * c0 + ml.y * c1;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 a = ldcg_f2(rr + dd * 8 + 2 * j);
-          o[2 * j] += a.x * w;
-          o[2 * j + 1] += a.y * w;
+          o[2 * j] = o[2 * j] * c0 + a[j].x * c1;
+          o[2 * j + 1] = o[2 * j + 1] * c0 + a[j].y * c1;
         }
+        M = mn;
       }
       const float inv = 1.0f / L;
       uint4 o4;

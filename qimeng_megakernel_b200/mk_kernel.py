@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from pathlib import Path
 from typing import Any
 
@@ -67,6 +68,7 @@ class MegaKernel:
         self._state_key = None
         self._device = None
         self._variant = 0
+        self._timeout_cycles = int(os.environ.get("QMK_TIMEOUT_CYCLES", "0"))   # device wait budget override (0 = default)
 
     # -- handle management -------------------------------------------------------------------
     def _validate(self, g: Globals) -> tuple:
@@ -150,6 +152,8 @@ class MegaKernel:
             self._device = dev
             if self._variant:
                 _lib.check(self._lib.qmk_set_kernel_variant(self._handle, self._variant), self._handle)
+            if self._timeout_cycles:
+                _lib.check(self._lib.qmk_set_timeout_cycles(self._handle, self._timeout_cycles))
         if skey != self._state_key:
             st = _lib.StatePtrs(**{f: _ptr(getattr(g, f, None)) for f in _STATE_FIELDS})
             st.out_tokens_len = int(g.out_tokens.numel()) // B if getattr(g, "out_tokens", None) is not None else 0
@@ -210,7 +214,9 @@ class MegaKernel:
             raise _lib.QmkError(d["rc"], f"status={d}")
 
     def set_timeout_cycles(self, cycles: int) -> None:
-        _lib.check(self._lib.qmk_set_timeout_cycles(self._handle, int(cycles)))
+        self._timeout_cycles = int(cycles)
+        if self._handle is not None:
+            _lib.check(self._lib.qmk_set_timeout_cycles(self._handle, int(cycles)))
 
     def set_kernel_variant(self, variant: int) -> None:
         """0: the batch-1 kernel when the shape and batch allow it; 1: always the batched kernel."""

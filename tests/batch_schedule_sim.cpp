@@ -1,7 +1,8 @@
 // CPU replay of the batched kernel's schedule (qimeng_megakernel_b200/csrc/qmk_batch_schedule.h): for several
 // model shapes and grid sizes, walks every CTA's unit range of every phase kind exactly as the device roles do
 // and checks that (1) every (row tile, k-block) unit is owned by exactly one CTA, and unit_owner agrees;
-// (2) a CTA has at most two partial segments per phase, so its two scratch slots are never used twice;
+// (2) a CTA has at most two partial segments per phase, and no two split tiles of a phase share the CTA that owns
+// their first unit, which is what the tile's accumulator slot is keyed on;
 // (3) the partial segments of a tile are exactly the CTAs unit_owner(first unit) .. unit_owner(last unit), which
 // is what the tile's ticket counts and what the last arriver sums; (4) the split-KV plan keeps its bounds.
 #include <cstdio>
@@ -49,8 +50,10 @@ static int check_phase(const BParams& p, int kind, int G) {
   }
   for (int x = 0; x < U; ++x)
     if (owner[x] == -1) return fail("unit not owned", x, kind, G);
+  std::set<int> acc_slots;
   for (auto& kv : partial_of_tile) {
     const int t = kv.first;
+    if (!acc_slots.insert(unit_owner(U, G, t * d.KB)).second) return fail("accumulator slot shared by two split tiles", t, kind, G);
     const int c_first = unit_owner(U, G, t * d.KB), c_last = unit_owner(U, G, (t + 1) * d.KB - 1);
     if ((int)kv.second.size() != tile_segments(U, G, d.KB, t))
       return fail("ticket count", t, (int)kv.second.size(), tile_segments(U, G, d.KB, t));
