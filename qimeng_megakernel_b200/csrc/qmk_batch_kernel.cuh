@@ -428,61 +428,74 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
   const int B = p.B;
   switch (kind) {
     case kQkv: {
-      const int row = t * kTileRows + e;
+      // A thread owns (sequence b, eight consecutive rows): four RoPE pairs of one head of Q, K or V.  Everything it
+      // reads or writes in global memory is a 16-byte piece; lanes 0-15 / 16-31 of a warp hold the sixteen row
+      // groups of one sequence, so the per-head sums of squares of the Q/K norm are warp shuffles.
+      const int rg = e & 15;
+      const int row = t * kTileRows + rg * 8;
       const int kdim = p.NKV * p.HD;
+      const bool in_range = row < p.QKV_ROWS;
       const bool is_v = row >= p.QDIM + kdim;
       const bool is_k = !is_v && row >= p.QDIM;
-      const int d = row % p.HD;
-      float* hs = reinterpret_cast<float*>(c.smem + Smem::kOffHs);
-      const int heads_in_tile = kTileRows / p.HD;          // 1 or 2
-      if (p.q_norm != nullptr) {
-        // per-head sums of squares of the bf16-rounded projections (_per_head_rms_norm, Qwen3 operations.py:52-63)
-        if (e < p.Bpad) {
-          for (int hh = 0; hh < heads_in_tile; ++hh) {
-            float s = 0.f;
-            for (int r = 0; r < p.HD; ++r) {
-              const float x = bf16_round(exch[(hh * p.HD + r) * kExchStride + e]);
-              s += x * x;
-            }
-            hs[hh * kMaxBatch + e] = s;
-          }
-        }
-        named_bar(kBarEpi, 128);
+      const int d0 = row % p.HD;
+      const uint16_t* nw = (is_v || !in_range) ? nullptr : (is_k ? p.k_norm : p.q_norm);
+      float wn[8];
+      if (nw != nullptr) {
+        const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(nw + (size_t)layer * p.HD + d0));
+        const uint32_t* ww = reinterpret_cast<const uint32_t*>(&w4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { wn[2 * j] = bf_lo(ww[j]); wn[2 * j + 1] = bf_hi(ww[j]); }
       }
-      if (row < p.QKV_ROWS) {
-        const uint16_t* nw = is_v ? nullptr : (is_k ? p.k_norm : p.q_norm);
-        float w_self = 1.f, w_part = 1.f;
-        if (nw != nullptr) {
-          w_self = bf16_bits_to_f32(__ldg(nw + (size_t)layer * p.HD + d));
-          w_part = bf16_bits_to_f32(__ldg(nw + (size_t)layer * p.HD + (d ^ 1)));
+      const int nit = (B + 7) / 8;
+#pragma unroll 1
+      for (int i = 0; i < nit; ++i) {
+        const int b = (e >> 4) + 8 * i;
+        const bool live = in_range && b < B && act_s[b] != 0;
+        const int bb = b < B ? b : 0;
+        const int pos = pos_s[bb];
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = bf16_round(exch[(rg * 8 + j) * kExchStride + bb]);
+        if (p.q_norm != nullptr) {
+          // _per_head_rms_norm (Qwen3 operations.py:52-63) on the bf16-rounded projection, fp32 until the end
+          float ssq = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ssq += x[j] * x[j];
+          const int lanes = p.HD / 8;   // row groups per head: 8 or 16
+          for (int o = 1; o < lanes; o <<= 1) ssq += __shfl_xor_sync(kFullMask, ssq, o);
+          if (nw != nullptr) {
+            const float f = rsqrtf(ssq / (float)p.HD + p.qk_eps);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = bf16_round(wn[j] * (x[j] * f));
+          }
         }
-        const int hh = e / p.HD;
-        for (int b = 0; b < B; ++b) {
-          if (!act_s[b]) continue;
-          float x = bf16_round(exch[e * kExchStride + b]);
-          float y = bf16_round(exch[(e ^ 1) * kExchStride + b]);
-          const int pos = pos_s[b];
-          unsigned short bits;
-          if (is_v) {
-            bits = f32_to_bf16_bits(x);
-          } else {
-            if (nw != nullptr) {
-              const float f = rsqrtf(hs[hh * kMaxBatch + b] / (float)p.HD + p.qk_eps);
-              x = bf16_round(w_self * (x * f));
-              y = bf16_round(w_part * (y * f));
-            }
-            const float cs = __ldg(p.rope_cos + (size_t)pos * p.HD + d);
-            const float sn = __ldg(p.rope_sin + (size_t)pos * p.HD + d);
-            const float rot = (d & 1) ? y : -y;
-            bits = f32_to_bf16_bits(x * cs + rot * sn);
+        if (!live) continue;
+        uint4 o4;
+        if (is_v) {
+          o4.x = pack_bf16x2(x[0], x[1]); o4.y = pack_bf16x2(x[2], x[3]);
+          o4.z = pack_bf16x2(x[4], x[5]); o4.w = pack_bf16x2(x[6], x[7]);
+        } else {
+          const float4* cp = reinterpret_cast<const float4*>(p.rope_cos + (size_t)pos * p.HD + d0);
+          const float4* sp = reinterpret_cast<const float4*>(p.rope_sin + (size_t)pos * p.HD + d0);
+          const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+          const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          float y[8];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {   // pair (2m, 2m+1): rotate_half gives (-odd, even)
+            y[j] = x[j] * cs[j] - x[j + 1] * sn[j];
+            y[j + 1] = x[j + 1] * cs[j + 1] + x[j] * sn[j + 1];
           }
-          if (!is_k && !is_v) {
-            p.q_post_rope[(size_t)b * p.QDIM + row] = bits;
-          } else {
-            const int col = is_k ? row - p.QDIM : row - p.QDIM - kdim;
-            uint16_t* cache = is_k ? p.k_cache : p.v_cache;
-            cache[(size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)pos * p.kv_seq_stride + col] = bits;
-          }
+          o4.x = pack_bf16x2(y[0], y[1]); o4.y = pack_bf16x2(y[2], y[3]);
+          o4.z = pack_bf16x2(y[4], y[5]); o4.w = pack_bf16x2(y[6], y[7]);
+        }
+        if (!is_k && !is_v) {
+          *reinterpret_cast<uint4*>(p.q_post_rope + (size_t)b * p.QDIM + row) = o4;
+        } else {
+          const int col = is_k ? row - p.QDIM : row - p.QDIM - kdim;
+          uint16_t* cache = is_k ? p.k_cache : p.v_cache;
+          *reinterpret_cast<uint4*>(cache + (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride +
+                                    (size_t)pos * p.kv_seq_stride + col) = o4;
         }
       }
       break;
@@ -490,34 +503,46 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
     case kOproj:
     case kDown: {
       // hidden[b, row] = bf16(hidden + bf16(projection)), zero projection for inactive rows
-      // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295)
-      const int row = t * kTileRows + e;
-#pragma unroll 1
-      for (int b0 = 0; b0 < B; b0 += 8) {
-        unsigned short oldv[8];
+      // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295).
+      // Same (sequence, eight rows) ownership: one 16-byte load and store of the residual stream per item, all loads
+      // issued first; the sums of squares for the next RMSNorm are reduced over the sixteen row groups by shuffles.
+      const int rg = e & 15;
+      const int row = t * kTileRows + rg * 8;
+      const bool in_range = row < p.H;
+      const int nit = (B + 7) / 8;
+      uint4 oldv[kMaxBatch / 8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)   // eight independent loads in flight
-          oldv[j] = (row < p.H && b0 + j < B) ? ldcg_u16(p.hidden + (size_t)(b0 + j) * p.H + row) : (unsigned short)0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int b = b0 + j;
-          if (b >= B) break;
-          float sq = 0.f;
-          if (row < p.H) {
-            const float add = act_s[b] ? bf16_round(exch[e * kExchStride + b]) : 0.f;
-            const unsigned short bits = f32_to_bf16_bits(bf16_bits_to_f32(oldv[j]) + add);
-            p.hidden[(size_t)b * p.H + row] = bits;
-            const float nv = bf16_bits_to_f32(bits);
-            sq = nv * nv;
-          }
-          exch[e * kExchStride + b] = sq;
-        }
+      for (int i = 0; i < kMaxBatch / 8; ++i) {
+        const int b = (e >> 4) + 8 * i;
+        oldv[i] = (i < nit && in_range && b < B) ? ldcg_u4(p.hidden + (size_t)b * p.H + row) : make_uint4(0, 0, 0, 0);
       }
-      named_bar(kBarEpi, 128);
-      if (e < B) {
-        float s = 0.f;
-        for (int r = 0; r < kTileRows; ++r) s += exch[r * kExchStride + e];
-        p.ss[t * kMaxBatch + e] = s;
+#pragma unroll
+      for (int i = 0; i < kMaxBatch / 8; ++i) {
+        if (i < nit) {
+          const int b = (e >> 4) + 8 * i;
+          const int bb = b < B ? b : 0;
+          const bool act = b < B && act_s[bb] != 0;
+          const uint32_t* ow = reinterpret_cast<const uint32_t*>(&oldv[i]);
+          float nv[8], sq = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float old = (j & 1) ? bf_hi(ow[j >> 1]) : bf_lo(ow[j >> 1]);
+            const float add = act ? bf16_round(exch[(rg * 8 + j) * kExchStride + bb]) : 0.f;
+            nv[j] = bf16_round(old + add);
+            sq += nv[j] * nv[j];
+          }
+          if (in_range && b < B) {
+            uint4 o4;
+            o4.x = pack_bf16x2(nv[0], nv[1]); o4.y = pack_bf16x2(nv[2], nv[3]);
+            o4.z = pack_bf16x2(nv[4], nv[5]); o4.w = pack_bf16x2(nv[6], nv[7]);
+            *reinterpret_cast<uint4*>(p.hidden + (size_t)b * p.H + row) = o4;
+          } else {
+            sq = 0.f;
+          }
+#pragma unroll
+          for (int o = 1; o < 16; o <<= 1) sq += __shfl_xor_sync(kFullMask, sq, o);
+          if (rg == 0 && b < B) p.ss[t * kMaxBatch + b] = sq;
+        }
       }
       break;
     }
@@ -636,9 +661,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
-    if (run) epilogue_tile(c, ph, kind, t, e);
-    else if ((kind == kQkv && p.q_norm != nullptr) || kind == kOproj || kind == kDown)
-      named_bar(kBarEpi, 128);         // keep the barrier count of epilogue_tile
+    if (run) epilogue_tile(c, ph, kind, t, e);   // (contains no barrier)
     named_bar(kBarEpi, 128);           // the exchange tile is free again
     u = u_end;
   }

@@ -76,7 +76,7 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
         loop_start.record()
 
     if host_loop:
-        # FusedGenerator.generate_greedy_fast (decode.py:1373-1395), B = 1
+        # FusedGenerator.generate_greedy_fast (decode.py:1373-1395): [H] state for one sequence, [B, H] for several
         saved = (globs.token_in, globs.out_tokens)
         globs.token_in = None
         globs.out_tokens = None
@@ -84,20 +84,19 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
         for i in range(ntok):
             pos = prompt_len + i
             emb = embed[output_tokens[:, pos]].to(dtype)
-            globs.hidden_states.copy_(emb.reshape(-1))
+            globs.hidden_states.copy_(emb.reshape(globs.hidden_states.shape))
             globs.position_id = pos
             if events:
                 events[i][0].record()
             schedule.call_mk(globs, mk)
             if events:
                 events[i][1].record()
-            output_tokens[:, pos + 1] = globs.logits.argmax()
+            output_tokens[:, pos + 1] = globs.logits.view(batch_size, -1).argmax(dim=-1)
         globs.token_in, globs.out_tokens = saved
     else:
-        row = output_tokens[0]
         saved = (globs.token_in, globs.out_tokens, globs.next_token)
-        globs.out_tokens = row
-        globs.token_in = row[prompt_len:prompt_len + 1].clone()
+        globs.out_tokens = output_tokens[0] if batch_size == 1 else output_tokens
+        globs.token_in = output_tokens[:, prompt_len].clone()
         globs.next_token = globs.token_in
         for i in range(ntok):
             globs.position_id = prompt_len + i

@@ -30,14 +30,27 @@ class PrefillOutput:
 @torch.inference_mode()
 def run_prefill_synthetic(config: dict, weights: dict, prompt_ids: torch.Tensor, max_new_tokens: int,
                           device: str | torch.device = "cuda:0", mk: Any = None) -> PrefillOutput:
-    """prompt_ids: [1, prompt_len] (or [prompt_len]) int64 token ids."""
-    ids = prompt_ids.view(1, -1).to(torch.int64)
-    if ids.shape[0] != 1:
-        raise NotImplementedError("the B200 route runs one sequence per GPU")
+    """prompt_ids: [B, prompt_len] (or [prompt_len]) int64 token ids; B > 1 gives [B, ...] state and runs the
+    batched kernel (all prompts of one length, like the reference's fused prefill for a padded batch)."""
+    ids = (prompt_ids.view(1, -1) if prompt_ids.dim() == 1 else prompt_ids).to(torch.int64)
     prompt_len = int(ids.shape[1])
     if prompt_len < 1:
         raise ValueError("empty prompt")
     dev = torch.device(device)
+    if ids.shape[0] > 1:
+        B = int(ids.shape[0])
+        g = synthetic.make_globals(config, weights, kv_seq_len=prompt_len + max(0, max_new_tokens), device=dev, batch=B)
+        mk = mk if mk is not None else mk_kernel.get_mk()
+        ids_dev = ids.to(dev)
+        g.token_in = torch.zeros(B, dtype=torch.int64, device=dev)
+        for pos in range(prompt_len):      # one position of every prompt per launch: fills the KV cache
+            g.token_in.copy_(ids_dev[:, pos])
+            g.position_id = pos
+            mk(g)
+        mk.check_status()
+        first = g.next_token.clone().view(B, 1)
+        g.token_in = None
+        return PrefillOutput(input_ids=ids_dev, first_gen_token=first, logits=g.logits.clone(), globs=g, mk=mk)
     g = synthetic.make_globals(config, weights, kv_seq_len=prompt_len + max(0, max_new_tokens), device=dev)
     mk = mk if mk is not None else mk_kernel.get_mk()
     host = ids[0].cpu().contiguous()

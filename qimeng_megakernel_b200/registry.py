@@ -13,14 +13,16 @@ import importlib
 from dataclasses import dataclass
 from typing import Any
 
-from .model_config import LLAMA_3_2_1B
+from .model_config import LLAMA_3_2_1B, QWEN3_0_6B
 
 HARDWARE_CHOICES = ("auto", "B200")
-# architectures with a compiled kernel shape: model key -> config
-MODELS = {"llama-3.2-1b": LLAMA_3_2_1B}
+# architectures with a kernel (the batch-1 kernel's compiled shape, or the batched kernel's runtime shapes): model key -> config
+MODELS = {"llama-3.2-1b": LLAMA_3_2_1B, "qwen3-0.6b": QWEN3_0_6B}
 _ALIASES = {"meta-llama/llama-3.2-1b": "llama-3.2-1b", "meta-llama/llama-3.2-1b-instruct": "llama-3.2-1b",
-            "llama3_2__1b": "llama-3.2-1b", "synthetic-llama-3.2-1b": "llama-3.2-1b"}
-MAX_BATCH = 1
+            "llama3_2__1b": "llama-3.2-1b", "synthetic-llama-3.2-1b": "llama-3.2-1b",
+            "qwen/qwen3-0.6b": "qwen3-0.6b", "qwen3__0_6b": "qwen3-0.6b", "synthetic-qwen3-0.6b": "qwen3-0.6b"}
+# sequences per GPU in one launch (the reference stops at 16, registry.py:212; more sequences shard over GPUs)
+MAX_BATCH = 64
 
 
 @dataclass(frozen=True)
@@ -67,7 +69,7 @@ def decode_schedule_package_name(model_name: str, hardware: str, batch_size: int
     resolve_model_key(model_name)
     resolve_hardware(hardware, device_name="B200" if hardware == "auto" else None)
     if batch_size > MAX_BATCH:
-        raise NotImplementedError(f"B200 decode supports batch_size<={MAX_BATCH} (sequences are sharded over GPUs)")
+        raise NotImplementedError(f"B200 decode supports batch_size<={MAX_BATCH} per GPU (more sequences shard over GPUs)")
     return "qimeng_megakernel_b200"
 
 

@@ -386,3 +386,49 @@ def test_argument_validation():
     with pytest.raises(ValueError):
         g = synthetic.make_globals(ODD, w, kv_seq_len=64, device="cuda", batch=65)
         mk_kernel.get_mk()(g)
+
+
+def test_decode_api_batched(small_config, small_weights):
+    """`decode(route='mk', hardware='B200')` with four prompts: the reference's host loop ([B, H] state, PyTorch
+    embedding and arg-max around call_mk) and the device-resident loop produce the same tokens, each row equal to
+    what the same prompt gives when decoded alone (rows are independent), with per-row EOS handling."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.decode import decode
+    from qimeng_megakernel_b200.prefill import run_prefill_synthetic
+    B, P, n_new = 4, 16, 12
+    prompts = synthetic.make_prompts(small_config["vocab_size"], B, P, seed=41)
+    outs = []
+    for host_loop in (True, False):
+        pre = run_prefill_synthetic(small_config, small_weights, prompts, n_new, device="cuda:0")
+        assert pre.first_gen_token.shape == (B, 1) and pre.logits.shape == (B, small_config["vocab_size"])
+        out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, decode_route="mk", hardware="B200",
+                     decode_time=True, ignore_eos=True, host_loop=host_loop)
+        assert out["generated_ids"].shape == (B, P + n_new)
+        assert out["per_row_new_tokens"].tolist() == [n_new] * B
+        assert out["timing"]["decode_window_new_tokens"] == B * (n_new - 1) and out["timing"]["kernel_tok_s"] > 0
+        outs.append(out["generated_ids"].cpu())
+        pre.mk.close()
+    # Split-K partial tiles are added at L2 in arrival order, so two runs may differ in the last bit of an fp32 sum;
+    # over a 4096-word vocabulary with bf16 logits that can flip a tie, after which a greedy row goes its own way.
+    # Hence: prompts and first tokens identical, and most rows identical to the end.
+    assert torch.equal(outs[0][:, :P + 1], outs[1][:, :P + 1])
+    assert sum(int(torch.equal(outs[0][b], outs[1][b])) for b in range(B)) >= B - 1
+    # each row alone through the batched kernel (batch 1): the same tokens as in the batch (rows are independent)
+    same = 0
+    for b in range(B):
+        pre = run_prefill_synthetic(small_config, small_weights, prompts[b], n_new, device="cuda:0")
+        pre.mk.set_kernel_variant(1)
+        out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, ignore_eos=True)
+        same += int(out["generated_ids"][0].cpu().tolist() == outs[1][b].tolist())
+        pre.mk.close()
+    assert same >= B - 1
+    # per-row EOS: every row stops at its own first EOS and is padded after it
+    eos = int(outs[1][2, P + 4])
+    pre = run_prefill_synthetic(small_config, small_weights, prompts, n_new, device="cuda:0")
+    out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, eos_token_ids=[eos], pad_token_id=0)
+    per_row = out["per_row_new_tokens"].tolist()
+    for b in range(B):
+        new = outs[1][b, P:].tolist()
+        assert per_row[b] == (new.index(eos) + 1 if eos in new else n_new)
+    pre.mk.close()

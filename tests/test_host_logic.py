@@ -36,10 +36,12 @@ def test_registry():
     sched = R.import_decode_schedule("llama-3.2-1b", "B200", 1)
     assert sched.get_mk is not None and sched.call_mk is not None and sched.scheduler is None
     assert sched.config.hidden_size == 2048
+    assert R.decode_schedule_package_name("llama-3.2-1b", "B200", batch_size=64) == "qimeng_megakernel_b200"
+    assert R.decode_schedule_package_name("Qwen/Qwen3-0.6B", "B200", batch_size=16) == "qimeng_megakernel_b200"
     with pytest.raises(NotImplementedError):
-        R.decode_schedule_package_name("llama-3.2-1b", "B200", batch_size=2)
+        R.decode_schedule_package_name("llama-3.2-1b", "B200", batch_size=65)
     with pytest.raises(NotImplementedError):
-        R.decode_schedule_package_name("qwen3-0.6b", "B200")
+        R.decode_schedule_package_name("qwen2.5-3b", "B200")
     with pytest.raises(ValueError):
         R.resolve_hardware("H100")
     assert R.resolve_hardware("auto", device_name="NVIDIA B200") == "B200"
