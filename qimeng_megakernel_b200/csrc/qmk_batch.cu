@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -108,7 +109,7 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
       rc = QMK_ERR_CUDA;
       break;
     }
-    e = cudaFuncSetAttribute(qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal);
+    e = cudaFuncSetAttribute(qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) { rc = fail(err, errlen, "cudaFuncSetAttribute", e); break; }
 
     int max_tiles = (V + kTileRows - 1) / kTileRows;
@@ -168,7 +169,7 @@ int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream) {
 void qmkb_geometry(const qmk_batch_ctx* c, int* ctas, int* threads, int* smem_bytes) {
   if (ctas && c) *ctas = c->n_sm;
   if (threads) *threads = kBatchThreads;
-  if (smem_bytes) *smem_bytes = Smem::kTotal;
+  if (smem_bytes) *smem_bytes = kSmemBudget;   // upper bound; a launch asks for smem_plan(Bpad).total
 }
 
 int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_args* a, cudaStream_t stream, char* err,
@@ -220,6 +221,16 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.vocab = d.vocab_size;
   p.B = st->batch;
   p.Bpad = (st->batch + 15) / 16 * 16;
+  SmemPlan plan = smem_plan(p.Bpad);
+  {
+    // measurement knob: fewer ring slots than fit (QMK_BATCH_MAX_STAGES, at least kMinStages)
+    static const int cap = [] { const char* e = getenv("QMK_BATCH_MAX_STAGES"); return e ? atoi(e) : 0; }();
+    if (cap >= kMinStages && cap < plan.stages) plan.stages = cap;
+  }
+  p.stages = plan.stages;
+  p.stage_bytes = plan.stage_bytes;
+  p.off_stages = plan.off_stages;
+  p.exch_stride = plan.exch_stride;
   p.pos = a->pos;
   p.phase_begin = a->phase_begin;
   p.phase_end = a->phase_end;
@@ -243,7 +254,7 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)c->n_sm);
   cfg.blockDim = dim3(kBatchThreads);
-  cfg.dynamicSmemBytes = Smem::kTotal;
+  cfg.dynamicSmemBytes = (size_t)plan.total;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another

@@ -40,30 +40,41 @@ namespace qmkb {
 
 using namespace qmk;
 
-constexpr int kStages = 7;
+constexpr int kMaxStages = 12;                          // ring slots; the launch uses as many as fit (smem_plan)
+constexpr int kMinStages = 7;
 constexpr int kABytes = kTileRows * kBlockK * 2;        // 16 KiB of weights per unit
-constexpr int kBBytes = kMaxBatch * kBlockK * 2;        // 8 KiB of activations per unit
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kExchStride = kMaxBatch + 1;              // floats per row of the exchange tile
 constexpr int kNumWarps = 10;
 constexpr int kBatchThreads = kNumWarps * 32;
 constexpr int kEpiWarp0 = 2, kStgWarp0 = 6;
 constexpr int kBarEpi = 1, kBarStg = 2, kBarAttn = 3;   // named barriers (0 is __syncthreads)
+constexpr int kSmemBudget = 227 * 1024;                 // dynamic shared memory a CTA may ask for on sm_100
 
+// Shared memory: a fixed header, then the fp32 exchange tile [128][Bpad + 1], then the ring on a 1024-byte boundary
+// (128-byte-swizzle atoms).  A ring slot holds 16 KiB of weights and Bpad * 128 bytes of activations, so small
+// batches get more slots: more weight bytes in flight per SM.
 struct Smem {
-  static constexpr int kOffStages = 0;                                        // 1024-byte aligned
-  static constexpr int kOffExch = kOffStages + kStages * kStageBytes;         // fp32 [128][65]
-  static constexpr int kOffBars = kOffExch + kTileRows * kExchStride * 4;     // mbarriers
-  //   a_full[kStages] b_full[kStages] empty[kStages] acc_full[2] acc_empty[2]
-  static constexpr int kNumBars = 3 * kStages + 4;
+  static constexpr int kOffBars = 0;                                          // mbarriers
+  //   a_full[kMaxStages] b_full[kMaxStages] empty[kMaxStages] acc_full[2] acc_empty[2]
+  static constexpr int kNumBars = 3 * kMaxStages + 4;
   static constexpr int kOffRs = kOffBars + kNumBars * 8;                      // float [64]  rsqrt factors
-  static constexpr int kOffHs = kOffRs + kMaxBatch * 4;                       // float [2][64] per-head sums
+  static constexpr int kOffHs = kOffRs + kMaxBatch * 4;                       // float [2][64] scratch of the prologue
   static constexpr int kOffPos = kOffHs + 2 * kMaxBatch * 4;                  // int [64]
   static constexpr int kOffAct = kOffPos + kMaxBatch * 4;                     // int [64]
   static constexpr int kOffCtl = kOffAct + kMaxBatch * 4;                     // control words
-  static constexpr int kUsed = kOffCtl + 64;
-  static constexpr int kTotal = kUsed + 1024;   // slack to place the stages on a 1024-byte boundary (swizzle atoms)
+  static constexpr int kOffExch = 2048;
+  static_assert(kOffCtl + 64 <= kOffExch, "header overflows");
 };
+struct SmemPlan { int off_stages, stage_bytes, stages, exch_stride, total; };
+__host__ __device__ inline SmemPlan smem_plan(int Bpad) {
+  SmemPlan s;
+  s.exch_stride = Bpad + 1;
+  s.off_stages = (Smem::kOffExch + kTileRows * s.exch_stride * 4 + 1023) / 1024 * 1024;
+  s.stage_bytes = kABytes + Bpad * kBlockK * 2;
+  s.stages = (kSmemBudget - 1024 - s.off_stages) / s.stage_bytes;     // 1024: slack to align the base
+  if (s.stages > kMaxStages) s.stages = kMaxStages;
+  s.total = s.off_stages + s.stages * s.stage_bytes + 1024;
+  return s;
+}
 // control words: [0] abort  [1] tensor-memory base  [2] Tmax  [3] flag of the epilogue group  [4] flag of the stagers
 // [5] flag of the attention group
 constexpr int kCAbort = 0, kCTmem = 1, kCTmax = 2, kCFlagEpi = 3, kCFlagStg = 4, kCFlagAttn = 5;
@@ -149,9 +160,14 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
 
 // Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
 // satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
-// the phase, 5 the CTA arrives at the phase's counter.
+// the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
+// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival.
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
   if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (5 * p.num_layers + 1) + ph) * 8 + slot] = globaltimer_ns();
+}
+
+__device__ __forceinline__ void trace_val(const BParams& p, int ph, int slot, unsigned long long v) {
+  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (5 * p.num_layers + 1) + ph) * 8 + slot] = v;
 }
 
 struct Ctx {
@@ -161,10 +177,10 @@ struct Ctx {
   uint32_t bars;     // shared address of the mbarriers
   int warp, lane;
   __device__ __forceinline__ uint32_t a_full(int s) const { return bars + s * 8; }
-  __device__ __forceinline__ uint32_t b_full(int s) const { return bars + (kStages + s) * 8; }
-  __device__ __forceinline__ uint32_t empty(int s) const { return bars + (2 * kStages + s) * 8; }
-  __device__ __forceinline__ uint32_t acc_full(int b) const { return bars + (3 * kStages + b) * 8; }
-  __device__ __forceinline__ uint32_t acc_empty(int b) const { return bars + (3 * kStages + 2 + b) * 8; }
+  __device__ __forceinline__ uint32_t b_full(int s) const { return bars + (kMaxStages + s) * 8; }
+  __device__ __forceinline__ uint32_t empty(int s) const { return bars + (2 * kMaxStages + s) * 8; }
+  __device__ __forceinline__ uint32_t acc_full(int b) const { return bars + (3 * kMaxStages + b) * 8; }
+  __device__ __forceinline__ uint32_t acc_empty(int b) const { return bars + (3 * kMaxStages + 2 + b) * 8; }
   __device__ __forceinline__ bool aborted() const { return ctl[kCAbort] != 0u; }
 };
 
@@ -212,7 +228,7 @@ static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* c
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, unsigned& n_issued) {
   const BParams& p = *c.p;
-  const uint32_t stages = smem_u32(c.smem + Smem::kOffStages);
+  const uint32_t stages = smem_u32(c.smem + p.off_stages);
   const uint64_t policy = l2_policy_evict_first();
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
   unsigned n = 0;
@@ -229,12 +245,12 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
     int t = lo / d.KB, kb = lo - t * d.KB;
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
-      const int s = (int)(n % kStages);
-      if (n >= (unsigned)kStages && !mbar_wait(c, c.empty(s), ((n / kStages) - 1u) & 1u, ph, 1)) {
+      const int s = (int)(n % (unsigned)p.stages);
+      if (n >= (unsigned)p.stages && !mbar_wait(c, c.empty(s), ((n / (unsigned)p.stages) - 1u) & 1u, ph, 1)) {
         n_issued = n;
         return;
       }
-      const uint32_t dst = stages + s * kStageBytes;
+      const uint32_t dst = stages + s * p.stage_bytes;
       mbar_expect_tx(c.a_full(s), (uint32_t)kABytes);
       if (kind == kUpGate) {
         tma_load_3d(dst, map, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
@@ -253,7 +269,7 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
   const BParams& p = *c.p;
-  const uint32_t stages = smem_u32(c.smem + Smem::kOffStages);
+  const uint32_t stages = smem_u32(c.smem + p.off_stages);
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)p.Bpad >> 3) << 17) | ((128u >> 4) << 24);
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
   unsigned n = 0, sg = 0;
@@ -266,16 +282,21 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
     unit_range(d.T * d.KB, G, cta, lo, hi);
     int kb = lo % d.KB;
     bool seg_start = true;
+    long long w_a = 0, w_b = 0;
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
       const unsigned buf = sg & 1u;
       if (seg_start && sg >= 2u && !mbar_wait(c, c.acc_empty(buf), ((sg >> 1) - 1u) & 1u, ph, 2)) return;
-      const int s = (int)(n % kStages);
-      const unsigned par = (n / kStages) & 1u;
+      const int s = (int)(n % (unsigned)p.stages);
+      const unsigned par = (n / (unsigned)p.stages) & 1u;
+      const long long t0 = clock64();
       if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
+      const long long t1 = clock64();
       if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
+      w_a += t1 - t0;
+      w_b += clock64() - t1;
       tmem_fence_after_sync();
-      const uint64_t da = desc_sw128(stages + s * kStageBytes), db = desc_sw128(stages + s * kStageBytes + kABytes);
+      const uint64_t da = desc_sw128(stages + s * p.stage_bytes), db = desc_sw128(stages + s * p.stage_bytes + kABytes);
       const uint32_t dcol = tmem + buf * (uint32_t)p.Bpad;
       // (k-step k reads 32 bytes further along K: the start-address field grows by 2)
       if (seg_start) mma_bf16_set(dcol, da, db, idesc);
@@ -291,6 +312,8 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
         seg_start = true;
       }
     }
+    trace_val(p, ph, 3, (unsigned long long)w_a);
+    trace_val(p, ph, 4, (unsigned long long)w_b);
   }
 }
 
@@ -311,16 +334,17 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
 // Stages the activation operand of units [lo, hi).  A warp takes D consecutive units at a time (the four warps
 // round-robin over groups of D) and a lane has NPL 16-byte pieces per unit: all D * NPL <= 16 loads of a group are
 // issued before the first is used, so that a warp pays one L2 round trip per group, not per unit or per piece.
-// 5 * D - 1 must stay below 2 * kStages: a warp that got two laps of the ring ahead of the tensor core would take an
+// 5 * D - 1 must stay below twice the number of ring slots: a warp that got two laps of the ring ahead of the tensor core would take an
 // old completion of a stage's mbarrier (same parity) for the one it waits for.
 template <int NPL, int D>
 __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
                                             const uint16_t* src, const uint16_t* gain, const float* rs) {
-  static_assert(4 * D + D - 1 < 2 * kStages, "a stager warp could run two ring laps ahead");
+  static_assert(4 * D + D - 1 < 2 * kMinStages, "a stager warp could run two ring laps ahead");
   const BParams& p = *c.p;
   const int sw = st >> 5, lane = st & 31;
   const int chunk = lane & 7;         // 16-byte piece inside the 128-byte k-block row
   const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
+  long long w_slot = 0, w_fill = 0;
 #pragma unroll 1
   for (int base = lo + sw * D; base < hi; base += 4 * D) {
     uint4 v[D][NPL];
@@ -343,10 +367,13 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       const int u = base + j;
       if (u >= hi) break;
       const unsigned nu = n + (unsigned)(u - lo);
-      const int s = (int)(nu % kStages);
-      const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / kStages) - 1u) & 1u, ph, 5);
+      const int s = (int)(nu % (unsigned)p.stages);
+      const long long t0 = clock64();
+      const bool ok = nu < (unsigned)p.stages || mbar_wait(c, c.empty(s), ((nu / (unsigned)p.stages) - 1u) & 1u, ph, 5);
+      const long long t1 = clock64();
+      w_slot += t1 - t0;
       if (!ok) continue;
-      unsigned char* dst = c.smem + Smem::kOffStages + s * kStageBytes + kABytes;
+      unsigned char* dst = c.smem + p.off_stages + s * p.stage_bytes + kABytes;
       const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4[j]);
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
@@ -365,7 +392,12 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       }
       fence_async_smem();
       mbar_arrive1(c.b_full(s));
+      w_fill += clock64() - t1;
     }
+  }
+  if (st == 0) {
+    trace_val(p, ph, 6, (unsigned long long)w_slot);
+    trace_val(p, ph, 7, (unsigned long long)w_fill);
   }
 }
 
@@ -455,7 +487,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         const int pos = pos_s[bb];
         float x[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = bf16_round(exch[(rg * 8 + j) * kExchStride + bb]);
+        for (int j = 0; j < 8; ++j) x[j] = bf16_round(exch[(rg * 8 + j) * p.exch_stride + bb]);
         if (p.q_norm != nullptr) {
           // _per_head_rms_norm (Qwen3 operations.py:52-63) on the bf16-rounded projection, fp32 until the end
           float ssq = 0.f;
@@ -527,7 +559,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float old = (j & 1) ? bf_hi(ow[j >> 1]) : bf_lo(ow[j >> 1]);
-            const float add = act ? bf16_round(exch[(rg * 8 + j) * kExchStride + bb]) : 0.f;
+            const float add = act ? bf16_round(exch[(rg * 8 + j) * p.exch_stride + bb]) : 0.f;
             nv[j] = bf16_round(old + add);
             sq += nv[j] * nv[j];
           }
@@ -553,7 +585,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
         for (int b = b0; b < b1 && b < B; ++b) {
           const unsigned short bits =
-              act_s[b] ? silu_mul(exch[u * kExchStride + b], exch[(64 + u) * kExchStride + b]) : (unsigned short)0;
+              act_s[b] ? silu_mul(exch[u * p.exch_stride + b], exch[(64 + u) * p.exch_stride + b]) : (unsigned short)0;
           p.silu_out[(size_t)b * p.I + unit] = bits;
         }
       }
@@ -563,7 +595,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       const int row = t * kTileRows + e;
       if (row < p.vocab) {
         for (int b = 0; b < B; ++b) {
-          const float v = act_s[b] ? exch[e * kExchStride + b] : -1e9f;
+          const float v = act_s[b] ? exch[e * p.exch_stride + b] : -1e9f;
           p.logits[(size_t)b * p.vocab + row] = f32_to_bf16_bits(v);
         }
       }
@@ -571,7 +603,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         unsigned long long best = 0ull;
         const int nrow = min(kTileRows, p.vocab - t * kTileRows);
         for (int r = 0; r < nrow; ++r) {
-          const float v = act_s[e] ? exch[r * kExchStride + e] : -1e9f;
+          const float v = act_s[e] ? exch[r * p.exch_stride + e] : -1e9f;
           const unsigned long long key = argmax_key(f32_to_bf16_bits(v), t * kTileRows + r);
           best = key > best ? key : best;
         }
@@ -616,7 +648,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
         tmem_wait_ld();
         if (full) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) exch[r * kExchStride + ch * 16 + j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j) exch[r * p.exch_stride + ch * 16 + j] = __uint_as_float(v[j]);
         } else {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
@@ -650,7 +682,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const bool run = c.ctl[kCFlagEpi] != 0u;
     if (run && !full) {
       __threadfence();
-      float* o = exch + r * kExchStride;
+      float* o = exch + r * p.exch_stride;
       float* sl = slot + r * 4;
 #pragma unroll 4
       for (int ch4 = 0; ch4 < p.Bpad / 4; ++ch4) {
@@ -944,7 +976,7 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
   c.warp = threadIdx.x >> 5;
   c.lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < p.stages; ++s) {
       mbar_init(c.a_full(s), 1);
       mbar_init(c.b_full(s), 32);
       mbar_init(c.empty(s), 1);
@@ -1018,10 +1050,10 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
   __syncthreads();
   if (threadIdx.x == 0 && c.aborted()) {
     // leave no tensor copy in flight into this CTA's shared memory: wait (bounded) for the last fills
-    const unsigned first = n_issued > (unsigned)kStages ? n_issued - kStages : 0u;
+    const unsigned first = n_issued > (unsigned)p.stages ? n_issued - (unsigned)p.stages : 0u;
     for (unsigned m = first; m < n_issued; ++m) {
       const long long t0 = clock64();
-      while (!mbar_try_wait(c.a_full((int)(m % kStages)), (m / kStages) & 1u)) {
+      while (!mbar_try_wait(c.a_full((int)(m % (unsigned)p.stages)), (m / (unsigned)p.stages) & 1u)) {
         if (clock64() - t0 > p.timeout_cycles) break;
       }
     }

@@ -57,6 +57,7 @@ struct BParams {
   int B, Bpad;                   // sequences, padded to a multiple of 16
   int pos;                       // position of every row when position_ids is null
   int phase_begin, phase_end;
+  int stages, stage_bytes, off_stages, exch_stride;   // shared-memory plan for this Bpad (smem_plan)
   int prologue;                  // 0 none; 1 sums of squares of `hidden`; 2 embed token_in, then sums of squares
   int wait_first;                // failure test: the first phase waits for a dependency nothing publishes
   float eps, qk_eps, scale_log2e;
