@@ -221,12 +221,7 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.vocab = d.vocab_size;
   p.B = st->batch;
   p.Bpad = (st->batch + 15) / 16 * 16;
-  SmemPlan plan = smem_plan(p.Bpad);
-  {
-    // measurement knob: fewer ring slots than fit (QMK_BATCH_MAX_STAGES, at least kMinStages)
-    static const int cap = [] { const char* e = getenv("QMK_BATCH_MAX_STAGES"); return e ? atoi(e) : 0; }();
-    if (cap >= kMinStages && cap < plan.stages) plan.stages = cap;
-  }
+  const SmemPlan plan = smem_plan(p.Bpad);
   p.stages = plan.stages;
   p.stage_bytes = plan.stage_bytes;
   p.off_stages = plan.off_stages;
@@ -235,6 +230,10 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.phase_begin = a->phase_begin;
   p.phase_end = a->phase_end;
   p.wait_first = a->wait_first;
+  {
+    static const int tm = [] { const char* e = getenv("QMK_TRACE_ISSUER"); return e ? atoi(e) : 0; }();
+    p.trace_mode = tm;
+  }
   p.eps = d.rms_norm_eps;
   p.qk_eps = d.qk_norm_eps > 0.f ? d.qk_norm_eps : d.rms_norm_eps;
   p.scale_log2e = d.attn_scale * 1.4426950408889634f;

@@ -40,8 +40,9 @@ namespace qmkb {
 
 using namespace qmk;
 
-constexpr int kMaxStages = 12;                          // ring slots; the launch uses as many as fit (smem_plan)
-constexpr int kMinStages = 7;
+constexpr int kStages = 8;                              // ring slots (a power of two: slot and parity of unit n are n & 7, (n >> 3) & 1;
+                                                        // more slots were measured to change nothing)
+constexpr int kMaxStages = kStages, kMinStages = kStages;
 constexpr int kABytes = kTileRows * kBlockK * 2;        // 16 KiB of weights per unit
 constexpr int kNumWarps = 10;
 constexpr int kBatchThreads = kNumWarps * 32;
@@ -70,9 +71,8 @@ __host__ __device__ inline SmemPlan smem_plan(int Bpad) {
   s.exch_stride = Bpad + 1;
   s.off_stages = (Smem::kOffExch + kTileRows * s.exch_stride * 4 + 1023) / 1024 * 1024;
   s.stage_bytes = kABytes + Bpad * kBlockK * 2;
-  s.stages = (kSmemBudget - 1024 - s.off_stages) / s.stage_bytes;     // 1024: slack to align the base
-  if (s.stages > kMaxStages) s.stages = kMaxStages;
-  s.total = s.off_stages + s.stages * s.stage_bytes + 1024;
+  s.stages = kStages;
+  s.total = s.off_stages + s.stages * s.stage_bytes;   // 227 KiB exactly at Bpad = 64; the base must be 1024-aligned
   return s;
 }
 // control words: [0] abort  [1] tensor-memory base  [2] Tmax  [3] flag of the epilogue group  [4] flag of the stagers
@@ -161,7 +161,7 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
 // Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
 // satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
 // the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
-// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival.
+// the weights / the activations of a unit (QMK_TRACE_ISSUER=1: for a free accumulator / issuing); 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival.
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
   if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (5 * p.num_layers + 1) + ph) * 8 + slot] = globaltimer_ns();
 }
@@ -186,6 +186,7 @@ struct Ctx {
 
 // Bounded wait on an mbarrier phase.  False when the budget expired or the CTA is aborting.
 static __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity, int phase, int detail) {
+  if (c.ctl[kCAbort] != 0u) return false;
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -201,7 +202,6 @@ static __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, u
   }
 }
 __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity, int phase, int detail) {
-  if (c.ctl[kCAbort] != 0u) return false;
   return mbar_try_wait(bar, parity) || mbar_wait_slow(c, bar, parity, phase, detail);
 }
 
@@ -245,8 +245,8 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
     int t = lo / d.KB, kb = lo - t * d.KB;
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
-      const int s = (int)(n % (unsigned)p.stages);
-      if (n >= (unsigned)p.stages && !mbar_wait(c, c.empty(s), ((n / (unsigned)p.stages) - 1u) & 1u, ph, 1)) {
+      const int s = (int)(n & (unsigned)(kStages - 1));
+      if (n >= (unsigned)kStages && !mbar_wait(c, c.empty(s), ((n / (unsigned)kStages) - 1u) & 1u, ph, 1)) {
         n_issued = n;
         return;
       }
@@ -273,6 +273,7 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)p.Bpad >> 3) << 17) | ((128u >> 4) << 24);
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
   unsigned n = 0, sg = 0;
+  const bool tr = p.trace != nullptr;
 #pragma unroll 1
   for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
     const int kind = phase_kind(ph, p.num_layers);
@@ -282,19 +283,22 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
     unit_range(d.T * d.KB, G, cta, lo, hi);
     int kb = lo % d.KB;
     bool seg_start = true;
-    long long w_a = 0, w_b = 0;
+    long long w_a = 0, w_b = 0, w_acc = 0, w_iss = 0;
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
       const unsigned buf = sg & 1u;
+      const long long tq = tr ? clock64() : 0;
       if (seg_start && sg >= 2u && !mbar_wait(c, c.acc_empty(buf), ((sg >> 1) - 1u) & 1u, ph, 2)) return;
-      const int s = (int)(n % (unsigned)p.stages);
-      const unsigned par = (n / (unsigned)p.stages) & 1u;
-      const long long t0 = clock64();
+      if (tr) w_acc += clock64() - tq;
+      const int s = (int)(n & (unsigned)(kStages - 1));
+      const unsigned par = (n / (unsigned)kStages) & 1u;
+      const long long t0 = tr ? clock64() : 0;
       if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
-      const long long t1 = clock64();
+      const long long t1 = tr ? clock64() : 0;
       if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
       w_a += t1 - t0;
-      w_b += clock64() - t1;
+      const long long t2 = tr ? clock64() : 0;
+      w_b += t2 - t1;
       tmem_fence_after_sync();
       const uint64_t da = desc_sw128(stages + s * p.stage_bytes), db = desc_sw128(stages + s * p.stage_bytes + kABytes);
       const uint32_t dcol = tmem + buf * (uint32_t)p.Bpad;
@@ -304,6 +308,7 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
 #pragma unroll
       for (int k = 1; k < kBlockK / 16; ++k) mma_bf16_add(dcol, da + 2u * k, db + 2u * k, idesc);
       mma_commit(c.empty(s));
+      if (tr) w_iss += clock64() - t2;
       seg_start = false;
       if (++kb == d.KB || u + 1 == hi) {
         mma_commit(c.acc_full(buf));
@@ -312,8 +317,8 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
         seg_start = true;
       }
     }
-    trace_val(p, ph, 3, (unsigned long long)w_a);
-    trace_val(p, ph, 4, (unsigned long long)w_b);
+    trace_val(p, ph, 3, (unsigned long long)(p.trace_mode == 1 ? w_acc : w_a));
+    trace_val(p, ph, 4, (unsigned long long)(p.trace_mode == 1 ? w_iss : w_b));
   }
 }
 
@@ -345,6 +350,7 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
   const int chunk = lane & 7;         // 16-byte piece inside the 128-byte k-block row
   const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
   long long w_slot = 0, w_fill = 0;
+  const bool tr = p.trace != nullptr;
 #pragma unroll 1
   for (int base = lo + sw * D; base < hi; base += 4 * D) {
     uint4 v[D][NPL];
@@ -367,10 +373,10 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       const int u = base + j;
       if (u >= hi) break;
       const unsigned nu = n + (unsigned)(u - lo);
-      const int s = (int)(nu % (unsigned)p.stages);
-      const long long t0 = clock64();
-      const bool ok = nu < (unsigned)p.stages || mbar_wait(c, c.empty(s), ((nu / (unsigned)p.stages) - 1u) & 1u, ph, 5);
-      const long long t1 = clock64();
+      const int s = (int)(nu & (unsigned)(kStages - 1));
+      const long long t0 = tr ? clock64() : 0;
+      const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / (unsigned)kStages) - 1u) & 1u, ph, 5);
+      const long long t1 = tr ? clock64() : 0;
       w_slot += t1 - t0;
       if (!ok) continue;
       unsigned char* dst = c.smem + p.off_stages + s * p.stage_bytes + kABytes;
@@ -392,7 +398,7 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       }
       fence_async_smem();
       mbar_arrive1(c.b_full(s));
-      w_fill += clock64() - t1;
+      if (tr) w_fill += clock64() - t1;
     }
   }
   if (st == 0) {
@@ -966,8 +972,11 @@ __device__ __forceinline__ void finalize(const Ctx& c, int e) {
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kBatchThreads, 1)
 qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ TensorMaps maps) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {   // the swizzle atoms need a 1024-byte aligned ring (true without static shared memory)
+    if (threadIdx.x == 0) report(p, kErrStageWait, 0, p.phase_begin, smem_u32(smem), 1024u, 9);
+    return;
+  }
   Ctx c;
   c.p = &p;
   c.smem = smem;
@@ -976,7 +985,7 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
   c.warp = threadIdx.x >> 5;
   c.lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(c.a_full(s), 1);
       mbar_init(c.b_full(s), 32);
       mbar_init(c.empty(s), 1);
@@ -1050,10 +1059,10 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
   __syncthreads();
   if (threadIdx.x == 0 && c.aborted()) {
     // leave no tensor copy in flight into this CTA's shared memory: wait (bounded) for the last fills
-    const unsigned first = n_issued > (unsigned)p.stages ? n_issued - (unsigned)p.stages : 0u;
+    const unsigned first = n_issued > (unsigned)kStages ? n_issued - (unsigned)kStages : 0u;
     for (unsigned m = first; m < n_issued; ++m) {
       const long long t0 = clock64();
-      while (!mbar_try_wait(c.a_full((int)(m % (unsigned)p.stages)), (m / (unsigned)p.stages) & 1u)) {
+      while (!mbar_try_wait(c.a_full((int)(m & (unsigned)(kStages - 1))), (m / (unsigned)kStages) & 1u)) {
         if (clock64() - t0 > p.timeout_cycles) break;
       }
     }

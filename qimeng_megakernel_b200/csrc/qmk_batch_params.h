@@ -59,6 +59,7 @@ struct BParams {
   int phase_begin, phase_end;
   int stages, stage_bytes, off_stages, exch_stride;   // shared-memory plan for this Bpad (smem_plan)
   int prologue;                  // 0 none; 1 sums of squares of `hidden`; 2 embed token_in, then sums of squares
+  int trace_mode;                // timeline slots 3 / 4: 0 issuer waits for operands, 1 accumulator wait and issue time
   int wait_first;                // failure test: the first phase waits for a dependency nothing publishes
   float eps, qk_eps, scale_log2e;
   long long timeout_cycles;
