@@ -43,7 +43,7 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   return pol;
 }
 // One contiguous chunk, global -> this CTA's shared memory; both addresses 16-byte aligned,
-// size a multiple of 16.  No multicast: the destination is the issuing CTA only.
+// size a multiple of 16.  The destination is the issuing CTA only.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
                                          uint64_t policy) {
   asm volatile(
