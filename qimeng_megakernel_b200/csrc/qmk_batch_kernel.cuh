@@ -754,24 +754,26 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
       for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
     }
     const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
-    constexpr int NLD = 8;               // K-row pieces (and V-row pieces) a lane keeps in flight
-    constexpr int KBK = NLD * KPL;       // keys per block: 32 (head_dim 64) or 16 (head_dim 128)
-#pragma unroll 1
-    for (int k0 = k_lo; k0 < k_hi; k0 += KBK) {
-      uint4 kk[NLD], vv[NLD];
+    // Keys are taken in half-blocks of NLD row pieces per lane (16 keys at head_dim 64, 8 at 128), double-buffered in
+    // registers: the loads of the next half-block are in flight while this one is multiplied.
+    constexpr int NLD = 4;
+    constexpr int KBK = NLD * KPL;
+    auto load_block = [&](uint4 (&kk)[NLD], uint4 (&vv)[NLD], int ks) {
 #pragma unroll
       for (int i = 0; i < NLD; ++i) {
-        const int k = k0 + i * KPL + sub;
+        const int k = ks + i * KPL + sub;
         kk[i] = k < k_hi ? ldcg_u4(p.k_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int i = 0; i < NLD; ++i) {
-        const int k = k0 + i * KPL + sub;
+        const int k = ks + i * KPL + sub;
         vv[i] = k < k_hi ? ldcg_u4(p.v_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
       }
+    };
+    auto use_block = [&](const uint4 (&kk)[NLD], const uint4 (&vv)[NLD], int ks) {
 #pragma unroll
       for (int i = 0; i < NLD; ++i) {
-        const bool valid = k0 + i * KPL + sub < k_hi;
+        const bool valid = ks + i * KPL + sub < k_hi;
         const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kk[i]);
         const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vv[i]);
         float kf[8], vf[8];
@@ -798,6 +800,15 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
           }
         }
       }
+    };
+    uint4 ka[NLD], va[NLD], kb2[NLD], vb2[NLD];
+    load_block(ka, va, k_lo);
+#pragma unroll 1
+    for (int k0 = k_lo; k0 < k_hi; k0 += 2 * KBK) {
+      load_block(kb2, vb2, k0 + KBK);          // (past the end: nothing is loaded, nothing is used)
+      use_block(ka, va, k0);
+      load_block(ka, va, k0 + 2 * KBK);
+      use_block(kb2, vb2, k0 + KBK);
     }
     // merge the KPL key sub-streams (lanes with equal dl)
 #pragma unroll

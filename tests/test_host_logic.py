@@ -152,3 +152,34 @@ def test_two_rank_sharding_and_max_over_ranks(tmp_path):
                          capture_output=True, text=True, env=env, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "VALUE 100.0" in out.stdout
+
+
+def test_batched_sharding_gives_every_rank_its_own_sequences():
+    """bench.py --batch B: rank r decodes prompts seeded 1 + r * B + b, so no sequence is decoded twice on any
+    number of GPUs, and the aggregate counts world * B * K tokens."""
+    from qimeng_megakernel_b200 import synthetic
+    B, world = 4, 2
+    rows = [synthetic.make_prompts(128256, B, 16, seed=1 + rank * B) for rank in range(world)]
+    allrows = torch.cat(rows)
+    assert allrows.shape == (world * B, 16)
+    assert len({tuple(r.tolist()) for r in allrows}) == world * B
+    # a single sequence decoded alone and row 0 of a batch start from the same prompt
+    assert torch.equal(synthetic.make_prompt(128256, 16, seed=1), rows[0][0])
+
+
+def test_batched_globals_shapes():
+    """make_globals(batch=B) allocates the reference's multi-batch state shapes; batch=None the single-batch ones."""
+    from qimeng_megakernel_b200 import synthetic
+    cfg = dict(num_hidden_layers=1, hidden_size=128, intermediate_size=256, head_dim=64, num_attention_heads=2,
+               num_key_value_heads=1, vocab_size=96, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+               max_position_embeddings=32, qk_norm=True)
+    w = synthetic.make_weights(cfg, seed=3, device="cpu", max_positions=32)
+    assert w["q_norm_weights"].shape == (1, 64) and w["k_norm_weights"].shape == (1, 64)
+    g = synthetic.make_globals(cfg, w, kv_seq_len=8, device="cpu", batch=5)
+    assert g.hidden_states.shape == (5, 128) and g.logits.shape == (5, 96) and g.k_cache.shape == (1, 5, 8, 1, 64)
+    assert g.next_token.shape == (5,) and g.q_norm_weights is not None
+    g1 = synthetic.make_globals(cfg, w, kv_seq_len=8, device="cpu")
+    assert g1.hidden_states.shape == (128,) and g1.k_cache.shape == (1, 1, 8, 1, 64)
+    from qimeng_megakernel_b200 import mk_kernel
+    with pytest.raises(ValueError):        # CPU tensors are refused: there is no CPU path
+        mk_kernel.MegaKernel.__new__(mk_kernel.MegaKernel)._validate(g)
