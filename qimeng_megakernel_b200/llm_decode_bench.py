@@ -5,7 +5,7 @@ The counterpart of the reference's `python -m benchmarks.llm_decode --hardware .
 (batch sizes x output lengths, warm-up + measured iterations, continuation forced past EOS), same per-run
 and per-cell keys (tok_s, tok_s_gpu, kernel_tok_s, ..., validation.length_complete / greedy_rerun_match).
 Differences: there is no checkpoint or tokenizer offline, so the model is the seeded synthetic
-Llama-3.2-1B and the prompt is 16 seeded token ids; text quality checks (gibberish / repetition) do not
+Llama-3.2-1B (or Qwen3-0.6B) shape and the prompts are 16 seeded token ids per row (batch sizes up to 64); text quality checks (gibberish / repetition) do not
 apply to token ids and are left out; weights are generated once, not re-read from disk every iteration
 (llm_decode.py:99-104 does); each cell also reports the HBM roofline fraction.
 """
@@ -21,7 +21,7 @@ import torch
 
 from . import mk_kernel, synthetic
 from .decode import decode as llm_decode
-from .model_config import LLAMA_3_2_1B
+from .model_config import LLAMA_3_2_1B, QWEN3_0_6B
 from .prefill import run_prefill_synthetic
 
 HBM_PEAK_GBS = 8000.0      # the "~8 TB/s" of the target specification; the measured copy bandwidth is lower
@@ -45,7 +45,9 @@ def _parse_args() -> argparse.Namespace:
 
 
 def _run_once(args, cfg, weights, mk, prompt, batch_size: int, output_len: int) -> dict:
-    prefill = run_prefill_synthetic(cfg, weights, prompt.view(1, -1), output_len, device=args.device, mk=mk)
+    prompts = prompt.view(1, -1) if batch_size == 1 else synthetic.make_prompts(
+        cfg["vocab_size"], batch_size, args.prompt_len, args.prompt_seed)   # row 0 is the single-sequence prompt
+    prefill = run_prefill_synthetic(cfg, weights, prompts, output_len, device=args.device, mk=mk)
     wall_t0 = time.perf_counter()
     out = llm_decode(args.model, prefill=prefill, max_new_tokens=output_len, decode_route="mk",
                      hardware=args.hardware, decode_time=True, ignore_eos=True, host_loop=args.host_loop)
@@ -70,7 +72,7 @@ def main() -> int:
     args = _parse_args()
     batch_sizes = [int(x) for x in args.batch_sizes.split(",") if x.strip()]
     output_lengths = [int(x) for x in args.output_lengths.split(",") if x.strip()]
-    cfg = dict(LLAMA_3_2_1B)
+    cfg = dict(QWEN3_0_6B if "qwen3" in args.model.lower() else LLAMA_3_2_1B)
     weights = synthetic.make_weights(cfg, seed=0, device=args.device, max_positions=max(2048, args.prompt_len + max(output_lengths) + 1))
     mk = mk_kernel.get_mk()
     prompt = synthetic.make_prompt(cfg["vocab_size"], args.prompt_len, args.prompt_seed)
