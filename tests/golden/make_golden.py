@@ -22,6 +22,10 @@ Fixtures:
   qwen3_l2_v4096.npz   the Qwen3-0.6B layer shape (hidden 1024, 16 / 8 heads of 128, intermediate 3072), 2 layers,
                        vocabulary 4096, through the reference's Qwen3 fused ops (per-head Q/K RMSNorm):
                        qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/decode_schedule/fused/operations.py
+  moe_block.npz        the reference's fused MoE block (qwen1_5_moe_a2_7b/.../fused/operations.py:151-268) on a small
+                       shape, once with a shared expert and 16 experts / top-4, once shaped like an OLMoE layer in
+                       miniature (no shared expert: its weights are zero; 64 experts / top-8, router logits ~ N(0,1)).
+                       Pins oracle/moe_oracle.py; no CUDA kernel implements this block yet.
   llama1b_cfg1.npz     (--full) the BASELINE configuration 1: 16 layers, vocabulary 128256, 16 seeded prompt
                        tokens then greedy decode; greedy tokens, top-8 logits per step, per-layer hidden
                        states of selected steps (bf16 and fp32).  Compared with the CUDA kernel on the GPU.
@@ -274,6 +278,68 @@ def make_qwen3():
     print("wrote qwen3_l2_v4096.npz")
 
 
+MOE_CASES = (dict(name="shared", hidden_size=256, intermediate_size=512, moe_intermediate_size=128, num_experts=16,
+                       num_experts_per_tok=4, shared=True, seed=11),
+                  dict(name="olmoe_like", hidden_size=256, intermediate_size=64, moe_intermediate_size=128,
+                       num_experts=64, num_experts_per_tok=8, shared=False, seed=12))
+
+
+def moe_weights(case: dict) -> dict:
+    """Seeded weights of one MoE layer (N(0, 0.02) like the dense models; router rows scaled so that the logits of a
+    unit-RMS input are ~ N(0, 1); gains drawn around 1)."""
+    gen = torch.Generator().manual_seed(case["seed"])
+    H, I, Ie, E = case["hidden_size"], case["intermediate_size"], case["moe_intermediate_size"], case["num_experts"]
+    r = lambda *shape, std=0.02: (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+    w = {"mlp_norm": (1.0 + 0.1 * torch.randn(H, generator=gen)).to(torch.bfloat16),
+         "shared_gate_proj": r(I, H), "shared_up_proj": r(I, H), "shared_down_proj": r(H, I),
+         "shared_expert_gate": r(H, 1), "router": r(E, H, std=H ** -0.5),
+         "expert_gate_up": r(E, 2 * Ie, H), "expert_down": r(E, H, Ie)}
+    if not case["shared"]:
+        for k in ("shared_gate_proj", "shared_up_proj", "shared_down_proj", "shared_expert_gate"):
+            w[k].zero_()
+    w["inputs"] = (torch.randn(6, H, generator=gen) * 0.7).to(torch.bfloat16)
+    return w
+
+
+def make_moe():
+    import importlib
+    mpkg = "qimeng_megakernel.models.LLM.qwen.qwen1_5_moe_a2_7b.A100.single_batch.decode_schedule"
+    pkg = importlib.import_module(mpkg)
+    ops = importlib.import_module(mpkg + ".fused.operations")
+    out = {}
+    for case in MOE_CASES:
+        C = pkg.QwenMoeConfig
+        for k in ("hidden_size", "intermediate_size", "moe_intermediate_size", "num_experts", "num_experts_per_tok"):
+            setattr(C, k, case[k])
+        C.rms_norm_eps = 1e-6
+        w = moe_weights(case)
+        H, Ie, K = case["hidden_size"], case["moe_intermediate_size"], case["num_experts_per_tok"]
+        for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+            c = lambda t: t.to(dtype).unsqueeze(0)       # one layer
+            g = pkg.Globals(
+                mlp_norm_weights=c(w["mlp_norm"]), shared_expert_gate_proj_weights=c(w["shared_gate_proj"]),
+                shared_expert_up_proj_weights=c(w["shared_up_proj"]), shared_expert_down_proj_weights=c(w["shared_down_proj"]),
+                shared_expert_gate_weights=c(w["shared_expert_gate"]), router_weights=c(w["router"]),
+                expert_gate_up_proj_weights=c(w["expert_gate_up"]), expert_down_proj_weights=c(w["expert_down"]),
+                hidden_states=torch.zeros(H, dtype=dtype), shared_out=torch.zeros(H, dtype=dtype),
+                routed_out=torch.zeros(H, dtype=dtype), silu_out=torch.zeros(Ie, dtype=dtype),
+                expert_indices=torch.zeros(K, dtype=torch.int64), expert_weights=torch.zeros(K, dtype=torch.float32))
+            recs = {"hidden": [], "shared_out": [], "routed_out": [], "expert_indices": [], "expert_weights": []}
+            for x in w["inputs"]:
+                g.hidden_states.copy_(x.to(dtype))
+                g.routed_out.zero_()
+                ops.fused_moe_block(g, 0)
+                recs["hidden"].append(bits(g.hidden_states.clone()))
+                recs["shared_out"].append(bits(g.shared_out.clone()))
+                recs["routed_out"].append(bits(g.routed_out.clone()))
+                recs["expert_indices"].append(g.expert_indices.clone().numpy())
+                recs["expert_weights"].append(g.expert_weights.clone().numpy())
+            for k, v in recs.items():
+                out[f"{case['name']}_{name}_{k}"] = np.stack(v)
+    np.savez_compressed(os.path.join(HERE, "moe_block.npz"), **out)
+    print("wrote moe_block.npz")
+
+
 def make_full(pkg, ops, n_new: int):
     cfg = dict(LLAMA_3_2_1B)
     t0 = time.time()
@@ -324,5 +390,7 @@ if __name__ == "__main__":
         make_batch(ops)
     if ap_only in ("", "qwen3"):
         make_qwen3()
+    if ap_only in ("", "moe"):
+        make_moe()
     if args.full:
         make_full(pkg, ops, args.new_tokens)

@@ -168,3 +168,36 @@ def test_oracle_edge_positions(small_config, small_weights):
         assert torch.isfinite(st.logits.float()).all()
     with pytest.raises((IndexError, RuntimeError)):
         fo.feed_token(st, 1, 8)            # beyond the cache
+
+
+def test_moe_block():
+    """The MoE block oracle (oracle/moe_oracle.py) against the reference's fused_moe_block: with a shared expert
+    (16 experts, top-4) and shaped like an OLMoE layer in miniature (64 experts, top-8, no shared expert)."""
+    import importlib.util
+    from oracle import moe_oracle as mo
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLD, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    z = np.load(os.path.join(GOLD, "moe_block.npz"))
+    for case in mg.MOE_CASES:
+        w = mg.moe_weights(case)
+        cfg = mo.MoeConfig(hidden_size=case["hidden_size"], intermediate_size=case["intermediate_size"],
+                           moe_intermediate_size=case["moe_intermediate_size"], num_experts=case["num_experts"],
+                           num_experts_per_tok=case["num_experts_per_tok"], rms_norm_eps=1e-6)
+        for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+            lw = mo.MoeLayerWeights(**{k: w[k].to(dtype) for k in (
+                "mlp_norm", "shared_gate_proj", "shared_up_proj", "shared_down_proj", "shared_expert_gate", "router",
+                "expert_gate_up", "expert_down")})
+            for i, x in enumerate(w["inputs"]):
+                r = mo.moe_block(cfg, lw, x.to(dtype))
+                key = f"{case['name']}_{name}_"
+                assert r["expert_indices"].tolist() == z[key + "expert_indices"][i].tolist(), f"{key} experts, input {i}"
+                assert np.allclose(r["expert_weights"].numpy(), z[key + "expert_weights"][i], rtol=1e-6, atol=0)
+                assert len(set(r["expert_indices"].tolist())) == case["num_experts_per_tok"]
+                for buf in ("shared_out", "routed_out", "hidden"):
+                    if dtype == torch.bfloat16:
+                        _assert_bits(r[buf], z[key + buf][i], f"{key}{buf} input {i}")
+                    else:
+                        assert torch.allclose(r[buf], torch.from_numpy(z[key + buf][i]), rtol=1e-5, atol=1e-6), f"{key}{buf}"
+                if not case["shared"]:
+                    assert float(r["shared_out"].float().abs().max()) == 0.0
