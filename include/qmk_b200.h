@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define QMK_ABI_VERSION 2
+#define QMK_ABI_VERSION 3
 
 /* Error codes (negative).  qmk_strerror() gives the text. */
 enum qmk_error {
@@ -48,9 +48,14 @@ enum qmk_error {
 /* Architecture families (selects epilogue variants). */
 enum qmk_arch {
   QMK_ARCH_LLAMA = 0,           /* RMSNorm -> QKV -> interleaved RoPE -> GQA -> SwiGLU    */
-  QMK_ARCH_QWEN3 = 1            /* the same with a per-head RMSNorm on Q and K before RoPE
+  QMK_ARCH_QWEN3 = 1,           /* the same with a per-head RMSNorm on Q and K before RoPE
                                    (qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/
                                    decode_schedule/fused/operations.py:52-120)             */
+  QMK_ARCH_MOE = 2              /* the Llama attention block with a mixture-of-experts MLP: router (fp32 softmax over
+                                   all experts, top-k, no renormalisation) and per-expert SwiGLU, no shared expert
+                                   (qimeng_megakernel/models/LLM/qwen/qwen1_5_moe_a2_7b/A100/single_batch/
+                                   decode_schedule/fused/operations.py:175-240 with the shared branch absent);
+                                   batched kernel only */
 };
 
 /*
@@ -76,6 +81,9 @@ typedef struct qmk_model_desc {
   float rms_norm_eps;
   float attn_scale;          /* 1/sqrt(head_dim), as the reference passes it (mk_kernel.py:61) */
   float qk_norm_eps;         /* QMK_ARCH_QWEN3: eps of the per-head Q/K norm (0 = rms_norm_eps)     */
+  int32_t num_experts;           /* QMK_ARCH_MOE: 8..128 experts (else 0)                            */
+  int32_t num_experts_per_tok;   /* QMK_ARCH_MOE: 1..16                                              */
+  int32_t moe_intermediate_size; /* QMK_ARCH_MOE: expert intermediate size, a multiple of 64         */
 } qmk_model_desc;
 
 /*
@@ -103,6 +111,10 @@ typedef struct qmk_weight_ptrs {
   const float* rope_sin;
   const void* q_norm;        /* QMK_ARCH_QWEN3: [L, HD] bf16, interleaved order; else NULL */
   const void* k_norm;        /* QMK_ARCH_QWEN3: [L, HD] bf16, interleaved order; else NULL */
+  /* QMK_ARCH_MOE (layouts of the reference's MoE Globals, globs.py:30-34; up_proj / gate_proj / down_proj unused): */
+  const void* router;            /* [L, E, H] bf16                                     */
+  const void* expert_gate_up;    /* [L, E, 2 * Ie, H] bf16, gate rows then up rows     */
+  const void* expert_down;       /* [L, E, H, Ie] bf16                                 */
 } qmk_weight_ptrs;
 
 /*
@@ -155,7 +167,8 @@ typedef struct qmk_status {
 
 typedef struct qmk_handle qmk_handle;
 
-/* Phase kinds inside one layer; phase index = layer * QMK_PHASES_PER_LAYER + kind, LM head last. */
+/* Phase kinds inside one layer; phase index = layer * QMK_PHASES_PER_LAYER + kind, LM head last.
+ * (QMK_ARCH_MOE has six phases per layer: QKV, attention, O-proj, router, expert up/gate, expert down.) */
 #define QMK_PHASES_PER_LAYER 5
 #define QMK_PHASE_QKV 0
 #define QMK_PHASE_ATTN 1

@@ -11,9 +11,10 @@ from pathlib import Path
 
 from ._build import LIB_PATH
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 ARCH_LLAMA = 0
 ARCH_QWEN3 = 1
+ARCH_MOE = 2
 MAX_BATCH = 64
 PHASES_PER_LAYER = 5
 PHASE_QKV, PHASE_ATTN, PHASE_OPROJ, PHASE_UPGATE, PHASE_DOWN = range(5)
@@ -28,13 +29,15 @@ class ModelDesc(C.Structure):
                 ("hidden_size", C.c_int32), ("intermediate_size", C.c_int32),
                 ("num_attention_heads", C.c_int32), ("num_key_value_heads", C.c_int32),
                 ("head_dim", C.c_int32), ("vocab_size", C.c_int32), ("rope_rows", C.c_int32),
-                ("rms_norm_eps", C.c_float), ("attn_scale", C.c_float), ("qk_norm_eps", C.c_float)]
+                ("rms_norm_eps", C.c_float), ("attn_scale", C.c_float), ("qk_norm_eps", C.c_float),
+                ("num_experts", C.c_int32), ("num_experts_per_tok", C.c_int32), ("moe_intermediate_size", C.c_int32)]
 
 
 class WeightPtrs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("attn_norm", "qkv", "o_proj", "mlp_norm", "up_proj", "gate_proj",
                                           "down_proj", "lm_head_norm", "lm_head", "embed_tokens",
-                                          "rope_cos", "rope_sin", "q_norm", "k_norm")]
+                                          "rope_cos", "rope_sin", "q_norm", "k_norm", "router", "expert_gate_up",
+                                          "expert_down")]
 
 
 class StatePtrs(C.Structure):

@@ -108,8 +108,10 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
   if (!tuned && qmkb_supported(d) != QMK_OK) return QMK_ERR_UNSUPPORTED_MODEL;
   if (d->num_layers < 0 || d->num_layers > 1024 || d->vocab_size < 1 || d->rope_rows < 1) return QMK_ERR_INVALID_ARG;
   if (!(d->rms_norm_eps > 0.f) || !(d->attn_scale > 0.f)) return QMK_ERR_INVALID_ARG;
-  const void* ptrs[] = {w->attn_norm, w->qkv, w->o_proj, w->mlp_norm, w->up_proj, w->gate_proj,
-                        w->down_proj, w->lm_head_norm, w->lm_head, w->rope_cos, w->rope_sin};
+  const bool moe = d->arch == QMK_ARCH_MOE;
+  const void* ptrs[] = {w->attn_norm, w->qkv, w->o_proj, w->mlp_norm, moe ? w->router : w->up_proj,
+                        moe ? w->expert_gate_up : w->gate_proj, moe ? w->expert_down : w->down_proj,
+                        w->lm_head_norm, w->lm_head, w->rope_cos, w->rope_sin};
   for (const void* p : ptrs)
     if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
   if (w->embed_tokens && !aligned16(w->embed_tokens)) return QMK_ERR_INVALID_ARG;
@@ -318,7 +320,7 @@ extern "C" int qmk_decode_step(qmk_handle* h, int32_t pos_id, void* cuda_stream)
   int rc = check_step_args(h, pos_id);
   if (rc) return rc;
   QMK_CUDA(h, cudaSetDevice(h->device));
-  if (use_batched(h)) return batched_launch(h, pos_id, 0, num_phases(h->desc.num_layers), 0, (cudaStream_t)cuda_stream);
+  if (use_batched(h)) return batched_launch(h, pos_id, 0, qmkb_num_phases(&h->desc), 0, (cudaStream_t)cuda_stream);
   Params p;
   fill_params(h, p, pos_id);
   return step_with(h, p, (cudaStream_t)cuda_stream);
@@ -328,7 +330,7 @@ extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin
                               void* cuda_stream) {
   int rc = check_step_args(h, pos_id);
   if (rc) return rc;
-  const int nph = num_phases(h->desc.num_layers);
+  const int nph = use_batched(h) ? qmkb_num_phases(&h->desc) : num_phases(h->desc.num_layers);
   if (phase_begin < 0 || phase_end > nph || phase_begin > phase_end || (mode != 0 && mode != 1))
     return QMK_ERR_INVALID_ARG;
   QMK_CUDA(h, cudaSetDevice(h->device));
@@ -394,7 +396,7 @@ extern "C" int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t ho
       h->st.next_token = (int64_t*)(h->d_tok + 1);
       h->st.out_tokens = nullptr;
       h->st.position_ids = nullptr;
-      rc = batched_launch(h, pos, 0, num_phases(h->desc.num_layers), 0, stream);
+      rc = batched_launch(h, pos, 0, qmkb_num_phases(&h->desc), 0, stream);
       h->st = saved;
     } else {
       Params p;
@@ -451,7 +453,7 @@ extern "C" int qmk_set_timeout_cycles(qmk_handle* h, int64_t cycles) {
 extern "C" int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes) {
   if (!h) return QMK_ERR_INVALID_ARG;
   if (device_buffer == nullptr) { h->trace = nullptr; return QMK_OK; }
-  const int64_t need = (int64_t)h->n_sm * num_phases(h->desc.num_layers) * 8 * 8;
+  const int64_t need = (int64_t)h->n_sm * (use_batched(h) ? qmkb_num_phases(&h->desc) : num_phases(h->desc.num_layers)) * 8 * 8;
   if (bytes < need || (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) return QMK_ERR_INVALID_ARG;
   h->trace = (unsigned long long*)device_buffer;
   return QMK_OK;
@@ -485,7 +487,15 @@ extern "C" int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id) {
   const long long H = d.hidden_size, I = d.intermediate_size;
   const long long QKV = (long long)(d.num_attention_heads + 2 * d.num_key_value_heads) * d.head_dim;
   const long long QD = (long long)d.num_attention_heads * d.head_dim;
-  const long long per_layer = 2 * (QKV * H + H * QD + 2 * I * H + H * I);
+  long long per_layer = 2 * (QKV * H + H * QD + 2 * I * H + H * I);
+  if (d.arch == QMK_ARCH_MOE) {
+    // experts touched by a step: at most one distinct set of top-k per row (an upper bound; the kernel reads the
+    // distinct experts only, which for near-uniform routing is min(E, about B * k))
+    const long long Bq = h->bound ? h->st.batch : 1;
+    long long touched = Bq * d.num_experts_per_tok;
+    if (touched > d.num_experts) touched = d.num_experts;
+    per_layer = 2 * (QKV * H + H * QD + (long long)d.num_experts * H + touched * 3 * H * d.moe_intermediate_size);
+  }
   const long long lm = 2ll * d.vocab_size * H;
   const long long kv_row = 2ll * d.num_key_value_heads * d.head_dim * 2;   // K and V, bf16
   const long long T = (long long)pos_id + 1;

@@ -26,6 +26,10 @@ struct qmk_batch_ctx {
   float* ws;
   float* ss;
   float* attn_part;
+  int* moe_ne;
+  int* moe_elist;
+  float* moe_w;
+  uint16_t* esilu;
   unsigned char* zero_begin;   // [phase_done | tile_tickets | attn_tickets | argmax_key]: zeroed before every launch
   size_t zero_bytes;
   unsigned* phase_done;
@@ -44,15 +48,24 @@ static int fail(char* err, size_t n, const char* what, cudaError_t e) {
 int qmkb_supported(const qmk_model_desc* d) {
   const int H = d->hidden_size, I = d->intermediate_size, NH = d->num_attention_heads, NKV = d->num_key_value_heads,
             HD = d->head_dim;
-  if (d->arch != QMK_ARCH_LLAMA && d->arch != QMK_ARCH_QWEN3) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (d->arch != QMK_ARCH_LLAMA && d->arch != QMK_ARCH_QWEN3 && d->arch != QMK_ARCH_MOE) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (d->arch == QMK_ARCH_MOE) {
+    if (d->num_experts < 8 || d->num_experts > kTileRows || d->num_experts_per_tok < 1 || d->num_experts_per_tok > 16 ||
+        d->num_experts_per_tok > d->num_experts || d->moe_intermediate_size < kBlockK ||
+        d->moe_intermediate_size % kBlockK != 0)
+      return QMK_ERR_UNSUPPORTED_MODEL;
+  }
   if (HD != 64 && HD != 128) return QMK_ERR_UNSUPPORTED_MODEL;
   if (NH < 1 || NKV < 1 || NH % NKV != 0) return QMK_ERR_UNSUPPORTED_MODEL;
   const int gq = NH / NKV;
   if (gq != 1 && gq != 2 && gq != 4) return QMK_ERR_UNSUPPORTED_MODEL;
-  if (H < kBlockK || H % kBlockK != 0 || H > 8192 || I < kBlockK || I % kBlockK != 0) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (H < kBlockK || H % kBlockK != 0 || H > 8192) return QMK_ERR_UNSUPPORTED_MODEL;
+  if (d->arch != QMK_ARCH_MOE && (I < kBlockK || I % kBlockK != 0)) return QMK_ERR_UNSUPPORTED_MODEL;
   if ((NH * HD) % kBlockK != 0 || NKV > 64) return QMK_ERR_UNSUPPORTED_MODEL;
   return QMK_OK;
 }
+
+int qmkb_num_phases(const qmk_model_desc* d) { return (d->arch == QMK_ARCH_MOE ? 6 : 5) * d->num_layers + 1; }
 
 typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -77,6 +90,7 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
   int rc = qmkb_supported(d);
   if (rc) return rc;
   if (d->arch == QMK_ARCH_QWEN3 && (!w->q_norm || !w->k_norm)) return QMK_ERR_INVALID_ARG;
+  if (d->arch == QMK_ARCH_MOE && (!w->router || !w->expert_gate_up || !w->expert_down)) return QMK_ERR_INVALID_ARG;
   qmk_batch_ctx* c = new (std::nothrow) qmk_batch_ctx();
   if (!c) return QMK_ERR_OOM;
   memset(c, 0, sizeof(*c));
@@ -96,12 +110,20 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     }
     encode_fn enc = (encode_fn)fn;
     int bad = 0;
+    const bool moe = d->arch == QMK_ARCH_MOE;
+    const int E = moe ? d->num_experts : 0, Ie = moe ? d->moe_intermediate_size : 0;
     if (L > 0) {
       bad |= make_map(enc, &c->maps.qkv, w->qkv, H, QKV, L, kTileRows);
       bad |= make_map(enc, &c->maps.o_proj, w->o_proj, QD, H, L, kTileRows);
-      bad |= make_map(enc, &c->maps.up, w->up_proj, H, I, L, kTileRows / 2);
-      bad |= make_map(enc, &c->maps.gate, w->gate_proj, H, I, L, kTileRows / 2);
-      bad |= make_map(enc, &c->maps.down, w->down_proj, I, H, L, kTileRows);
+      if (moe) {
+        bad |= make_map(enc, &c->maps.router, w->router, H, E, L, kTileRows);
+        bad |= make_map(enc, &c->maps.egu, w->expert_gate_up, H, 2 * Ie, (long long)L * E, kTileRows / 2);
+        bad |= make_map(enc, &c->maps.edown, w->expert_down, Ie, H, (long long)L * E, kTileRows);
+      } else {
+        bad |= make_map(enc, &c->maps.up, w->up_proj, H, I, L, kTileRows / 2);
+        bad |= make_map(enc, &c->maps.gate, w->gate_proj, H, I, L, kTileRows / 2);
+        bad |= make_map(enc, &c->maps.down, w->down_proj, I, H, L, kTileRows);
+      }
     }
     bad |= make_map(enc, &c->maps.lm_head, w->lm_head, H, V, 1, kTileRows);
     if (bad) {
@@ -113,7 +135,7 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     if (e != cudaSuccess) { rc = fail(err, errlen, "cudaFuncSetAttribute", e); break; }
 
     int max_tiles = (V + kTileRows - 1) / kTileRows;
-    const int t_upgate = (I + kTileRows / 2 - 1) / (kTileRows / 2), t_qkv = (QKV + kTileRows - 1) / kTileRows;
+    const int t_upgate = moe ? E * (Ie / (kTileRows / 2)) : (I + kTileRows / 2 - 1) / (kTileRows / 2), t_qkv = (QKV + kTileRows - 1) / kTileRows;
     if (t_upgate > max_tiles) max_tiles = t_upgate;
     if (t_qkv > max_tiles) max_tiles = t_qkv;
     if ((H + kTileRows - 1) / kTileRows > max_tiles) max_tiles = (H + kTileRows - 1) / kTileRows;
@@ -121,18 +143,25 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     const size_t b_ws = align_up((size_t)n_sm * 2 * kTileRows * kMaxBatch * 4, 256);
     const size_t b_ss = align_up((size_t)((H + kTileRows - 1) / kTileRows) * kMaxBatch * 4, 256);
     const size_t b_part = align_up(((size_t)n_sm * 8 + (size_t)kMaxBatch * NKV) * gq * (HD + 2) * 4, 256);
-    const size_t b_done = align_up((size_t)(5 * L + 1 + 2) * 4, 256);
+    const size_t b_done = align_up((size_t)(6 * L + 1 + 2) * 4, 256);
+    const size_t b_moe = moe ? align_up(256 + (size_t)E * 4, 256) + align_up((size_t)E * kMaxBatch * 4, 256) +
+                                   align_up((size_t)E * kMaxBatch * Ie * 2, 256) : 0;
     const size_t b_tt = align_up((size_t)max_tiles * 4, 256);
     const size_t b_at = align_up((size_t)kMaxBatch * NKV * 4, 256);
     const size_t b_am = align_up((size_t)kMaxBatch * 8, 256);
     const size_t b_status = 256;
-    c->scratch_bytes = b_ws + b_ss + b_part + b_done + b_tt + b_at + b_am + b_status;
+    c->scratch_bytes = b_ws + b_ss + b_part + b_moe + b_done + b_tt + b_at + b_am + b_status;
     e = cudaMalloc((void**)&c->scratch, c->scratch_bytes);
     if (e != cudaSuccess) { rc = QMK_ERR_OOM; fail(err, errlen, "cudaMalloc", e); break; }
     unsigned char* q = c->scratch;
     c->ws = (float*)q; q += b_ws;
     c->ss = (float*)q; q += b_ss;
     c->attn_part = (float*)q; q += b_part;
+    if (moe) {
+      c->moe_ne = (int*)q; c->moe_elist = (int*)(q + 256); q += align_up(256 + (size_t)E * 4, 256);
+      c->moe_w = (float*)q; q += align_up((size_t)E * kMaxBatch * 4, 256);
+      c->esilu = (uint16_t*)q; q += align_up((size_t)E * kMaxBatch * Ie * 2, 256);
+    }
     c->zero_begin = q;
     c->phase_done = (unsigned*)q; q += b_done;
     c->tile_tickets = (unsigned*)q; q += b_tt;
@@ -209,6 +238,15 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.argmax_key = c->argmax_key;
   p.phase_done = c->phase_done;
   p.status = c->status;
+  p.moe_ne = c->moe_ne;
+  p.moe_elist = c->moe_elist;
+  p.moe_w = c->moe_w;
+  p.esilu = c->esilu;
+  const bool moe = d.arch == QMK_ARCH_MOE;
+  p.E = moe ? d.num_experts : 0;
+  p.topk = moe ? d.num_experts_per_tok : 0;
+  p.Ie = moe ? d.moe_intermediate_size : 0;
+  p.ppl = moe ? 6 : 5;
   p.trace = a->trace;
   p.H = d.hidden_size;
   p.I = d.intermediate_size;
@@ -241,8 +279,8 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   // The first phase of the launch, when it starts with an RMSNorm, needs the sums of squares of the residual
   // stream: computed by a prologue (with the embedding of token_in when the step starts at phase 0).
   if (a->phase_begin < a->phase_end) {
-    const int k0 = phase_kind(a->phase_begin, p.num_layers);
-    if (k0 == kQkv || k0 == kUpGate || k0 == kLmHead)
+    const int k0 = phase_kind(p, a->phase_begin);
+    if (phase_normed(k0))
       p.prologue = (a->phase_begin == 0 && st->token_in != nullptr) ? 2 : 1;
   }
   if (a->wait_first) p.prologue = 0;

@@ -11,6 +11,9 @@ struct qmk_batch_ctx;
 // Checks the descriptor against what the batched kernel supports (QMK_OK or QMK_ERR_UNSUPPORTED_MODEL).
 int qmkb_supported(const qmk_model_desc* d);
 
+// Phases of one decode step for this descriptor (5 per layer, MoE 6, plus the LM head).
+int qmkb_num_phases(const qmk_model_desc* d);
+
 // Builds the tensor maps of the weight matrices and allocates the scratch on the current device.
 int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk_batch_ctx** out, char* err, size_t errlen);
 void qmkb_destroy(qmk_batch_ctx* c);

@@ -76,11 +76,13 @@ __host__ __device__ inline SmemPlan smem_plan(int Bpad) {
   return s;
 }
 // control words: [0] abort  [1] tensor-memory base  [2] Tmax  [3] flag of the epilogue group  [4] flag of the stagers
-// [5] flag of the attention group
-constexpr int kCAbort = 0, kCTmem = 1, kCTmax = 2, kCFlagEpi = 3, kCFlagStg = 4, kCFlagAttn = 5;
+// [5] flag of the attention group  [7] / [8] number of selected experts as read by the stagers / the epilogue group
+constexpr int kCAbort = 0, kCTmem = 1, kCTmax = 2, kCFlagEpi = 3, kCFlagStg = 4, kCFlagAttn = 5, kCNeStg = 7, kCNeEpi = 8;
 
 struct TensorMaps {
   CUtensorMap qkv, o_proj, up, gate, down, lm_head;   // 3-D {k, row, layer}; box {64, 128 (up/gate: 64), 1}
+  // MoE: router {H, E, L} box 128 rows; expert gate|up {H, 2 * Ie, L * E} box 64 rows; expert down {Ie, H, L * E} box 128
+  CUtensorMap router, egu, edown;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -163,11 +165,11 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
 // the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
 // the weights / the activations of a unit (QMK_TRACE_ISSUER=1: for a free accumulator / issuing); 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival.
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
-  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (5 * p.num_layers + 1) + ph) * 8 + slot] = globaltimer_ns();
+  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = globaltimer_ns();
 }
 
 __device__ __forceinline__ void trace_val(const BParams& p, int ph, int slot, unsigned long long v) {
-  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (5 * p.num_layers + 1) + ph) * 8 + slot] = v;
+  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = v;
 }
 
 struct Ctx {
@@ -223,6 +225,16 @@ static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* c
   }
 }
 
+// Number of distinct experts of this step, for the two expert phases of a MoE layer: valid once every CTA has finished
+// the layer's router phase (one thread calls this; 0 after a wait that gave up).
+static __device__ __noinline__ int expert_count(const Ctx& c, int ph) {
+  const BParams& p = *c.p;
+  const int rph = phase_layer(p, ph) * p.ppl + 3;
+  if (rph >= p.phase_begin && !counter_wait(c, p.phase_done + 1 + rph, gridDim.x, ph)) return 0;
+  return (int)ld_acquire_gpu(reinterpret_cast<const unsigned*>(p.moe_ne));
+}
+__device__ __forceinline__ bool is_expert_kind(int kind) { return kind == kEUpGate || kind == kEDown; }
+
 // ------------------------------------------------------------------------------------------------
 // producer (one thread)
 // ------------------------------------------------------------------------------------------------
@@ -234,15 +246,22 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
   unsigned n = 0;
 #pragma unroll 1
   for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
-    const int kind = phase_kind(ph, p.num_layers);
+    const int kind = phase_kind(p, ph);
     if (kind == kAttn) continue;
-    const int layer = kind == kLmHead ? 0 : ph / 5;
-    const PhaseDims d = phase_dims(p, kind);
+    const int layer = phase_layer(p, ph);
+    const int ne = is_expert_kind(kind) ? expert_count(c, ph) : 0;
+    const PhaseDims d = phase_dims(p, kind, ne);
     int lo, hi;
     unit_range(d.T * d.KB, G, cta, lo, hi);
     const CUtensorMap* map = kind == kQkv ? &maps.qkv : kind == kOproj ? &maps.o_proj : kind == kUpGate ? &maps.up
-                           : kind == kDown ? &maps.down : &maps.lm_head;
-    int t = lo / d.KB, kb = lo - t * d.KB;
+                           : kind == kDown ? &maps.down : kind == kRouter ? &maps.router : &maps.lm_head;
+    const int per = p.Ie > 0 ? p.Ie / kBlockK : 1;   // 64-row tiles (k-blocks) of one expert
+    int t = d.KB > 0 ? lo / d.KB : 0, kb = lo - t * d.KB;
+    int zslot = -1, zval = 0;   // expert phases: the selected expert's index is fetched when the slot changes
+    auto expert_z = [&](int slot) {
+      if (slot != zslot) { zslot = slot; zval = layer * p.E + __ldcg(p.moe_elist + slot); }
+      return zval;
+    };
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
       const int s = (int)(n & (unsigned)(kStages - 1));
@@ -255,6 +274,13 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
       if (kind == kUpGate) {
         tma_load_3d(dst, map, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
         tma_load_3d(dst + kABytes / 2, &maps.gate, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
+      } else if (kind == kEUpGate) {   // tile t = (selected expert t / per, 64 gate rows + 64 up rows of that expert)
+        const int z = expert_z(t / per), lt = t % per;
+        tma_load_3d(dst, &maps.egu, kb * kBlockK, lt * (kTileRows / 2), z, c.a_full(s), policy);
+        tma_load_3d(dst + kABytes / 2, &maps.egu, kb * kBlockK, p.Ie + lt * (kTileRows / 2), z, c.a_full(s), policy);
+      } else if (kind == kEDown) {     // k-block kb = (selected expert kb / per, its k-block kb % per)
+        const int z = expert_z(kb / per);
+        tma_load_3d(dst, &maps.edown, (kb % per) * kBlockK, t * kTileRows, z, c.a_full(s), policy);
       } else {
         tma_load_3d(dst, map, kb * kBlockK, t * kTileRows, layer, c.a_full(s), policy);
       }
@@ -276,12 +302,12 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
   const bool tr = p.trace != nullptr;
 #pragma unroll 1
   for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
-    const int kind = phase_kind(ph, p.num_layers);
+    const int kind = phase_kind(p, ph);
     if (kind == kAttn) continue;
-    const PhaseDims d = phase_dims(p, kind);
+    const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? expert_count(c, ph) : 0);
     int lo, hi;
     unit_range(d.T * d.KB, G, cta, lo, hi);
-    int kb = lo % d.KB;
+    int kb = d.KB > 0 ? lo % d.KB : 0;
     bool seg_start = true;
     long long w_a = 0, w_b = 0, w_acc = 0, w_iss = 0;
 #pragma unroll 1
@@ -331,7 +357,7 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
   needed = true;
   if (ph > p.phase_begin) return counter_wait(c, p.phase_done + ph, gridDim.x, ph);          // counter of phase ph - 1
   if (p.prologue != 0) return counter_wait(c, p.phase_done + 0, gridDim.x, ph);
-  if (p.wait_first) return counter_wait(c, p.phase_done + (ph > 0 ? ph : num_phases(p.num_layers) + 1), gridDim.x, ph);
+  if (p.wait_first) return counter_wait(c, p.phase_done + (ph > 0 ? ph : num_phases(p) + 1), gridDim.x, ph);
   needed = false;
   return true;
 }
@@ -343,7 +369,10 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
 // old completion of a stage's mbarrier (same parity) for the one it waits for.
 template <int NPL, int D>
 __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
-                                            const uint16_t* src, const uint16_t* gain, const float* rs) {
+                                            const uint16_t* src, const uint16_t* gain, const float* rs,
+                                            int per = 0, const float* wsc = nullptr) {
+  // per > 0 (expert down-projection): k-block kb of the phase is k-block kb % per of selected expert kb / per; the
+  // source is that expert's SiLU(gate) * up [slot, row, Ie] and every row is scaled by its router weight wsc[slot, row]
   static_assert(4 * D + D - 1 < 2 * kMinStages, "a stager warp could run two ring laps ahead");
   const BParams& p = *c.p;
   const int sw = st >> 5, lane = st & 31;
@@ -355,17 +384,28 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
   for (int base = lo + sw * D; base < hi; base += 4 * D) {
     uint4 v[D][NPL];
     uint4 g4[D];
+    float sc[D][NPL];
 #pragma unroll
     for (int j = 0; j < D; ++j) {
       const int u = base + j;
-      const int k0 = (u % d.KB) * kBlockK + chunk * 8;
+      const int kbu = u < hi ? u % d.KB : 0;
+      const int k0 = kbu * kBlockK + chunk * 8;
       g4[j] = make_uint4(0, 0, 0, 0);
       if (gain != nullptr && u < hi) g4[j] = __ldg(reinterpret_cast<const uint4*>(gain + k0));
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
         const int r = row0 + 4 * i;
         v[j][i] = make_uint4(0, 0, 0, 0);
-        if (u < hi && r < p.B) v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
+        sc[j][i] = 0.f;
+        if (u < hi && r < p.B) {
+          if (per > 0) {
+            const int slot = kbu / per;
+            v[j][i] = ldcg_u4(src + ((size_t)slot * kMaxBatch + r) * p.Ie + (kbu % per) * kBlockK + chunk * 8);
+            sc[j][i] = ldcg_f32(wsc + slot * kMaxBatch + r);
+          } else {
+            v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
+          }
+        }
       }
     }
 #pragma unroll
@@ -393,6 +433,10 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
             const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
             w[q] = pack_bf16x2(a, b);
           }
+        } else if (per > 0) {
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v[j][i]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf_lo(w[q]) * sc[j][i], bf_hi(w[q]) * sc[j][i]);
         }
         *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[j][i];
       }
@@ -410,18 +454,19 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
 __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int st, unsigned& n) {
   // st: thread index inside the stager group, 0..127
   const BParams& p = *c.p;
-  const int layer = kind == kLmHead ? 0 : ph / 5;
-  const PhaseDims d = phase_dims(p, kind);
-  int lo, hi;
-  unit_range(d.T * d.KB, (int)gridDim.x, (int)blockIdx.x, lo, hi);
+  const int layer = phase_layer(p, ph);
   if (st == 0) {
     bool needed;
     const bool ok = phase_dependency(c, ph, needed);
     (void)ok;
+    if (is_expert_kind(kind)) c.ctl[kCNeStg] = (unsigned)expert_count(c, ph);
     trace_put(p, ph, 0);
   }
   named_bar(kBarStg, 128);
-  const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
+  const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? (int)c.ctl[kCNeStg] : 0);
+  int lo, hi;
+  unit_range(d.T * d.KB, (int)gridDim.x, (int)blockIdx.x, lo, hi);
+  const bool normed = phase_normed(kind);
   float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
   if (normed) {
     if (st < p.Bpad) {
@@ -432,14 +477,18 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
     }
     named_bar(kBarStg, 128);
   }
-  const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : p.hidden;
+  const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : kind == kEDown ? p.esilu : p.hidden;
   const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
-                       : kind == kUpGate ? p.mlp_norm + (size_t)layer * p.H : p.lm_norm;
-  switch (p.Bpad) {
-    case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
-    case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
-    case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
-    default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs); break;
+                       : kind == kLmHead ? p.lm_norm : p.mlp_norm + (size_t)layer * p.H;
+  const int per = kind == kEDown ? p.Ie / kBlockK : 0;
+  const float* wsc = kind == kEDown ? p.moe_w : nullptr;
+  if (hi > lo) {
+    switch (p.Bpad) {
+      case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
+      case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
+      case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
+      default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
+    }
   }
   n += (unsigned)(hi - lo);
 }
@@ -462,7 +511,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
   float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
   const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
   const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
-  const int layer = kind == kLmHead ? 0 : ph / 5;
+  const int layer = phase_layer(p, ph);
   const int B = p.B;
   switch (kind) {
     case kQkv: {
@@ -538,7 +587,71 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       }
       break;
     }
+    case kRouter: {
+      // fused_router (qwen1_5_moe_a2_7b/.../fused/operations.py:175-194): fp32 softmax over all experts, the k largest
+      // probabilities as they are (no renormalisation), lowest index first on equal values.  Column b of the tile is
+      // overwritten by row b's selection (probability, 0 elsewhere); then the distinct experts of the step are listed
+      // in ascending order and every (selected expert, row) gets its weight for the expert down-projection.
+      const int E = p.E;
+      if (e < p.Bpad) {
+        const bool act = e < B && act_s[e] != 0;
+        float mx = -INFINITY;
+        for (int x = 0; x < E; ++x) mx = fmaxf(mx, exch[x * p.exch_stride + e]);
+        float sum = 0.f;
+        for (int x = 0; x < E; ++x) sum += __expf(exch[x * p.exch_stride + e] - mx);
+        const float inv = 1.0f / sum;
+        // mark the k largest by negating them in place (probabilities are positive), then clean up
+        for (int x = 0; x < E; ++x) exch[x * p.exch_stride + e] = __expf(exch[x * p.exch_stride + e] - mx) * inv;
+        for (int j = 0; j < p.topk; ++j) {
+          float best = -1.f;
+          int bi = 0;
+          for (int x = 0; x < E; ++x) {
+            const float v = exch[x * p.exch_stride + e];
+            if (v > best) { best = v; bi = x; }
+          }
+          exch[bi * p.exch_stride + e] = -best;
+        }
+        for (int x = 0; x < E; ++x) {
+          const float v = exch[x * p.exch_stride + e];
+          exch[x * p.exch_stride + e] = (act && v < 0.f) ? -v : 0.f;
+        }
+      }
+      named_bar(kBarEpi, 128);
+      int* slot_of = reinterpret_cast<int*>(c.smem + Smem::kOffHs);   // [128] (the prologue's scratch, free now)
+      if (e < E) {
+        bool any = false;
+        for (int b = 0; b < B; ++b) any |= exch[e * p.exch_stride + b] > 0.f;
+        slot_of[e] = any ? 1 : 0;
+      }
+      named_bar(kBarEpi, 128);
+      if (e == 0) {
+        int n = 0;
+        for (int x = 0; x < E; ++x) {
+          if (slot_of[x]) { p.moe_elist[n] = x; slot_of[x] = n++; } else slot_of[x] = -1;
+        }
+        *p.moe_ne = n;
+      }
+      named_bar(kBarEpi, 128);
+      if (e < E && slot_of[e] >= 0)
+        for (int b = 0; b < kMaxBatch; ++b) p.moe_w[slot_of[e] * kMaxBatch + b] = b < B ? exch[e * p.exch_stride + b] : 0.f;
+      break;
+    }
+    case kEUpGate: {
+      // fused_routed_expert_upgate (operations.py:197-219): gate and up rounded to bf16 (a bf16 linear), SiLU(gate) * up
+      // in fp32, one rounding.  Tile rows 0..63 are gate rows, 64..127 the up rows of the same units of one expert.
+      const int per = p.Ie / kBlockK;
+      const int slot = t / per, lt = t % per;
+      const int u = e & 63, half = e >> 6;
+      const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
+      for (int b = b0; b < b1 && b < B; ++b) {
+        const float g = bf16_round(exch[u * p.exch_stride + b]), up = bf16_round(exch[(64 + u) * p.exch_stride + b]);
+        const float v = act_s[b] ? (g / (1.0f + __expf(-g))) * up : 0.f;
+        p.esilu[((size_t)slot * kMaxBatch + b) * p.Ie + lt * (kTileRows / 2) + u] = f32_to_bf16_bits(v);
+      }
+      break;
+    }
     case kOproj:
+    case kEDown:
     case kDown: {
       // hidden[b, row] = bf16(hidden + bf16(projection)), zero projection for inactive rows
       // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295).
@@ -624,8 +737,15 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
   // e: thread index in the epilogue group; the warp's lane quarter of tensor memory is (warp % 4)
   const BParams& p = *c.p;
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
-  const PhaseDims d = phase_dims(p, kind);
+  int ne = 0;
+  if (is_expert_kind(kind)) {
+    if (e == 0) c.ctl[kCNeEpi] = (unsigned)expert_count(c, ph);
+    named_bar(kBarEpi, 128);
+    ne = (int)c.ctl[kCNeEpi];
+  }
+  const PhaseDims d = phase_dims(p, kind, ne);
   const int U = d.T * d.KB;
+  if (U == 0) return;
   int lo, hi;
   unit_range(U, G, cta, lo, hi);
   float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
@@ -913,7 +1033,7 @@ __device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
   }
   named_bar(kBarAttn, 256);
   if (c.ctl[kCFlagAttn] != 0u) {
-    const int layer = ph / 5, gq = p.NH / p.NKV;
+    const int layer = phase_layer(p, ph), gq = p.NH / p.NKV;
     if (p.HD == 64) {
       if (gq == 4) attention_items<64, 4>(c, layer, aw);
       else if (gq == 2) attention_items<64, 2>(c, layer, aw);
@@ -966,7 +1086,7 @@ __device__ __forceinline__ void prologue(const Ctx& c, int e) {
 __device__ __forceinline__ void finalize(const Ctx& c, int e) {
   // CTA 0, after every CTA has finished the LM head: tokens out
   const BParams& p = *c.p;
-  const int lm = 5 * p.num_layers;
+  const int lm = p.ppl * p.num_layers;
   if (e == 0) c.ctl[kCFlagEpi] = counter_wait(c, p.phase_done + 1 + lm, gridDim.x, lm) ? 1u : 0u;
   named_bar(kBarEpi, 128);
   if (c.ctl[kCFlagEpi] != 0u && e < p.B) {
@@ -1047,7 +1167,7 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
     if (epi && p.prologue != 0) prologue(c, gi);
 #pragma unroll 1
     for (int ph = p.phase_begin; ph < p.phase_end; ++ph) {
-      const int kind = phase_kind(ph, p.num_layers);
+      const int kind = phase_kind(p, ph);
       if (kind == kAttn) {
         attention_phase(c, ph, c.warp - kEpiWarp0);
       } else if (epi) {
@@ -1063,7 +1183,7 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
         stage_phase(c, ph, kind, gi, n);
       }
     }
-    if (epi && blockIdx.x == 0 && p.phase_end == num_phases(p.num_layers)) finalize(c, gi);
+    if (epi && blockIdx.x == 0 && p.phase_end == num_phases(p)) finalize(c, gi);
   }
   __syncwarp();
   tmem_fence_before_sync();

@@ -14,8 +14,10 @@ constexpr int kTileRows = 128;         // weight rows per tile (M of the tensor-
 constexpr int kBlockK = 64;            // bf16 elements per k-block: 128 bytes, one swizzle row
 constexpr int kMaxSplits = 64;         // split-KV partials per (sequence, kv head)
 
-// Phase kinds inside a layer; phase index = layer * 5 + kind, the LM head is phase 5 * L.
-enum Kind : int { kQkv = 0, kAttn = 1, kOproj = 2, kUpGate = 3, kDown = 4, kLmHead = 5 };
+// Phase kinds inside a layer; phase index = layer * ppl + position in the layer (ppl = 5, MoE: 6), the LM head is last.
+enum Kind : int { kQkv = 0, kAttn = 1, kOproj = 2, kUpGate = 3, kDown = 4, kLmHead = 5,
+                  // MoE layers (six phases: QKV, attention, O-proj, router, expert up/gate, expert down)
+                  kRouter = 6, kEUpGate = 7, kEDown = 8 };
 
 struct BParams {
   // ---- weights that are read with plain loads (the matrices come through tensor maps) ----
@@ -51,9 +53,16 @@ struct BParams {
   unsigned long long* argmax_key;   // [B]  (ordered logit bits << 32) | ~row
   unsigned* phase_done;          // [1 + phases]  CTAs that finished the prologue / each phase (zeroed per launch)
   unsigned* status;              // [8]
+  // MoE (null / 0 otherwise): what the router phase leaves for the two expert phases of its layer
+  int* moe_ne;                   // [1]  distinct experts selected by the active rows of this step
+  int* moe_elist;                // [E]  their indices, ascending
+  float* moe_w;                  // [E, kMaxBatch]  router weight of (slot, row), 0 where the row did not select it
+  uint16_t* esilu;               // [E, kMaxBatch, Ie]  SiLU(gate) * up of (slot, row), bf16
   unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off
   // ---- shape ----
   int H, I, NH, NKV, HD, QKV_ROWS, QDIM, num_layers, vocab;
+  int E, topk, Ie;               // MoE: experts, experts per token, expert intermediate size (E = 0: dense model)
+  int ppl;                       // phases per layer: 5 (dense) or 6 (MoE)
   int B, Bpad;                   // sequences, padded to a multiple of 16
   int pos;                       // position of every row when position_ids is null
   int phase_begin, phase_end;

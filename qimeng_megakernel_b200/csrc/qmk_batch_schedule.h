@@ -23,15 +23,28 @@ struct PhaseDims {
   int KB;       // k-blocks
   int rows;     // output rows (units) per tile
 };
-QMKB_HD int phase_kind(int ph, int L) { return ph >= 5 * L ? (int)kLmHead : ph % 5; }
-QMKB_HD int num_phases(int L) { return 5 * L + 1; }
-QMKB_HD PhaseDims phase_dims(const BParams& p, int kind) {
+QMKB_HD int phase_kind(const BParams& p, int ph) {
+  if (ph >= p.ppl * p.num_layers) return (int)kLmHead;
+  const int i = ph % p.ppl;
+  if (p.ppl == 6 && i >= 3) return i == 3 ? (int)kRouter : (i == 4 ? (int)kEUpGate : (int)kEDown);
+  return i;
+}
+QMKB_HD int phase_layer(const BParams& p, int ph) { return ph >= p.ppl * p.num_layers ? 0 : ph / p.ppl; }
+QMKB_HD int num_phases(const BParams& p) { return p.ppl * p.num_layers + 1; }
+QMKB_HD bool phase_normed(int kind) {
+  return kind == kQkv || kind == kUpGate || kind == kLmHead || kind == kRouter || kind == kEUpGate;
+}
+// ne: number of distinct experts selected in this step (expert phases only; known once the layer's router is done)
+QMKB_HD PhaseDims phase_dims(const BParams& p, int kind, int ne = 0) {
   PhaseDims d;
   switch (kind) {
     case kQkv: d.N = p.QKV_ROWS; d.K = p.H; d.rows = kTileRows; break;
     case kOproj: d.N = p.H; d.K = p.QDIM; d.rows = kTileRows; break;
     case kUpGate: d.N = p.I; d.K = p.H; d.rows = kTileRows / 2; break;   // 64 up rows + the 64 gate rows of the same units
     case kDown: d.N = p.H; d.K = p.I; d.rows = kTileRows; break;
+    case kRouter: d.N = p.E; d.K = p.H; d.rows = kTileRows; break;       // one tile (E <= 128)
+    case kEUpGate: d.N = ne * p.Ie; d.K = p.H; d.rows = kTileRows / 2; break;   // 64 gate rows + 64 up rows of one expert
+    case kEDown: d.N = p.H; d.K = ne * p.Ie; d.rows = kTileRows; break;  // one GEMM over the k-blocks of all selected experts
     default: d.N = p.vocab; d.K = p.H; d.rows = kTileRows; break;
   }
   d.T = (d.N + d.rows - 1) / d.rows;

@@ -25,7 +25,8 @@ _WEIGHT_FIELDS = (("attn_norm", "attn_norm_weights"), ("qkv", "qkv_weights"), ("
                   ("gate_proj", "gate_proj_weights"), ("down_proj", "down_proj_weights"),
                   ("lm_head_norm", "lm_head_norm_weights"), ("lm_head", "lm_head_weights"),
                   ("embed_tokens", "embed_tokens"), ("rope_cos", "rope_cos"), ("rope_sin", "rope_sin"),
-                  ("q_norm", "q_norm_weights"), ("k_norm", "k_norm_weights"))
+                  ("q_norm", "q_norm_weights"), ("k_norm", "k_norm_weights"), ("router", "router_weights"),
+                  ("expert_gate_up", "expert_gate_up_proj_weights"), ("expert_down", "expert_down_proj_weights"))
 _STATE_FIELDS = ("hidden_states", "q_post_rope", "k_cache", "v_cache", "attn_out", "silu_out", "logits",
                  "next_token", "token_in", "out_tokens", "position_ids", "active_mask")
 
@@ -80,9 +81,15 @@ class MegaKernel:
         _check_tensor("qkv_weights", g.qkv_weights, bf, (L, (NH + 2 * NKV) * HD, H))
         _check_tensor("o_proj_weights", g.o_proj_weights, bf, (L, H, NH * HD))
         _check_tensor("mlp_norm_weights", g.mlp_norm_weights, bf, (L, H))
-        _check_tensor("up_proj_weights", g.up_proj_weights, bf, (L, I, H))
-        _check_tensor("gate_proj_weights", g.gate_proj_weights, bf, (L, I, H))
-        _check_tensor("down_proj_weights", g.down_proj_weights, bf, (L, H, I))
+        if cfg.num_experts:
+            E, Ie = cfg.num_experts, cfg.moe_intermediate_size
+            _check_tensor("router_weights", g.router_weights, bf, (L, E, H))
+            _check_tensor("expert_gate_up_proj_weights", g.expert_gate_up_proj_weights, bf, (L, E, 2 * Ie, H))
+            _check_tensor("expert_down_proj_weights", g.expert_down_proj_weights, bf, (L, E, H, Ie))
+        else:
+            _check_tensor("up_proj_weights", g.up_proj_weights, bf, (L, I, H))
+            _check_tensor("gate_proj_weights", g.gate_proj_weights, bf, (L, I, H))
+            _check_tensor("down_proj_weights", g.down_proj_weights, bf, (L, H, I))
         _check_tensor("lm_head_norm_weights", g.lm_head_norm_weights, bf, (H,))
         _check_tensor("lm_head_weights", g.lm_head_weights, bf, (V, H))
         if g.embed_tokens is not None:
@@ -138,11 +145,13 @@ class MegaKernel:
         if wkey != self._weights_key:
             self.close()
             cfg = LlamaConfig
-            desc = _lib.ModelDesc(_lib.ABI_VERSION, _lib.ARCH_QWEN3 if cfg.qk_norm else _lib.ARCH_LLAMA,
+            arch = _lib.ARCH_MOE if cfg.num_experts else (_lib.ARCH_QWEN3 if cfg.qk_norm else _lib.ARCH_LLAMA)
+            desc = _lib.ModelDesc(_lib.ABI_VERSION, arch,
                                   cfg.num_hidden_layers, cfg.hidden_size,
                                   cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads,
                                   cfg.head_dim, cfg.vocab_size, rows, float(cfg.rms_norm_eps),
-                                  1.0 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps))
+                                  1.0 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps), int(cfg.num_experts),
+                                  int(cfg.num_experts_per_tok), int(cfg.moe_intermediate_size))
             w = _lib.WeightPtrs(**{c: _ptr(getattr(g, f, None)) for c, f in _WEIGHT_FIELDS})
             h = C.c_void_p()
             _lib.check(self._lib.qmk_create(C.byref(desc), C.byref(w), dev.index or 0, C.byref(h)))

@@ -26,10 +26,14 @@ class LlamaConfig:
     # Qwen3: per-head RMSNorm on Q and K before RoPE (the reference's Qwen3Config,
     # qimeng_megakernel/models/LLM/qwen/qwen3__0_6b/A100/single_batch/decode_schedule/model_config.py:4-16)
     qk_norm = False
+    # mixture of experts (the reference's QwenMoeConfig fields, qwen1_5_moe_a2_7b/.../model_config.py:20-24); 0 = dense
+    num_experts = 0
+    num_experts_per_tok = 0
+    moe_intermediate_size = 0
 
     _KEYS = ("num_hidden_layers", "hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
              "num_key_value_heads", "vocab_size", "rms_norm_eps", "rope_theta", "rope_scaling",
-             "max_position_embeddings", "qk_norm")
+             "max_position_embeddings", "qk_norm", "num_experts", "num_experts_per_tok", "moe_intermediate_size")
 
     @classmethod
     def update_from_dict(cls, config: dict) -> None:
@@ -51,6 +55,9 @@ class LlamaConfig:
         cls.rope_scaling = tuple(rs) if rs else None
         cls.max_position_embeddings = int(config.get("max_position_embeddings", 8192))
         cls.qk_norm = bool(config.get("qk_norm", False))
+        cls.num_experts = int(config.get("num_experts", 0) or 0)
+        cls.num_experts_per_tok = int(config.get("num_experts_per_tok", 0) or 0)
+        cls.moe_intermediate_size = int(config.get("moe_intermediate_size", 0) or 0)
 
     @classmethod
     def update_from_hf(cls, config) -> None:
@@ -79,5 +86,12 @@ QWEN3_0_6B = dict(num_hidden_layers=28, hidden_size=1024, intermediate_size=3072
                   num_attention_heads=16, num_key_value_heads=8, vocab_size=151936, rms_norm_eps=1e-6,
                   rope_theta=1000000.0, rope_scaling=None, max_position_embeddings=40960, qk_norm=True)
 
+# OLMoE-1B-7B shape (BASELINE configuration 5): MHA 16 x 128, 64 experts, top-8, expert intermediate 1024, no shared expert
+OLMOE_1B_7B = dict(num_hidden_layers=16, hidden_size=2048, intermediate_size=1024, head_dim=128,
+                   num_attention_heads=16, num_key_value_heads=16, vocab_size=50304, rms_norm_eps=1e-5,
+                   rope_theta=10000.0, rope_scaling=None, max_position_embeddings=4096, qk_norm=False,
+                   num_experts=64, num_experts_per_tok=8, moe_intermediate_size=1024)
+
 # The reference keeps one config class per model package; here one runtime descriptor serves every shape.
 Qwen3Config = LlamaConfig
+QwenMoeConfig = LlamaConfig

@@ -17,6 +17,7 @@ WEIGHT_NAMES = ("attn_norm_weights", "qkv_weights", "o_proj_weights", "mlp_norm_
                 "gate_proj_weights", "down_proj_weights", "lm_head_norm_weights", "lm_head_weights",
                 "embed_tokens", "rope_cos", "rope_sin")
 QK_NORM_NAMES = ("q_norm_weights", "k_norm_weights")
+MOE_NAMES = ("router_weights", "expert_gate_up_proj_weights", "expert_down_proj_weights")
 
 
 def make_weights(config: dict, seed: int = 0, device: str | torch.device = "cpu", std: float = 0.02,
@@ -39,16 +40,27 @@ def make_weights(config: dict, seed: int = 0, device: str | torch.device = "cpu"
             flat[i].copy_(torch.randn(flat.shape[1], generator=gen, device=dev, dtype=torch.float32) * std)
         return out
 
+    E, Ie = int(config.get("num_experts", 0) or 0), int(config.get("moe_intermediate_size", 0) or 0)
     w = {
         "qkv_weights": mat(L, (NH + 2 * NKV) * HD, H),
         "o_proj_weights": mat(L, H, NH * HD),
-        "up_proj_weights": mat(L, I, H),
-        "gate_proj_weights": mat(L, I, H),
-        "down_proj_weights": mat(L, H, I),
+    }
+    if E:   # experts instead of the dense MLP; router rows scaled so that its logits are ~ N(0, 1): near-uniform load
+        w["router_weights"] = (mat(L, E, H).float() * (H ** -0.5 / std)).to(torch.bfloat16)
+        w["expert_gate_up_proj_weights"] = mat(L * E, 2 * Ie, H).view(L, E, 2 * Ie, H)
+        w["expert_down_proj_weights"] = mat(L * E, H, Ie).view(L, E, H, Ie)
+        for name in ("up_proj_weights", "gate_proj_weights", "down_proj_weights"):   # placeholders (never read)
+            w[name] = torch.zeros(1, dtype=torch.bfloat16, device=dev)
+    else:
+        w.update({
+            "up_proj_weights": mat(L, I, H),
+            "gate_proj_weights": mat(L, I, H),
+            "down_proj_weights": mat(L, H, I)})
+    w.update({
         "attn_norm_weights": torch.ones(L, H, dtype=torch.bfloat16, device=dev),
         "mlp_norm_weights": torch.ones(L, H, dtype=torch.bfloat16, device=dev),
         "lm_head_norm_weights": torch.ones(H, dtype=torch.bfloat16, device=dev),
-    }
+    })
     lm = torch.empty(V, H, dtype=torch.bfloat16, device=dev)
     rows = 8192
     for r0 in range(0, V, rows):
@@ -92,7 +104,7 @@ def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | tor
                       config["vocab_size"])
     bf = torch.bfloat16
     moved = {}
-    names = WEIGHT_NAMES + tuple(n for n in QK_NORM_NAMES if n in weights)
+    names = WEIGHT_NAMES + tuple(n for n in QK_NORM_NAMES + MOE_NAMES if n in weights)
     for name in names:
         t = weights[name]
         key = t.data_ptr()

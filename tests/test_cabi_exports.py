@@ -59,7 +59,7 @@ def test_missing_library_raises_import_error(tmp_path):
 def test_unsupported_descriptor_is_rejected(lib):
     """Validation that happens before any CUDA call: a descriptor that matches no compiled shape."""
     from qimeng_megakernel_b200 import _lib
-    desc = _lib.ModelDesc(_lib.ABI_VERSION, _lib.ARCH_LLAMA, 2, 1000, 8192, 32, 8, 64, 4096, 128, 1e-5, 0.125, 0.0)
+    desc = _lib.ModelDesc(_lib.ABI_VERSION, _lib.ARCH_LLAMA, 2, 1000, 8192, 32, 8, 64, 4096, 128, 1e-5, 0.125, 0.0, 0, 0, 0)
     w = _lib.WeightPtrs(**{n: 256 for n, _ in _lib.WeightPtrs._fields_})
     h = ctypes.c_void_p()
     # neither kernel takes a hidden size that is not a multiple of 64, a head_dim of 32, or 3 query heads per kv head
