@@ -126,7 +126,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (rank 0, N = 1 only)")
     ap.add_argument("--batch", type=int, default=1, help="sequences per GPU (> 1, or any --model but llama: the batched kernel)")
-    ap.add_argument("--model", default="llama-3.2-1b", choices=["llama-3.2-1b", "qwen3-0.6b"])
+    ap.add_argument("--model", default="llama-3.2-1b", choices=["llama-3.2-1b", "qwen3-0.6b", "olmoe-1b-7b"])
     ap.add_argument("--kernel", default="auto", choices=["auto", "batched"], help="batched: the batched kernel also at batch 1")
     args = ap.parse_args()
     K, W = args.steps, max(3, args.warmup)
@@ -279,8 +279,8 @@ def main_batched(args, K: int, W: int) -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     from qimeng_megakernel_b200 import mk_kernel, synthetic
-    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, QWEN3_0_6B
-    config = dict(LLAMA_3_2_1B if args.model == "llama-3.2-1b" else QWEN3_0_6B)
+    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, OLMOE_1B_7B, QWEN3_0_6B
+    config = dict({"llama-3.2-1b": LLAMA_3_2_1B, "qwen3-0.6b": QWEN3_0_6B, "olmoe-1b-7b": OLMOE_1B_7B}[args.model])
     B = args.batch
     kv_len = PROMPT_LEN + W + K + 1
     if not torch.cuda.is_available():
@@ -381,6 +381,10 @@ def main_batched(args, K: int, W: int) -> None:
                          "kernel": "qmk_batch_kernel (one persistent launch per decode step)"},
             "clocks": clocks, "cpu_baseline": None,
         }
+        if config.get("num_experts"):
+            line["config"]["experts_touched_last_layer_last_step"] = mk.last_expert_count()
+            line["config"]["bytes_note"] = ("algorithmic bytes count min(E, B * k) experts per layer (upper bound of the "
+                                            "distinct experts a step reads)")
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

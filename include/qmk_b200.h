@@ -237,6 +237,10 @@ int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes);
 /* Algorithmic HBM bytes of one decode step at KV length pos_id+1 (weights + KV read + KV write). */
 int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id);
 
+/* QMK_ARCH_MOE: number of distinct experts the last layer's router selected in the last step (synchronises the
+ * stream of the last launch); the bytes of a MoE step depend on it.  0 for other architectures. */
+int qmk_last_expert_count(qmk_handle* h, int32_t* out);
+
 /* Number of kernels the library has launched through this handle. */
 int64_t qmk_launch_count(const qmk_handle* h);
 

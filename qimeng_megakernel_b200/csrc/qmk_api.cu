@@ -503,6 +503,16 @@ extern "C" int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id) {
   return d.num_layers * per_layer + lm + B * (d.num_layers * kv_row * T + d.num_layers * kv_row);
 }
 
+extern "C" int qmk_last_expert_count(qmk_handle* h, int32_t* out) {
+  if (!h || !out) return QMK_ERR_INVALID_ARG;
+  *out = 0;
+  if (!h->bctx || !qmkb_expert_count_ptr(h->bctx)) return QMK_OK;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
+  QMK_CUDA(h, cudaMemcpy(out, qmkb_expert_count_ptr(h->bctx), sizeof(int32_t), cudaMemcpyDeviceToHost));
+  return QMK_OK;
+}
+
 extern "C" int64_t qmk_launch_count(const qmk_handle* h) { return h ? h->launches : 0; }
 
 extern "C" int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes) {

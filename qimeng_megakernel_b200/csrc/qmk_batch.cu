@@ -188,6 +188,7 @@ void qmkb_destroy(qmk_batch_ctx* c) {
 }
 
 unsigned* qmkb_status_ptr(qmk_batch_ctx* c) { return c->status; }
+const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c) { return c->moe_ne; }
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c) { return c->scratch_bytes; }
 
 int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream) {

@@ -33,5 +33,6 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
 // Device status record (8 words) and a full reset of the scratch after a failed launch.
 unsigned* qmkb_status_ptr(qmk_batch_ctx* c);
 int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream);
+const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c);   // device address of the step's distinct-expert count, or null
 void qmkb_geometry(const qmk_batch_ctx* c, int* ctas, int* threads, int* smem_bytes);
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c);

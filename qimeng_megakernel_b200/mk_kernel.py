@@ -249,6 +249,12 @@ class MegaKernel:
     def step_bytes(self, pos: int) -> int:
         return int(self._lib.qmk_step_bytes(self._handle, pos))
 
+    def last_expert_count(self) -> int:
+        """MoE: distinct experts selected by the last layer's router in the last step (synchronises)."""
+        n = C.c_int32()
+        _lib.check(self._lib.qmk_last_expert_count(self._handle, C.byref(n)), self._handle)
+        return n.value
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.qmk_launch_count(self._handle)) if self._handle is not None else 0

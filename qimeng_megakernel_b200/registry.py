@@ -13,14 +13,14 @@ import importlib
 from dataclasses import dataclass
 from typing import Any
 
-from .model_config import LLAMA_3_2_1B, QWEN3_0_6B
+from .model_config import LLAMA_3_2_1B, OLMOE_1B_7B, QWEN3_0_6B
 
 HARDWARE_CHOICES = ("auto", "B200")
 # architectures with a kernel (the batch-1 kernel's compiled shape, or the batched kernel's runtime shapes): model key -> config
-MODELS = {"llama-3.2-1b": LLAMA_3_2_1B, "qwen3-0.6b": QWEN3_0_6B}
+MODELS = {"llama-3.2-1b": LLAMA_3_2_1B, "qwen3-0.6b": QWEN3_0_6B, "olmoe-1b-7b": OLMOE_1B_7B}
 _ALIASES = {"meta-llama/llama-3.2-1b": "llama-3.2-1b", "meta-llama/llama-3.2-1b-instruct": "llama-3.2-1b",
             "llama3_2__1b": "llama-3.2-1b", "synthetic-llama-3.2-1b": "llama-3.2-1b",
-            "qwen/qwen3-0.6b": "qwen3-0.6b", "qwen3__0_6b": "qwen3-0.6b", "synthetic-qwen3-0.6b": "qwen3-0.6b"}
+            "qwen/qwen3-0.6b": "qwen3-0.6b", "allenai/olmoe-1b-7b-0924": "olmoe-1b-7b", "synthetic-olmoe-1b-7b": "olmoe-1b-7b", "qwen3__0_6b": "qwen3-0.6b", "synthetic-qwen3-0.6b": "qwen3-0.6b"}
 # sequences per GPU in one launch (the reference stops at 16, registry.py:212; more sequences shard over GPUs)
 MAX_BATCH = 64
 
