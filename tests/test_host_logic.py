@@ -38,6 +38,8 @@ def test_registry():
     assert sched.config.hidden_size == 2048
     assert R.decode_schedule_package_name("llama-3.2-1b", "B200", batch_size=64) == "qimeng_megakernel_b200"
     assert R.decode_schedule_package_name("Qwen/Qwen3-0.6B", "B200", batch_size=16) == "qimeng_megakernel_b200"
+    assert R.decode_schedule_package_name("allenai/OLMoE-1B-7B-0924", "B200", batch_size=32) == "qimeng_megakernel_b200"
+    assert R.MODELS["olmoe-1b-7b"]["num_experts"] == 64 and R.MODELS["olmoe-1b-7b"]["num_experts_per_tok"] == 8
     with pytest.raises(NotImplementedError):
         R.decode_schedule_package_name("llama-3.2-1b", "B200", batch_size=65)
     with pytest.raises(NotImplementedError):
