@@ -212,8 +212,18 @@ static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* c
   if (c.ctl[kCAbort] != 0u) return false;
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {
-    const unsigned v = ld_acquire_gpu(counter);
-    if (v >= target) return true;
+    // Polled with relaxed loads, one acquire load at the end: acquire loads in a tight loop from
+    // three threads of a CTA slowed the warps of the same SM that were still working (the router's epilogue took 60 us
+    // with them, 20 us without).
+#ifdef QMK_POLL_ACQUIRE
+    unsigned v = ld_acquire_gpu(counter);
+#else
+    unsigned v = ld_relaxed_gpu(counter);
+#endif
+    if (v >= target) {
+      v = ld_acquire_gpu(counter);
+      return true;
+    }
     if ((it & 15u) == 0u) {
       if (c.ctl[kCAbort] != 0u) return false;
       if (clock64() - t0 > c.p->timeout_cycles) {
@@ -252,7 +262,7 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
     const int ne = is_expert_kind(kind) ? expert_count(c, ph) : 0;
     const PhaseDims d = phase_dims(p, kind, ne);
     int lo, hi;
-    unit_range(d.T * d.KB, G, cta, lo, hi);
+    unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, G), cta, lo, hi);
     const CUtensorMap* map = kind == kQkv ? &maps.qkv : kind == kOproj ? &maps.o_proj : kind == kUpGate ? &maps.up
                            : kind == kDown ? &maps.down : kind == kRouter ? &maps.router : &maps.lm_head;
     const int per = p.Ie > 0 ? p.Ie / kBlockK : 1;   // 64-row tiles (k-blocks) of one expert
@@ -306,7 +316,7 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
     if (kind == kAttn) continue;
     const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? expert_count(c, ph) : 0);
     int lo, hi;
-    unit_range(d.T * d.KB, G, cta, lo, hi);
+    unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, G), cta, lo, hi);
     int kb = d.KB > 0 ? lo % d.KB : 0;
     bool seg_start = true;
     long long w_a = 0, w_b = 0, w_acc = 0, w_iss = 0;
@@ -367,7 +377,7 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
 // issued before the first is used, so that a warp pays one L2 round trip per group, not per unit or per piece.
 // 5 * D - 1 must stay below twice the number of ring slots: a warp that got two laps of the ring ahead of the tensor core would take an
 // old completion of a stage's mbarrier (same parity) for the one it waits for.
-template <int NPL, int D>
+template <int NPL, int D, bool EXPERT>
 __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
                                             const uint16_t* src, const uint16_t* gain, const float* rs,
                                             int per = 0, const float* wsc = nullptr) {
@@ -384,7 +394,7 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
   for (int base = lo + sw * D; base < hi; base += 4 * D) {
     uint4 v[D][NPL];
     uint4 g4[D];
-    float sc[D][NPL];
+    float sc[EXPERT ? D : 1][EXPERT ? NPL : 1];
 #pragma unroll
     for (int j = 0; j < D; ++j) {
       const int u = base + j;
@@ -396,12 +406,12 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       for (int i = 0; i < NPL; ++i) {
         const int r = row0 + 4 * i;
         v[j][i] = make_uint4(0, 0, 0, 0);
-        sc[j][i] = 0.f;
+        if (EXPERT) sc[EXPERT ? j : 0][EXPERT ? i : 0] = 0.f;
         if (u < hi && r < p.B) {
-          if (per > 0) {
+          if (EXPERT) {
             const int slot = kbu / per;
             v[j][i] = ldcg_u4(src + ((size_t)slot * kMaxBatch + r) * p.Ie + (kbu % per) * kBlockK + chunk * 8);
-            sc[j][i] = ldcg_f32(wsc + slot * kMaxBatch + r);
+            sc[EXPERT ? j : 0][EXPERT ? i : 0] = ldcg_f32(wsc + slot * kMaxBatch + r);
           } else {
             v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
           }
@@ -433,10 +443,11 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
             const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
             w[q] = pack_bf16x2(a, b);
           }
-        } else if (per > 0) {
+        } else if (EXPERT) {
           uint32_t* w = reinterpret_cast<uint32_t*>(&v[j][i]);
+          const float f = sc[EXPERT ? j : 0][EXPERT ? i : 0];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf_lo(w[q]) * sc[j][i], bf_hi(w[q]) * sc[j][i]);
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf_lo(w[q]) * f, bf_hi(w[q]) * f);
         }
         *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[j][i];
       }
@@ -465,7 +476,7 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   named_bar(kBarStg, 128);
   const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? (int)c.ctl[kCNeStg] : 0);
   int lo, hi;
-  unit_range(d.T * d.KB, (int)gridDim.x, (int)blockIdx.x, lo, hi);
+  unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, (int)gridDim.x), (int)blockIdx.x, lo, hi);
   const bool normed = phase_normed(kind);
   float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
   if (normed) {
@@ -483,11 +494,21 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   const int per = kind == kEDown ? p.Ie / kBlockK : 0;
   const float* wsc = kind == kEDown ? p.moe_w : nullptr;
   if (hi > lo) {
-    switch (p.Bpad) {
-      case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
-      case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
-      case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
-      default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, normed ? gain : nullptr, rs, per, wsc); break;
+    const uint16_t* gn = normed ? gain : nullptr;
+    if (kind == kEDown) {
+      switch (p.Bpad) {
+        case 16: stage_units<4, 2, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+        case 32: stage_units<8, 2, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+        case 48: stage_units<12, 1, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+        default: stage_units<16, 1, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+      }
+    } else {
+      switch (p.Bpad) {
+        case 16: stage_units<4, 2, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        case 32: stage_units<8, 2, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        case 48: stage_units<12, 1, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        default: stage_units<16, 1, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+      }
     }
   }
   n += (unsigned)(hi - lo);
@@ -593,29 +614,43 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       // overwritten by row b's selection (probability, 0 elsewhere); then the distinct experts of the step are listed
       // in ascending order and every (selected expert, row) gets its weight for the expert down-projection.
       const int E = p.E;
-      if (e < p.Bpad) {
-        const bool act = e < B && act_s[e] != 0;
-        float mx = -INFINITY;
-        for (int x = 0; x < E; ++x) mx = fmaxf(mx, exch[x * p.exch_stride + e]);
-        float sum = 0.f;
-        for (int x = 0; x < E; ++x) sum += __expf(exch[x * p.exch_stride + e] - mx);
-        const float inv = 1.0f / sum;
-        // mark the k largest by negating them in place (probabilities are positive), then clean up
-        for (int x = 0; x < E; ++x) exch[x * p.exch_stride + e] = __expf(exch[x * p.exch_stride + e] - mx) * inv;
-        for (int j = 0; j < p.topk; ++j) {
-          float best = -1.f;
-          int bi = 0;
-          for (int x = 0; x < E; ++x) {
-            const float v = exch[x * p.exch_stride + e];
-            if (v > best) { best = v; bi = x; }
-          }
-          exch[bi * p.exch_stride + e] = -best;
-        }
-        for (int x = 0; x < E; ++x) {
-          const float v = exch[x * p.exch_stride + e];
-          exch[x * p.exch_stride + e] = (act && v < 0.f) ? -v : 0.f;
-        }
+      // tpr consecutive lanes share a row: each takes the experts x = q, q + tpr, ...; maxima, sums and the k winners
+      // are combined with shuffles.  A winner is marked by negating its (positive) exponential in place.
+      const int tpr = p.Bpad <= 16 ? 8 : (p.Bpad <= 32 ? 4 : 2);
+      const int b = e / tpr, q = e % tpr;
+      const bool rowok = b < p.Bpad;
+      const int bb = rowok ? b : 0;
+      const bool act = b < B && act_s[bb] != 0;
+      float mx = -INFINITY;
+      for (int x = q; x < E; x += tpr) mx = fmaxf(mx, exch[x * p.exch_stride + bb]);
+      for (int o = 1; o < tpr; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
+      float sum = 0.f;
+      for (int x = q; x < E; x += tpr) {
+        const float pe = __expf(exch[x * p.exch_stride + bb] - mx);
+        if (rowok) exch[x * p.exch_stride + bb] = pe;
+        sum += pe;
       }
+      for (int o = 1; o < tpr; o <<= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
+      const float inv = 1.0f / sum;
+      for (int j = 0; j < p.topk; ++j) {
+        float best = -1.f;
+        int bi = E;
+        for (int x = q; x < E; x += tpr) {
+          const float v = rowok ? exch[x * p.exch_stride + bb] : 0.f;
+          if (v > best) { best = v; bi = x; }
+        }
+        for (int o = 1; o < tpr; o <<= 1) {
+          const float ob = __shfl_xor_sync(kFullMask, best, o);
+          const int oi = __shfl_xor_sync(kFullMask, bi, o);
+          if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (rowok && bi < E && bi % tpr == q) exch[bi * p.exch_stride + bb] = -best;
+      }
+      if (rowok)
+        for (int x = q; x < E; x += tpr) {
+          const float v = exch[x * p.exch_stride + bb];
+          exch[x * p.exch_stride + bb] = (act && v < 0.f) ? -v * inv : 0.f;
+        }
       named_bar(kBarEpi, 128);
       int* slot_of = reinterpret_cast<int*>(c.smem + Smem::kOffHs);   // [128] (the prologue's scratch, free now)
       if (e < E) {
@@ -736,7 +771,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
 __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, uint32_t tmem, int e, unsigned& sg) {
   // e: thread index in the epilogue group; the warp's lane quarter of tensor memory is (warp % 4)
   const BParams& p = *c.p;
-  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int cta = (int)blockIdx.x;
   int ne = 0;
   if (is_expert_kind(kind)) {
     if (e == 0) c.ctl[kCNeEpi] = (unsigned)expert_count(c, ph);
@@ -746,6 +781,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
   const PhaseDims d = phase_dims(p, kind, ne);
   const int U = d.T * d.KB;
   if (U == 0) return;
+  const int G = phase_ctas(kind, U, (int)gridDim.x);   // CTAs that share this phase's units
   int lo, hi;
   unit_range(U, G, cta, lo, hi);
   float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);

@@ -51,8 +51,17 @@ QMKB_HD PhaseDims phase_dims(const BParams& p, int kind, int ne = 0) {
   d.KB = d.K / kBlockK;
   return d;
 }
-// Units [lo, hi) of CTA c out of G, for U units.
+// CTAs that share a phase's units: all of them, except for the router's single tile, whose 256 KB are not worth 32
+// partial tiles added onto one accumulator (each CTA then takes at least eight units).
+QMKB_HD int phase_ctas(int kind, int U, int G) {
+  if (kind != kRouter) return G;
+  const int g = U / 8;
+  return g < 1 ? 1 : (g < G ? g : G);
+}
+
+// Units [lo, hi) of CTA c out of G, for U units (none for c >= G).
 QMKB_HD void unit_range(int U, int G, int c, int& lo, int& hi) {
+  if (c >= G) { lo = hi = 0; return; }
   lo = (int)(((long long)c * U) / G);
   hi = (int)(((long long)(c + 1) * U) / G);
 }
