@@ -483,7 +483,13 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
     if (st < p.Bpad) {
       float tot = 0.f;
       const int nt = (p.H + kTileRows - 1) / kTileRows;
-      for (int t = 0; t < nt; ++t) tot += ldcg_f32(p.ss + t * kMaxBatch + st);
+      for (int t0 = 0; t0 < nt; t0 += 16) {   // sixteen partial sums per round trip, added in tile order
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = t0 + j < nt ? ldcg_f32(p.ss + (t0 + j) * kMaxBatch + st) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) tot += v[j];
+      }
       rs[st] = rsqrtf(tot / (float)p.H + p.eps);
     }
     named_bar(kBarStg, 128);
