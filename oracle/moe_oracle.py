@@ -10,10 +10,10 @@ Only tests/ may import this module.  It restates, in plain PyTorch on the CPU, t
       fused_moe_block                243-268   shared + routed, sigmoid gate on the shared branch, residual adds
 The attention half of that model is the dense path already restated in oracle/fused_oracle.py (MHA, head_dim 128).
 
-No CUDA kernel of this repository implements the MoE block yet: this module and its fixture
-(tests/golden/moe_block.npz, made by tests/golden/make_golden.py from the real reference) are the parity target
-the kernel will be held to.  Parity pin: tests/test_oracle_golden.py::test_moe_block checks this restatement
-against the fixture bit for bit.
+Parity pin: tests/test_oracle_golden.py::test_moe_block checks this restatement bit for bit against the fixture
+tests/golden/moe_block.npz, which tests/golden/make_golden.py made from the real reference.  The batched CUDA
+kernel's MoE phases (router, expert up/gate, expert down-projection) are held to this module by
+tests/test_gpu_moe.py; the kernel has no shared expert, so that test gives the shared branch zero weights.
 """
 from __future__ import annotations
 

@@ -185,3 +185,25 @@ def test_batched_globals_shapes():
     from qimeng_megakernel_b200 import mk_kernel
     with pytest.raises(ValueError):        # CPU tensors are refused: there is no CPU path
         mk_kernel.MegaKernel.__new__(mk_kernel.MegaKernel)._validate(g)
+
+
+def test_moe_synthetic_model_and_config():
+    """Mixture-of-experts descriptors: config fields, the layouts of the reference's MoE Globals, router rows scaled so
+    that the logits of a unit-RMS input have unit variance (near-uniform expert load), no dense MLP weights."""
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.model_config import LlamaConfig, OLMOE_1B_7B
+    cfg = dict(OLMOE_1B_7B, num_hidden_layers=1, hidden_size=256, num_attention_heads=2, num_key_value_heads=2,
+               vocab_size=64, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, max_position_embeddings=32)
+    w = synthetic.make_weights(cfg, seed=5, device="cpu", max_positions=32)
+    assert w["router_weights"].shape == (1, 16, 256)
+    assert w["expert_gate_up_proj_weights"].shape == (1, 16, 256, 256) and w["expert_down_proj_weights"].shape == (1, 16, 256, 128)
+    assert w["up_proj_weights"].numel() == 1                      # placeholder: a MoE layer has no dense MLP
+    x = torch.randn(4096, 256)
+    x = x / x.pow(2).mean(-1, keepdim=True).sqrt()
+    logits = x @ w["router_weights"][0].float().t()
+    assert 0.8 < float(logits.std()) < 1.2
+    g = synthetic.make_globals(cfg, w, kv_seq_len=8, device="cpu", batch=2)
+    assert g.router_weights is not None and g.expert_down_proj_weights.shape == (1, 16, 256, 128)
+    assert LlamaConfig.num_experts == 16 and LlamaConfig.num_experts_per_tok == 4 and LlamaConfig.moe_intermediate_size == 128
+    LlamaConfig.update_from_dict(dict(cfg, num_experts=0, num_experts_per_tok=0, moe_intermediate_size=0))
+    assert LlamaConfig.num_experts == 0
