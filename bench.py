@@ -128,6 +128,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1, help="sequences per GPU (> 1, or any --model but llama: the batched kernel)")
     ap.add_argument("--model", default="llama-3.2-1b", choices=["llama-3.2-1b", "qwen3-0.6b", "olmoe-1b-7b"])
     ap.add_argument("--kernel", default="auto", choices=["auto", "batched"], help="batched: the batched kernel also at batch 1")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="batched runs only: keep this many decoder layers (a small case for a profiler capture; the line says so)")
     args = ap.parse_args()
     K, W = args.steps, max(3, args.warmup)
     if args.batch != 1 or args.model != "llama-3.2-1b" or args.kernel == "batched":
@@ -281,6 +283,8 @@ def main_batched(args, K: int, W: int) -> None:
     from qimeng_megakernel_b200 import mk_kernel, synthetic
     from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, OLMOE_1B_7B, QWEN3_0_6B
     config = dict({"llama-3.2-1b": LLAMA_3_2_1B, "qwen3-0.6b": QWEN3_0_6B, "olmoe-1b-7b": OLMOE_1B_7B}[args.model])
+    if args.layers > 0:
+        config["num_hidden_layers"] = min(args.layers, config["num_hidden_layers"])
     B = args.batch
     kv_len = PROMPT_LEN + W + K + 1
     if not torch.cuda.is_available():
@@ -371,6 +375,7 @@ def main_batched(args, K: int, W: int) -> None:
             "config": {"workload": f"{args.model} shape, bf16, {B} independent seeded 16-token prompts per GPU, greedy decode "
                                    "forced past EOS", "decode_steps": K,
                        "kv_lengths": [first_timed_pos + 1, first_timed_pos + K], "sequences_per_gpu": B,
+                       "decoder_layers": config["num_hidden_layers"],
                        "sharding": "sequences sharded over the GPUs, full weight copy each, no collective",
                        "l2": "inputs larger than L2: every step streams the weights through a 126 MB L2",
                        "launch": {"ctas": ctas, "threads": threads, "smem_bytes": smem}},
