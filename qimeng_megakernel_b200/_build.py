@@ -14,7 +14,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB_PATH = CSRC / "libqmk_b200.so"
 SOURCES = ["qmk_api.cu", "qmk_static.cu", "qmk_batch.cu"]
-HEADERS = ["qmk_megakernel.cuh", "qmk_kernel.cuh", "qmk_phases.cuh", "qmk_umma.cuh", "qmk_attention.cuh", "qmk_staging.cuh", "qmk_device.cuh",
+HEADERS = ["qmk_megakernel.cuh", "qmk_kernel.cuh", "qmk_phases.cuh", "qmk_attention.cuh", "qmk_staging.cuh", "qmk_device.cuh",
            "qmk_params.h", "qmk_schedule.h", "qmk_batch_kernel.cuh", "qmk_batch_params.h", "qmk_batch_schedule.h", "qmk_batch_host.h", "../../include/qmk_b200.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
@@ -52,22 +52,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return _compile(LIB_PATH, SOURCES, [], verbose)
 
 
-# The same C ABI with the weight stream multiplied by tcgen05.mma from a CTA-level ring (qmk_umma.cuh)
-# instead of mma.sync from per-warp rings.  Slower at batch 1 (measured), kept as the base of the
-# batched path; tests/test_gpu_umma_path.py holds it to the same parity bar.
-UMMA_DIR = CSRC / "umma"
-UMMA_LIB_PATH = UMMA_DIR / "libqmk_b200.so"
-
-
-def build_umma(force: bool = False, verbose: bool = False) -> Path:
-    UMMA_DIR.mkdir(exist_ok=True)
-    if not force and UMMA_LIB_PATH.exists():
-        t = UMMA_LIB_PATH.stat().st_mtime
-        if not any((CSRC / f).resolve().stat().st_mtime > t for f in SOURCES + HEADERS):
-            return UMMA_LIB_PATH
-    return _compile(UMMA_LIB_PATH, SOURCES, ["-DQMK_UMMA=1"], verbose)
-
-
 if __name__ == "__main__":
     print(build(force=True, verbose=True))
-    print(build_umma(force=True))

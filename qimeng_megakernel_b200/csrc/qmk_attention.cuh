@@ -61,7 +61,7 @@ __device__ __forceinline__ bool stage_attn_part(Worker<S>& s, const Params& p, u
       }
       if (__all_sync(kFullMask, ok)) break;
       if ((it & 15u) == 15u && poll_give_up(p, t0, ok, vq[0].x >> 16, tag, warp, ph, lane)) return false;
-      poll_pause(it);   // (no tile parking here: a compute warp already holds its K / V block in registers)
+      // (no tile parking here: a compute warp already holds its K / V block in registers)
     }
 #pragma unroll
     for (int j = 0; j < NQ; ++j)
@@ -289,7 +289,6 @@ __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph
         s.aborted = true;
         return;
       }
-      poll_pause(it);
     }
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
@@ -315,7 +314,6 @@ __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph
     *reinterpret_cast<uint32_t*>(p.attn_out + e + d) = w;
     if (p.sync) st_handoff(p.t_attn + e + d, make_uint2((w & 0xffffu) | tagw, (w >> 16) | tagw));
   }
-  flush_handoff();
 }
 
 // ---- phase 1: attention.  CTA c < NKV * Pc computes CTA-part (kv head c / Pc, part c % Pc): warp w takes
@@ -405,7 +403,6 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
       if (d == 0) st_handoff(reinterpret_cast<uint4*>(rec + HD), make_uint4(__float_as_uint(M), rtag, __float_as_uint(den), rtag));
     }
   }
-  flush_handoff();
   if (s.w == 0) {
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
     trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);

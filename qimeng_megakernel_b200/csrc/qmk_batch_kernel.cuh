@@ -215,11 +215,7 @@ static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* c
     // Polled with relaxed loads, one acquire load at the end: acquire loads in a tight loop from
     // three threads of a CTA slowed the warps of the same SM that were still working (the router's epilogue took 60 us
     // with them, 20 us without).
-#ifdef QMK_POLL_ACQUIRE
-    unsigned v = ld_acquire_gpu(counter);
-#else
     unsigned v = ld_relaxed_gpu(counter);
-#endif
     if (v >= target) {
       v = ld_acquire_gpu(counter);
       return true;

@@ -52,11 +52,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       : "memory");
 }
 
-// Pull a contiguous range into L2 without a destination (16-byte aligned, size a multiple of 16).
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-
 // ---- tensor memory (TMEM), used here as a per-warp parking space for weight tiles ----
 // One warp allocates all 512 columns for the CTA (one CTA per SM, so the allocation cannot block) and
 // publishes the base address through shared memory; the same warp frees them before the CTA exits.
@@ -140,11 +135,7 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 // store lingers on the SM behind the warp's polling loads until something flushes it.  Measured on B200 (step at KV
 // 33 / 201 / 1040): plain stores 695 us; plain stores followed by a __threadfence() that nothing waits for
 // 565 / 570 / 580 us; exchanges without any fence 495 / 519 / 543 us.  (st.relaxed.gpu, st.cg, system-scope or
-// doubled fences, pauses: all equal to or worse than the plain store + fence.)  QMK_ST_MODE 0 = plain stores,
-// QMK_FENCE 1 = fence after a phase's stores; the pair (0, 1) is the older scheme.
-#ifndef QMK_ST_MODE
-#define QMK_ST_MODE 3
-#endif
+// doubled fences, pauses: all equal to or worse than the plain store + fence.)
 __device__ __forceinline__ void exch_drop_u32(void* p, uint32_t v) {
   unsigned old;
   asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
@@ -156,36 +147,11 @@ __device__ __forceinline__ void exch_drop_u64(void* p, uint32_t lo, uint32_t hi)
                : "l"(p), "l"((unsigned long long)lo | ((unsigned long long)hi << 32))
                : "memory");
 }
-__device__ __forceinline__ void st_handoff(uint32_t* p, uint32_t v) {
-#if QMK_ST_MODE == 3
-  exch_drop_u32(p, v);
-#else
-  *p = v;
-#endif
-}
-__device__ __forceinline__ void st_handoff(uint32_t* p, uint2 v) {
-#if QMK_ST_MODE == 3
-  exch_drop_u64(p, v.x, v.y);
-#else
-  *reinterpret_cast<uint2*>(p) = v;
-#endif
-}
+__device__ __forceinline__ void st_handoff(uint32_t* p, uint32_t v) { exch_drop_u32(p, v); }
+__device__ __forceinline__ void st_handoff(uint32_t* p, uint2 v) { exch_drop_u64(p, v.x, v.y); }
 __device__ __forceinline__ void st_handoff(void* p, uint4 v) {
-#if QMK_ST_MODE == 3
   exch_drop_u64(p, v.x, v.y);
   exch_drop_u64(reinterpret_cast<unsigned char*>(p) + 8, v.z, v.w);
-#else
-  *reinterpret_cast<uint4*>(p) = v;
-#endif
-}
-#ifndef QMK_FENCE
-#define QMK_FENCE 0
-#endif
-// Push this warp's plain hand-off stores out (nothing waits for it); not needed with exchanges.
-__device__ __forceinline__ void flush_handoff() {
-#if QMK_FENCE == 1
-  __threadfence();
-#endif
 }
 
 // ---- L2-coherent loads (activations written by other SMs inside the same launch) ----

@@ -27,32 +27,8 @@
 
 namespace qmk {
 
-// 1: weights are multiplied by tcgen05.mma from a CTA-level ring (qmk_umma.cuh);
-// 0: by mma.sync from per-warp rings (qmk_phases.cuh).
-#ifndef QMK_UMMA
-#define QMK_UMMA 0
-#endif
-#if QMK_UMMA && !defined(QMK_TMEM_SLOTS)
-#define QMK_TMEM_SLOTS 0   // tensor memory holds the accumulators there, nothing is parked
-#endif
-#ifndef QMK_WORKERS
-#define QMK_WORKERS 8
-#endif
-#ifndef QMK_SLOTS
-#if QMK_UMMA
-#define QMK_SLOTS 3   // (sizes the ring region: three 64-KiB group slots there)
-#else
-#define QMK_SLOTS 2
-#endif
-#endif
-#ifndef QMK_KV_STAGE
-#define QMK_KV_STAGE 1
-#endif
-#ifndef QMK_KV_EARLY
-#define QMK_KV_EARLY 1   // copy the next layer's first K/V block from the up/gate phase already (else: from its own QKV phase)
-#endif
-constexpr int kWorkers = QMK_WORKERS;  // warps per CTA (all of them stream weights)
-constexpr int kSlots = QMK_SLOTS;      // ring slots (8 KiB tiles) per warp
+constexpr int kWorkers = 8;            // warps per CTA (all of them stream weights)
+constexpr int kSlots = 2;              // ring slots (8 KiB tiles) per warp (a third slot made every hand-off slower)
 constexpr int kThreads = kWorkers * 32;
 constexpr unsigned kAbortFlag = 0xffffffffu;
 
@@ -64,10 +40,9 @@ struct SmemLayout {
   static constexpr int kActBigA = S::I * 2;                                   // silu_out (bf16)
   static constexpr int kActBigB = S::QDIM * 4 + 2 * S::NKV * S::HD * 2;       // q fp32 + new K/V rows bf16
   static constexpr int kActBig = kActBigA > kActBigB ? kActBigA : kActBigB;
-  // first attention block of every warp (K and V rows of 32 keys, 8 KiB), copied in while the QKV phase runs;
-  // only when the rings leave room for it (two slots per warp)
-  static constexpr bool kKvStage = QMK_KV_STAGE && !QMK_UMMA && kSlots <= 2;
-  static constexpr int kKvStageBytes = kKvStage ? kWorkers * 16 * 512 : 0;
+  // first attention block of every warp (K and V rows of 32 keys, 8 KiB), copied in ahead of the attention phase
+  static constexpr bool kKvStage = true;
+  static constexpr int kKvStageBytes = kWorkers * 16 * 512;
   static constexpr int kOffRing = 0;
   static constexpr int kOffKvStage = kOffRing + kRingBytes;
   static constexpr int kOffActA = kOffKvStage + kKvStageBytes;
@@ -126,10 +101,8 @@ struct Worker {
   unsigned i_slot;         // slot the next issue goes into
   unsigned c_slot, c_par;  // slot and mbarrier parity of the next tile to consume
   TileCursor<S> cur;       // where the weight stream is; also holds this worker's item ranges
-  TileCursor<S> pf;        // the same stream, kL2Ahead tiles further: what is being pulled into L2
   uint32_t tmem;           // tensor-memory address of this warp's parking space (its lane quarter, its column half)
   unsigned t_head, t_count;   // oldest parked tile and number of parked tiles (FIFO, all older than the ring's tiles)
-  unsigned groups_done;       // tcgen05 path: groups of this CTA in the phases before the current one
   StreamBases wb;
   float res;               // residual stream value of row (cur.r0 + lane), bf16-exact
   bool res_valid;
@@ -138,51 +111,21 @@ struct Worker {
   uint64_t policy;
 };
 
-// Optional far look-ahead (off by default).  The shared-memory ring holds 24 KiB per warp; while a warp
-// waits for activations at a phase boundary the ring is full and HBM idles.  With QMK_L2_AHEAD = n the
-// stream is also run n tiles further ahead with cp.async.bulk.prefetch.L2.  Measured on B200: n = 3 changes
-// nothing (592 us per step either way, the up/gate phase does not get shorter), n >= 6 (57 MB ahead) is
-// slower, so the prefetched lines evidently do not survive in L2 until the ring asks for them.
-#ifndef QMK_L2_AHEAD
-#define QMK_L2_AHEAD 0
-#endif
-constexpr int kL2Ahead = QMK_L2_AHEAD;
-
-template <class S>
-__device__ __forceinline__ void prefetch_one(Worker<S>& s, const Params& p) {
-  if (kL2Ahead <= 0 || s.pf.done(p.phase_end)) return;
-  const Tile t = s.pf.next(s.wb, p.num_layers, p.phase_end);
-  if (s.lane == 0) {
-    bulk_prefetch_l2(t.a, t.bytes_a);
-    if (t.b != nullptr) bulk_prefetch_l2(t.b, kChunkBytes);
-  }
-}
-
 // Issue the next tile of the stream into the oldest free slot, if any tile is left: one 8-KiB bulk
 // copy, or two 4-KiB copies completing on the same mbarrier.
 template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
   if (s.aborted || s.cur.done(p.phase_end)) return;
-  Tile t = s.cur.next(s.wb, p.num_layers, p.phase_end);
-#ifdef QMK_PROBE_L2_WINDOW   // measurement only (wrong results): every tile comes from one L2-resident window
-  t.a = s.wb.lm_head + ((size_t)(t.a - (const unsigned char*)nullptr) & (size_t)(QMK_PROBE_L2_WINDOW - 1));
-  if (t.b != nullptr) t.b = s.wb.lm_head + ((size_t)(t.b - (const unsigned char*)nullptr) & (size_t)(QMK_PROBE_L2_WINDOW - 1));
-#endif
+  const Tile t = s.cur.next(s.wb, p.num_layers, p.phase_end);
   if (s.lane == 0) {
     const uint32_t bar = s.bars + s.i_slot * 8;
     const uint32_t dst = s.ring + s.i_slot * (2 * kChunkBytes);
-#ifdef QMK_PROBE_NO_COPY   // measurement only (wrong results): no weight traffic at all, the slot is "there" at once
-    mbar_expect_tx(bar, 0u);
-    (void)dst;
-#else
     mbar_expect_tx(bar, t.bytes_a + (t.b != nullptr ? (uint32_t)kChunkBytes : 0u));
     bulk_g2s(dst, t.a, t.bytes_a, bar, s.policy);
     if (t.b != nullptr) bulk_g2s(dst + kChunkBytes, t.b, kChunkBytes, bar, s.policy);
-#endif
   }
   ++s.n_issued;
   s.i_slot = (s.i_slot + 1 == kSlots) ? 0u : s.i_slot + 1;
-  prefetch_one(s, p);
 }
 
 // Bounded wait on one ring slot.  Returns false (and flags the error) on expiry.  The spin with its
@@ -311,18 +254,12 @@ __device__ __forceinline__ void diag_reduce(const float (&cc)[4], int lane, floa
 // tcgen05.ld, so the product is bit-identical whichever way a tile took.  Parked tiles are older
 // than every tile in the ring: consume them first.
 // ------------------------------------------------------------------------------------------
-#ifndef QMK_TMEM_SLOTS
-#define QMK_TMEM_SLOTS 4
-#endif
-constexpr int kTSlots = QMK_TMEM_SLOTS;
+constexpr int kTSlots = 4;
 constexpr int kTileCols = 2 * kChunkBytes / (32 * 4);   // 32-bit columns one tile takes in a 32-lane quarter
 static_assert(kTSlots * kTileCols * (kWorkers / 4) <= 512, "parking space exceeds the tensor memory");
 
 // A tile moves to and from tensor memory in pieces of kPieceSteps k-steps (4 registers per k-step).
-#ifndef QMK_TMEM_PIECE_STEPS
-#define QMK_TMEM_PIECE_STEPS 2
-#endif
-constexpr int kPieceSteps = QMK_TMEM_PIECE_STEPS;
+constexpr int kPieceSteps = 2;
 __device__ __forceinline__ void tmem_st_piece(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
 __device__ __forceinline__ void tmem_st_piece(uint32_t taddr, const uint32_t (&r)[8]) { tmem_st8(taddr, r); }
 __device__ __forceinline__ void tmem_ld_piece(uint32_t (&r)[16], uint32_t taddr) { tmem_ld16(r, taddr); }
@@ -400,62 +337,6 @@ __device__ __forceinline__ void consume_tile(Worker<S>& s, const Params& p, int 
   const uint32_t t0 = acquire_tile(s, p, ph);
   mma_chunk_pair(cc, t0, two ? t0 + kChunkBytes : t0, xf, s.lane);
   release_tile(s, p);
-}
-
-// Two tiles at once against the same activations: their ldmatrix / mma chains interleave, which hides
-// most of the latency a single warp would otherwise sit through tile after tile (two warps per
-// scheduler cannot hide it).  ca / cb must be zero on entry; the sums equal those of consume_tile.
-template <class S>
-__device__ __forceinline__ void consume_two(Worker<S>& s, const Params& p, int ph, float (&ca)[4], float (&cb)[4],
-                                            const XFrag& xf, bool two_a, bool two_b) {
-  if (kTSlots > 0 && s.t_count > 0) {   // parked tiles first, one by one
-    consume_tile(s, p, ph, ca, xf, two_a);
-    consume_tile(s, p, ph, cb, xf, two_b);
-    return;
-  }
-  const uint32_t ta = acquire_tile(s, p, ph);
-  const uint32_t tb = acquire_tile(s, p, ph);
-  const uint32_t addr_a = ldmatrix_lane_addr(ta, two_a ? ta + kChunkBytes : ta, s.lane);
-  const uint32_t addr_b = ldmatrix_lane_addr(tb, two_b ? tb + kChunkBytes : tb, s.lane);
-  float c[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) c[i][j] = 0.f;
-#pragma unroll
-  for (int t = 0; t < 16; ++t) {
-    uint32_t fa[4], fb[4];
-    ldmatrix_x4(fa, addr_a + t * 256);
-    ldmatrix_x4(fb, addr_b + t * 256);
-    mma_bf16_16816(c[t & 3], fa, xf.b[2 * t], xf.b[2 * t + 1]);
-    mma_bf16_16816(c[4 + (t & 3)], fb, xf.b[2 * t], xf.b[2 * t + 1]);
-  }
-  __syncwarp();
-  issue_one(s, p);
-  issue_one(s, p);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    ca[j] += (c[0][j] + c[1][j]) + (c[2][j] + c[3][j]);
-    cb[j] += (c[4][j] + c[5][j]) + (c[6][j] + c[7][j]);
-  }
-}
-// diag_reduce of two products, the shuffles of both in flight together.
-__device__ __forceinline__ void diag_reduce2(const float (&ca)[4], const float (&cb)[4], int lane, float& a0, float& a1,
-                                             float& b0, float& b1) {
-  const int r = lane >> 2, q2 = (lane & 3) * 2;
-  a0 = r == q2 ? ca[0] : (r == q2 + 1 ? ca[1] : 0.f);
-  a1 = r == q2 ? ca[2] : (r == q2 + 1 ? ca[3] : 0.f);
-  b0 = r == q2 ? cb[0] : (r == q2 + 1 ? cb[1] : 0.f);
-  b1 = r == q2 ? cb[2] : (r == q2 + 1 ? cb[3] : 0.f);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float x0 = __shfl_xor_sync(kFullMask, a0, o), x1 = __shfl_xor_sync(kFullMask, a1, o);
-    const float x2 = __shfl_xor_sync(kFullMask, b0, o), x3 = __shfl_xor_sync(kFullMask, b1, o);
-    a0 += x0;
-    a1 += x1;
-    b0 += x2;
-    b1 += x3;
-  }
 }
 
 }  // namespace qmk

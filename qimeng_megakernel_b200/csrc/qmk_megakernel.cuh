@@ -2,9 +2,6 @@
 #pragma once
 #include "qmk_kernel.cuh"
 
-#if QMK_UMMA
-#include "qmk_umma.cuh"
-#else
 
 namespace qmk {
 
@@ -40,11 +37,6 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.wb.lm_head = reinterpret_cast<const unsigned char*>(p.lm_head);
   s.cur.init(s.g, s.nwt, p.vocab, p.phase_begin);
   s.cur.seek(s.wb, p.num_layers, p.phase_end);
-  s.pf = s.cur;
-  if (kL2Ahead > 0) {   // run the look-ahead cursor kSlots + kL2Ahead tiles in front
-#pragma unroll 1
-    for (int i = 0; i < kSlots + kL2Ahead; ++i) prefetch_one(s, p);
-  }
 #pragma unroll 1
   for (int i = 0; i < kSlots; ++i) issue_one(s, p);
 
@@ -117,5 +109,3 @@ __global__ void __launch_bounds__(kThreads, 1) qmk_decode_kernel(const __grid_co
 }
 
 }  // namespace qmk
-
-#endif  // QMK_UMMA

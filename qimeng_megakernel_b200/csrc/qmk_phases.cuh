@@ -74,7 +74,6 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
   return f32_to_bf16_bits(sl * bf16_round(up));
 }
 
-#if !QMK_UMMA
 // ---- the streaming phase -----------------------------------------------------------------------
 // An item is what one lane of the epilogue owns: a QKV RoPE pair or SwiGLU unit (one tile each), or a
 // row of O-proj / LM head (two rows per tile) or of down-proj (two rows per I/2048 tiles, one tile
@@ -85,11 +84,6 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
 // order, decode_kernel/down_proj_gemv_residual.cu:39-52, 225-234).
 // LM head (fused_rms_lmhead_gemv, operations.py:303-321) also keeps the arg-max of the bf16 logits,
 // lowest index on ties, replacing `logits.argmax()` of the host loop (decode.py:1391-1395).
-#ifndef QMK_PAIR_TILES
-#define QMK_PAIR_TILES 0
-#endif
-constexpr bool kPairTiles = QMK_PAIR_TILES != 0;
-
 template <class S>
 __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kind) {
   using L = SmemLayout<S>;
@@ -148,9 +142,9 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   // (the staging area is free from the end of that layer's attention on, and the copy then has ten microseconds to
   // land); the first layer of a launch does it in its own QKV phase.
   if (!s.aborted) {
-    if (QMK_KV_EARLY && kind == kUpGate && layer + 1 < p.num_layers && ph + 3 < p.phase_end)
+    if (kind == kUpGate && layer + 1 < p.num_layers && ph + 3 < p.phase_end)
       prefetch_attn_rows<S>(p, smem, layer + 1, s.w, s.lane);
-    if (kind == kQkv && (!QMK_KV_EARLY || layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
+    if (kind == kQkv && (layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
   }
 
   int i0, i1;
@@ -184,24 +178,6 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
 #pragma unroll 1
       for (int i = 0; i < nb; i += step) {
         float cc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (kPairTiles && nsl == 1 && i + step < nb) {   // two tiles of the same activations at once
-          float cb[4] = {0.f, 0.f, 0.f, 0.f};
-          consume_two(s, p, ph, cc, cb, xf, unit_tiles || (i + 1 < nb), unit_tiles || (i + step + 1 < nb));
-          float a0, a1, b0, b1;
-          diag_reduce2(cc, cb, s.lane, a0, a1, b0, b1);
-          if (s.lane == i) {
-            va = a0;
-            vb = a1;
-          }
-          if (!unit_tiles && s.lane == i + 1) va = a1;
-          i += step;
-          if (s.lane == i) {
-            va = b0;
-            vb = b1;
-          }
-          if (!unit_tiles && s.lane == i + 1) va = b1;
-          continue;
-        }
 #pragma unroll 1
         for (int k = 0; k < nsl; ++k) {
           if (nsl > 1) load_xfrag(xf, act + k * kChunkBytes, s.lane);
@@ -245,10 +221,6 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
       if (residual && ib == i0) s.res_valid = true;
     }
   }
-  // Push this warp's tagged stores out now.  Nothing waits for the fence itself (the warp would only
-  // start polling for the next phase), but without it the stores linger behind the polling loads and
-  // every consumer sees them about a microsecond later (measured: 16 % of the whole step).
-  flush_handoff();
   if (s.w == 0) {
     trace_put(p, ph, 3, (unsigned long long)(tq1 - tq0), s.lane);
     trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
@@ -292,10 +264,6 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   }
 }
 
-#endif  // !QMK_UMMA
-
 }  // namespace qmk
 
-#if !QMK_UMMA
 #include "qmk_attention.cuh"
-#endif

@@ -211,78 +211,4 @@ struct TileCursor {
   }
 };
 
-// ------------------------------------------------------------------------------------------
-// CTA-level stream for the tcgen05 path.  A CTA owns a contiguous range of rows (or RoPE pairs, or
-// SwiGLU units) of every projection and streams them in GROUPS of 16 row chunks of 4 KiB: one
-// group fills one 64-KiB ring slot and is multiplied by sixteen tcgen05.mma (M = 128: 16 chunks x 8
-// sixteen-byte pieces; see qmk_umma.cuh).  Slot s of a group holds
-//   QKV      row 2*a0 + 16*g + s                        (pairs stay in adjacent slots)   one copy per group
-//   O-proj   row r0 + 16*g + s                                                            one copy per group
-//   up/gate  even s: up row u0 + 8*g + s/2, odd s: gate row of the same unit              one copy per slot
-//   down     row r0 + 16*g + s, k-slice j (a group takes I/2048 ring slots in a row)      one copy per slot
-//   LM head  row l0 + 16*g + s                                                            one copy per group
-// ------------------------------------------------------------------------------------------
-constexpr int kGroupRows = 16;
-constexpr int kGroupBytes = kGroupRows * kChunkBytes;
-
-template <class S>
-struct CtaRanges {
-  int a0, a1;   // QKV RoPE pairs
-  int r0, r1;   // rows of the residual phases
-  int u0, u1;   // SwiGLU units
-  int l0, l1;   // LM head rows
-
-  QMK_HD void init(int cta, int grid, int vocab) {
-    split_range_u32(S::QKV_ROWS / 2, grid, cta, a0, a1);
-    split_range_u32(S::H, grid, cta, r0, r1);
-    split_range_u32(S::I, grid, cta, u0, u1);
-    split_range_u32((unsigned)vocab, grid, cta, l0, l1);
-  }
-  // 4-KiB slots (row chunks per k-slice) of this CTA in a phase of kind k
-  QMK_HD int slots(int k) const {
-    switch (k) {
-      case kQkv: return 2 * (a1 - a0);
-      case kOproj: case kDown: return r1 - r0;
-      case kUpGate: return 2 * (u1 - u0);
-      case kLmHead: return l1 - l0;
-      default: return 0;
-    }
-  }
-  QMK_HD int groups(int k) const { return (slots(k) + kGroupRows - 1) / kGroupRows; }
-  QMK_HD int group_slots(int k, int g) const {
-    const int left = slots(k) - g * kGroupRows;
-    return left < kGroupRows ? left : kGroupRows;
-  }
-};
-
-// Calls f(offset in the ring slot, source, bytes) for every bulk copy of group g (k-slice j) of a phase.
-template <class S, class F>
-QMK_HD void for_each_group_copy(const StreamBases& w, const CtaRanges<S>& R, int layer, int kind, int g, int j, F&& f) {
-  const int n = R.group_slots(kind, g);
-  const size_t row_b = (size_t)kChunkBytes;
-  switch (kind) {
-    case kQkv:
-      f(0u, w.qkv + ((size_t)layer * S::QKV_ROWS + 2 * (size_t)R.a0 + (size_t)g * kGroupRows) * row_b, (uint32_t)(n * kChunkBytes));
-      break;
-    case kOproj:
-      f(0u, w.o_proj + ((size_t)layer * S::H + R.r0 + (size_t)g * kGroupRows) * row_b, (uint32_t)(n * kChunkBytes));
-      break;
-    case kUpGate:
-      for (int s = 0; s < n; ++s) {
-        const size_t u = (size_t)layer * S::I + R.u0 + (size_t)g * (kGroupRows / 2) + (s >> 1);
-        f((uint32_t)(s * kChunkBytes), ((s & 1) ? w.gate : w.up) + u * row_b, (uint32_t)kChunkBytes);
-      }
-      break;
-    case kDown:
-      for (int s = 0; s < n; ++s) {
-        const size_t row = (size_t)layer * S::H + R.r0 + (size_t)g * kGroupRows + s;
-        f((uint32_t)(s * kChunkBytes), w.down + (row * S::I + (size_t)j * kChunkElems) * 2, (uint32_t)kChunkBytes);
-      }
-      break;
-    default:
-      f(0u, w.lm_head + ((size_t)R.l0 + (size_t)g * kGroupRows) * row_b, (uint32_t)(n * kChunkBytes));
-      break;
-  }
-}
-
 }  // namespace qmk

@@ -27,18 +27,11 @@ static __device__ __noinline__ bool poll_give_up(const Params& p, long long t0, 
   return false;
 }
 
-// Optional pause between two polls of words that are not there yet (measured on B200: any pause only
-// adds latency, the polling traffic itself does not disturb the weight stream; default off).
-#ifndef QMK_POLL_SLEEP_NS
-#define QMK_POLL_SLEEP_NS 0
-#endif
-__device__ __forceinline__ void poll_pause(unsigned it) {
-  if (QMK_POLL_SLEEP_NS > 0) __nanosleep(it < 2 ? QMK_POLL_SLEEP_NS / 2 : QMK_POLL_SLEEP_NS);
-}
+// While a poll waits, keep the weight stream moving (tensor-memory parking, qmk_kernel.cuh).  A pause between two
+// polls only adds latency; the polling traffic itself does not disturb the weight stream (both measured on B200).
 template <class S>
 __device__ __forceinline__ void poll_backoff(Worker<S>& s, const Params& p, unsigned it) {
-  park_one(s, p);   // use the wait: keep the weight stream moving (tensor-memory parking, qmk_kernel.cuh)
-  if (QMK_POLL_SLEEP_NS > 0) __nanosleep(it < 2 ? QMK_POLL_SLEEP_NS / 2 : QMK_POLL_SLEEP_NS);
+  park_one(s, p);
 }
 
 // Poll NPL uint4 per lane (4 tagged words each) starting at word `word0` until every word carries `tag`.
@@ -179,17 +172,9 @@ __device__ __forceinline__ void prefetch_attn_rows(const Params& p, unsigned cha
 // CTA barrier followed by a look at the CTA's abort word.  Every warp of the CTA executes the same
 // sequence of these (also warps that have given up), so a bounded wait that expires in one warp
 // never leaves the others stuck at a barrier.
-// Barrier of the CTA's worker warps (on the tcgen05 path the CTA also has control warps, which never join it).
-__device__ __forceinline__ void worker_barrier() {
-#if QMK_UMMA
-  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
-#else
-  __syncthreads();
-#endif
-}
 template <class S>
 __device__ __forceinline__ void cta_sync(Worker<S>& s, const unsigned char* smem) {
-  worker_barrier();
+  __syncthreads();
   if (reinterpret_cast<const volatile unsigned*>(smem + SmemLayout<S>::kOffCtl)[kCtlAbort] != 0u) s.cta_abort = true;
 }
 template <class S>
