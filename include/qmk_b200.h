@@ -154,8 +154,10 @@ typedef struct qmk_state_ptrs {
 
 /* Device-side status record, filled when a bounded wait expires. */
 typedef struct qmk_status {
-  int32_t code;      /* 0 = healthy; 1 = dependency-counter wait expired; 2 = weight-copy wait expired;
-                        3 = activation-staging wait expired */
+  int32_t code;      /* 0 = healthy; 1 = dependency wait expired; 2 = weight-copy wait expired;
+                        3 = activation-staging wait expired; 4 = (batched kernel) an active row's position was
+                        outside the KV cache or the RoPE table: that row was treated as inactive, `seen` is the
+                        position, `expected` the limit, `detail` the row; qmk_poll_status returns QMK_ERR_POSITION */
   int32_t sm;        /* CTA (one per SM) that reported */
   int32_t warp;
   int32_t phase;     /* global phase index: layer*5 + {0 qkv,1 attn,2 oproj,3 upgate,4 down}; 5*L = lm head */
@@ -241,6 +243,13 @@ int64_t qmk_step_bytes(const qmk_handle* h, int32_t pos_id);
  * stream of the last launch); the bytes of a MoE step depend on it.  0 for other architectures. */
 int qmk_last_expert_count(qmk_handle* h, int32_t* out);
 
+/* QMK_ARCH_MOE: what the last router phase selected (the reference keeps it in Globals.expert_indices /
+ * expert_weights, qwen1_5_moe_a2_7b/.../decode_schedule/globs.py:41-42, for one row): `count` distinct experts of the
+ * step, their indices ascending in experts[0..count), and weights[slot * 64 + row] = router probability of row `row`
+ * for experts[slot], 0 where the row did not select it.  experts: int32[num_experts], weights: float[num_experts * 64]
+ * (host memory).  Synchronises the stream of the last launch. */
+int qmk_last_expert_routing(qmk_handle* h, int32_t* count, int32_t* experts, float* weights);
+
 /* Number of kernels the library has launched through this handle. */
 int64_t qmk_launch_count(const qmk_handle* h);
 
@@ -257,10 +266,26 @@ int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, in
  * on a device share it: run them on one stream, one after the other (overlapping calls race); what must
  * start at zero is cleared by each call.  The first call on a device does the set-up (symbol address,
  * kernel attribute): make it outside any stream capture.  A model whose scratch would not fit returns
- * QMK_ERR_SCRATCH_TOO_LARGE.  Asynchronous on `cuda_stream`; not thread-safe. */
+ * QMK_ERR_SCRATCH_TOO_LARGE; a state with position_ids or active_mask (which the batch-1 kernel does not
+ * have) returns QMK_ERR_INVALID_ARG.  Asynchronous on `cuda_stream`; not thread-safe. */
 #define QMK_STATIC_SCRATCH_MAX_BYTES (2u << 20)
 int qmk_decode_step_static(const qmk_model_desc* desc, const qmk_weight_ptrs* weights, const qmk_state_ptrs* state,
                            int32_t pos_id, int device, void* cuda_stream);
+
+/* Companions of qmk_decode_step_static (no counterparts in the reference either; none of them allocates).
+ * qmk_static_poll_status: synchronises the stream of the last static launch on `device` and copies the
+ * status record out of the fixed array.  The record of an expired wait is sticky: later static calls do
+ * not clear it, so the failure is still there when the caller gets round to polling.  When it is non-zero
+ * the whole array is cleared and QMK_ERR_DEVICE_TIMEOUT is returned; results of the failed launch and of
+ * launches queued behind it must be discarded.
+ * qmk_static_set_timeout_cycles: the wait budget of static launches on `device` (0 = default 2e9 cycles).
+ * qmk_static_set_wait_first_dependency: the failure-detection knob of qmk_set_wait_first_dependency for
+ * the static path (the first phase waits for words nothing writes).
+ * qmk_static_last_cuda_error: text behind the last QMK_ERR_CUDA of a static entry point. */
+int qmk_static_poll_status(int device, qmk_status* out);
+int qmk_static_set_timeout_cycles(int device, int64_t cycles);
+int qmk_static_set_wait_first_dependency(int device, int32_t on);
+const char* qmk_static_last_cuda_error(void);
 
 void qmk_destroy(qmk_handle* h);
 const char* qmk_strerror(int code);

@@ -68,11 +68,16 @@ SYMBOLS = [
     ("qmk_set_wait_first_dependency", C.c_int, [C.c_void_p, C.c_int32]),
     ("qmk_step_bytes", C.c_int64, [C.c_void_p, C.c_int32]),
     ("qmk_last_expert_count", C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    ("qmk_last_expert_routing", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     ("qmk_launch_count", C.c_int64, [C.c_void_p]),
     ("qmk_launch_geometry", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                       C.POINTER(C.c_int32)]),
     ("qmk_decode_step_static", C.c_int, [C.POINTER(ModelDesc), C.POINTER(WeightPtrs), C.POINTER(StatePtrs), C.c_int32,
                                          C.c_int, C.c_void_p]),
+    ("qmk_static_poll_status", C.c_int, [C.c_int, C.POINTER(Status)]),
+    ("qmk_static_set_timeout_cycles", C.c_int, [C.c_int, C.c_int64]),
+    ("qmk_static_set_wait_first_dependency", C.c_int, [C.c_int, C.c_int32]),
+    ("qmk_static_last_cuda_error", C.c_char_p, []),
     ("qmk_destroy", None, [C.c_void_p]),
     ("qmk_strerror", C.c_char_p, [C.c_int]),
     ("qmk_last_cuda_error", C.c_char_p, [C.c_void_p]),

@@ -52,7 +52,12 @@ struct qmk_handle {
   int last_kernel;         // 0 batch-1 kernel, 1 batched kernel: whose status record the next poll reads
 };
 
-static bool use_batched(const qmk_handle* h) { return !h->tuned_shape || h->variant == 1 || (h->bound && h->st.batch != 1); }
+// The batch-1 kernel has neither per-row positions nor an active mask: a state that carries either goes to the
+// batched kernel, so that the same state behaves the same under both kernel variants.
+static bool use_batched(const qmk_handle* h) {
+  return !h->tuned_shape || h->variant == 1 ||
+         (h->bound && (h->st.batch != 1 || h->st.position_ids != nullptr || h->st.active_mask != nullptr));
+}
 
 static int ensure_bctx(qmk_handle* h) {
   if (h->bctx) return QMK_OK;
@@ -429,6 +434,12 @@ extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
   out->expected = words[kStExpected];
   out->detail = (int32_t)words[kStDetail];
   out->reserved = 0;
+  if (out->code == kErrRowPosition) {
+    // no wait expired: a row's position was out of range, the row was switched off and the step completed
+    QMK_CUDA(h, cudaMemsetAsync(status, 0, 32, h->last_stream));
+    QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
+    return QMK_ERR_POSITION;
+  }
   if (out->code != 0) {
     // The aborted launch left half-written tagged words: start over from a clean slate.
     int rc = reset_scratch(h, h->last_stream);
@@ -510,6 +521,19 @@ extern "C" int qmk_last_expert_count(qmk_handle* h, int32_t* out) {
   QMK_CUDA(h, cudaSetDevice(h->device));
   QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
   QMK_CUDA(h, cudaMemcpy(out, qmkb_expert_count_ptr(h->bctx), sizeof(int32_t), cudaMemcpyDeviceToHost));
+  return QMK_OK;
+}
+
+extern "C" int qmk_last_expert_routing(qmk_handle* h, int32_t* count, int32_t* experts, float* weights) {
+  if (!h || !count || !experts || !weights) return QMK_ERR_INVALID_ARG;
+  *count = 0;
+  if (!h->bctx || !qmkb_expert_count_ptr(h->bctx)) return QMK_OK;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
+  const int E = h->desc.num_experts;
+  QMK_CUDA(h, cudaMemcpy(count, qmkb_expert_count_ptr(h->bctx), sizeof(int32_t), cudaMemcpyDeviceToHost));
+  QMK_CUDA(h, cudaMemcpy(experts, qmkb_expert_list_ptr(h->bctx), sizeof(int32_t) * E, cudaMemcpyDeviceToHost));
+  QMK_CUDA(h, cudaMemcpy(weights, qmkb_expert_weight_ptr(h->bctx), sizeof(float) * E * 64, cudaMemcpyDeviceToHost));
   return QMK_OK;
 }
 

@@ -189,6 +189,8 @@ void qmkb_destroy(qmk_batch_ctx* c) {
 
 unsigned* qmkb_status_ptr(qmk_batch_ctx* c) { return c->status; }
 const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c) { return c->moe_ne; }
+const int* qmkb_expert_list_ptr(const qmk_batch_ctx* c) { return c->moe_elist; }
+const float* qmkb_expert_weight_ptr(const qmk_batch_ctx* c) { return c->moe_w; }
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c) { return c->scratch_bytes; }
 
 int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream) {
@@ -266,6 +268,7 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.off_stages = plan.off_stages;
   p.exch_stride = plan.exch_stride;
   p.pos = a->pos;
+  p.pos_limit = st->kv_seq_len < d.rope_rows ? st->kv_seq_len : d.rope_rows;
   p.phase_begin = a->phase_begin;
   p.phase_end = a->phase_end;
   p.wait_first = a->wait_first;

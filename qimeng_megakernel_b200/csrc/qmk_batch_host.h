@@ -34,5 +34,9 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
 unsigned* qmkb_status_ptr(qmk_batch_ctx* c);
 int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream);
 const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c);   // device address of the step's distinct-expert count, or null
+// Device addresses of what the last router phase left: the distinct experts in ascending order [E] and the router
+// weight of every (slot, row) [E, 64] (0 where the row did not pick the expert); null for a dense model.
+const int* qmkb_expert_list_ptr(const qmk_batch_ctx* c);
+const float* qmkb_expert_weight_ptr(const qmk_batch_ctx* c);
 void qmkb_geometry(const qmk_batch_ctx* c, int* ctas, int* threads, int* smem_bytes);
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c);

@@ -1101,7 +1101,11 @@ __device__ __forceinline__ void prologue(const Ctx& c, int e) {
   for (int b = (int)blockIdx.x; b < p.B; b += (int)gridDim.x) {
     uint16_t* h = p.hidden + (size_t)b * p.H;
     const uint16_t* src = h;
-    if (p.prologue == 2) src = p.embed + (size_t)p.token_in[b] * p.H;
+    if (p.prologue == 2) {   // (a token id outside the vocabulary is clamped, as the batch-1 kernel does)
+      long long tok = p.token_in[b];
+      tok = tok < 0 ? 0 : (tok >= p.vocab ? (long long)p.vocab - 1 : tok);
+      src = p.embed + (size_t)tok * p.H;
+    }
     float s = 0.f;
     for (int i = e; i < p.H / 8; i += 128) {
       const uint4 v = ldcg_u4(src + i * 8);
@@ -1132,7 +1136,8 @@ __device__ __forceinline__ void finalize(const Ctx& c, int e) {
     const unsigned long long win = __ldcg(p.argmax_key + e);
     const long long tok = (long long)(0xffffffffu - (unsigned)(win & 0xffffffffull));
     if (p.next_token) p.next_token[e] = tok;
-    if (p.out_tokens && (long long)pos_s[e] + 1 < p.out_tokens_len) p.out_tokens[(size_t)e * p.out_tokens_len + pos_s[e] + 1] = tok;
+    if (p.out_tokens && pos_s[e] >= 0 && (long long)pos_s[e] + 1 < p.out_tokens_len)
+      p.out_tokens[(size_t)e * p.out_tokens_len + pos_s[e] + 1] = tok;
   }
 }
 
@@ -1170,8 +1175,17 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
     const int b = threadIdx.x;
     int* pos_s = reinterpret_cast<int*>(smem + Smem::kOffPos);
     int* act_s = reinterpret_cast<int*>(smem + Smem::kOffAct);
-    pos_s[b] = b < p.B ? (p.position_ids ? p.position_ids[b] : p.pos) : 0;
-    act_s[b] = b < p.B ? (p.active_mask ? (int)p.active_mask[b] : 1) : 0;
+    int pos = b < p.B ? (p.position_ids ? p.position_ids[b] : p.pos) : 0;
+    int act = b < p.B ? (p.active_mask ? (int)p.active_mask[b] : 1) : 0;
+    // An active row whose position lies outside the KV cache or the RoPE table would read and write out of bounds:
+    // it is switched off (no KV write, zero projections, like a finished row) and the launch reports it.
+    if (act != 0 && (pos < 0 || pos >= p.pos_limit)) {
+      if (blockIdx.x == 0) report(p, kErrRowPosition, 0, p.phase_begin, (unsigned)pos, (unsigned)p.pos_limit, b);
+      act = 0;
+      pos = -1;
+    }
+    pos_s[b] = pos;
+    act_s[b] = act;
   }
   __syncthreads();
   if (threadIdx.x == 0) {

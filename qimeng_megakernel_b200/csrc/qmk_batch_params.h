@@ -65,6 +65,7 @@ struct BParams {
   int ppl;                       // phases per layer: 5 (dense) or 6 (MoE)
   int B, Bpad;                   // sequences, padded to a multiple of 16
   int pos;                       // position of every row when position_ids is null
+  int pos_limit;                 // min(kv_seq_len, rope_rows): an active row at or beyond it is switched off and reported
   int phase_begin, phase_end;
   int stages, stage_bytes, off_stages, exch_stride;   // shared-memory plan for this Bpad (smem_plan)
   int prologue;                  // 0 none; 1 sums of squares of `hidden`; 2 embed token_in, then sums of squares

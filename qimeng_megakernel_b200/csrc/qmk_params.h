@@ -9,8 +9,9 @@ namespace qmk {
 
 // Words of the device status record (mirrors qmk_status in the C ABI).
 enum StatusWord : int { kStCode = 0, kStSm = 1, kStWarp = 2, kStPhase = 3, kStSeen = 4, kStExpected = 5, kStDetail = 6 };
-// 1: a producer's tagged words never arrived; 2: a weight copy never completed; 3: another warp of the CTA never staged its part
-enum StatusCode : int { kOkCode = 0, kErrCounterWait = 1, kErrCopyWait = 2, kErrStageWait = 3 };
+// 1: a producer's tagged words never arrived; 2: a weight copy never completed; 3: another warp of the CTA never staged its part;
+// 4: (batched kernel) an active row's position lies outside the KV cache or the RoPE table: the row was treated as inactive
+enum StatusCode : int { kOkCode = 0, kErrCounterWait = 1, kErrCopyWait = 2, kErrStageWait = 3, kErrRowPosition = 4 };
 
 struct Params {
   // ---- weights (bf16 as raw 16-bit words) ----

@@ -10,8 +10,11 @@
 // Consequences the caller must know:
 //  * every GPU that loads the library holds kStaticScratchBytes (2 MiB) of device memory until exit;
 //  * all calls on a device share that one array.  Its contents survive from call to call; the words
-//    that must start at zero (arg-max key, LM-head ticket, status record) are cleared at the start of
-//    every call, the tagged words need no clearing because each call uses fresh tags;
+//    that must start at zero (arg-max key, LM-head ticket) are cleared at the start of every call, the
+//    tagged words need no clearing because each call uses fresh tags;
+//  * the status record of a bounded wait that expired also lives in the array and is NOT cleared by
+//    later calls: it stays until qmk_static_poll_status reads it (and then clears the whole array), so
+//    a failure cannot be lost behind steps that were queued after it;
 //  * two calls that overlap on the same GPU (two streams, two threads) race on the array: issue them
 //    on one stream, one after the other;
 //  * the first call on a device performs the set-up (symbol address, kernel attribute, device
@@ -62,7 +65,13 @@ struct DeviceSetup {
   unsigned char* scratch;   // DEVICE address of g_static_scratch on this device (from cudaGetSymbolAddress)
   int n_sm;
   unsigned launch_seq;
+  long long timeout_cycles;   // device-side wait budget (qmk_static_set_timeout_cycles), 0 = default
+  int wait_first;             // failure-detection knob (qmk_static_set_wait_first_dependency)
+  cudaStream_t last_stream;   // stream of the last launch: what qmk_static_poll_status synchronises
+  size_t status_off;          // offset of the status record used by the last launch
+  bool launched;
 };
+constexpr long long kDefaultTimeoutCycles = 2000000000ll;
 DeviceSetup g_setup[kMaxDevices];
 char g_static_err[256];
 
@@ -123,6 +132,8 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
   for (void* p : sp)
     if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
   if (st->batch != 1 || st->kv_seq_len < 1) return QMK_ERR_INVALID_ARG;
+  // the batch-1 kernel has neither per-row positions nor an active mask: refuse rather than ignore them
+  if (st->position_ids != nullptr || st->active_mask != nullptr) return QMK_ERR_INVALID_ARG;
   if (st->token_in && !w->embed_tokens) return QMK_ERR_INVALID_ARG;
   if (pos_id < 0 || pos_id >= st->kv_seq_len || pos_id >= d->rope_rows) return QMK_ERR_POSITION;
 
@@ -137,8 +148,9 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
     if ((nwt + 1) * units >= (1ull << 32)) return QMK_ERR_INVALID_ARG;
   }
   cudaStream_t stream = (cudaStream_t)cuda_stream;
-  // what must start at zero: LM-head ticket, arg-max key, status record (one contiguous tail region)
-  e = cudaMemsetAsync(dev.scratch + lay.tickets, 0, lay.total - lay.tickets, stream);
+  // what must start at zero: LM-head ticket and arg-max key (contiguous).  The status record behind them is left
+  // alone: a record written by an earlier call stays until qmk_static_poll_status has read it.
+  e = cudaMemsetAsync(dev.scratch + lay.tickets, 0, lay.status - lay.tickets, stream);
   if (e != cudaSuccess) return fail(e, "cudaMemsetAsync");
 
   Params p;
@@ -184,16 +196,20 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
   p.phase_begin = 0;
   p.phase_end = num_phases(d->num_layers);
   p.sync = 1;
-  p.wait_first = 0;
+  p.wait_first = dev.wait_first;
+  if (dev.wait_first) {   // the first phase will wait for words nothing writes: no stale tag may match by accident
+    e = cudaMemsetAsync(dev.scratch, 0, lay.tickets, stream);
+    if (e != cudaSuccess) return fail(e, "cudaMemsetAsync");
+  }
   if (dev.launch_seq >= (1u << 23)) {   // tags would wrap: start over on a cleared array
-    e = cudaMemsetAsync(dev.scratch, 0, lay.total, stream);
+    e = cudaMemsetAsync(dev.scratch, 0, lay.status, stream);
     if (e != cudaSuccess) return fail(e, "cudaMemsetAsync");
     dev.launch_seq = 0;
   }
   p.launch_seq = ++dev.launch_seq;
   p.eps = d->rms_norm_eps;
   p.scale_log2e = d->attn_scale * 1.4426950408889634f;
-  p.timeout_cycles = 2000000000ll;
+  p.timeout_cycles = dev.timeout_cycles > 0 ? dev.timeout_cycles : kDefaultTimeoutCycles;
 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -208,5 +224,60 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
   cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p);
   if (e != cudaSuccess) return fail(e, "cudaLaunchKernelEx");
+  dev.last_stream = stream;
+  dev.status_off = lay.status;
+  dev.launched = true;
   return QMK_OK;
 }
+
+// Reads the status record that qmk_decode_step_static launches leave in the static array: synchronises the stream of
+// the last launch on `device`, copies the 32-byte record to the host (a cudaMemcpy into the caller's struct: nothing
+// is allocated).  A non-zero record means a bounded wait expired in some launch since the last poll: the whole array
+// is then cleared (half-written hand-off words of the aborted launch must not survive) and QMK_ERR_DEVICE_TIMEOUT is
+// returned; the outputs of that launch and of launches queued behind it are not to be trusted.
+extern "C" int qmk_static_poll_status(int device, qmk_status* out) {
+  if (!out || device < 0 || device >= kMaxDevices) return QMK_ERR_INVALID_ARG;
+  memset(out, 0, sizeof(*out));
+  DeviceSetup& dev = g_setup[device];
+  if (!dev.ready || !dev.launched) return QMK_OK;   // nothing was ever launched on this device
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return fail(e, "cudaSetDevice");
+  e = cudaStreamSynchronize(dev.last_stream);
+  if (e != cudaSuccess) return fail(e, "cudaStreamSynchronize");
+  unsigned words[8];
+  e = cudaMemcpy(words, dev.scratch + dev.status_off, sizeof(words), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(e, "cudaMemcpy(status)");
+  out->code = (int32_t)words[kStCode];
+  out->sm = (int32_t)words[kStSm];
+  out->warp = (int32_t)words[kStWarp];
+  out->phase = (int32_t)words[kStPhase];
+  out->seen = words[kStSeen];
+  out->expected = words[kStExpected];
+  out->detail = (int32_t)words[kStDetail];
+  if (out->code != 0) {
+    e = cudaMemsetAsync(dev.scratch, 0, kStaticScratchBytes, dev.last_stream);
+    if (e != cudaSuccess) return fail(e, "cudaMemsetAsync");
+    e = cudaStreamSynchronize(dev.last_stream);
+    if (e != cudaSuccess) return fail(e, "cudaStreamSynchronize");
+    return QMK_ERR_DEVICE_TIMEOUT;
+  }
+  return QMK_OK;
+}
+
+// Wait budget of the static entry point's launches on `device`, in SM clock cycles (0 restores the default, 2e9).
+extern "C" int qmk_static_set_timeout_cycles(int device, int64_t cycles) {
+  if (device < 0 || device >= kMaxDevices || (cycles != 0 && cycles < 1000)) return QMK_ERR_INVALID_ARG;
+  g_setup[device].timeout_cycles = cycles;
+  return QMK_OK;
+}
+
+// Failure-detection knob, the counterpart of qmk_set_wait_first_dependency: while set, the first phase of every
+// static launch on `device` also waits for hand-off words that nothing writes, so its bounded wait must expire.
+extern "C" int qmk_static_set_wait_first_dependency(int device, int32_t on) {
+  if (device < 0 || device >= kMaxDevices) return QMK_ERR_INVALID_ARG;
+  g_setup[device].wait_first = on ? 1 : 0;
+  return QMK_OK;
+}
+
+// Text of the last CUDA runtime error seen by the static entry points (QMK_ERR_CUDA), empty if none.
+extern "C" const char* qmk_static_last_cuda_error(void) { return g_static_err; }

@@ -1,18 +1,22 @@
 """`decode()` for the B200 megakernel route: the host token loop around the kernel.
 
-Mirrors the reference's `decode(..., decode_route="mk")` -> `_decode_mk` -> `FusedGenerator.generate_greedy_fast`
-(qimeng_megakernel/models/LLM/decode.py:1885-2063, 536-849, 1340-1435): same arguments, same return dictionary
-{"generated_ids", "new_tokens", "per_row_new_tokens", "timing"}, same timing keys and definitions
-(decode.py:755-794): the first generated token belongs to prefill, so the decode window holds
-max_new_tokens - 1 kernel steps and `kernel_tok_s` divides those tokens by the sum of the per-step CUDA
-event spans around the kernel call.
+Host-side counterpart of the reference's `decode(..., decode_route="mk")` -> `_decode_mk` ->
+`FusedGenerator.generate_greedy_fast` / `generate_with_eos` (qimeng_megakernel/models/LLM/decode.py:1885-2063, 536-849,
+1340-1435).  The argument names, the returned dictionary {"generated_ids", "new_tokens", "per_row_new_tokens",
+"timing"} and the timing keys are that function's interface and are reproduced key for key (decode.py:755-794), as is
+its post-hoc end-of-sequence scan (decode.py:1397-1430), so that callers and benchmark scripts written against the
+reference read the same fields: the first generated token belongs to prefill, the decode window holds
+max_new_tokens - 1 kernel steps and `kernel_tok_s` divides those tokens by the sum of the per-step CUDA event spans
+around the kernel call.
 
 Two loops are offered:
   host_loop=True   the reference's loop verbatim: embed the token with PyTorch, copy into hidden_states,
                    set position_id, call_mk, arg-max of globs.logits with PyTorch.
   host_loop=False  (default) the kernel embeds the token itself and feeds its own arg-max back
                    (globs.token_in / next_token / out_tokens), so a step is exactly one launch.
-Only greedy decoding is implemented; sampling arguments other than the greedy defaults raise.
+With sampling arguments (temperature > 0 together with top_p / top_k / min_p, or a presence penalty; decode.py:53-143)
+the kernel still embeds the fed token itself and the next token is drawn from `globs.logits` on the device after every
+step (sampling.py); `seed` makes the draws reproducible.
 """
 from __future__ import annotations
 
@@ -23,12 +27,13 @@ import torch
 
 from .prefill import PrefillOutput
 from .registry import import_decode_schedule, resolve_hardware
+from .sampling import is_greedy, sample_logits
 
 
 def _is_greedy(kw: dict) -> bool:
-    return (float(kw.get("temperature", 0.0)) <= 0.0 and float(kw.get("top_p", 1.0)) >= 1.0
-            and int(kw.get("top_k", 0) or 0) <= 0 and float(kw.get("min_p", 0.0)) <= 0.0
-            and float(kw.get("presence_penalty", 0.0)) == 0.0)
+    """Greedy by the reference's rule (no temperature, or no filter that could exclude a token) and no penalty."""
+    return (is_greedy(float(kw.get("temperature", 0.0)), float(kw.get("top_p", 1.0)), int(kw.get("top_k", 0) or 0),
+                      float(kw.get("min_p", 0.0))) and float(kw.get("presence_penalty", 0.0)) == 0.0)
 
 
 @torch.inference_mode()
@@ -39,8 +44,7 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
     if decode_route != "mk":
         raise NotImplementedError(f"route {decode_route!r}: this package implements the compiled 'mk' route only "
                                   "(the PyTorch routes live in the reference)")
-    if not _is_greedy(kwargs):
-        raise NotImplementedError("only greedy decoding is implemented on the B200 route")
+    sampled = not _is_greedy(kwargs)
     hardware = resolve_hardware(hardware)
     ids = prefill.input_ids
     batch_size, prompt_len = int(ids.shape[0]), int(ids.shape[1])
@@ -54,6 +58,11 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
         raise ValueError("prefill.globs is required (run_prefill_synthetic builds it)")
     if int(globs.k_cache.shape[2]) < prompt_len + max_new_tokens:
         raise ValueError("KV cache shorter than prompt_len + max_new_tokens")
+    # Per-row positions (the reference's multi-batch state): the kernel reads them instead of position_id, so they are
+    # advanced on the stream after every step as the reference's loop does (decode.py:1398-1400).
+    pids = getattr(globs, "position_ids", None)
+    if pids is not None and int(pids.max()) + max_new_tokens > int(globs.k_cache.shape[2]):
+        raise ValueError("KV cache shorter than the largest row position + max_new_tokens")
     setup_t0 = time.perf_counter()
     schedule = import_decode_schedule(model_name, hardware, batch_size=batch_size)
     static_megakernel = bool(getattr(schedule.package, "STATIC_MEGAKERNEL", False))
@@ -75,7 +84,35 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
         start_wall = time.perf_counter()
         loop_start.record()
 
-    if host_loop:
+    if sampled:
+        # FusedGenerator.generate (decode.py:1147-1170) with _sample_logits after every step: the drawn token is fed
+        # back through token_in, so a step is still one kernel launch plus the device-side draw
+        saved = (globs.token_in, globs.out_tokens, globs.next_token)
+        globs.out_tokens = None
+        globs.token_in = output_tokens[:, prompt_len].clone()
+        penalty = float(kwargs.get("presence_penalty", 0.0))
+        gen = None
+        if kwargs.get("seed") is not None:
+            gen = torch.Generator(device=device)
+            gen.manual_seed(int(kwargs["seed"]))
+        for i in range(ntok):
+            pos = prompt_len + i
+            globs.position_id = pos
+            if events:
+                events[i][0].record()
+            schedule.call_mk(globs, mk)
+            if events:
+                events[i][1].record()
+            if pids is not None:
+                pids.add_(1)
+            nxt = sample_logits(globs.logits.view(batch_size, -1), temperature=float(kwargs.get("temperature", 0.0)),
+                                top_p=float(kwargs.get("top_p", 1.0)), top_k=int(kwargs.get("top_k", 0) or 0),
+                                min_p=float(kwargs.get("min_p", 0.0)), presence_penalty=penalty,
+                                generated_ids=output_tokens[:, :pos + 1] if penalty != 0.0 else None, generator=gen)
+            output_tokens[:, pos + 1] = nxt
+            globs.token_in.copy_(nxt)
+        globs.token_in, globs.out_tokens, globs.next_token = saved
+    elif host_loop:
         # FusedGenerator.generate_greedy_fast (decode.py:1373-1395): [H] state for one sequence, [B, H] for several
         saved = (globs.token_in, globs.out_tokens)
         globs.token_in = None
@@ -91,6 +128,8 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
             schedule.call_mk(globs, mk)
             if events:
                 events[i][1].record()
+            if pids is not None:
+                pids.add_(1)
             output_tokens[:, pos + 1] = globs.logits.view(batch_size, -1).argmax(dim=-1)
         globs.token_in, globs.out_tokens = saved
     else:
@@ -105,6 +144,8 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
             schedule.call_mk(globs, mk)
             if events:
                 events[i][1].record()
+            if pids is not None:
+                pids.add_(1)
         globs.token_in, globs.out_tokens, globs.next_token = saved
 
     timing = None
@@ -114,7 +155,8 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
         decode_wall_s = time.perf_counter() - start_wall
         decode_gpu_s = loop_start.elapsed_time(loop_end) / 1000.0
         mk_kernel_gpu_s = sum(a.elapsed_time(b) for a, b in events) / 1000.0
-    mk.check_status()
+    if ntok > 0:
+        mk.check_status()
 
     # post-hoc EOS scan (decode.py:1397-1430)
     num_new_after_first = ntok
@@ -140,7 +182,7 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
     if decode_time:
         effective = int(per_row.sum())
         window = max(effective - batch_size, 0)
-        step_bytes = sum(mk.step_bytes(prompt_len + i) for i in range(ntok)) / max(ntok, 1)
+        step_bytes = sum(mk.step_bytes(prompt_len + i) for i in range(ntok)) / ntok if ntok > 0 else 0.0
         timing = {
             "instruction_setup_wall_s": instruction_setup_wall_s, "queue_build_wall_s": 0.0, "tensorize_wall_s": 0.0,
             "decode_wall_s": decode_wall_s, "decode_gpu_s": decode_gpu_s, "mk_kernel_gpu_s": mk_kernel_gpu_s,
@@ -157,7 +199,8 @@ def decode(model_name: str, *, prefill: PrefillOutput, max_new_tokens: int, deco
         print("[mk] decode_time_fast: wall=%.3f s, gpu=%.3f s, mk_kernel_gpu=%.3f s, effective_new_tokens=%d, "
               "tok/s[wall=%.2f gpu=%.2f kernel=%.2f], decode_window_new_tokens=%d (B200 %s loop)"
               % (decode_wall_s, decode_gpu_s, mk_kernel_gpu_s, effective, timing["effective_tok_s_wall"],
-                 timing["effective_tok_s_gpu"], timing["kernel_tok_s"], window, "host" if host_loop else "device"),
+                 timing["effective_tok_s_gpu"], timing["kernel_tok_s"], window,
+                 "sampling" if sampled else ("host" if host_loop else "device")),
               flush=True)
     total_new = num_new_after_first + 1
     return {"generated_ids": output_tokens[:, :prompt_len + total_new],

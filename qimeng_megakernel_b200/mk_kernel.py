@@ -212,7 +212,7 @@ class MegaKernel:
 
     def poll_status(self) -> dict:
         st = _lib.Status()
-        rc = self._lib.qmk_poll_status(self._handle, C.byref(st))
+        rc = self._lib.qmk_poll_status(self._handle, C.byref(st)) if self._handle is not None else 0   # nothing launched yet
         d = {f: getattr(st, f) for f, _ in _lib.Status._fields_}
         d["rc"] = rc
         return d
@@ -247,13 +247,35 @@ class MegaKernel:
             _lib.check(self._lib.qmk_set_trace(self._handle, buf.data_ptr(), buf.numel() * 8))
 
     def step_bytes(self, pos: int) -> int:
-        return int(self._lib.qmk_step_bytes(self._handle, pos))
+        return int(self._lib.qmk_step_bytes(self._handle, pos)) if self._handle is not None else 0
+
+    def decode_step(self, pos: int) -> None:
+        """One more decode step at position `pos` on the state bound by the last `mk(globs)` call (no tensor
+        re-validation: the form a device-resident token loop and the benchmark's timed loops use)."""
+        if self._handle is None:
+            raise RuntimeError("decode_step needs a bound state: call mk(globs) once first")
+        _lib.check(self._lib.qmk_decode_step(self._handle, int(pos), self._stream()), self._handle)
 
     def last_expert_count(self) -> int:
         """MoE: distinct experts selected by the last layer's router in the last step (synchronises)."""
         n = C.c_int32()
         _lib.check(self._lib.qmk_last_expert_count(self._handle, C.byref(n)), self._handle)
         return n.value
+
+    def last_expert_routing(self) -> list[dict]:
+        """MoE: per row of the last step, {expert index: router weight} as the last router phase selected them."""
+        E = int(LlamaConfig.num_experts)
+        n = C.c_int32()
+        experts = (C.c_int32 * E)()
+        weights = (C.c_float * (E * _lib.MAX_BATCH))()
+        _lib.check(self._lib.qmk_last_expert_routing(self._handle, C.byref(n), experts, weights), self._handle)
+        rows = [dict() for _ in range(_lib.MAX_BATCH)]
+        for slot in range(n.value):
+            for b in range(_lib.MAX_BATCH):
+                wgt = weights[slot * _lib.MAX_BATCH + b]
+                if wgt > 0.0:
+                    rows[b][int(experts[slot])] = float(wgt)
+        return rows
 
     @property
     def launch_count(self) -> int:

@@ -92,6 +92,22 @@ def make_prompts(vocab_size: int, batch: int, length: int = 16, seed: int = 1) -
     return torch.stack([make_prompt(vocab_size, length, seed + b) for b in range(batch)])
 
 
+def random_kv_rows(config: dict, rows: int, seed: int, batch: int = 1, std: float = 0.9):
+    """Seeded stand-in for a KV cache that `rows` earlier tokens have filled: (k, v) bf16 CPU tensors
+    [L, batch, rows, NKV, HD] ~ N(0, std) (the spread K and V rows have with N(0, 0.02) weights and a normalised
+    2048-wide input).  The same seed gives the same rows on every machine (CPU generator), so a fixture made with
+    them can be checked elsewhere without shipping the cache."""
+    L, NKV, HD = config["num_hidden_layers"], config["num_key_value_heads"], config["head_dim"]
+    gen = torch.Generator()
+    gen.manual_seed(seed)
+    k = torch.empty(L, batch, rows, NKV, HD, dtype=torch.bfloat16)
+    v = torch.empty(L, batch, rows, NKV, HD, dtype=torch.bfloat16)
+    for layer in range(L):
+        k[layer].copy_(torch.randn(batch, rows, NKV, HD, generator=gen) * std)
+        v[layer].copy_(torch.randn(batch, rows, NKV, HD, generator=gen) * std)
+    return k, v
+
+
 def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | torch.device = "cuda",
                  batch: int | None = None) -> Globals:
     """Allocate the buffers the reference's fused prefill allocates

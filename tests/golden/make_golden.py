@@ -25,10 +25,20 @@ Fixtures:
   moe_block.npz        the reference's fused MoE block (qwen1_5_moe_a2_7b/.../fused/operations.py:151-268) on a small
                        shape, once with a shared expert and 16 experts / top-4, once shaped like an OLMoE layer in
                        miniature (no shared expert: its weights are zero; 64 experts / top-8, router logits ~ N(0,1)).
-                       Pins oracle/moe_oracle.py; no CUDA kernel implements this block yet.
-  llama1b_cfg1.npz     (--full) the BASELINE configuration 1: 16 layers, vocabulary 128256, 16 seeded prompt
+                       Pins oracle/moe_oracle.py.
+  moe_olmoe_layer.npz  the same block at the full OLMoE-1B-7B layer shape (hidden 2048, 64 experts, top-8, expert
+                       intermediate 1024, no shared expert), 8 input rows: experts, router weights, routed output
+                       and new hidden state in bf16 and fp32.  The weights are regenerated from the seed by
+                       moe_weights(MOE_LAYER_CASE); the CUDA kernel's MoE phases are compared with it on the GPU.
+  sampling.npz         the reference's _sample_logits (qimeng_megakernel/models/LLM/decode.py:53-143) on seeded logits
+                       for a grid of temperature / top-k / top-p / min-p / presence-penalty settings: the probability
+                       vector it hands to torch.multinomial (captured by wrapping that call) or its greedy token.
+  llama1b_cfg1.npz     (--full) the full-size Llama-3.2-1B workload: 16 layers, vocabulary 128256, 16 seeded prompt
                        tokens then greedy decode; greedy tokens, top-8 logits per step, per-layer hidden
                        states of selected steps (bf16 and fp32).  Compared with the CUDA kernel on the GPU.
+  llama1b_kv1040.npz   (--full) the same full-size model, ONE decode step at position 1039 on a KV cache whose first
+                       1039 rows are seeded random rows (synthetic.random_kv_rows, seed 1040): top-8 logits, arg-max
+                       and per-layer hidden states in bf16 and fp32.  Long-context evidence at full size.
 """
 from __future__ import annotations
 
@@ -340,6 +350,136 @@ def make_moe():
     print("wrote moe_block.npz")
 
 
+MOE_LAYER_CASE = dict(name="olmoe_layer", hidden_size=2048, intermediate_size=64, moe_intermediate_size=1024,
+                      num_experts=64, num_experts_per_tok=8, shared=False, seed=13, rows=8)
+
+
+def make_moe_layer():
+    """fused_moe_block of the reference at the full OLMoE layer shape (one layer, MOE_LAYER_CASE)."""
+    import importlib
+    mpkg = "qimeng_megakernel.models.LLM.qwen.qwen1_5_moe_a2_7b.A100.single_batch.decode_schedule"
+    pkg = importlib.import_module(mpkg)
+    ops = importlib.import_module(mpkg + ".fused.operations")
+    case = MOE_LAYER_CASE
+    C = pkg.QwenMoeConfig
+    for k in ("hidden_size", "intermediate_size", "moe_intermediate_size", "num_experts", "num_experts_per_tok"):
+        setattr(C, k, case[k])
+    C.rms_norm_eps = 1e-5
+    w = moe_weights(case)
+    gen = torch.Generator().manual_seed(case["seed"] + 100)
+    inputs = (torch.randn(case["rows"], case["hidden_size"], generator=gen) * 0.7).to(torch.bfloat16)
+    H, Ie, K = case["hidden_size"], case["moe_intermediate_size"], case["num_experts_per_tok"]
+    out = {"inputs": bits(inputs)}
+    for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        c = lambda t: t.to(dtype).unsqueeze(0)
+        g = pkg.Globals(
+            mlp_norm_weights=c(w["mlp_norm"]), shared_expert_gate_proj_weights=c(w["shared_gate_proj"]),
+            shared_expert_up_proj_weights=c(w["shared_up_proj"]), shared_expert_down_proj_weights=c(w["shared_down_proj"]),
+            shared_expert_gate_weights=c(w["shared_expert_gate"]), router_weights=c(w["router"]),
+            expert_gate_up_proj_weights=c(w["expert_gate_up"]), expert_down_proj_weights=c(w["expert_down"]),
+            hidden_states=torch.zeros(H, dtype=dtype), shared_out=torch.zeros(H, dtype=dtype),
+            routed_out=torch.zeros(H, dtype=dtype), silu_out=torch.zeros(Ie, dtype=dtype),
+            expert_indices=torch.zeros(K, dtype=torch.int64), expert_weights=torch.zeros(K, dtype=torch.float32))
+        recs = {"hidden": [], "routed_out": [], "expert_indices": [], "expert_weights": []}
+        for x in inputs:
+            g.hidden_states.copy_(x.to(dtype))
+            g.routed_out.zero_()
+            ops.fused_moe_block(g, 0)
+            recs["hidden"].append(bits(g.hidden_states.clone()))
+            recs["routed_out"].append(bits(g.routed_out.clone()))
+            recs["expert_indices"].append(g.expert_indices.clone().numpy())
+            recs["expert_weights"].append(g.expert_weights.clone().numpy())
+        for k, v in recs.items():
+            out[f"{name}_{k}"] = np.stack(v)
+    np.savez_compressed(os.path.join(HERE, "moe_olmoe_layer.npz"), **out)
+    print("wrote moe_olmoe_layer.npz")
+
+
+SAMPLING_CASES = (
+    dict(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0, presence_penalty=0.0),
+    dict(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0, presence_penalty=1.5),
+    dict(temperature=0.7, top_p=1.0, top_k=0, min_p=0.0, presence_penalty=0.0),     # greedy by the reference's rule
+    dict(temperature=0.7, top_p=0.9, top_k=0, min_p=0.0, presence_penalty=0.0),
+    dict(temperature=1.3, top_p=1.0, top_k=40, min_p=0.0, presence_penalty=0.0),
+    dict(temperature=1.0, top_p=1.0, top_k=0, min_p=0.02, presence_penalty=0.0),
+    dict(temperature=0.8, top_p=0.95, top_k=50, min_p=0.01, presence_penalty=0.6),
+    dict(temperature=1.0, top_p=1.0, top_k=0, min_p=0.9, presence_penalty=0.0),      # min-p leaves nothing: fall-back
+    dict(temperature=0.5, top_p=0.0, top_k=5, min_p=0.0, presence_penalty=0.0),      # top-p keeps the first token only
+)
+
+
+def sampling_inputs():
+    """Seeded logits [3, 1000] (bf16-representable, spread like LM-head logits) and already generated ids [3, 12]."""
+    gen = torch.Generator().manual_seed(2024)
+    logits = (torch.randn(3, 1000, generator=gen) * 2.5).to(torch.bfloat16)
+    generated = torch.randint(0, 1000, (3, 12), generator=gen, dtype=torch.int64)
+    # make sure the penalty matters: every row has already produced its current best token
+    generated[:, 0] = logits.float().argmax(dim=-1)
+    return logits, generated
+
+
+def make_sampling():
+    """Runs the reference's _sample_logits row by row with torch.multinomial wrapped, recording what it samples from."""
+    import importlib
+    dec = importlib.import_module("qimeng_megakernel.models.LLM.decode")
+    logits, generated = sampling_inputs()
+    out = {}
+    real = torch.multinomial
+    for ci, case in enumerate(SAMPLING_CASES):
+        probs_rows, greedy_rows = [], []
+        for b in range(logits.shape[0]):
+            captured = []
+
+            def spy(p, *a, **k):
+                captured.append(p.clone())
+                return real(p, *a, **k)
+
+            torch.multinomial = spy
+            try:
+                tok = dec._sample_logits(logits[b], generated_ids=generated[b:b + 1], **case)
+            finally:
+                torch.multinomial = real
+            if captured:
+                probs_rows.append(captured[0].float().numpy())
+                greedy_rows.append(-1)
+            else:
+                probs_rows.append(np.zeros(logits.shape[1], dtype=np.float32))
+                greedy_rows.append(int(tok))
+        out[f"case{ci}_probs"] = np.stack(probs_rows)
+        out[f"case{ci}_greedy"] = np.array(greedy_rows, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "sampling.npz"), **out)
+    print("wrote sampling.npz")
+
+
+LONG_POS, LONG_KV_SEED = 1039, 1040
+
+
+def make_long(pkg, ops):
+    """One full-size Llama-3.2-1B decode step at position LONG_POS over a seeded random KV cache."""
+    cfg = dict(LLAMA_3_2_1B)
+    t0 = time.time()
+    w = synthetic.make_weights(cfg, seed=0, device="cpu", max_positions=2048)
+    token = int(synthetic.make_prompt(cfg["vocab_size"], 1, seed=5)[0])
+    k, v = synthetic.random_kv_rows(cfg, LONG_POS, LONG_KV_SEED)
+    L = cfg["num_hidden_layers"]
+    out = {"token": np.int64(token), "pos": np.int64(LONG_POS), "kv_seed": np.int64(LONG_KV_SEED)}
+    for name, dtype in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        g = ref_globals(pkg, cfg, w, LONG_POS + 1, dtype)
+        g.k_cache[:, :, :LONG_POS].copy_(k.to(dtype))
+        g.v_cache[:, :, :LONG_POS].copy_(v.to(dtype))
+        r = {}
+        nxt = step(ops, g, L, token, LONG_POS, r)
+        tv, ti = r["logits"].float().topk(8)
+        out[f"{name}_top8_values"] = tv.numpy().astype(np.float32)
+        out[f"{name}_top8_indices"] = ti.numpy().astype(np.int64)
+        out[f"{name}_argmax"] = np.int64(nxt)
+        out[f"{name}_layer_hidden"] = bits(r["layer_hidden"])
+        out[f"{name}_attn_out_last_layer"] = bits(r["attn_out"])
+        print(name, nxt, "%.0fs" % (time.time() - t0), flush=True)
+    np.savez_compressed(os.path.join(HERE, "llama1b_kv1040.npz"), **out)
+    print("wrote llama1b_kv1040.npz")
+
+
 def make_full(pkg, ops, n_new: int):
     cfg = dict(LLAMA_3_2_1B)
     t0 = time.time()
@@ -392,5 +532,11 @@ if __name__ == "__main__":
         make_qwen3()
     if ap_only in ("", "moe"):
         make_moe()
-    if args.full:
+    if ap_only in ("", "moe_layer"):
+        make_moe_layer()
+    if ap_only in ("", "sampling"):
+        make_sampling()
+    if args.full and ap_only in ("", "long"):
+        make_long(pkg, ops)
+    if args.full and ap_only in ("", "full"):
         make_full(pkg, ops, args.new_tokens)

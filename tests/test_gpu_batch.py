@@ -220,6 +220,145 @@ def test_llama_shape_batch8_steps(llama_small):
     g.out_tokens = None
 
 
+def whole_steps(env, n_steps, first_pos, prompts, what, untied_floor=0.5):
+    """Teacher-forced whole steps at positions first_pos, first_pos + 1, ...: last-layer hidden state of every row against
+    the fp32 oracle (rtol 2e-2, or 1.25x the bf16 oracle's own distance where larger), arg-max exact on untied rows."""
+    from qimeng_megakernel_b200.model_config import LlamaConfig
+    st, st32, g, mk, cfg = env.st, env.st32, env.g, env.mk, env.cfg
+    LlamaConfig.update_from_dict(cfg)
+    B = env.B
+    g.token_in = torch.zeros(B, dtype=torch.int64, device="cuda")
+    g.active_mask.fill_(1)
+    total = agree = 0
+    for step in range(n_steps):
+        toks = prompts[:, step].tolist()
+        positions = [first_pos[b] + step for b in range(B)]
+        ref = fo.feed_tokens(st, toks, positions, record_layers=True)
+        fo.feed_tokens(st32, toks, positions, record_layers=True)
+        g.token_in.copy_(prompts[:, step])
+        g.position_ids.copy_(torch.tensor(positions, dtype=torch.int32))
+        g.position_id = max(positions)
+        mk(g)
+        torch.cuda.synchronize()
+        hid = g.hidden_states.float().cpu()
+        h32, h16 = st32.layer_hidden[-1].float(), st.layer_hidden[-1].float()
+        for b in range(B):
+            gap = U.rel_l2(h16[b], h32[b])
+            assert U.rel_l2(hid[b], h32[b]) <= max(2e-2, 1.25 * gap), f"{what} step {step} row {b}: hidden vs fp32 oracle"
+        got = g.next_token.tolist()
+        assert got == fo._bh(g.logits).float().argmax(dim=-1).tolist()
+        top2 = st.logits.float().topk(2, dim=-1).values
+        for b in range(B):
+            if float(top2[b, 0] - top2[b, 1]) > 2 * 2.0 ** -8 * abs(float(top2[b, 0])):
+                total += 1
+                agree += int(got[b] == ref[b])
+                assert got[b] == ref[b], f"{what} step {step} row {b}: arg-max {got[b]} != oracle {ref[b]} on an untied row"
+    assert total >= untied_floor * B * n_steps and agree == total
+    mk.check_status()
+    g.token_in = None
+
+
+@pytest.mark.parametrize("batch", [32, 64])
+def test_llama_layer_shape_large_batches(small_config, batch):
+    """The Llama-3.2-1B layer shape (hidden 2048, 32 / 8 heads of 64, SwiGLU 8192; 2 layers) at the batch sizes of the
+    batch-sharded workload, 32 and 64 sequences per GPU: every op at ragged positions over a filled cache with one
+    finished row, then four whole steps from ragged starting positions."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import synthetic
+    env = Env(small_config, batch, 320, seed=1234)
+    try:
+        gen = torch.Generator().manual_seed(batch)
+        k, v = synthetic.random_kv_rows(small_config, 320, seed=batch, batch=batch, std=0.5)
+        for s_ in (env.st, env.st32):
+            s_.k_cache.copy_(k); s_.v_cache.copy_(v)
+        embed_rows(env.st, random_tokens(env.cfg, batch, 50 + batch))
+        positions = [int(x) for x in torch.randint(0, 300, (batch,), generator=gen)]
+        positions[0], positions[1], positions[-1] = 0, 31, 319
+        active = [1] * batch
+        active[3] = 0
+        per_op_walk(env, positions, active, modes=(1,))
+        env.g.k_cache.copy_(k); env.g.v_cache.copy_(v)
+        for s_ in (env.st, env.st32):
+            s_.k_cache.copy_(k); s_.v_cache.copy_(v)
+        first = [int(x) for x in torch.randint(0, 300, (batch,), generator=gen)]
+        prompts = synthetic.make_prompts(small_config["vocab_size"], batch, 4, seed=900 + batch)
+        whole_steps(env, 4, first, prompts, f"batch {batch}")
+    finally:
+        env.close()
+
+
+def test_qwen3_layer_shape_batch16_long_context():
+    """The Qwen3-0.6B layer shape (2 layers, per-head Q/K norm, head_dim 128) with sixteen sequences whose caches hold
+    about a thousand tokens each: every op at ragged positions around 1,000 (split-KV with many key ranges and the
+    record merge), then three whole steps continuing from there."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.model_config import QWEN3_0_6B
+    cfg = dict(QWEN3_0_6B, num_hidden_layers=2, vocab_size=4096, max_position_embeddings=4096)
+    B, S = 16, 1056
+    env = Env(cfg, B, S, seed=2468)
+    try:
+        k, v = synthetic.random_kv_rows(cfg, S, seed=16, batch=B, std=0.5)
+        for s_ in (env.st, env.st32):
+            s_.k_cache.copy_(k); s_.v_cache.copy_(v)
+        gen = torch.Generator().manual_seed(16)
+        embed_rows(env.st, random_tokens(cfg, B, 61))
+        positions = [int(x) for x in torch.randint(960, 1050, (B,), generator=gen)]
+        positions[0], positions[1], positions[2] = 1039, 1023, 1024
+        per_op_walk(env, positions, [1] * B, modes=(1,))
+        env.g.k_cache.copy_(k); env.g.v_cache.copy_(v)
+        for s_ in (env.st, env.st32):
+            s_.k_cache.copy_(k); s_.v_cache.copy_(v)
+        first = [int(x) for x in torch.randint(990, 1040, (B,), generator=gen)]
+        prompts = synthetic.make_prompts(cfg["vocab_size"], B, 3, seed=1600)
+        whole_steps(env, 3, first, prompts, "qwen3 batch 16")
+    finally:
+        env.close()
+
+
+def test_out_of_range_row_is_switched_off_and_reported(small_config):
+    """A row whose position lies beyond the KV cache must not be read or written there: the kernel treats it as a
+    finished row and the status record says which row (no device fault: the guard is what is being tested, and the
+    cache is allocated one row longer than the length that is bound, so even a missed guard would stay in owned memory)."""
+    _need_gpu()
+    import ctypes as C
+    from qimeng_megakernel_b200 import _lib, synthetic
+    env = Env(small_config, 4, 33, seed=1234)
+    try:
+        g, mk = env.g, env.mk
+        g.token_in = torch.tensor([5, 6, -7, 10 ** 9], dtype=torch.int64, device="cuda")   # bad ids are clamped
+        g.position_ids.copy_(torch.tensor([3, 4, 5, 6], dtype=torch.int32))
+        g.position_id = 6
+        mk(g)                                   # creates and binds the handle with S = 33
+        torch.cuda.synchronize()
+        mk.check_status()
+        # bind the same buffers again with a KV length one shorter than what is allocated
+        lib = mk._lib
+        st = _lib.StatePtrs(**{f: (getattr(g, f).data_ptr() if getattr(g, f, None) is not None else None)
+                               for f in ("hidden_states", "q_post_rope", "k_cache", "v_cache", "attn_out", "silu_out",
+                                         "logits", "next_token", "token_in", "position_ids", "active_mask")})
+        st.batch, st.kv_seq_len, st.out_tokens_len = 4, 32, 0
+        # (the layer stride follows kv_seq_len, so use a dedicated cache of exactly [L, 4, 32] rows plus a spare tail)
+        L, NKV, HD = small_config["num_hidden_layers"], small_config["num_key_value_heads"], small_config["head_dim"]
+        kc = torch.zeros(L * 4 * 32 * NKV * HD + NKV * HD, dtype=torch.bfloat16, device="cuda")
+        vc = torch.zeros_like(kc)
+        st.k_cache, st.v_cache = kc.data_ptr(), vc.data_ptr()
+        _lib.check(lib.qmk_bind_state(mk._handle, C.byref(st)), mk._handle)
+        g.position_ids.copy_(torch.tensor([3, -1, 5, 32], dtype=torch.int32))   # rows 1 and 3 are out of range; row 3's
+        # cache row 32 of the last layer would be the spare tail
+        g.token_in.copy_(torch.tensor([5, 6, 7, 8], dtype=torch.int64))
+        _lib.check(lib.qmk_decode_step(mk._handle, 5, torch.cuda.current_stream().cuda_stream), mk._handle)
+        torch.cuda.synchronize()
+        status = mk.poll_status()
+        assert status["rc"] == -6 and status["code"] == 4 and status["detail"] in (1, 3), status
+        assert float(kc[-NKV * HD:].float().abs().max()) == 0.0 and float(vc[-NKV * HD:].float().abs().max()) == 0.0
+        assert bool((g.logits[1].float() <= -9e8).all()) and bool((g.logits[3].float() <= -9e8).all())
+        assert bool((g.logits[0].float() > -9e8).all())
+        assert mk.poll_status()["rc"] == 0      # read once, then clean
+    finally:
+        env.close()
+
+
 def test_batched_kernel_at_batch_one_llama_shape(small_config, small_weights):
     """The batched kernel serving one sequence with the reference's single-batch shapes ([H] state)."""
     _need_gpu()

@@ -257,7 +257,7 @@ def test_argument_validation(env):
 
 
 def test_full_size_against_reference_fixture():
-    """BASELINE configuration 1 at full size (16 layers, vocabulary 128256) against outputs of the real
+    """The full-size Llama-3.2-1B workload (16 layers, vocabulary 128256) against outputs of the real
     reference (tests/golden/llama1b_cfg1.npz): 32 teacher-forced steps.  Top-1 agreement >= 99 % per step
     (exact where the reference's top-2 logits are not tied), top-8 logit values within bf16 tolerance,
     per-layer hidden states within rtol 2e-2 (relative L2) of the reference's fp32 run (see the bound below)
@@ -359,4 +359,85 @@ def test_decode_api_host_and_device_loops(small_config, small_weights):
     first = outs[0][16:].index(eos)
     assert out["per_row_new_tokens"].tolist() == [first + 1]
     assert out["new_tokens"].shape[1] == first + 1
+    pre.mk.close()
+
+
+def test_full_size_step_at_kv1040_against_reference_fixture():
+    """One full-size decode step (16 layers, vocabulary 128256) at position 1039, over a KV cache whose first 1039 rows
+    are the seeded random rows the fixture was made with (tests/golden/llama1b_kv1040.npz, outputs of the real
+    reference): the long end of the decode-length sweep at full size.  Per-layer hidden states within rtol 2e-2
+    (relative L2) of the reference's fp32 run -- or 1.25x the reference's own bf16-to-fp32 distance where that is
+    larger -- top-8 logits within bf16 tolerance, arg-max exact unless the reference's top two are tied."""
+    import os
+    import numpy as np
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from qimeng_megakernel_b200 import mk_kernel, synthetic
+    from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama1b_kv1040.npz"))
+    cfg = dict(LLAMA_3_2_1B)
+    pos, tok = int(z["pos"]), int(z["token"])
+    w = synthetic.make_weights(cfg, seed=0, device="cpu", max_positions=2048)
+    g = synthetic.make_globals(cfg, w, kv_seq_len=pos + 1, device="cuda")
+    del w
+    k, v = synthetic.random_kv_rows(cfg, pos, int(z["kv_seed"]))
+    g.k_cache[:, :, :pos].copy_(k)
+    g.v_cache[:, :, :pos].copy_(v)
+    mk = mk_kernel.get_mk()
+    ref32 = torch.from_numpy(z["fp32_layer_hidden"])
+    ref16 = torch.from_numpy(z["bf16_layer_hidden"].copy()).view(torch.bfloat16).float()
+    for l in (0, 7, 15):
+        g.hidden_states.copy_(g.embed_tokens[tok]); g.position_id = pos
+        mk.run_phases(g, 0, 5 * (l + 1), 1)
+        got = g.hidden_states.float().cpu()
+        gap = U.rel_l2(ref16[l], ref32[l])
+        assert U.rel_l2(got, ref32[l]) <= max(2e-2, 1.25 * gap), f"layer {l}: {U.rel_l2(got, ref32[l]):.4g} vs fp32"
+        assert U.rel_l2(got, ref16[l]) <= max(2e-2, 1.5 * gap), f"layer {l}: {U.rel_l2(got, ref16[l]):.4g} vs bf16"
+        if l == 15:
+            ref_attn = torch.from_numpy(z["bf16_attn_out_last_layer"].copy()).view(torch.bfloat16).float()
+            assert U.rel_l2(g.attn_out, ref_attn) <= 3e-2, "attention output of the last layer over 1040 keys"
+    g.hidden_states.copy_(g.embed_tokens[tok]); g.position_id = pos
+    mk(g)
+    torch.cuda.synchronize()
+    mk.check_status()
+    logits = g.logits.float().cpu()
+    ref_idx, ref_val = z["bf16_top8_indices"], torch.from_numpy(z["bf16_top8_values"])
+    got_val = logits[torch.from_numpy(ref_idx)]
+    assert float((got_val - ref_val).abs().max()) <= 3e-2 * float(ref_val.abs().max()) + 1e-3
+    assert int(g.next_token.item()) == int(logits.argmax())
+    if float(ref_val[0] - ref_val[1]) > 2 * 2 ** -8 * float(ref_val[0].abs()):
+        assert int(g.next_token.item()) == int(z["bf16_argmax"])
+    mk.close()
+
+
+def test_decode_api_sampling(small_config, small_weights):
+    """`decode()` with sampling arguments: the kernel still feeds the fed token itself, the next token is drawn from
+    the kernel's logits on the device.  top_k = 1 is greedy in distribution and must reproduce the greedy text; a fixed
+    seed reproduces the draws; a strong presence penalty forbids repeating the penalised token."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.decode import decode
+    from qimeng_megakernel_b200.prefill import run_prefill_synthetic
+    prompt = synthetic.make_prompt(small_config["vocab_size"], 16, seed=23)
+    n_new = 12
+
+    def run(**kw):
+        pre = run_prefill_synthetic(small_config, small_weights, prompt, n_new, device="cuda:0")
+        out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, ignore_eos=True, decode_time=True, **kw)
+        pre.mk.close()
+        assert out["timing"]["kernel_steps"] == n_new - 1
+        return out["generated_ids"][0].tolist()
+
+    greedy = run()
+    assert run(temperature=0.8, top_k=1) == greedy
+    a, b = run(temperature=1.5, top_p=0.95, seed=7), run(temperature=1.5, top_p=0.95, seed=7)
+    assert a == b and a[:17] == greedy[:17] and a != greedy     # prompt and first token come from prefill
+    pen = run(temperature=0.0, presence_penalty=50.0)
+    new = pen[16:]
+    assert len(set(new[1:])) == len(new[1:]), "with a prohibitive presence penalty no generated token may repeat"
+    two = synthetic.make_prompts(small_config["vocab_size"], 2, 16, seed=29)
+    pre = run_prefill_synthetic(small_config, small_weights, two, n_new, device="cuda:0")
+    out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, ignore_eos=True, temperature=1.0, top_k=20, seed=3)
+    assert out["generated_ids"].shape == (2, 16 + n_new) and int(out["generated_ids"].max()) < small_config["vocab_size"]
     pre.mk.close()

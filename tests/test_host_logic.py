@@ -120,8 +120,8 @@ def test_decode_rejects_other_routes():
                         logits=torch.zeros(1, 8))
     with pytest.raises(NotImplementedError):
         decode("llama-3.2-1b", prefill=pre, max_new_tokens=4, decode_route="fused")
-    with pytest.raises(NotImplementedError):
-        decode("llama-3.2-1b", prefill=pre, max_new_tokens=4, temperature=0.7)
+    with pytest.raises(ValueError):     # sampling is implemented: the call gets as far as the missing device state
+        decode("llama-3.2-1b", prefill=pre, max_new_tokens=4, temperature=0.7, top_p=0.9)
     out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=0)
     assert out["new_tokens"].shape == (1, 0)
 

@@ -201,3 +201,31 @@ def test_moe_block():
                         assert torch.allclose(r[buf], torch.from_numpy(z[key + buf][i]), rtol=1e-5, atol=1e-6), f"{key}{buf}"
                 if not case["shared"]:
                     assert float(r["shared_out"].float().abs().max()) == 0.0
+
+
+def test_moe_block_olmoe_layer_shape():
+    """The MoE block oracle at the full OLMoE-1B-7B layer shape (hidden 2048, 64 experts, top-8, expert intermediate
+    1024) against the reference's fused_moe_block (tests/golden/moe_olmoe_layer.npz)."""
+    import importlib.util
+    from oracle import moe_oracle as mo
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLD, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    z = np.load(os.path.join(GOLD, "moe_olmoe_layer.npz"))
+    case = mg.MOE_LAYER_CASE
+    w = mg.moe_weights(case)
+    inputs = _as_bf16(z["inputs"])
+    cfg = mo.MoeConfig(hidden_size=case["hidden_size"], intermediate_size=case["intermediate_size"],
+                       moe_intermediate_size=case["moe_intermediate_size"], num_experts=case["num_experts"],
+                       num_experts_per_tok=case["num_experts_per_tok"], rms_norm_eps=1e-5)
+    lw = mo.MoeLayerWeights(**{k: w[k] for k in ("mlp_norm", "shared_gate_proj", "shared_up_proj", "shared_down_proj",
+                                                "shared_expert_gate", "router", "expert_gate_up", "expert_down")})
+    distinct = set()
+    for i, x in enumerate(inputs):
+        r = mo.moe_block(cfg, lw, x)
+        assert r["expert_indices"].tolist() == z["bf16_expert_indices"][i].tolist(), f"experts, input {i}"
+        assert np.allclose(r["expert_weights"].numpy(), z["bf16_expert_weights"][i], rtol=1e-6, atol=0)
+        _assert_bits(r["routed_out"], z["bf16_routed_out"][i], f"routed_out input {i}")
+        _assert_bits(r["hidden"], z["bf16_hidden"][i], f"hidden input {i}")
+        distinct |= set(r["expert_indices"].tolist())
+    assert len(distinct) > 24      # near-uniform routing: eight rows touch a good part of the 64 experts

@@ -81,6 +81,9 @@ def test_static_scratch_entry_matches_handle_entry(small_config, small_weights):
         assert torch.equal(got, logits), f"call {pos}: same kernel, same inputs: logits should be identical"
         assert int(g.next_token.item()) == token
         assert torch.equal(g.hidden_states.float().cpu(), hidden)
+    # both steps were healthy: the status record in the fixed array is clean
+    status = _lib.Status()
+    assert lib.qmk_static_poll_status(0, C.byref(status)) == 0 and status.code == 0
     # a model whose scratch cannot fit the fixed array is refused with its own error code
     big = _lib.ModelDesc(**{f: getattr(desc, f) for f, _ in _lib.ModelDesc._fields_})
     big.num_attention_heads = 4096
@@ -89,3 +92,56 @@ def test_static_scratch_entry_matches_handle_entry(small_config, small_weights):
     assert b"fixed array" in lib.qmk_strerror(rc)
     # a position outside the cache is refused before anything is launched
     assert lib.qmk_decode_step_static(C.byref(desc), C.byref(w), C.byref(st), 16, 0, stream) == -6
+
+    # per-row positions / an active mask do not exist in the batch-1 kernel: refused, not ignored
+    pid = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    st2 = _lib.StatePtrs(**{f: getattr(st, f) for f, _ in _lib.StatePtrs._fields_})
+    st2.position_ids = pid.data_ptr()
+    assert lib.qmk_decode_step_static(C.byref(desc), C.byref(w), C.byref(st2), 0, 0, stream) == -1
+
+
+def test_static_entry_reports_an_expired_wait_and_recovers(small_config, small_weights):
+    """A caller of the allocation-free entry point has no handle to poll, so the record of a bounded wait that ran
+    out stays in the fixed array until qmk_static_poll_status reads it.  The wait is made to run out on the host's
+    terms: the first phase waits, with a one-millisecond budget, for hand-off words that nothing writes; the kernel
+    returns by itself and the context stays usable.  A healthy call afterwards matches the handle-based entry point."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from qimeng_megakernel_b200 import _lib, mk_kernel, synthetic
+    lib = _lib.load()
+    cfg = small_config
+    tok = int(synthetic.make_prompt(cfg["vocab_size"], 1, seed=78)[0])
+    g = synthetic.make_globals(cfg, small_weights, kv_seq_len=16, device="cuda:0")
+    desc, w, st = _structs(g, cfg, _lib)
+    stream = torch.cuda.current_stream().cuda_stream
+    status = _lib.Status()
+    assert lib.qmk_static_set_timeout_cycles(0, 999) == -1            # below the smallest budget
+    assert lib.qmk_static_set_timeout_cycles(0, 2_000_000) == 0       # about a millisecond
+    assert lib.qmk_static_set_wait_first_dependency(0, 1) == 0
+    try:
+        g.hidden_states.copy_(g.embed_tokens[tok])
+        assert lib.qmk_decode_step_static(C.byref(desc), C.byref(w), C.byref(st), 0, 0, stream) == 0
+        # a second step queued behind the failed one must not wipe the record
+        lib.qmk_static_set_wait_first_dependency(0, 0)
+        assert lib.qmk_decode_step_static(C.byref(desc), C.byref(w), C.byref(st), 1, 0, stream) == 0
+        rc = lib.qmk_static_poll_status(0, C.byref(status))
+        assert rc == _lib.ERR_DEVICE_TIMEOUT, f"expected the expired wait to be reported, got {rc}"
+        assert status.code != 0 and status.phase == 0
+        assert lib.qmk_static_poll_status(0, C.byref(status)) == 0 and status.code == 0   # read once, then clean
+    finally:
+        lib.qmk_static_set_wait_first_dependency(0, 0)
+        lib.qmk_static_set_timeout_cycles(0, 0)
+    # healthy again: same result as the handle-based entry point on the same input
+    g_ref = synthetic.make_globals(cfg, small_weights, kv_seq_len=16, device="cuda:0")
+    mk = mk_kernel.get_mk()
+    g_ref.hidden_states.copy_(g_ref.embed_tokens[tok]); g_ref.position_id = 0
+    mk(g_ref)
+    torch.cuda.synchronize()
+    mk.check_status()
+    g2 = synthetic.make_globals(cfg, small_weights, kv_seq_len=16, device="cuda:0")
+    desc2, w2, st2 = _structs(g2, cfg, _lib)
+    g2.hidden_states.copy_(g2.embed_tokens[tok])
+    assert lib.qmk_decode_step_static(C.byref(desc2), C.byref(w2), C.byref(st2), 0, 0, stream) == 0
+    assert lib.qmk_static_poll_status(0, C.byref(status)) == 0 and status.code == 0
+    assert torch.equal(g2.logits, g_ref.logits) and int(g2.next_token.item()) == int(g_ref.next_token.item())
+    mk.close()
