@@ -250,6 +250,11 @@ int qmk_last_expert_count(qmk_handle* h, int32_t* out);
  * (host memory).  Synchronises the stream of the last launch. */
 int qmk_last_expert_routing(qmk_handle* h, int32_t* count, int32_t* experts, float* weights);
 
+/* QMK_ARCH_MOE: distinct experts read, summed over every router phase (layer and step) since the counter was last
+ * reset: each one stands for 3 * hidden_size * moe_intermediate_size bf16 weights streamed from HBM, which is what a
+ * benchmark needs to turn a timed run into achieved bytes.  Synchronises the stream of the last launch. */
+int qmk_expert_reads(qmk_handle* h, int64_t* total, int32_t reset);
+
 /* Number of kernels the library has launched through this handle. */
 int64_t qmk_launch_count(const qmk_handle* h);
 

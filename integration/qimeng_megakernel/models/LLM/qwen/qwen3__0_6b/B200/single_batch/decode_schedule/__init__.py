@@ -1,0 +1,9 @@
+"""B200 decode schedule of Qwen3-0.6B: the compiled route is libqmk_b200.so, whose kernel owns its scheduler and
+dependency tracking.  Attributes are what qimeng_megakernel/models/LLM/registry.py:238-262 (import_decode_schedule)
+and decode.py:600-642 read from a decode-schedule package."""
+from qimeng_megakernel_b200 import Globals, LlamaConfig, ModelConfig  # noqa: F401  (same fields as the A100 Globals)
+from qimeng_megakernel_b200.model_config import Qwen3Config  # noqa: F401
+
+# decode.py:609-642 skips queue building and tensorising, 688-689 / 1383-1384 skip barriers.zero_()
+STATIC_MEGAKERNEL = True
+HARDWARE = "B200"

@@ -69,6 +69,7 @@ SYMBOLS = [
     ("qmk_step_bytes", C.c_int64, [C.c_void_p, C.c_int32]),
     ("qmk_last_expert_count", C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     ("qmk_last_expert_routing", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
+    ("qmk_expert_reads", C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int32]),
     ("qmk_launch_count", C.c_int64, [C.c_void_p]),
     ("qmk_launch_geometry", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                       C.POINTER(C.c_int32)]),

@@ -537,6 +537,19 @@ extern "C" int qmk_last_expert_routing(qmk_handle* h, int32_t* count, int32_t* e
   return QMK_OK;
 }
 
+extern "C" int qmk_expert_reads(qmk_handle* h, int64_t* total, int32_t reset) {
+  if (!h || !total) return QMK_ERR_INVALID_ARG;
+  *total = 0;
+  if (!h->bctx || !qmkb_expert_reads_ptr(h->bctx)) return QMK_OK;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  QMK_CUDA(h, cudaStreamSynchronize(h->last_stream));
+  unsigned long long v = 0;
+  QMK_CUDA(h, cudaMemcpy(&v, qmkb_expert_reads_ptr(h->bctx), sizeof(v), cudaMemcpyDeviceToHost));
+  *total = (int64_t)v;
+  if (reset) QMK_CUDA(h, cudaMemset(qmkb_expert_reads_ptr(h->bctx), 0, sizeof(v)));
+  return QMK_OK;
+}
+
 extern "C" int64_t qmk_launch_count(const qmk_handle* h) { return h ? h->launches : 0; }
 
 extern "C" int qmk_launch_geometry(const qmk_handle* h, int32_t* ctas, int32_t* threads, int32_t* smem_bytes) {

@@ -27,6 +27,7 @@ struct qmk_batch_ctx {
   float* ss;
   float* attn_part;
   int* moe_ne;
+  unsigned long long* moe_ne_sum;
   int* moe_elist;
   float* moe_w;
   uint16_t* esilu;
@@ -158,7 +159,7 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     c->ss = (float*)q; q += b_ss;
     c->attn_part = (float*)q; q += b_part;
     if (moe) {
-      c->moe_ne = (int*)q; c->moe_elist = (int*)(q + 256); q += align_up(256 + (size_t)E * 4, 256);
+      c->moe_ne = (int*)q; c->moe_ne_sum = (unsigned long long*)(q + 64); c->moe_elist = (int*)(q + 256); q += align_up(256 + (size_t)E * 4, 256);
       c->moe_w = (float*)q; q += align_up((size_t)E * kMaxBatch * 4, 256);
       c->esilu = (uint16_t*)q; q += align_up((size_t)E * kMaxBatch * Ie * 2, 256);
     }
@@ -190,6 +191,7 @@ void qmkb_destroy(qmk_batch_ctx* c) {
 unsigned* qmkb_status_ptr(qmk_batch_ctx* c) { return c->status; }
 const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c) { return c->moe_ne; }
 const int* qmkb_expert_list_ptr(const qmk_batch_ctx* c) { return c->moe_elist; }
+unsigned long long* qmkb_expert_reads_ptr(const qmk_batch_ctx* c) { return c->moe_ne_sum; }
 const float* qmkb_expert_weight_ptr(const qmk_batch_ctx* c) { return c->moe_w; }
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c) { return c->scratch_bytes; }
 
@@ -243,6 +245,7 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.status = c->status;
   p.moe_ne = c->moe_ne;
   p.moe_elist = c->moe_elist;
+  p.moe_ne_sum = c->moe_ne_sum;
   p.moe_w = c->moe_w;
   p.esilu = c->esilu;
   const bool moe = d.arch == QMK_ARCH_MOE;

@@ -37,6 +37,7 @@ const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c);   // device address of
 // Device addresses of what the last router phase left: the distinct experts in ascending order [E] and the router
 // weight of every (slot, row) [E, 64] (0 where the row did not pick the expert); null for a dense model.
 const int* qmkb_expert_list_ptr(const qmk_batch_ctx* c);
+unsigned long long* qmkb_expert_reads_ptr(const qmk_batch_ctx* c);   // device counter: distinct experts over all router phases
 const float* qmkb_expert_weight_ptr(const qmk_batch_ctx* c);
 void qmkb_geometry(const qmk_batch_ctx* c, int* ctas, int* threads, int* smem_bytes);
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c);

@@ -667,6 +667,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
           if (slot_of[x]) { p.moe_elist[n] = x; slot_of[x] = n++; } else slot_of[x] = -1;
         }
         *p.moe_ne = n;
+        atomicAdd(p.moe_ne_sum, (unsigned long long)n);
       }
       named_bar(kBarEpi, 128);
       if (e < E && slot_of[e] >= 0)

@@ -56,6 +56,7 @@ struct BParams {
   // MoE (null / 0 otherwise): what the router phase leaves for the two expert phases of its layer
   int* moe_ne;                   // [1]  distinct experts selected by the active rows of this step
   int* moe_elist;                // [E]  their indices, ascending
+  unsigned long long* moe_ne_sum; // [1]  distinct experts summed over every router phase since the last reset
   float* moe_w;                  // [E, kMaxBatch]  router weight of (slot, row), 0 where the row did not select it
   uint16_t* esilu;               // [E, kMaxBatch, Ie]  SiLU(gate) * up of (slot, row), bf16
   unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off

@@ -262,6 +262,12 @@ class MegaKernel:
         _lib.check(self._lib.qmk_last_expert_count(self._handle, C.byref(n)), self._handle)
         return n.value
 
+    def expert_reads(self, reset: bool = False) -> int:
+        """MoE: distinct experts read, summed over every router phase since the last reset (synchronises)."""
+        n = C.c_int64()
+        _lib.check(self._lib.qmk_expert_reads(self._handle, C.byref(n), 1 if reset else 0), self._handle)
+        return n.value
+
     def last_expert_routing(self) -> list[dict]:
         """MoE: per row of the last step, {expert index: router weight} as the last router phase selected them."""
         E = int(LlamaConfig.num_experts)
