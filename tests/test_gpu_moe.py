@@ -185,7 +185,7 @@ def test_moe_block_and_steps(shape, batch):
             assert g.next_token.tolist() == own.tolist()
             for b in range(nb):
                 top2 = ref_logits[b].topk(2).values
-                if active[b] and float(top2[0] - top2[1]) > 4 * 2.0 ** -8 * abs(float(top2[0])):
+                if active[b] and b not in near_tie and float(top2[0] - top2[1]) > 4 * 2.0 ** -8 * abs(float(top2[0])):
                     assert int(g.next_token[b]) == int(ref_logits[b].argmax()), f"step {step} row {b} arg-max"
         mk.check_status()
     finally:
