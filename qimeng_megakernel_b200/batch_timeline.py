@@ -40,11 +40,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--model", default="llama-3.2-1b", choices=sorted(MODELS))
     ap.add_argument("--pos", type=int, default=299)
-    ap.add_argument("--issuer", action="store_true",
-                    help="record the issuer's accumulator-wait / issue time instead of its operand waits")
     args = ap.parse_args()
-    if args.issuer:
-        os.environ["QMK_TRACE_ISSUER"] = "1"
     cfg = dict(MODELS[args.model])
     B, dev = args.batch, torch.device("cuda")
     w = synthetic.make_weights(cfg, seed=0, device=dev, max_positions=max(2048, args.pos + 8))

@@ -442,7 +442,6 @@ extern "C" int qmk_poll_status(qmk_handle* h, qmk_status* out) {
   }
   if (out->code != 0) {
     // The aborted launch left half-written tagged words: start over from a clean slate.
-    if (h->last_kernel == 1 && h->bctx) qmkb_print_wait_log(h->bctx);
     int rc = reset_scratch(h, h->last_stream);
     if (rc) return rc;
     if (h->bctx) {

@@ -22,22 +22,22 @@ struct qmk_batch_ctx {
   TensorMaps maps;
   unsigned char* scratch;
   size_t scratch_bytes;
-  // regions of the scratch (tagged hand-off words and records first: they are never cleared between launches)
-  uint32_t *t_hid, *t_q, *t_kv, *t_attn, *t_silu, *t_esilu;
-  unsigned long long *ss_rec, *part_rec, *attn_rec, *moe_ne_rec;
-  unsigned* part_cnt;
+  // regions of the scratch
+  long long* ws;
+  float* ss;
+  float* attn_part;
   int* moe_ne;
   unsigned long long* moe_ne_sum;
   int* moe_elist;
   float* moe_w;
-  unsigned char* zero_begin;   // [phase_done | argmax_key]: zeroed before every launch
+  uint16_t* esilu;
+  unsigned char* zero_begin;   // [phase_done | tile_tickets | attn_tickets | argmax_key]: zeroed before every launch
   size_t zero_bytes;
   unsigned* phase_done;
+  unsigned* tile_tickets;
+  unsigned* attn_tickets;
   unsigned long long* argmax_key;
   unsigned* status;
-  unsigned* wait_log;
-  unsigned epoch;              // launches since the scratch was last cleared: makes every launch's tags distinct
-  int last_batch;              // rows beyond the batch keep old tags: a change of batch size starts from a cleared scratch
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -135,44 +135,41 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     e = cudaFuncSetAttribute(qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) { rc = fail(err, errlen, "cudaFuncSetAttribute", e); break; }
 
+    int max_tiles = (V + kTileRows - 1) / kTileRows;
+    const int t_upgate = moe ? E * (Ie / (kTileRows / 2)) : (I + kTileRows / 2 - 1) / (kTileRows / 2), t_qkv = (QKV + kTileRows - 1) / kTileRows;
+    if (t_upgate > max_tiles) max_tiles = t_upgate;
+    if (t_qkv > max_tiles) max_tiles = t_qkv;
+    if ((H + kTileRows - 1) / kTileRows > max_tiles) max_tiles = (H + kTileRows - 1) / kTileRows;
     const int gq = NH / NKV;
-    const size_t b_hid = align_up((size_t)kMaxBatch * H * 4, 256);
-    const size_t b_q = align_up((size_t)kMaxBatch * QD * 4, 256);
-    const size_t b_kv = align_up((size_t)kMaxBatch * 2 * NKV * HD * 4, 256);
-    const size_t b_silu = moe ? 0 : align_up((size_t)kMaxBatch * I * 4, 256);
-    const size_t b_esilu = moe ? align_up((size_t)E * kMaxBatch * Ie * 4, 256) : 0;
-    const size_t b_ss = align_up((size_t)((H + kTileRows - 1) / kTileRows) * kMaxBatch * 8, 256);
-    const size_t b_part = align_up((size_t)2 * n_sm * kTileRows * kMaxBatch * 8, 256);
-    const size_t b_arec = align_up(((size_t)n_sm * 8 + (size_t)kMaxBatch * NKV) * gq * (HD + 2) * 8, 256);
-    const size_t b_moe = moe ? align_up(256 + (size_t)E * 4, 256) + align_up((size_t)E * kMaxBatch * 4, 256) : 0;
+    const size_t b_ws = align_up((size_t)n_sm * kTileRows * kMaxBatch * 8, 256);
+    const size_t b_ss = align_up((size_t)((H + kTileRows - 1) / kTileRows) * kMaxBatch * 4, 256);
+    const size_t b_part = align_up(((size_t)n_sm * 8 + (size_t)kMaxBatch * NKV) * gq * (HD + 2) * 4, 256);
     const size_t b_done = align_up((size_t)(6 * L + 1 + 2) * 4, 256);
+    const size_t b_moe = moe ? align_up(256 + (size_t)E * 4, 256) + align_up((size_t)E * kMaxBatch * 4, 256) +
+                                   align_up((size_t)E * kMaxBatch * Ie * 2, 256) : 0;
+    const size_t b_tt = align_up((size_t)max_tiles * 4, 256);
+    const size_t b_at = align_up((size_t)kMaxBatch * NKV * 4, 256);
     const size_t b_am = align_up((size_t)kMaxBatch * 8, 256);
-    const size_t b_status = 256, b_log = align_up((1 + 64 * 8) * 4, 256);
-    c->scratch_bytes = b_log + b_hid + 2 * b_q + b_kv + b_silu + b_esilu + b_ss + b_part + b_arec + 256 + align_up((size_t)2 * n_sm * 4, 256) + b_moe + b_done + b_am + b_status;
+    const size_t b_status = 256;
+    c->scratch_bytes = b_ws + b_ss + b_part + b_moe + b_done + b_tt + b_at + b_am + b_status;
     e = cudaMalloc((void**)&c->scratch, c->scratch_bytes);
     if (e != cudaSuccess) { rc = QMK_ERR_OOM; fail(err, errlen, "cudaMalloc", e); break; }
     unsigned char* q = c->scratch;
-    c->t_hid = (uint32_t*)q; q += b_hid;
-    c->t_q = (uint32_t*)q; q += b_q;
-    c->t_attn = (uint32_t*)q; q += b_q;
-    c->t_kv = (uint32_t*)q; q += b_kv;
-    c->t_silu = (uint32_t*)q; q += b_silu;
-    c->t_esilu = (uint32_t*)q; q += b_esilu;
-    c->ss_rec = (unsigned long long*)q; q += b_ss;
-    c->part_rec = (unsigned long long*)q; q += b_part;
-    c->attn_rec = (unsigned long long*)q; q += b_arec;
-    c->moe_ne_rec = (unsigned long long*)q; q += 256;
-    c->part_cnt = (unsigned*)q; q += align_up((size_t)2 * n_sm * 4, 256);
+    c->ws = (long long*)q; q += b_ws;
+    c->ss = (float*)q; q += b_ss;
+    c->attn_part = (float*)q; q += b_part;
     if (moe) {
       c->moe_ne = (int*)q; c->moe_ne_sum = (unsigned long long*)(q + 64); c->moe_elist = (int*)(q + 256); q += align_up(256 + (size_t)E * 4, 256);
       c->moe_w = (float*)q; q += align_up((size_t)E * kMaxBatch * 4, 256);
+      c->esilu = (uint16_t*)q; q += align_up((size_t)E * kMaxBatch * Ie * 2, 256);
     }
     c->zero_begin = q;
     c->phase_done = (unsigned*)q; q += b_done;
+    c->tile_tickets = (unsigned*)q; q += b_tt;
+    c->attn_tickets = (unsigned*)q; q += b_at;
     c->argmax_key = (unsigned long long*)q; q += b_am;
     c->zero_bytes = (size_t)(q - c->zero_begin);
-    c->status = (unsigned*)q; q += b_status;
-    c->wait_log = (unsigned*)q;
+    c->status = (unsigned*)q;
     e = cudaMemset(c->scratch, 0, c->scratch_bytes);
     if (e != cudaSuccess) { rc = fail(err, errlen, "cudaMemset", e); break; }
   } while (0);
@@ -198,22 +195,8 @@ unsigned long long* qmkb_expert_reads_ptr(const qmk_batch_ctx* c) { return c->mo
 const float* qmkb_expert_weight_ptr(const qmk_batch_ctx* c) { return c->moe_w; }
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c) { return c->scratch_bytes; }
 
-// With QMK_DEBUG_WAITS set in the environment: prints the waits that were pending when the last launch gave up.
-void qmkb_print_wait_log(qmk_batch_ctx* c) {
-  if (!getenv("QMK_DEBUG_WAITS")) return;
-  unsigned log[1 + 64 * 8];
-  if (cudaMemcpy(log, c->wait_log, sizeof(log), cudaMemcpyDeviceToHost) != cudaSuccess) return;
-  const unsigned n = log[0] < 64u ? log[0] : 64u;
-  fprintf(stderr, "qmk: %u waits gave up (first %u shown): cta warp phase detail seen expected why(1 own budget, 2 another CTA reported)\n", log[0], n);
-  for (unsigned i = 0; i < n; ++i) {
-    const unsigned* e = log + 1 + i * 8;
-    fprintf(stderr, "qmk:   %3u %2u %4u %3u %10u %10u %u\n", e[0], e[1], e[2], e[3], e[4], e[5], e[6]);
-  }
-}
-
 int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream) {
   const cudaError_t e = cudaMemsetAsync(c->scratch, 0, c->scratch_bytes, stream);
-  c->epoch = 0;
   return e == cudaSuccess ? QMK_OK : QMK_ERR_CUDA;
 }
 
@@ -252,25 +235,19 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.kv_seq_stride = (long long)d.num_key_value_heads * d.head_dim;
   p.kv_batch_stride = (long long)st->kv_seq_len * p.kv_seq_stride;
   p.kv_layer_stride = (long long)st->batch * p.kv_batch_stride;
-  p.t_hid = c->t_hid;
-  p.t_q = c->t_q;
-  p.t_kv = c->t_kv;
-  p.t_attn = c->t_attn;
-  p.t_silu = c->t_silu;
-  p.t_esilu = c->t_esilu;
-  p.ss_rec = c->ss_rec;
-  p.part_rec = c->part_rec;
-  p.part_cnt = c->part_cnt;
-  p.attn_rec = c->attn_rec;
-  p.moe_ne_rec = c->moe_ne_rec;
+  p.ws = c->ws;
+  p.tile_tickets = c->tile_tickets;
+  p.ss = c->ss;
+  p.attn_part = c->attn_part;
+  p.attn_tickets = c->attn_tickets;
   p.argmax_key = c->argmax_key;
   p.phase_done = c->phase_done;
   p.status = c->status;
-  p.wait_log = c->wait_log;
   p.moe_ne = c->moe_ne;
   p.moe_elist = c->moe_elist;
   p.moe_ne_sum = c->moe_ne_sum;
   p.moe_w = c->moe_w;
+  p.esilu = c->esilu;
   const bool moe = d.arch == QMK_ARCH_MOE;
   p.E = moe ? d.num_experts : 0;
   p.topk = moe ? d.num_experts_per_tok : 0;
@@ -302,24 +279,17 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.qk_eps = d.qk_norm_eps > 0.f ? d.qk_norm_eps : d.rms_norm_eps;
   p.scale_log2e = d.attn_scale * 1.4426950408889634f;
   p.timeout_cycles = a->timeout_cycles;
-  // What the first phase of the launch reads is tagged by a prologue from the caller's buffers (with the embedding of
-  // token_in when the step starts at phase 0).  The failure test skips it: the first phase then waits in vain.
-  p.prologue = (a->phase_begin == 0 && st->token_in != nullptr) ? 2 : 1;
-  if (a->wait_first) p.prologue = 0;
-  cudaError_t e;
-  // Tags are unique per launch, so nothing is cleared between launches -- except when a stale word could pass for a
-  // fresh one: rows beyond the batch are not rewritten (a change of batch size), the launch counter is about to wrap,
-  // or the failure test waits for words that nothing must write.
-  if (c->last_batch != st->batch || c->epoch >= (1u << 18) || a->wait_first) {
-    e = cudaMemsetAsync(c->scratch, 0, (size_t)((unsigned char*)c->status - c->scratch), stream);
-    if (e != cudaSuccess) return fail(err, errlen, "cudaMemsetAsync", e);
-    c->epoch = 0;
-    c->last_batch = st->batch;
-  } else {
-    e = cudaMemsetAsync(c->zero_begin, 0, c->zero_bytes, stream);
-    if (e != cudaSuccess) return fail(err, errlen, "cudaMemsetAsync", e);
+  // The first phase of the launch, when it starts with an RMSNorm, needs the sums of squares of the residual
+  // stream: computed by a prologue (with the embedding of token_in when the step starts at phase 0).
+  if (a->phase_begin < a->phase_end) {
+    const int k0 = phase_kind(p, a->phase_begin);
+    if (phase_normed(k0))
+      p.prologue = (a->phase_begin == 0 && st->token_in != nullptr) ? 2 : 1;
   }
-  p.epoch = ++c->epoch;
+  if (a->wait_first) p.prologue = 0;
+
+  cudaError_t e = cudaMemsetAsync(c->zero_begin, 0, c->zero_bytes, stream);
+  if (e != cudaSuccess) return fail(err, errlen, "cudaMemsetAsync", e);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)c->n_sm);

@@ -33,7 +33,6 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
 // Device status record (8 words) and a full reset of the scratch after a failed launch.
 unsigned* qmkb_status_ptr(qmk_batch_ctx* c);
 int qmkb_reset(qmk_batch_ctx* c, cudaStream_t stream);
-void qmkb_print_wait_log(qmk_batch_ctx* c);   // QMK_DEBUG_WAITS=1: what the last launch was waiting for when it gave up
 const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c);   // device address of the step's distinct-expert count, or null
 // Device addresses of what the last router phase left: the distinct experts in ascending order [E] and the router
 // weight of every (slot, row) [E, 64] (0 where the row did not pick the expert); null for a dense model.

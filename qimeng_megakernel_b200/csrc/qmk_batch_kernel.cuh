@@ -11,19 +11,15 @@
 // units of a phase, 128 x 64 weights = 16 KiB each, are dealt to the CTAs as equal contiguous ranges,
 // so every SM streams the same number of bytes whatever the matrix shape.  A maximal run of units of
 // one row tile is a SEGMENT, accumulated in tensor memory.  A segment that covers the whole K is
-// finished by its CTA.  Otherwise the CTA that holds the tile's last units FINISHES the tile: the other
-// CTAs write their partial tiles as self-validating records {fp32, tag} and go on; the finisher adds the
-// records to its own accumulator in a fixed order (ascending CTA), so a step gives the same bits every
-// time.  A CTA works through its range head segment first (a partial somebody waits for), whole tiles
-// next, tail segment last (qmk_batch_schedule.h).  The reference splits K in the down-projection only
-// and adds the partials with bf16 compare-and-swap in arrival order
+// finished by its CTA; otherwise the partial tile is added to the tile's fixed-point accumulator at L2
+// (64-bit integer reductions, nothing returned: the sum does not depend on the order of arrival, so a
+// step gives the same bits every time) and the CTA that arrives last at the tile's ticket takes the sum
+// out and runs the epilogue.  The reference splits K in the
+// down-projection only and adds the partials with bf16 compare-and-swap in arrival order
 // (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/down_proj_gemv_residual.cu:39-52).
 //
-// Phases hand data to one another without counters or fences: every activation that crosses SMs is a
-// 32-bit word {bf16, 16-bit tag of (launch, producing phase)}, every fp32 value a 64-bit record
-// {fp32, 32-bit tag}; consumers poll the data itself (the idea of NCCL's LL protocol, as in the batch-1
-// kernel).  The reference's cross-SM protocol is counters with acquire spins (decode_kernel/utils.cuh:266-328).
-// The weight stream runs ahead across phase boundaries.  What each phase computes, rounding points
+// Phases are separated by grid-wide arrival counters (one per phase, zeroed by the host before the
+// launch); the weight stream runs ahead across them.  What each phase computes, rounding points
 // included, follows the reference's fused PyTorch ops for [B, H] state
 // (.../A100/single_batch/decode_schedule/fused/operations.py:126-321; per-row positions and the active
 // mask as in decode_pos_id / row_active there; Qwen3's per-head Q/K RMSNorm:
@@ -143,10 +139,25 @@ __device__ __forceinline__ void mma_bf16_add(uint32_t d_tmem, uint64_t da, uint6
       "l"(da), "l"(db), "r"(idesc)
       : "memory");
 }
+// Split-K partial tiles meet in a FIXED-POINT accumulator at L2.  fp32 additions in arrival order would make the last bit
+// of a sum depend on timing; 64-bit integer additions are associative, so the sum of the partials -- each rounded once to
+// a multiple of 2^-36, finer than fp32 resolves above 2^-12 -- is the same whatever order they arrive in, and two runs
+// of a step give the same bits.
+constexpr float kFixScale = 68719476736.0f;              // 2^36
+constexpr double kFixInv = 1.0 / 68719476736.0;
+__device__ __forceinline__ long long to_fixed(float v) { return __float2ll_rn(v * kFixScale); }
+__device__ __forceinline__ void red_add_s64(long long* addr, long long v) {
+  asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
+}
+// Reads an accumulator and leaves zero for its next user, in one operation at L2.
+__device__ __forceinline__ long long exch_zero_s64(long long* addr) {
+  long long old;
+  asm volatile("atom.relaxed.gpu.global.exch.b64 %0, [%1], %2;" : "=l"(old) : "l"(addr), "l"(0ll) : "memory");
+  return old;
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-
 
 static __device__ __noinline__ void report(const BParams& p, int code, int warp, int phase, unsigned seen, unsigned expected,
                                            int detail) {
@@ -161,26 +172,14 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
   }
 }
 
-// Every wait that gives up -- its own budget ran out (why 1) or it found that another CTA had reported (why 2) -- leaves
-// a line in the wait log (the first 64 do): what a launch was waiting for when it stopped, for the host to print.
-static __device__ __noinline__ void log_wait(const BParams& p, int warp, int phase, int detail, unsigned seen,
-                                             unsigned expected, unsigned why) {
-  if ((threadIdx.x & 31u) != 0u && detail != 16) return;   // one line per warp is enough (detail 16: every thread waits alone)
-  const unsigned i = atomicAdd(p.wait_log, 1u);
-  if (i < 64u) {
-    unsigned* e = p.wait_log + 1 + i * 8;
-    e[0] = blockIdx.x; e[1] = (unsigned)warp; e[2] = (unsigned)phase; e[3] = (unsigned)detail;
-    e[4] = seen; e[5] = expected; e[6] = why; e[7] = 0u;
-  }
-}
-
-// Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the stagers (attention:
-// the first worker) have the phase's input, 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group
-// enters the phase, 5 the CTA's last output of the phase is written.  Cycle sums over the phase's units: 3 / 4 the issuer
-// waiting for the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / filling.
+// Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
+// satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
+// the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
+// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival.
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
   if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = globaltimer_ns();
 }
+
 __device__ __forceinline__ void trace_val(const BParams& p, int ph, int slot, unsigned long long v) {
   if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = v;
 }
@@ -207,9 +206,8 @@ static __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, u
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (c.ctl[kCAbort] != 0u) return false;
-      // (twice the budget of a data wait: these waits sit downstream of one, which should be the one to report)
+      // (twice the budget of a dependency wait: these waits sit downstream of one, which should be the one to report)
       if (clock64() - t0 > 2 * c.p->timeout_cycles) {
-        log_wait(*c.p, c.warp, phase, detail, parity, bar, 1u);
         report(*c.p, kErrCopyWait, c.warp, phase, parity, bar, detail);
         c.ctl[kCAbort] = 1u;
         return false;
@@ -221,11 +219,14 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t p
   return mbar_try_wait(bar, parity) || mbar_wait_slow(c, bar, parity, phase, detail);
 }
 
-// Bounded wait until `*counter` reaches `target` (the LM head's arrivals, before the tokens are written out).
+// Bounded wait until `*counter` reaches `target` (arrivals of all CTAs at the end of a phase).
 static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* counter, unsigned target, int phase) {
   if (c.ctl[kCAbort] != 0u) return false;
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {
+    // Polled with relaxed loads, one acquire load at the end: acquire loads in a tight loop from
+    // three threads of a CTA slowed the warps of the same SM that were still working (the router's epilogue took 60 us
+    // with them, 20 us without).
     unsigned v = ld_relaxed_gpu(counter);
     if (v >= target) {
       v = ld_acquire_gpu(counter);
@@ -242,115 +243,20 @@ static __device__ __noinline__ bool counter_wait(const Ctx& c, const unsigned* c
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// tags and self-validating data
-// ------------------------------------------------------------------------------------------------
-// 16-bit tag of the bf16 words phase `ph` of this launch writes; ph = phase_begin - 1 (possibly -1) is the prologue.
-// A consumer whose producing phase lies before the launch's first phase reads what the prologue tagged.
-__device__ __forceinline__ unsigned tag16(const BParams& p, int src_ph) {
-  if (src_ph < p.phase_begin) src_ph = p.phase_begin - 1;
-  return (p.epoch * (unsigned)(num_phases(p) + 1) + (unsigned)(src_ph + 1)) % 65535u + 1u;
-}
-// 32-bit tag of the fp32 records (never 0; the host restarts the epoch on a cleared scratch before it could wrap).
-__device__ __forceinline__ unsigned tag32(const BParams& p, int src_ph) {
-  if (src_ph < p.phase_begin) src_ph = p.phase_begin - 1;
-  return p.epoch * 8192u + (unsigned)(src_ph + 2);
-}
-__device__ __forceinline__ unsigned long long make_rec(float v, unsigned tag) {
-  return (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
-}
-__device__ __forceinline__ bool rec_ok(unsigned long long r, unsigned tag) { return (unsigned)(r >> 32) == tag; }
-__device__ __forceinline__ float rec_val(unsigned long long r) { return __uint_as_float((unsigned)r); }
-
-// Loads that are repeated until the data is there: L2 only, never merged or hoisted by the compiler.
-__device__ __forceinline__ uint4 poll_ld_u4(const void* ptr) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
-  return v;
-}
-__device__ __forceinline__ ulonglong2 poll_ld_rec2(const void* ptr) {
-  ulonglong2 v;
-  asm volatile("ld.global.cg.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(ptr) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned long long poll_ld_rec(const void* ptr) {
-  unsigned long long v;
-  asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(v) : "l"(ptr) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_rec2(void* ptr, unsigned long long a, unsigned long long b) {
-  asm volatile("st.global.v2.u64 [%0], {%1,%2};" ::"l"(ptr), "l"(a), "l"(b) : "memory");
-}
-__device__ __forceinline__ void st_rec(void* ptr, unsigned long long a) {
-  asm volatile("st.global.u64 [%0], %1;" ::"l"(ptr), "l"(a) : "memory");
-}
-// four tagged words carry `tagw` (= tag << 16) in their upper halves
-__device__ __forceinline__ bool tags4_ok(const uint4& v, unsigned tagw) {
-  return (((v.x ^ tagw) | (v.y ^ tagw) | (v.z ^ tagw) | (v.w ^ tagw)) & 0xffff0000u) == 0u;
-}
-// 8 tagged words (two 16-byte pieces) -> 8 bf16 packed in 16 bytes
-__device__ __forceinline__ uint4 untag8(const uint4& a, const uint4& b) {
-  return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16),
-                    (b.z & 0xffffu) | (b.w << 16));
-}
-// 8 packed bf16 -> two 16-byte pieces of tagged words
-__device__ __forceinline__ void tag8(const uint4& v, unsigned tagw, uint4& a, uint4& b) {
-  a = make_uint4((v.x & 0xffffu) | tagw, (v.x >> 16) | tagw, (v.y & 0xffffu) | tagw, (v.y >> 16) | tagw);
-  b = make_uint4((v.z & 0xffffu) | tagw, (v.z >> 16) | tagw, (v.w & 0xffffu) | tagw, (v.w >> 16) | tagw);
-}
-__device__ __forceinline__ void st_tagged8(uint32_t* dst, const uint4& v, unsigned tagw) {
-  uint4 a, b;
-  tag8(v, tagw, a, b);
-  reinterpret_cast<uint4*>(dst)[0] = a;
-  reinterpret_cast<uint4*>(dst)[1] = b;
-}
-
-// The slow side of a data poll (non-inlined: runs only when the data is not there yet): checks the CTA's abort word,
-// the device-wide status word (another CTA gave up: whoever waits for its output would wait in vain) and the budget.
-// Returns true when the caller must give up.
-static __device__ __noinline__ bool poll_expired(const Ctx& c, long long t0, int phase, unsigned seen, unsigned expected,
-                                                 int detail) {
-  if (c.ctl[kCAbort] != 0u) return true;
-  const unsigned code = ld_relaxed_gpu(c.p->status + kStCode);
-  if (code != 0u && code != (unsigned)kErrRowPosition) {   // (a switched-off row is reported but stops nothing)
-    log_wait(*c.p, c.warp, phase, detail, seen, expected, 2u);
-    c.ctl[kCAbort] = 1u;
-    return true;
-  }
-  if (clock64() - t0 > c.p->timeout_cycles) {
-    log_wait(*c.p, c.warp, phase, detail, seen, expected, 1u);
-    report(*c.p, kErrCounterWait, c.warp, phase, seen, expected, detail);
-    c.ctl[kCAbort] = 1u;
-    return true;
-  }
-  return false;
-}
-
-// Number of distinct experts of this step, for the two expert phases of a MoE layer: the router phase's finisher
-// publishes {count, tag} after the expert list and the router weights are written and fenced (one thread calls this;
-// 0 after a wait that gave up).  A router phase that ran in an earlier launch is taken on stream order.
+// Number of distinct experts of this step, for the two expert phases of a MoE layer: valid once every CTA has finished
+// the layer's router phase (one thread calls this; 0 after a wait that gave up).
 static __device__ __noinline__ int expert_count(const Ctx& c, int ph) {
   const BParams& p = *c.p;
   const int rph = phase_layer(p, ph) * p.ppl + 3;
-  if (rph < p.phase_begin) return *reinterpret_cast<const volatile int*>(p.moe_ne);
-  if (c.ctl[kCAbort] != 0u) return 0;
-  const unsigned tag = tag32(p, rph);
-  const long long t0 = clock64();
-  for (unsigned it = 1;; ++it) {
-    const unsigned long long r = poll_ld_rec(p.moe_ne_rec);
-    if (rec_ok(r, tag)) {
-      __threadfence();   // (acquire side of the router's fence: the list and the weights are read after this)
-      return (int)(unsigned)r;
-    }
-    if ((it & 15u) == 0u && poll_expired(c, t0, ph, (unsigned)(r >> 32), tag, 7)) return 0;
-  }
+  if (rph >= p.phase_begin && !counter_wait(c, p.phase_done + 1 + rph, gridDim.x, ph)) return 0;
+  return (int)ld_acquire_gpu(reinterpret_cast<const unsigned*>(p.moe_ne));
 }
 __device__ __forceinline__ bool is_expert_kind(int kind) { return kind == kEUpGate || kind == kEDown; }
 
 // ------------------------------------------------------------------------------------------------
 // producer (one thread)
 // ------------------------------------------------------------------------------------------------
-static __device__ __noinline__ void producer(const Ctx& c, const TensorMaps& maps, unsigned& n_issued) {
+__device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, unsigned& n_issued) {
   const BParams& p = *c.p;
   const uint32_t stages = smem_u32(c.smem + p.off_stages);
   const uint64_t policy = l2_policy_evict_first();
@@ -365,42 +271,38 @@ static __device__ __noinline__ void producer(const Ctx& c, const TensorMaps& map
     const PhaseDims d = phase_dims(p, kind, ne);
     int lo, hi;
     unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, G), cta, lo, hi);
-    const UnitRuns R = unit_runs(lo, hi, d.KB);
     const CUtensorMap* map = kind == kQkv ? &maps.qkv : kind == kOproj ? &maps.o_proj : kind == kUpGate ? &maps.up
                            : kind == kDown ? &maps.down : kind == kRouter ? &maps.router : &maps.lm_head;
     const int per = p.Ie > 0 ? p.Ie / kBlockK : 1;   // 64-row tiles (k-blocks) of one expert
+    int t = d.KB > 0 ? lo / d.KB : 0, kb = lo - t * d.KB;
     int zslot = -1, zval = 0;   // expert phases: the selected expert's index is fetched when the slot changes
     auto expert_z = [&](int slot) {
       if (slot != zslot) { zslot = slot; zval = layer * p.E + __ldcg(p.moe_elist + slot); }
       return zval;
     };
 #pragma unroll 1
-    for (int r = 0; r < 3; ++r) {
-      int t = d.KB > 0 ? R.lo[r] / d.KB : 0, kb = R.lo[r] - t * d.KB;
-#pragma unroll 1
-      for (int u = R.lo[r]; u < R.hi[r]; ++u, ++n) {
-        const int s = (int)(n & (unsigned)(kStages - 1));
-        if (n >= (unsigned)kStages && !mbar_wait(c, c.empty(s), ((n / (unsigned)kStages) - 1u) & 1u, ph, 1)) {
-          n_issued = n;
-          return;
-        }
-        const uint32_t dst = stages + s * p.stage_bytes;
-        mbar_expect_tx(c.a_full(s), (uint32_t)kABytes);
-        if (kind == kUpGate) {
-          tma_load_3d(dst, map, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
-          tma_load_3d(dst + kABytes / 2, &maps.gate, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
-        } else if (kind == kEUpGate) {   // tile t = (selected expert t / per, 64 gate rows + 64 up rows of that expert)
-          const int z = expert_z(t / per), lt = t % per;
-          tma_load_3d(dst, &maps.egu, kb * kBlockK, lt * (kTileRows / 2), z, c.a_full(s), policy);
-          tma_load_3d(dst + kABytes / 2, &maps.egu, kb * kBlockK, p.Ie + lt * (kTileRows / 2), z, c.a_full(s), policy);
-        } else if (kind == kEDown) {     // k-block kb = (selected expert kb / per, its k-block kb % per)
-          const int z = expert_z(kb / per);
-          tma_load_3d(dst, &maps.edown, (kb % per) * kBlockK, t * kTileRows, z, c.a_full(s), policy);
-        } else {
-          tma_load_3d(dst, map, kb * kBlockK, t * kTileRows, layer, c.a_full(s), policy);
-        }
-        if (++kb == d.KB) { kb = 0; ++t; }
+    for (int u = lo; u < hi; ++u, ++n) {
+      const int s = (int)(n & (unsigned)(kStages - 1));
+      if (n >= (unsigned)kStages && !mbar_wait(c, c.empty(s), ((n / (unsigned)kStages) - 1u) & 1u, ph, 1)) {
+        n_issued = n;
+        return;
       }
+      const uint32_t dst = stages + s * p.stage_bytes;
+      mbar_expect_tx(c.a_full(s), (uint32_t)kABytes);
+      if (kind == kUpGate) {
+        tma_load_3d(dst, map, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
+        tma_load_3d(dst + kABytes / 2, &maps.gate, kb * kBlockK, t * (kTileRows / 2), layer, c.a_full(s), policy);
+      } else if (kind == kEUpGate) {   // tile t = (selected expert t / per, 64 gate rows + 64 up rows of that expert)
+        const int z = expert_z(t / per), lt = t % per;
+        tma_load_3d(dst, &maps.egu, kb * kBlockK, lt * (kTileRows / 2), z, c.a_full(s), policy);
+        tma_load_3d(dst + kABytes / 2, &maps.egu, kb * kBlockK, p.Ie + lt * (kTileRows / 2), z, c.a_full(s), policy);
+      } else if (kind == kEDown) {     // k-block kb = (selected expert kb / per, its k-block kb % per)
+        const int z = expert_z(kb / per);
+        tma_load_3d(dst, &maps.edown, (kb % per) * kBlockK, t * kTileRows, z, c.a_full(s), policy);
+      } else {
+        tma_load_3d(dst, map, kb * kBlockK, t * kTileRows, layer, c.a_full(s), policy);
+      }
+      if (++kb == d.KB) { kb = 0; ++t; }
     }
   }
   n_issued = n;
@@ -409,7 +311,7 @@ static __device__ __noinline__ void producer(const Ctx& c, const TensorMaps& map
 // ------------------------------------------------------------------------------------------------
 // issuer (one thread)
 // ------------------------------------------------------------------------------------------------
-static __device__ __noinline__ void issuer(const Ctx& c, uint32_t tmem) {
+__device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
   const BParams& p = *c.p;
   const uint32_t stages = smem_u32(c.smem + p.off_stages);
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)p.Bpad >> 3) << 17) | ((128u >> 4) << 24);
@@ -423,40 +325,37 @@ static __device__ __noinline__ void issuer(const Ctx& c, uint32_t tmem) {
     const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? expert_count(c, ph) : 0);
     int lo, hi;
     unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, G), cta, lo, hi);
-    const UnitRuns R = unit_runs(lo, hi, d.KB);
+    int kb = d.KB > 0 ? lo % d.KB : 0;
+    bool seg_start = true;
     long long w_a = 0, w_b = 0;
 #pragma unroll 1
-    for (int r = 0; r < 3; ++r) {
-      int kb = d.KB > 0 ? R.lo[r] % d.KB : 0;
-      bool seg_start = true;
-#pragma unroll 1
-      for (int u = R.lo[r]; u < R.hi[r]; ++u, ++n) {
-        const unsigned buf = sg & 1u;
-        if (seg_start && sg >= 2u && !mbar_wait(c, c.acc_empty(buf), ((sg >> 1) - 1u) & 1u, ph, 2)) return;
-        const int s = (int)(n & (unsigned)(kStages - 1));
-        const unsigned par = (n / (unsigned)kStages) & 1u;
-        const long long t0 = tr ? clock64() : 0;
-        if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
-        const long long t1 = tr ? clock64() : 0;
-        if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
-        w_a += t1 - t0;
-        w_b += (tr ? clock64() : 0) - t1;
-        tmem_fence_after_sync();
-        const uint64_t da = desc_sw128(stages + s * p.stage_bytes), db = desc_sw128(stages + s * p.stage_bytes + kABytes);
-        const uint32_t dcol = tmem + buf * (uint32_t)p.Bpad;
-        // (k-step k reads 32 bytes further along K: the start-address field grows by 2)
-        if (seg_start) mma_bf16_set(dcol, da, db, idesc);
-        else mma_bf16_add(dcol, da, db, idesc);
+    for (int u = lo; u < hi; ++u, ++n) {
+      const unsigned buf = sg & 1u;
+      if (seg_start && sg >= 2u && !mbar_wait(c, c.acc_empty(buf), ((sg >> 1) - 1u) & 1u, ph, 2)) return;
+      const int s = (int)(n & (unsigned)(kStages - 1));
+      const unsigned par = (n / (unsigned)kStages) & 1u;
+      const long long t0 = tr ? clock64() : 0;
+      if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
+      const long long t1 = tr ? clock64() : 0;
+      if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
+      w_a += t1 - t0;
+      const long long t2 = tr ? clock64() : 0;
+      w_b += t2 - t1;
+      tmem_fence_after_sync();
+      const uint64_t da = desc_sw128(stages + s * p.stage_bytes), db = desc_sw128(stages + s * p.stage_bytes + kABytes);
+      const uint32_t dcol = tmem + buf * (uint32_t)p.Bpad;
+      // (k-step k reads 32 bytes further along K: the start-address field grows by 2)
+      if (seg_start) mma_bf16_set(dcol, da, db, idesc);
+      else mma_bf16_add(dcol, da, db, idesc);
 #pragma unroll
-        for (int k = 1; k < kBlockK / 16; ++k) mma_bf16_add(dcol, da + 2u * k, db + 2u * k, idesc);
-        mma_commit(c.empty(s));
-        seg_start = false;
-        if (++kb == d.KB || u + 1 == R.hi[r]) {
-          mma_commit(c.acc_full(buf));
-          ++sg;
-          kb = kb == d.KB ? 0 : kb;
-          seg_start = true;
-        }
+      for (int k = 1; k < kBlockK / 16; ++k) mma_bf16_add(dcol, da + 2u * k, db + 2u * k, idesc);
+      mma_commit(c.empty(s));
+      seg_start = false;
+      if (++kb == d.KB || u + 1 == hi) {
+        mma_commit(c.acc_full(buf));
+        ++sg;
+        kb = kb == d.KB ? 0 : kb;
+        seg_start = true;
       }
     }
     trace_val(p, ph, 3, (unsigned long long)w_a);
@@ -467,140 +366,99 @@ static __device__ __noinline__ void issuer(const Ctx& c, uint32_t tmem) {
 // ------------------------------------------------------------------------------------------------
 // stagers (128 threads): activation operand of every unit
 // ------------------------------------------------------------------------------------------------
-// What a phase's activation operand is read from: tagged words [row, K] (expert down-projection: [slot, row, Ie]).
-struct StageSrc {
-  const uint32_t* words;     // tagged source
-  unsigned tagw;             // expected tag << 16
-  bool checked;              // false: the producer ran in an earlier launch, the words are taken on stream order
-  const uint16_t* gain;      // RMSNorm gain of the phase, or null
-  const float* wsc;          // expert down-projection: router weight of (slot, row)
-  int per;                   // expert down-projection: k-blocks per expert (0 otherwise)
-};
+__device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& needed) {
+  // what must have finished before phase ph reads its input: the phase before it, or the prologue
+  const BParams& p = *c.p;
+  needed = true;
+  if (ph > p.phase_begin) return counter_wait(c, p.phase_done + ph, gridDim.x, ph);          // counter of phase ph - 1
+  if (p.prologue != 0) return counter_wait(c, p.phase_done + 0, gridDim.x, ph);
+  if (p.wait_first) return counter_wait(c, p.phase_done + (ph > 0 ? ph : num_phases(p) + 1), gridDim.x, ph);
+  needed = false;
+  return true;
+}
 
-// Stages the activation operand of the CTA's units of one phase: `total` units in the order of the runs R, at ring
-// positions n, n + 1, ...  Ring positions are dealt to the four warps in groups of D by position, not by unit:
-// group g = position / D belongs to warp g % 4, so a warp always fills the same ring slots, lap after lap, and the wait
-// for a slot's previous occupant to be consumed (an mbarrier parity wait, which cannot tell a phase from the one two
-// laps before it) is never more than one lap ahead of the wait the same warp made for that slot before.  A lane owns the
-// 16-byte piece `chunk` of the 128-byte k-block row of the batch rows row0, row0 + 4, ...; the rows are taken in PASSES
-// passes of NPL rows so that the 2 * D * NPL loads of a pass (tagged words are twice the size of the bf16 they carry)
-// fit the registers; all loads of a pass are issued before the first is used and repeated until every word carries the
-// tag.
-template <int NPL, int PASSES, int D, bool EXPERT>
-static __device__ __noinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, const UnitRuns& R, int total, int st,
-                                                unsigned n, const StageSrc& src, const float* rs) {
-  static_assert(kStages % (4 * D) == 0, "every warp must own whole ring slots");
+// Stages the activation operand of units [lo, hi).  A warp takes D consecutive units at a time (the four warps
+// round-robin over groups of D) and a lane has NPL 16-byte pieces per unit: all D * NPL <= 16 loads of a group are
+// issued before the first is used, so that a warp pays one L2 round trip per group, not per unit or per piece.
+// 5 * D - 1 must stay below twice the number of ring slots: a warp that got two laps of the ring ahead of the tensor core would take an
+// old completion of a stage's mbarrier (same parity) for the one it waits for.
+template <int NPL, int D, bool EXPERT>
+__device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
+                                            const uint16_t* src, const uint16_t* gain, const float* rs,
+                                            int per = 0, const float* wsc = nullptr) {
+  // per > 0 (expert down-projection): k-block kb of the phase is k-block kb % per of selected expert kb / per; the
+  // source is that expert's SiLU(gate) * up [slot, row, Ie] and every row is scaled by its router weight wsc[slot, row]
+  static_assert(4 * D + D - 1 < 2 * kMinStages, "a stager warp could run two ring laps ahead");
   const BParams& p = *c.p;
   const int sw = st >> 5, lane = st & 31;
   const int chunk = lane & 7;         // 16-byte piece inside the 128-byte k-block row
   const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
   long long w_slot = 0, w_fill = 0;
   const bool tr = p.trace != nullptr;
-  const int la = R.hi[0] - R.lo[0], lab = la + R.hi[1] - R.lo[1];
-  auto unit_at = [&](int i) { return i < la ? R.lo[0] + i : (i < lab ? R.lo[1] + (i - la) : R.lo[2] + (i - lab)); };
-  // first group of this warp at or after ring position n
-  unsigned g0 = n / (unsigned)D;
-  g0 += ((unsigned)sw + 4u - (g0 & 3u)) & 3u;
-  bool first_group = true;
 #pragma unroll 1
-  for (unsigned g = g0; g * (unsigned)D < n + (unsigned)total; g += 4u) {
-    const int base = (int)(g * (unsigned)D) - (int)n;   // index of the group's first position in the phase's unit sequence (may be < 0)
-    bool slot_ok[D];
+  for (int base = lo + sw * D; base < hi; base += 4 * D) {
+    uint4 v[D][NPL];
+    uint4 g4[D];
+    float sc[EXPERT ? D : 1][EXPERT ? NPL : 1];
 #pragma unroll
-    for (int j = 0; j < D; ++j) slot_ok[j] = false;
-#pragma unroll 1
-    for (int q = 0; q < PASSES; ++q) {
-      uint4 va[D][NPL], vb[D][NPL];
-      int off[D][NPL];   // word offset of the lane's piece in the source, -1: nothing to fetch (row or unit past the end)
-      float sc[EXPERT ? D : 1][EXPERT ? NPL : 1];
-      uint4 g4[D];
+    for (int j = 0; j < D; ++j) {
+      const int u = base + j;
+      const int kbu = u < hi ? u % d.KB : 0;
+      const int k0 = kbu * kBlockK + chunk * 8;
+      g4[j] = make_uint4(0, 0, 0, 0);
+      if (gain != nullptr && u < hi) g4[j] = __ldg(reinterpret_cast<const uint4*>(gain + k0));
 #pragma unroll
-      for (int j = 0; j < D; ++j) {
-        const bool have = base + j >= 0 && base + j < total;
-        const int kbu = have ? unit_at(base + j) % d.KB : 0;
-        const int k0 = kbu * kBlockK + chunk * 8;
-        g4[j] = make_uint4(0, 0, 0, 0);
-        if (src.gain != nullptr && have) g4[j] = __ldg(reinterpret_cast<const uint4*>(src.gain + k0));
-#pragma unroll
-        for (int i = 0; i < NPL; ++i) {
-          const int r = row0 + 4 * (q * NPL + i);
-          off[j][i] = -1;
-          if (EXPERT) sc[EXPERT ? j : 0][EXPERT ? i : 0] = 0.f;
-          if (have && r < p.B) {
-            if (EXPERT) {
-              const int slot = kbu / src.per;
-              off[j][i] = (slot * kMaxBatch + r) * p.Ie + (kbu % src.per) * kBlockK + chunk * 8;
-              sc[EXPERT ? j : 0][EXPERT ? i : 0] = ldcg_f32(src.wsc + slot * kMaxBatch + r);
-            } else {
-              off[j][i] = r * d.K + k0;
-            }
+      for (int i = 0; i < NPL; ++i) {
+        const int r = row0 + 4 * i;
+        v[j][i] = make_uint4(0, 0, 0, 0);
+        if (EXPERT) sc[EXPERT ? j : 0][EXPERT ? i : 0] = 0.f;
+        if (u < hi && r < p.B) {
+          if (EXPERT) {
+            const int slot = kbu / per;
+            v[j][i] = ldcg_u4(src + ((size_t)slot * kMaxBatch + r) * p.Ie + (kbu % per) * kBlockK + chunk * 8);
+            sc[EXPERT ? j : 0][EXPERT ? i : 0] = ldcg_f32(wsc + slot * kMaxBatch + r);
+          } else {
+            v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
           }
         }
       }
-      // fetch until every word of the pass carries the tag
-      const long long tp0 = clock64();
-      for (unsigned it = 1;; ++it) {
-        bool ok = true;
+    }
 #pragma unroll
-        for (int j = 0; j < D; ++j)
+    for (int j = 0; j < D; ++j) {
+      const int u = base + j;
+      if (u >= hi) break;
+      const unsigned nu = n + (unsigned)(u - lo);
+      const int s = (int)(nu & (unsigned)(kStages - 1));
+      const long long t0 = tr ? clock64() : 0;
+      const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / (unsigned)kStages) - 1u) & 1u, ph, 5);
+      const long long t1 = tr ? clock64() : 0;
+      w_slot += t1 - t0;
+      if (!ok) continue;
+      unsigned char* dst = c.smem + p.off_stages + s * p.stage_bytes + kABytes;
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4[j]);
 #pragma unroll
-          for (int i = 0; i < NPL; ++i) {
-            va[j][i] = vb[j][i] = make_uint4(0, 0, 0, 0);
-            if (off[j][i] >= 0) {
-              va[j][i] = poll_ld_u4(src.words + off[j][i]);
-              vb[j][i] = poll_ld_u4(src.words + off[j][i] + 4);
-            }
+      for (int i = 0; i < NPL; ++i) {
+        const int r = row0 + 4 * i;
+        if (gain != nullptr && r < p.B) {
+          const float f = rs[r];
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v[j][i]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float a = bf16_round(bf_lo(w[q]) * f) * bf_lo(gw[q]);
+            const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
+            w[q] = pack_bf16x2(a, b);
           }
-        if (src.checked) {
+        } else if (EXPERT) {
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v[j][i]);
+          const float f = sc[EXPERT ? j : 0][EXPERT ? i : 0];
 #pragma unroll
-          for (int j = 0; j < D; ++j)
-#pragma unroll
-            for (int i = 0; i < NPL; ++i)
-              if (off[j][i] >= 0) ok = ok && tags4_ok(va[j][i], src.tagw) && tags4_ok(vb[j][i], src.tagw);
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf_lo(w[q]) * f, bf_hi(w[q]) * f);
         }
-        if (__all_sync(kFullMask, ok)) break;
-        if ((it & 7u) == 0u && __any_sync(kFullMask, poll_expired(c, tp0, ph, va[0][0].x >> 16, src.tagw >> 16, 5))) return;
+        *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[j][i];
       }
-      if (q == 0 && first_group && base <= 0 && (st & 31) == 0) trace_put(p, ph, 0);
-      first_group = false;
-#pragma unroll
-      for (int j = 0; j < D; ++j) {
-        if (base + j < 0 || base + j >= total) continue;
-        const unsigned nu = g * (unsigned)D + (unsigned)j;
-        const int s = (int)(nu & (unsigned)(kStages - 1));
-        const long long t0 = tr ? clock64() : 0;
-        if (q == 0) slot_ok[j] = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / (unsigned)kStages) - 1u) & 1u, ph, 5);
-        const long long t1 = tr ? clock64() : 0;
-        w_slot += t1 - t0;
-        if (!slot_ok[j]) continue;
-        unsigned char* dst = c.smem + p.off_stages + s * p.stage_bytes + kABytes;
-        const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4[j]);
-#pragma unroll
-        for (int i = 0; i < NPL; ++i) {
-          const int r = row0 + 4 * (q * NPL + i);
-          uint4 v = untag8(va[j][i], vb[j][i]);
-          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
-          if (src.gain != nullptr && r < p.B) {
-            const float f = rs[r];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              const float a = bf16_round(bf_lo(w[x]) * f) * bf_lo(gw[x]);
-              const float b = bf16_round(bf_hi(w[x]) * f) * bf_hi(gw[x]);
-              w[x] = pack_bf16x2(a, b);
-            }
-          } else if (EXPERT) {
-            const float f = sc[EXPERT ? j : 0][EXPERT ? i : 0];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) w[x] = pack_bf16x2(bf_lo(w[x]) * f, bf_hi(w[x]) * f);
-          }
-          *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
-        }
-        if (q == PASSES - 1) {
-          fence_async_smem();
-          mbar_arrive1(c.b_full(s));
-        }
-        if (tr) w_fill += clock64() - t1;
-      }
+      fence_async_smem();
+      mbar_arrive1(c.b_full(s));
+      if (tr) w_fill += clock64() - t1;
     }
   }
   if (st == 0) {
@@ -609,108 +467,645 @@ static __device__ __noinline__ void stage_units(const Ctx& c, int ph, const Phas
   }
 }
 
-// Reciprocal RMS of every row of the residual stream: the producing residual phase left one record {sum of squares,
-// tag} per (row tile, row); thread st < B adds its row's records in tile order (sixteen per round trip).
-__device__ __forceinline__ void stage_rs(const Ctx& c, int ph, int st, unsigned tag, float* rs) {
-  const BParams& p = *c.p;
-  if (st >= p.Bpad) return;
-  if (st >= p.B) { rs[st] = 0.f; return; }
-  float tot = 0.f;
-  const int nt = (p.H + kTileRows - 1) / kTileRows;
-  const long long t0 = clock64();
-  for (int tb = 0; tb < nt; tb += 16) {
-    unsigned long long v[16];
-    for (unsigned it = 1;; ++it) {
-      bool ok = true;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = tb + j < nt ? poll_ld_rec(p.ss_rec + (size_t)(tb + j) * kMaxBatch + st) : 0ull;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) ok = ok && (tb + j >= nt || rec_ok(v[j], tag));
-      if (ok) break;
-      if ((it & 7u) == 0u && poll_expired(c, t0, ph, (unsigned)(v[0] >> 32), tag, 6)) { rs[st] = 0.f; return; }
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) tot += tb + j < nt ? rec_val(v[j]) : 0.f;
-  }
-  rs[st] = rsqrtf(tot / (float)p.H + p.eps);
-}
-
-static __device__ __noinline__ void stage_phase(const Ctx& c, int ph, int kind, int st, unsigned& n) {
+__device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int st, unsigned& n) {
   // st: thread index inside the stager group, 0..127
   const BParams& p = *c.p;
   const int layer = phase_layer(p, ph);
-  named_bar(kBarStg, 128);   // every stager is done with the phase before: its rs factors and control word are free
-  if (is_expert_kind(kind)) {
-    if (st == 0) c.ctl[kCNeStg] = (unsigned)expert_count(c, ph);
-    named_bar(kBarStg, 128);
+  if (st == 0) {
+    bool needed;
+    const bool ok = phase_dependency(c, ph, needed);
+    (void)ok;
+    if (is_expert_kind(kind)) c.ctl[kCNeStg] = (unsigned)expert_count(c, ph);
+    trace_put(p, ph, 0);
   }
+  named_bar(kBarStg, 128);
   const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? (int)c.ctl[kCNeStg] : 0);
   int lo, hi;
   unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, (int)gridDim.x), (int)blockIdx.x, lo, hi);
   const bool normed = phase_normed(kind);
   float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
-  if (hi > lo) {
-    if (normed) stage_rs(c, ph, st, tag32(p, hidden_source(kind, ph)), rs);
+  if (normed) {
+    if (st < p.Bpad) {
+      float tot = 0.f;
+      const int nt = (p.H + kTileRows - 1) / kTileRows;
+      for (int t0 = 0; t0 < nt; t0 += 16) {   // sixteen partial sums per round trip, added in tile order
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = t0 + j < nt ? ldcg_f32(p.ss + (t0 + j) * kMaxBatch + st) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) tot += v[j];
+      }
+      rs[st] = rsqrtf(tot / (float)p.H + p.eps);
+    }
     named_bar(kBarStg, 128);
-    StageSrc src;
-    const int sph = normed ? hidden_source(kind, ph) : ph - 1;
-    src.words = kind == kOproj ? p.t_attn : kind == kDown ? p.t_silu : kind == kEDown ? p.t_esilu : p.t_hid;
-    src.tagw = tag16(p, sph) << 16;
-    src.checked = !(kind == kEDown && sph < p.phase_begin);
-    src.gain = !normed ? nullptr
-             : kind == kQkv ? p.attn_norm + (size_t)layer * p.H
-             : kind == kLmHead ? p.lm_norm : p.mlp_norm + (size_t)layer * p.H;
-    src.wsc = kind == kEDown ? p.moe_w : nullptr;
-    src.per = kind == kEDown ? p.Ie / kBlockK : 0;
-    const UnitRuns R = unit_runs(lo, hi, d.KB);
-    const int total = hi - lo;
+  }
+  const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : kind == kEDown ? p.esilu : p.hidden;
+  const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
+                       : kind == kLmHead ? p.lm_norm : p.mlp_norm + (size_t)layer * p.H;
+  const int per = kind == kEDown ? p.Ie / kBlockK : 0;
+  const float* wsc = kind == kEDown ? p.moe_w : nullptr;
+  if (hi > lo) {
+    const uint16_t* gn = normed ? gain : nullptr;
     if (kind == kEDown) {
       switch (p.Bpad) {
-        case 16: stage_units<4, 1, 2, true>(c, ph, d, R, total, st, n, src, rs); break;
-        case 32: stage_units<8, 1, 1, true>(c, ph, d, R, total, st, n, src, rs); break;
-        case 48: stage_units<6, 2, 1, true>(c, ph, d, R, total, st, n, src, rs); break;
-        default: stage_units<8, 2, 1, true>(c, ph, d, R, total, st, n, src, rs); break;
+        case 16: stage_units<4, 2, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+        case 32: stage_units<8, 2, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+        case 48: stage_units<12, 1, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
+        default: stage_units<16, 1, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
       }
     } else {
       switch (p.Bpad) {
-        case 16: stage_units<4, 1, 2, false>(c, ph, d, R, total, st, n, src, rs); break;
-        case 32: stage_units<8, 1, 1, false>(c, ph, d, R, total, st, n, src, rs); break;
-        case 48: stage_units<6, 2, 1, false>(c, ph, d, R, total, st, n, src, rs); break;
-        default: stage_units<8, 2, 1, false>(c, ph, d, R, total, st, n, src, rs); break;
+        case 16: stage_units<4, 2, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        case 32: stage_units<8, 2, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        case 48: stage_units<12, 1, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        default: stage_units<16, 1, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
       }
     }
   }
   n += (unsigned)(hi - lo);
 }
 
-}  // namespace qmkb
+// ------------------------------------------------------------------------------------------------
+// epilogues (128 threads, e = thread index in the group) on the fp32 tile exch[128][65]
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned short silu_mul(float up, float gate) {
+  // fused_mlp_upgate (operations.py:265-282): both products rounded to bf16, SiLU rounded, product rounded
+  const float g = bf16_round(gate);
+  const float sl = bf16_round(g / (1.0f + __expf(-g)));
+  return f32_to_bf16_bits(sl * bf16_round(up));
+}
+__device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, int row) {
+  return ((unsigned long long)float_ordered_bits(bf16_bits_to_f32(bits)) << 32) | (0xffffffffu - (unsigned)row);
+}
 
-#include "qmk_batch_epilogue.cuh"
-#include "qmk_batch_attention.cuh"
+__device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, int t, int e) {
+  const BParams& p = *c.p;
+  float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
+  const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
+  const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
+  const int layer = phase_layer(p, ph);
+  const int B = p.B;
+  switch (kind) {
+    case kQkv: {
+      // A thread owns (sequence b, eight consecutive rows): four RoPE pairs of one head of Q, K or V.  Everything it
+      // reads or writes in global memory is a 16-byte piece; lanes 0-15 / 16-31 of a warp hold the sixteen row
+      // groups of one sequence, so the per-head sums of squares of the Q/K norm are warp shuffles.
+      const int rg = e & 15;
+      const int row = t * kTileRows + rg * 8;
+      const int kdim = p.NKV * p.HD;
+      const bool in_range = row < p.QKV_ROWS;
+      const bool is_v = row >= p.QDIM + kdim;
+      const bool is_k = !is_v && row >= p.QDIM;
+      const int d0 = row % p.HD;
+      const uint16_t* nw = (is_v || !in_range) ? nullptr : (is_k ? p.k_norm : p.q_norm);
+      float wn[8];
+      if (nw != nullptr) {
+        const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(nw + (size_t)layer * p.HD + d0));
+        const uint32_t* ww = reinterpret_cast<const uint32_t*>(&w4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { wn[2 * j] = bf_lo(ww[j]); wn[2 * j + 1] = bf_hi(ww[j]); }
+      }
+      const int nit = (B + 7) / 8;
+#pragma unroll 1
+      for (int i = 0; i < nit; ++i) {
+        const int b = (e >> 4) + 8 * i;
+        const bool live = in_range && b < B && act_s[b] != 0;
+        const int bb = b < B ? b : 0;
+        const int pos = pos_s[bb];
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = bf16_round(exch[(rg * 8 + j) * p.exch_stride + bb]);
+        if (p.q_norm != nullptr) {
+          // _per_head_rms_norm (Qwen3 operations.py:52-63) on the bf16-rounded projection, fp32 until the end
+          float ssq = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ssq += x[j] * x[j];
+          const int lanes = p.HD / 8;   // row groups per head: 8 or 16
+          for (int o = 1; o < lanes; o <<= 1) ssq += __shfl_xor_sync(kFullMask, ssq, o);
+          if (nw != nullptr) {
+            const float f = rsqrtf(ssq / (float)p.HD + p.qk_eps);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = bf16_round(wn[j] * (x[j] * f));
+          }
+        }
+        if (!live) continue;
+        uint4 o4;
+        if (is_v) {
+          o4.x = pack_bf16x2(x[0], x[1]); o4.y = pack_bf16x2(x[2], x[3]);
+          o4.z = pack_bf16x2(x[4], x[5]); o4.w = pack_bf16x2(x[6], x[7]);
+        } else {
+          const float4* cp = reinterpret_cast<const float4*>(p.rope_cos + (size_t)pos * p.HD + d0);
+          const float4* sp = reinterpret_cast<const float4*>(p.rope_sin + (size_t)pos * p.HD + d0);
+          const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+          const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          float y[8];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {   // pair (2m, 2m+1): rotate_half gives (-odd, even)
+            y[j] = x[j] * cs[j] - x[j + 1] * sn[j];
+            y[j + 1] = x[j + 1] * cs[j + 1] + x[j] * sn[j + 1];
+          }
+          o4.x = pack_bf16x2(y[0], y[1]); o4.y = pack_bf16x2(y[2], y[3]);
+          o4.z = pack_bf16x2(y[4], y[5]); o4.w = pack_bf16x2(y[6], y[7]);
+        }
+        if (!is_k && !is_v) {
+          *reinterpret_cast<uint4*>(p.q_post_rope + (size_t)b * p.QDIM + row) = o4;
+        } else {
+          const int col = is_k ? row - p.QDIM : row - p.QDIM - kdim;
+          uint16_t* cache = is_k ? p.k_cache : p.v_cache;
+          *reinterpret_cast<uint4*>(cache + (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride +
+                                    (size_t)pos * p.kv_seq_stride + col) = o4;
+        }
+      }
+      break;
+    }
+    case kRouter: {
+      // fused_router (qwen1_5_moe_a2_7b/.../fused/operations.py:175-194): fp32 softmax over all experts, the k largest
+      // probabilities as they are (no renormalisation), lowest index first on equal values.  Column b of the tile is
+      // overwritten by row b's selection (probability, 0 elsewhere); then the distinct experts of the step are listed
+      // in ascending order and every (selected expert, row) gets its weight for the expert down-projection.
+      const int E = p.E;
+      // tpr consecutive lanes share a row: each takes the experts x = q, q + tpr, ...; maxima, sums and the k winners
+      // are combined with shuffles.  A winner is marked by negating its (positive) exponential in place.
+      const int tpr = p.Bpad <= 16 ? 8 : (p.Bpad <= 32 ? 4 : 2);
+      const int b = e / tpr, q = e % tpr;
+      const bool rowok = b < p.Bpad;
+      const int bb = rowok ? b : 0;
+      const bool act = b < B && act_s[bb] != 0;
+      float mx = -INFINITY;
+      for (int x = q; x < E; x += tpr) mx = fmaxf(mx, exch[x * p.exch_stride + bb]);
+      for (int o = 1; o < tpr; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
+      float sum = 0.f;
+      for (int x = q; x < E; x += tpr) {
+        const float pe = __expf(exch[x * p.exch_stride + bb] - mx);
+        if (rowok) exch[x * p.exch_stride + bb] = pe;
+        sum += pe;
+      }
+      for (int o = 1; o < tpr; o <<= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
+      const float inv = 1.0f / sum;
+      for (int j = 0; j < p.topk; ++j) {
+        float best = -1.f;
+        int bi = E;
+        for (int x = q; x < E; x += tpr) {
+          const float v = rowok ? exch[x * p.exch_stride + bb] : 0.f;
+          if (v > best) { best = v; bi = x; }
+        }
+        for (int o = 1; o < tpr; o <<= 1) {
+          const float ob = __shfl_xor_sync(kFullMask, best, o);
+          const int oi = __shfl_xor_sync(kFullMask, bi, o);
+          if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (rowok && bi < E && bi % tpr == q) exch[bi * p.exch_stride + bb] = -best;
+      }
+      if (rowok)
+        for (int x = q; x < E; x += tpr) {
+          const float v = exch[x * p.exch_stride + bb];
+          exch[x * p.exch_stride + bb] = (act && v < 0.f) ? -v * inv : 0.f;
+        }
+      named_bar(kBarEpi, 128);
+      int* slot_of = reinterpret_cast<int*>(c.smem + Smem::kOffHs);   // [128] (the prologue's scratch, free now)
+      if (e < E) {
+        bool any = false;
+        for (int b = 0; b < B; ++b) any |= exch[e * p.exch_stride + b] > 0.f;
+        slot_of[e] = any ? 1 : 0;
+      }
+      named_bar(kBarEpi, 128);
+      if (e == 0) {
+        int n = 0;
+        for (int x = 0; x < E; ++x) {
+          if (slot_of[x]) { p.moe_elist[n] = x; slot_of[x] = n++; } else slot_of[x] = -1;
+        }
+        *p.moe_ne = n;
+        atomicAdd(p.moe_ne_sum, (unsigned long long)n);
+      }
+      named_bar(kBarEpi, 128);
+      if (e < E && slot_of[e] >= 0)
+        for (int b = 0; b < kMaxBatch; ++b) p.moe_w[slot_of[e] * kMaxBatch + b] = b < B ? exch[e * p.exch_stride + b] : 0.f;
+      break;
+    }
+    case kEUpGate: {
+      // fused_routed_expert_upgate (operations.py:197-219): gate and up rounded to bf16 (a bf16 linear), SiLU(gate) * up
+      // in fp32, one rounding.  Tile rows 0..63 are gate rows, 64..127 the up rows of the same units of one expert.
+      const int per = p.Ie / kBlockK;
+      const int slot = t / per, lt = t % per;
+      const int u = e & 63, half = e >> 6;
+      const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
+      for (int b = b0; b < b1 && b < B; ++b) {
+        const float g = bf16_round(exch[u * p.exch_stride + b]), up = bf16_round(exch[(64 + u) * p.exch_stride + b]);
+        const float v = act_s[b] ? (g / (1.0f + __expf(-g))) * up : 0.f;
+        p.esilu[((size_t)slot * kMaxBatch + b) * p.Ie + lt * (kTileRows / 2) + u] = f32_to_bf16_bits(v);
+      }
+      break;
+    }
+    case kOproj:
+    case kEDown:
+    case kDown: {
+      // hidden[b, row] = bf16(hidden + bf16(projection)), zero projection for inactive rows
+      // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295).
+      // Same (sequence, eight rows) ownership: one 16-byte load and store of the residual stream per item, all loads
+      // issued first; the sums of squares for the next RMSNorm are reduced over the sixteen row groups by shuffles.
+      const int rg = e & 15;
+      const int row = t * kTileRows + rg * 8;
+      const bool in_range = row < p.H;
+      const int nit = (B + 7) / 8;
+      uint4 oldv[kMaxBatch / 8];
+#pragma unroll
+      for (int i = 0; i < kMaxBatch / 8; ++i) {
+        const int b = (e >> 4) + 8 * i;
+        oldv[i] = (i < nit && in_range && b < B) ? ldcg_u4(p.hidden + (size_t)b * p.H + row) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxBatch / 8; ++i) {
+        if (i < nit) {
+          const int b = (e >> 4) + 8 * i;
+          const int bb = b < B ? b : 0;
+          const bool act = b < B && act_s[bb] != 0;
+          const uint32_t* ow = reinterpret_cast<const uint32_t*>(&oldv[i]);
+          float nv[8], sq = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float old = (j & 1) ? bf_hi(ow[j >> 1]) : bf_lo(ow[j >> 1]);
+            const float add = act ? bf16_round(exch[(rg * 8 + j) * p.exch_stride + bb]) : 0.f;
+            nv[j] = bf16_round(old + add);
+            sq += nv[j] * nv[j];
+          }
+          if (in_range && b < B) {
+            uint4 o4;
+            o4.x = pack_bf16x2(nv[0], nv[1]); o4.y = pack_bf16x2(nv[2], nv[3]);
+            o4.z = pack_bf16x2(nv[4], nv[5]); o4.w = pack_bf16x2(nv[6], nv[7]);
+            *reinterpret_cast<uint4*>(p.hidden + (size_t)b * p.H + row) = o4;
+          } else {
+            sq = 0.f;
+          }
+#pragma unroll
+          for (int o = 1; o < 16; o <<= 1) sq += __shfl_xor_sync(kFullMask, sq, o);
+          if (rg == 0 && b < B) p.ss[t * kMaxBatch + b] = sq;
+        }
+      }
+      break;
+    }
+    case kUpGate: {
+      const int u = e & 63, half = e >> 6;
+      const int unit = t * (kTileRows / 2) + u;
+      if (unit < p.I) {
+        const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
+        for (int b = b0; b < b1 && b < B; ++b) {
+          const unsigned short bits =
+              act_s[b] ? silu_mul(exch[u * p.exch_stride + b], exch[(64 + u) * p.exch_stride + b]) : (unsigned short)0;
+          p.silu_out[(size_t)b * p.I + unit] = bits;
+        }
+      }
+      break;
+    }
+    default: {   // LM head: logits and the per-row arg-max (lowest index on ties)
+      const int row = t * kTileRows + e;
+      if (row < p.vocab) {
+        for (int b = 0; b < B; ++b) {
+          const float v = act_s[b] ? exch[e * p.exch_stride + b] : -1e9f;
+          p.logits[(size_t)b * p.vocab + row] = f32_to_bf16_bits(v);
+        }
+      }
+      if (e < B) {
+        unsigned long long best = 0ull;
+        const int nrow = min(kTileRows, p.vocab - t * kTileRows);
+        for (int r = 0; r < nrow; ++r) {
+          const float v = act_s[e] ? exch[r * p.exch_stride + e] : -1e9f;
+          const unsigned long long key = argmax_key(f32_to_bf16_bits(v), t * kTileRows + r);
+          best = key > best ? key : best;
+        }
+        atomicMax(p.argmax_key + e, best);
+      }
+      break;
+    }
+  }
+}
 
-namespace qmkb {
+__device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, uint32_t tmem, int e, unsigned& sg) {
+  // e: thread index in the epilogue group; the warp's lane quarter of tensor memory is (warp % 4)
+  const BParams& p = *c.p;
+  const int cta = (int)blockIdx.x;
+  int ne = 0;
+  if (is_expert_kind(kind)) {
+    if (e == 0) c.ctl[kCNeEpi] = (unsigned)expert_count(c, ph);
+    named_bar(kBarEpi, 128);
+    ne = (int)c.ctl[kCNeEpi];
+  }
+  const PhaseDims d = phase_dims(p, kind, ne);
+  const int U = d.T * d.KB;
+  if (U == 0) return;
+  const int G = phase_ctas(kind, U, (int)gridDim.x);   // CTAs that share this phase's units
+  int lo, hi;
+  unit_range(U, G, cta, lo, hi);
+  float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
+  const int quarter = c.warp & 3;
+  const int r = quarter * 32 + c.lane;           // accumulator row (= tile row) of this thread
+  const int nchunk = p.Bpad / 16;
+  int u = lo;
+#pragma unroll 1
+  while (u < hi) {
+    const int t = u / d.KB, kb_lo = u - t * d.KB;
+    const int u_end = min(hi, (t + 1) * d.KB);
+    const bool full = kb_lo == 0 && u_end == (t + 1) * d.KB;
+    const unsigned buf = sg & 1u;
+    const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
+    if (e == 0 && u == lo) trace_put(p, ph, 1);
+    // accumulator of a tile that is split over several CTAs: the slot of the CTA that owns the tile's first unit
+    // (a CTA owns the first unit of at most one split tile, so the slot is the tile's alone)
+    const int c_first = unit_owner(U, G, t * d.KB);
+    long long* slot = p.ws + (size_t)c_first * (size_t)(kTileRows * p.Bpad);
+    if (ok) {
+      tmem_fence_after_sync();
+#pragma unroll 1
+      for (int ch = 0; ch < nchunk; ++ch) {
+        uint32_t v[16];
+        tmem_ld16(v, tmem + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)p.Bpad + ch * 16);
+        tmem_wait_ld();
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) exch[r * p.exch_stride + ch * 16 + j] = __uint_as_float(v[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) red_add_s64(slot + (size_t)(ch * 16 + j) * kTileRows + r, to_fixed(__uint_as_float(v[j])));
+        }
+      }
+      tmem_fence_before_sync();
+      mbar_arrive1(c.acc_empty(buf));
+    }
+    ++sg;
+    // One thread decides for the group whether this CTA finishes the tile: a full segment always does; a partial one
+    // has added its tile to the tile's accumulator at L2, takes a ticket, and the last of the tile's segments to
+    // arrive reads the sum (and leaves the accumulator zeroed for its next user, a phase later).
+    if (!full) __threadfence();
+    named_bar(kBarEpi, 128);
+    if (e == 0) {
+      unsigned fin = 0u;
+      if (ok && !c.aborted()) {
+        if (full) {
+          fin = 1u;
+        } else {
+          const unsigned old = atom_add_acq_rel_gpu(p.tile_tickets + t, 1u);
+          fin = old + 1u == (unsigned)tile_segments(U, G, d.KB, t) ? 1u : 0u;
+          if (fin) p.tile_tickets[t] = 0u;
+        }
+      }
+      c.ctl[kCFlagEpi] = fin;
+    }
+    named_bar(kBarEpi, 128);
+    const bool run = c.ctl[kCFlagEpi] != 0u;
+    if (run && !full) {
+      __threadfence();
+      float* o = exch + r * p.exch_stride;
+#pragma unroll 1
+      for (int ch = 0; ch < nchunk; ++ch) {
+        long long x[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = exch_zero_s64(slot + (size_t)(ch * 16 + j) * kTileRows + r);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[ch * 16 + j] = (float)((double)x[j] * kFixInv);
+      }
+    }
+    named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
+    if (run) epilogue_tile(c, ph, kind, t, e);   // (contains no barrier)
+    named_bar(kBarEpi, 128);           // the exchange tile is free again
+    u = u_end;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// attention: eight workers per CTA, one (sequence, kv head, key range) item per warp at a time
+// ------------------------------------------------------------------------------------------------
+template <int HD, int GQ>
+__device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw) {
+  const BParams& p = *c.p;
+  constexpr int LPR = HD / 8;          // lanes per K/V row (16 bytes each)
+  constexpr int KPL = 32 / LPR;        // keys per load instruction
+  const int lane = c.lane;
+  const int sub = lane / LPR, dl = lane % LPR;
+  const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
+  const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
+  const int NW = (int)gridDim.x * 8, gw = (int)blockIdx.x * 8 + aw;
+  const int Tmax = (int)c.ctl[kCTmax];
+  const int seqs = p.B * p.NKV;
+  int ck, nch;
+  attn_plan(Tmax, seqs, NW, ck, nch);
+  const int items = seqs * nch;
+  constexpr int REC = GQ * (HD + 2);
+#pragma unroll 1
+  for (int item = gw; item < items; item += NW) {
+    const int ch = item % nch, sq = item / nch;
+    const int kvh = sq % p.NKV, b = sq / p.NKV;
+    const int T = pos_s[b] + 1;
+    const int nsplit = (T + ck - 1) / ck;
+    uint16_t* outp = p.attn_out + (size_t)b * p.QDIM + (size_t)kvh * GQ * HD;
+    if (!act_s[b]) {   // fused_decode_attention zeroes the output of an inactive row (operations.py:226-231)
+      if (ch == 0)
+        for (int i = lane; i < GQ * HD / 8; i += 32) reinterpret_cast<uint4*>(outp)[i] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    if (ch >= nsplit) continue;
+    const int k_lo = ch * ck, k_hi = min(T, k_lo + ck);
+    float q[GQ][8], acc[GQ][8], m[GQ], l[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const uint4 qv = ldcg_u4(p.q_post_rope + (size_t)b * p.QDIM + (size_t)(kvh * GQ + g) * HD + dl * 8);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        q[g][2 * j] = bf_lo(w[j]) * p.scale_log2e;
+        q[g][2 * j + 1] = bf_hi(w[j]) * p.scale_log2e;
+      }
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+    }
+    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
+    // Keys are taken in half-blocks of NLD row pieces per lane (16 keys at head_dim 64, 8 at 128), double-buffered in
+    // registers: the loads of the next half-block are in flight while this one is multiplied.
+    constexpr int NLD = 4;
+    constexpr int KBK = NLD * KPL;
+    auto load_block = [&](uint4 (&kk)[NLD], uint4 (&vv)[NLD], int ks) {
+#pragma unroll
+      for (int i = 0; i < NLD; ++i) {
+        const int k = ks + i * KPL + sub;
+        kk[i] = k < k_hi ? ldcg_u4(p.k_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < NLD; ++i) {
+        const int k = ks + i * KPL + sub;
+        vv[i] = k < k_hi ? ldcg_u4(p.v_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    auto use_block = [&](const uint4 (&kk)[NLD], const uint4 (&vv)[NLD], int ks) {
+#pragma unroll
+      for (int i = 0; i < NLD; ++i) {
+        const bool valid = ks + i * KPL + sub < k_hi;
+        const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kk[i]);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vv[i]);
+        float kf[8], vf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          kf[2 * j] = bf_lo(kw[j]); kf[2 * j + 1] = bf_hi(kw[j]);
+          vf[2 * j] = bf_lo(vw[j]); vf[2 * j + 1] = bf_hi(vw[j]);
+        }
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s += q[g][j] * kf[j];
+#pragma unroll
+          for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(kFullMask, s, o);
+          if (valid) {
+            const float mn = fmaxf(m[g], s);
+            const float corr = exp2f(m[g] - mn);     // 0 when m was -inf
+            const float pe = exp2f(s - mn);
+            l[g] = l[g] * corr + pe;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pe * vf[j];
+            m[g] = mn;
+          }
+        }
+      }
+    };
+    uint4 ka[NLD], va[NLD], kb2[NLD], vb2[NLD];
+    load_block(ka, va, k_lo);
+#pragma unroll 1
+    for (int k0 = k_lo; k0 < k_hi; k0 += 2 * KBK) {
+      load_block(kb2, vb2, k0 + KBK);          // (past the end: nothing is loaded, nothing is used)
+      use_block(ka, va, k0);
+      load_block(ka, va, k0 + 2 * KBK);
+      use_block(kb2, vb2, k0 + KBK);
+    }
+    // merge the KPL key sub-streams (lanes with equal dl)
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        const float mo = __shfl_xor_sync(kFullMask, m[g], o);
+        const float lo_ = __shfl_xor_sync(kFullMask, l[g], o);
+        const float mn = fmaxf(m[g], mo);
+        const float ca = mn == -INFINITY ? 0.f : exp2f(m[g] - mn);
+        const float cb = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+        l[g] = l[g] * ca + lo_ * cb;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float ao = __shfl_xor_sync(kFullMask, acc[g][j], o);
+          acc[g][j] = acc[g][j] * ca + ao * cb;
+        }
+        m[g] = mn;
+      }
+    }
+    if (nsplit == 1) {
+      if (sub == 0) {
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float inv = 1.0f / l[g];
+          uint4 o4;
+          o4.x = pack_bf16x2(acc[g][0] * inv, acc[g][1] * inv);
+          o4.y = pack_bf16x2(acc[g][2] * inv, acc[g][3] * inv);
+          o4.z = pack_bf16x2(acc[g][4] * inv, acc[g][5] * inv);
+          o4.w = pack_bf16x2(acc[g][6] * inv, acc[g][7] * inv);
+          *reinterpret_cast<uint4*>(outp + g * HD + dl * 8) = o4;
+        }
+      }
+      continue;
+    }
+    float* rec = p.attn_part + (size_t)item * REC;
+    if (sub == 0) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        float4* dst = reinterpret_cast<float4*>(rec + g * (HD + 2) + dl * 8);
+        // (HD + 2) * 4 bytes per head record keeps 8-byte alignment only: write as float2 pairs
+        float2* d2 = reinterpret_cast<float2*>(dst);
+        d2[0] = make_float2(acc[g][0], acc[g][1]);
+        d2[1] = make_float2(acc[g][2], acc[g][3]);
+        d2[2] = make_float2(acc[g][4], acc[g][5]);
+        d2[3] = make_float2(acc[g][6], acc[g][7]);
+        if (dl == 0) *reinterpret_cast<float2*>(rec + g * (HD + 2) + HD) = make_float2(m[g], l[g]);
+      }
+    }
+    __threadfence();
+    __syncwarp();
+    unsigned last = 0u;
+    if (lane == 0) {
+      const unsigned old = atom_add_acq_rel_gpu(p.attn_tickets + sq, 1u);
+      last = old == (unsigned)(nsplit - 1) ? 1u : 0u;
+      if (last) p.attn_tickets[sq] = 0u;
+    }
+    last = __shfl_sync(kFullMask, last, 0);
+    if (!last) continue;
+    __threadfence();
+    // merge the nsplit records of this (sequence, kv head): every lane takes (head, 8 dims) pieces and folds the
+    // records in split order (loads of four records in flight)
+    const float* recs = p.attn_part + (size_t)(sq * nch) * REC;
+    for (int piece = lane; piece < GQ * LPR; piece += 32) {
+      const int g = piece / LPR, dd = piece % LPR;
+      float M = -INFINITY, L = 0.f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int s = 0; s < nsplit; ++s) {
+        const float* rr = recs + (size_t)s * REC + g * (HD + 2);
+        const float2 ml = ldcg_f2(rr + HD);
+        float2 a[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = ldcg_f2(rr + dd * 8 + 2 * j);
+        const float mn = fmaxf(M, ml.x);
+        const float c0 = exp2f(M - mn), c1 = exp2f(ml.x - mn);
+        L = L * c0 + ml.y * c1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[2 * j] = o[2 * j] * c0 + a[j].x * c1;
+          o[2 * j + 1] = o[2 * j + 1] * c0 + a[j].y * c1;
+        }
+        M = mn;
+      }
+      const float inv = 1.0f / L;
+      uint4 o4;
+      o4.x = pack_bf16x2(o[0] * inv, o[1] * inv);
+      o4.y = pack_bf16x2(o[2] * inv, o[3] * inv);
+      o4.z = pack_bf16x2(o[4] * inv, o[5] * inv);
+      o4.w = pack_bf16x2(o[6] * inv, o[7] * inv);
+      *reinterpret_cast<uint4*>(outp + g * HD + dd * 8) = o4;
+    }
+  }
+}
+
+__device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
+  const BParams& p = *c.p;
+  if (aw == 0 && c.lane == 0) {
+    bool needed;
+    const bool ok = phase_dependency(c, ph, needed);
+    c.ctl[kCFlagAttn] = ok ? 1u : 0u;
+    trace_put(p, ph, 0);
+  }
+  named_bar(kBarAttn, 256);
+  if (c.ctl[kCFlagAttn] != 0u) {
+    const int layer = phase_layer(p, ph), gq = p.NH / p.NKV;
+    if (p.HD == 64) {
+      if (gq == 4) attention_items<64, 4>(c, layer, aw);
+      else if (gq == 2) attention_items<64, 2>(c, layer, aw);
+      else attention_items<64, 1>(c, layer, aw);
+    } else {
+      if (gq == 4) attention_items<128, 4>(c, layer, aw);
+      else if (gq == 2) attention_items<128, 2>(c, layer, aw);
+      else attention_items<128, 1>(c, layer, aw);
+    }
+  }
+  __threadfence();
+  named_bar(kBarAttn, 256);
+  if (aw == 0 && c.lane == 0 && !c.aborted()) {
+    red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+    trace_put(p, ph, 5);
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
 // prologue / finalize (epilogue group)
 // ------------------------------------------------------------------------------------------------
-// Copies `n` bf16 (a multiple of 8) into tagged words.
-__device__ __forceinline__ void tag_row(uint32_t* dst, const uint16_t* src, int n, unsigned tagw, int e) {
-  for (int i = e; i < n / 8; i += 128) st_tagged8(dst + i * 8, ldcg_u4(src + i * 8), tagw);
-}
-
-static __device__ __noinline__ void prologue(const Ctx& c, int e) {
-  // What the first phase of the launch reads comes from the caller's buffers: rows b = cta, cta + G, ... are copied into
-  // the tagged scratch under the tag of "the phase before the first" -- the residual stream (optionally the embedding
-  // row of token_in[b]) with its sum of squares, and, when the launch starts in the middle of a layer, the first
-  // phase's own input (q and this position's K / V row, the attention output, or the SwiGLU output).
+__device__ __forceinline__ void prologue(const Ctx& c, int e) {
+  // rows b = cta, cta + G, ...: optional embedding of token_in[b], then the sum of squares of hidden[b]
   const BParams& p = *c.p;
   float* red = reinterpret_cast<float*>(c.smem + Smem::kOffHs);
-  const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
-  const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
   const int nt = (p.H + kTileRows - 1) / kTileRows;
-  const unsigned tagw = tag16(p, p.phase_begin - 1) << 16;
-  const unsigned rtag = tag32(p, p.phase_begin - 1);
-  const int kind0 = phase_kind(p, p.phase_begin), layer0 = phase_layer(p, p.phase_begin);
   for (int b = (int)blockIdx.x; b < p.B; b += (int)gridDim.x) {
     uint16_t* h = p.hidden + (size_t)b * p.H;
     const uint16_t* src = h;
@@ -723,7 +1118,6 @@ static __device__ __noinline__ void prologue(const Ctx& c, int e) {
     for (int i = e; i < p.H / 8; i += 128) {
       const uint4 v = ldcg_u4(src + i * 8);
       if (p.prologue == 2) reinterpret_cast<uint4*>(h)[i] = v;
-      st_tagged8(p.t_hid + (size_t)b * p.H + i * 8, v, tagw);
       const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
       for (int j = 0; j < 4; ++j) s += bf_lo(w[j]) * bf_lo(w[j]) + bf_hi(w[j]) * bf_hi(w[j]);
@@ -731,23 +1125,12 @@ static __device__ __noinline__ void prologue(const Ctx& c, int e) {
     s = warp_sum(s);
     if (c.lane == 0) red[e >> 5] = s;
     named_bar(kBarEpi, 128);
-    if (e < nt) st_rec(p.ss_rec + (size_t)e * kMaxBatch + b, make_rec(e == 0 ? red[0] + red[1] + red[2] + red[3] : 0.f, rtag));
+    if (e < nt) p.ss[e * kMaxBatch + b] = e == 0 ? red[0] + red[1] + red[2] + red[3] : 0.f;
     named_bar(kBarEpi, 128);
-    if (kind0 == kAttn) {
-      tag_row(p.t_q + (size_t)b * p.QDIM, p.q_post_rope + (size_t)b * p.QDIM, p.QDIM, tagw, e);
-      if (act_s[b]) {
-        const int kdim = p.NKV * p.HD;
-        const size_t row = (size_t)layer0 * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)pos_s[b] * p.kv_seq_stride;
-        tag_row(p.t_kv + ((size_t)b * 2 + 0) * kdim, p.k_cache + row, kdim, tagw, e);
-        tag_row(p.t_kv + ((size_t)b * 2 + 1) * kdim, p.v_cache + row, kdim, tagw, e);
-      }
-    } else if (kind0 == kOproj) {
-      tag_row(p.t_attn + (size_t)b * p.QDIM, p.attn_out + (size_t)b * p.QDIM, p.QDIM, tagw, e);
-    } else if (kind0 == kDown) {
-      tag_row(p.t_silu + (size_t)b * p.I, p.silu_out + (size_t)b * p.I, p.I, tagw, e);
-    }
   }
-  __threadfence();   // (push the tagged words out; nothing waits for this fence)
+  __threadfence();
+  named_bar(kBarEpi, 128);
+  if (e == 0) red_release_gpu_add(p.phase_done + 0, 1u);
 }
 
 __device__ __forceinline__ void finalize(const Ctx& c, int e) {
@@ -850,11 +1233,11 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
       } else if (epi) {
         if (gi == 0) trace_put(p, ph, 2);
         epilogue_phase(c, ph, kind, tmem, gi, sg);
-        if (gi == 0) trace_put(p, ph, 5);
-        if (kind == kLmHead) {   // the tokens are written once every CTA's logits and arg-max keys are out
-          __threadfence();
-          named_bar(kBarEpi, 128);
-          if (gi == 0 && !c.aborted()) red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+        __threadfence();
+        named_bar(kBarEpi, 128);
+        if (gi == 0 && !c.aborted()) {
+          red_release_gpu_add(p.phase_done + 1 + ph, 1u);
+          trace_put(p, ph, 5);
         }
       } else {
         stage_phase(c, ph, kind, gi, n);

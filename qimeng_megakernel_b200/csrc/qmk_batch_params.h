@@ -45,29 +45,20 @@ struct BParams {
   const unsigned char* active_mask;   // [B] or null (then every row is active)
   long long kv_layer_stride, kv_batch_stride, kv_seq_stride;   // elements
   // ---- library-owned scratch ----
-  // Hand-off between phases is by self-validating data: nothing is counted, nothing is fenced.  Activations that cross
-  // SMs are 32-bit words {bf16 value, 16-bit tag of (launch, producing phase)}; fp32 values travel as 64-bit records
-  // {fp32 bits, 32-bit tag}.  A consumer polls the data itself until every word carries the tag it expects.
-  uint32_t* t_hid;               // [kMaxBatch, H]          residual stream
-  uint32_t* t_q;                 // [kMaxBatch, QDIM]       q after RoPE
-  uint32_t* t_kv;                // [kMaxBatch, 2, NKV*HD]  this step's K row and V row
-  uint32_t* t_attn;              // [kMaxBatch, QDIM]       attention output
-  uint32_t* t_silu;              // [kMaxBatch, I]          SwiGLU output
-  uint32_t* t_esilu;             // [E, kMaxBatch, Ie]      SiLU(gate) * up of (expert slot, row) (MoE)
-  unsigned long long* ss_rec;    // [H/128, kMaxBatch]      sums of squares of the residual stream per row tile
-  unsigned long long* part_rec;  // [2, CTAs, Bpad, 128] fixed-point accumulators of split tiles (zero between uses)
-  unsigned* part_cnt;            // [2, CTAs]  contributions announced to a split tile's accumulator (zero between uses)
-  unsigned long long* attn_rec;  // [items, GQ * (HD + 2)]  split-KV partials (acc, max, sum)
-  unsigned long long* moe_ne_rec;   // [1] {number of distinct experts, tag}: published last by the router phase
+  long long* ws;                 // [CTAs, Bpad, 128] fixed-point accumulators of split tiles (zero between uses)
+  unsigned* tile_tickets;        // [row tiles]   arrivals of a tile's partial segments
+  float* ss;                     // [H/128, kMaxBatch]  sums of squares of the residual stream, per row tile
+  float* attn_part;              // [items, G, HD + 2]  split-KV partials (acc, max, sum)
+  unsigned* attn_tickets;        // [B * NKV]
   unsigned long long* argmax_key;   // [B]  (ordered logit bits << 32) | ~row
-  unsigned* phase_done;          // [1 + phases]  CTAs that finished the LM head (zeroed per launch; only that slot is used)
+  unsigned* phase_done;          // [1 + phases]  CTAs that finished the prologue / each phase (zeroed per launch)
   unsigned* status;              // [8]
-  unsigned* wait_log;            // [1 + 64 * 8]  count, then {CTA, warp, phase, detail, seen, expected, why, 0} of the waits that gave up
   // MoE (null / 0 otherwise): what the router phase leaves for the two expert phases of its layer
-  int* moe_ne;                   // [1]  distinct experts selected by the active rows of this step (host query)
+  int* moe_ne;                   // [1]  distinct experts selected by the active rows of this step
   int* moe_elist;                // [E]  their indices, ascending
   unsigned long long* moe_ne_sum; // [1]  distinct experts summed over every router phase since the last reset
   float* moe_w;                  // [E, kMaxBatch]  router weight of (slot, row), 0 where the row did not select it
+  uint16_t* esilu;               // [E, kMaxBatch, Ie]  SiLU(gate) * up of (slot, row), bf16
   unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off
   // ---- shape ----
   int H, I, NH, NKV, HD, QKV_ROWS, QDIM, num_layers, vocab;
@@ -78,9 +69,7 @@ struct BParams {
   int pos_limit;                 // min(kv_seq_len, rope_rows): an active row at or beyond it is switched off and reported
   int phase_begin, phase_end;
   int stages, stage_bytes, off_stages, exch_stride;   // shared-memory plan for this Bpad (smem_plan)
-  int prologue;                  // 0 none (failure test); 1 tag the first phase's inputs from the caller's buffers;
-                                 // 2 the same with hidden = embedding rows of token_in
-  unsigned epoch;                // number of this launch (per context): makes every launch's tags distinct
+  int prologue;                  // 0 none; 1 sums of squares of `hidden`; 2 embed token_in, then sums of squares
   int wait_first;                // failure test: the first phase waits for a dependency nothing publishes
   float eps, qk_eps, scale_log2e;
   long long timeout_cycles;

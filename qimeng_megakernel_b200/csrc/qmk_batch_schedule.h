@@ -34,26 +34,6 @@ QMKB_HD int num_phases(const BParams& p) { return p.ppl * p.num_layers + 1; }
 QMKB_HD bool phase_normed(int kind) {
   return kind == kQkv || kind == kUpGate || kind == kLmHead || kind == kRouter || kind == kEUpGate;
 }
-// Which phase produced the residual stream (hidden states and their sums of squares) that phase ph reads: the last
-// residual phase before it (down / expert-down projection of the layer before, or this layer's O-projection).  A result
-// below the first phase of the launch means: the launch's prologue, which tags the caller's buffers.
-QMKB_HD int hidden_source(int kind, int ph) {
-  switch (kind) {
-    case kOproj: case kEDown: return ph - 3;
-    case kDown: case kEUpGate: return ph - 2;
-    default: return ph - 1;     // QKV, up/gate, router, LM head
-  }
-}
-// Ordinal of a phase among the phases that multiply weights (attention does not): its parity selects which of the two
-// partial-record areas the phase's contributing segments write.  Two phases next to each other in this order never share
-// an area; two phases with the same parity are always separated by a phase that starts with an RMSNorm, which cannot
-// begin before every tile of the phases before it is finished, i.e. before every partial record has been read.
-QMKB_HD int gemm_ordinal(const BParams& p, int ph) {
-  const int per = p.ppl - 1;
-  if (ph >= p.ppl * p.num_layers) return per * p.num_layers;
-  const int i = ph % p.ppl;
-  return (ph / p.ppl) * per + (i == 0 ? 0 : i - 1);
-}
 // ne: number of distinct experts selected in this step (expert phases only; known once the layer's router is done)
 QMKB_HD PhaseDims phase_dims(const BParams& p, int kind, int ne = 0) {
   PhaseDims d;
@@ -93,37 +73,6 @@ QMKB_HD int unit_owner(int U, int G, int u) { return (int)((((long long)u + 1) *
 QMKB_HD int tile_segments(int U, int G, int KB, int t) {
   if (U < G) return KB;
   return unit_owner(U, G, (t + 1) * KB - 1) - unit_owner(U, G, t * KB) + 1;
-}
-
-// Order in which a CTA works through its units [lo, hi): first the HEAD segment of its last row tile (units of a tile
-// that other CTAs finish: a partial result that somebody else waits for, so it is produced first), then the row tiles
-// it owns completely, and last the TAIL segment of its first tile (the tile's last units: this CTA finishes that tile
-// from its own accumulator plus the partial results of the CTAs before it, which by then have long been written).
-// A range inside one tile is a single run.  Units inside a run are taken in ascending order.
-struct UnitRuns { int lo[3], hi[3]; };
-QMKB_HD UnitRuns unit_runs(int lo, int hi, int KB) {
-  UnitRuns r;
-  for (int i = 0; i < 3; ++i) r.lo[i] = r.hi[i] = 0;
-  if (lo >= hi) return r;
-  const int tl = lo / KB, th = (hi - 1) / KB;
-  if (tl == th) { r.lo[0] = lo; r.hi[0] = hi; return r; }
-  const int f0 = lo % KB == 0 ? lo : (tl + 1) * KB;    // first unit of the first complete tile
-  const int h0 = hi % KB == 0 ? hi : th * KB;          // first unit of the head segment
-  r.lo[0] = h0; r.hi[0] = hi;
-  r.lo[1] = f0; r.hi[1] = h0;
-  r.lo[2] = lo; r.hi[2] = f0;
-  return r;
-}
-// A segment [u0, u1) of row tile t (u1 <= (t + 1) * KB) is FULL when it holds all k-blocks of the tile; otherwise it
-// FINISHES the tile when it holds the tile's last unit, else it CONTRIBUTES a partial result.  A CTA has at most one
-// contributing and at most one finishing partial segment per phase.
-QMKB_HD bool seg_first(int u0, int KB) { return u0 % KB == 0; }
-QMKB_HD bool seg_last(int u1, int KB) { return u1 % KB == 0; }
-// The CTAs that contribute to row tile t, in ascending order: j = 0 .. tile_segments - 2 (the finisher is the last
-// segment and not listed).  With at least as many units as CTAs every CTA owns units and the contributors are
-// consecutive CTAs; with fewer, every unit has its own CTA.
-QMKB_HD int tile_contributor(int U, int G, int KB, int t, int j) {
-  return U < G ? unit_owner(U, G, t * KB + j) : unit_owner(U, G, t * KB) + j;
 }
 
 // Split-KV plan: keys per item `ck` (a multiple of 32) and items per (sequence, kv head) `nch`, for the longest

@@ -1,11 +1,10 @@
 // CPU replay of the batched kernel's schedule (qimeng_megakernel_b200/csrc/qmk_batch_schedule.h): for several
-// model shapes and grid sizes, walks every CTA's unit runs of every phase kind exactly as the device roles do
-// and checks that (1) every (row tile, k-block) unit is owned by exactly one CTA and appears exactly once in its runs,
-// and unit_owner agrees; (2) a CTA has at most one contributing and at most one finishing partial segment per phase
-// (a contributor writes ONE slot, keyed on the CTA); (3) every tile has exactly one segment that holds its last unit
-// (the finisher), and the contributors the finisher enumerates with tile_contributor are exactly the CTAs that wrote a
-// contributing segment of that tile, in ascending order; (4) the split-KV plan keeps its bounds.
-#include <algorithm>
+// model shapes and grid sizes, walks every CTA's unit range of every phase kind exactly as the device roles do
+// and checks that (1) every (row tile, k-block) unit is owned by exactly one CTA, and unit_owner agrees;
+// (2) a CTA has at most two partial segments per phase, and no two split tiles of a phase share the CTA that owns
+// their first unit, which is what the tile's accumulator slot is keyed on;
+// (3) the partial segments of a tile are exactly the CTAs unit_owner(first unit) .. unit_owner(last unit), which
+// is what the tile's ticket counts and what the last arriver sums; (4) the split-KV plan keeps its bounds.
 #include <cstdio>
 #include <map>
 #include <set>
@@ -20,60 +19,57 @@ static int fail(const char* what, int a = 0, int b = 0, int c = 0) {
   return 1;
 }
 
-static int check_phase(const BParams& p, int kind, int Gall, int ne = 0) {
-  const PhaseDims d = phase_dims(p, kind, ne);
+static int check_phase(const BParams& p, int kind, int G) {
+  const PhaseDims d = phase_dims(p, kind);
   if (d.K % kBlockK != 0 || d.T < 1 || d.KB < 1) return fail("dims", kind, d.K, d.T);
   const int U = d.T * d.KB;
-  const int G = phase_ctas(kind, U, Gall);   // CTAs that share the phase's units (the others have none)
   std::vector<int> owner(U, -1);
-  std::map<int, std::vector<int>> contrib_of_tile;   // tile -> CTAs with a contributing segment, in CTA order
-  std::map<int, int> finisher_of_tile;               // tile -> CTA that holds its last unit
+  std::map<int, std::vector<int>> partial_of_tile;   // tile -> CTAs with a partial segment
   for (int c = 0; c < G; ++c) {
     int lo, hi;
     unit_range(U, G, c, lo, hi);
     if (lo < 0 || hi > U || lo > hi) return fail("range", c, lo, hi);
-    const UnitRuns R = unit_runs(lo, hi, d.KB);
-    int n_contrib = 0, n_finish_partial = 0, seen = 0;
-    for (int r = 0; r < 3; ++r) {
-      if (R.lo[r] > R.hi[r] || (R.lo[r] < R.hi[r] && (R.lo[r] < lo || R.hi[r] > hi))) return fail("run bounds", c, r, kind);
-      int u = R.lo[r];
-      while (u < R.hi[r]) {   // the segment walk of the device roles
-        const int t = u / d.KB;
-        const int u_end = R.hi[r] < (t + 1) * d.KB ? R.hi[r] : (t + 1) * d.KB;
-        for (int x = u; x < u_end; ++x) {
-          if (owner[x] != -1) return fail("unit owned twice", x, owner[x], c);
-          owner[x] = c;
-          ++seen;
-          if (unit_owner(U, G, x) != c) return fail("unit_owner disagrees", x, unit_owner(U, G, x), c);
-        }
-        const bool first = seg_first(u, d.KB), last = seg_last(u_end, d.KB);
-        if (last) {
-          if (finisher_of_tile.count(t)) return fail("two finishers", t, c, kind);
-          finisher_of_tile[t] = c;
-          if (!first) ++n_finish_partial;
-          if (r == 0 && R.hi[1] > R.lo[1]) return fail("a finishing segment must not come first when other runs follow", c, t, kind);
-        } else {
-          ++n_contrib;
-          contrib_of_tile[t].push_back(c);
-          if (r != 0) return fail("a contributing segment must be the first run", c, r, kind);
-        }
-        u = u_end;
+    std::set<int> slots_used;
+    int u = lo;
+    while (u < hi) {   // the segment walk of epilogue_phase
+      const int t = u / d.KB, kb_lo = u - t * d.KB;
+      const int u_end = hi < (t + 1) * d.KB ? hi : (t + 1) * d.KB;
+      const bool full = kb_lo == 0 && u_end == (t + 1) * d.KB;
+      for (int x = u; x < u_end; ++x) {
+        if (owner[x] != -1) return fail("unit owned twice", x, owner[x], c);
+        owner[x] = c;
+        if (unit_owner(U, G, x) != c) return fail("unit_owner disagrees", x, unit_owner(U, G, x), c);
       }
+      if (!full) {
+        const int which = t == lo / d.KB ? 0 : 1;
+        if (!slots_used.insert(which).second) return fail("scratch slot used twice in a phase", c, t, which);
+        partial_of_tile[t].push_back(c);
+      }
+      u = u_end;
     }
-    if (seen != hi - lo) return fail("runs do not cover the range", c, seen, hi - lo);
-    if (n_contrib > 1 || n_finish_partial > 1) return fail("more than one partial segment of a kind", c, n_contrib, n_finish_partial);
   }
   for (int x = 0; x < U; ++x)
     if (owner[x] == -1) return fail("unit not owned", x, kind, G);
-  for (int t = 0; t < d.T; ++t) {
-    if (!finisher_of_tile.count(t)) return fail("tile without finisher", t, kind, G);
-    if (finisher_of_tile[t] != unit_owner(U, G, (t + 1) * d.KB - 1)) return fail("finisher is not the owner of the last unit", t, kind, G);
-    const std::vector<int>& cs = contrib_of_tile[t];
-    if ((int)cs.size() != tile_segments(U, G, d.KB, t) - 1) return fail("contributor count", t, (int)cs.size(), tile_segments(U, G, d.KB, t));
-    std::vector<int> sorted(cs.begin(), cs.end());
-    std::sort(sorted.begin(), sorted.end());
-    for (int j = 0; j < (int)sorted.size(); ++j)
-      if (tile_contributor(U, G, d.KB, t, j) != sorted[j]) return fail("tile_contributor disagrees", t, j, sorted[j]);
+  std::set<int> acc_slots;
+  for (auto& kv : partial_of_tile) {
+    const int t = kv.first;
+    if (!acc_slots.insert(unit_owner(U, G, t * d.KB)).second) return fail("accumulator slot shared by two split tiles", t, kind, G);
+    const int c_first = unit_owner(U, G, t * d.KB), c_last = unit_owner(U, G, (t + 1) * d.KB - 1);
+    if ((int)kv.second.size() != tile_segments(U, G, d.KB, t))
+      return fail("ticket count", t, (int)kv.second.size(), tile_segments(U, G, d.KB, t));
+    // the last arriver walks CTAs c_first..c_last, skips those without units, and must meet exactly the writers
+    int i = 0;
+    for (int cc = c_first; cc <= c_last; ++cc) {
+      int clo, chi;
+      unit_range(U, G, cc, clo, chi);
+      if (clo == chi) continue;
+      if (i >= (int)kv.second.size() || kv.second[i] != cc) return fail("reader meets another CTA than the writers", t, cc, i);
+      ++i;
+      const int which = t == clo / d.KB ? 0 : 1;
+      // writer side: tile t is the CTA's first tile iff it contains unit clo
+      if ((which == 0) != (clo >= t * d.KB && clo < (t + 1) * d.KB)) return fail("slot choice", t, cc, which);
+    }
+    if (i != (int)kv.second.size()) return fail("reader misses a writer", t, i, (int)kv.second.size());
   }
   return 0;
 }
@@ -91,13 +87,6 @@ int main() {
       p.QDIM = s.NH * s.HD;
       for (int kind : {kQkv, kOproj, kUpGate, kDown, kLmHead})
         if (int rc = check_phase(p, kind, G)) return rc;
-      if (s.H == 2048 && s.I == 1024) {   // the mixture-of-experts shape: router tile and the two expert phases
-        p.E = 64; p.Ie = 1024; p.ppl = 6; p.topk = 8;
-        if (int rc = check_phase(p, kRouter, G)) return rc;
-        for (int ne : {1, 8, 33, 64})
-          for (int kind : {kEUpGate, kEDown})
-            if (int rc = check_phase(p, kind, G, ne)) return rc;
-      }
     }
   for (int Tmax : {1, 31, 32, 33, 500, 2048, 8192, 100000})
     for (int seqs : {1, 8, 16, 64, 512, 1024})

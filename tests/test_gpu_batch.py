@@ -548,22 +548,17 @@ def test_decode_api_batched(small_config, small_weights):
         assert out["timing"]["decode_window_new_tokens"] == B * (n_new - 1) and out["timing"]["kernel_tok_s"] > 0
         outs.append(out["generated_ids"].cpu())
         pre.mk.close()
-    # Split-K partial tiles are added at L2 in arrival order, so two runs may differ in the last bit of an fp32 sum.
-    # With these synthetic weights (bf16 logits over 4096 words, top two often a unit in the last place apart) that
-    # flips an arg-max every few dozen tokens, after which a greedy row goes its own way: the loops must agree on
-    # the prompts, on most first tokens, and on most of the text; exactness is held by the teacher-forced tests.
-    assert torch.equal(outs[0][:, :P], outs[1][:, :P])
-    assert int((outs[0][:, P] == outs[1][:, P]).sum()) >= B - 1
-    assert float((outs[0] == outs[1]).float().mean()) >= 0.75
-    # each row alone through the batched kernel (batch 1): rows are independent, so the same text up to such a flip
-    agree = 0.0
+    # Split-K partial tiles meet in a fixed-point accumulator (integer additions: no dependence on arrival order), so
+    # the kernel is deterministic: both loops feed it the same tokens and must produce the same text, bit for bit.
+    assert torch.equal(outs[0], outs[1])
+    # each row alone through the batched kernel (batch 1): rows are independent and the padded tensor-core columns are
+    # zero, so a row decoded alone gives the same text as the same row inside the batch
     for b in range(B):
         pre = run_prefill_synthetic(small_config, small_weights, prompts[b], n_new, device="cuda:0")
         pre.mk.set_kernel_variant(1)
         out = decode("llama-3.2-1b", prefill=pre, max_new_tokens=n_new, ignore_eos=True)
-        agree += float((out["generated_ids"][0].cpu() == outs[1][b]).float().mean()) / B
+        assert torch.equal(out["generated_ids"][0].cpu(), outs[1][b]), f"row {b} alone differs from the row in the batch"
         pre.mk.close()
-    assert agree >= 0.75
     # per-row EOS: every row stops at its own first EOS and is padded after it
     eos = int(outs[1][2, P + 4])
     pre = run_prefill_synthetic(small_config, small_weights, prompts, n_new, device="cuda:0")
