@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define QMK_ABI_VERSION 3
+#define QMK_ABI_VERSION 4
 
 /* Error codes (negative).  qmk_strerror() gives the text. */
 enum qmk_error {
@@ -150,6 +150,13 @@ typedef struct qmk_state_ptrs {
   const uint8_t* active_mask;    /* optional uint8[B]: 0 = the row is finished: no KV write, zero attention
                                     output and projections, logits -1e9 (row_active in the reference's
                                     fused operations.py:226-317); NULL = all rows active */
+  const int32_t* kv_slots;       /* optional int32[B]: the sequence of the KV cache that row b attends to and appends
+                                    its K / V row to; NULL = row b owns sequence b.  With it the rows of one step may be
+                                    consecutive positions of the same sequence -- a row attends to every earlier
+                                    position, also to those written by other rows of the same step -- which is how a
+                                    prompt is prefilled 64 tokens per launch (the reference's fused prefill is a
+                                    PyTorch pass, llama/llama3_2__1b/A100/fused_prefill.py:185-335); batched kernel only */
+  int32_t kv_batch;              /* sequences in k_cache / v_cache when kv_slots is given (0 = batch) */
 } qmk_state_ptrs;
 
 /* Device-side status record, filled when a bounded wait expires. */

@@ -11,7 +11,7 @@ from pathlib import Path
 
 from ._build import LIB_PATH
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 ARCH_LLAMA = 0
 ARCH_QWEN3 = 1
 ARCH_MOE = 2
@@ -44,7 +44,7 @@ class StatePtrs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("hidden_states", "q_post_rope", "k_cache", "v_cache", "attn_out",
                                           "silu_out", "logits", "next_token", "token_in", "out_tokens")] + \
                [("out_tokens_len", C.c_int64), ("batch", C.c_int32), ("kv_seq_len", C.c_int32),
-                ("position_ids", C.c_void_p), ("active_mask", C.c_void_p)]
+                ("position_ids", C.c_void_p), ("active_mask", C.c_void_p), ("kv_slots", C.c_void_p), ("kv_batch", C.c_int32)]
 
 
 class Status(C.Structure):

@@ -56,7 +56,8 @@ struct qmk_handle {
 // batched kernel, so that the same state behaves the same under both kernel variants.
 static bool use_batched(const qmk_handle* h) {
   return !h->tuned_shape || h->variant == 1 ||
-         (h->bound && (h->st.batch != 1 || h->st.position_ids != nullptr || h->st.active_mask != nullptr));
+         (h->bound && (h->st.batch != 1 || h->st.position_ids != nullptr || h->st.active_mask != nullptr ||
+                       h->st.kv_slots != nullptr));
 }
 
 static int ensure_bctx(qmk_handle* h) {
@@ -206,6 +207,7 @@ extern "C" int qmk_bind_state(qmk_handle* h, const qmk_state_ptrs* s) {
     if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
   if (s->token_in && !h->w.embed_tokens) return QMK_ERR_INVALID_ARG;
   if (s->out_tokens && s->out_tokens_len < 1) return QMK_ERR_INVALID_ARG;
+  if (s->kv_batch < 0 || (s->kv_slots == nullptr && s->kv_batch != 0 && s->kv_batch != s->batch)) return QMK_ERR_INVALID_ARG;
   h->st = *s;
   h->bound = true;
   if (use_batched(h)) {
@@ -262,7 +264,7 @@ static void fill_params(const qmk_handle* h, Params& p, int pos) {
   p.out_tokens = (long long*)s.out_tokens;
   p.out_tokens_len = s.out_tokens_len;
   p.kv_seq_stride = (long long)Shape::NKV * Shape::HD;
-  p.kv_layer_stride = (long long)s.batch * s.kv_seq_len * p.kv_seq_stride;
+  p.kv_layer_stride = (long long)(s.kv_batch > 0 ? s.kv_batch : s.batch) * s.kv_seq_len * p.kv_seq_stride;
   p.part_rec = h->part_rec;
   p.t_hid_o = h->t_hid_o;
   p.t_hid_d = h->t_hid_d;

@@ -234,7 +234,9 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.active_mask = st->active_mask;
   p.kv_seq_stride = (long long)d.num_key_value_heads * d.head_dim;
   p.kv_batch_stride = (long long)st->kv_seq_len * p.kv_seq_stride;
-  p.kv_layer_stride = (long long)st->batch * p.kv_batch_stride;
+  p.kv_slots = st->kv_slots;
+  p.kv_batch = st->kv_batch > 0 ? st->kv_batch : st->batch;
+  p.kv_layer_stride = (long long)p.kv_batch * p.kv_batch_stride;
   p.ws = c->ws;
   p.tile_tickets = c->tile_tickets;
   p.ss = c->ss;

@@ -62,7 +62,8 @@ struct Smem {
   static constexpr int kOffHs = kOffRs + kMaxBatch * 4;                       // float [2][64] scratch of the prologue
   static constexpr int kOffPos = kOffHs + 2 * kMaxBatch * 4;                  // int [64]
   static constexpr int kOffAct = kOffPos + kMaxBatch * 4;                     // int [64]
-  static constexpr int kOffCtl = kOffAct + kMaxBatch * 4;                     // control words
+  static constexpr int kOffSlot = kOffAct + kMaxBatch * 4;                    // int [64]  KV-cache sequence of every row
+  static constexpr int kOffCtl = kOffSlot + kMaxBatch * 4;                    // control words
   static constexpr int kOffExch = 2048;
   static_assert(kOffCtl + 64 <= kOffExch, "header overflows");
 };
@@ -543,6 +544,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
   float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
   const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
   const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
+  const int* slot_s = reinterpret_cast<const int*>(c.smem + Smem::kOffSlot);
   const int layer = phase_layer(p, ph);
   const int B = p.B;
   switch (kind) {
@@ -613,7 +615,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         } else {
           const int col = is_k ? row - p.QDIM : row - p.QDIM - kdim;
           uint16_t* cache = is_k ? p.k_cache : p.v_cache;
-          *reinterpret_cast<uint4*>(cache + (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride +
+          *reinterpret_cast<uint4*>(cache + (size_t)layer * p.kv_layer_stride + (size_t)slot_s[b] * p.kv_batch_stride +
                                     (size_t)pos * p.kv_seq_stride + col) = o4;
         }
       }
@@ -883,6 +885,7 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
   const int sub = lane / LPR, dl = lane % LPR;
   const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
   const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
+  const int* slot_s = reinterpret_cast<const int*>(c.smem + Smem::kOffSlot);
   const int NW = (int)gridDim.x * 8, gw = (int)blockIdx.x * 8 + aw;
   const int Tmax = (int)c.ctl[kCTmax];
   const int seqs = p.B * p.NKV;
@@ -919,7 +922,7 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
     }
-    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)b * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
+    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)slot_s[b] * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
     // Keys are taken in half-blocks of NLD row pieces per lane (16 keys at head_dim 64, 8 at 128), double-buffered in
     // registers: the loads of the next half-block are in flight while this one is multiplied.
     constexpr int NLD = 4;
@@ -1187,13 +1190,17 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
     int act = b < p.B ? (p.active_mask ? (int)p.active_mask[b] : 1) : 0;
     // An active row whose position lies outside the KV cache or the RoPE table would read and write out of bounds:
     // it is switched off (no KV write, zero projections, like a finished row) and the launch reports it.
-    if (act != 0 && (pos < 0 || pos >= p.pos_limit)) {
+    // (the same goes for a row that names a sequence the KV cache does not have)
+    int slot = b < p.B ? (p.kv_slots ? p.kv_slots[b] : b) : 0;
+    if (act != 0 && (pos < 0 || pos >= p.pos_limit || slot < 0 || slot >= p.kv_batch)) {
       if (blockIdx.x == 0) report(p, kErrRowPosition, 0, p.phase_begin, (unsigned)pos, (unsigned)p.pos_limit, b);
       act = 0;
       pos = -1;
     }
+    if (slot < 0 || slot >= p.kv_batch) slot = 0;
     pos_s[b] = pos;
     act_s[b] = act;
+    reinterpret_cast<int*>(smem + Smem::kOffSlot)[b] = slot;
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -43,6 +43,8 @@ struct BParams {
   long long out_tokens_len;
   const int* position_ids;       // [B] or null (then every row is at `pos`)
   const unsigned char* active_mask;   // [B] or null (then every row is active)
+  const int* kv_slots;           // [B] or null: the sequence of the KV cache row b reads and appends to (null: sequence b)
+  int kv_batch;                  // sequences in the KV cache
   long long kv_layer_stride, kv_batch_stride, kv_seq_stride;   // elements
   // ---- library-owned scratch ----
   long long* ws;                 // [CTAs, Bpad, 128] fixed-point accumulators of split tiles (zero between uses)

@@ -133,7 +133,7 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
     if (!p || !aligned16(p)) return QMK_ERR_INVALID_ARG;
   if (st->batch != 1 || st->kv_seq_len < 1) return QMK_ERR_INVALID_ARG;
   // the batch-1 kernel has neither per-row positions nor an active mask: refuse rather than ignore them
-  if (st->position_ids != nullptr || st->active_mask != nullptr) return QMK_ERR_INVALID_ARG;
+  if (st->position_ids != nullptr || st->active_mask != nullptr || st->kv_slots != nullptr) return QMK_ERR_INVALID_ARG;
   if (st->token_in && !w->embed_tokens) return QMK_ERR_INVALID_ARG;
   if (pos_id < 0 || pos_id >= st->kv_seq_len || pos_id >= d->rope_rows) return QMK_ERR_POSITION;
 
@@ -179,7 +179,7 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
   p.out_tokens = (long long*)st->out_tokens;
   p.out_tokens_len = st->out_tokens_len;
   p.kv_seq_stride = (long long)Shape::NKV * Shape::HD;
-  p.kv_layer_stride = (long long)st->batch * st->kv_seq_len * p.kv_seq_stride;
+  p.kv_layer_stride = (long long)(st->kv_batch > 0 ? st->kv_batch : st->batch) * st->kv_seq_len * p.kv_seq_stride;
   p.part_rec = (unsigned long long*)(dev.scratch + lay.part_rec);
   p.t_hid_o = (uint32_t*)(dev.scratch + lay.t_hid_o);
   p.t_hid_d = (uint32_t*)(dev.scratch + lay.t_hid_d);

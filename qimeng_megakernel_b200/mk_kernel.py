@@ -28,7 +28,7 @@ _WEIGHT_FIELDS = (("attn_norm", "attn_norm_weights"), ("qkv", "qkv_weights"), ("
                   ("q_norm", "q_norm_weights"), ("k_norm", "k_norm_weights"), ("router", "router_weights"),
                   ("expert_gate_up", "expert_gate_up_proj_weights"), ("expert_down", "expert_down_proj_weights"))
 _STATE_FIELDS = ("hidden_states", "q_post_rope", "k_cache", "v_cache", "attn_out", "silu_out", "logits",
-                 "next_token", "token_in", "out_tokens", "position_ids", "active_mask")
+                 "next_token", "token_in", "out_tokens", "position_ids", "active_mask", "kv_slots")
 
 
 def _check_tensor(name: str, t: torch.Tensor, dtype: torch.dtype, shape: tuple) -> None:
@@ -102,11 +102,16 @@ class MegaKernel:
             _check_tensor("k_norm_weights", g.k_norm_weights, bf, (L, HD))
         if g.k_cache.dim() != 5:
             raise ValueError("globs.k_cache must be [L, B, S, NKV, HD]")
-        B, S = int(g.k_cache.shape[1]), int(g.k_cache.shape[2])
+        Bc, S = int(g.k_cache.shape[1]), int(g.k_cache.shape[2])
+        # rows of the step: one per sequence of the cache, unless kv_slots says which sequence every row belongs to
+        slots = getattr(g, "kv_slots", None)
+        B = int(slots.numel()) if slots is not None else Bc
         if not 1 <= B <= _lib.MAX_BATCH:
             raise ValueError(f"batch {B} outside 1..{_lib.MAX_BATCH}")
-        _check_tensor("k_cache", g.k_cache, bf, (L, B, S, NKV, HD))
-        _check_tensor("v_cache", g.v_cache, bf, (L, B, S, NKV, HD))
+        _check_tensor("k_cache", g.k_cache, bf, (L, Bc, S, NKV, HD))
+        _check_tensor("v_cache", g.v_cache, bf, (L, Bc, S, NKV, HD))
+        if slots is not None:
+            _check_tensor("kv_slots", slots, torch.int32, (B,))
 
         def state(name, width):
             t = getattr(g, name)
@@ -132,7 +137,7 @@ class MegaKernel:
             if g.active_mask.dtype not in (torch.uint8, torch.bool):
                 raise TypeError("globs.active_mask must be uint8 or bool")
             _check_tensor("active_mask", g.active_mask, g.active_mask.dtype, (B,))
-        return rows, S, B
+        return rows, S, B, Bc
 
     def _ensure(self, g: Globals) -> None:
         wkey = tuple(_ptr(getattr(g, f, None)) for _, f in _WEIGHT_FIELDS) + tuple(
@@ -140,7 +145,7 @@ class MegaKernel:
         skey = tuple(_sig(getattr(g, f, None)) for f in _STATE_FIELDS)
         if wkey == self._weights_key and skey == self._state_key:
             return
-        rows, S, B = self._validate(g)
+        rows, S, B, Bc = self._validate(g)
         dev = g.hidden_states.device
         if wkey != self._weights_key:
             self.close()
@@ -168,6 +173,7 @@ class MegaKernel:
             st.out_tokens_len = int(g.out_tokens.numel()) // B if getattr(g, "out_tokens", None) is not None else 0
             st.batch = B
             st.kv_seq_len = S
+            st.kv_batch = Bc
             _lib.check(self._lib.qmk_bind_state(self._handle, C.byref(st)), self._handle)
             self._state_key = skey
 

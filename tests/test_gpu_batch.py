@@ -572,3 +572,39 @@ def test_decode_api_batched(small_config, small_weights):
         new = outs[1][b, P:].tolist()
         assert per_row[b] == (new.index(eos) + 1 if eos in new else n_new)
     pre.mk.close()
+
+
+@pytest.mark.parametrize("batch,prompt_len", [(3, 20), (1, 70), (5, 16)])
+def test_fused_prefill_matches_token_by_token(small_config, small_weights, batch, prompt_len):
+    """Prefill with the rows of a launch being consecutive positions of a sequence (kv_slots): the KV cache it leaves,
+    the logits of the last prompt position and the first generated token against the token-by-token path (one decode
+    step per position) and against the CPU oracle; 64 tokens per launch, several short prompts per launch."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import synthetic
+    from qimeng_megakernel_b200.prefill import prefill_plan, run_prefill_synthetic
+    prompts = synthetic.make_prompts(small_config["vocab_size"], batch, prompt_len, seed=300 + batch)
+    fused = run_prefill_synthetic(small_config, small_weights, prompts, 4, device="cuda:0", fused=True)
+    assert fused.launches == len(prefill_plan(batch, prompt_len)) < prompt_len
+    fused.mk.close()
+    slow = run_prefill_synthetic(small_config, small_weights, prompts if batch > 1 else prompts[0], 4, device="cuda:0", fused=False)
+    slow.mk.close()
+    assert slow.launches == prompt_len
+    L = small_config["num_hidden_layers"]
+    for layer in range(L):
+        for name in ("k_cache", "v_cache"):
+            a = getattr(fused.globs, name)[layer, :, :prompt_len].float().cpu()
+            e = getattr(slow.globs, name)[layer, :, :prompt_len].float().cpu()
+            assert U.rel_l2(a, e) <= 1e-2, f"{name} layer {layer}: fused prefill vs token by token {U.rel_l2(a, e):.4g}"
+        assert float(fused.globs.k_cache[layer, :, prompt_len:].float().abs().max()) == 0.0   # nothing past the prompt
+    # the oracle's view of the last prompt position
+    st = U.oracle_state(small_config, small_weights, prompt_len + 4, torch.bfloat16, batch=batch if batch > 1 else None)
+    for pos in range(prompt_len):
+        fo.feed_tokens(st, prompts[:, pos].tolist(), [pos] * batch) if batch > 1 else fo.feed_token(st, int(prompts[0, pos]), pos)
+    ref = fo._bh(st.logits).float()
+    got = fused.logits.float().cpu()
+    for b in range(batch):
+        assert U.rel_l2(got[b], ref[b]) <= 3e-2, f"row {b}: logits of the last prompt position vs oracle"
+        assert int(fused.first_gen_token[b]) == int(got[b].argmax())
+        top2 = ref[b].topk(2).values
+        if float(top2[0] - top2[1]) > 4 * 2.0 ** -8 * abs(float(top2[0])):
+            assert int(fused.first_gen_token[b]) == int(ref[b].argmax()), f"row {b}: first generated token"

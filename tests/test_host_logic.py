@@ -207,3 +207,20 @@ def test_moe_synthetic_model_and_config():
     assert LlamaConfig.num_experts == 16 and LlamaConfig.num_experts_per_tok == 4 and LlamaConfig.moe_intermediate_size == 128
     LlamaConfig.update_from_dict(dict(cfg, num_experts=0, num_experts_per_tok=0, moe_intermediate_size=0))
     assert LlamaConfig.num_experts == 0
+
+
+def test_prefill_plan_orders_positions_per_sequence():
+    """The launches of a fused prefill: every (sequence, position) exactly once, at most 64 rows per launch, and inside
+    and across launches the positions of a sequence ascend without gaps (a row may only attend to what is already
+    in the cache or appended earlier in the same launch)."""
+    from qimeng_megakernel_b200.prefill import prefill_plan
+    for batch, plen in ((1, 16), (1, 70), (3, 20), (32, 16), (5, 64), (7, 130), (64, 1)):
+        plan = prefill_plan(batch, plen)
+        seen = {}
+        for launch in plan:
+            assert 1 <= len(launch) <= 64
+            for s, p in launch:
+                assert seen.get(s, -1) == p - 1, (batch, plen, s, p)
+                seen[s] = p
+        assert seen == {s: plen - 1 for s in range(batch)}
+    assert len(prefill_plan(1, 16)) == 1 and len(prefill_plan(32, 16)) == 8 and len(prefill_plan(1, 70)) == 2
