@@ -84,6 +84,10 @@ typedef struct qmk_model_desc {
   int32_t num_experts;           /* QMK_ARCH_MOE: 8..128 experts (else 0)                            */
   int32_t num_experts_per_tok;   /* QMK_ARCH_MOE: 1..16                                              */
   int32_t moe_intermediate_size; /* QMK_ARCH_MOE: expert intermediate size, a multiple of 64         */
+  int32_t ep_world;              /* QMK_ARCH_MOE: expert-parallel ranks (0 or 1 = off; 2, 4, 8; divides num_experts):
+                                    this handle holds num_experts / ep_world experts, expert_gate_up / expert_down are
+                                    [L, num_experts / ep_world, ...]; everything else is replicated             */
+  int32_t ep_rank;               /* this handle's rank: it holds experts [ep_rank, ep_rank + 1) * num_experts / ep_world */
 } qmk_model_desc;
 
 /*
@@ -256,6 +260,17 @@ int qmk_last_expert_count(qmk_handle* h, int32_t* out);
  * for experts[slot], 0 where the row did not select it.  experts: int32[num_experts], weights: float[num_experts * 64]
  * (host memory).  Synchronises the stream of the last launch. */
 int qmk_last_expert_routing(qmk_handle* h, int32_t* count, int32_t* experts, float* weights);
+
+/* Expert parallelism over the GPUs of one box (no counterpart in the reference, which has no distributed code; the
+ * math that is split is its routed accumulate, qwen1_5_moe_a2_7b/.../fused/operations.py:220-268).  One process per GPU,
+ * one handle each, created with ep_world / ep_rank in the descriptor.  qmk_ep_export allocates this rank's exchange
+ * buffer and writes its 64-byte inter-process memory handle; the caller gathers the handles of all ranks (over
+ * torch.distributed or any other channel) and passes them, in rank order, to qmk_ep_connect, which maps the peers'
+ * buffers.  From then on every decode step of every rank must be launched in the same order on all ranks: inside the
+ * expert down-projection each rank stores its partial tiles into the peers' buffers and adds up what it receives, in rank
+ * order.  A peer that never shows up ends the bounded wait with QMK_ERR_DEVICE_TIMEOUT. */
+int qmk_ep_export(qmk_handle* h, void* ipc_handle_out);
+int qmk_ep_connect(qmk_handle* h, const void* ipc_handles);
 
 /* QMK_ARCH_MOE: distinct experts read, summed over every router phase (layer and step) since the counter was last
  * reset: each one stands for 3 * hidden_size * moe_intermediate_size bf16 weights streamed from HBM, which is what a

@@ -30,7 +30,8 @@ class ModelDesc(C.Structure):
                 ("num_attention_heads", C.c_int32), ("num_key_value_heads", C.c_int32),
                 ("head_dim", C.c_int32), ("vocab_size", C.c_int32), ("rope_rows", C.c_int32),
                 ("rms_norm_eps", C.c_float), ("attn_scale", C.c_float), ("qk_norm_eps", C.c_float),
-                ("num_experts", C.c_int32), ("num_experts_per_tok", C.c_int32), ("moe_intermediate_size", C.c_int32)]
+                ("num_experts", C.c_int32), ("num_experts_per_tok", C.c_int32), ("moe_intermediate_size", C.c_int32),
+                ("ep_world", C.c_int32), ("ep_rank", C.c_int32)]
 
 
 class WeightPtrs(C.Structure):
@@ -69,6 +70,8 @@ SYMBOLS = [
     ("qmk_step_bytes", C.c_int64, [C.c_void_p, C.c_int32]),
     ("qmk_last_expert_count", C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     ("qmk_last_expert_routing", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
+    ("qmk_ep_export", C.c_int, [C.c_void_p, C.c_void_p]),
+    ("qmk_ep_connect", C.c_int, [C.c_void_p, C.c_void_p]),
     ("qmk_expert_reads", C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int32]),
     ("qmk_launch_count", C.c_int64, [C.c_void_p]),
     ("qmk_launch_geometry", C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32),

@@ -539,6 +539,20 @@ extern "C" int qmk_last_expert_routing(qmk_handle* h, int32_t* count, int32_t* e
   return QMK_OK;
 }
 
+extern "C" int qmk_ep_export(qmk_handle* h, void* ipc_handle_out) {
+  if (!h || !ipc_handle_out) return QMK_ERR_INVALID_ARG;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  int rc = ensure_bctx(h);
+  if (rc) return rc;
+  return qmkb_ep_export(h->bctx, ipc_handle_out, h->cuda_err, sizeof(h->cuda_err));
+}
+
+extern "C" int qmk_ep_connect(qmk_handle* h, const void* ipc_handles) {
+  if (!h || !ipc_handles || !h->bctx) return QMK_ERR_INVALID_ARG;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  return qmkb_ep_connect(h->bctx, ipc_handles, h->cuda_err, sizeof(h->cuda_err));
+}
+
 extern "C" int qmk_expert_reads(qmk_handle* h, int64_t* total, int32_t reset) {
   if (!h || !total) return QMK_ERR_INVALID_ARG;
   *total = 0;

@@ -38,6 +38,12 @@ struct qmk_batch_ctx {
   unsigned* attn_tickets;
   unsigned long long* argmax_key;
   unsigned* status;
+  unsigned epoch;
+  // expert parallelism
+  unsigned char* ep_local;       // this rank's exchange buffer (data, then flags)
+  size_t ep_data_bytes, ep_bytes;
+  void* ep_peer[8];              // every rank's buffer as mapped here (own = ep_local); null until connected
+  bool ep_connected;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -54,6 +60,11 @@ int qmkb_supported(const qmk_model_desc* d) {
     if (d->num_experts < 8 || d->num_experts > kTileRows || d->num_experts_per_tok < 1 || d->num_experts_per_tok > 16 ||
         d->num_experts_per_tok > d->num_experts || d->moe_intermediate_size < kBlockK ||
         d->moe_intermediate_size % kBlockK != 0)
+      return QMK_ERR_UNSUPPORTED_MODEL;
+  }
+  if (d->ep_world > 1) {
+    if (d->arch != QMK_ARCH_MOE || (d->ep_world != 2 && d->ep_world != 4 && d->ep_world != 8) ||
+        d->num_experts % d->ep_world != 0 || d->ep_rank < 0 || d->ep_rank >= d->ep_world)
       return QMK_ERR_UNSUPPORTED_MODEL;
   }
   if (HD != 64 && HD != 128) return QMK_ERR_UNSUPPORTED_MODEL;
@@ -113,13 +124,14 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     int bad = 0;
     const bool moe = d->arch == QMK_ARCH_MOE;
     const int E = moe ? d->num_experts : 0, Ie = moe ? d->moe_intermediate_size : 0;
+    const int El = d->ep_world > 1 ? E / d->ep_world : E;   // experts this rank holds
     if (L > 0) {
       bad |= make_map(enc, &c->maps.qkv, w->qkv, H, QKV, L, kTileRows);
       bad |= make_map(enc, &c->maps.o_proj, w->o_proj, QD, H, L, kTileRows);
       if (moe) {
         bad |= make_map(enc, &c->maps.router, w->router, H, E, L, kTileRows);
-        bad |= make_map(enc, &c->maps.egu, w->expert_gate_up, H, 2 * Ie, (long long)L * E, kTileRows / 2);
-        bad |= make_map(enc, &c->maps.edown, w->expert_down, Ie, H, (long long)L * E, kTileRows);
+        bad |= make_map(enc, &c->maps.egu, w->expert_gate_up, H, 2 * Ie, (long long)L * El, kTileRows / 2);
+        bad |= make_map(enc, &c->maps.edown, w->expert_down, Ie, H, (long long)L * El, kTileRows);
       } else {
         bad |= make_map(enc, &c->maps.up, w->up_proj, H, I, L, kTileRows / 2);
         bad |= make_map(enc, &c->maps.gate, w->gate_proj, H, I, L, kTileRows / 2);
@@ -182,8 +194,47 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
   return QMK_OK;
 }
 
+int qmkb_ep_export(qmk_batch_ctx* c, void* ipc_handle_out, char* err, size_t errlen) {
+  const qmk_model_desc& d = c->desc;
+  if (d.ep_world <= 1 || !ipc_handle_out) return QMK_ERR_INVALID_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the ABI documents a 64-byte handle");
+  if (!c->ep_local) {
+    const size_t tiles = (size_t)((d.hidden_size + kTileRows - 1) / kTileRows);
+    c->ep_data_bytes = align_up((size_t)2 * d.ep_world * tiles * kTileRows * kMaxBatch * 4, 256);
+    c->ep_bytes = c->ep_data_bytes + align_up((size_t)2 * d.ep_world * tiles * 4, 256);
+    cudaError_t e = cudaMalloc((void**)&c->ep_local, c->ep_bytes);
+    if (e != cudaSuccess) { fail(err, errlen, "cudaMalloc(exchange buffer)", e); return QMK_ERR_OOM; }
+    e = cudaMemset(c->ep_local, 0, c->ep_bytes);
+    if (e != cudaSuccess) return fail(err, errlen, "cudaMemset", e);
+  }
+  cudaIpcMemHandle_t hnd;
+  const cudaError_t e = cudaIpcGetMemHandle(&hnd, c->ep_local);
+  if (e != cudaSuccess) return fail(err, errlen, "cudaIpcGetMemHandle", e);
+  memcpy(ipc_handle_out, &hnd, sizeof(hnd));
+  return QMK_OK;
+}
+
+int qmkb_ep_connect(qmk_batch_ctx* c, const void* ipc_handles, char* err, size_t errlen) {
+  const qmk_model_desc& d = c->desc;
+  if (d.ep_world <= 1 || !ipc_handles || !c->ep_local) return QMK_ERR_INVALID_ARG;
+  if (c->ep_connected) return QMK_OK;
+  for (int r = 0; r < d.ep_world; ++r) {
+    if (r == d.ep_rank) { c->ep_peer[r] = c->ep_local; continue; }
+    cudaIpcMemHandle_t hnd;
+    memcpy(&hnd, (const unsigned char*)ipc_handles + (size_t)r * sizeof(hnd), sizeof(hnd));
+    const cudaError_t e = cudaIpcOpenMemHandle(&c->ep_peer[r], hnd, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(err, errlen, "cudaIpcOpenMemHandle", e);
+  }
+  c->ep_connected = true;
+  return QMK_OK;
+}
+
 void qmkb_destroy(qmk_batch_ctx* c) {
   if (!c) return;
+  if (c->ep_connected)
+    for (int r = 0; r < c->desc.ep_world; ++r)
+      if (r != c->desc.ep_rank && c->ep_peer[r]) cudaIpcCloseMemHandle(c->ep_peer[r]);
+  if (c->ep_local) cudaFree(c->ep_local);
   if (c->scratch) cudaFree(c->scratch);
   delete c;
 }
@@ -256,6 +307,19 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.Ie = moe ? d.moe_intermediate_size : 0;
   p.ppl = moe ? 6 : 5;
   p.trace = a->trace;
+  p.epoch = ++c->epoch;
+  p.ep_world = moe && d.ep_world > 1 ? d.ep_world : 1;
+  p.ep_rank = p.ep_world > 1 ? d.ep_rank : 0;
+  if (p.ep_world > 1) {
+    if (!c->ep_connected) {
+      if (err && errlen) snprintf(err, errlen, "expert parallelism: qmk_ep_connect has not been called");
+      return QMK_ERR_NOT_BOUND;
+    }
+    for (int r = 0; r < p.ep_world; ++r) {
+      p.ep_buf[r] = (float*)c->ep_peer[r];
+      p.ep_flag[r] = (unsigned*)((unsigned char*)c->ep_peer[r] + c->ep_data_bytes);
+    }
+  }
   p.H = d.hidden_size;
   p.I = d.intermediate_size;
   p.NH = d.num_attention_heads;

@@ -39,5 +39,8 @@ const int* qmkb_expert_count_ptr(const qmk_batch_ctx* c);   // device address of
 const int* qmkb_expert_list_ptr(const qmk_batch_ctx* c);
 unsigned long long* qmkb_expert_reads_ptr(const qmk_batch_ctx* c);   // device counter: distinct experts over all router phases
 const float* qmkb_expert_weight_ptr(const qmk_batch_ctx* c);
+// Expert parallelism: exchange buffer of this rank (allocated on first call; its inter-process handle) and the peers' buffers.
+int qmkb_ep_export(qmk_batch_ctx* c, void* ipc_handle_out, char* err, size_t errlen);
+int qmkb_ep_connect(qmk_batch_ctx* c, const void* ipc_handles, char* err, size_t errlen);
 void qmkb_geometry(const qmk_batch_ctx* c, int* ctas, int* threads, int* smem_bytes);
 size_t qmkb_scratch_bytes(const qmk_batch_ctx* c);

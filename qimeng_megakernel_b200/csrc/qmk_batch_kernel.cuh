@@ -539,6 +539,72 @@ __device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, in
   return ((unsigned long long)float_ordered_bits(bf16_bits_to_f32(bits)) << 32) | (0xffffffffu - (unsigned)row);
 }
 
+// Expert parallelism: the finished partial tile of this rank (exch, row tile t of the expert down-projection) is stored
+// into this rank's slot of every peer's exchange buffer, a flag with the tag of (launch, layer) follows after a
+// system-scope fence, then the flags of the other ranks are awaited in THIS rank's buffer (bounded) and the slots are added
+// in rank order -- the same order on every rank, so all ranks hold the same bits afterwards.  128 threads, e = tile row.
+static __device__ __noinline__ void ep_exchange(const Ctx& c, int ph, int t, int e) {
+  const BParams& p = *c.p;
+  float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
+  const int W = p.ep_world, me = p.ep_rank, layer = phase_layer(p, ph);
+  const int T = (p.H + kTileRows - 1) / kTileRows;
+  // Exchanges are numbered over the launches (all ranks launch in lockstep); the number is the flag's tag and its low
+  // bit picks one of two buffers, so a rank that runs one exchange ahead never overwrites a tile a peer still reads.
+  const unsigned seq = p.epoch * (unsigned)p.num_layers + (unsigned)layer;
+  const unsigned tag = seq + 1u;
+  const int par = (int)(seq & 1u);
+  const size_t tile_f = (size_t)kTileRows * p.Bpad;
+  const size_t fidx = (size_t)(par * W + me) * T + t;                  // my slot in a peer's buffer
+  for (int d = 0; d < W; ++d) {
+    if (d == me) continue;
+    float4* dst = reinterpret_cast<float4*>(p.ep_buf[d] + fidx * tile_f + (size_t)e * p.Bpad);
+    for (int q = 0; q < p.Bpad / 4; ++q)
+      dst[q] = make_float4(exch[e * p.exch_stride + 4 * q], exch[e * p.exch_stride + 4 * q + 1],
+                           exch[e * p.exch_stride + 4 * q + 2], exch[e * p.exch_stride + 4 * q + 3]);
+  }
+  __threadfence_system();
+  named_bar(kBarEpi, 128);
+  if (e < W && e != me) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ep_flag[e] + fidx), "r"(tag) : "memory");
+    // wait for rank e's tile in my own buffer
+    const unsigned* flag = p.ep_flag[me] + (size_t)(par * W + e) * T + t;
+    const long long t0 = clock64();
+    for (unsigned it = 1;; ++it) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v == tag) break;
+      if ((it & 15u) == 0u) {
+        if (c.ctl[kCAbort] != 0u) break;
+        if (clock64() - t0 > c.p->timeout_cycles) {
+          report(p, kErrCounterWait, c.warp, ph, v, tag, 32 + e);
+          c.ctl[kCAbort] = 1u;
+          break;
+        }
+      }
+    }
+  }
+  named_bar(kBarEpi, 128);
+  if (c.ctl[kCAbort] == 0u) {
+    for (int q = 0; q < p.Bpad / 4; ++q) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < W; ++s) {
+        float4 v;
+        if (s == me) {
+          v = make_float4(exch[e * p.exch_stride + 4 * q], exch[e * p.exch_stride + 4 * q + 1],
+                          exch[e * p.exch_stride + 4 * q + 2], exch[e * p.exch_stride + 4 * q + 3]);
+        } else {
+          v = __ldcg(reinterpret_cast<const float4*>(p.ep_buf[me] + ((size_t)(par * W + s) * T + t) * tile_f +
+                                                     (size_t)e * p.Bpad) + q);
+        }
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      exch[e * p.exch_stride + 4 * q] = acc.x; exch[e * p.exch_stride + 4 * q + 1] = acc.y;
+      exch[e * p.exch_stride + 4 * q + 2] = acc.z; exch[e * p.exch_stride + 4 * q + 3] = acc.w;
+    }
+  }
+  named_bar(kBarEpi, 128);
+}
+
 __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, int t, int e) {
   const BParams& p = *c.p;
   float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
@@ -673,9 +739,13 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       }
       named_bar(kBarEpi, 128);
       if (e == 0) {
+        // (expert parallelism: only the experts this rank holds are listed, under their local index; every rank runs the
+        // same router on the same rows, so the ranks' lists together are the step's selection)
+        const int per_rank = p.ep_world > 1 ? E / p.ep_world : E;
+        const int e_lo = p.ep_world > 1 ? p.ep_rank * per_rank : 0;
         int n = 0;
         for (int x = 0; x < E; ++x) {
-          if (slot_of[x]) { p.moe_elist[n] = x; slot_of[x] = n++; } else slot_of[x] = -1;
+          if (slot_of[x] && x >= e_lo && x < e_lo + per_rank) { p.moe_elist[n] = x - e_lo; slot_of[x] = n++; } else slot_of[x] = -1;
         }
         *p.moe_ne = n;
         atomicAdd(p.moe_ne_sum, (unsigned long long)n);
@@ -706,6 +776,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295).
       // Same (sequence, eight rows) ownership: one 16-byte load and store of the residual stream per item, all loads
       // issued first; the sums of squares for the next RMSNorm are reduced over the sixteen row groups by shuffles.
+      if (kind == kEDown && p.ep_world > 1) ep_exchange(c, ph, t, e);   // exch := sum over the ranks' partial tiles
       const int rg = e & 15;
       const int row = t * kTileRows + rg * 8;
       const bool in_range = row < p.H;
@@ -794,7 +865,20 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
   }
   const PhaseDims d = phase_dims(p, kind, ne);
   const int U = d.T * d.KB;
-  if (U == 0) return;
+  if (U == 0) {
+    // Expert parallelism, no selected expert on this rank: the other ranks still wait for this rank's partial tiles, and
+    // the residual stream still has to be updated from theirs: zero tiles, dealt to the CTAs, take the usual way out.
+    if (kind == kEDown && p.ep_world > 1) {
+      float* ex = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
+      for (int t = cta; t < d.T; t += (int)gridDim.x) {
+        for (int j = 0; j < p.Bpad; ++j) ex[e * p.exch_stride + j] = 0.f;
+        named_bar(kBarEpi, 128);
+        epilogue_tile(c, ph, kind, t, e);
+        named_bar(kBarEpi, 128);
+      }
+    }
+    return;
+  }
   const int G = phase_ctas(kind, U, (int)gridDim.x);   // CTAs that share this phase's units
   int lo, hi;
   unit_range(U, G, cta, lo, hi);

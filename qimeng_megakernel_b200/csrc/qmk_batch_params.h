@@ -62,6 +62,14 @@ struct BParams {
   float* moe_w;                  // [E, kMaxBatch]  router weight of (slot, row), 0 where the row did not select it
   uint16_t* esilu;               // [E, kMaxBatch, Ie]  SiLU(gate) * up of (slot, row), bf16
   unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off
+  // ---- expert parallelism (ep_world > 1): every rank holds E / ep_world experts, attention and router are replicated;
+  // after its local expert down-projection a rank stores each finished [128 rows, Bpad] fp32 partial tile into its slot
+  // of every peer's exchange buffer (plain peer stores over NVLink), publishes a flag, waits (bounded) on its OWN
+  // buffer's flags and sums the slots in rank order.  Buffer of a rank: [2 (layer parity), ep_world (source), tiles,
+  // 128, Bpad] floats, flags [2, ep_world, tiles] words holding the tag of (launch, layer).
+  float* ep_buf[8];              // exchange buffer of every rank as mapped into this process (own included)
+  unsigned* ep_flag[8];
+  int ep_rank, ep_world;
   // ---- shape ----
   int H, I, NH, NKV, HD, QKV_ROWS, QDIM, num_layers, vocab;
   int E, topk, Ie;               // MoE: experts, experts per token, expert intermediate size (E = 0: dense model)
@@ -72,6 +80,7 @@ struct BParams {
   int phase_begin, phase_end;
   int stages, stage_bytes, off_stages, exch_stride;   // shared-memory plan for this Bpad (smem_plan)
   int prologue;                  // 0 none; 1 sums of squares of `hidden`; 2 embed token_in, then sums of squares
+  unsigned epoch;                // number of this launch (per context): tags of the expert-parallel exchange
   int wait_first;                // failure test: the first phase waits for a dependency nothing publishes
   float eps, qk_eps, scale_log2e;
   long long timeout_cycles;

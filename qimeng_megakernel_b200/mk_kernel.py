@@ -83,9 +83,10 @@ class MegaKernel:
         _check_tensor("mlp_norm_weights", g.mlp_norm_weights, bf, (L, H))
         if cfg.num_experts:
             E, Ie = cfg.num_experts, cfg.moe_intermediate_size
+            El = E // cfg.ep_world if cfg.ep_world > 1 else E      # experts this rank holds (expert parallelism)
             _check_tensor("router_weights", g.router_weights, bf, (L, E, H))
-            _check_tensor("expert_gate_up_proj_weights", g.expert_gate_up_proj_weights, bf, (L, E, 2 * Ie, H))
-            _check_tensor("expert_down_proj_weights", g.expert_down_proj_weights, bf, (L, E, H, Ie))
+            _check_tensor("expert_gate_up_proj_weights", g.expert_gate_up_proj_weights, bf, (L, El, 2 * Ie, H))
+            _check_tensor("expert_down_proj_weights", g.expert_down_proj_weights, bf, (L, El, H, Ie))
         else:
             _check_tensor("up_proj_weights", g.up_proj_weights, bf, (L, I, H))
             _check_tensor("gate_proj_weights", g.gate_proj_weights, bf, (L, I, H))
@@ -156,7 +157,8 @@ class MegaKernel:
                                   cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads,
                                   cfg.head_dim, cfg.vocab_size, rows, float(cfg.rms_norm_eps),
                                   1.0 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps), int(cfg.num_experts),
-                                  int(cfg.num_experts_per_tok), int(cfg.moe_intermediate_size))
+                                  int(cfg.num_experts_per_tok), int(cfg.moe_intermediate_size),
+                                  int(cfg.ep_world), int(cfg.ep_rank))
             w = _lib.WeightPtrs(**{c: _ptr(getattr(g, f, None)) for c, f in _WEIGHT_FIELDS})
             h = C.c_void_p()
             _lib.check(self._lib.qmk_create(C.byref(desc), C.byref(w), dev.index or 0, C.byref(h)))
@@ -267,6 +269,19 @@ class MegaKernel:
         n = C.c_int32()
         _lib.check(self._lib.qmk_last_expert_count(self._handle, C.byref(n)), self._handle)
         return n.value
+
+    def ep_export(self, g: Globals) -> bytes:
+        """Expert parallelism: creates the handle for `g` if need be and returns the 64-byte inter-process handle of this
+        rank's exchange buffer (to be gathered over all ranks and passed to ep_connect)."""
+        self._ensure(g)
+        buf = C.create_string_buffer(64)
+        _lib.check(self._lib.qmk_ep_export(self._handle, buf), self._handle)
+        return buf.raw
+
+    def ep_connect(self, handles: list[bytes]) -> None:
+        """Expert parallelism: maps the exchange buffers of all ranks (their handles in rank order)."""
+        blob = b"".join(handles)
+        _lib.check(self._lib.qmk_ep_connect(self._handle, C.c_char_p(blob)), self._handle)
 
     def expert_reads(self, reset: bool = False) -> int:
         """MoE: distinct experts read, summed over every router phase since the last reset (synchronises)."""

@@ -30,10 +30,14 @@ class LlamaConfig:
     num_experts = 0
     num_experts_per_tok = 0
     moe_intermediate_size = 0
+    # expert parallelism (B200 addition): ranks that share the experts, and this process's rank; 0 / 1 = off
+    ep_world = 0
+    ep_rank = 0
 
     _KEYS = ("num_hidden_layers", "hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
              "num_key_value_heads", "vocab_size", "rms_norm_eps", "rope_theta", "rope_scaling",
-             "max_position_embeddings", "qk_norm", "num_experts", "num_experts_per_tok", "moe_intermediate_size")
+             "max_position_embeddings", "qk_norm", "num_experts", "num_experts_per_tok", "moe_intermediate_size",
+             "ep_world", "ep_rank")
 
     @classmethod
     def update_from_dict(cls, config: dict) -> None:
@@ -58,6 +62,8 @@ class LlamaConfig:
         cls.num_experts = int(config.get("num_experts", 0) or 0)
         cls.num_experts_per_tok = int(config.get("num_experts_per_tok", 0) or 0)
         cls.moe_intermediate_size = int(config.get("moe_intermediate_size", 0) or 0)
+        cls.ep_world = int(config.get("ep_world", 0) or 0)
+        cls.ep_rank = int(config.get("ep_rank", 0) or 0)
 
     @classmethod
     def update_from_hf(cls, config) -> None:

@@ -224,3 +224,53 @@ def test_prefill_plan_orders_positions_per_sequence():
                 seen[s] = p
         assert seen == {s: plen - 1 for s in range(batch)}
     assert len(prefill_plan(1, 16)) == 1 and len(prefill_plan(32, 16)) == 8 and len(prefill_plan(1, 70)) == 2
+
+
+def test_expert_partition_and_rank_order_sum_two_gloo_ranks(tmp_path):
+    """Host side of expert parallelism with two gloo ranks on the CPU: each rank keeps its block of experts
+    (expert_parallel.shard_moe_weights), computes the weighted sum over the selected experts it holds with the oracle's
+    per-expert math, the partials are gathered and added in rank order, and the result is the oracle's routed output."""
+    script = tmp_path / "rank.py"
+    script.write_text(textwrap.dedent(f"""
+        import sys, torch, torch.distributed as dist
+        sys.path.insert(0, {ROOT!r})
+        from qimeng_megakernel_b200 import expert_parallel as ep
+        from oracle import moe_oracle as mo
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        gen = torch.Generator().manual_seed(5)
+        H, Ie, E, K = 64, 32, 8, 3
+        r = lambda *s, std=0.05: torch.randn(*s, generator=gen) * std
+        w = mo.MoeLayerWeights(mlp_norm=torch.ones(H), shared_gate_proj=torch.zeros(8, H), shared_up_proj=torch.zeros(8, H),
+                               shared_down_proj=torch.zeros(H, 8), shared_expert_gate=torch.zeros(H, 1), router=r(E, H, std=0.3),
+                               expert_gate_up=r(E, 2 * Ie, H), expert_down=r(E, H, Ie))
+        cfg = mo.MoeConfig(hidden_size=H, intermediate_size=8, moe_intermediate_size=Ie, num_experts=E, num_experts_per_tok=K)
+        x = r(H, std=1.0)
+        full = mo.moe_block(cfg, w, x)
+        lo, hi = ep.expert_range(rank, world, E)
+        shard = ep.shard_moe_weights({{"expert_gate_up_proj_weights": w.expert_gate_up.unsqueeze(0),
+                                       "expert_down_proj_weights": w.expert_down.unsqueeze(0)}}, rank, world)
+        assert shard["expert_gate_up_proj_weights"].shape[1] == E // world
+        wl = mo.MoeLayerWeights(**{{**w.__dict__, "expert_gate_up": shard["expert_gate_up_proj_weights"][0],
+                                    "expert_down": shard["expert_down_proj_weights"][0]}})
+        part = torch.zeros(H)
+        for e_id, p in zip(full["expert_indices"].tolist(), full["expert_weights"].tolist()):
+            if lo <= e_id < hi:                      # the rank lists only the experts it holds, under their local index
+                part += mo.routed_expert(cfg, wl, full["normed"], e_id - lo).float() * p
+        parts = [torch.zeros(H) for _ in range(world)]
+        dist.all_gather(parts, part)
+        total = torch.zeros(H)
+        for p_ in parts:                             # rank order, on every rank
+            total += p_
+        assert torch.allclose(total, full["routed_out"].float(), rtol=1e-5, atol=1e-6), (total - full["routed_out"]).abs().max()
+        print("rank", rank, "ok")
+        dist.destroy_process_group()
+    """))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29517", str(script)],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.count("ok") == 2, out.stdout + out.stderr
+    from qimeng_megakernel_b200 import expert_parallel as ep
+    assert ep.expert_range(3, 8, 64) == (24, 32)
+    with pytest.raises(ValueError):
+        ep.expert_range(0, 3, 64)
