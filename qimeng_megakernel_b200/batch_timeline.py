@@ -1,7 +1,7 @@
 """In-kernel timeline of one decode step of the batched kernel: time and achieved HBM GB/s per phase kind.
 
     python -m qimeng_megakernel_b200.batch_timeline [--batch 8] [--model llama-3.2-1b|qwen3-0.6b|olmoe-1b-7b]
-                                                    [--pos 299] [--issuer]
+                                                    [--pos 299]
 
 Runs `--pos` + 1 persistent steps (the last one with `qmk_set_trace` attached) and reads the globaltimer stamps
 every CTA leaves per phase: when the phase's dependency became visible, when the CTA's first accumulator was
@@ -83,7 +83,7 @@ def main() -> None:
     T = args.pos + 1
     print(f"# {args.model} shape, {B} sequences, KV length {T}" + (f", {experts} experts read in the last layer" if moe else ""))
     print("# per phase kind, mean over layers, microseconds: span | dependency visible | first accumulator | arrival spread |"
-          " issuer waits (weights, activations%s) | stager warp 0 (slot wait, fill)" % (": accumulator wait, issue" if args.issuer else ""))
+          " issuer waits (weights, activations) | stager warp 0 (slot wait, fill)")
     total = 0.0
     for kind in names + ("lm_head",):
         a = torch.tensor(rows[kind])

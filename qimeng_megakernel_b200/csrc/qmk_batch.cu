@@ -30,7 +30,13 @@ struct qmk_batch_ctx {
   unsigned long long* moe_ne_sum;
   int* moe_elist;
   float* moe_w;
-  uint16_t* esilu;
+  unsigned char* ximg;
+  unsigned char* eimg;
+  unsigned char* aimg;
+  unsigned char* simg;
+  unsigned* img_done;
+  size_t img_bytes;       // ximg, aimg and simg are one range
+  int img_batch;          // batch size the images were last used with
   unsigned char* zero_begin;   // [phase_done | tile_tickets | attn_tickets | argmax_key]: zeroed before every launch
   size_t zero_bytes;
   unsigned* phase_done;
@@ -158,12 +164,15 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     const size_t b_part = align_up(((size_t)n_sm * 8 + (size_t)kMaxBatch * NKV) * gq * (HD + 2) * 4, 256);
     const size_t b_done = align_up((size_t)(6 * L + 1 + 2) * 4, 256);
     const size_t b_moe = moe ? align_up(256 + (size_t)E * 4, 256) + align_up((size_t)E * kMaxBatch * 4, 256) +
-                                   align_up((size_t)E * kMaxBatch * Ie * 2, 256) : 0;
+                                   align_up((size_t)E * kMaxBatch * Ie * 2, 256) +
+                                   0 : 0;
+    const size_t b_img = align_up((size_t)H * kMaxBatch * 2, 256) + align_up((size_t)NH * HD * kMaxBatch * 2, 256) +
+                         (moe ? 0 : align_up((size_t)I * kMaxBatch * 2, 256));
     const size_t b_tt = align_up((size_t)max_tiles * 4, 256);
     const size_t b_at = align_up((size_t)kMaxBatch * NKV * 4, 256);
     const size_t b_am = align_up((size_t)kMaxBatch * 8, 256);
     const size_t b_status = 256;
-    c->scratch_bytes = b_ws + b_ss + b_part + b_moe + b_done + b_tt + b_at + b_am + b_status;
+    c->scratch_bytes = b_ws + b_ss + b_part + b_moe + b_img + 2 * b_done + b_tt + b_at + b_am + b_status;
     e = cudaMalloc((void**)&c->scratch, c->scratch_bytes);
     if (e != cudaSuccess) { rc = QMK_ERR_OOM; fail(err, errlen, "cudaMalloc", e); break; }
     unsigned char* q = c->scratch;
@@ -173,10 +182,15 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
     if (moe) {
       c->moe_ne = (int*)q; c->moe_ne_sum = (unsigned long long*)(q + 64); c->moe_elist = (int*)(q + 256); q += align_up(256 + (size_t)E * 4, 256);
       c->moe_w = (float*)q; q += align_up((size_t)E * kMaxBatch * 4, 256);
-      c->esilu = (uint16_t*)q; q += align_up((size_t)E * kMaxBatch * Ie * 2, 256);
+      c->eimg = q; q += align_up((size_t)E * kMaxBatch * Ie * 2, 256);
     }
+    c->ximg = q; c->img_bytes = b_img; c->img_batch = 0;
+    q += align_up((size_t)H * kMaxBatch * 2, 256);
+    c->aimg = q; q += align_up((size_t)NH * HD * kMaxBatch * 2, 256);
+    c->simg = q; if (!moe) q += align_up((size_t)I * kMaxBatch * 2, 256);
     c->zero_begin = q;
     c->phase_done = (unsigned*)q; q += b_done;
+    c->img_done = (unsigned*)q; q += b_done;
     c->tile_tickets = (unsigned*)q; q += b_tt;
     c->attn_tickets = (unsigned*)q; q += b_at;
     c->argmax_key = (unsigned long long*)q; q += b_am;
@@ -300,7 +314,17 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.moe_elist = c->moe_elist;
   p.moe_ne_sum = c->moe_ne_sum;
   p.moe_w = c->moe_w;
-  p.esilu = c->esilu;
+  p.ximg = c->ximg;
+  p.eimg = c->eimg;
+  p.aimg = c->aimg;
+  p.simg = c->simg;
+  p.img_done = c->img_done;
+  p.pre_bpad = 32;
+  p.pre_lm_units = 2 * (d.hidden_size / kBlockK);
+  p.dense_img = 1;
+  if (const char* v = getenv("QMK_PRE_BPAD")) p.pre_bpad = atoi(v);
+  if (const char* v = getenv("QMK_PRE_LM")) p.pre_lm_units = atoi(v);
+  if (const char* v = getenv("QMK_DENSE_IMG")) p.dense_img = atoi(v);
   const bool moe = d.arch == QMK_ARCH_MOE;
   p.E = moe ? d.num_experts : 0;
   p.topk = moe ? d.num_experts_per_tok : 0;
@@ -356,6 +380,11 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
 
   cudaError_t e = cudaMemsetAsync(c->zero_begin, 0, c->zero_bytes, stream);
   if (e != cudaSuccess) return fail(err, errlen, "cudaMemsetAsync", e);
+  if (c->img_batch != st->batch) {   // the images' layout follows the padded batch, and rows from B up must read as zero
+    e = cudaMemsetAsync(c->ximg, 0, c->img_bytes, stream);
+    if (e != cudaSuccess) return fail(err, errlen, "cudaMemsetAsync", e);
+    c->img_batch = st->batch;
+  }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)c->n_sm);

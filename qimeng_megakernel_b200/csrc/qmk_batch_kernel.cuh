@@ -176,13 +176,20 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
 // Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
 // satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
 // the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
-// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival.
+// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival (7 in
+// the expert phases, which have no fill time: the issuer waiting for a free accumulator).
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
   if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = globaltimer_ns();
 }
 
 __device__ __forceinline__ void trace_val(const BParams& p, int ph, int slot, unsigned long long v) {
   if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = v;
+}
+
+// Byte offset of the 16-byte piece that holds (batch row b, column col) in an activation image: k-block col / 64, then
+// [Bpad rows][128 bytes] with the eight 16-byte pieces of a row swizzled by the row, as the tensor core reads a ring slot.
+__device__ __forceinline__ size_t img_piece(int Bpad, int b, int col) {
+  return (size_t)(col >> 6) * (size_t)(Bpad * 128) + (size_t)(b * 128 + ((((col & 63) >> 3) ^ (b & 7)) << 4));
 }
 
 struct Ctx {
@@ -278,7 +285,7 @@ __device__ __forceinline__ void producer(const Ctx& c, const TensorMaps& maps, u
     int t = d.KB > 0 ? lo / d.KB : 0, kb = lo - t * d.KB;
     int zslot = -1, zval = 0;   // expert phases: the selected expert's index is fetched when the slot changes
     auto expert_z = [&](int slot) {
-      if (slot != zslot) { zslot = slot; zval = layer * p.E + __ldcg(p.moe_elist + slot); }
+      if (slot != zslot) { zslot = slot; zval = layer * (p.E / p.ep_world) + __ldcg(p.moe_elist + slot); }   // (E / ep_world experts per layer on this rank)
       return zval;
     };
 #pragma unroll 1
@@ -328,14 +335,16 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
     unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, G), cta, lo, hi);
     int kb = d.KB > 0 ? lo % d.KB : 0;
     bool seg_start = true;
-    long long w_a = 0, w_b = 0;
+    long long w_a = 0, w_b = 0, w_acc = 0;
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
       const unsigned buf = sg & 1u;
+      const long long ta = tr ? clock64() : 0;
       if (seg_start && sg >= 2u && !mbar_wait(c, c.acc_empty(buf), ((sg >> 1) - 1u) & 1u, ph, 2)) return;
       const int s = (int)(n & (unsigned)(kStages - 1));
       const unsigned par = (n / (unsigned)kStages) & 1u;
       const long long t0 = tr ? clock64() : 0;
+      w_acc += t0 - ta;
       if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
       const long long t1 = tr ? clock64() : 0;
       if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
@@ -361,6 +370,7 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
     }
     trace_val(p, ph, 3, (unsigned long long)w_a);
     trace_val(p, ph, 4, (unsigned long long)w_b);
+    if (is_expert_kind(kind)) trace_val(p, ph, 7, (unsigned long long)w_acc);   // (these phases have no stager fill time)
   }
 }
 
@@ -383,12 +393,12 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
 // issued before the first is used, so that a warp pays one L2 round trip per group, not per unit or per piece.
 // 5 * D - 1 must stay below twice the number of ring slots: a warp that got two laps of the ring ahead of the tensor core would take an
 // old completion of a stage's mbarrier (same parity) for the one it waits for.
-template <int NPL, int D, bool EXPERT>
+template <int NPL, int D>
 __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
                                             const uint16_t* src, const uint16_t* gain, const float* rs,
-                                            int per = 0, const float* wsc = nullptr) {
-  // per > 0 (expert down-projection): k-block kb of the phase is k-block kb % per of selected expert kb / per; the
-  // source is that expert's SiLU(gate) * up [slot, row, Ie] and every row is scaled by its router weight wsc[slot, row]
+                                            unsigned char* img = nullptr) {
+  // img != nullptr (router phase): the staged block of every unit is also stored, in the same swizzled layout, as
+  // k-block u % KB of a global image [KB][Bpad * 128 bytes] that the expert up/gate phase fetches with bulk copies
   static_assert(4 * D + D - 1 < 2 * kMinStages, "a stager warp could run two ring laps ahead");
   const BParams& p = *c.p;
   const int sw = st >> 5, lane = st & 31;
@@ -400,7 +410,6 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
   for (int base = lo + sw * D; base < hi; base += 4 * D) {
     uint4 v[D][NPL];
     uint4 g4[D];
-    float sc[EXPERT ? D : 1][EXPERT ? NPL : 1];
 #pragma unroll
     for (int j = 0; j < D; ++j) {
       const int u = base + j;
@@ -412,16 +421,7 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       for (int i = 0; i < NPL; ++i) {
         const int r = row0 + 4 * i;
         v[j][i] = make_uint4(0, 0, 0, 0);
-        if (EXPERT) sc[EXPERT ? j : 0][EXPERT ? i : 0] = 0.f;
-        if (u < hi && r < p.B) {
-          if (EXPERT) {
-            const int slot = kbu / per;
-            v[j][i] = ldcg_u4(src + ((size_t)slot * kMaxBatch + r) * p.Ie + (kbu % per) * kBlockK + chunk * 8);
-            sc[EXPERT ? j : 0][EXPERT ? i : 0] = ldcg_f32(wsc + slot * kMaxBatch + r);
-          } else {
-            v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
-          }
-        }
+        if (u < hi && r < p.B) v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
       }
     }
 #pragma unroll
@@ -436,6 +436,7 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       w_slot += t1 - t0;
       if (!ok) continue;
       unsigned char* dst = c.smem + p.off_stages + s * p.stage_bytes + kABytes;
+      unsigned char* gdst = img != nullptr ? img + (size_t)(u % d.KB) * (size_t)(p.Bpad * 128) : nullptr;
       const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4[j]);
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
@@ -449,14 +450,12 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
             const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
             w[q] = pack_bf16x2(a, b);
           }
-        } else if (EXPERT) {
-          uint32_t* w = reinterpret_cast<uint32_t*>(&v[j][i]);
-          const float f = sc[EXPERT ? j : 0][EXPERT ? i : 0];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf_lo(w[q]) * f, bf_hi(w[q]) * f);
         }
-        *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[j][i];
+        const int off = r * 128 + ((chunk ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst + off) = v[j][i];
+        if (gdst != nullptr) *reinterpret_cast<uint4*>(gdst + off) = v[j][i];
       }
+      if (gdst != nullptr) __threadfence();   // the image is read by other CTAs once this phase's counter is complete
       fence_async_smem();
       mbar_arrive1(c.b_full(s));
       if (tr) w_fill += clock64() - t1;
@@ -465,6 +464,43 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
   if (st == 0) {
     trace_val(p, ph, 6, (unsigned long long)w_slot);
     trace_val(p, ph, 7, (unsigned long long)w_fill);
+  }
+}
+
+// Activation operand of units [lo, hi) from a global image [KB][Bpad * 128 bytes] that already has the layout of a ring
+// slot's activation half: one bulk copy per unit, issued by lane 0 of the warp that owns the unit (units are dealt to the
+// four warps round-robin), completing on the slot's b_full barrier together with the 32 arrivals of the warp.
+__device__ __forceinline__ void stage_images(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
+                                             const unsigned char* img) {
+  const BParams& p = *c.p;
+  const int sw = st >> 5, lane = st & 31;
+  const uint32_t bytes = (uint32_t)p.Bpad * 128u;
+  // the image was written with ordinary stores by other CTAs (seen through the phase counter): order them before this
+  // thread's bulk copies, which read through the async proxy
+  asm volatile("fence.proxy.async;" ::: "memory");
+  long long w_slot = 0;
+  const bool tr = p.trace != nullptr;
+#pragma unroll 1
+  for (int u = lo + sw; u < hi; u += 4) {
+    const unsigned nu = n + (unsigned)(u - lo);
+    const int s = (int)(nu & (unsigned)(kStages - 1));
+    const long long t0 = tr ? clock64() : 0;
+    const bool ok = nu < (unsigned)kStages || mbar_wait(c, c.empty(s), ((nu / (unsigned)kStages) - 1u) & 1u, ph, 5);
+    if (tr) w_slot += clock64() - t0;
+    if (!ok) continue;
+    if (lane == 0) {
+      const uint32_t dst = smem_u32(c.smem + p.off_stages + s * p.stage_bytes + kABytes);
+      const unsigned char* g = img + (size_t)(u % d.KB) * bytes;
+      asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(c.b_full(s)), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                   "l"(g), "r"(bytes), "r"(c.b_full(s))
+                   : "memory");
+    }
+    __syncwarp();
+    mbar_arrive1(c.b_full(s));
+  }
+  if (st == 0) {
+    trace_val(p, ph, 6, (unsigned long long)w_slot);
   }
 }
 
@@ -483,7 +519,17 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   const PhaseDims d = phase_dims(p, kind, is_expert_kind(kind) ? (int)c.ctl[kCNeStg] : 0);
   int lo, hi;
   unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, (int)gridDim.x), (int)blockIdx.x, lo, hi);
-  const bool normed = phase_normed(kind);
+  // Where the operand comes from.  Expert phases: images (the normalised residual stream stored by the router phase's
+  // stagers; SiLU(gate) * up times the router weight stored by the expert up/gate epilogue).  O-proj and down-proj: the
+  // image the attention / up-gate phase stored beside its plain output, when that phase ran in this launch.  Normalised
+  // phases with enough work per k-block (wide batches; the LM head when a CTA walks the k-blocks more than once): an
+  // image built by a pre-pass, CTA i normalising k-block i, behind one more grid-wide counter.  Else: staged per unit.
+  const bool expert = is_expert_kind(kind);
+  const bool plain_img = (kind == kOproj || kind == kDown) && ph > p.phase_begin && p.dense_img != 0;
+  const bool normed = phase_normed(kind) && !expert;
+  const int KBx = p.H / kBlockK;
+  const bool pre = normed && kind != kRouter && p.H % kBlockK == 0 &&
+                   (kind == kLmHead ? (d.T * d.KB) / (int)gridDim.x >= p.pre_lm_units : p.Bpad >= p.pre_bpad);   // (the same on every CTA)
   float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
   if (normed) {
     if (st < p.Bpad) {
@@ -500,26 +546,50 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
     }
     named_bar(kBarStg, 128);
   }
-  const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : kind == kEDown ? p.esilu : p.hidden;
+  const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : p.hidden;
   const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
                        : kind == kLmHead ? p.lm_norm : p.mlp_norm + (size_t)layer * p.H;
-  const int per = kind == kEDown ? p.Ie / kBlockK : 0;
-  const float* wsc = kind == kEDown ? p.moe_w : nullptr;
+  if (pre) {
+    // (every CTA takes part, also one without units in this phase: the counter's target is the number of k-blocks)
+    const int chunk = st & 7;
+    for (int kb = (int)blockIdx.x; kb < KBx; kb += (int)gridDim.x) {
+      const int k0 = kb * kBlockK + chunk * 8;
+      const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gain + k0));
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
+      for (int r = st >> 3; r < p.Bpad; r += 16) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < p.B) {
+          v = ldcg_u4(src + (size_t)r * p.H + k0);
+          const float f = rs[r];
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float a = bf16_round(bf_lo(w[q]) * f) * bf_lo(gw[q]);
+            const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
+            w[q] = pack_bf16x2(a, b);
+          }
+        }
+        *reinterpret_cast<uint4*>(p.ximg + img_piece(p.Bpad, r, k0)) = v;
+      }
+      __threadfence();
+      named_bar(kBarStg, 128);
+      if (st == 0) atom_add_acq_rel_gpu(p.img_done + ph, 1u);
+    }
+    if (st == 0) counter_wait(c, p.img_done + ph, (unsigned)KBx, ph);
+    named_bar(kBarStg, 128);
+  }
   if (hi > lo) {
     const uint16_t* gn = normed ? gain : nullptr;
-    if (kind == kEDown) {
-      switch (p.Bpad) {
-        case 16: stage_units<4, 2, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
-        case 32: stage_units<8, 2, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
-        case 48: stage_units<12, 1, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
-        default: stage_units<16, 1, true>(c, ph, d, lo, hi, st, n, src, gn, rs, per, wsc); break;
-      }
+    if (expert || plain_img || pre) {
+      const unsigned char* img = kind == kEDown ? p.eimg : kind == kOproj ? p.aimg : kind == kDown ? p.simg : p.ximg;
+      stage_images(c, ph, d, lo, hi, st, n, img);
     } else {
+      unsigned char* img = kind == kRouter ? p.ximg : nullptr;
       switch (p.Bpad) {
-        case 16: stage_units<4, 2, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
-        case 32: stage_units<8, 2, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
-        case 48: stage_units<12, 1, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
-        default: stage_units<16, 1, false>(c, ph, d, lo, hi, st, n, src, gn, rs); break;
+        case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
+        case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
+        case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
+        default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
       }
     }
   }
@@ -758,14 +828,24 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
     case kEUpGate: {
       // fused_routed_expert_upgate (operations.py:197-219): gate and up rounded to bf16 (a bf16 linear), SiLU(gate) * up
       // in fp32, one rounding.  Tile rows 0..63 are gate rows, 64..127 the up rows of the same units of one expert.
+      // The result goes out as the activation operand of the expert down-projection: times the row's router weight
+      // (rounded to bf16 again: the weight rides in the operand), as k-block (slot, lt) of the image [slot * per + lt]
+      // [Bpad rows][128 bytes, 16-byte pieces swizzled by the row], rows from B up zeroed.
       const int per = p.Ie / kBlockK;
       const int slot = t / per, lt = t % per;
       const int u = e & 63, half = e >> 6;
+      float* wrow = reinterpret_cast<float*>(c.smem + Smem::kOffHs);   // [64] router weights of this expert's rows
+      if (e < kMaxBatch) wrow[e] = ldcg_f32(p.moe_w + slot * kMaxBatch + e);
+      named_bar(kBarEpi, 128);
       const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
-      for (int b = b0; b < b1 && b < B; ++b) {
-        const float g = bf16_round(exch[u * p.exch_stride + b]), up = bf16_round(exch[(64 + u) * p.exch_stride + b]);
-        const float v = act_s[b] ? (g / (1.0f + __expf(-g))) * up : 0.f;
-        p.esilu[((size_t)slot * kMaxBatch + b) * p.Ie + lt * (kTileRows / 2) + u] = f32_to_bf16_bits(v);
+      unsigned char* blk = p.eimg + (size_t)(slot * per + lt) * (size_t)(p.Bpad * 128);
+      for (int b = b0; b < b1; ++b) {
+        float v = 0.f;
+        if (b < B && act_s[b]) {
+          const float g = bf16_round(exch[u * p.exch_stride + b]), up = bf16_round(exch[(64 + u) * p.exch_stride + b]);
+          v = bf16_round((g / (1.0f + __expf(-g))) * up) * wrow[b];
+        }
+        *reinterpret_cast<unsigned short*>(blk + b * 128 + (((u >> 3) ^ (b & 7)) << 4) + (u & 7) * 2) = f32_to_bf16_bits(v);
       }
       break;
     }
@@ -826,6 +906,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
           const unsigned short bits =
               act_s[b] ? silu_mul(exch[u * p.exch_stride + b], exch[(64 + u) * p.exch_stride + b]) : (unsigned short)0;
           p.silu_out[(size_t)b * p.I + unit] = bits;
+          *reinterpret_cast<unsigned short*>(p.simg + img_piece(p.Bpad, b, unit) + (unit & 7) * 2) = bits;
         }
       }
       break;
@@ -986,7 +1067,10 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
     uint16_t* outp = p.attn_out + (size_t)b * p.QDIM + (size_t)kvh * GQ * HD;
     if (!act_s[b]) {   // fused_decode_attention zeroes the output of an inactive row (operations.py:226-231)
       if (ch == 0)
-        for (int i = lane; i < GQ * HD / 8; i += 32) reinterpret_cast<uint4*>(outp)[i] = make_uint4(0, 0, 0, 0);
+        for (int i = lane; i < GQ * HD / 8; i += 32) {
+          reinterpret_cast<uint4*>(outp)[i] = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(p.aimg + img_piece(p.Bpad, b, kvh * GQ * HD + i * 8)) = make_uint4(0, 0, 0, 0);
+        }
       continue;
     }
     if (ch >= nsplit) continue;
@@ -1093,6 +1177,7 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
           o4.z = pack_bf16x2(acc[g][4] * inv, acc[g][5] * inv);
           o4.w = pack_bf16x2(acc[g][6] * inv, acc[g][7] * inv);
           *reinterpret_cast<uint4*>(outp + g * HD + dl * 8) = o4;
+          *reinterpret_cast<uint4*>(p.aimg + img_piece(p.Bpad, b, (kvh * GQ + g) * HD + dl * 8)) = o4;
         }
       }
       continue;
@@ -1152,6 +1237,7 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
       o4.z = pack_bf16x2(o[4] * inv, o[5] * inv);
       o4.w = pack_bf16x2(o[6] * inv, o[7] * inv);
       *reinterpret_cast<uint4*>(outp + g * HD + dd * 8) = o4;
+      *reinterpret_cast<uint4*>(p.aimg + img_piece(p.Bpad, b, (kvh * GQ + g) * HD + dd * 8)) = o4;
     }
   }
 }

@@ -60,7 +60,15 @@ struct BParams {
   int* moe_elist;                // [E]  their indices, ascending
   unsigned long long* moe_ne_sum; // [1]  distinct experts summed over every router phase since the last reset
   float* moe_w;                  // [E, kMaxBatch]  router weight of (slot, row), 0 where the row did not select it
-  uint16_t* esilu;               // [E, kMaxBatch, Ie]  SiLU(gate) * up of (slot, row), bf16
+  // activation operands kept as images of a ring slot's activation half: [k-block][Bpad rows][128 bytes, swizzled]
+  unsigned char* ximg;           // H / 64 k-blocks: the normalised residual stream (router phase, or a pre-pass)
+  unsigned char* aimg;           // QDIM / 64 k-blocks: the attention output (written by the attention phase)
+  unsigned char* simg;           // I / 64 k-blocks: SiLU(gate) * up (written by the up/gate epilogue)
+  unsigned* img_done;            // [phases]  k-blocks of ximg built by the pre-pass of a phase (zeroed per launch)
+  int pre_bpad;                  // normalised layer phases use the pre-pass from this padded batch on
+  int pre_lm_units;              // the LM head uses it when a CTA has at least this many units
+  int dense_img;                 // O-proj / down-proj read aimg / simg (when their producer ran in the launch)
+  unsigned char* eimg;           // selected-expert slot * (Ie / 64) + k-block: SiLU(gate) * up * router weight
   unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off
   // ---- expert parallelism (ep_world > 1): every rank holds E / ep_world experts, attention and router are replicated;
   // after its local expert down-projection a rank stores each finished [128 rows, Bpad] fp32 partial tile into its slot

@@ -52,7 +52,7 @@ def main() -> None:
         mk(g)
         torch.cuda.synchronize()
         mk.check_status()
-        mine = g.logits.view(torch.int16).cpu()
+        mine = g.logits.contiguous().view(torch.uint8).cpu()      # bytes: gloo gathers no 16-bit types
         gathered = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
         if not all(torch.equal(gathered[0], t) for t in gathered):
