@@ -312,12 +312,13 @@ def run_batch1(args, K: int, W: int, D: Dist, local_rank: int) -> dict | None:
     return line
 
 
-def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_rank: int, ep: int = 1) -> dict | None:
+def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_rank: int, ep: int = 1, tp: int = 1) -> dict | None:
     """B independent seeded sequences per GPU (batch-sharded over the ranks, no collective), every step one launch of
     the batched kernel; the device feeds each row's arg-max back as its next token.  Same timing rules as the headline.
     ep > 1 (mixture-of-experts shapes, one rank per GPU, world == ep): every rank decodes the SAME B sequences and holds
-    E / ep experts; the partial expert outputs cross NVLink inside the kernel.  Total work is fixed: strong scaling."""
-    from qimeng_megakernel_b200 import expert_parallel, mk_kernel, synthetic
+    E / ep experts; the partial expert outputs cross NVLink inside the kernel.  Total work is fixed: strong scaling.
+    tp > 1 (dense shapes, world == tp): the same, with every projection cut over the ranks (tensor parallelism)."""
+    from qimeng_megakernel_b200 import expert_parallel, mk_kernel, synthetic, tensor_parallel
     from qimeng_megakernel_b200.model_config import LLAMA_3_2_1B, OLMOE_1B_7B, QWEN3_0_6B
     dev = D.dev
     config = dict({"llama-3.2-1b": LLAMA_3_2_1B, "qwen3-0.6b": QWEN3_0_6B, "olmoe-1b-7b": OLMOE_1B_7B}[model])
@@ -331,12 +332,20 @@ def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_
         weights = expert_parallel.shard_moe_weights(weights, D.rank, ep)      # the full copies are dropped here
         config = expert_parallel.shard_config(config, D.rank, ep)
         torch.cuda.empty_cache()
+    full_vocab = config["vocab_size"]
+    if tp > 1:
+        if D.world != tp or config.get("num_experts"):
+            raise SystemExit("--tp N needs a dense --model and exactly N ranks (torchrun --nproc-per-node N)")
+        weights = tensor_parallel.shard_weights(config, weights, D.rank, tp)
+        config = tensor_parallel.shard_config(config, D.rank, tp)
+        torch.cuda.empty_cache()
     g = synthetic.make_globals(config, weights, kv_seq_len=kv_len, device=dev, batch=B)
     mk = mk_kernel.get_mk()
     mk.set_kernel_variant(1)
-    if ep > 1:
+    if ep > 1 or tp > 1:
         expert_parallel.connect(mk, g)
-    prompts = synthetic.make_prompts(config["vocab_size"], B, PROMPT_LEN, seed=1 + (0 if ep > 1 else D.rank * B)).to(dev)
+    par = max(ep, tp)                        # ranks that decode the same sequences together
+    prompts = synthetic.make_prompts(full_vocab, B, PROMPT_LEN, seed=1 + (0 if par > 1 else D.rank * B)).to(dev)
     g.token_in = torch.zeros(B, dtype=torch.int64, device=dev)
     g.next_token = torch.zeros(B, dtype=torch.int64, device=dev)
     for pos in range(PROMPT_LEN):           # the prompts, one position per launch (fills the KV cache)
@@ -396,13 +405,13 @@ def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_
     mk.close()
     line = None
     if D.rank == 0:
-        world = 1 if ep > 1 else D.world       # under expert parallelism all ranks decode the same sequences
+        world = 1 if par > 1 else D.world      # under model parallelism all ranks decode the same sequences
         peak, peak_src = measured_peak_gbs()
         achieved = step_bytes / (kernel_s / K) / 1e9
         line = {
             "metric": f"decode kernel_tok_s at batch {B} per GPU ({model} shape)", "value": world * B * K / kernel_s,
             "unit": "tokens/s", "n_gpus": D.world, "steps": K, "warmup": W, "ms_per_step": kernel_s / K * 1e3,
-            "higher_is_better": True, "scaling": "strong" if ep > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if par > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{model} shape, bf16, {B} independent seeded 16-token prompts per GPU, greedy decode "
                                    "forced past EOS", "decode_steps": K,
                        "kv_lengths": [first_timed_pos + 1, first_timed_pos + K], "sequences_per_gpu": B,
@@ -410,7 +419,11 @@ def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_
                        "sharding": (f"expert parallel over {ep} GPUs: the same sequences on every GPU, {config['num_experts'] // ep} of "
                                     f"{config['num_experts']} experts each, partial expert outputs pushed to the peers over NVLink "
                                     "inside the kernel and added in rank order; roofline figures are rank 0's own bytes"
-                                    if ep > 1 else "sequences sharded over the GPUs, full weight copy each, no collective"),
+                                    if ep > 1 else
+                                    f"tensor parallel over {tp} GPUs: the same sequences on every GPU, 1 / {tp} of every projection "
+                                    "each, partial O-proj and down-proj sums pushed to the peers over NVLink inside the kernel and "
+                                    "added in rank order, arg-max over the ranks' vocabulary slices; roofline figures are rank 0's own bytes"
+                                    if tp > 1 else "sequences sharded over the GPUs, full weight copy each, no collective"),
                        "l2": "inputs larger than L2: every step streams the weights through a 126 MB L2",
                        "launch": {"ctas": ctas, "threads": threads, "smem_bytes": smem}},
             "e2e": {"value": world * B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
@@ -444,11 +457,12 @@ def main() -> None:
     ap.add_argument("--model", default="llama-3.2-1b", choices=["llama-3.2-1b", "qwen3-0.6b", "olmoe-1b-7b"])
     ap.add_argument("--kernel", default="auto", choices=["auto", "batched"], help="batched: the batched kernel also at batch 1")
     ap.add_argument("--ep", type=int, default=1, help="expert parallelism over this many GPUs (mixture-of-experts --model; equals the number of ranks)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor parallelism over this many GPUs (dense --model; equals the number of ranks; batched kernel)")
     ap.add_argument("--layers", type=int, default=0,
                     help="batched runs only: keep this many decoder layers (a small case for a profiler capture; the line says so)")
     args = ap.parse_args()
     K, W = args.steps, max(3, args.warmup)
-    single = args.batch != 1 or args.model != "llama-3.2-1b" or args.kernel == "batched"
+    single = args.batch != 1 or args.model != "llama-3.2-1b" or args.kernel == "batched" or args.tp > 1
     if args.impl == "reference":
         if single:
             raise SystemExit("--impl reference times the headline workload (batch 1, Llama-3.2-1B shape) only")
@@ -462,7 +476,7 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     D = Dist(dev)
     if single:
-        line = run_batched(args.model, args.batch, K, W, args.layers, D, local_rank, ep=args.ep)
+        line = run_batched(args.model, args.batch, K, W, args.layers, D, local_rank, ep=args.ep, tp=args.tp)
     else:
         line = run_batch1(args, K, W, D, local_rank)
         if not args.no_secondary:

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define QMK_ABI_VERSION 4
+#define QMK_ABI_VERSION 5
 
 /* Error codes (negative).  qmk_strerror() gives the text. */
 enum qmk_error {
@@ -88,6 +88,17 @@ typedef struct qmk_model_desc {
                                     this handle holds num_experts / ep_world experts, expert_gate_up / expert_down are
                                     [L, num_experts / ep_world, ...]; everything else is replicated             */
   int32_t ep_rank;               /* this handle's rank: it holds experts [ep_rank, ep_rank + 1) * num_experts / ep_world */
+  int32_t tp_world;              /* QMK_ARCH_LLAMA / QMK_ARCH_QWEN3: tensor-parallel ranks (0 or 1 = off; 2, 4, 8).  The
+                                    descriptor then describes this rank's SLICE: num_attention_heads, num_key_value_heads,
+                                    intermediate_size and vocab_size are the whole model's divided by tp_world, the weight
+                                    tensors are the matching slices (Q/K/V rows of its heads, O-proj columns of its heads,
+                                    up/gate rows and down-proj columns of its intermediate units, LM-head rows of its
+                                    vocabulary slice), hidden_size and the norms are whole.  The partial sums of the O-proj
+                                    and down-proj phases are exchanged like the expert tiles (qmk_ep_export /
+                                    qmk_ep_connect); the arg-max runs over all ranks' vocabulary slices.  logits is this
+                                    rank's [B, vocab_size] slice                                                   */
+  int32_t tp_rank;               /* this handle's rank; its LM-head rows are global rows tp_rank * vocab_size ...   */
+  int32_t embed_rows;            /* rows of embed_tokens (0 = vocab_size): the whole vocabulary under tensor parallelism */
 } qmk_model_desc;
 
 /*
@@ -242,9 +253,10 @@ int qmk_set_kernel_variant(qmk_handle* h, int32_t variant);
 
 /* Optional device timeline (the counterpart of the reference's ENABLE_PROFILING clock64 buffer,
  * qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/multi_batch/decode_kernel/profiling.cuh:7-35, selected
- * at run time instead of compile time).  device_buffer: uint64 [CTAs, phases, 8] globaltimer nanoseconds,
- * slots 0 dependency satisfied, 1 activations staged, 2 first worker enters, 5 first worker leaves,
- * 6 last worker leaves.  NULL switches tracing off. */
+ * at run time instead of compile time).  device_buffer: uint64 [CTAs, phases, W], W = 8 words for the batch-1 kernel
+ * (globaltimer nanoseconds: 0 dependency satisfied, 1 activations staged, 2 first worker enters, 5 first worker
+ * leaves, 6 last worker leaves) and 16 for the batched kernel (stamps and cycle sums, listed in
+ * csrc/qmk_batch_kernel.cuh).  NULL switches tracing off. */
 int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes);
 
 /* Algorithmic HBM bytes of one decode step at KV length pos_id+1 (weights + KV read + KV write). */

@@ -11,7 +11,7 @@ from pathlib import Path
 
 from ._build import LIB_PATH
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 ARCH_LLAMA = 0
 ARCH_QWEN3 = 1
 ARCH_MOE = 2
@@ -31,7 +31,8 @@ class ModelDesc(C.Structure):
                 ("head_dim", C.c_int32), ("vocab_size", C.c_int32), ("rope_rows", C.c_int32),
                 ("rms_norm_eps", C.c_float), ("attn_scale", C.c_float), ("qk_norm_eps", C.c_float),
                 ("num_experts", C.c_int32), ("num_experts_per_tok", C.c_int32), ("moe_intermediate_size", C.c_int32),
-                ("ep_world", C.c_int32), ("ep_rank", C.c_int32)]
+                ("ep_world", C.c_int32), ("ep_rank", C.c_int32),
+                ("tp_world", C.c_int32), ("tp_rank", C.c_int32), ("embed_rows", C.c_int32)]
 
 
 class WeightPtrs(C.Structure):

@@ -40,6 +40,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--model", default="llama-3.2-1b", choices=sorted(MODELS))
     ap.add_argument("--pos", type=int, default=299)
+    ap.add_argument("--detail", default="", help="phase kind whose per-CTA stamps (second layer) are listed for the CTAs that had work")
     args = ap.parse_args()
     cfg = dict(MODELS[args.model])
     B, dev = args.batch, torch.device("cuda")
@@ -57,7 +58,7 @@ def main() -> None:
     for pos in range(args.pos + 1):
         g.position_id = pos
         if pos == args.pos:
-            trace = torch.zeros(mk.geometry()[0], nph, 8, dtype=torch.int64, device=dev)
+            trace = torch.zeros(mk.geometry()[0], nph, 16, dtype=torch.int64, device=dev)
             mk.set_trace(trace)
         mk(g)
     torch.cuda.synchronize()
@@ -79,11 +80,12 @@ def main() -> None:
             float(first[first > 0].min() - prev) if bool((first > 0).any()) else 0.0,
             float(arr.max() - arr[arr > 0].min()),
             float(t[:, ph, 3].mean()) / ghz, float(t[:, ph, 4].mean()) / ghz,
-            float(t[:, ph, 6].mean()) / ghz, float(t[:, ph, 7].mean()) / ghz))
+            float(t[:, ph, 6].mean()) / ghz, float(t[:, ph, 7].mean()) / ghz,
+            float(t[:, ph, 8].mean()) / ghz, float(t[:, ph, 9].mean()) / ghz, float(t[:, ph, 10].mean()) / ghz))
     T = args.pos + 1
     print(f"# {args.model} shape, {B} sequences, KV length {T}" + (f", {experts} experts read in the last layer" if moe else ""))
     print("# per phase kind, mean over layers, microseconds: span | dependency visible | first accumulator | arrival spread |"
-          " issuer waits (weights, activations) | stager warp 0 (slot wait, fill)")
+          " issuer (waits: weights, activations, accumulator; issuing MMAs; commits) | stager warp 0 (slot wait, fill)")
     total = 0.0
     for kind in names + ("lm_head",):
         a = torch.tensor(rows[kind])
@@ -91,9 +93,19 @@ def main() -> None:
         nbytes = phase_bytes(cfg, kind, T, B, experts)
         total += float(a[:, 0].sum())
         print(f"{kind:14s} n={len(rows[kind]):3d} span {m[0] / 1e3:7.2f}  dep {m[1] / 1e3:5.2f}  first-acc {m[2] / 1e3:5.2f}  "
-              f"spread {m[3] / 1e3:6.2f}  issuer {m[4] / 1e3:6.2f} {m[5] / 1e3:6.2f}  stager {m[6] / 1e3:6.2f} {m[7] / 1e3:6.2f}  "
+              f"spread {m[3] / 1e3:6.2f}  issuer {m[4] / 1e3:6.2f} {m[5] / 1e3:6.2f} {m[8] / 1e3:6.2f} {m[9] / 1e3:6.2f} {m[10] / 1e3:6.2f}  "
+              f"stager {m[6] / 1e3:6.2f} {m[7] / 1e3:6.2f}  "
               f"| {nbytes / 1e6:9.2f} MB -> {nbytes / float(m[0]) :8.1f} GB/s  (phase total {float(a[:, 0].sum()) / 1e3:8.1f} us)")
     print(f"step total {total / 1e3:.1f} us")
+    if args.detail:
+        ph = ppl + names.index(args.detail) if args.detail != "lm_head" else ppl * L
+        prev = float(t[:, ph - 1, 5].max())
+        print(f"# {args.detail}, phase {ph}: per CTA with work, microseconds after the previous phase's last arrival: dependency |"
+              " first accumulator | arrival")
+        for cta in range(t.shape[0]):
+            if float(t[cta, ph, 1]) > 0 or args.detail == "attn":
+                v = [float(t[cta, ph, k]) for k in (0, 1, 5)]
+                print(f"  cta {cta:3d} " + " ".join(f"{(x - prev) / 1e3:8.2f}" if x > 0 else "       -" for x in v))
 
 
 if __name__ == "__main__":

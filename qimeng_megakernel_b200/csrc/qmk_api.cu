@@ -466,7 +466,7 @@ extern "C" int qmk_set_timeout_cycles(qmk_handle* h, int64_t cycles) {
 extern "C" int qmk_set_trace(qmk_handle* h, void* device_buffer, int64_t bytes) {
   if (!h) return QMK_ERR_INVALID_ARG;
   if (device_buffer == nullptr) { h->trace = nullptr; return QMK_OK; }
-  const int64_t need = (int64_t)h->n_sm * (use_batched(h) ? qmkb_num_phases(&h->desc) : num_phases(h->desc.num_layers)) * 8 * 8;
+  const int64_t need = (int64_t)h->n_sm * (use_batched(h) ? qmkb_num_phases(&h->desc) * 2 : num_phases(h->desc.num_layers)) * 8 * 8;   // 16 words per (CTA, phase) in the batched kernel, 8 in the batch-1 kernel
   if (bytes < need || (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) return QMK_ERR_INVALID_ARG;
   h->trace = (unsigned long long*)device_buffer;
   return QMK_OK;

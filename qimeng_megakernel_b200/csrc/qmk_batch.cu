@@ -47,7 +47,7 @@ struct qmk_batch_ctx {
   unsigned epoch;
   // expert parallelism
   unsigned char* ep_local;       // this rank's exchange buffer (data, then flags)
-  size_t ep_data_bytes, ep_bytes;
+  size_t ep_data_bytes, ep_flag_bytes, ep_key_bytes, ep_bytes;
   void* ep_peer[8];              // every rank's buffer as mapped here (own = ep_local); null until connected
   bool ep_connected;
 };
@@ -71,6 +71,11 @@ int qmkb_supported(const qmk_model_desc* d) {
   if (d->ep_world > 1) {
     if (d->arch != QMK_ARCH_MOE || (d->ep_world != 2 && d->ep_world != 4 && d->ep_world != 8) ||
         d->num_experts % d->ep_world != 0 || d->ep_rank < 0 || d->ep_rank >= d->ep_world)
+      return QMK_ERR_UNSUPPORTED_MODEL;
+  }
+  if (d->tp_world > 1) {
+    if (d->arch == QMK_ARCH_MOE || (d->tp_world != 2 && d->tp_world != 4 && d->tp_world != 8) || d->tp_rank < 0 ||
+        d->tp_rank >= d->tp_world || d->embed_rows < d->vocab_size * d->tp_world)
       return QMK_ERR_UNSUPPORTED_MODEL;
   }
   if (HD != 64 && HD != 128) return QMK_ERR_UNSUPPORTED_MODEL;
@@ -208,14 +213,21 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
   return QMK_OK;
 }
 
+static int exchange_world(const qmk_model_desc& d) { return d.ep_world > 1 ? d.ep_world : (d.tp_world > 1 ? d.tp_world : 1); }
+static int exchange_rank(const qmk_model_desc& d) { return d.ep_world > 1 ? d.ep_rank : (d.tp_world > 1 ? d.tp_rank : 0); }
+
 int qmkb_ep_export(qmk_batch_ctx* c, void* ipc_handle_out, char* err, size_t errlen) {
   const qmk_model_desc& d = c->desc;
-  if (d.ep_world <= 1 || !ipc_handle_out) return QMK_ERR_INVALID_ARG;
+  const int xw = exchange_world(d);
+  if (xw <= 1 || !ipc_handle_out) return QMK_ERR_INVALID_ARG;
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the ABI documents a 64-byte handle");
   if (!c->ep_local) {
     const size_t tiles = (size_t)((d.hidden_size + kTileRows - 1) / kTileRows);
-    c->ep_data_bytes = align_up((size_t)2 * d.ep_world * tiles * kTileRows * kMaxBatch * 4, 256);
-    c->ep_bytes = c->ep_data_bytes + align_up((size_t)2 * d.ep_world * tiles * 4, 256);
+    // [2 buffers][source rank][tile][128][64] floats | [2][source][tile] flags | [source][64] arg-max keys | [source] key flags
+    c->ep_data_bytes = align_up((size_t)2 * xw * tiles * kTileRows * kMaxBatch * 4, 256);
+    c->ep_flag_bytes = align_up((size_t)2 * xw * tiles * 4, 256);
+    c->ep_key_bytes = align_up((size_t)xw * kMaxBatch * 8, 256);
+    c->ep_bytes = c->ep_data_bytes + c->ep_flag_bytes + c->ep_key_bytes + 256;
     cudaError_t e = cudaMalloc((void**)&c->ep_local, c->ep_bytes);
     if (e != cudaSuccess) { fail(err, errlen, "cudaMalloc(exchange buffer)", e); return QMK_ERR_OOM; }
     e = cudaMemset(c->ep_local, 0, c->ep_bytes);
@@ -230,10 +242,11 @@ int qmkb_ep_export(qmk_batch_ctx* c, void* ipc_handle_out, char* err, size_t err
 
 int qmkb_ep_connect(qmk_batch_ctx* c, const void* ipc_handles, char* err, size_t errlen) {
   const qmk_model_desc& d = c->desc;
-  if (d.ep_world <= 1 || !ipc_handles || !c->ep_local) return QMK_ERR_INVALID_ARG;
+  const int xw = exchange_world(d), xr = exchange_rank(d);
+  if (xw <= 1 || !ipc_handles || !c->ep_local) return QMK_ERR_INVALID_ARG;
   if (c->ep_connected) return QMK_OK;
-  for (int r = 0; r < d.ep_world; ++r) {
-    if (r == d.ep_rank) { c->ep_peer[r] = c->ep_local; continue; }
+  for (int r = 0; r < xw; ++r) {
+    if (r == xr) { c->ep_peer[r] = c->ep_local; continue; }
     cudaIpcMemHandle_t hnd;
     memcpy(&hnd, (const unsigned char*)ipc_handles + (size_t)r * sizeof(hnd), sizeof(hnd));
     const cudaError_t e = cudaIpcOpenMemHandle(&c->ep_peer[r], hnd, cudaIpcMemLazyEnablePeerAccess);
@@ -246,8 +259,8 @@ int qmkb_ep_connect(qmk_batch_ctx* c, const void* ipc_handles, char* err, size_t
 void qmkb_destroy(qmk_batch_ctx* c) {
   if (!c) return;
   if (c->ep_connected)
-    for (int r = 0; r < c->desc.ep_world; ++r)
-      if (r != c->desc.ep_rank && c->ep_peer[r]) cudaIpcCloseMemHandle(c->ep_peer[r]);
+    for (int r = 0; r < exchange_world(c->desc); ++r)
+      if (r != exchange_rank(c->desc) && c->ep_peer[r]) cudaIpcCloseMemHandle(c->ep_peer[r]);
   if (c->ep_local) cudaFree(c->ep_local);
   if (c->scratch) cudaFree(c->scratch);
   delete c;
@@ -334,14 +347,22 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.epoch = ++c->epoch;
   p.ep_world = moe && d.ep_world > 1 ? d.ep_world : 1;
   p.ep_rank = p.ep_world > 1 ? d.ep_rank : 0;
-  if (p.ep_world > 1) {
+  p.x_world = exchange_world(d);
+  p.x_rank = exchange_rank(d);
+  p.x_per_layer = d.tp_world > 1 ? 2 : 1;
+  p.vocab_offset = d.tp_world > 1 ? d.tp_rank * d.vocab_size : 0;
+  p.embed_rows = d.embed_rows > 0 ? d.embed_rows : d.vocab_size;
+  if (p.x_world > 1) {
     if (!c->ep_connected) {
-      if (err && errlen) snprintf(err, errlen, "expert parallelism: qmk_ep_connect has not been called");
+      if (err && errlen) snprintf(err, errlen, "model parallelism: qmk_ep_connect has not been called");
       return QMK_ERR_NOT_BOUND;
     }
-    for (int r = 0; r < p.ep_world; ++r) {
-      p.ep_buf[r] = (float*)c->ep_peer[r];
-      p.ep_flag[r] = (unsigned*)((unsigned char*)c->ep_peer[r] + c->ep_data_bytes);
+    for (int r = 0; r < p.x_world; ++r) {
+      unsigned char* base = (unsigned char*)c->ep_peer[r];
+      p.ep_buf[r] = (float*)base;
+      p.ep_flag[r] = (unsigned*)(base + c->ep_data_bytes);
+      p.ep_key[r] = (unsigned long long*)(base + c->ep_data_bytes + c->ep_flag_bytes);
+      p.ep_kflag[r] = (unsigned*)(base + c->ep_data_bytes + c->ep_flag_bytes + c->ep_key_bytes);
     }
   }
   p.H = d.hidden_size;

@@ -49,6 +49,7 @@ constexpr int kNumWarps = 10;
 constexpr int kBatchThreads = kNumWarps * 32;
 constexpr int kEpiWarp0 = 2, kStgWarp0 = 6;
 constexpr int kBarEpi = 1, kBarStg = 2, kBarAttn = 3;   // named barriers (0 is __syncthreads)
+constexpr int kTraceSlots = 16;                         // 64-bit words per (CTA, phase) of the optional timeline
 constexpr int kSmemBudget = 227 * 1024;                 // dynamic shared memory a CTA may ask for on sm_100
 
 // Shared memory: a fixed header, then the fp32 exchange tile [128][Bpad + 1], then the ring on a 1024-byte boundary
@@ -56,7 +57,10 @@ constexpr int kSmemBudget = 227 * 1024;                 // dynamic shared memory
 // batches get more slots: more weight bytes in flight per SM.
 struct Smem {
   static constexpr int kOffBars = 0;                                          // mbarriers
-  //   a_full[kMaxStages] b_full[kMaxStages] empty[kMaxStages] acc_full[2] acc_empty[2]
+  //   full[kMaxStages] (unused)[kMaxStages] empty[kMaxStages / 2] ... acc_full[2] acc_empty[2]
+  // A slot's `full` barrier collects both operands of a unit: the producer's arrive with the weight bytes expected, and
+  // the 32 arrivals of the stager warp (after its stores, or with the bytes of its bulk copy expected).  `empty` is per
+  // PAIR of slots: the issuer commits once per two units, and a slot is refilled when its pair has been consumed.
   static constexpr int kNumBars = 3 * kMaxStages + 4;
   static constexpr int kOffRs = kOffBars + kNumBars * 8;                      // float [64]  rsqrt factors
   static constexpr int kOffHs = kOffRs + kMaxBatch * 4;                       // float [2][64] scratch of the prologue
@@ -79,7 +83,9 @@ __host__ __device__ inline SmemPlan smem_plan(int Bpad) {
 }
 // control words: [0] abort  [1] tensor-memory base  [2] Tmax  [3] flag of the epilogue group  [4] flag of the stagers
 // [5] flag of the attention group  [7] / [8] number of selected experts as read by the stagers / the epilogue group
-constexpr int kCAbort = 0, kCTmem = 1, kCTmax = 2, kCFlagEpi = 3, kCFlagStg = 4, kCFlagAttn = 5, kCNeStg = 7, kCNeEpi = 8;
+// [10..13] router epilogue: experts listed by each of its four warps
+constexpr int kCAbort = 0, kCTmem = 1, kCTmax = 2, kCFlagEpi = 3, kCFlagStg = 4, kCFlagAttn = 5, kCNeStg = 7, kCNeEpi = 8,
+              kCRouterCnt = 10;   // [10..13] listed experts per epilogue warp
 
 struct TensorMaps {
   CUtensorMap qkv, o_proj, up, gate, down, lm_head;   // 3-D {k, row, layer}; box {64, 128 (up/gate: 64), 1}
@@ -150,7 +156,8 @@ __device__ __forceinline__ long long to_fixed(float v) { return __float2ll_rn(v 
 __device__ __forceinline__ void red_add_s64(long long* addr, long long v) {
   asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
 }
-// Reads an accumulator and leaves zero for its next user, in one operation at L2.
+// Reads an accumulator and leaves zero for its next user, in one operation at L2.  (Plain loads followed by stores of
+// zero were measured equal.)
 __device__ __forceinline__ long long exch_zero_s64(long long* addr) {
   long long old;
   asm volatile("atom.relaxed.gpu.global.exch.b64 %0, [%1], %2;" : "=l"(old) : "l"(addr), "l"(0ll) : "memory");
@@ -173,17 +180,18 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
   }
 }
 
-// Optional timeline (qmk_set_trace), eight 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
+// Optional timeline (qmk_set_trace), sixteen 64-bit slots per (CTA, phase), globaltimer ns: 0 the phase's dependency is
 // satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
 // the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
-// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival (7 in
-// the expert phases, which have no fill time: the issuer waiting for a free accumulator).
+// the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival 8 the issuer
+// waiting for a free accumulator, 9 issuing a unit's four MMAs, 10 the commits.  (More stamps inside the epilogue path were
+// measured to cost a fifth of the step at 64 rows with tracing off: the kernel sits at its register cap.)
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
-  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = globaltimer_ns();
+  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * kTraceSlots + slot] = globaltimer_ns();
 }
 
 __device__ __forceinline__ void trace_val(const BParams& p, int ph, int slot, unsigned long long v) {
-  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * 8 + slot] = v;
+  if (p.trace != nullptr) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * kTraceSlots + slot] = v;
 }
 
 // Byte offset of the 16-byte piece that holds (batch row b, column col) in an activation image: k-block col / 64, then
@@ -199,8 +207,8 @@ struct Ctx {
   uint32_t bars;     // shared address of the mbarriers
   int warp, lane;
   __device__ __forceinline__ uint32_t a_full(int s) const { return bars + s * 8; }
-  __device__ __forceinline__ uint32_t b_full(int s) const { return bars + (kMaxStages + s) * 8; }
-  __device__ __forceinline__ uint32_t empty(int s) const { return bars + (2 * kMaxStages + s) * 8; }
+  __device__ __forceinline__ uint32_t b_full(int s) const { return bars + s * 8; }   // (the same barrier)
+  __device__ __forceinline__ uint32_t empty(int s) const { return bars + (2 * kMaxStages + (s >> 1)) * 8; }
   __device__ __forceinline__ uint32_t acc_full(int b) const { return bars + (3 * kMaxStages + b) * 8; }
   __device__ __forceinline__ uint32_t acc_empty(int b) const { return bars + (3 * kMaxStages + 2 + b) * 8; }
   __device__ __forceinline__ bool aborted() const { return ctl[kCAbort] != 0u; }
@@ -335,7 +343,7 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
     unit_range(d.T * d.KB, phase_ctas(kind, d.T * d.KB, G), cta, lo, hi);
     int kb = d.KB > 0 ? lo % d.KB : 0;
     bool seg_start = true;
-    long long w_a = 0, w_b = 0, w_acc = 0;
+    long long w_a = 0, w_b = 0, w_acc = 0, w_mma = 0, w_commit = 0;
 #pragma unroll 1
     for (int u = lo; u < hi; ++u, ++n) {
       const unsigned buf = sg & 1u;
@@ -347,7 +355,6 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
       w_acc += t0 - ta;
       if (!mbar_wait(c, c.a_full(s), par, ph, 3)) return;
       const long long t1 = tr ? clock64() : 0;
-      if (!mbar_wait(c, c.b_full(s), par, ph, 4)) return;
       w_a += t1 - t0;
       const long long t2 = tr ? clock64() : 0;
       w_b += t2 - t1;
@@ -359,7 +366,8 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
       else mma_bf16_add(dcol, da, db, idesc);
 #pragma unroll
       for (int k = 1; k < kBlockK / 16; ++k) mma_bf16_add(dcol, da + 2u * k, db + 2u * k, idesc);
-      mma_commit(c.empty(s));
+      const long long t3 = tr ? clock64() : 0;
+      if (n & 1u) mma_commit(c.empty(s));   // frees this slot and the one before it
       seg_start = false;
       if (++kb == d.KB || u + 1 == hi) {
         mma_commit(c.acc_full(buf));
@@ -367,10 +375,13 @@ __device__ __forceinline__ void issuer(const Ctx& c, uint32_t tmem) {
         kb = kb == d.KB ? 0 : kb;
         seg_start = true;
       }
+      if (tr) { const long long t4 = clock64(); w_mma += t3 - t2; w_commit += t4 - t3; }
     }
     trace_val(p, ph, 3, (unsigned long long)w_a);
     trace_val(p, ph, 4, (unsigned long long)w_b);
-    if (is_expert_kind(kind)) trace_val(p, ph, 7, (unsigned long long)w_acc);   // (these phases have no stager fill time)
+    trace_val(p, ph, 8, (unsigned long long)w_acc);
+    trace_val(p, ph, 9, (unsigned long long)w_mma);
+    trace_val(p, ph, 10, (unsigned long long)w_commit);
   }
 }
 
@@ -613,14 +624,14 @@ __device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, in
 // into this rank's slot of every peer's exchange buffer, a flag with the tag of (launch, layer) follows after a
 // system-scope fence, then the flags of the other ranks are awaited in THIS rank's buffer (bounded) and the slots are added
 // in rank order -- the same order on every rank, so all ranks hold the same bits afterwards.  128 threads, e = tile row.
-static __device__ __noinline__ void ep_exchange(const Ctx& c, int ph, int t, int e) {
+static __device__ __noinline__ void ep_exchange(const Ctx& c, int ph, int t, int e, int which) {
   const BParams& p = *c.p;
   float* exch = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
-  const int W = p.ep_world, me = p.ep_rank, layer = phase_layer(p, ph);
+  const int W = p.x_world, me = p.x_rank, layer = phase_layer(p, ph);
   const int T = (p.H + kTileRows - 1) / kTileRows;
   // Exchanges are numbered over the launches (all ranks launch in lockstep); the number is the flag's tag and its low
   // bit picks one of two buffers, so a rank that runs one exchange ahead never overwrites a tile a peer still reads.
-  const unsigned seq = p.epoch * (unsigned)p.num_layers + (unsigned)layer;
+  const unsigned seq = (p.epoch * (unsigned)p.num_layers + (unsigned)layer) * (unsigned)p.x_per_layer + (unsigned)which;
   const unsigned tag = seq + 1u;
   const int par = (int)(seq & 1u);
   const size_t tile_f = (size_t)kTileRows * p.Bpad;
@@ -764,65 +775,118 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       // in ascending order and every (selected expert, row) gets its weight for the expert down-projection.
       const int E = p.E;
       // tpr consecutive lanes share a row: each takes the experts x = q, q + tpr, ...; maxima, sums and the k winners
-      // are combined with shuffles.  A winner is marked by negating its (positive) exponential in place.
-      const int tpr = p.Bpad <= 16 ? 8 : (p.Bpad <= 32 ? 4 : 2);
-      const int b = e / tpr, q = e % tpr;
+      // are combined with shuffles.  A winner is marked by negating its (positive) exponential in place.  Every pass
+      // reads its values eight at a time before it uses them: one shared-memory latency per eight, not per value.
+      const int lg = p.Bpad <= 16 ? 3 : (p.Bpad <= 32 ? 2 : 1), tpr = 1 << lg;
+      const int b = e >> lg, q = e & (tpr - 1);
       const bool rowok = b < p.Bpad;
       const int bb = rowok ? b : 0;
       const bool act = b < B && act_s[bb] != 0;
+      const int stride = p.exch_stride;
+      float* col = exch + bb;
       float mx = -INFINITY;
-      for (int x = q; x < E; x += tpr) mx = fmaxf(mx, exch[x * p.exch_stride + bb]);
+      for (int x0 = q; x0 < E; x0 += 8 * tpr) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { const int x = x0 + u * tpr; v[u] = x < E ? col[x * stride] : -INFINITY; }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mx = fmaxf(mx, v[u]);
+      }
       for (int o = 1; o < tpr; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
       float sum = 0.f;
-      for (int x = q; x < E; x += tpr) {
-        const float pe = __expf(exch[x * p.exch_stride + bb] - mx);
-        if (rowok) exch[x * p.exch_stride + bb] = pe;
-        sum += pe;
+      for (int x0 = q; x0 < E; x0 += 8 * tpr) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { const int x = x0 + u * tpr; v[u] = x < E ? __expf(col[x * stride] - mx) : 0.f; }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int x = x0 + u * tpr;
+          if (rowok && x < E) col[x * stride] = v[u];
+          sum += v[u];
+        }
       }
       for (int o = 1; o < tpr; o <<= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
       const float inv = 1.0f / sum;
       for (int j = 0; j < p.topk; ++j) {
         float best = -1.f;
         int bi = E;
-        for (int x = q; x < E; x += tpr) {
-          const float v = rowok ? exch[x * p.exch_stride + bb] : 0.f;
-          if (v > best) { best = v; bi = x; }
+        for (int x0 = q; x0 < E; x0 += 8 * tpr) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { const int x = x0 + u * tpr; v[u] = x < E ? (rowok ? col[x * stride] : 0.f) : -2.f; }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (v[u] > best) { best = v[u]; bi = x0 + u * tpr; }
         }
         for (int o = 1; o < tpr; o <<= 1) {
           const float ob = __shfl_xor_sync(kFullMask, best, o);
           const int oi = __shfl_xor_sync(kFullMask, bi, o);
           if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
-        if (rowok && bi < E && bi % tpr == q) exch[bi * p.exch_stride + bb] = -best;
+        if (rowok && bi < E && (bi & (tpr - 1)) == q) col[bi * stride] = -best;
       }
       if (rowok)
-        for (int x = q; x < E; x += tpr) {
-          const float v = exch[x * p.exch_stride + bb];
-          exch[x * p.exch_stride + bb] = (act && v < 0.f) ? -v * inv : 0.f;
+        for (int x0 = q; x0 < E; x0 += 8 * tpr) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { const int x = x0 + u * tpr; v[u] = x < E ? col[x * stride] : 0.f; }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int x = x0 + u * tpr;
+            if (x < E) col[x * stride] = (act && v[u] < 0.f) ? -v[u] * inv : 0.f;
+          }
         }
       named_bar(kBarEpi, 128);
+      // The distinct experts of the step in ascending order: thread x looks at expert x, slots come from a ballot per warp
+      // and the warps' counts.  (Expert parallelism: only the experts this rank holds are listed, under their local index;
+      // every rank runs the same router on the same rows, so the ranks' lists together are the step's selection.)
       int* slot_of = reinterpret_cast<int*>(c.smem + Smem::kOffHs);   // [128] (the prologue's scratch, free now)
-      if (e < E) {
-        bool any = false;
-        for (int b = 0; b < B; ++b) any |= exch[e * p.exch_stride + b] > 0.f;
-        slot_of[e] = any ? 1 : 0;
-      }
-      named_bar(kBarEpi, 128);
-      if (e == 0) {
-        // (expert parallelism: only the experts this rank holds are listed, under their local index; every rank runs the
-        // same router on the same rows, so the ranks' lists together are the step's selection)
-        const int per_rank = p.ep_world > 1 ? E / p.ep_world : E;
-        const int e_lo = p.ep_world > 1 ? p.ep_rank * per_rank : 0;
-        int n = 0;
-        for (int x = 0; x < E; ++x) {
-          if (slot_of[x] && x >= e_lo && x < e_lo + per_rank) { p.moe_elist[n] = x - e_lo; slot_of[x] = n++; } else slot_of[x] = -1;
+      const int per_rank = p.ep_world > 1 ? E / p.ep_world : E;
+      const int e_lo = p.ep_world > 1 ? p.ep_rank * per_rank : 0;
+      bool any = false;
+      if (e < E && e >= e_lo && e < e_lo + per_rank) {
+        const float* row = exch + e * stride;
+        for (int b0 = 0; b0 < B; b0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = b0 + u < B ? row[b0 + u] : 0.f;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) any |= v[u] > 0.f;
         }
-        *p.moe_ne = n;
-        atomicAdd(p.moe_ne_sum, (unsigned long long)n);
+      }
+      const unsigned ballot = __ballot_sync(kFullMask, any);
+      if (c.lane == 0) c.ctl[kCRouterCnt + (e >> 5)] = (unsigned)__popc(ballot);
+      named_bar(kBarEpi, 128);
+      int before = 0, total = 0;
+      for (int w = 0; w < 4; ++w) {
+        const int cw = (int)c.ctl[kCRouterCnt + w];
+        before += w < (e >> 5) ? cw : 0;
+        total += cw;
+      }
+      const int slot = any ? before + __popc(ballot & ((1u << c.lane) - 1u)) : -1;
+      slot_of[e] = slot;
+      if (any) p.moe_elist[slot] = e - e_lo;
+      if (e == 0) {
+        *p.moe_ne = total;
+        atomicAdd(p.moe_ne_sum, (unsigned long long)total);
       }
       named_bar(kBarEpi, 128);
-      if (e < E && slot_of[e] >= 0)
-        for (int b = 0; b < kMaxBatch; ++b) p.moe_w[slot_of[e] * kMaxBatch + b] = b < B ? exch[e * p.exch_stride + b] : 0.f;
+      // router weight of every (listed expert, row), zero for rows that did not select it: all threads, row-contiguous stores
+      for (int i0 = e; i0 < E * kMaxBatch; i0 += 128 * 4) {
+        float v[4];
+        int sl[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 128, x = i >> 6, bc = i & (kMaxBatch - 1);
+          sl[u] = i < E * kMaxBatch ? slot_of[x] : -1;
+          v[u] = (sl[u] >= 0 && bc < B) ? exch[x * stride + bc] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 128;
+          if (sl[u] >= 0) p.moe_w[sl[u] * kMaxBatch + (i & (kMaxBatch - 1))] = v[u];
+        }
+      }
       break;
     }
     case kEUpGate: {
@@ -856,7 +920,9 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       // (fused_oproj_gemv_residual / fused_mlp_down_residual, operations.py:251-262, 285-295).
       // Same (sequence, eight rows) ownership: one 16-byte load and store of the residual stream per item, all loads
       // issued first; the sums of squares for the next RMSNorm are reduced over the sixteen row groups by shuffles.
-      if (kind == kEDown && p.ep_world > 1) ep_exchange(c, ph, t, e);   // exch := sum over the ranks' partial tiles
+      // model parallelism: the tile holds this rank's partial sums (its experts, or its slice of the K dimension);
+      // exch := sum over the ranks' tiles, in rank order on every rank
+      if (p.x_world > 1 && (kind == kEDown || p.x_per_layer == 2)) ep_exchange(c, ph, t, e, kind == kDown ? 1 : 0);
       const int rg = e & 15;
       const int row = t * kTileRows + rg * 8;
       const bool in_range = row < p.H;
@@ -924,7 +990,7 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         const int nrow = min(kTileRows, p.vocab - t * kTileRows);
         for (int r = 0; r < nrow; ++r) {
           const float v = act_s[e] ? exch[r * p.exch_stride + e] : -1e9f;
-          const unsigned long long key = argmax_key(f32_to_bf16_bits(v), t * kTileRows + r);
+          const unsigned long long key = argmax_key(f32_to_bf16_bits(v), p.vocab_offset + t * kTileRows + r);
           best = key > best ? key : best;
         }
         atomicMax(p.argmax_key + e, best);
@@ -949,7 +1015,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
   if (U == 0) {
     // Expert parallelism, no selected expert on this rank: the other ranks still wait for this rank's partial tiles, and
     // the residual stream still has to be updated from theirs: zero tiles, dealt to the CTAs, take the usual way out.
-    if (kind == kEDown && p.ep_world > 1) {
+    if (kind == kEDown && p.x_world > 1) {
       float* ex = reinterpret_cast<float*>(c.smem + Smem::kOffExch);
       for (int t = cta; t < d.T; t += (int)gridDim.x) {
         for (int j = 0; j < p.Bpad; ++j) ex[e * p.exch_stride + j] = 0.f;
@@ -1002,7 +1068,8 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     // One thread decides for the group whether this CTA finishes the tile: a full segment always does; a partial one
     // has added its tile to the tile's accumulator at L2, takes a ticket, and the last of the tile's segments to
     // arrive reads the sum (and leaves the accumulator zeroed for its next user, a phase later).
-    if (!full) __threadfence();
+    // (no fence per thread: the barrier orders the group's additions before thread 0's acquire-release ticket, whose
+    // release is cumulative over what the barrier made visible to it)
     named_bar(kBarEpi, 128);
     if (e == 0) {
       unsigned fin = 0u;
@@ -1032,7 +1099,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
-    if (run) epilogue_tile(c, ph, kind, t, e);   // (contains no barrier)
+    if (run) epilogue_tile(c, ph, kind, t, e);
     named_bar(kBarEpi, 128);           // the exchange tile is free again
     u = u_end;
   }
@@ -1284,7 +1351,7 @@ __device__ __forceinline__ void prologue(const Ctx& c, int e) {
     const uint16_t* src = h;
     if (p.prologue == 2) {   // (a token id outside the vocabulary is clamped, as the batch-1 kernel does)
       long long tok = p.token_in[b];
-      tok = tok < 0 ? 0 : (tok >= p.vocab ? (long long)p.vocab - 1 : tok);
+      tok = tok < 0 ? 0 : (tok >= p.embed_rows ? (long long)p.embed_rows - 1 : tok);
       src = p.embed + (size_t)tok * p.H;
     }
     float s = 0.f;
@@ -1312,6 +1379,51 @@ __device__ __forceinline__ void finalize(const Ctx& c, int e) {
   const int lm = p.ppl * p.num_layers;
   if (e == 0) c.ctl[kCFlagEpi] = counter_wait(c, p.phase_done + 1 + lm, gridDim.x, lm) ? 1u : 0u;
   named_bar(kBarEpi, 128);
+  if (p.x_world > 1 && p.x_per_layer == 2) {
+    // Tensor parallelism: every rank holds a slice of the vocabulary and the arg-max key of its slice (the key carries the
+    // global row).  Keys go to the peers' buffers like the partial tiles do: store, flag, bounded wait on the local flags.
+    const int W = p.x_world, me = p.x_rank;
+    const unsigned tag = p.epoch;
+    if (c.ctl[kCFlagEpi] != 0u) {
+      if (e < p.B) {
+        const unsigned long long mine = __ldcg(p.argmax_key + e);
+        for (int d = 0; d < W; ++d)
+          if (d != me) p.ep_key[d][me * kMaxBatch + e] = mine;
+      }
+      __threadfence_system();
+      named_bar(kBarEpi, 128);
+      if (e < W && e != me) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ep_kflag[e] + me), "r"(tag) : "memory");
+        const unsigned* flag = p.ep_kflag[me] + e;
+        const long long t0 = clock64();
+        for (unsigned it = 1;; ++it) {
+          unsigned v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (v == tag) break;
+          if ((it & 15u) == 0u) {
+            if (c.ctl[kCAbort] != 0u) break;
+            if (clock64() - t0 > c.p->timeout_cycles) {
+              report(p, kErrCounterWait, c.warp, lm, v, tag, 48 + e);
+              c.ctl[kCAbort] = 1u;
+              break;
+            }
+          }
+        }
+      }
+      named_bar(kBarEpi, 128);
+      if (c.ctl[kCAbort] == 0u && e < p.B) {
+        unsigned long long best = __ldcg(p.argmax_key + e);
+        for (int s = 0; s < W; ++s) {
+          if (s == me) continue;
+          const unsigned long long k = __ldcg(p.ep_key[me] + s * kMaxBatch + e);
+          best = k > best ? k : best;
+        }
+        p.argmax_key[e] = best;
+      }
+      named_bar(kBarEpi, 128);
+      if (c.ctl[kCAbort] != 0u) return;
+    }
+  }
   if (c.ctl[kCFlagEpi] != 0u && e < p.B) {
     const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
     const unsigned long long win = __ldcg(p.argmax_key + e);
@@ -1341,9 +1453,8 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
   c.lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(c.a_full(s), 1);
-      mbar_init(c.b_full(s), 32);
-      mbar_init(c.empty(s), 1);
+      mbar_init(c.a_full(s), 33);
+      if ((s & 1) == 0) mbar_init(c.empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(c.acc_full(b), 1);
@@ -1410,8 +1521,7 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
       } else if (epi) {
         if (gi == 0) trace_put(p, ph, 2);
         epilogue_phase(c, ph, kind, tmem, gi, sg);
-        __threadfence();
-        named_bar(kBarEpi, 128);
+        named_bar(kBarEpi, 128);           // the group's stores, then thread 0's release on the phase counter
         if (gi == 0 && !c.aborted()) {
           red_release_gpu_add(p.phase_done + 1 + ph, 1u);
           trace_put(p, ph, 5);
@@ -1430,8 +1540,10 @@ qmk_batch_kernel(const __grid_constant__ BParams p, const __grid_constant__ Tens
     const unsigned first = n_issued > (unsigned)kStages ? n_issued - (unsigned)kStages : 0u;
     for (unsigned m = first; m < n_issued; ++m) {
       const long long t0 = clock64();
+      // (a slot's barrier also counts the stagers' arrivals, which an aborting CTA may never make: a short bound, a bulk
+      // copy lands within microseconds)
       while (!mbar_try_wait(c.a_full((int)(m & (unsigned)(kStages - 1))), (m / (unsigned)kStages) & 1u)) {
-        if (clock64() - t0 > p.timeout_cycles) break;
+        if (clock64() - t0 > 400000) break;
       }
     }
   }

@@ -69,7 +69,7 @@ struct BParams {
   int pre_lm_units;              // the LM head uses it when a CTA has at least this many units
   int dense_img;                 // O-proj / down-proj read aimg / simg (when their producer ran in the launch)
   unsigned char* eimg;           // selected-expert slot * (Ie / 64) + k-block: SiLU(gate) * up * router weight
-  unsigned long long* trace;     // optional [CTAs, phases, 8] globaltimer stamps (ns); null = off
+  unsigned long long* trace;     // optional [CTAs, phases, 16] timeline words; null = off
   // ---- expert parallelism (ep_world > 1): every rank holds E / ep_world experts, attention and router are replicated;
   // after its local expert down-projection a rank stores each finished [128 rows, Bpad] fp32 partial tile into its slot
   // of every peer's exchange buffer (plain peer stores over NVLink), publishes a flag, waits (bounded) on its OWN
@@ -77,7 +77,13 @@ struct BParams {
   // 128, Bpad] floats, flags [2, ep_world, tiles] words holding the tag of (launch, layer).
   float* ep_buf[8];              // exchange buffer of every rank as mapped into this process (own included)
   unsigned* ep_flag[8];
-  int ep_rank, ep_world;
+  int ep_rank, ep_world;         // expert parallelism: which experts the router lists (1 / 0 when off)
+  int x_world, x_rank;           // ranks that exchange partial tiles (expert or tensor parallelism; 1 / 0 when off)
+  int x_per_layer;               // exchanges per layer: 1 (expert down-projection) or 2 (O-proj and down-proj: tensor parallelism)
+  unsigned long long* ep_key[8]; // tensor parallelism: [source rank, 64] arg-max keys of the ranks' vocabulary slices
+  unsigned* ep_kflag[8];         // [source rank] tag (launch) of the keys
+  int vocab_offset;              // global row of this rank's first LM-head row (tensor parallelism; else 0)
+  int embed_rows;                // rows of the embedding table (the whole vocabulary also when the LM head is a slice)
   // ---- shape ----
   int H, I, NH, NKV, HD, QKV_ROWS, QDIM, num_layers, vocab;
   int E, topk, Ie;               // MoE: experts, experts per token, expert intermediate size (E = 0: dense model)

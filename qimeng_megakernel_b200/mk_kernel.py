@@ -94,7 +94,7 @@ class MegaKernel:
         _check_tensor("lm_head_norm_weights", g.lm_head_norm_weights, bf, (H,))
         _check_tensor("lm_head_weights", g.lm_head_weights, bf, (V, H))
         if g.embed_tokens is not None:
-            _check_tensor("embed_tokens", g.embed_tokens, bf, (V, H))
+            _check_tensor("embed_tokens", g.embed_tokens, bf, (cfg.embed_rows or V, H))
         rows = int(g.rope_cos.shape[0])
         _check_tensor("rope_cos", g.rope_cos, torch.float32, (rows, HD))
         _check_tensor("rope_sin", g.rope_sin, torch.float32, (rows, HD))
@@ -158,7 +158,8 @@ class MegaKernel:
                                   cfg.head_dim, cfg.vocab_size, rows, float(cfg.rms_norm_eps),
                                   1.0 / math.sqrt(cfg.head_dim), float(cfg.rms_norm_eps), int(cfg.num_experts),
                                   int(cfg.num_experts_per_tok), int(cfg.moe_intermediate_size),
-                                  int(cfg.ep_world), int(cfg.ep_rank))
+                                  int(cfg.ep_world), int(cfg.ep_rank), int(cfg.tp_world), int(cfg.tp_rank),
+                                  int(cfg.embed_rows))
             w = _lib.WeightPtrs(**{c: _ptr(getattr(g, f, None)) for c, f in _WEIGHT_FIELDS})
             h = C.c_void_p()
             _lib.check(self._lib.qmk_create(C.byref(desc), C.byref(w), dev.index or 0, C.byref(h)))

@@ -33,11 +33,14 @@ class LlamaConfig:
     # expert parallelism (B200 addition): ranks that share the experts, and this process's rank; 0 / 1 = off
     ep_world = 0
     ep_rank = 0
+    tp_world = 0         # tensor parallelism: the other fields then describe this rank's slice (tensor_parallel.shard_config)
+    tp_rank = 0
+    embed_rows = 0       # rows of embed_tokens when they differ from vocab_size (tensor parallelism)
 
     _KEYS = ("num_hidden_layers", "hidden_size", "intermediate_size", "head_dim", "num_attention_heads",
              "num_key_value_heads", "vocab_size", "rms_norm_eps", "rope_theta", "rope_scaling",
              "max_position_embeddings", "qk_norm", "num_experts", "num_experts_per_tok", "moe_intermediate_size",
-             "ep_world", "ep_rank")
+             "ep_world", "ep_rank", "tp_world", "tp_rank", "embed_rows")
 
     @classmethod
     def update_from_dict(cls, config: dict) -> None:
@@ -64,6 +67,9 @@ class LlamaConfig:
         cls.moe_intermediate_size = int(config.get("moe_intermediate_size", 0) or 0)
         cls.ep_world = int(config.get("ep_world", 0) or 0)
         cls.ep_rank = int(config.get("ep_rank", 0) or 0)
+        cls.tp_world = int(config.get("tp_world", 0) or 0)
+        cls.tp_rank = int(config.get("tp_rank", 0) or 0)
+        cls.embed_rows = int(config.get("embed_rows", 0) or 0)
 
     @classmethod
     def update_from_hf(cls, config) -> None:

@@ -123,7 +123,7 @@ def make_globals(config: dict, weights: dict, kv_seq_len: int, device: str | tor
     names = WEIGHT_NAMES + tuple(n for n in QK_NORM_NAMES + MOE_NAMES if n in weights)
     for name in names:
         t = weights[name]
-        key = t.data_ptr()
+        key = (t.data_ptr(), tuple(t.shape))     # (a slice that starts a tensor shares its address)
         if key not in moved:
             moved[key] = t.to(dev).contiguous()
         weights_dev = moved[key]

@@ -1,7 +1,8 @@
 """Worker of tests/test_gpu_expert_parallel.py: one process per GPU (torchrun, gloo for the control plane).
 
-Every rank builds the same seeded mixture-of-experts model, keeps its block of experts, connects the exchange buffers and
-decodes the same teacher-forced steps; rank 0 also runs the whole model on its own GPU.  Checks: every rank ends a step
+`ep` (default): every rank builds the same seeded mixture-of-experts model and keeps its block of experts.  `tp`: the same
+seeded dense model, every rank keeps its slice of every projection (tensor parallelism).  Either way the ranks connect the
+exchange buffers and decode the same teacher-forced steps; rank 0 also runs the whole model on its own GPU.  Checks: every rank ends a step
 with bit-identical logits (the partial tiles are added in rank order on every rank); the expert-parallel result matches the
 one-GPU result (hidden state within 1e-2 relative L2, arg-max equal wherever the one-GPU top two are not tied); and, in
 the second part, a rank that does not launch makes the others' bounded wait run out into QMK_ERR_DEVICE_TIMEOUT, after
@@ -16,12 +17,16 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from qimeng_megakernel_b200 import _lib, expert_parallel as ep, mk_kernel, synthetic  # noqa: E402
+from qimeng_megakernel_b200 import _lib, expert_parallel as ep, mk_kernel, synthetic, tensor_parallel as tp  # noqa: E402
 from qimeng_megakernel_b200.model_config import LlamaConfig  # noqa: E402
 
-CFG = dict(num_hidden_layers=2, hidden_size=256, intermediate_size=64, head_dim=128, num_attention_heads=2,
+MOE = dict(num_hidden_layers=2, hidden_size=256, intermediate_size=64, head_dim=128, num_attention_heads=2,
            num_key_value_heads=2, vocab_size=777, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
            max_position_embeddings=256, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128)
+# dense: 4 query / 2 KV heads of 64, intermediate 512, a vocabulary whose slices are not multiples of the tile height
+DENSE = dict(num_hidden_layers=2, hidden_size=256, intermediate_size=512, head_dim=64, num_attention_heads=4,
+             num_key_value_heads=2, vocab_size=1500, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+             max_position_embeddings=256)
 
 
 def main() -> None:
@@ -30,11 +35,18 @@ def main() -> None:
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dev = torch.device("cuda", torch.cuda.current_device())
     B, steps = 5, 6
+    mode = sys.argv[1] if len(sys.argv) > 1 else "ep"
+    CFG = DENSE if mode == "tp" else MOE
     full = synthetic.make_weights(CFG, seed=77, device="cpu", gain_jitter=0.1, max_positions=64)
     prompts = synthetic.make_prompts(CFG["vocab_size"], B, steps, seed=3)
     # ---- this rank's shard
-    cfg_r = ep.shard_config(CFG, rank, world)
-    g = synthetic.make_globals(cfg_r, ep.shard_moe_weights(full, rank, world), kv_seq_len=32, device=dev, batch=B)
+    if mode == "tp":
+        cfg_r = tp.shard_config(CFG, rank, world)
+        shard = tp.shard_weights(CFG, full, rank, world)
+    else:
+        cfg_r = ep.shard_config(CFG, rank, world)
+        shard = ep.shard_moe_weights(full, rank, world)
+    g = synthetic.make_globals(cfg_r, shard, kv_seq_len=32, device=dev, batch=B)
     g.token_in = torch.zeros(B, dtype=torch.int64, device=dev)
     mk = mk_kernel.get_mk()
     LlamaConfig.update_from_dict(cfg_r)
@@ -52,11 +64,16 @@ def main() -> None:
         mk(g)
         torch.cuda.synchronize()
         mk.check_status()
-        mine = g.logits.contiguous().view(torch.uint8).cpu()      # bytes: gloo gathers no 16-bit types
+        # what every rank must agree on, bit for bit: the residual stream and the chosen tokens (and, when every rank
+        # holds the whole LM head, the logits); as bytes: gloo gathers no 16-bit types
+        parts = [g.hidden_states.contiguous().view(torch.uint8).flatten(), g.next_token.view(torch.uint8).flatten()]
+        if mode != "tp":
+            parts.append(g.logits.contiguous().view(torch.uint8).flatten())
+        mine = torch.cat(parts).cpu()
         gathered = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
         if not all(torch.equal(gathered[0], t) for t in gathered):
-            print(f"rank {rank} step {step}: ranks disagree on the logits", flush=True); ok = False
+            print(f"rank {rank} step {step}: ranks disagree on the state after the step", flush=True); ok = False
         if rank == 0:
             LlamaConfig.update_from_dict(CFG)
             g1.token_in.copy_(prompts[:, step]); g1.position_id = step
@@ -68,6 +85,11 @@ def main() -> None:
             if rel > 1e-2:
                 print(f"step {step}: hidden state differs from the one-GPU run, relative L2 {rel:.4g}", flush=True); ok = False
             ref = g1.logits.float()
+            if mode == "tp":     # this rank's slice of the logits against the same rows of the one-GPU logits
+                vl = g.logits.shape[-1]
+                gap = float((g.logits.float() - ref[:, :vl]).abs().max())
+                if gap > 2e-2 * float(ref.abs().max()):
+                    print(f"step {step}: logits slice differs from the one-GPU run by {gap:.4g}", flush=True); ok = False
             top2 = ref.topk(2, dim=-1).values
             for b in range(B):
                 if float(top2[b, 0] - top2[b, 1]) > 4 * 2.0 ** -8 * abs(float(top2[b, 0])) and int(g.next_token[b]) != int(g1.next_token[b]):

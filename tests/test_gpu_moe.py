@@ -155,6 +155,8 @@ def test_moe_block_and_steps(shape, batch):
         g.k_cache.zero_(); g.v_cache.zero_()
         g.token_in = torch.zeros(nb, dtype=torch.int64, device="cuda")
         prompts = synthetic.make_prompts(cfg["vocab_size"], nb, 6, seed=3)
+        worst = worst_tie = 0.0
+        checked = ties = 0
         for step in range(6):
             positions = [step] * nb
             for s in (st, st32):
@@ -179,6 +181,10 @@ def test_moe_block_and_steps(shape, batch):
                 # a row that routes on a near tie may legitimately pick the other expert: one expert term of the
                 # weighted sum then differs, a few per cent of the hidden state
                 bound = 6e-2 if b in near_tie else max(2e-2, 1.5 * gap)
+                if b in near_tie:
+                    worst_tie, ties = max(worst_tie, U.rel_l2(got[b], h32)), ties + 1
+                else:
+                    worst, checked = max(worst, U.rel_l2(got[b], h32)), checked + 1
                 assert U.rel_l2(got[b], h32) <= bound, f"step {step} row {b}: hidden vs fp32 oracle"
             ref_logits = fo._bh(st.logits).float()
             own = fo._bh(g.logits).float().argmax(dim=-1)
@@ -188,6 +194,8 @@ def test_moe_block_and_steps(shape, batch):
                 if active[b] and b not in near_tie and float(top2[0] - top2[1]) > 4 * 2.0 ** -8 * abs(float(top2[0])):
                     assert int(g.next_token[b]) == int(ref_logits[b].argmax()), f"step {step} row {b} arg-max"
         mk.check_status()
+        print(f"measured: MoE whole steps, {nb} rows: hidden state vs fp32 relative L2 max {worst:.4g} over {checked} rows "
+              f"(rows that route on a near tie: {worst_tie:.4g} over {ties})")
     finally:
         mk.close()
 

@@ -274,3 +274,40 @@ def test_expert_partition_and_rank_order_sum_two_gloo_ranks(tmp_path):
     assert ep.expert_range(3, 8, 64) == (24, 32)
     with pytest.raises(ValueError):
         ep.expert_range(0, 3, 64)
+
+
+def test_tensor_parallel_slices_add_up():
+    """tensor_parallel.shard_weights on the CPU: the ranks' partial O-proj and down-proj products add up to the whole
+    product, Q/K/V slices are the heads of the rank, LM-head slices tile the vocabulary; bad splits are refused."""
+    from qimeng_megakernel_b200 import tensor_parallel as tp
+    cfg = dict(num_hidden_layers=1, hidden_size=64, intermediate_size=256, head_dim=16, num_attention_heads=8,
+               num_key_value_heads=4, vocab_size=100)
+    gen = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float64)
+    qd, kd = 8 * 16, 4 * 16
+    w = {"qkv_weights": r(1, qd + 2 * kd, 64), "o_proj_weights": r(1, 64, qd), "up_proj_weights": r(1, 256, 64),
+         "gate_proj_weights": r(1, 256, 64), "down_proj_weights": r(1, 64, 256), "lm_head_weights": r(100, 64),
+         "embed_tokens": r(100, 64)}
+    x, attn, act = r(64), r(qd), r(256)
+    for world in (2, 4):
+        shards = [tp.shard_weights(cfg, w, k, world) for k in range(world)]
+        cfgs = [tp.shard_config(cfg, k, world) for k in range(world)]
+        assert all(c["embed_rows"] == 100 and c["vocab_size"] == 100 // world and c["tp_rank"] == k for k, c in enumerate(cfgs))
+        ql, kl, il = qd // world, kd // world, 256 // world
+        o = sum(s["o_proj_weights"][0] @ attn[k * ql:(k + 1) * ql] for k, s in enumerate(shards))
+        assert torch.allclose(o, w["o_proj_weights"][0] @ attn)
+        dn = sum(s["down_proj_weights"][0] @ act[k * il:(k + 1) * il] for k, s in enumerate(shards))
+        assert torch.allclose(dn, w["down_proj_weights"][0] @ act)
+        full_qkv = w["qkv_weights"][0] @ x
+        for k, s in enumerate(shards):
+            y = s["qkv_weights"][0] @ x
+            assert torch.equal(y[:ql], full_qkv[k * ql:(k + 1) * ql])
+            assert torch.equal(y[ql:ql + kl], full_qkv[qd + k * kl:qd + (k + 1) * kl])
+            assert torch.equal(y[ql + kl:], full_qkv[qd + kd + k * kl:qd + kd + (k + 1) * kl])
+            assert torch.equal(s["up_proj_weights"][0], w["up_proj_weights"][0, k * il:(k + 1) * il])
+            assert s["embed_tokens"] is w["embed_tokens"]
+        assert torch.equal(torch.cat([s["lm_head_weights"] for s in shards]), w["lm_head_weights"])
+    with pytest.raises(ValueError):
+        tp.shard_config(cfg, 0, 8)          # 4 KV heads over 8 ranks
+    with pytest.raises(ValueError):
+        tp.shard_config(dict(cfg, num_experts=8), 0, 2)
