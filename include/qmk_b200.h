@@ -229,6 +229,16 @@ int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin, int32_t p
 int qmk_generate_host(qmk_handle* h, int64_t* host_tokens, int64_t host_tokens_len, int32_t first_pos,
                       int32_t n_steps, int32_t teacher_forced, int64_t* host_argmax, void* cuda_stream);
 
+/* Device-resident run of n_steps greedy steps from position first_pos (the second half of generate_greedy_fast,
+ * decode.py:1340-1435, with the token loop on the device): step 0 reads state.token_in, every later step the arg-max of
+ * the step before; each step writes next_token and, when bound, out_tokens[pos + 1].  Needs token_in and embed_tokens.
+ * Batch-1 kernel: ONE persistent launch runs all n_steps -- the token crosses from the last phase of a step to the first
+ * phase of the next as a tagged word, and every warp's weight stream runs on across the step boundary.  Batched kernel:
+ * the same run as n_steps launches (token_in must alias next_token; per-row position_ids are not advanced, so they must
+ * be null).  1 <= n_steps <= 4096; positions first_pos .. first_pos + n_steps - 1 must lie inside the KV cache and the
+ * RoPE tables.  Asynchronous on `cuda_stream`. */
+int qmk_generate_device(qmk_handle* h, int32_t first_pos, int32_t n_steps, void* cuda_stream);
+
 /* Reads the device status record (synchronises the stream it was last launched on). */
 int qmk_poll_status(qmk_handle* h, qmk_status* out);
 

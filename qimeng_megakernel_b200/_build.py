@@ -15,7 +15,7 @@ CSRC = Path(__file__).resolve().parent / "csrc"
 LIB_PATH = CSRC / "libqmk_b200.so"
 SOURCES = ["qmk_api.cu", "qmk_static.cu", "qmk_batch.cu"]
 HEADERS = ["qmk_megakernel.cuh", "qmk_kernel.cuh", "qmk_phases.cuh", "qmk_attention.cuh", "qmk_staging.cuh", "qmk_device.cuh",
-           "qmk_params.h", "qmk_schedule.h", "qmk_batch_kernel.cuh", "qmk_batch_params.h", "qmk_batch_schedule.h", "qmk_batch_host.h", "../../include/qmk_b200.h"]
+           "qmk_params.h", "qmk_schedule.h", "qmk_batch_kernel.cuh", "qmk_batch_device.cuh", "qmk_batch_params.h", "qmk_batch_schedule.h", "qmk_batch_host.h", "../../include/qmk_b200.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 

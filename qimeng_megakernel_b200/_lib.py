@@ -82,6 +82,7 @@ SYMBOLS = [
     ("qmk_static_poll_status", C.c_int, [C.c_int, C.POINTER(Status)]),
     ("qmk_static_set_timeout_cycles", C.c_int, [C.c_int, C.c_int64]),
     ("qmk_static_set_wait_first_dependency", C.c_int, [C.c_int, C.c_int32]),
+    ("qmk_generate_device", C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     ("qmk_static_last_cuda_error", C.c_char_p, []),
     ("qmk_destroy", None, [C.c_void_p]),
     ("qmk_strerror", C.c_char_p, [C.c_int]),

@@ -282,6 +282,8 @@ static void fill_params(const qmk_handle* h, Params& p, int pos) {
   p.scale_log2e = h->desc.attn_scale * 1.4426950408889634f;
   p.timeout_cycles = h->timeout_cycles;
   p.wait_first = 0;
+  p.n_steps = 1;
+  p.tok_word = (unsigned long long*)(h->d_tok + 8);   // (d_tok[0..1] are qmk_generate_host's token buffers)
 }
 
 static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
@@ -294,7 +296,8 @@ static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another
   attr[0].val.cooperative = h->cooperative;
-  p.launch_seq = ++h->launch_seq;
+  p.launch_seq = h->launch_seq + 1;   // number of the launch's first step; every step takes one
+  h->launch_seq += (unsigned)(p.n_steps > 0 ? p.n_steps : 1);
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p));
@@ -331,6 +334,31 @@ extern "C" int qmk_decode_step(qmk_handle* h, int32_t pos_id, void* cuda_stream)
   Params p;
   fill_params(h, p, pos_id);
   return step_with(h, p, (cudaStream_t)cuda_stream);
+}
+
+extern "C" int qmk_generate_device(qmk_handle* h, int32_t first_pos, int32_t n_steps, void* cuda_stream) {
+  if (!h || n_steps < 1 || n_steps > 4096 || first_pos < 0) return QMK_ERR_INVALID_ARG;
+  int rc = check_step_args(h, first_pos + n_steps - 1);
+  if (rc) return rc;
+  // the steps feed themselves: the first one reads token_in, the others the arg-max of the step before
+  if (!h->st.token_in || !h->w.embed_tokens) return QMK_ERR_INVALID_ARG;
+  QMK_CUDA(h, cudaSetDevice(h->device));
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  if (use_batched(h)) {
+    // the batched kernel runs one step per launch: the same run as n launches (token_in must alias next_token, as in
+    // the device-resident loop of the host mirror)
+    if (n_steps > 1 && ((const void*)h->st.token_in != (const void*)h->st.next_token || h->st.position_ids != nullptr))
+      return QMK_ERR_INVALID_ARG;   // (per-row positions are advanced by the caller between steps)
+    for (int i = 0; i < n_steps; ++i) {
+      rc = batched_launch(h, first_pos + i, 0, qmkb_num_phases(&h->desc), 0, stream);
+      if (rc) return rc;
+    }
+    return QMK_OK;
+  }
+  Params p;
+  fill_params(h, p, first_pos);
+  p.n_steps = n_steps;
+  return step_with(h, p, stream);
 }
 
 extern "C" int qmk_run_phases(qmk_handle* h, int32_t pos_id, int32_t phase_begin, int32_t phase_end, int32_t mode,

@@ -172,7 +172,7 @@ struct AttnPartial {
 template <class S>
 __device__ __forceinline__ void attn_blocks(const Params& p, unsigned char* smem, int layer, int kvh, int k0, int k1,
                                             bool staged_kv, bool first_in_smem, KvBlock<S>& blk, int w, int lane,
-                                            AttnPartial& out) {
+                                            AttnPartial& out, int pos) {
   using L = SmemLayout<S>;
   constexpr int HD = S::HD, GQA = S::GQA;
   static_assert(GQA <= 8, "one mma row per query head of the group");
@@ -192,7 +192,7 @@ __device__ __forceinline__ void attn_blocks(const Params& p, unsigned char* smem
   for (int kb = k0; kb < k1; kb += kAttnBlockKeys) {
     if (kb == k0 && first_in_smem) take_staged_kv_block(blk, smem, w, lane);
     else load_kv_block(blk, p, layer, kvh, kb, k1, lane);
-    if (staged_kv) patch_new_row(blk, smem, kvh, kb, k1, p.pos, lane);
+    if (staged_kv) patch_new_row(blk, smem, kvh, kb, k1, pos, lane);
     // scores
     float sc0[4], sc1[4];
     float bmax = -INFINITY;
@@ -262,7 +262,7 @@ template <class S>
 __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph, int head, int P, unsigned tagw) {
   constexpr int HD = S::HD, DPL = S::HD / 32;
   constexpr int kBatch = 8;
-  const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
+  const unsigned rtag = (p.launch_seq + (unsigned)s.step) * 256u + (unsigned)(ph & 255) + 1u;
   float M = -INFINITY, den = 0.f, num[DPL];
 #pragma unroll
   for (int d = 0; d < DPL; ++d) num[d] = 0.f;
@@ -330,12 +330,12 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   static_assert(kWorkers * GQA * HD * 4 <= 2 * L::kActSmall && L::kOffActB == L::kOffActA + L::kActSmall,
                 "the partial outputs use both small activation buffers");
   int bpw, Pc;
-  const int T = p.pos + 1;
+  const int T = p.pos + s.step + 1;
   attn_plan(T, bpw, Pc);
   const int cta = (int)blockIdx.x;
   const int n_compute = S::NKV * Pc;
   const int n_merge = Pc > 1 ? S::NH : 0;
-  const unsigned tagw = phase_tag(p, ph) << 16;
+  const unsigned tagw = phase_tag(p, s.step, ph) << 16;
   if (cta >= n_compute) {   // no staging, no barrier on these CTAs
     if (cta < n_compute + n_merge && s.w == 0 && !s.aborted) {
       const long long tq1 = clock64();
@@ -355,7 +355,7 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   const int n_active = (part_keys + bpw * kAttnBlockKeys - 1) / (bpw * kAttnBlockKeys);   // warps that have keys
   const bool has = k0 < T && !s.aborted;
   KvBlock<S> blk;   // (its first rows have been on their way since the QKV phase started: prefetch_attn_rows)
-  if (!s.aborted && !stage_attn_part<S>(s, p, smem, tagged, phase_tag(p, ph - 1), ph)) flag_abort(s, smem);
+  if (!s.aborted && !stage_attn_part<S>(s, p, smem, tagged, phase_tag(p, s.step, ph - 1), ph)) flag_abort(s, smem);
   cta_sync(s, smem);
   if (s.cta_abort) return;
   const long long tq1 = clock64();
@@ -365,7 +365,8 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   float* mlpart = reinterpret_cast<float*>(smem + L::kOffActD + S::QDIM * 2);   // [warp][head][m, l] (behind the bf16 q)
   if (has) {
     AttnPartial r;
-    attn_blocks<S>(p, smem, phase_layer(ph), kvh, k0, k1, tagged, L::kKvStage && ph > p.phase_begin, blk, s.w, s.lane, r);
+    attn_blocks<S>(p, smem, phase_layer(ph), kvh, k0, k1, tagged, L::kKvStage && (ph > p.phase_begin || s.step > 0), blk, s.w, s.lane, r,
+                   p.pos + s.step);
     const int g = s.lane >> 2, t = s.lane & 3;
     if (g < GQA) {
       float4* dst = reinterpret_cast<float4*>(opart + ((size_t)(s.w * GQA + g) * HD + 16 * t));
@@ -397,7 +398,7 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
       p.attn_out[head * HD + d] = bits;
       if (p.sync) st_handoff(p.t_attn + head * HD + d, (uint32_t)bits | tagw);
     } else {
-      const unsigned rtag = p.launch_seq * 256u + (unsigned)(ph & 255) + 1u;
+      const unsigned rtag = (p.launch_seq + (unsigned)s.step) * 256u + (unsigned)(ph & 255) + 1u;
       unsigned long long* rec = part_record<S>(p, head, part);
       st_handoff(reinterpret_cast<uint32_t*>(rec + d), make_uint2(__float_as_uint(num), rtag));
       if (d == 0) st_handoff(reinterpret_cast<uint4*>(rec + HD), make_uint4(__float_as_uint(M), rtag, __float_as_uint(den), rtag));
@@ -414,12 +415,13 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
 // out of the streaming loop's, and the other way round.  Takes and returns the two abort flags of the warp.
 template <class S>
 static __device__ __noinline__ unsigned phase_attn_call(const Params& p, unsigned char* smem, int ph, int lane, int w,
-                                                        unsigned aborted) {
+                                                        unsigned aborted, int step) {
   Worker<S> s;
   s.lane = lane;
   s.w = w;
   s.nwt = (int)gridDim.x * kWorkers;
   s.g = (int)blockIdx.x * kWorkers + w;
+  s.step = step;
   s.aborted = aborted != 0u;
   s.cta_abort = false;
   phase_attn(s, p, smem, ph);

@@ -155,7 +155,8 @@ int qmkb_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int n_sm, qmk
       rc = QMK_ERR_CUDA;
       break;
     }
-    e = cudaFuncSetAttribute(qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    e = cudaFuncSetAttribute(plain::qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(traced::qmk_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) { rc = fail(err, errlen, "cudaFuncSetAttribute", e); break; }
 
     int max_tiles = (V + kTileRows - 1) / kTileRows;
@@ -417,7 +418,9 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   attr[0].val.cooperative = a->cooperative;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, qmk_batch_kernel, p, c->maps);
+  // (the kernel without the timeline's code unless a trace buffer is attached)
+  e = p.trace != nullptr ? cudaLaunchKernelEx(&cfg, traced::qmk_batch_kernel, p, c->maps)
+                         : cudaLaunchKernelEx(&cfg, plain::qmk_batch_kernel, p, c->maps);
   if (e != cudaSuccess) return fail(err, errlen, "cudaLaunchKernelEx(qmk_batch_kernel)", e);
   return QMK_OK;
 }

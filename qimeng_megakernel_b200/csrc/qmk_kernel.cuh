@@ -84,8 +84,8 @@ __device__ __forceinline__ void trace_put(const Params& p, int ph, int slot, uns
 // Tag of (launch, phase): 1..65535, consecutive phases and launches get consecutive tags, so a stale
 // word (every tagged word is rewritten by every full step) cannot carry the tag a reader waits for.
 // 0 = never written.
-__device__ __forceinline__ unsigned phase_tag(const Params& p, int ph) {
-  return (p.launch_seq * (unsigned)num_phases(p.num_layers) + (unsigned)ph) % 65535u + 1u;
+__device__ __forceinline__ unsigned phase_tag(const Params& p, int step, int ph) {
+  return ((p.launch_seq + (unsigned)step) * (unsigned)num_phases(p.num_layers) + (unsigned)ph) % 65535u + 1u;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -94,6 +94,7 @@ __device__ __forceinline__ unsigned phase_tag(const Params& p, int ph) {
 template <class S>
 struct Worker {
   int lane, w, g, nwt;
+  int step;            // step of the launch this warp is in (0 unless the launch runs several steps)
   uint32_t ring;       // shared address of this warp's first slot
   uint32_t bars;       // shared address of this warp's first mbarrier
   uint32_t ctl;        // shared address of the control words

@@ -24,6 +24,7 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.tmem = reinterpret_cast<const volatile uint32_t*>(smem + L::kOffCtl)[kCtlTmem] + ((uint32_t)(32 * (w & 3)) << 16) +
            (uint32_t)((w >> 2) * kTSlots * kTileCols);
   s.i_slot = s.c_slot = s.c_par = 0;
+  s.step = 0;
   s.res = 0.f;
   s.res_valid = false;
   s.aborted = false;
@@ -35,23 +36,41 @@ __device__ __forceinline__ void worker_main(const Params& p, unsigned char* smem
   s.wb.gate = reinterpret_cast<const unsigned char*>(p.gate);
   s.wb.down = reinterpret_cast<const unsigned char*>(p.down);
   s.wb.lm_head = reinterpret_cast<const unsigned char*>(p.lm_head);
-  s.cur.init(s.g, s.nwt, p.vocab, p.phase_begin);
+  s.cur.init(s.g, s.nwt, p.vocab, p.phase_begin, p.n_steps);
   s.cur.seek(s.wb, p.num_layers, p.phase_end);
 #pragma unroll 1
   for (int i = 0; i < kSlots; ++i) issue_one(s, p);
 
+  // A launch runs n_steps decode steps (one unless the caller asked for a device-resident run of several): the weight
+  // stream of this warp runs on across the step boundary, so the first tiles of the next step are in the ring and in
+  // tensor memory while the step's token is still being decided.
 #pragma unroll 1
-  for (int ph = p.phase_begin; ph < p.phase_end && !s.cta_abort; ++ph) {
-    if (w == 0) trace_put(p, ph, 2, globaltimer_ns(), lane);
-    const int kind = phase_kind(ph, p.num_layers);
-    if (kind == kAttn) {
-      const unsigned f = phase_attn_call<S>(p, smem, ph, lane, w, s.aborted ? 1u : 0u);
-      s.aborted = (f & 1u) != 0u;
-      s.cta_abort = (f & 2u) != 0u;
+  for (; s.step < p.n_steps && !s.cta_abort; ++s.step) {
+    s.res_valid = false;   // the residual stream restarts from the new token's embedding row
+    if (s.step > 0 && w == 0) {
+      // cos / sin of the new position.  Every warp of the CTA has left the last QKV epilogue of the step before (it
+      // passed the CTA barriers of the later phases with this warp), and reads the table only after the barrier of
+      // this step's first staging.
+      float* rope = reinterpret_cast<float*>(smem + SmemLayout<S>::kOffRope);
+      const int pos = p.pos + s.step;
+      for (int i = lane; i < S::HD; i += 32) {
+        rope[i] = __ldg(p.rope_cos + (size_t)pos * S::HD + i);
+        rope[S::HD + i] = __ldg(p.rope_sin + (size_t)pos * S::HD + i);
+      }
     }
-    else phase_stream(s, p, smem, ph, kind);
-    if (w == 0) {
-      trace_put(p, ph, 5, globaltimer_ns(), lane);
+#pragma unroll 1
+    for (int ph = p.phase_begin; ph < p.phase_end && !s.cta_abort; ++ph) {
+      if (w == 0) trace_put(p, ph, 2, globaltimer_ns(), lane);
+      const int kind = phase_kind(ph, p.num_layers);
+      if (kind == kAttn) {
+        const unsigned f = phase_attn_call<S>(p, smem, ph, lane, w, s.aborted ? 1u : 0u, s.step);
+        s.aborted = (f & 1u) != 0u;
+        s.cta_abort = (f & 2u) != 0u;
+      }
+      else phase_stream(s, p, smem, ph, kind);
+      if (w == 0) {
+        trace_put(p, ph, 5, globaltimer_ns(), lane);
+      }
     }
   }
   if (s.n_acquired != s.n_issued) {

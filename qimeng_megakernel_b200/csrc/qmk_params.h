@@ -56,11 +56,15 @@ struct Params {
   // ---- scalars ----
   int num_layers;
   int vocab;
-  int pos;                       // position of the token being fed
+  int pos;                       // position of the token being fed (to the launch's first step)
   int phase_begin, phase_end;    // phases executed by this launch
   int sync;                      // 1: phases hand off through tagged words; 0: single phase, stream-ordered
   int wait_first;                // 1: also wait for the dependency of phase_begin (debug / failure test)
-  unsigned launch_seq;           // number of this launch (per handle): makes every launch's tags distinct
+  unsigned launch_seq;           // number of this launch's first step (per handle): makes every step's tags distinct
+  int n_steps;                   // decode steps run by this launch (> 1: whole steps only; step i is position pos + i, fed
+                                 // the arg-max of step i - 1 through tok_word)
+  unsigned long long* tok_word;  // {token id, tag = number of the step that produced it + 1}: the token hand-off between
+                                 // the steps of one launch
   float eps;
   float scale_log2e;             // attn_scale * log2(e)
   long long timeout_cycles;      // bounded-wait budget

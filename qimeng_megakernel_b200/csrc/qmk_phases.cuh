@@ -11,9 +11,10 @@ namespace qmk {
 // when the step is fed a token id (the reference does `hidden_states.copy_(embed[ids])` on the
 // host side, qimeng_megakernel/models/LLM/decode.py:1376-1377).
 template <class S>
-__device__ __forceinline__ const uint16_t* residual_src(const Params& p, int layer) {
-  if (layer == 0 && p.token_in != nullptr) {
-    long long tok = __ldcg(p.token_in);
+__device__ __forceinline__ const uint16_t* residual_src(Worker<S>& s, const Params& p, int layer, int ph) {
+  if (layer == 0 && (p.token_in != nullptr || s.step > 0)) {
+    long long tok = s.step > 0 ? poll_token(s, p, ph) : __ldcg(p.token_in);
+    if (tok < 0 && s.step > 0) return nullptr;
     if (tok < 0) tok = 0;
     if (tok >= p.vocab) tok = p.vocab - 1;
     return p.embed + (size_t)tok * S::H;
@@ -33,7 +34,7 @@ __device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, in
 // tagged, to the scratch the attention phase of this step reads.
 template <class S>
 __device__ __forceinline__ void epilogue_qkv(const Params& p, const unsigned char* smem, int layer, int unit,
-                                             float a, float b, unsigned tagw) {
+                                             float a, float b, unsigned tagw, int pos) {
   const float* rope = reinterpret_cast<const float*>(smem + SmemLayout<S>::kOffRope);
   const int row = 2 * unit;
   a = bf16_round(a);
@@ -53,12 +54,12 @@ __device__ __forceinline__ void epilogue_qkv(const Params& p, const unsigned cha
       dst = p.q_post_rope + row;
       tdst = p.t_q + row;
     } else {
-      dst = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - kStart);
+      dst = p.k_cache + (size_t)layer * p.kv_layer_stride + (size_t)pos * p.kv_seq_stride + (row - kStart);
       tdst = p.t_q + S::QDIM + (row - kStart);
     }
   } else {
     packed = pack_bf16x2(a, b);
-    dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)p.pos * p.kv_seq_stride + (row - vStart);
+    dst = p.v_cache + (size_t)layer * p.kv_layer_stride + (size_t)pos * p.kv_seq_stride + (row - vStart);
     tdst = p.t_q + S::QDIM + S::NKV * S::HD + (row - vStart);
   }
   if (row < kStart) *reinterpret_cast<uint32_t*>(dst) = packed;
@@ -91,8 +92,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   static_assert(S::QDIM == kChunkElems && S::H == kChunkElems, "rows of QKV/O/up/gate/LM must be one chunk");
   const int layer = phase_layer(ph);
   const bool tagged = p.sync && (ph > p.phase_begin || p.wait_first);
-  const unsigned tag_in = phase_tag(p, ph - 1);
-  const unsigned tagw = phase_tag(p, ph) << 16;
+  const unsigned tag_in = phase_tag(p, s.step, ph - 1);
+  const unsigned tagw = phase_tag(p, s.step, ph) << 16;
   const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
   const int sbuf = small_buf_index(ph, p.num_layers);
   unsigned char* act = smem + (kind == kDown ? L::kOffActD : (sbuf ? L::kOffActB : L::kOffActA));
@@ -120,8 +121,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     const uint32_t* tsrc = kind == kOproj ? p.t_attn : (kind == kUpGate ? p.t_hid_o : p.t_hid_d);
     const uint16_t* psrc = kind == kOproj ? p.attn_out
                                           : (kind == kQkv || (kind == kLmHead && p.num_layers == 0)
-                                                 ? residual_src<S>(p, layer) : p.hidden);
-    if (!s.aborted && !fetch_part<S::H>(s, p, tsrc, psrc, tagged, tag_in, ph, part)) flag_abort(s, smem);
+                                                 ? residual_src<S>(s, p, layer, ph) : p.hidden);
+    if (!s.aborted && (psrc == nullptr || !fetch_part<S::H>(s, p, tsrc, psrc, tagged, tag_in, ph, part))) flag_abort(s, smem);
     if (normed) {
       const float ss = s.aborted ? 0.f : part_sumsq(part);
       if (s.lane == 0) sumsq[s.w] = ss;
@@ -143,8 +144,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   // land); the first layer of a launch does it in its own QKV phase.
   if (!s.aborted) {
     if (kind == kUpGate && layer + 1 < p.num_layers && ph + 3 < p.phase_end)
-      prefetch_attn_rows<S>(p, smem, layer + 1, s.w, s.lane);
-    if (kind == kQkv && (layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane);
+      prefetch_attn_rows<S>(p, smem, layer + 1, s.w, s.lane, p.pos + s.step);
+    if (kind == kQkv && (layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane, p.pos + s.step);
   }
 
   int i0, i1;
@@ -161,7 +162,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     XFrag xf;
     if (nsl == 1) load_xfrag(xf, act, s.lane);
     const bool residual = kind == kOproj || kind == kDown;
-    const uint16_t* res = kind == kOproj ? residual_src<S>(p, layer) : p.hidden;
+    const uint16_t* res = kind == kOproj ? residual_src<S>(s, p, layer, ph) : p.hidden;
+    if (res == nullptr) { flag_abort(s, smem); res = p.hidden; }
     uint32_t* tres = kind == kOproj ? p.t_hid_o : p.t_hid_d;
 #pragma unroll 1
     for (int ib = i0; ib < i1 && !s.aborted; ib += 32) {
@@ -195,7 +197,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
       if (s.lane < nb && !s.aborted) {
         const int item = ib + s.lane;
         switch (kind) {
-          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb, tagw); break;
+          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb, tagw, p.pos + s.step); break;
           case kUpGate: {
             const unsigned short bits = epilogue_silu(va, vb);
             p.silu_out[item] = bits;
@@ -246,7 +248,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     atomicMax(cta_key, best);
     __threadfence();
     if (atomicAdd(ctl + kCtlLmArrive, 1u) == (unsigned)(kWorkers - 1)) {
-      const unsigned long long k = atomicMax(cta_key, 0ull);
+      const unsigned long long k = atomicExch(cta_key, 0ull);   // (both words are left zero for the launch's next step)
+      ctl[kCtlLmArrive] = 0u;
       atomicMax(p.argmax_key, k);
       __threadfence();
       unsigned* lm_ticket = p.tickets + 64;
@@ -255,10 +258,13 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
         const unsigned long long win = atomicMax(p.argmax_key, 0ull);
         const long long tok = (long long)(0xffffffffu - (unsigned)(win & 0xffffffffull));
         if (p.next_token) *p.next_token = tok;
-        if (p.out_tokens && (long long)p.pos + 1 < p.out_tokens_len) p.out_tokens[p.pos + 1] = tok;
+        const long long at = (long long)p.pos + s.step + 1;
+        if (p.out_tokens && at < p.out_tokens_len) p.out_tokens[at] = tok;
         *p.argmax_key = 0ull;
         *lm_ticket = 0u;
         __threadfence();
+        // the token hand-off to the launch's next step, after the resets it must not overtake
+        st_handoff(reinterpret_cast<uint32_t*>(p.tok_word), make_uint2((unsigned)tok, p.launch_seq + (unsigned)s.step + 1u));
       }
     }
   }

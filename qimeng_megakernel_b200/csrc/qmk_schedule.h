@@ -104,18 +104,20 @@ struct TileCursor {
   int l0, l1;              // LM head rows
   // position in the stream
   int ph, kind;            // phase being issued and its kind
+  int first_ph, steps_left;  // multi-step launches: the stream wraps from phase_end to first_ph, steps_left - 1 more times
   int left;                // tiles left in that phase
   int sub;                 // down-proj: k-slice of the next tile
   int rows_left;           // rows (O-proj / LM / down) still to be covered, to spot the odd last row
   const unsigned char* p0; // next source (first chunk)
   const unsigned char* p1; // up/gate: gate row
 
-  QMK_HD void init(int g, int nwt, int vocab, int phase_begin) {
+  QMK_HD void init(int g, int nwt, int vocab, int phase_begin, int steps = 1) {
     split_range_u32(S::QKV_ROWS / 2, nwt, g, q0, q1);
     split_range_u32(S::H, nwt, g, r0, r1);
     split_range_u32(S::I, nwt, g, u0, u1);
     split_range_u32((unsigned)vocab, nwt, g, l0, l1);
-    ph = phase_begin;
+    ph = first_ph = phase_begin;
+    steps_left = steps;
     kind = left = sub = rows_left = 0;
     p0 = p1 = nullptr;
   }
@@ -134,7 +136,12 @@ struct TileCursor {
 
   // Position on the first phase >= ph in which this worker streams weights; set its first sources.
   QMK_HD void seek(const StreamBases& w, int num_layers, int phase_end) {
-    while (ph < phase_end) {
+    for (;;) {
+      if (ph >= phase_end) {
+        if (steps_left <= 1) return;
+        --steps_left;            // the next step of the launch: the same phases again
+        ph = first_ph;
+      }
       const int layer = ph / kPhasesPerLayer;
       const int k = layer >= num_layers ? (int)kLmHead : ph - layer * kPhasesPerLayer;
       const int n = tiles(k);

@@ -54,6 +54,22 @@ __device__ __forceinline__ bool poll_tagged(Worker<S>& s, const Params& p, const
   }
 }
 
+// Steps after the first of a multi-step launch: the token fed to the step is the arg-max of the step before, handed over
+// as one 64-bit word {token id, tag}; every warp polls it (bounded) before it reads its part of the embedding row.
+// Returns -1 when the wait gave up.
+template <class S>
+__device__ __forceinline__ long long poll_token(Worker<S>& s, const Params& p, int ph) {
+  const unsigned want = p.launch_seq + (unsigned)s.step;   // (number of the producing step) + 1
+  const long long t0 = clock64();
+  for (unsigned it = 0;; ++it) {
+    const unsigned long long w = __ldcg(p.tok_word);
+    if (it > 0) poll_backoff(s, p, it);
+    const bool ok = (unsigned)(w >> 32) == want;
+    if (__all_sync(kFullMask, ok)) return (long long)(unsigned)(w & 0xffffffffull);
+    if ((it & 15u) == 15u && poll_give_up(p, t0, ok, (unsigned)(w >> 32), want, s.w, ph, s.lane)) return -1;
+  }
+}
+
 // 4 tagged words -> 4 bf16 packed in 8 bytes.
 __device__ __forceinline__ uint2 untag4(const uint4& v) {
   return make_uint2((v.x & 0xffffu) | (v.y << 16), (v.z & 0xffffu) | (v.w << 16));
@@ -142,10 +158,10 @@ __device__ __forceinline__ const uint4* kv_piece(const Params& p, int layer, int
 // starts; each lane copies exactly the pieces it will read back itself, so its own wait_group is all the
 // synchronisation needed.  Without room in shared memory the rows are only pulled into L2.
 template <class S>
-__device__ __forceinline__ void prefetch_attn_rows(const Params& p, unsigned char* smem, int layer, int w, int lane) {
+__device__ __forceinline__ void prefetch_attn_rows(const Params& p, unsigned char* smem, int layer, int w, int lane, int pos) {
   using L = SmemLayout<S>;
   int bpw, Pc;
-  const int T = p.pos + 1;
+  const int T = pos + 1;
   attn_plan(T, bpw, Pc);
   const int cta = (int)blockIdx.x;
   if (cta >= S::NKV * Pc) return;

@@ -188,6 +188,8 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
   p.t_silu = (uint32_t*)(dev.scratch + lay.t_silu);
   p.tickets = (unsigned*)(dev.scratch + lay.tickets);
   p.argmax_key = (unsigned long long*)(dev.scratch + lay.argmax);
+  p.tok_word = (unsigned long long*)(dev.scratch + lay.argmax + 64);
+  p.n_steps = 1;
   p.status = (unsigned*)(dev.scratch + lay.status);
   p.trace = nullptr;
   p.num_layers = d->num_layers;

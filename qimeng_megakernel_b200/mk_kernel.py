@@ -219,6 +219,12 @@ class MegaKernel:
                                                first_pos, n_steps, 1 if teacher_forced else 0, ha,
                                                self._stream()), self._handle)
 
+    def generate_device(self, g: Globals, first_pos: int, n_steps: int) -> None:
+        """n_steps greedy steps from first_pos with the token loop on the device (g.token_in feeds the first step, every
+        later one takes the arg-max of the step before): one persistent launch on the batch-1 kernel."""
+        self._ensure(g)
+        _lib.check(self._lib.qmk_generate_device(self._handle, int(first_pos), int(n_steps), self._stream()), self._handle)
+
     def poll_status(self) -> dict:
         st = _lib.Status()
         rc = self._lib.qmk_poll_status(self._handle, C.byref(st)) if self._handle is not None else 0   # nothing launched yet

@@ -98,7 +98,7 @@ QWEN3_0_6B = dict(num_hidden_layers=28, hidden_size=1024, intermediate_size=3072
                   num_attention_heads=16, num_key_value_heads=8, vocab_size=151936, rms_norm_eps=1e-6,
                   rope_theta=1000000.0, rope_scaling=None, max_position_embeddings=40960, qk_norm=True)
 
-# OLMoE-1B-7B shape (BASELINE configuration 5): MHA 16 x 128, 64 experts, top-8, expert intermediate 1024, no shared expert
+# OLMoE-1B-7B shape (the mixture-of-experts workload of the benchmark): MHA 16 x 128, 64 experts, top-8, expert intermediate 1024, no shared expert
 OLMOE_1B_7B = dict(num_hidden_layers=16, hidden_size=2048, intermediate_size=1024, head_dim=128,
                    num_attention_heads=16, num_key_value_heads=16, vocab_size=50304, rms_norm_eps=1e-5,
                    rope_theta=10000.0, rope_scaling=None, max_position_embeddings=4096, qk_norm=False,

@@ -110,6 +110,36 @@ int run_attn_plan() {
   return 0;
 }
 
+// A launch of several steps: every worker's stream is its one-step stream, repeated, and ends after the last step.
+int run_multi_step(int nsm, int warps, int layers, int vocab, int steps) {
+  using S = ShapeLlama1B;
+  StreamBases w;
+  unsigned char* base = reinterpret_cast<unsigned char*>(uintptr_t(1) << 40);
+  w.qkv = base; w.o_proj = base + (size_t(1) << 36); w.up = base + (size_t(2) << 36); w.gate = base + (size_t(3) << 36);
+  w.down = base + (size_t(4) << 36); w.lm_head = base + (size_t(5) << 36);
+  const int nwt = nsm * warps, nph = num_phases(layers);
+  for (int g = 0; g < nwt; ++g) {
+    std::vector<Tile> one;
+    TileCursor<S> a;
+    a.init(g, nwt, vocab, 0);
+    a.seek(w, layers, nph);
+    while (!a.done(nph)) one.push_back(a.next(w, layers, nph));
+    TileCursor<S> b;
+    b.init(g, nwt, vocab, 0, steps);
+    b.seek(w, layers, nph);
+    size_t n = 0;
+    while (!b.done(nph)) {
+      if (one.empty()) return fail("a worker without tiles streams in a multi-step launch", g, 0);
+      const Tile t = b.next(w, layers, nph), &r = one[n % one.size()];
+      if (t.a != r.a || t.b != r.b || t.bytes_a != r.bytes_a) return fail("multi-step stream differs from the repeated step", g, (int)n);
+      ++n;
+      if (n > one.size() * (size_t)steps) return fail("multi-step stream does not end", g, (int)n);
+    }
+    if (n != one.size() * (size_t)steps) return fail("multi-step stream length", g, (int)n, (int)(one.size() * steps));
+  }
+  return 0;
+}
+
 int main() {
   struct Case { int nsm, warps, layers, vocab, pb, pe; };
   const Case cases[] = {
@@ -124,6 +154,7 @@ int main() {
     }
   }
   if (run_attn_plan()) return 1;
+  if (run_multi_step(148, 8, 2, 128256, 3) || run_multi_step(4, 8, 1, 37, 5) || run_multi_step(148, 8, 0, 4096, 2)) return 1;
   std::puts("schedule ok");
   return 0;
 }

@@ -206,6 +206,30 @@ def test_device_token_loop_and_host_generate(env):
         g.position_id = pos
         mk(g)
     assert dev_tokens.tolist() == out_a
+    logits_c = g.logits.clone()
+    # path D: the same run as persistent multi-step launches (qmk_generate_device): the token crosses the step boundary
+    # inside the kernel.  Chunks of 1, 5, 7 and the rest; tokens and the last logits must be the single-step loop's, bit for bit.
+    g.k_cache.zero_(); g.v_cache.zero_()
+    dev_tokens[len(prompt):] = 0
+    g.next_token = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for pos in range(len(prompt) - 1):
+        g.token_in.copy_(dev_tokens[pos:pos + 1]); g.position_id = pos
+        saved = dev_tokens[pos + 1].clone()
+        mk(g)
+        dev_tokens[pos + 1] = saved
+    g.token_in.copy_(dev_tokens[len(prompt) - 1:len(prompt)])
+    g.next_token = g.token_in
+    pos, left = len(prompt) - 1, n_new
+    for chunk in (1, 5, 7, n_new):
+        n = min(chunk, left)
+        if n <= 0:
+            break
+        mk.generate_device(g, pos, n)
+        pos, left = pos + n, left - n
+    torch.cuda.synchronize()
+    mk.check_status()
+    assert dev_tokens.tolist() == out_a, "multi-step launches disagree with the one-step loop"
+    assert torch.equal(g.logits.view(torch.int16), logits_c.view(torch.int16))
     g.token_in = None; g.out_tokens = None
     g.next_token = torch.zeros(1, dtype=torch.int64, device="cuda")
     mk.check_status()
