@@ -44,7 +44,7 @@ WORKLOAD = ("Llama-3.2-1B shape (16 layers, hidden 2048, 32/8 heads x 64, SwiGLU
 METRIC = "decode kernel_tok_s at batch 1 (Llama-1B shape)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of qmk_decode_kernel (KV length 36), from the ncu
 # capture summarised in profiles/qmk_decode_kernel_step_llama1b.md.
-TRAFFIC_BYTES_PER_LAUNCH = 2.4787e9
+TRAFFIC_BYTES_PER_LAUNCH = 2.4791e9   # dram__bytes_read + write of one decode step (profiles/qmk_decode_kernel_step_llama1b.md)
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -475,7 +475,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (rank 0, N = 1 only)")
     ap.add_argument("--no-secondary", action="store_true", help="headline line only: skip the short runs of the other workload shapes")
-    ap.add_argument("--steps-per-launch", type=int, default=64,
+    ap.add_argument("--steps-per-launch", type=int, default=1,
                     help="headline run: decode steps per persistent launch of the batch-1 kernel in the device-timed loop")
     ap.add_argument("--batch", type=int, default=1, help="sequences per GPU (> 1, or any --model but llama: the batched kernel)")
     ap.add_argument("--model", default="llama-3.2-1b", choices=["llama-3.2-1b", "qwen3-0.6b", "olmoe-1b-7b"])

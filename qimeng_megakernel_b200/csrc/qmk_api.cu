@@ -156,6 +156,9 @@ extern "C" int qmk_create(const qmk_model_desc* d, const qmk_weight_ptrs* w, int
     }
     e = cudaFuncSetAttribute(qmk_decode_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SmemLayout<Shape>::kTotal);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmk_decode_kernel<ShapeLlama1BSteps>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout<Shape>::kTotal);
     if (e != cudaSuccess) { rc = cuda_fail(h, e, "cudaFuncSetAttribute"); break; }
     const size_t b_part = align_up((size_t)Shape::NH * kMaxSplits * (Shape::HD + 2) * 8, 256);
     const size_t b_hid = align_up((size_t)Shape::H * 4, 256);
@@ -296,11 +299,13 @@ static int launch(qmk_handle* h, Params& p, cudaStream_t stream) {
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;   // all CTAs co-resident: they wait on one another
   attr[0].val.cooperative = h->cooperative;
+  p.stream_end = p.phase_end + (p.n_steps > 1 ? (p.n_steps - 1) * num_phases(p.num_layers) : 0);
   p.launch_seq = h->launch_seq + 1;   // number of the launch's first step; every step takes one
   h->launch_seq += (unsigned)(p.n_steps > 0 ? p.n_steps : 1);
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p));
+  if (p.n_steps > 1) QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<ShapeLlama1BSteps>, p));   // the multi-step instance
+  else QMK_CUDA(h, cudaLaunchKernelEx(&cfg, qmk_decode_kernel<Shape>, p));
   h->launches++;
   h->last_stream = stream;
   h->last_kernel = 0;

@@ -259,10 +259,10 @@ __device__ __forceinline__ void attn_blocks(const Params& p, unsigned char* smem
 // ---- merge unit: one query head; polls the P partial records of that head (eight at a time, all
 // loads in flight together), merges them with a running maximum and writes attn_out.
 template <class S>
-__device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph, int head, int P, unsigned tagw) {
+__device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph, int gph, int head, int P, unsigned tagw) {
   constexpr int HD = S::HD, DPL = S::HD / 32;
   constexpr int kBatch = 8;
-  const unsigned rtag = (p.launch_seq + (unsigned)s.step) * 256u + (unsigned)(ph & 255) + 1u;
+  const unsigned rtag = p.launch_seq * (unsigned)num_phases(p.num_layers) + (unsigned)gph + 1u;   // unique per (step, phase)
   float M = -INFINITY, den = 0.f, num[DPL];
 #pragma unroll
   for (int d = 0; d < DPL; ++d) num[d] = 0.f;
@@ -322,7 +322,7 @@ __device__ __forceinline__ void attn_merge(Worker<S>& s, const Params& p, int ph
 // Pc == 1 (T <= 256): that is attn_out.  Otherwise the merged partial is a record, and merge unit m (query head m)
 // on warp 0 of CTA NKV * Pc + m polls the Pc records of its head.
 template <class S>
-__device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsigned char* smem, int ph) {
+__device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int gph) {
   using L = SmemLayout<S>;
   constexpr int HD = S::HD, GQA = S::GQA;
   static_assert(GQA * HD == kThreads, "the in-CTA merge gives every thread one (head, dim)");
@@ -330,16 +330,16 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   static_assert(kWorkers * GQA * HD * 4 <= 2 * L::kActSmall && L::kOffActB == L::kOffActA + L::kActSmall,
                 "the partial outputs use both small activation buffers");
   int bpw, Pc;
-  const int T = p.pos + s.step + 1;
+  const int T = step_pos<S>(p, smem) + 1;
   attn_plan(T, bpw, Pc);
   const int cta = (int)blockIdx.x;
   const int n_compute = S::NKV * Pc;
   const int n_merge = Pc > 1 ? S::NH : 0;
-  const unsigned tagw = phase_tag(p, s.step, ph) << 16;
+  const unsigned tagw = phase_tag(p, gph) << 16;
   if (cta >= n_compute) {   // no staging, no barrier on these CTAs
     if (cta < n_compute + n_merge && s.w == 0 && !s.aborted) {
       const long long tq1 = clock64();
-      attn_merge(s, p, ph, cta - n_compute, Pc, tagw);
+      attn_merge(s, p, ph, gph, cta - n_compute, Pc, tagw);
       trace_put(p, ph, 6, (unsigned long long)(clock64() - tq1), s.lane);
     }
     return;
@@ -355,7 +355,7 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   const int n_active = (part_keys + bpw * kAttnBlockKeys - 1) / (bpw * kAttnBlockKeys);   // warps that have keys
   const bool has = k0 < T && !s.aborted;
   KvBlock<S> blk;   // (its first rows have been on their way since the QKV phase started: prefetch_attn_rows)
-  if (!s.aborted && !stage_attn_part<S>(s, p, smem, tagged, phase_tag(p, s.step, ph - 1), ph)) flag_abort(s, smem);
+  if (!s.aborted && !stage_attn_part<S>(s, p, smem, tagged, phase_tag(p, gph - 1), ph)) flag_abort(s, smem);
   cta_sync(s, smem);
   if (s.cta_abort) return;
   const long long tq1 = clock64();
@@ -365,8 +365,8 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
   float* mlpart = reinterpret_cast<float*>(smem + L::kOffActD + S::QDIM * 2);   // [warp][head][m, l] (behind the bf16 q)
   if (has) {
     AttnPartial r;
-    attn_blocks<S>(p, smem, phase_layer(ph), kvh, k0, k1, tagged, L::kKvStage && (ph > p.phase_begin || s.step > 0), blk, s.w, s.lane, r,
-                   p.pos + s.step);
+    attn_blocks<S>(p, smem, phase_layer(ph), kvh, k0, k1, tagged, L::kKvStage && gph > p.phase_begin, blk, s.w, s.lane, r,
+                   T - 1);
     const int g = s.lane >> 2, t = s.lane & 3;
     if (g < GQA) {
       float4* dst = reinterpret_cast<float4*>(opart + ((size_t)(s.w * GQA + g) * HD + 16 * t));
@@ -398,7 +398,7 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
       p.attn_out[head * HD + d] = bits;
       if (p.sync) st_handoff(p.t_attn + head * HD + d, (uint32_t)bits | tagw);
     } else {
-      const unsigned rtag = (p.launch_seq + (unsigned)s.step) * 256u + (unsigned)(ph & 255) + 1u;
+      const unsigned rtag = p.launch_seq * (unsigned)num_phases(p.num_layers) + (unsigned)gph + 1u;
       unsigned long long* rec = part_record<S>(p, head, part);
       st_handoff(reinterpret_cast<uint32_t*>(rec + d), make_uint2(__float_as_uint(num), rtag));
       if (d == 0) st_handoff(reinterpret_cast<uint4*>(rec + HD), make_uint4(__float_as_uint(M), rtag, __float_as_uint(den), rtag));
@@ -415,16 +415,15 @@ __device__ __forceinline__ void phase_attn(Worker<S>& s, const Params& p, unsign
 // out of the streaming loop's, and the other way round.  Takes and returns the two abort flags of the warp.
 template <class S>
 static __device__ __noinline__ unsigned phase_attn_call(const Params& p, unsigned char* smem, int ph, int lane, int w,
-                                                        unsigned aborted, int step) {
+                                                        unsigned aborted, int gph) {
   Worker<S> s;
   s.lane = lane;
   s.w = w;
   s.nwt = (int)gridDim.x * kWorkers;
   s.g = (int)blockIdx.x * kWorkers + w;
-  s.step = step;
   s.aborted = aborted != 0u;
   s.cta_abort = false;
-  phase_attn(s, p, smem, ph);
+  phase_attn(s, p, smem, ph, gph);
   return (s.aborted ? 1u : 0u) | (s.cta_abort ? 2u : 0u);
 }
 

@@ -51,7 +51,8 @@ struct SmemLayout {
   static constexpr int kOffBars = kOffActD + kActBig;                // kWorkers*kSlots u64
   static constexpr int kOffCtl = kOffBars + kWorkers * kSlots * 8;   // control words (128 B)
   static constexpr int kOffRope = kOffCtl + 128;                     // cos[HD], sin[HD] of this step's position
-  static constexpr int kTotal = kOffRope + S::HD * 8;
+  static constexpr int kOffPos = kOffRope + S::HD * 8;               // position of the step the CTA is in (one int)
+  static constexpr int kTotal = kOffPos + 16;
 };
 // control block, 32-bit words from kOffCtl:
 //   [0] abort word (non-zero: a warp of this CTA gave up)   [8] lm_arrive   [10..11] CTA arg-max key (u64)
@@ -84,8 +85,10 @@ __device__ __forceinline__ void trace_put(const Params& p, int ph, int slot, uns
 // Tag of (launch, phase): 1..65535, consecutive phases and launches get consecutive tags, so a stale
 // word (every tagged word is rewritten by every full step) cannot carry the tag a reader waits for.
 // 0 = never written.
-__device__ __forceinline__ unsigned phase_tag(const Params& p, int step, int ph) {
-  return ((p.launch_seq + (unsigned)step) * (unsigned)num_phases(p.num_layers) + (unsigned)ph) % 65535u + 1u;
+// gph: the phase counted over the steps of the launch (step * num_phases + phase; launch_seq numbers the launch's first
+// step, every step takes one number, so consecutive launches continue the same sequence).
+__device__ __forceinline__ unsigned phase_tag(const Params& p, int gph) {
+  return (p.launch_seq * (unsigned)num_phases(p.num_layers) + (unsigned)gph) % 65535u + 1u;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -94,7 +97,6 @@ __device__ __forceinline__ unsigned phase_tag(const Params& p, int step, int ph)
 template <class S>
 struct Worker {
   int lane, w, g, nwt;
-  int step;            // step of the launch this warp is in (0 unless the launch runs several steps)
   uint32_t ring;       // shared address of this warp's first slot
   uint32_t bars;       // shared address of this warp's first mbarrier
   uint32_t ctl;        // shared address of the control words
@@ -112,12 +114,21 @@ struct Worker {
   uint64_t policy;
 };
 
+// Position of the decode step the CTA is in: written by warp 0 with the step's RoPE row (kernel entry, and the first phase
+// of every later step of a multi-step launch), read after a CTA barrier of the same step.
+template <class S>
+__device__ __forceinline__ int step_pos(const Params& p, const unsigned char* smem) {
+  if constexpr (S::kMulti) return *reinterpret_cast<const volatile int*>(smem + SmemLayout<S>::kOffPos);
+  else return p.pos;
+}
+
 // Issue the next tile of the stream into the oldest free slot, if any tile is left: one 8-KiB bulk
 // copy, or two 4-KiB copies completing on the same mbarrier.
 template <class S>
 __device__ __forceinline__ void issue_one(Worker<S>& s, const Params& p) {
-  if (s.aborted || s.cur.done(p.phase_end)) return;
-  const Tile t = s.cur.next(s.wb, p.num_layers, p.phase_end);
+  const int end = S::kMulti ? p.stream_end : p.phase_end;
+  if (s.aborted || s.cur.done(end)) return;
+  const Tile t = s.cur.next(s.wb, p.num_layers, end);
   if (s.lane == 0) {
     const uint32_t bar = s.bars + s.i_slot * 8;
     const uint32_t dst = s.ring + s.i_slot * (2 * kChunkBytes);

@@ -57,7 +57,8 @@ struct Params {
   int num_layers;
   int vocab;
   int pos;                       // position of the token being fed (to the launch's first step)
-  int phase_begin, phase_end;    // phases executed by this launch
+  int phase_begin, phase_end;    // phases executed by this launch (by every step of it)
+  int stream_end;                // where the weight stream of the launch ends: phase_end + (n_steps - 1) * phases per step
   int sync;                      // 1: phases hand off through tagged words; 0: single phase, stream-ordered
   int wait_first;                // 1: also wait for the dependency of phase_begin (debug / failure test)
   unsigned launch_seq;           // number of this launch's first step (per handle): makes every step's tags distinct

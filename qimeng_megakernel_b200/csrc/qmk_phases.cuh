@@ -11,10 +11,15 @@ namespace qmk {
 // when the step is fed a token id (the reference does `hidden_states.copy_(embed[ids])` on the
 // host side, qimeng_megakernel/models/LLM/decode.py:1376-1377).
 template <class S>
-__device__ __forceinline__ const uint16_t* residual_src(Worker<S>& s, const Params& p, int layer, int ph) {
-  if (layer == 0 && (p.token_in != nullptr || s.step > 0)) {
-    long long tok = s.step > 0 ? poll_token(s, p, ph) : __ldcg(p.token_in);
-    if (tok < 0 && s.step > 0) return nullptr;
+__device__ __forceinline__ const uint16_t* residual_src(Worker<S>& s, const Params& p, int layer, int ph, bool wait, int gph) {
+  const int step = (S::kMulti && layer == 0) ? gph / num_phases(p.num_layers) : 0;
+  if (layer == 0 && (p.token_in != nullptr || step > 0)) {
+    // (wait: the QKV phase, which is the first to need the token of a later step; the O-projection reads the word the
+    // QKV phase of the same step has already seen)
+    long long tok = step == 0 ? __ldcg(p.token_in)
+                  : (wait ? wait_token(p, p.launch_seq + (unsigned)step, s.w, ph, s.lane)
+                          : (long long)(unsigned)(__ldcg(p.tok_word) & 0xffffffffull));
+    if (tok < 0 && step > 0) return nullptr;
     if (tok < 0) tok = 0;
     if (tok >= p.vocab) tok = p.vocab - 1;
     return p.embed + (size_t)tok * S::H;
@@ -86,14 +91,14 @@ __device__ __forceinline__ unsigned short epilogue_silu(float up, float gate) {
 // LM head (fused_rms_lmhead_gemv, operations.py:303-321) also keeps the arg-max of the bf16 logits,
 // lowest index on ties, replacing `logits.argmax()` of the host loop (decode.py:1391-1395).
 template <class S>
-__device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kind) {
+__device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsigned char* smem, int ph, int kind, int gph) {
   using L = SmemLayout<S>;
   constexpr int kSlices = S::I / kChunkElems;
   static_assert(S::QDIM == kChunkElems && S::H == kChunkElems, "rows of QKV/O/up/gate/LM must be one chunk");
   const int layer = phase_layer(ph);
   const bool tagged = p.sync && (ph > p.phase_begin || p.wait_first);
-  const unsigned tag_in = phase_tag(p, s.step, ph - 1);
-  const unsigned tagw = phase_tag(p, s.step, ph) << 16;
+  const unsigned tag_in = phase_tag(p, gph - 1);
+  const unsigned tagw = phase_tag(p, gph) << 16;
   const bool normed = kind == kQkv || kind == kUpGate || kind == kLmHead;
   const int sbuf = small_buf_index(ph, p.num_layers);
   unsigned char* act = smem + (kind == kDown ? L::kOffActD : (sbuf ? L::kOffActB : L::kOffActA));
@@ -121,7 +126,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     const uint32_t* tsrc = kind == kOproj ? p.t_attn : (kind == kUpGate ? p.t_hid_o : p.t_hid_d);
     const uint16_t* psrc = kind == kOproj ? p.attn_out
                                           : (kind == kQkv || (kind == kLmHead && p.num_layers == 0)
-                                                 ? residual_src<S>(s, p, layer, ph) : p.hidden);
+                                                 ? residual_src<S>(s, p, layer, ph, true, gph) : p.hidden);
     if (!s.aborted && (psrc == nullptr || !fetch_part<S::H>(s, p, tsrc, psrc, tagged, tag_in, ph, part))) flag_abort(s, smem);
     if (normed) {
       const float ss = s.aborted ? 0.f : part_sumsq(part);
@@ -144,8 +149,8 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
   // land); the first layer of a launch does it in its own QKV phase.
   if (!s.aborted) {
     if (kind == kUpGate && layer + 1 < p.num_layers && ph + 3 < p.phase_end)
-      prefetch_attn_rows<S>(p, smem, layer + 1, s.w, s.lane, p.pos + s.step);
-    if (kind == kQkv && (layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane, p.pos + s.step);
+      prefetch_attn_rows<S>(p, smem, layer + 1, s.w, s.lane, step_pos<S>(p, smem));
+    if (kind == kQkv && (layer == 0 || ph - 2 < p.phase_begin)) prefetch_attn_rows<S>(p, smem, layer, s.w, s.lane, step_pos<S>(p, smem));
   }
 
   int i0, i1;
@@ -162,8 +167,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     XFrag xf;
     if (nsl == 1) load_xfrag(xf, act, s.lane);
     const bool residual = kind == kOproj || kind == kDown;
-    const uint16_t* res = kind == kOproj ? residual_src<S>(s, p, layer, ph) : p.hidden;
-    if (res == nullptr) { flag_abort(s, smem); res = p.hidden; }
+    const uint16_t* res = kind == kOproj ? residual_src<S>(s, p, layer, ph, false, gph) : p.hidden;
     uint32_t* tres = kind == kOproj ? p.t_hid_o : p.t_hid_d;
 #pragma unroll 1
     for (int ib = i0; ib < i1 && !s.aborted; ib += 32) {
@@ -197,7 +201,7 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
       if (s.lane < nb && !s.aborted) {
         const int item = ib + s.lane;
         switch (kind) {
-          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb, tagw, p.pos + s.step); break;
+          case kQkv: epilogue_qkv<S>(p, smem, layer, item, va, vb, tagw, step_pos<S>(p, smem)); break;
           case kUpGate: {
             const unsigned short bits = epilogue_silu(va, vb);
             p.silu_out[item] = bits;
@@ -248,8 +252,13 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
     atomicMax(cta_key, best);
     __threadfence();
     if (atomicAdd(ctl + kCtlLmArrive, 1u) == (unsigned)(kWorkers - 1)) {
-      const unsigned long long k = atomicExch(cta_key, 0ull);   // (both words are left zero for the launch's next step)
-      ctl[kCtlLmArrive] = 0u;
+      unsigned long long k;
+      if constexpr (S::kMulti) {   // both words are left zero for the launch's next step
+        k = atomicExch(cta_key, 0ull);
+        ctl[kCtlLmArrive] = 0u;
+      } else {
+        k = atomicMax(cta_key, 0ull);
+      }
       atomicMax(p.argmax_key, k);
       __threadfence();
       unsigned* lm_ticket = p.tickets + 64;
@@ -258,13 +267,15 @@ __device__ __forceinline__ void phase_stream(Worker<S>& s, const Params& p, unsi
         const unsigned long long win = atomicMax(p.argmax_key, 0ull);
         const long long tok = (long long)(0xffffffffu - (unsigned)(win & 0xffffffffull));
         if (p.next_token) *p.next_token = tok;
-        const long long at = (long long)p.pos + s.step + 1;
+        const int step = S::kMulti ? gph / num_phases(p.num_layers) : 0;
+        const long long at = (long long)p.pos + step + 1;
         if (p.out_tokens && at < p.out_tokens_len) p.out_tokens[at] = tok;
         *p.argmax_key = 0ull;
         *lm_ticket = 0u;
         __threadfence();
         // the token hand-off to the launch's next step, after the resets it must not overtake
-        st_handoff(reinterpret_cast<uint32_t*>(p.tok_word), make_uint2((unsigned)tok, p.launch_seq + (unsigned)s.step + 1u));
+        if constexpr (S::kMulti)
+          st_handoff(reinterpret_cast<uint32_t*>(p.tok_word), make_uint2((unsigned)tok, p.launch_seq + (unsigned)step + 1u));
       }
     }
   }

@@ -38,6 +38,13 @@ struct ShapeLlama1B {
   static constexpr int QKV_ROWS = (NH + 2 * NKV) * HD;
   static constexpr int QDIM = NH * HD;
   static constexpr int GQA = NH / NKV;
+  static constexpr bool kMulti = false;   // kernel instance for launches of one decode step
+};
+// The same shape, compiled for launches that run several decode steps (the token loop inside the kernel).  A separate
+// instance because the kernel has no register to spare: the few extra values of the multi-step form cost the one-step
+// form 2 % when compiled in.
+struct ShapeLlama1BSteps : ShapeLlama1B {
+  static constexpr bool kMulti = true;
 };
 
 QMK_HD int phase_kind(int ph, int num_layers) {
@@ -103,21 +110,19 @@ struct TileCursor {
   int u0, u1;              // SwiGLU units
   int l0, l1;              // LM head rows
   // position in the stream
-  int ph, kind;            // phase being issued and its kind
-  int first_ph, steps_left;  // multi-step launches: the stream wraps from phase_end to first_ph, steps_left - 1 more times
+  int ph, kind;            // phase being issued (in a launch of several steps: step * num_phases + phase) and its kind
   int left;                // tiles left in that phase
   int sub;                 // down-proj: k-slice of the next tile
   int rows_left;           // rows (O-proj / LM / down) still to be covered, to spot the odd last row
   const unsigned char* p0; // next source (first chunk)
   const unsigned char* p1; // up/gate: gate row
 
-  QMK_HD void init(int g, int nwt, int vocab, int phase_begin, int steps = 1) {
+  QMK_HD void init(int g, int nwt, int vocab, int phase_begin) {
     split_range_u32(S::QKV_ROWS / 2, nwt, g, q0, q1);
     split_range_u32(S::H, nwt, g, r0, r1);
     split_range_u32(S::I, nwt, g, u0, u1);
     split_range_u32((unsigned)vocab, nwt, g, l0, l1);
-    ph = first_ph = phase_begin;
-    steps_left = steps;
+    ph = phase_begin;
     kind = left = sub = rows_left = 0;
     p0 = p1 = nullptr;
   }
@@ -136,14 +141,13 @@ struct TileCursor {
 
   // Position on the first phase >= ph in which this worker streams weights; set its first sources.
   QMK_HD void seek(const StreamBases& w, int num_layers, int phase_end) {
-    for (;;) {
-      if (ph >= phase_end) {
-        if (steps_left <= 1) return;
-        --steps_left;            // the next step of the launch: the same phases again
-        ph = first_ph;
-      }
-      const int layer = ph / kPhasesPerLayer;
-      const int k = layer >= num_layers ? (int)kLmHead : ph - layer * kPhasesPerLayer;
+    // (phase_end may lie beyond one step's phases: a launch of n whole steps streams phases [0, n * num_phases), the
+    // same matrices again in every step)
+    const int np = num_phases(num_layers);
+    while (ph < phase_end) {
+      const int lp = ph < np ? ph : ph % np;
+      const int layer = lp / kPhasesPerLayer;
+      const int k = layer >= num_layers ? (int)kLmHead : lp - layer * kPhasesPerLayer;
       const int n = tiles(k);
       if (n > 0) {
         kind = k;

@@ -56,17 +56,16 @@ __device__ __forceinline__ bool poll_tagged(Worker<S>& s, const Params& p, const
 
 // Steps after the first of a multi-step launch: the token fed to the step is the arg-max of the step before, handed over
 // as one 64-bit word {token id, tag}; every warp polls it (bounded) before it reads its part of the embedding row.
-// Returns -1 when the wait gave up.
-template <class S>
-__device__ __forceinline__ long long poll_token(Worker<S>& s, const Params& p, int ph) {
-  const unsigned want = p.launch_seq + (unsigned)s.step;   // (number of the producing step) + 1
+// Returns -1 when the wait gave up.  A real call with plain arguments: the poll's code and registers stay out of the
+// streaming loop (inlined, with the tensor-memory parking that the other polls do while they wait, it cost the whole
+// kernel 4 %); the wait is a microsecond per step.
+static __device__ __noinline__ long long wait_token(const Params& p, unsigned want, int warp, int ph, int lane) {
   const long long t0 = clock64();
   for (unsigned it = 0;; ++it) {
     const unsigned long long w = __ldcg(p.tok_word);
-    if (it > 0) poll_backoff(s, p, it);
     const bool ok = (unsigned)(w >> 32) == want;
     if (__all_sync(kFullMask, ok)) return (long long)(unsigned)(w & 0xffffffffull);
-    if ((it & 15u) == 15u && poll_give_up(p, t0, ok, (unsigned)(w >> 32), want, s.w, ph, s.lane)) return -1;
+    if ((it & 15u) == 15u && poll_give_up(p, t0, ok, (unsigned)(w >> 32), want, warp, ph, lane)) return -1;
   }
 }
 

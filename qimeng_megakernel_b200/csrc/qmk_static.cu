@@ -208,6 +208,7 @@ extern "C" int qmk_decode_step_static(const qmk_model_desc* d, const qmk_weight_
     if (e != cudaSuccess) return fail(e, "cudaMemsetAsync");
     dev.launch_seq = 0;
   }
+  p.stream_end = p.phase_end;
   p.launch_seq = ++dev.launch_seq;
   p.eps = d->rms_norm_eps;
   p.scale_log2e = d->attn_scale * 1.4426950408889634f;

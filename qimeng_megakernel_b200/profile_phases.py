@@ -1,6 +1,7 @@
 """Runs every phase of one decode step as its own launch and reports time and achieved HBM GB/s per phase.
 
-    python -m qimeng_megakernel_b200.profile_phases [--pos 500] [--reps 20] [--layer 1]
+    python -m qimeng_megakernel_b200.profile_phases [--pos 500] [--reps 20]
+    python -m qimeng_megakernel_b200.profile_phases --one-each     # six launches, one per phase kind: for a profiler
 
 The persistent kernel normally runs all phases in one launch; `qmk_run_phases(mode 0)` launches the same
 device code one phase at a time (stream-ordered, no cross-SM waits), which is what `ncu` needs to attribute
@@ -31,6 +32,9 @@ def main() -> None:
     ap.add_argument("--pos", type=int, default=500)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warm-steps", type=int, default=2, help="full persistent steps before the phase launches")
+    ap.add_argument("--one-each", action="store_true",
+                    help="launch the five phases of layer 1 and the LM head once each, in order, and stop (launches 4..9 of "
+                         "the process with the default two warm steps and the binding launch)")
     args = ap.parse_args()
     cfg = dict(LLAMA_3_2_1B)
     w = synthetic.make_weights(cfg, seed=0, device="cuda", max_positions=max(2048, args.pos + 8))
@@ -46,8 +50,14 @@ def main() -> None:
     # One event pair around the same phase kind of ALL layers, queued back to back: each layer has its
     # own weights (16 x 12.6 MB for the smallest phase), so no launch finds its weights in the 126 MB L2,
     # and the host's launch latency is hidden behind the queue.
-    stream = torch.cuda.current_stream().cuda_stream
     mk.run_phases(g, 0, 1, 0)            # binds the state
+    if args.one_each:
+        for ph in [5 + k for k in range(5)] + [5 * L]:
+            mk.run_phases(g, ph, ph + 1, 0)
+        torch.cuda.synchronize()
+        mk.check_status()
+        print("one launch per phase kind done")
+        return
     for k, name in enumerate(NAMES + ("lm_head",)):
         phs = [5 * L] * 4 if name == "lm_head" else [l * 5 + k for l in range(L)]
         times = []
@@ -55,7 +65,7 @@ def main() -> None:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for ph in phs:
-                mk._lib.qmk_run_phases(mk._handle, args.pos, ph, ph + 1, 0, stream)
+                mk.run_phases(g, ph, ph + 1, 0)
             b.record()
             torch.cuda.synchronize()
             times.append(a.elapsed_time(b) * 1e3 / len(phs))

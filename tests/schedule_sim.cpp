@@ -125,12 +125,13 @@ int run_multi_step(int nsm, int warps, int layers, int vocab, int steps) {
     a.seek(w, layers, nph);
     while (!a.done(nph)) one.push_back(a.next(w, layers, nph));
     TileCursor<S> b;
-    b.init(g, nwt, vocab, 0, steps);
-    b.seek(w, layers, nph);
+    const int end = steps * nph;      // the stream of a launch of `steps` whole steps ends here
+    b.init(g, nwt, vocab, 0);
+    b.seek(w, layers, end);
     size_t n = 0;
-    while (!b.done(nph)) {
+    while (!b.done(end)) {
       if (one.empty()) return fail("a worker without tiles streams in a multi-step launch", g, 0);
-      const Tile t = b.next(w, layers, nph), &r = one[n % one.size()];
+      const Tile t = b.next(w, layers, end), &r = one[n % one.size()];
       if (t.a != r.a || t.b != r.b || t.bytes_a != r.bytes_a) return fail("multi-step stream differs from the repeated step", g, (int)n);
       ++n;
       if (n > one.size() * (size_t)steps) return fail("multi-step stream does not end", g, (int)n);
