@@ -51,12 +51,13 @@ QMKB_HD PhaseDims phase_dims(const BParams& p, int kind, int ne = 0) {
   d.KB = d.K / kBlockK;
   return d;
 }
-// CTAs that share a phase's units: all of them, except for the router's single tile, whose 256 KB are not worth 32
-// partial tiles added onto one accumulator (each CTA then takes at least eight units).
+// CTAs that share a phase's units: all of them; the router's single tile has only K / 64 units and gives one to each of
+// as many CTAs (measured: 37 us per router phase with eight units on each of four CTAs, whose stagers then pay a round
+// trip per pair of units; one unit per CTA is 2-3 % of the whole mixture-of-experts step faster, the 32 partial tiles
+// meeting in the tile's fixed-point accumulator).
 QMKB_HD int phase_ctas(int kind, int U, int G) {
   if (kind != kRouter) return G;
-  const int g = U / 8;
-  return g < 1 ? 1 : (g < G ? g : G);
+  return U < 1 ? 1 : (U < G ? U : G);
 }
 
 // Units [lo, hi) of CTA c out of G, for U units (none for c >= G).

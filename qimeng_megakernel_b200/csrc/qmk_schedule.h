@@ -145,7 +145,8 @@ struct TileCursor {
     // same matrices again in every step)
     const int np = num_phases(num_layers);
     while (ph < phase_end) {
-      const int lp = ph < np ? ph : ph % np;
+      int lp = ph;
+      if constexpr (S::kMulti) lp = ph < np ? ph : ph % np;
       const int layer = lp / kPhasesPerLayer;
       const int k = layer >= num_layers ? (int)kLmHead : lp - layer * kPhasesPerLayer;
       const int n = tiles(k);

@@ -271,6 +271,14 @@ class MegaKernel:
             raise RuntimeError("decode_step needs a bound state: call mk(globs) once first")
         _lib.check(self._lib.qmk_decode_step(self._handle, int(pos), self._stream()), self._handle)
 
+    def run_phases_bound(self, pos: int, phase_begin: int, phase_end: int, mode: int = 0) -> None:
+        """run_phases on the state bound by the last `mk(globs)` / `run_phases(globs, ...)` call, without tensor
+        re-validation (a profiling loop that launches single phases back to back)."""
+        if self._handle is None:
+            raise RuntimeError("run_phases_bound needs a bound state: call run_phases(globs, ...) once first")
+        _lib.check(self._lib.qmk_run_phases(self._handle, int(pos), int(phase_begin), int(phase_end), int(mode),
+                                            self._stream()), self._handle)
+
     def last_expert_count(self) -> int:
         """MoE: distinct experts selected by the last layer's router in the last step (synchronises)."""
         n = C.c_int32()

@@ -65,7 +65,7 @@ def main() -> None:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for ph in phs:
-                mk.run_phases(g, ph, ph + 1, 0)
+                mk.run_phases_bound(args.pos, ph, ph + 1, 0)
             b.record()
             torch.cuda.synchronize()
             times.append(a.elapsed_time(b) * 1e3 / len(phs))

@@ -112,7 +112,7 @@ int run_attn_plan() {
 
 // A launch of several steps: every worker's stream is its one-step stream, repeated, and ends after the last step.
 int run_multi_step(int nsm, int warps, int layers, int vocab, int steps) {
-  using S = ShapeLlama1B;
+  using S = ShapeLlama1BSteps;   // (the cursor of the multi-step kernel instance)
   StreamBases w;
   unsigned char* base = reinterpret_cast<unsigned char*>(uintptr_t(1) << 40);
   w.qkv = base; w.o_proj = base + (size_t(1) << 36); w.up = base + (size_t(2) << 36); w.gate = base + (size_t(3) << 36);
