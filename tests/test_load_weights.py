@@ -11,6 +11,8 @@ import sys
 import pytest
 import torch
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
 
 def write_checkpoint(path, cfg, w, tied, model_type):
     from safetensors.torch import save_file
@@ -90,7 +92,7 @@ def test_synthetic_checkpoint_round_trip(tmp_path, family, tied):
 
 
 def test_agrees_with_the_reference_loader(tmp_path):
-    ref = os.environ.get("QMK_REFERENCE_ROOT", "/root/reference")
+    ref = os.environ.get("QMK_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
     if not os.path.isdir(os.path.join(ref, "qimeng_megakernel")):
         pytest.skip("no reference checkout on this machine")
     if ref not in sys.path:

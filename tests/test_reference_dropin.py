@@ -3,7 +3,7 @@ registry edits applied (integration/enable_b200.py), the reference's `import_dec
 (qimeng_megakernel/models/LLM/registry.py:238-262) resolves to the B200 packages and yields what `_decode_mk`
 (decode.py:600-642) reads: get_mk, call_mk, Globals, the config class and STATIC_MEGAKERNEL, which selects the branch
 that builds no instruction queues and never zeroes a barrier tensor.  Needs an importable reference checkout (found
-through QMK_REFERENCE_ROOT or at /root/reference); skipped elsewhere.  No GPU and no kernel launch."""
+through QMK_REFERENCE_ROOT, else a directory `reference` beside this repository); skipped elsewhere.  No GPU and no kernel launch."""
 import importlib
 import inspect
 import os
@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.fixture(scope="module")
 def reference_registry():
-    ref = os.environ.get("QMK_REFERENCE_ROOT", "/root/reference")
+    ref = os.environ.get("QMK_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
     if not os.path.isdir(os.path.join(ref, "qimeng_megakernel")):
         pytest.skip("no reference checkout on this machine")
     for p in (ref, os.path.join(ROOT, "integration")):
