@@ -555,7 +555,8 @@ static __device__ __noinline__ void ep_exchange(const Ctx& c, int ph, int t, int
       dst[q] = make_float4(exch[e * p.exch_stride + 4 * q], exch[e * p.exch_stride + 4 * q + 1],
                            exch[e * p.exch_stride + 4 * q + 2], exch[e * p.exch_stride + 4 * q + 3]);
   }
-  __threadfence_system();
+  // (no fence per thread: the barrier orders the group's peer stores before the publishing thread's release at system
+  // scope, which is cumulative over what the barrier made visible to it)
   named_bar(kBarEpi, 128);
   if (e < W && e != me) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ep_flag[e] + fidx), "r"(tag) : "memory");

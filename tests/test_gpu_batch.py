@@ -578,6 +578,45 @@ def test_decode_api_batched(small_config, small_weights):
     pre.mk.close()
 
 
+def test_generate_device_on_the_batched_kernel(small_config, small_weights):
+    """qmk_generate_device with three sequences: the batched kernel runs the n steps as n launches; tokens equal the loop of
+    single steps; per-row positions or a token_in that does not alias next_token are refused."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import _lib, mk_kernel, synthetic
+    B, n = 3, 6
+    prompts = synthetic.make_prompts(small_config["vocab_size"], B, 4, seed=5)
+    runs = []
+    for multi in (False, True):
+        g = synthetic.make_globals(small_config, small_weights, kv_seq_len=32, device="cuda:0", batch=B)
+        mk = mk_kernel.get_mk()
+        g.token_in = torch.zeros(B, dtype=torch.int64, device="cuda")
+        g.out_tokens = torch.zeros(B, 32, dtype=torch.int64, device="cuda")
+        for pos in range(4):
+            g.token_in.copy_(prompts[:, pos]); g.position_id = pos
+            mk(g)
+        g.token_in.copy_(g.next_token)
+        g.next_token = g.token_in
+        if multi:
+            mk.generate_device(g, 4, n)
+        else:
+            for i in range(n):
+                g.position_id = 4 + i
+                mk(g)
+        torch.cuda.synchronize()
+        mk.check_status()
+        runs.append(g.out_tokens[:, 5:5 + n].cpu().clone())
+        if multi:
+            g.position_ids = torch.full((B,), 4 + n, dtype=torch.int32, device="cuda")
+            with pytest.raises(_lib.QmkError):
+                mk.generate_device(g, 4 + n, 2)          # per-row positions are advanced by the caller, not here
+            g.position_ids = None
+            g.next_token = torch.zeros(B, dtype=torch.int64, device="cuda")
+            with pytest.raises(_lib.QmkError):
+                mk.generate_device(g, 4 + n, 2)          # the steps could not feed themselves
+        mk.close()
+    assert torch.equal(runs[0], runs[1])
+
+
 @pytest.mark.parametrize("batch,prompt_len", [(3, 20), (1, 70), (5, 16)])
 def test_fused_prefill_matches_token_by_token(small_config, small_weights, batch, prompt_len):
     """Prefill with the rows of a launch being consecutive positions of a sequence (kv_slots): the KV cache it leaves,
