@@ -451,7 +451,10 @@ def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_
             "e2e": {"value": world * B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
             "gpu_launches": launches + K + 1,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": step_bytes,
+                         "traffic": (BATCHED_TRAFFIC_RATIO[(model, B)][0] * step_bytes
+                                     if (model, B) in BATCHED_TRAFFIC_RATIO and ep == 1 and tp == 1 else None),
+                         "traffic_source": BATCHED_TRAFFIC_RATIO.get((model, B), (None, None))[1] if ep == 1 and tp == 1 else None,
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": step_bytes,
                          "kernel": "qmk_batch_kernel (one persistent launch per decode step)"},
             "clocks": clocks, "cpu_baseline": None,
         }
@@ -465,6 +468,11 @@ def run_batched(model: str, B: int, K: int, W: int, layers: int, D: Dist, local_
 
 
 SECONDARY = (("llama-3.2-1b", 32), ("qwen3-0.6b", 16), ("olmoe-1b-7b", 32))
+# DRAM traffic / algorithmic bytes of one qmk_batch_kernel launch where an ncu capture exists (profiles/): the capture of
+# the OLMoE case held 3 of the 16 layers (a few GB on the device); traffic grows with the layers like the algorithmic
+# bytes do, so the ratio is applied to the full step's bytes.
+BATCHED_TRAFFIC_RATIO = {("llama-3.2-1b", 8): (1.014, "profiles/qmk_batch_kernel_step_llama1b_b8.md"),
+                         ("olmoe-1b-7b", 32): (1.006, "profiles/qmk_batch_kernel_step_olmoe_b32_3layers.md (3-layer capture, scaled by bytes)")}
 
 
 def main() -> None:
