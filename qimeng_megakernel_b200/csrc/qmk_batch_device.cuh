@@ -952,11 +952,18 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const int t = u / d.KB, kb_lo = u - t * d.KB;
     const int u_end = min(hi, (t + 1) * d.KB);
     const bool full = kb_lo == 0 && u_end == (t + 1) * d.KB;
+    // A tile that is split over several CTAs is finished by the CTA that owns its FIRST unit: that CTA's range ends inside
+    // the tile, so it reaches the tile last, when the others (whose ranges start with the tile's later units) have long
+    // added their parts.  The others add their partial tile to the tile's fixed-point accumulator at L2 and count
+    // themselves in with one release (no ticket to wait for); the owner keeps its own part in shared memory, waits for
+    // the count, takes the sum out (leaving zero for the accumulator's next user, a phase later) and adds its own part in
+    // the same fixed point: the result is the integer sum of all parts, whatever the order.
+    const bool owner = kb_lo == 0 && !full;
     const unsigned buf = sg & 1u;
     const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
     if (e == 0 && u == lo) trace_put(p, ph, 1);
-    // accumulator of a tile that is split over several CTAs: the slot of the CTA that owns the tile's first unit
-    // (a CTA owns the first unit of at most one split tile, so the slot is the tile's alone)
+    // accumulator of a split tile: the slot of the owner (a CTA owns the first unit of at most one split tile, so the
+    // slot is the tile's alone)
     const int c_first = unit_owner(U, G, t * d.KB);
     long long* slot = p.ws + (size_t)c_first * (size_t)(kTileRows * p.Bpad);
     if (ok) {
@@ -966,7 +973,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
         uint32_t v[16];
         tmem_ld16(v, tmem + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)p.Bpad + ch * 16);
         tmem_wait_ld();
-        if (full) {
+        if (full || owner) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) exch[r * p.exch_stride + ch * 16 + j] = __uint_as_float(v[j]);
         } else {
@@ -978,21 +985,22 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
       mbar_arrive1(c.acc_empty(buf));
     }
     ++sg;
-    // One thread decides for the group whether this CTA finishes the tile: a full segment always does; a partial one
-    // has added its tile to the tile's accumulator at L2, takes a ticket, and the last of the tile's segments to
-    // arrive reads the sum (and leaves the accumulator zeroed for its next user, a phase later).
-    // (no fence per thread: the barrier orders the group's additions before thread 0's acquire-release ticket, whose
-    // release is cumulative over what the barrier made visible to it)
+    // (no fence per thread: the barrier orders the group's additions before thread 0's release on the tile's count,
+    // which is cumulative over what the barrier made visible to it)
     named_bar(kBarEpi, 128);
     if (e == 0) {
       unsigned fin = 0u;
       if (ok && !c.aborted()) {
         if (full) {
           fin = 1u;
+        } else if (owner) {
+          const unsigned others = (unsigned)tile_segments(U, G, d.KB, t) - 1u;
+          if (counter_wait(c, p.tile_tickets + t, others, ph)) {
+            p.tile_tickets[t] = 0u;
+            fin = 1u;
+          }
         } else {
-          const unsigned old = atom_add_acq_rel_gpu(p.tile_tickets + t, 1u);
-          fin = old + 1u == (unsigned)tile_segments(U, G, d.KB, t) ? 1u : 0u;
-          if (fin) p.tile_tickets[t] = 0u;
+          red_release_gpu_add(p.tile_tickets + t, 1u);
         }
       }
       c.ctl[kCFlagEpi] = fin;
@@ -1000,7 +1008,6 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     named_bar(kBarEpi, 128);
     const bool run = c.ctl[kCFlagEpi] != 0u;
     if (run && !full) {
-      __threadfence();
       float* o = exch + r * p.exch_stride;
 #pragma unroll 1
       for (int ch = 0; ch < nchunk; ++ch) {
@@ -1008,7 +1015,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
 #pragma unroll
         for (int j = 0; j < 16; ++j) x[j] = exch_zero_s64(slot + (size_t)(ch * 16 + j) * kTileRows + r);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[ch * 16 + j] = (float)((double)x[j] * kFixInv);
+        for (int j = 0; j < 16; ++j) o[ch * 16 + j] = (float)((double)(x[j] + to_fixed(o[ch * 16 + j])) * kFixInv);
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)

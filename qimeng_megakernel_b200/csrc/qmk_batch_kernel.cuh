@@ -11,10 +11,12 @@
 // units of a phase, 128 x 64 weights = 16 KiB each, are dealt to the CTAs as equal contiguous ranges,
 // so every SM streams the same number of bytes whatever the matrix shape.  A maximal run of units of
 // one row tile is a SEGMENT, accumulated in tensor memory.  A segment that covers the whole K is
-// finished by its CTA; otherwise the partial tile is added to the tile's fixed-point accumulator at L2
-// (64-bit integer reductions, nothing returned: the sum does not depend on the order of arrival, so a
-// step gives the same bits every time) and the CTA that arrives last at the tile's ticket takes the sum
-// out and runs the epilogue.  The reference splits K in the
+// finished by its CTA.  A tile that is split over several CTAs is finished by the CTA that owns its first
+// unit (its range ends inside the tile, so it gets there last): the others add their partial tiles to the
+// tile's fixed-point accumulator at L2 (64-bit integer reductions, nothing returned) and count themselves
+// in with one release; the owner waits for the count, takes the sum out and adds its own part in the same
+// fixed point, so the result does not depend on the order of arrival and a step gives the same bits every
+// time.  The reference splits K in the
 // down-projection only and adds the partials with bf16 compare-and-swap in arrival order
 // (qimeng_megakernel/models/LLM/llama/llama3_2__1b/A100/single_batch/decode_kernel/down_proj_gemv_residual.cu:39-52).
 //
