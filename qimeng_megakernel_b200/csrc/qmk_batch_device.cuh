@@ -318,8 +318,11 @@ __device__ __forceinline__ bool phase_dependency(const Ctx& c, int ph, bool& nee
 // old completion of a stage's mbarrier (same parity) for the one it waits for.
 template <int NPL, int D>
 __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDims& d, int lo, int hi, int st, unsigned n,
-                                            const uint16_t* src, const uint16_t* gain, const float* rs,
+                                            const uint16_t* src, const uint16_t* gain, float* rs,
                                             unsigned char* img = nullptr) {
+  // gain != nullptr: a normalised phase.  The rsqrt factors rs[Bpad] are computed here, by the threads st < Bpad from the
+  // previous phase's partial sums of squares, AFTER every warp has issued the loads of its first group: one L2 round
+  // trip for both.  All 128 stager threads call this function then (it contains one barrier of the group).
   // img != nullptr (router phase): the staged block of every unit is also stored, in the same swizzled layout, as
   // k-block u % KB of a global image [KB][Bpad * 128 bytes] that the expert up/gate phase fetches with bulk copies
   static_assert(4 * D + D - 1 < 2 * kMinStages, "a stager warp could run two ring laps ahead");
@@ -329,6 +332,22 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
   const int row0 = lane >> 3;         // first batch row of this lane (then +4, +8, ...)
   long long w_slot = 0, w_fill = 0;
   const bool tr = (kTraceOn && p.trace != nullptr);
+  bool need_rs = gain != nullptr;
+  auto compute_rs = [&]() {
+    if (st < p.Bpad) {
+      float tot = 0.f;
+      const int nt = (p.H + kTileRows - 1) / kTileRows;
+      for (int t0 = 0; t0 < nt; t0 += 16) {   // sixteen partial sums per round trip, added in tile order
+        float x[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = t0 + j < nt ? ldcg_f32(p.ss + (t0 + j) * kMaxBatch + st) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) tot += x[j];
+      }
+      rs[st] = rsqrtf(tot / (float)p.H + p.eps);
+    }
+    named_bar(kBarStg, 128);
+  };
 #pragma unroll 1
   for (int base = lo + sw * D; base < hi; base += 4 * D) {
     uint4 v[D][NPL];
@@ -346,6 +365,10 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
         v[j][i] = make_uint4(0, 0, 0, 0);
         if (u < hi && r < p.B) v[j][i] = ldcg_u4(src + (size_t)r * d.K + k0);
       }
+    }
+    if (need_rs) {   // (first group of this warp: its loads are in flight)
+      need_rs = false;
+      compute_rs();
     }
 #pragma unroll
     for (int j = 0; j < D; ++j) {
@@ -384,6 +407,7 @@ __device__ __forceinline__ void stage_units(const Ctx& c, int ph, const PhaseDim
       if (tr) w_fill += clock64() - t1;
     }
   }
+  if (need_rs) compute_rs();   // a warp without units in this phase still takes part in the barrier
   if (st == 0) {
     trace_val(p, ph, 6, (unsigned long long)w_slot);
     trace_val(p, ph, 7, (unsigned long long)w_fill);
@@ -454,7 +478,7 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   const bool pre = normed && kind != kRouter && p.H % kBlockK == 0 &&
                    (kind == kLmHead ? (d.T * d.KB) / (int)gridDim.x >= p.pre_lm_units : p.Bpad >= p.pre_bpad);   // (the same on every CTA)
   float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
-  if (normed) {
+  if (pre) {   // the pre-pass needs the rsqrt factors up front (the per-unit path computes them behind its first loads)
     if (st < p.Bpad) {
       float tot = 0.f;
       const int nt = (p.H + kTileRows - 1) / kTileRows;
@@ -501,19 +525,19 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
     if (st == 0) counter_wait(c, p.img_done + ph, (unsigned)KBx, ph);
     named_bar(kBarStg, 128);
   }
-  if (hi > lo) {
-    const uint16_t* gn = normed ? gain : nullptr;
-    if (expert || plain_img || pre) {
+  const uint16_t* gn = normed ? gain : nullptr;
+  if (expert || plain_img || pre) {
+    if (hi > lo) {
       const unsigned char* img = kind == kEDown ? p.eimg : kind == kOproj ? p.aimg : kind == kDown ? p.simg : p.ximg;
       stage_images(c, ph, d, lo, hi, st, n, img);
-    } else {
-      unsigned char* img = kind == kRouter ? p.ximg : nullptr;
-      switch (p.Bpad) {
-        case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
-        case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
-        case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
-        default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
-      }
+    }
+  } else if (hi > lo || gn != nullptr) {   // (a normalised phase: every stager thread takes part in the rsqrt barrier)
+    unsigned char* img = kind == kRouter ? p.ximg : nullptr;
+    switch (p.Bpad) {
+      case 16: stage_units<4, 2>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
+      case 32: stage_units<8, 2>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
+      case 48: stage_units<12, 1>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
+      default: stage_units<16, 1>(c, ph, d, lo, hi, st, n, src, gn, rs, img); break;
     }
   }
   n += (unsigned)(hi - lo);
