@@ -478,49 +478,60 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
   const bool pre = normed && kind != kRouter && p.H % kBlockK == 0 &&
                    (kind == kLmHead ? (d.T * d.KB) / (int)gridDim.x >= p.pre_lm_units : p.Bpad >= p.pre_bpad);   // (the same on every CTA)
   float* rs = reinterpret_cast<float*>(c.smem + Smem::kOffRs);
-  if (pre) {   // the pre-pass needs the rsqrt factors up front (the per-unit path computes them behind its first loads)
-    if (st < p.Bpad) {
-      float tot = 0.f;
-      const int nt = (p.H + kTileRows - 1) / kTileRows;
-      for (int t0 = 0; t0 < nt; t0 += 16) {   // sixteen partial sums per round trip, added in tile order
-        float v[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = t0 + j < nt ? ldcg_f32(p.ss + (t0 + j) * kMaxBatch + st) : 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) tot += v[j];
-      }
-      rs[st] = rsqrtf(tot / (float)p.H + p.eps);
-    }
-    named_bar(kBarStg, 128);
-  }
   const uint16_t* src = kind == kOproj ? p.attn_out : kind == kDown ? p.silu_out : p.hidden;
   const uint16_t* gain = kind == kQkv ? p.attn_norm + (size_t)layer * p.H
                        : kind == kLmHead ? p.lm_norm : p.mlp_norm + (size_t)layer * p.H;
   if (pre) {
-    // (every CTA takes part, also one without units in this phase: the counter's target is the number of k-blocks)
+    // CTA i normalises k-block i (only these CTAs need the rsqrt factors, computed while the block's rows are in flight);
+    // every CTA, also one without units in this phase, then waits for all k-blocks.
     const int chunk = st & 7;
+    bool need_rs = true;
     for (int kb = (int)blockIdx.x; kb < KBx; kb += (int)gridDim.x) {
       const int k0 = kb * kBlockK + chunk * 8;
       const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gain + k0));
       const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
-      for (int r = st >> 3; r < p.Bpad; r += 16) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < p.B) {
-          v = ldcg_u4(src + (size_t)r * p.H + k0);
-          const float f = rs[r];
-          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+      uint4 v[kMaxBatch / 16];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float a = bf16_round(bf_lo(w[q]) * f) * bf_lo(gw[q]);
-            const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
-            w[q] = pack_bf16x2(a, b);
-          }
-        }
-        *reinterpret_cast<uint4*>(p.ximg + img_piece(p.Bpad, r, k0)) = v;
+      for (int i = 0; i < kMaxBatch / 16; ++i) {
+        const int r = (st >> 3) + 16 * i;
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (r < p.B) v[i] = ldcg_u4(src + (size_t)r * p.H + k0);
       }
-      __threadfence();
-      named_bar(kBarStg, 128);
-      if (st == 0) atom_add_acq_rel_gpu(p.img_done + ph, 1u);
+      if (need_rs) {
+        need_rs = false;
+        if (st < p.Bpad) {
+          float tot = 0.f;
+          const int nt = (p.H + kTileRows - 1) / kTileRows;
+          for (int t0 = 0; t0 < nt; t0 += 16) {   // sixteen partial sums per round trip, added in tile order
+            float x[16];
+#pragma unroll
+            for (int j2 = 0; j2 < 16; ++j2) x[j2] = t0 + j2 < nt ? ldcg_f32(p.ss + (t0 + j2) * kMaxBatch + st) : 0.f;
+#pragma unroll
+            for (int j2 = 0; j2 < 16; ++j2) tot += x[j2];
+          }
+          rs[st] = rsqrtf(tot / (float)p.H + p.eps);
+        }
+        named_bar(kBarStg, 128);
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxBatch / 16; ++i) {
+        const int r = (st >> 3) + 16 * i;
+        if (r < p.Bpad) {
+          if (r < p.B) {
+            const float f = rs[r];
+            uint32_t* w = reinterpret_cast<uint32_t*>(&v[i]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float a = bf16_round(bf_lo(w[q]) * f) * bf_lo(gw[q]);
+              const float b = bf16_round(bf_hi(w[q]) * f) * bf_hi(gw[q]);
+              w[q] = pack_bf16x2(a, b);
+            }
+          }
+          *reinterpret_cast<uint4*>(p.ximg + img_piece(p.Bpad, r, k0)) = v[i];
+        }
+      }
+      named_bar(kBarStg, 128);   // the group's stores, then one release on the count (cumulative over the barrier)
+      if (st == 0) red_release_gpu_add(p.img_done + ph, 1u);
     }
     if (st == 0) counter_wait(c, p.img_done + ph, (unsigned)KBx, ph);
     named_bar(kBarStg, 128);
