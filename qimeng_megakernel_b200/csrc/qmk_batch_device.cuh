@@ -1218,7 +1218,8 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
         if (dl == 0) *reinterpret_cast<float2*>(rec + g * (HD + 2) + HD) = make_float2(m[g], l[g]);
       }
     }
-    __threadfence();
+    // (no fence per lane: the warp barrier orders the lanes' record stores before lane 0's acquire-release ticket, and
+    // the second one orders lane 0's acquire before the other lanes' reads of the records)
     __syncwarp();
     unsigned last = 0u;
     if (lane == 0) {
@@ -1228,7 +1229,7 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
     }
     last = __shfl_sync(kFullMask, last, 0);
     if (!last) continue;
-    __threadfence();
+    __syncwarp();
     // merge the nsplit records of this (sequence, kv head): every lane takes (head, 8 dims) pieces and folds the
     // records in split order (loads of four records in flight)
     const float* recs = p.attn_part + (size_t)(sq * nch) * REC;
@@ -1285,8 +1286,7 @@ __device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
       else attention_items<128, 1>(c, layer, aw);
     }
   }
-  __threadfence();
-  named_bar(kBarAttn, 256);
+  named_bar(kBarAttn, 256);   // the workers' stores, then one release on the phase counter
   if (aw == 0 && c.lane == 0 && !c.aborted()) {
     red_release_gpu_add(p.phase_done + 1 + ph, 1u);
     trace_put(p, ph, 5);
