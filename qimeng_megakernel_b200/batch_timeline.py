@@ -97,6 +97,13 @@ def main() -> None:
               f"stager {m[6] / 1e3:6.2f} {m[7] / 1e3:6.2f}  "
               f"| {nbytes / 1e6:9.2f} MB -> {nbytes / float(m[0]) :8.1f} GB/s  (phase total {float(a[:, 0].sum()) / 1e3:8.1f} us)")
     print(f"step total {total / 1e3:.1f} us")
+    k = names.index("attn")
+    loop = torch.stack([t[:, l * ppl + k, 3] for l in range(L)]).mean(0) / ghz / 1e3     # us per CTA (warp 0's last item)
+    keys = torch.stack([t[:, l * ppl + k, 4] for l in range(L)]).mean(0)
+    busy = loop > 0
+    if bool(busy.any()):
+        print(f"# attention, warp 0 of every CTA with an item: key loop {float(loop[busy].mean()):.2f} us for {float(keys[busy].mean()):.0f} keys "
+              f"(max {float(loop[busy].max()):.2f} us); the rest of the phase's span is the dependency, the records, the ticket and the merge")
     if args.detail:
         ph = ppl + names.index(args.detail) if args.detail != "lm_head" else ppl * L
         prev = float(t[:, ph - 1, 5].max())

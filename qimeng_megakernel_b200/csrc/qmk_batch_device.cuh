@@ -1063,13 +1063,50 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
 // ------------------------------------------------------------------------------------------------
 // attention: eight workers per CTA, one (sequence, kv head, key range) item per warp at a time
 // ------------------------------------------------------------------------------------------------
+// The key loop runs on the tensor pipe (mma.sync; a warp-level product of 16 x 8 tiles is the right size for one
+// query row of GQ <= 8 heads against a block of keys).  g = lane / 4, t = lane % 4.
+//   scores  S[head][key] = q . k : m16n8k16 bf16, A = q (row = query head of the group; rows past the group and rows
+//     8..15 are zero), B = K.  n-tile j holds keys 8j..8j+7 (column g = key 8j + g).  The contraction index may be
+//     permuted freely as long as q and K agree, so lane (g, t) takes the 16-byte pieces t, 4 + t, 8 + t, ... of its
+//     key's row and the same pieces of q: every piece feeds two k-steps (words x,y and z,w).
+//     Result: lane (g, t) holds S[head g][keys 8j + 2t, 8j + 2t + 1].
+//   output  O[head][dim] = sum_key P V : m16n8k8 tf32 (P rounded to tf32, the sum l taken over the same rounded values;
+//     V is bf16 and exact), A = P, B = V.  k-step ks contracts keys 8ks..8ks+7 in the order (k = t -> key 8ks + 2t,
+//     k = t + 4 -> key 8ks + 2t + 1): the probabilities the lane already holds.  n-tile jn column g is dim
+//     (HD / 8) g + jn, so lane (g, t) loads dims (HD / 8) g .. + HD / 8 of keys 8ks + 2t and 8ks + 2t + 1.
+//     Result: lane (g, t) holds O[head g][dims (HD / 4) t + jn] (c0 of n-tile jn) and [(HD / 4) t + HD / 8 + jn] (c1).
+// A block is 32 keys at head_dim 64 (16 row pieces of K and 16 of V per lane) and 8 keys at 128 (4 and 4).  The K pieces
+// of the next block are requested as soon as the scores of this one exist, its V pieces after the P V products.
+__device__ __forceinline__ void mma_qk(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_pv(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
 template <int HD, int GQ>
-__device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw) {
+__device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw, int trace_ph) {
   const BParams& p = *c.p;
-  constexpr int LPR = HD / 8;          // lanes per K/V row (16 bytes each)
-  constexpr int KPL = 32 / LPR;        // keys per load instruction
+  static_assert(HD == 64 || HD == 128, "row pieces are laid out for head_dim 64 and 128");
+  static_assert(GQ <= 8, "one mma row per query head of the group");
+  constexpr int LPR = HD / 8;          // 16-byte pieces per K/V row
+  constexpr int QP = HD / 32;          // K pieces per key per lane (two k-steps each)
+  constexpr int VP = HD / 64;          // V pieces per key per lane
+  constexpr int NT = HD == 64 ? 4 : 1; // n-tiles (8 keys each) per block (measured: two n-tiles at head_dim 128 spill)
+  constexpr int BK = NT * 8;           // keys per block
+  constexpr int NJ = HD / 8;           // n-tiles of the output
+  constexpr int DPT = HD / 4;          // output dims per lane
   const int lane = c.lane;
-  const int sub = lane / LPR, dl = lane % LPR;
+  const int g = lane >> 2, t = lane & 3;
   const int* pos_s = reinterpret_cast<const int*>(c.smem + Smem::kOffPos);
   const int* act_s = reinterpret_cast<const int*>(c.smem + Smem::kOffAct);
   const int* slot_s = reinterpret_cast<const int*>(c.smem + Smem::kOffSlot);
@@ -1097,126 +1134,123 @@ __device__ __forceinline__ void attention_items(const Ctx& c, int layer, int aw)
     }
     if (ch >= nsplit) continue;
     const int k_lo = ch * ck, k_hi = min(T, k_lo + ck);
-    float q[GQ][8], acc[GQ][8], m[GQ], l[GQ];
+    // q pieces of head g: the same pieces of the row as the lane's K pieces
+    uint4 q[QP];
 #pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      const uint4 qv = ldcg_u4(p.q_post_rope + (size_t)b * p.QDIM + (size_t)(kvh * GQ + g) * HD + dl * 8);
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(&qv);
+    for (int h = 0; h < QP; ++h) q[h] = make_uint4(0u, 0u, 0u, 0u);
+    if (g < GQ) {
+      const uint16_t* qrow = p.q_post_rope + (size_t)b * p.QDIM + (size_t)(kvh * GQ + g) * HD;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        q[g][2 * j] = bf_lo(w[j]) * p.scale_log2e;
-        q[g][2 * j + 1] = bf_hi(w[j]) * p.scale_log2e;
-      }
-      m[g] = -INFINITY;
-      l[g] = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+      for (int h = 0; h < QP; ++h) q[h] = ldcg_u4(qrow + (4 * h + t) * 8);
     }
-    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)slot_s[b] * p.kv_batch_stride + (size_t)kvh * HD + dl * 8;
-    // Keys are taken in half-blocks of NLD row pieces per lane (16 keys at head_dim 64, 8 at 128), double-buffered in
-    // registers: the loads of the next half-block are in flight while this one is multiplied.
-    constexpr int NLD = 4;
-    constexpr int KBK = NLD * KPL;
-    auto load_block = [&](uint4 (&kk)[NLD], uint4 (&vv)[NLD], int ks) {
+    const size_t base = (size_t)layer * p.kv_layer_stride + (size_t)slot_s[b] * p.kv_batch_stride + (size_t)kvh * HD;
+    // rows past the end of the range are clamped to its last row (their probability is 0)
+    uint4 kk[NT][QP], vv[NT][2][VP];
+    auto load_k = [&](int kb) {
 #pragma unroll
-      for (int i = 0; i < NLD; ++i) {
-        const int k = ks + i * KPL + sub;
-        kk[i] = k < k_hi ? ldcg_u4(p.k_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
-      }
+      for (int j = 0; j < NT; ++j) {
+        const uint16_t* row = p.k_cache + base + (size_t)min(kb + 8 * j + g, k_hi - 1) * p.kv_seq_stride;
 #pragma unroll
-      for (int i = 0; i < NLD; ++i) {
-        const int k = ks + i * KPL + sub;
-        vv[i] = k < k_hi ? ldcg_u4(p.v_cache + base + (size_t)k * p.kv_seq_stride) : make_uint4(0, 0, 0, 0);
+        for (int h = 0; h < QP; ++h) kk[j][h] = ldcg_u4(row + (4 * h + t) * 8);
       }
     };
-    auto use_block = [&](const uint4 (&kk)[NLD], const uint4 (&vv)[NLD], int ks) {
+    auto load_v = [&](int kb) {
 #pragma unroll
-      for (int i = 0; i < NLD; ++i) {
-        const bool valid = ks + i * KPL + sub < k_hi;
-        const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kk[i]);
-        const uint32_t* vw = reinterpret_cast<const uint32_t*>(&vv[i]);
-        float kf[8], vf[8];
+      for (int ks = 0; ks < NT; ++ks)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          kf[2 * j] = bf_lo(kw[j]); kf[2 * j + 1] = bf_hi(kw[j]);
-          vf[2 * j] = bf_lo(vw[j]); vf[2 * j + 1] = bf_hi(vw[j]);
+        for (int e = 0; e < 2; ++e) {
+          const uint16_t* row = p.v_cache + base + (size_t)min(kb + 8 * ks + 2 * t + e, k_hi - 1) * p.kv_seq_stride;
+#pragma unroll
+          for (int h = 0; h < VP; ++h) vv[ks][e][h] = ldcg_u4(row + g * LPR + h * 8);
         }
-#pragma unroll
-        for (int g = 0; g < GQ; ++g) {
-          float s = 0.f;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) s += q[g][j] * kf[j];
-#pragma unroll
-          for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(kFullMask, s, o);
-          if (valid) {
-            const float mn = fmaxf(m[g], s);
-            const float corr = exp2f(m[g] - mn);     // 0 when m was -inf
-            const float pe = exp2f(s - mn);
-            l[g] = l[g] * corr + pe;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pe * vf[j];
-            m[g] = mn;
-          }
-        }
-      }
     };
-    uint4 ka[NLD], va[NLD], kb2[NLD], vb2[NLD];
-    load_block(ka, va, k_lo);
+    float m = -INFINITY, l = 0.f, o0[NJ], o1[NJ];
+#pragma unroll
+    for (int i = 0; i < NJ; ++i) o0[i] = o1[i] = 0.f;
+    const long long tq0 = (kTraceOn && p.trace != nullptr) ? clock64() : 0;
+    load_k(k_lo);
+    load_v(k_lo);
 #pragma unroll 1
-    for (int k0 = k_lo; k0 < k_hi; k0 += 2 * KBK) {
-      load_block(kb2, vb2, k0 + KBK);          // (past the end: nothing is loaded, nothing is used)
-      use_block(ka, va, k0);
-      load_block(ka, va, k0 + 2 * KBK);
-      use_block(kb2, vb2, k0 + KBK);
-    }
-    // merge the KPL key sub-streams (lanes with equal dl)
+    for (int kb = k_lo; kb < k_hi; kb += BK) {
+      float sc0[NT], sc1[NT];
+      float bmax = -INFINITY;
 #pragma unroll
-    for (int o = LPR; o < 32; o <<= 1) {
+      for (int j = 0; j < NT; ++j) {
+        float cc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        const float mo = __shfl_xor_sync(kFullMask, m[g], o);
-        const float lo_ = __shfl_xor_sync(kFullMask, l[g], o);
-        const float mn = fmaxf(m[g], mo);
-        const float ca = mn == -INFINITY ? 0.f : exp2f(m[g] - mn);
-        const float cb = mn == -INFINITY ? 0.f : exp2f(mo - mn);
-        l[g] = l[g] * ca + lo_ * cb;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float ao = __shfl_xor_sync(kFullMask, acc[g][j], o);
-          acc[g][j] = acc[g][j] * ca + ao * cb;
+        for (int h = 0; h < QP; ++h) {
+          mma_qk(cc, q[h].x, q[h].y, kk[j][h].x, kk[j][h].y);
+          mma_qk(cc, q[h].z, q[h].w, kk[j][h].z, kk[j][h].w);
         }
-        m[g] = mn;
+        const int key = kb + 8 * j + 2 * t;
+        sc0[j] = key < k_hi ? cc[0] * p.scale_log2e : -INFINITY;
+        sc1[j] = key + 1 < k_hi ? cc[1] * p.scale_log2e : -INFINITY;
+        bmax = fmaxf(bmax, fmaxf(sc0[j], sc1[j]));
       }
-    }
-    if (nsplit == 1) {
-      if (sub == 0) {
+      if (kb + BK < k_hi) load_k(kb + BK);
+      bmax = fmaxf(bmax, __shfl_xor_sync(kFullMask, bmax, 1));
+      bmax = fmaxf(bmax, __shfl_xor_sync(kFullMask, bmax, 2));
+      const float m_new = fmaxf(m, bmax);          // finite: key kb of the block is always valid
+      const float corr = exp2f(m - m_new);
+      m = m_new;
+      l *= corr;
 #pragma unroll
-        for (int g = 0; g < GQ; ++g) {
-          const float inv = 1.0f / l[g];
+      for (int i = 0; i < NJ; ++i) {
+        o0[i] *= corr;
+        o1[i] *= corr;
+      }
+#pragma unroll
+      for (int ks = 0; ks < NT; ++ks) {
+        const uint32_t a0 = (__float_as_uint(exp2f(sc0[ks] - m_new)) + 0x1000u) & 0xffffe000u;
+        const uint32_t a2 = (__float_as_uint(exp2f(sc1[ks] - m_new)) + 0x1000u) & 0xffffe000u;
+        l += __uint_as_float(a0) + __uint_as_float(a2);
+#pragma unroll
+        for (int jn = 0; jn < NJ; ++jn) {
+          const uint32_t wa = word_of(vv[ks][0][jn >> 3], (jn >> 1) & 3), wb = word_of(vv[ks][1][jn >> 3], (jn >> 1) & 3);
+          const uint32_t b0 = (jn & 1) ? (wa & 0xffff0000u) : (wa << 16);
+          const uint32_t b1 = (jn & 1) ? (wb & 0xffff0000u) : (wb << 16);
+          float cc[4] = {o0[jn], o1[jn], 0.f, 0.f};
+          mma_pv(cc, a0, a2, b0, b1);
+          o0[jn] = cc[0];
+          o1[jn] = cc[1];
+        }
+      }
+      if (kb + BK < k_hi) load_v(kb + BK);
+    }
+    l += __shfl_xor_sync(kFullMask, l, 1);
+    l += __shfl_xor_sync(kFullMask, l, 2);
+    if (kTraceOn && p.trace != nullptr && aw == 0 && lane == 0) {   // timeline: cycles of this warp's key loop, keys it walked
+      trace_val(p, trace_ph, 3, (unsigned long long)(clock64() - tq0));
+      trace_val(p, trace_ph, 4, (unsigned long long)(k_hi - k_lo));
+    }
+    // lane (g, t) with g < GQ now holds dims DPT t .. DPT t + DPT of head g: o0 the first NJ of them, o1 the rest
+    if (nsplit == 1) {
+      if (g < GQ) {
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int i = 0; i < DPT / 8; ++i) {
+          const float* src = i < NJ / 8 ? o0 + i * 8 : o1 + (i - NJ / 8) * 8;
           uint4 o4;
-          o4.x = pack_bf16x2(acc[g][0] * inv, acc[g][1] * inv);
-          o4.y = pack_bf16x2(acc[g][2] * inv, acc[g][3] * inv);
-          o4.z = pack_bf16x2(acc[g][4] * inv, acc[g][5] * inv);
-          o4.w = pack_bf16x2(acc[g][6] * inv, acc[g][7] * inv);
-          *reinterpret_cast<uint4*>(outp + g * HD + dl * 8) = o4;
-          *reinterpret_cast<uint4*>(p.aimg + img_piece(p.Bpad, b, (kvh * GQ + g) * HD + dl * 8)) = o4;
+          o4.x = pack_bf16x2(src[0] * inv, src[1] * inv);
+          o4.y = pack_bf16x2(src[2] * inv, src[3] * inv);
+          o4.z = pack_bf16x2(src[4] * inv, src[5] * inv);
+          o4.w = pack_bf16x2(src[6] * inv, src[7] * inv);
+          *reinterpret_cast<uint4*>(outp + g * HD + DPT * t + i * 8) = o4;
+          *reinterpret_cast<uint4*>(p.aimg + img_piece(p.Bpad, b, (kvh * GQ + g) * HD + DPT * t + i * 8)) = o4;
         }
       }
       continue;
     }
     float* rec = p.attn_part + (size_t)item * REC;
-    if (sub == 0) {
+    if (g < GQ) {
+      // (HD + 2) * 4 bytes per head record keeps 8-byte alignment only: write as float2 pairs
+      float2* d2 = reinterpret_cast<float2*>(rec + g * (HD + 2) + DPT * t);
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        float4* dst = reinterpret_cast<float4*>(rec + g * (HD + 2) + dl * 8);
-        // (HD + 2) * 4 bytes per head record keeps 8-byte alignment only: write as float2 pairs
-        float2* d2 = reinterpret_cast<float2*>(dst);
-        d2[0] = make_float2(acc[g][0], acc[g][1]);
-        d2[1] = make_float2(acc[g][2], acc[g][3]);
-        d2[2] = make_float2(acc[g][4], acc[g][5]);
-        d2[3] = make_float2(acc[g][6], acc[g][7]);
-        if (dl == 0) *reinterpret_cast<float2*>(rec + g * (HD + 2) + HD) = make_float2(m[g], l[g]);
+      for (int i = 0; i < NJ / 2; ++i) {
+        d2[i] = make_float2(o0[2 * i], o0[2 * i + 1]);
+        d2[NJ / 2 + i] = make_float2(o1[2 * i], o1[2 * i + 1]);
       }
+      if (t == 0) *reinterpret_cast<float2*>(rec + g * (HD + 2) + HD) = make_float2(m, l);
     }
     // (no fence per lane: the warp barrier orders the lanes' record stores before lane 0's acquire-release ticket, and
     // the second one orders lane 0's acquire before the other lanes' reads of the records)
@@ -1277,13 +1311,13 @@ __device__ __forceinline__ void attention_phase(const Ctx& c, int ph, int aw) {
   if (c.ctl[kCFlagAttn] != 0u) {
     const int layer = phase_layer(p, ph), gq = p.NH / p.NKV;
     if (p.HD == 64) {
-      if (gq == 4) attention_items<64, 4>(c, layer, aw);
-      else if (gq == 2) attention_items<64, 2>(c, layer, aw);
-      else attention_items<64, 1>(c, layer, aw);
+      if (gq == 4) attention_items<64, 4>(c, layer, aw, ph);
+      else if (gq == 2) attention_items<64, 2>(c, layer, aw, ph);
+      else attention_items<64, 1>(c, layer, aw, ph);
     } else {
-      if (gq == 4) attention_items<128, 4>(c, layer, aw);
-      else if (gq == 2) attention_items<128, 2>(c, layer, aw);
-      else attention_items<128, 1>(c, layer, aw);
+      if (gq == 4) attention_items<128, 4>(c, layer, aw, ph);
+      else if (gq == 2) attention_items<128, 2>(c, layer, aw, ph);
+      else attention_items<128, 1>(c, layer, aw, ph);
     }
   }
   named_bar(kBarAttn, 256);   // the workers' stores, then one release on the phase counter

@@ -54,6 +54,18 @@ def rel_l2(actual: torch.Tensor, expected: torch.Tensor) -> float:
     return float((a - e).norm() / e.norm().clamp_min(1e-30))
 
 
+def untied(top: float, second: float, units: int = 2) -> bool:
+    """True if the two best bf16 logits are more than `units` bf16 units of the larger one apart.  Kernel and oracle
+    each round a logit to bf16 after sums taken in different orders, so either value may land one unit away from the
+    other side's; a gap of two units or less can therefore tie or flip without either side being wrong."""
+    import math
+    top, second = float(top), float(second)
+    if top == 0.0:
+        return False
+    unit = 2.0 ** (math.floor(math.log2(abs(top))) - 7)
+    return top - second > units * unit
+
+
 def bf16_ulps(actual: torch.Tensor, expected: torch.Tensor) -> torch.Tensor:
     """Distance in bf16 units-in-the-last-place of `expected` (both bf16)."""
     a = actual.cpu().view(torch.int16).to(torch.int32)
