@@ -471,8 +471,8 @@ SECONDARY = (("llama-3.2-1b", 32), ("qwen3-0.6b", 16), ("olmoe-1b-7b", 32))
 # DRAM traffic / algorithmic bytes of one qmk_batch_kernel launch where an ncu capture exists (profiles/): the capture of
 # the OLMoE case held 3 of the 16 layers (a few GB on the device); traffic grows with the layers like the algorithmic
 # bytes do, so the ratio is applied to the full step's bytes.
-BATCHED_TRAFFIC_RATIO = {("llama-3.2-1b", 8): (1.014, "profiles/qmk_batch_kernel_step_llama1b_b8.md"),
-                         ("olmoe-1b-7b", 32): (1.006, "profiles/qmk_batch_kernel_step_olmoe_b32_3layers.md (3-layer capture, scaled by bytes)")}
+BATCHED_TRAFFIC_RATIO = {("llama-3.2-1b", 8): (1.012, "profiles/qmk_batch_kernel_step_llama1b_b8.md"),
+                         ("olmoe-1b-7b", 32): (1.009, "profiles/qmk_batch_kernel_step_olmoe_b32_3layers.md (3-layer capture, scaled by bytes)")}
 
 
 def main() -> None:

@@ -92,6 +92,8 @@ def main() -> None:
         m = a.mean(0)
         nbytes = phase_bytes(cfg, kind, T, B, experts)
         total += float(a[:, 0].sum())
+        if kind == "attn":     # no issuer, no stagers: words 3 and 4 of this phase are the key-loop figures printed below
+            m[4:] = 0.0
         print(f"{kind:14s} n={len(rows[kind]):3d} span {m[0] / 1e3:7.2f}  dep {m[1] / 1e3:5.2f}  first-acc {m[2] / 1e3:5.2f}  "
               f"spread {m[3] / 1e3:6.2f}  issuer {m[4] / 1e3:6.2f} {m[5] / 1e3:6.2f} {m[8] / 1e3:6.2f} {m[9] / 1e3:6.2f} {m[10] / 1e3:6.2f}  "
               f"stager {m[6] / 1e3:6.2f} {m[7] / 1e3:6.2f}  "
