@@ -110,10 +110,11 @@ def main() -> None:
         ph = ppl + names.index(args.detail) if args.detail != "lm_head" else ppl * L
         prev = float(t[:, ph - 1, 5].max())
         print(f"# {args.detail}, phase {ph}: per CTA with work, microseconds after the previous phase's last arrival: dependency |"
-              " first accumulator | arrival")
+              " first accumulator | last accumulator | its part read out | count released or all parts counted | tile complete |"
+              " tile epilogue done | arrival")
         for cta in range(t.shape[0]):
             if float(t[cta, ph, 1]) > 0 or args.detail == "attn":
-                v = [float(t[cta, ph, k]) for k in (0, 1, 5)]
+                v = [float(t[cta, ph, k]) for k in (0, 1, 11, 12, 13, 14, 15, 5)]
                 print(f"  cta {cta:3d} " + " ".join(f"{(x - prev) / 1e3:8.2f}" if x > 0 else "       -" for x in v))
 
 

@@ -96,8 +96,11 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
 // satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
 // the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
 // the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival 8 the issuer
-// waiting for a free accumulator, 9 issuing a unit's four MMAs, 10 the commits.  (More stamps inside the epilogue path were
-// measured to cost a fifth of the step at 64 rows with tracing off: the kernel sits at its register cap.)
+// waiting for a free accumulator, 9 issuing a unit's four MMAs, 10 the commits.  Stamps of the CTA's LAST tile part: 11 its
+// accumulator complete, 12 part read out of tensor memory, 13 count released (owner: all parts counted), 14 tile complete
+// in shared memory, 15 tile epilogue done (14 / 15 only on the CTA that finishes the tile).  (Stamps inside the epilogue
+// path were measured to cost a fifth of the step at 64 rows when compiled into the untraced kernel: it sits at its
+// register cap, so they exist in the traced build only.)
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
   if ((kTraceOn && p.trace != nullptr)) p.trace[((size_t)blockIdx.x * (size_t)num_phases(p) + ph) * kTraceSlots + slot] = globaltimer_ns();
 }
@@ -126,12 +129,29 @@ struct Ctx {
   __device__ __forceinline__ bool aborted() const { return ctl[kCAbort] != 0u; }
 };
 
+// A try_wait that lets the hardware park the thread for up to `ns` nanoseconds (it returns at once when the phase
+// completes).  Without the hint the issuing and the producing thread spin through a phase's tail and take issue slots
+// from the epilogue warps on their schedulers: 2 % of the step.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait on an mbarrier phase.  False when the budget expired or the CTA is aborting.
 static __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity, int phase, int detail) {
   if (c.ctl[kCAbort] != 0u) return false;
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
     if ((it & 63u) == 0u) {
       if (c.ctl[kCAbort] != 0u) return false;
       // (twice the budget of a dependency wait: these waits sit downstream of one, which should be the one to report)
@@ -559,8 +579,10 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned short silu_mul(float up, float gate) {
   // fused_mlp_upgate (operations.py:265-282): both products rounded to bf16, SiLU rounded, product rounded
+  // (the quotient is rounded to bf16 right away: the approximate division differs from the exact one in the last fp32
+  // bits only, and unlike it is branch-free, so eight of these interleave in the epilogue)
   const float g = bf16_round(gate);
-  const float sl = bf16_round(g / (1.0f + __expf(-g)));
+  const float sl = bf16_round(__fdividef(g, 1.0f + __expf(-g)));
   return f32_to_bf16_bits(sl * bf16_round(up));
 }
 __device__ __forceinline__ unsigned long long argmax_key(unsigned short bits, int row) {
@@ -851,13 +873,33 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       named_bar(kBarEpi, 128);
       const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
       unsigned char* blk = p.eimg + (size_t)(slot * per + lt) * (size_t)(p.Bpad * 128);
-      for (int b = b0; b < b1; ++b) {
-        float v = 0.f;
-        if (b < B && act_s[b]) {
-          const float g = bf16_round(exch[u * p.exch_stride + b]), up = bf16_round(exch[(64 + u) * p.exch_stride + b]);
-          v = bf16_round((g / (1.0f + __expf(-g))) * up) * wrow[b];
+      // (eight rows at a time, loads / arithmetic / stores in separate passes: the four epilogue warps have a scheduler
+      // each to themselves, so independent chains side by side are the only way to hide instruction latency)
+      const float* grow = exch + u * p.exch_stride;
+      const float* urow = exch + (64 + u) * p.exch_stride;
+      for (int bb = b0; bb < b1; bb += 8) {
+        float g[8], up[8], w[8];
+        bool on[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int b = bb + k;
+          on[k] = (b < B) & (act_s[b] != 0);     // (no short circuit: a branch per row would serialise the loads)
+          g[k] = grow[b];
+          up[k] = urow[b];
+          w[k] = wrow[b];
         }
-        *reinterpret_cast<unsigned short*>(blk + b * 128 + (((u >> 3) ^ (b & 7)) << 4) + (u & 7) * 2) = f32_to_bf16_bits(v);
+        unsigned short bits[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float gr = bf16_round(g[k]);
+          const float v = on[k] ? bf16_round(__fdividef(gr, 1.0f + __expf(-gr)) * bf16_round(up[k])) * w[k] : 0.f;
+          bits[k] = f32_to_bf16_bits(v);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int b = bb + k;
+          *reinterpret_cast<unsigned short*>(blk + b * 128 + (((u >> 3) ^ (b & 7)) << 4) + (u & 7) * 2) = bits[k];
+        }
       }
       break;
     }
@@ -881,32 +923,56 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         const int b = (e >> 4) + 8 * i;
         oldv[i] = (i < nit && in_range && b < B) ? ldcg_u4(p.hidden + (size_t)b * p.H + row) : make_uint4(0, 0, 0, 0);
       }
+      // four items at a time, every pass over all four before the next pass (independent chains side by side: see
+      // kEUpGate); items past the batch carry zeros through the arithmetic and are not stored
 #pragma unroll
-      for (int i = 0; i < kMaxBatch / 8; ++i) {
-        if (i < nit) {
-          const int b = (e >> 4) + 8 * i;
-          const int bb = b < B ? b : 0;
-          const bool act = b < B && act_s[bb] != 0;
-          const uint32_t* ow = reinterpret_cast<const uint32_t*>(&oldv[i]);
-          float nv[8], sq = 0.f;
+      for (int i0 = 0; i0 < kMaxBatch / 8; i0 += 4) {
+        if (i0 < nit) {
+          float add[4][8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float old = (j & 1) ? bf_hi(ow[j >> 1]) : bf_lo(ow[j >> 1]);
-            const float add = act ? bf16_round(exch[(rg * 8 + j) * p.exch_stride + bb]) : 0.f;
-            nv[j] = bf16_round(old + add);
-            sq += nv[j] * nv[j];
+          for (int k = 0; k < 4; ++k) {
+            const int b = (e >> 4) + 8 * (i0 + k);
+            const int bb = b < B ? b : 0;
+            const bool act = (b < B) & (act_s[bb] != 0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float v = exch[(rg * 8 + j) * p.exch_stride + bb];
+              add[k][j] = act ? v : 0.f;
+            }
           }
-          if (in_range && b < B) {
-            uint4 o4;
-            o4.x = pack_bf16x2(nv[0], nv[1]); o4.y = pack_bf16x2(nv[2], nv[3]);
-            o4.z = pack_bf16x2(nv[4], nv[5]); o4.w = pack_bf16x2(nv[6], nv[7]);
-            *reinterpret_cast<uint4*>(p.hidden + (size_t)b * p.H + row) = o4;
-          } else {
-            sq = 0.f;
+          float sq[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int b = (e >> 4) + 8 * (i0 + k);
+            const uint32_t* ow = reinterpret_cast<const uint32_t*>(&oldv[i0 + k]);
+            float nv[8];
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              nv[j] = bf16_round(bf_lo(ow[j >> 1]) + bf16_round(add[k][j]));
+              nv[j + 1] = bf16_round(bf_hi(ow[j >> 1]) + bf16_round(add[k][j + 1]));
+              s0 += nv[j] * nv[j];
+              s1 += nv[j + 1] * nv[j + 1];
+            }
+            sq[k] = 0.f;
+            if (in_range && b < B) {
+              uint4 o4;
+              o4.x = pack_bf16x2(nv[0], nv[1]); o4.y = pack_bf16x2(nv[2], nv[3]);
+              o4.z = pack_bf16x2(nv[4], nv[5]); o4.w = pack_bf16x2(nv[6], nv[7]);
+              *reinterpret_cast<uint4*>(p.hidden + (size_t)b * p.H + row) = o4;
+              sq[k] = s0 + s1;
+            }
           }
 #pragma unroll
-          for (int o = 1; o < 16; o <<= 1) sq += __shfl_xor_sync(kFullMask, sq, o);
-          if (rg == 0 && b < B) p.ss[t * kMaxBatch + b] = sq;
+          for (int o = 1; o < 16; o <<= 1) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) sq[k] += __shfl_xor_sync(kFullMask, sq[k], o);
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int b = (e >> 4) + 8 * (i0 + k);
+            if (rg == 0 && b < B) p.ss[t * kMaxBatch + b] = sq[k];
+          }
         }
       }
       break;
@@ -916,11 +982,32 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       const int unit = t * (kTileRows / 2) + u;
       if (unit < p.I) {
         const int b0 = half * (p.Bpad / 2), b1 = b0 + p.Bpad / 2;
-        for (int b = b0; b < b1 && b < B; ++b) {
-          const unsigned short bits =
-              act_s[b] ? silu_mul(exch[u * p.exch_stride + b], exch[(64 + u) * p.exch_stride + b]) : (unsigned short)0;
-          p.silu_out[(size_t)b * p.I + unit] = bits;
-          *reinterpret_cast<unsigned short*>(p.simg + img_piece(p.Bpad, b, unit) + (unit & 7) * 2) = bits;
+        const float* grow = exch + u * p.exch_stride;
+        const float* urow = exch + (64 + u) * p.exch_stride;
+        for (int bb = b0; bb < b1 && bb < B; bb += 8) {   // eight rows at a time: loads, arithmetic, stores (see kEUpGate)
+          float g[8], up[8];
+          bool on[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int b = bb + k;
+            on[k] = (b < B) & (act_s[b] != 0);
+            g[k] = grow[b];
+            up[k] = urow[b];
+          }
+          unsigned short bits[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const unsigned short v = silu_mul(g[k], up[k]);
+            bits[k] = on[k] ? v : (unsigned short)0;
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int b = bb + k;
+            if (b < B) {
+              p.silu_out[(size_t)b * p.I + unit] = bits[k];
+              *reinterpret_cast<unsigned short*>(p.simg + img_piece(p.Bpad, b, unit) + (unit & 7) * 2) = bits[k];
+            }
+          }
         }
       }
       break;
@@ -928,19 +1015,40 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
     default: {   // LM head: logits and the per-row arg-max (lowest index on ties)
       const int row = t * kTileRows + e;
       if (row < p.vocab) {
-        for (int b = 0; b < B; ++b) {
-          const float v = act_s[b] ? exch[e * p.exch_stride + b] : -1e9f;
-          p.logits[(size_t)b * p.vocab + row] = f32_to_bf16_bits(v);
+        const float* lrow = exch + e * p.exch_stride;
+        for (int bb = 0; bb < B; bb += 8) {      // eight rows at a time: loads, then stores
+          unsigned short bits[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int b = bb + k;
+            const float v = lrow[b];            // (b < Bpad: the padded batch is a multiple of 16)
+            bits[k] = f32_to_bf16_bits(((b < B) & (act_s[b] != 0)) ? v : -1e9f);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (bb + k < B) p.logits[(size_t)(bb + k) * p.vocab + row] = bits[k];
         }
       }
       if (e < B) {
-        unsigned long long best = 0ull;
+        // four independent maxima side by side (the key holds the row, so their maximum is the scan's result)
+        unsigned long long bst[4] = {0ull, 0ull, 0ull, 0ull};
         const int nrow = min(kTileRows, p.vocab - t * kTileRows);
-        for (int r = 0; r < nrow; ++r) {
-          const float v = act_s[e] ? exch[r * p.exch_stride + e] : -1e9f;
-          const unsigned long long key = argmax_key(f32_to_bf16_bits(v), p.vocab_offset + t * kTileRows + r);
-          best = key > best ? key : best;
+        const bool on = act_s[e] != 0;
+        const float* col = exch + e;
+        for (int r0 = 0; r0 < nrow; r0 += 4) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int r = r0 + k;
+            if (r < nrow) {
+              const float v = on ? col[r * p.exch_stride] : -1e9f;
+              const unsigned long long key = argmax_key(f32_to_bf16_bits(v), p.vocab_offset + t * kTileRows + r);
+              bst[k] = key > bst[k] ? key : bst[k];
+            }
+          }
         }
+        unsigned long long best = bst[0] > bst[1] ? bst[0] : bst[1];
+        const unsigned long long b23 = bst[2] > bst[3] ? bst[2] : bst[3];
+        best = best > b23 ? best : b23;
         atomicMax(p.argmax_key + e, best);
       }
       break;
@@ -997,6 +1105,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const unsigned buf = sg & 1u;
     const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
     if (e == 0 && u == lo) trace_put(p, ph, 1);
+    if (kTraceOn && e == 0) trace_put(p, ph, 11);   // (overwritten per tile: the CTA's last accumulator)
     // accumulator of a split tile: the slot of the owner (a CTA owns the first unit of at most one split tile, so the
     // slot is the tile's alone)
     const int c_first = unit_owner(U, G, t * d.KB);
@@ -1023,6 +1132,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     // (no fence per thread: the barrier orders the group's additions before thread 0's release on the tile's count,
     // which is cumulative over what the barrier made visible to it)
     named_bar(kBarEpi, 128);
+    if (kTraceOn && e == 0) trace_put(p, ph, 12);   // the part is in shared memory or on its way to the tile's accumulator
     if (e == 0) {
       unsigned fin = 0u;
       if (ok && !c.aborted()) {
@@ -1039,6 +1149,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
         }
       }
       c.ctl[kCFlagEpi] = fin;
+      if (kTraceOn) trace_put(p, ph, 13);           // count released, or (owner) all parts counted
     }
     named_bar(kBarEpi, 128);
     const bool run = c.ctl[kCFlagEpi] != 0u;
@@ -1054,8 +1165,10 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
+    if (kTraceOn && e == 0 && run) trace_put(p, ph, 14);
     if (run) epilogue_tile(c, ph, kind, t, e);
     named_bar(kBarEpi, 128);           // the exchange tile is free again
+    if (kTraceOn && e == 0 && run) trace_put(p, ph, 15);
     u = u_end;
   }
 }
