@@ -1013,43 +1013,73 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
       break;
     }
     default: {   // LM head: logits and the per-row arg-max (lowest index on ties)
-      const int row = t * kTileRows + e;
-      if (row < p.vocab) {
-        const float* lrow = exch + e * p.exch_stride;
-        for (int bb = 0; bb < B; bb += 8) {      // eight rows at a time: loads, then stores
-          unsigned short bits[8];
+      const int nrow = min(kTileRows, p.vocab - t * kTileRows);
+      if (p.vocab % 8 == 0 && (reinterpret_cast<unsigned long long>(p.logits) & 15ull) == 0ull) {
+        // a thread owns (sequence b, eight consecutive vocabulary rows): one 16-byte store per item, as in the residual
+        // epilogue (the tile's rows end on a multiple of eight)
+        const int rg = e & 15, r0 = rg * 8;
+        const int nit = (B + 7) / 8;
+        if (r0 < nrow) {
+#pragma unroll 2
+          for (int i = 0; i < nit; ++i) {
+            const int b = (e >> 4) + 8 * i;
+            const int bb = b < B ? b : 0;
+            const bool on = (b < B) & (act_s[bb] != 0);
+            float v[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int b = bb + k;
-            const float v = lrow[b];            // (b < Bpad: the padded batch is a multiple of 16)
-            bits[k] = f32_to_bf16_bits(((b < B) & (act_s[b] != 0)) ? v : -1e9f);
+            for (int j = 0; j < 8; ++j) v[j] = exch[(r0 + j) * p.exch_stride + bb];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = on ? v[j] : -1e9f;
+            uint4 o4;
+            o4.x = pack_bf16x2(v[0], v[1]); o4.y = pack_bf16x2(v[2], v[3]);
+            o4.z = pack_bf16x2(v[4], v[5]); o4.w = pack_bf16x2(v[6], v[7]);
+            if (b < B) *reinterpret_cast<uint4*>(p.logits + (size_t)b * p.vocab + t * kTileRows + r0) = o4;
           }
+        }
+      } else {
+        const int row = t * kTileRows + e;
+        if (row < p.vocab) {
+          const float* lrow = exch + e * p.exch_stride;
+          for (int bb = 0; bb < B; bb += 8) {      // eight rows at a time: loads, then stores
+            unsigned short bits[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            if (bb + k < B) p.logits[(size_t)(bb + k) * p.vocab + row] = bits[k];
+            for (int k = 0; k < 8; ++k) {
+              const int b = bb + k;
+              const float v = lrow[b];            // (b < Bpad: the padded batch is a multiple of 16)
+              bits[k] = f32_to_bf16_bits(((b < B) & (act_s[b] != 0)) ? v : -1e9f);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              if (bb + k < B) p.logits[(size_t)(bb + k) * p.vocab + row] = bits[k];
+          }
         }
       }
-      if (e < B) {
-        // four independent maxima side by side (the key holds the row, so their maximum is the scan's result)
-        unsigned long long bst[4] = {0ull, 0ull, 0ull, 0ull};
-        const int nrow = min(kTileRows, p.vocab - t * kTileRows);
-        const bool on = act_s[e] != 0;
-        const float* col = exch + e;
-        for (int r0 = 0; r0 < nrow; r0 += 4) {
+      {
+        // arg-max: all 128 threads, 8 / 4 / 2 of them per sequence (a share of the tile's rows each, four independent
+        // maxima side by side; the key holds the row, so the maximum of the maxima is the scan's result)
+        const int lg = p.Bpad <= 16 ? 3 : (p.Bpad <= 32 ? 2 : 1);
+        const int nb = kTileRows >> lg;              // sequences side by side = rows per thread: 16 / 32 / 64
+        const int b = e & (nb - 1), part = e >> (7 - lg);
+        if (b < B) {
+          unsigned long long bst[4] = {0ull, 0ull, 0ull, 0ull};
+          const bool on = act_s[b] != 0;
+          const float* col = exch + b;
+          const int r_lo = part * nb, r_hi = min(nrow, r_lo + nb);
+          for (int r0 = r_lo; r0 < r_hi; r0 += 4) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int r = r0 + k;
-            if (r < nrow) {
-              const float v = on ? col[r * p.exch_stride] : -1e9f;
+            for (int k = 0; k < 4; ++k) {
+              const int r = r0 + k;
+              const float x = col[min(r, r_hi - 1) * p.exch_stride];
+              const float v = on ? x : -1e9f;
               const unsigned long long key = argmax_key(f32_to_bf16_bits(v), p.vocab_offset + t * kTileRows + r);
-              bst[k] = key > bst[k] ? key : bst[k];
+              bst[k] = (r < r_hi && key > bst[k]) ? key : bst[k];
             }
           }
+          unsigned long long best = bst[0] > bst[1] ? bst[0] : bst[1];
+          const unsigned long long b23 = bst[2] > bst[3] ? bst[2] : bst[3];
+          best = best > b23 ? best : b23;
+          if (r_lo < nrow) atomicMax(p.argmax_key + b, best);
         }
-        unsigned long long best = bst[0] > bst[1] ? bst[0] : bst[1];
-        const unsigned long long b23 = bst[2] > bst[3] ? bst[2] : bst[3];
-        best = best > b23 ? best : b23;
-        atomicMax(p.argmax_key + e, best);
       }
       break;
     }
@@ -1105,7 +1135,8 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const unsigned buf = sg & 1u;
     const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
     if (e == 0 && u == lo) trace_put(p, ph, 1);
-    if (kTraceOn && e == 0) trace_put(p, ph, 11);   // (overwritten per tile: the CTA's last accumulator)
+    const bool stamp = kTraceOn && e == 0 && u_end == hi;   // (a read of the global timer costs about a microsecond: last part only)
+    if (stamp) trace_put(p, ph, 11);
     // accumulator of a split tile: the slot of the owner (a CTA owns the first unit of at most one split tile, so the
     // slot is the tile's alone)
     const int c_first = unit_owner(U, G, t * d.KB);
@@ -1132,7 +1163,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     // (no fence per thread: the barrier orders the group's additions before thread 0's release on the tile's count,
     // which is cumulative over what the barrier made visible to it)
     named_bar(kBarEpi, 128);
-    if (kTraceOn && e == 0) trace_put(p, ph, 12);   // the part is in shared memory or on its way to the tile's accumulator
+    if (stamp) trace_put(p, ph, 12);   // the part is in shared memory or on its way to the tile's accumulator
     if (e == 0) {
       unsigned fin = 0u;
       if (ok && !c.aborted()) {
@@ -1149,7 +1180,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
         }
       }
       c.ctl[kCFlagEpi] = fin;
-      if (kTraceOn) trace_put(p, ph, 13);           // count released, or (owner) all parts counted
+      if (stamp) trace_put(p, ph, 13);           // count released, or (owner) all parts counted
     }
     named_bar(kBarEpi, 128);
     const bool run = c.ctl[kCFlagEpi] != 0u;
@@ -1165,10 +1196,10 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
-    if (kTraceOn && e == 0 && run) trace_put(p, ph, 14);
+    if (stamp && run) trace_put(p, ph, 14);
     if (run) epilogue_tile(c, ph, kind, t, e);
     named_bar(kBarEpi, 128);           // the exchange tile is free again
-    if (kTraceOn && e == 0 && run) trace_put(p, ph, 15);
+    if (stamp && run) trace_put(p, ph, 15);
     u = u_end;
   }
 }

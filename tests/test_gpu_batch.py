@@ -262,6 +262,67 @@ def whole_steps(env, n_steps, first_pos, prompts, what, untied_floor=0.4):
     g.token_in = None
 
 
+def pair_walk(env, positions, active):
+    """Two phases per launch, from identical inputs: a residual projection and the normalised projection behind it (O-proj ->
+    up/gate, down -> the next layer's QKV, the last down -> LM head).  The second phase then works from what the first
+    one's epilogue left on the device (residual stream, sums of squares for the RMSNorm) behind the phase counter, where
+    the per-op walk gives every phase the oracle's inputs."""
+    from qimeng_megakernel_b200.model_config import LlamaConfig
+    st, g, mk, cfg = env.st, env.g, env.mk, env.cfg
+    LlamaConfig.update_from_dict(cfg)
+    L = cfg["num_hidden_layers"]
+    st.position_ids, st.active_mask = list(positions), [bool(a) for a in active]
+    nb = env.B or 1
+    act = [b for b in range(nb) if active[b]]
+    bh = fo._bh
+    for layer in range(L):
+        what = f"layer {layer} pos {positions}"
+        fo.qkv_rope(st, layer)
+        fo.decode_attention(st, layer)
+        U.push_state(st, g); h_in = st.hidden_states.clone()
+        fo.oproj_residual(st, layer); fo.mlp_upgate(st, layer)
+        mk.run_phases(g, layer * 5 + 2, layer * 5 + 4, 1)
+        assert_op_close(g.hidden_states, st.hidden_states, f"o-proj hidden (pair) {what}", h_in)
+        assert_op_close(g.silu_out, st.silu_out, f"silu_out behind o-proj {what}")
+        U.push_state(st, g); h_in = st.hidden_states.clone()
+        fo.mlp_down_residual(st, layer)
+        if layer + 1 < L:
+            fo.qkv_rope(st, layer + 1)
+            mk.run_phases(g, layer * 5 + 4, layer * 5 + 6, 1)
+            assert_op_close(g.hidden_states, st.hidden_states, f"down hidden (pair) {what}", h_in)
+            for b in act:
+                assert_op_close(bh(g.q_post_rope)[b], bh(st.q_post_rope)[b], f"q_post_rope behind down, row {b} {what}")
+                assert_op_close(g.k_cache[layer + 1, b, positions[b]], st.k_cache[layer + 1, b, positions[b]], f"k behind down, row {b} {what}")
+                assert_op_close(g.v_cache[layer + 1, b, positions[b]], st.v_cache[layer + 1, b, positions[b]], f"v behind down, row {b} {what}")
+            # (the oracle has now run layer + 1's QKV: the loop's own call repeats it from the same hidden state)
+        else:
+            fo.lm_head(st)
+            mk.run_phases(g, layer * 5 + 4, layer * 5 + 6, 1)
+            assert_op_close(g.hidden_states, st.hidden_states, f"down hidden (pair) {what}", h_in)
+            assert_op_close(g.logits, st.logits, f"logits behind the last down {what}")
+    mk.check_status()
+
+
+@pytest.mark.parametrize("batch", [8, 32])
+def test_phase_pairs_from_identical_inputs(small_config, batch):
+    """Llama layer shape, 2 layers: the pairs of pair_walk at ragged positions over a filled cache, one finished row."""
+    _need_gpu()
+    from qimeng_megakernel_b200 import synthetic
+    env = Env(small_config, batch, 320, seed=4321)
+    try:
+        gen = torch.Generator().manual_seed(7 + batch)
+        k, v = synthetic.random_kv_rows(small_config, 320, seed=batch, batch=batch, std=0.5)
+        for s_ in (env.st, env.st32):
+            s_.k_cache.copy_(k); s_.v_cache.copy_(v)
+        embed_rows(env.st, random_tokens(env.cfg, batch, 70 + batch))
+        positions = [int(x) for x in torch.randint(0, 300, (batch,), generator=gen)]
+        active = [1] * batch
+        active[2] = 0
+        pair_walk(env, positions, active)
+    finally:
+        env.close()
+
+
 @pytest.mark.parametrize("batch", [32, 64])
 def test_llama_layer_shape_large_batches(small_config, batch):
     """The Llama-3.2-1B layer shape (hidden 2048, 32 / 8 heads of 64, SwiGLU 8192; 2 layers) at the batch sizes of the
