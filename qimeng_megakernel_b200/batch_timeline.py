@@ -99,6 +99,18 @@ def main() -> None:
               f"stager {m[6] / 1e3:6.2f} {m[7] / 1e3:6.2f}  "
               f"| {nbytes / 1e6:9.2f} MB -> {nbytes / float(m[0]) :8.1f} GB/s  (phase total {float(a[:, 0].sum()) / 1e3:8.1f} us)")
     print(f"step total {total / 1e3:.1f} us")
+    print("# tail of a CTA's last tile part, mean over layers and over the CTAs that have the figure, microseconds: last accumulator"
+          " to arrival | part read out of tensor memory | count released or all parts counted | sum read back | tile epilogue")
+    for kind in names + ("lm_head",):
+        if kind == "attn":
+            continue
+        phs = [ph for ph in range(nph) if ("lm_head" if ph == ppl * L else names[ph % ppl]) == kind]
+        cols = []
+        for k in (12, 13, 14, 15):
+            x = torch.cat([t[:, ph, k] for ph in phs])
+            cols.append(float(x[x > 0].mean()) / ghz / 1e3 if bool((x > 0).any()) else 0.0)
+        la = torch.cat([(t[:, ph, 5] - t[:, ph, 11])[t[:, ph, 11] > 0] for ph in phs])
+        print(f"{kind:14s} {float(la.mean()) / 1e3:6.2f} | " + " ".join(f"{x:6.2f}" for x in cols))
     k = names.index("attn")
     loop = torch.stack([t[:, l * ppl + k, 3] for l in range(L)]).mean(0) / ghz / 1e3     # us per CTA (warp 0's last item)
     keys = torch.stack([t[:, l * ppl + k, 4] for l in range(L)]).mean(0)
@@ -110,12 +122,14 @@ def main() -> None:
         ph = ppl + names.index(args.detail) if args.detail != "lm_head" else ppl * L
         prev = float(t[:, ph - 1, 5].max())
         print(f"# {args.detail}, phase {ph}: per CTA with work, microseconds after the previous phase's last arrival: dependency |"
-              " first accumulator | last accumulator | its part read out | count released or all parts counted | tile complete |"
-              " tile epilogue done | arrival")
+              " first accumulator | last accumulator | arrival; then durations of the last tile part: read out of tensor memory |"
+              " count released or all parts counted | sum read back | tile epilogue")
         for cta in range(t.shape[0]):
             if float(t[cta, ph, 1]) > 0 or args.detail == "attn":
-                v = [float(t[cta, ph, k]) for k in (0, 1, 11, 12, 13, 14, 15, 5)]
-                print(f"  cta {cta:3d} " + " ".join(f"{(x - prev) / 1e3:8.2f}" if x > 0 else "       -" for x in v))
+                v = [float(t[cta, ph, k]) for k in (0, 1, 11, 5)]
+                d = [float(t[cta, ph, k]) / ghz / 1e3 for k in (12, 13, 14, 15)]
+                print(f"  cta {cta:3d} " + " ".join(f"{(x - prev) / 1e3:8.2f}" if x > 0 else "       -" for x in v) + "   " +
+                      " ".join(f"{x:6.2f}" if x > 0 else "     -" for x in d))
 
 
 if __name__ == "__main__":

@@ -63,7 +63,7 @@ __device__ __forceinline__ void mma_bf16_add(uint32_t d_tmem, uint64_t da, uint6
 // a multiple of 2^-36, finer than fp32 resolves above 2^-12 -- is the same whatever order they arrive in, and two runs
 // of a step give the same bits.
 constexpr float kFixScale = 68719476736.0f;              // 2^36
-constexpr double kFixInv = 1.0 / 68719476736.0;
+constexpr float kFixInv = 1.0f / 68719476736.0f;       // (a power of two: the product is exact)
 __device__ __forceinline__ long long to_fixed(float v) { return __float2ll_rn(v * kFixScale); }
 __device__ __forceinline__ void red_add_s64(long long* addr, long long v) {
   asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
@@ -96,9 +96,9 @@ static __device__ __noinline__ void report(const BParams& p, int code, int warp,
 // satisfied (stagers / attention), 1 the CTA's first accumulator of the phase is complete, 2 the epilogue group enters
 // the phase, 5 the CTA arrives at the phase's counter.  Cycle sums over the phase's units: 3 / 4 the issuer waiting for
 // the weights / the activations of a unit; 6 / 7 stager warp 0 waiting for a free slot / from there to its arrival 8 the issuer
-// waiting for a free accumulator, 9 issuing a unit's four MMAs, 10 the commits.  Stamps of the CTA's LAST tile part: 11 its
-// accumulator complete, 12 part read out of tensor memory, 13 count released (owner: all parts counted), 14 tile complete
-// in shared memory, 15 tile epilogue done (14 / 15 only on the CTA that finishes the tile).  (Stamps inside the epilogue
+// waiting for a free accumulator, 9 issuing a unit's four MMAs, 10 the commits.  The CTA's LAST tile part: 11 stamp of its
+// accumulator complete, then cycle counts: 12 part read out of tensor memory, 13 count released (owner: all parts counted),
+// 14 sum read back, 15 tile epilogue (14 / 15 only on the CTA that finishes the tile).  (Stamps inside the epilogue
 // path were measured to cost a fifth of the step at 64 rows when compiled into the untraced kernel: it sits at its
 // register cap, so they exist in the traced build only.)
 __device__ __forceinline__ void trace_put(const BParams& p, int ph, int slot) {
@@ -963,15 +963,23 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
               sq[k] = s0 + s1;
             }
           }
-#pragma unroll
-          for (int o = 1; o < 16; o <<= 1) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) sq[k] += __shfl_xor_sync(kFullMask, sq[k], o);
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int b = (e >> 4) + 8 * (i0 + k);
-            if (rg == 0 && b < B) p.ss[t * kMaxBatch + b] = sq[k];
+          // The four sums over the sixteen row groups with five shuffles instead of sixteen (a shuffle costs the
+          // epilogue warp ~0.1 us here): lanes 8 apart swap two of the four sums, lanes 4 apart one of the remaining
+          // two, then the four lanes that hold the same item add up.  Item 2 * (bit 3 of rg) + (bit 2 of rg) ends in
+          // the lane.
+          {
+            const bool h8 = (rg & 8) != 0, h4 = (rg & 4) != 0;
+            float k0 = h8 ? sq[2] : sq[0], k1 = h8 ? sq[3] : sq[1];
+            const float s0 = h8 ? sq[0] : sq[2], s1 = h8 ? sq[1] : sq[3];
+            k0 += __shfl_xor_sync(kFullMask, s0, 8);
+            k1 += __shfl_xor_sync(kFullMask, s1, 8);
+            float kk = h4 ? k1 : k0;
+            const float ss = h4 ? k0 : k1;
+            kk += __shfl_xor_sync(kFullMask, ss, 4);
+            kk += __shfl_xor_sync(kFullMask, kk, 2);
+            kk += __shfl_xor_sync(kFullMask, kk, 1);
+            const int b = (e >> 4) + 8 * (i0 + (h8 ? 2 : 0) + (h4 ? 1 : 0));
+            if ((rg & 3) == 0 && b < B) p.ss[t * kMaxBatch + b] = kk;
           }
         }
       }
@@ -1135,7 +1143,9 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     const unsigned buf = sg & 1u;
     const bool ok = __all_sync(kFullMask, mbar_wait(c, c.acc_full(buf), (sg >> 1) & 1u, ph, 6));
     if (e == 0 && u == lo) trace_put(p, ph, 1);
-    const bool stamp = kTraceOn && e == 0 && u_end == hi;   // (a read of the global timer costs about a microsecond: last part only)
+    // (cycle counts, not stamps: a read of the global timer costs about a microsecond, five of them distorted the tail)
+    const bool stamp = kTraceOn && e == 0 && u_end == hi && p.trace != nullptr;
+    long long tk = stamp ? clock64() : 0;
     if (stamp) trace_put(p, ph, 11);
     // accumulator of a split tile: the slot of the owner (a CTA owns the first unit of at most one split tile, so the
     // slot is the tile's alone)
@@ -1163,7 +1173,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
     // (no fence per thread: the barrier orders the group's additions before thread 0's release on the tile's count,
     // which is cumulative over what the barrier made visible to it)
     named_bar(kBarEpi, 128);
-    if (stamp) trace_put(p, ph, 12);   // the part is in shared memory or on its way to the tile's accumulator
+    if (stamp) { const long long n = clock64(); trace_val(p, ph, 12, (unsigned long long)(n - tk)); tk = n; }   // part read out of tensor memory
     if (e == 0) {
       unsigned fin = 0u;
       if (ok && !c.aborted()) {
@@ -1180,7 +1190,7 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
         }
       }
       c.ctl[kCFlagEpi] = fin;
-      if (stamp) trace_put(p, ph, 13);           // count released, or (owner) all parts counted
+      if (stamp) { const long long n = clock64(); trace_val(p, ph, 13, (unsigned long long)(n - tk)); tk = n; }   // count released, or (owner) all parts counted
     }
     named_bar(kBarEpi, 128);
     const bool run = c.ctl[kCFlagEpi] != 0u;
@@ -1192,14 +1202,14 @@ __device__ __forceinline__ void epilogue_phase(const Ctx& c, int ph, int kind, u
 #pragma unroll
         for (int j = 0; j < 16; ++j) x[j] = exch_zero_s64(slot + (size_t)(ch * 16 + j) * kTileRows + r);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[ch * 16 + j] = (float)((double)(x[j] + to_fixed(o[ch * 16 + j])) * kFixInv);
+        for (int j = 0; j < 16; ++j) o[ch * 16 + j] = __ll2float_rn(x[j] + to_fixed(o[ch * 16 + j])) * kFixInv;   // (no fp64: its rate made this loop the read-back's cost)
       }
     }
     named_bar(kBarEpi, 128);           // the tile is complete in shared memory (or nobody runs)
-    if (stamp && run) trace_put(p, ph, 14);
+    if (stamp && run) { const long long n = clock64(); trace_val(p, ph, 14, (unsigned long long)(n - tk)); tk = n; }   // sum read back (split tiles)
     if (run) epilogue_tile(c, ph, kind, t, e);
     named_bar(kBarEpi, 128);           // the exchange tile is free again
-    if (stamp && run) trace_put(p, ph, 15);
+    if (stamp && run) trace_val(p, ph, 15, (unsigned long long)(clock64() - tk));                             // tile epilogue
     u = u_end;
   }
 }
