@@ -923,6 +923,35 @@ __device__ __forceinline__ void epilogue_tile(const Ctx& c, int ph, int kind, in
         const int b = (e >> 4) + 8 * i;
         oldv[i] = (i < nit && in_range && b < B) ? ldcg_u4(p.hidden + (size_t)b * p.H + row) : make_uint4(0, 0, 0, 0);
       }
+      if (nit == 1) {
+        // up to eight sequences: one item per thread (the four-item pass below would carry three empty ones: measured
+        // 4.0 us against 2.8 us for this path)
+        const int b = e >> 4;
+        const int bb = b < B ? b : 0;
+        const bool act = (b < B) & (act_s[bb] != 0);
+        const uint32_t* ow = reinterpret_cast<const uint32_t*>(&oldv[0]);
+        float nv[8], s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float a0 = exch[(rg * 8 + j) * p.exch_stride + bb], a1 = exch[(rg * 8 + j + 1) * p.exch_stride + bb];
+          nv[j] = bf16_round(bf_lo(ow[j >> 1]) + bf16_round(act ? a0 : 0.f));
+          nv[j + 1] = bf16_round(bf_hi(ow[j >> 1]) + bf16_round(act ? a1 : 0.f));
+          s0 += nv[j] * nv[j];
+          s1 += nv[j + 1] * nv[j + 1];
+        }
+        float sq = 0.f;
+        if (in_range && b < B) {
+          uint4 o4;
+          o4.x = pack_bf16x2(nv[0], nv[1]); o4.y = pack_bf16x2(nv[2], nv[3]);
+          o4.z = pack_bf16x2(nv[4], nv[5]); o4.w = pack_bf16x2(nv[6], nv[7]);
+          *reinterpret_cast<uint4*>(p.hidden + (size_t)b * p.H + row) = o4;
+          sq = s0 + s1;
+        }
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) sq += __shfl_xor_sync(kFullMask, sq, o);
+        if (rg == 0 && b < B) p.ss[t * kMaxBatch + b] = sq;
+        break;
+      }
       // four items at a time, every pass over all four before the next pass (independent chains side by side: see
       // kEUpGate); items past the batch carry zeros through the arithmetic and are not stored
 #pragma unroll
