@@ -5,7 +5,8 @@
 //   warp 1      issuer     one lane issues tcgen05.mma (M = 128 weight rows, N = padded batch, K = 16)
 //   warps 2-5   epilogue   read accumulators from tensor memory, finish the phase's arithmetic
 //   warps 6-9   stagers    build the activation operand ([batch, 64] bf16, RMSNorm applied) in shared memory
-// In the attention phase warps 2-9 are eight attention workers.
+// In the attention phase warps 2-9 are eight attention workers: one (sequence, kv head, key range) item per warp, scores
+// and P.V on the tensor pipe with warp-level mma.sync (the query heads of the kv head are the rows of a 16 x 8 tile).
 //
 // Every projection is a stream-K GEMM  out[b, n] = sum_k X[b, k] * W[n, k]:  the (row tile, k-block)
 // units of a phase, 128 x 64 weights = 16 KiB each, are dealt to the CTAs as equal contiguous ranges,
