@@ -333,12 +333,11 @@ int qmkb_launch(qmk_batch_ctx* c, const qmk_state_ptrs* st, const qmkb_launch_ar
   p.aimg = c->aimg;
   p.simg = c->simg;
   p.img_done = c->img_done;
+  // (measured choices: the pre-pass pays from 32 padded sequences on and, in the LM head, when a CTA walks the k-blocks at
+  // least twice; O-proj / down-proj read the images their producers left)
   p.pre_bpad = 32;
   p.pre_lm_units = 2 * (d.hidden_size / kBlockK);
   p.dense_img = 1;
-  if (const char* v = getenv("QMK_PRE_BPAD")) p.pre_bpad = atoi(v);
-  if (const char* v = getenv("QMK_PRE_LM")) p.pre_lm_units = atoi(v);
-  if (const char* v = getenv("QMK_DENSE_IMG")) p.dense_img = atoi(v);
   const bool moe = d.arch == QMK_ARCH_MOE;
   p.E = moe ? d.num_experts : 0;
   p.topk = moe ? d.num_experts_per_tok : 0;
