@@ -311,3 +311,17 @@ def test_tensor_parallel_slices_add_up():
         tp.shard_config(cfg, 0, 8)          # 4 KV heads over 8 ranks
     with pytest.raises(ValueError):
         tp.shard_config(dict(cfg, num_experts=8), 0, 2)
+
+
+def test_untied_rule_counts_in_bf16_units():
+    """The arg-max tests skip rows whose two best bf16 logits are within two bf16 units of each other: the unit is the
+    spacing of bf16 at the larger value (2^(e - 7) for a value in [2^e, 2^(e+1))), not a fixed fraction of it."""
+    from tests import _util as U
+    # at 3.125 (in [2, 4)) the unit is 2^-6 = 0.015625
+    assert not U.untied(3.125, 3.125 - 2 * 0.015625)        # exactly two units apart: either side may round across
+    assert U.untied(3.125, 3.125 - 3 * 0.015625)
+    # at 1.0 the unit is 2^-7; just below a power of two the criterion uses the spacing at the top value
+    assert not U.untied(1.0, 1.0 - 2 * 2.0 ** -7)
+    assert U.untied(1.0, 1.0 - 2.5 * 2.0 ** -7)
+    assert not U.untied(0.0, -1.0)                           # (no logit scale to speak of)
+    assert U.untied(-2.0, -2.5)                              # negative logits: the unit of |top|
