@@ -6,6 +6,7 @@
 // (3) the partial segments of a tile are exactly the CTAs unit_owner(first unit) .. unit_owner(last unit), which
 // is what the tile's ticket counts and what the last arriver sums; (4) the split-KV plan keeps its bounds.
 #include <cstdio>
+#include <algorithm>
 #include <map>
 #include <set>
 #include <vector>
@@ -96,6 +97,33 @@ int main() {
         if (ck < 32 || ck % 32 != 0) return fail("ck", Tmax, seqs, ck);
         if (nch < 1 || nch > kMaxSplits || (long long)nch * ck < Tmax) return fail("nch", Tmax, seqs, nch);
         if ((long long)seqs * nch > (long long)NW + seqs && nch > 1) return fail("items bound", Tmax, seqs, nch);
+      }
+  // The attention key loop's walk over a key range (csrc/qmk_batch_device.cuh, attention_items): blocks of 32 keys at
+  // head_dim 64 and 8 at 128; lane (g, t) scores keys kb + 8j + 2t and + 1 of n-tile j, loads K rows kb + 8j + g and V rows
+  // kb + 8ks + 2t (+ 1), clamped to the last row of the range.  Every key of the range must be scored exactly once, and
+  // no load may leave the range.
+  for (int hd : {64, 128})
+    for (int k_lo : {0, 32, 96})
+      for (int len : {1, 2, 7, 8, 9, 31, 32, 33, 64, 100, 160}) {
+        const int k_hi = k_lo + len, NT = hd == 64 ? 4 : 1, BK = NT * 8;
+        std::map<int, int> scored;
+        for (int kb = k_lo; kb < k_hi; kb += BK)
+          for (int lane = 0; lane < 32; ++lane) {
+            const int g = lane >> 2, t = lane & 3;
+            for (int j = 0; j < NT; ++j) {
+              const int krow = std::min(kb + 8 * j + g, k_hi - 1);
+              if (krow < k_lo || krow >= k_hi) return fail("K row leaves the range", hd, k_lo, krow);
+              for (int e = 0; e < 2; ++e) {
+                const int vrow = std::min(kb + 8 * j + 2 * t + e, k_hi - 1);
+                if (vrow < k_lo || vrow >= k_hi) return fail("V row leaves the range", hd, k_lo, vrow);
+                const int key = kb + 8 * j + 2 * t + e;
+                if (g == 0 && key < k_hi) ++scored[key];      // (the four lanes t of a head hold the block's 8 NT scores)
+              }
+            }
+          }
+        if ((int)scored.size() != len) return fail("keys scored", hd, k_lo, (int)scored.size());
+        for (const auto& kv : scored)
+          if (kv.second != 1 || kv.first < k_lo) return fail("key scored twice", hd, kv.first, kv.second);
       }
   std::printf("batch schedule ok\n");
   return 0;
