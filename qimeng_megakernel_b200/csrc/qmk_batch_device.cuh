@@ -580,7 +580,8 @@ __device__ __forceinline__ void stage_phase(const Ctx& c, int ph, int kind, int 
 __device__ __forceinline__ unsigned short silu_mul(float up, float gate) {
   // fused_mlp_upgate (operations.py:265-282): both products rounded to bf16, SiLU rounded, product rounded
   // (the quotient is rounded to bf16 right away: the approximate division differs from the exact one in the last fp32
-  // bits only, and unlike it is branch-free, so eight of these interleave in the epilogue)
+  // bits only, and unlike it is branch-free, so eight of these interleave in the epilogue; the reference builds its kernels
+  // with --use_fast_math: .../A100/multi_batch/decode_kernel/Makefile:39)
   const float g = bf16_round(gate);
   const float sl = bf16_round(__fdividef(g, 1.0f + __expf(-g)));
   return f32_to_bf16_bits(sl * bf16_round(up));
